@@ -1,0 +1,174 @@
+/*
+ * llmb200_kernels.h -- thin C ABI over the sm_100a kernels of the decode path.
+ *
+ * Plain pointers and sizes only. Every pointer named d_* is CUDA device memory
+ * on the current device; `stream` is a cudaStream_t passed as void*. Functions
+ * return 0 on success, a positive cudaError_t value when CUDA reports one and
+ * a negative B200_E_* code for rejected arguments. Nothing here allocates
+ * device memory.
+ *
+ * Each launcher states which reference dispatch(es) it stands in for
+ * (src/nn/fast_metal.m line of the metal_enqueue_* function, and the kernel in
+ * shaders/q8_kernels.metal).
+ *
+ * Packed weight layout ("row-sliced"):
+ *   Q8_0  row r = cols int8 quants, then cols/32 binary16 scales; rows are
+ *         row_stride bytes apart, row_stride = round_up(34*cols/32, 16).
+ *   F16   row r = cols binary16 values; row_stride = round_up(2*cols, 16).
+ * Values are exactly those of the reference's 34-byte block stream / half
+ * array; only the placement differs, so that every 16-byte load of a row is
+ * aligned and a warp reads 512 contiguous bytes.
+ */
+#ifndef LLMB200_KERNELS_H
+#define LLMB200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_E_BADARG   (-1)
+#define B200_E_TOOLARGE (-2)
+#define B200_E_STATE    (-3)
+
+#define B200_WT_Q8  0
+#define B200_WT_F16 1
+
+#define B200_MAX_PEERS 8
+
+/* Bytes between consecutive rows of a packed matrix with `cols` columns. */
+size_t b200_packed_row_stride(int wtype, int cols);
+
+/* fp32 [rows, cols] (leading dimension ld floats, device) -> packed Q8_0 rows.
+ * Source row r lands in packed row dst_row0 + r*dst_row_step.
+ * Replaces quantize_row_q8/wmat_create_q8 (src/nn/wmat.c:19-61); bit-exact. */
+int b200_q8_pack(const float *d_src, long long ld, int rows, int cols,
+                 void *d_dst, long long dst_row_stride, int dst_row0, int dst_row_step,
+                 void *stream);
+/* Same for F16 (src/nn/wmat.c:63-75). */
+int b200_f16_pack(const float *d_src, long long ld, int rows, int cols,
+                  void *d_dst, long long dst_row_stride, int dst_row0, int dst_row_step,
+                  void *stream);
+/* Packed Q8_0 rows -> the reference's canonical stream of 34-byte blocks
+ * {u16 d; i8 qs[32]} (src/nn/wmat.c:14-17), rows*cols/32 blocks, row-major. */
+int b200_q8_unpack_blocks(const void *d_packed, long long row_stride, int rows, int cols,
+                          void *d_blocks, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Fused matrix-vector product  y = W . f(x)
+ *
+ * One launch covers what the reference enqueues as rms_norm + q8_matvec /
+ * f16_matvec (+ residual_add, silu_mul / gelu_mul, CPU embedding copy, CPU
+ * argmax): src/nn/fast_metal.m:253-289, 309-341, 428-462 and
+ * src/nn/fast_inference.c:386-392, 469-476.
+ *
+ * Input assembly (in_mode), all in fp32:
+ *   B200_IN_VEC    x = in_vec[cols]
+ *   B200_IN_RESID  h = resid_in + S, S = sum over n_slots of slots[s][0..cols)
+ *                  (if slot_norm_gamma: S <- rmsnorm(S) * slot_norm_gamma first);
+ *                  block 0 stores h to resid_out; x = h
+ *   B200_IN_EMBED  h = emb[tokens[*pos]][0..cols) * emb_scale; stored to
+ *                  resid_out by block 0; x = h
+ * then, if norm_gamma != NULL, x <- x * rsqrt(mean(x^2)+eps) * norm_gamma.
+ *
+ * Output (out_mode):
+ *   B200_OUT_STORE  out[p][out_offset + r] = y[r] for every peer p < n_out
+ *   B200_OUT_GLU    rows come in (gate, up) pairs: out[0][out_offset + r/2] =
+ *                   act(y[r]) * y[r+1], act = SiLU (0) or tanh-GELU (1)
+ * With d_argmax_scratch != NULL (B200_OUT_STORE only) the launch also leaves
+ * the largest y[r] and its row index plus out_offset (first one on ties, as
+ * the reference's argmax) in *d_argmax_val[p] / *d_argmax_idx[p], p < n_argmax_out.
+ *
+ * Tensor-parallel hand-shake (all optional, n_wait = 0 / n_signal = 0 to
+ * disable): before reading `slots` the kernel waits, with an iteration limit,
+ * until wait_flags[i] >= E for i < n_wait, E = *epoch * epoch_mul + epoch_add;
+ * after its last store it writes E into signal_flags[p][signal_index], p < n_signal. A wait
+ * that runs out sets *err = 1 and the kernel carries on without hanging.
+ * ---------------------------------------------------------------------- */
+enum { B200_IN_VEC = 0, B200_IN_RESID = 1, B200_IN_EMBED = 2 };
+enum { B200_OUT_STORE = 0, B200_OUT_GLU = 1 };
+
+typedef struct b200_matvec_args {
+    /* weights */
+    const void *d_w; long long row_stride; int rows, cols, wtype;
+    /* input assembly */
+    int in_mode;
+    const float *d_in_vec;
+    const float *d_resid_in; float *d_resid_out;
+    const float *d_slots; int n_slots; long long slot_stride;   /* floats between slots */
+    const float *d_slot_norm_gamma;
+    const float *d_emb; const int *d_tokens; const int *d_pos; float emb_scale;
+    const float *d_norm_gamma; float eps;
+    /* output */
+    int out_mode, act;
+    float *d_out[B200_MAX_PEERS]; int n_out; long long out_offset;
+    float *d_argmax_scratch;                       /* 2 words per block, or NULL: no argmax */
+    float *d_argmax_val[B200_MAX_PEERS];           /* [0] of each receives the largest y */
+    int   *d_argmax_idx[B200_MAX_PEERS];           /* [0] of each receives its row + out_offset */
+    int    n_argmax_out;
+    /* bookkeeping done by the last block to finish */
+    unsigned *d_ticket;            /* one zero-initialised word; required when any of the below is used */
+    int advance_pos;               /* (*d_pos_rw)++ */
+    int *d_pos_rw;
+    int advance_epoch;             /* *d_epoch_rw = *d_epoch + 1 */
+    unsigned *d_epoch_rw;
+    int *d_next_token; const int *d_prompt_len;   /* tokens[pos+1] = argmax unless pos+1 < *prompt_len */
+    /* tensor-parallel flags */
+    const unsigned *d_wait_flags; int n_wait;
+    unsigned *d_signal_flags[B200_MAX_PEERS]; int n_signal, signal_index;
+    const unsigned *d_epoch; int epoch_mul, epoch_add;   /* flag value = *d_epoch * epoch_mul + epoch_add */
+    int *d_err;
+    /* launch shape: 0 = choose (a multiple of the SM count) */
+    int grid;
+    int use_pdl;                   /* programmatic dependent launch: prefetch weights under the previous kernel's tail */
+} b200_matvec_args;
+
+int b200_matvec(const b200_matvec_args *a, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Decode attention for one new token over an F16 KV cache, split over the
+ * sequence. One launch covers per_head_rms_norm(q), per_head_rms_norm(k),
+ * rope, kv_cache_store and attention of the reference
+ * (src/nn/fast_metal.m:343-426; shaders/q8_kernels.metal:165-331).
+ *
+ *   qkv        fp32 [n_q*hd | n_kv*hd | n_kv*hd] of the new token (unnormalised)
+ *   q/k_gamma  [hd] or NULL (no QK-norm)
+ *   inv_freq   [hd/2] fp32, 1/theta^(2d/hd); angle = pos * inv_freq[d]
+ *   k/v_cache  binary16 [n_kv][max_seq][hd]; row *pos is written by this launch
+ *   out        fp32 [n_q*hd]
+ *   scratch    fp32, b200_attn_scratch_floats(n_q, hd, n_split) floats
+ *   tickets    n_kv zero-initialised words
+ * Keys 0..*pos are attended (no window), scores scaled by 1/sqrt(hd).
+ * ---------------------------------------------------------------------- */
+typedef struct b200_attn_args {
+    const float *d_qkv; const float *d_q_gamma; const float *d_k_gamma; const float *d_inv_freq;
+    void *d_k_cache; void *d_v_cache;
+    float *d_out; float *d_scratch; unsigned *d_tickets;
+    const int *d_pos;
+    int n_q, n_kv, hd, max_seq, n_split;
+    float eps;
+    int use_pdl;
+} b200_attn_args;
+
+size_t b200_attn_scratch_floats(int n_q, int hd, int n_split);
+int    b200_attn_decode(const b200_attn_args *a, void *stream);
+
+/* Last tensor-parallel step of a token: waits for every rank's (value, index)
+ * pair, takes the largest (lowest index on ties), stores it as tokens[pos+1]
+ * unless that position belongs to the prompt, and advances *pos. */
+int b200_tp_argmax_finalize(const float *d_vals, const int *d_idx, int n_ranks,
+                            const unsigned *d_wait_flags, const unsigned *d_epoch,
+                            int epoch_mul, int epoch_add,
+                            int *d_tokens, int *d_pos, const int *d_prompt_len,
+                            unsigned *d_epoch_rw, int *d_err, int use_pdl, void *stream);
+
+/* Number of kernel launches issued through this ABI since the last reset
+ * (what bench.py reports as gpu_launches). */
+unsigned long long b200_launch_count(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMB200_KERNELS_H */

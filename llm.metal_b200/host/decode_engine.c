@@ -1,0 +1,916 @@
+/*
+ * Decode engine of libllmb200 (host side, C): persistent state, the per-token
+ * CUDA graph and the greedy generate loop.
+ *
+ * Stands in for src/nn/fast_inference.c of llm.metal: InferenceState (:58-95),
+ * inference_state_init_common (:171-275), forward_token (:376-467) and
+ * inference_generate (:614-675). What the reference enqueues as 17 (Qwen3) or
+ * 19 (Gemma3) barrier-separated dispatches per layer becomes five launches:
+ *
+ *   qkv     embedding / residual assembly + RMSNorm + fused Q|K|V matvec
+ *   attn    QK-norm + RoPE + KV store + split-sequence attention (F16 cache)
+ *   o       O matvec into this rank's all-reduce slot on every peer
+ *   gateup  slot sum + residual + RMSNorm + interleaved gate/up matvec + SiLU/GELU*up
+ *   down    down matvec into the second all-reduce slot
+ *
+ * and the LM head launch does final norm + matvec + greedy argmax, so the next
+ * token id never leaves the device. The whole token is one CUDA graph whose
+ * nodes are chained by programmatic dependent launch; position, token ids and
+ * the tensor-parallel epoch live in device memory, so the same graph is
+ * replayed for every position.
+ *
+ * Tensor parallelism (one process per GPU): matrices are sliced at upload
+ * (rows of Q/K/V, gate, up, LM head; input columns of O and down; every cut a
+ * multiple of 32, so Q8_0 blocks are those of the unsharded quantisation), the
+ * O and down kernels store their partial vectors straight into every peer's
+ * slot over NVLink and raise a flag, and the consumer kernel sums the slots in
+ * rank order -- the all-reduce is the epilogue of one kernel and the prologue
+ * of the next.
+ */
+#include "internal.h"
+#include "../../include/llmb200_inference.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/stat.h>
+#include <time.h>
+
+typedef struct { void *w; long long stride; int rows, cols; } PackedMat;
+
+typedef struct {
+    PackedMat qkv, o, gateup, down;
+    float *g_input, *g_post_attn, *g_pre_ff, *g_post_ff, *g_qn, *g_kn;
+    float *inv_freq;
+    void *k_cache, *v_cache;
+    int loaded;
+} Layer;
+
+enum { K_QKV = 0, K_ATTN, K_O, K_GATEUP, K_DOWN, K_LM, K_KINDS };
+
+struct InferenceState {
+    int D, Hq, Hkv, hd, IS, V, L, max_seq, use_fp16, wtype;
+    ModelType mt;
+    int tp_rank, tp_size, Hq_l, Hkv_l, IS_l, V_l;
+    float emb_scale;
+    int eos[4], n_eos;
+
+    Layer *layers;
+    PackedMat lm;
+    float *g_final, *emb;
+    int finished;
+    unsigned long long weight_bytes;
+
+    /* activations and scratch (device) */
+    float *resid[2], *qkv, *attn_out, *act, *attn_scratch, *am_scratch;
+    unsigned *attn_tickets, *mv_ticket;
+    int n_split;
+
+    /* control words (device): pos, prompt_len, err, epoch, tokens[max_seq+2] */
+    int *d_pos, *d_prompt_len, *d_err, *d_tokens;
+    unsigned *d_epoch;
+
+    /* all-reduce region, shared with the peers */
+    char *comm;
+    size_t comm_bytes, off_slots_o, off_slots_dn, off_flags, off_am_val, off_am_idx, off_logits;
+    char *peer[B200_MAX_PEERS];
+    int connected;
+
+    /* host side */
+    float *h_logits;
+    int *h_tok;              /* pinned ring for generated ids */
+    int *h_ctl;              /* pinned staging for control writes */
+    cudaEvent_t tok_ev[4];
+    cudaEvent_t ev_a, ev_b;
+    cudaGraphExec_t g_full, g_nolm;
+    int use_pdl;
+    int cur_len;
+    double last_decode_ms, last_prefill_ms;
+    int last_n_decoded;
+
+    /* instrumentation */
+    cudaEvent_t *prof_ev;
+    int prof_n, prof_cap, prof_on;
+    int *prof_kind;
+};
+
+static int g_tp_rank = -1, g_tp_size = -1;
+
+int llmb200_set_tp(int rank, int world)
+{
+    if (world < 1 || world > B200_MAX_PEERS || rank < 0 || rank >= world) return B200_E_BADARG;
+    g_tp_rank = rank; g_tp_size = world;
+    return 0;
+}
+
+static void tp_from_env(int *rank, int *world)
+{
+    *rank = 0; *world = 1;
+    if (g_tp_size > 0) { *rank = g_tp_rank; *world = g_tp_size; return; }
+    const char *w = getenv("LLMB200_TP_SIZE"), *r = getenv("LLMB200_TP_RANK");
+    if (w && r && atoi(w) >= 1 && atoi(w) <= B200_MAX_PEERS && atoi(r) >= 0 && atoi(r) < atoi(w)) {
+        *world = atoi(w); *rank = atoi(r);
+    }
+}
+
+static double now_ms(void)
+{
+    struct timespec t;
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    return t.tv_sec * 1000.0 + t.tv_nsec / 1e6;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+/* ------------------------------------------------------------ allocation */
+
+static int alloc_mat(PackedMat *m, int wtype, int rows, int cols)
+{
+    m->rows = rows; m->cols = cols;
+    m->stride = (long long)b200_packed_row_stride(wtype, cols);
+    CU_TRY(cudaMalloc(&m->w, (size_t)m->stride * (size_t)rows), return -1);
+    return 0;
+}
+
+static float *dev_zero(size_t bytes)
+{
+    void *p = NULL;
+    CU_TRY(cudaMalloc(&p, bytes ? bytes : 4), return NULL);
+    CU_TRY(cudaMemsetAsync(p, 0, bytes ? bytes : 4, g_rt.stream), { cudaFree(p); return NULL; });
+    return (float *)p;
+}
+
+InferenceState *llmb200_state_begin(const llmb200_config *c)
+{
+    if (!c || c->d_model <= 0 || c->n_layers <= 0 || c->n_q_heads <= 0 || c->n_kv_heads <= 0 ||
+        c->head_dim <= 0 || c->intermediate_size <= 0 || c->vocab_size <= 0 || c->max_seq_len <= 0) {
+        fprintf(stderr, "[FastGen] invalid model configuration\n");
+        return NULL;
+    }
+    if (fast_metal_init() != 0) {
+        fprintf(stderr, "[FastGen] CUDA init failed\n");
+        return NULL;
+    }
+    int max_seq = c->max_seq_len;
+    if (max_seq > 4096) {
+        fprintf(stderr, "[FastGen] Warning: clamping max_seq_len to 4096 (kernel limit)\n");
+        max_seq = 4096;
+    }
+    InferenceState *s = calloc(1, sizeof(*s));
+    if (!s) { fast_metal_shutdown(); return NULL; }
+    s->D = c->d_model; s->Hq = c->n_q_heads; s->Hkv = c->n_kv_heads; s->hd = c->head_dim;
+    s->IS = c->intermediate_size; s->V = c->vocab_size; s->L = c->n_layers; s->max_seq = max_seq;
+    s->use_fp16 = c->use_fp16 ? 1 : 0;
+    s->wtype = s->use_fp16 ? B200_WT_F16 : B200_WT_Q8;
+    s->mt = c->model_type == MODEL_GEMMA3 ? MODEL_GEMMA3 : MODEL_QWEN3;
+    s->emb_scale = s->mt == MODEL_GEMMA3 ? sqrtf((float)s->D) : 1.0f;
+    if (s->mt == MODEL_GEMMA3) { s->eos[0] = 1; s->eos[1] = 106; s->n_eos = 2; }
+    else { s->eos[0] = 151645; s->eos[1] = 151643; s->n_eos = 2; }
+    tp_from_env(&s->tp_rank, &s->tp_size);
+    const int k = s->tp_size;
+    const int align = s->wtype == B200_WT_Q8 ? 32 : 8;
+    if (s->Hkv % k || s->Hq % k || s->IS % k || s->V % k || (s->IS / k) % align || (s->Hq / k * s->hd) % align ||
+        s->D % align || (s->hd != 64 && s->hd != 128 && s->hd != 256) ||
+        (s->Hq / s->Hkv != 1 && s->Hq / s->Hkv != 2 && s->Hq / s->Hkv != 4 && s->Hq / s->Hkv != 8) || s->Hq % s->Hkv) {
+        fprintf(stderr, "[FastGen] unsupported shape for %d-way tensor parallelism (heads %d/%d, head_dim %d, ffn %d, vocab %d)\n",
+                k, s->Hq, s->Hkv, s->hd, s->IS, s->V);
+        free(s); fast_metal_shutdown();
+        return NULL;
+    }
+    s->Hq_l = s->Hq / k; s->Hkv_l = s->Hkv / k; s->IS_l = s->IS / k; s->V_l = s->V / k;
+
+    s->layers = calloc((size_t)s->L, sizeof(Layer));
+    if (!s->layers) goto fail;
+    const int qkv_rows = (s->Hq_l + 2 * s->Hkv_l) * s->hd;
+    const size_t cache_bytes = (size_t)s->Hkv_l * max_seq * s->hd * 2;
+    for (int i = 0; i < s->L; ++i) {
+        Layer *ly = &s->layers[i];
+        if (alloc_mat(&ly->qkv, s->wtype, qkv_rows, s->D) || alloc_mat(&ly->o, s->wtype, s->D, s->Hq_l * s->hd) ||
+            alloc_mat(&ly->gateup, s->wtype, 2 * s->IS_l, s->D) || alloc_mat(&ly->down, s->wtype, s->D, s->IS_l))
+            goto fail;
+        ly->k_cache = dev_zero(cache_bytes);
+        ly->v_cache = dev_zero(cache_bytes);
+        if (!ly->k_cache || !ly->v_cache) goto fail;
+        s->weight_bytes += (unsigned long long)ly->qkv.stride * ly->qkv.rows + (unsigned long long)ly->o.stride * ly->o.rows +
+                           (unsigned long long)ly->gateup.stride * ly->gateup.rows + (unsigned long long)ly->down.stride * ly->down.rows;
+    }
+    if (alloc_mat(&s->lm, s->wtype, s->V_l, s->D)) goto fail;
+    s->weight_bytes += (unsigned long long)s->lm.stride * s->lm.rows;
+
+    /* sequence splits: enough blocks to cover the GPU, at least 64 keys each at full length */
+    s->n_split = 148 / s->Hkv_l;
+    if (s->n_split > 32) s->n_split = 32;
+    if (s->n_split > (max_seq + 63) / 64) s->n_split = (max_seq + 63) / 64;
+    if (s->n_split < 1) s->n_split = 1;
+
+    s->resid[0] = dev_zero((size_t)s->D * 4);
+    s->resid[1] = dev_zero((size_t)s->D * 4);
+    s->qkv = dev_zero((size_t)qkv_rows * 4);
+    s->attn_out = dev_zero((size_t)s->Hq_l * s->hd * 4);
+    s->act = dev_zero((size_t)s->IS_l * 4);
+    s->attn_scratch = dev_zero(b200_attn_scratch_floats(s->Hq_l, s->hd, s->n_split) * 4);
+    s->am_scratch = dev_zero((size_t)2 * 148 * 32 * 4);
+    s->attn_tickets = (unsigned *)dev_zero((size_t)s->Hkv_l * 4);
+    s->mv_ticket = (unsigned *)dev_zero(4);
+    int *ctl = (int *)dev_zero((size_t)(8 + max_seq + 2) * 4);
+    if (!s->resid[0] || !s->resid[1] || !s->qkv || !s->attn_out || !s->act || !s->attn_scratch || !s->am_scratch ||
+        !s->attn_tickets || !s->mv_ticket || !ctl)
+        goto fail;
+    s->d_pos = ctl; s->d_prompt_len = ctl + 1; s->d_err = ctl + 2; s->d_epoch = (unsigned *)(ctl + 3);
+    s->d_tokens = ctl + 8;
+
+    /* all-reduce region: [slots_o 8xD][slots_dn 8xD][flags 3x8][am_val 8][am_idx 8][logits V] */
+    size_t off = 0;
+    s->off_slots_o = off;  off += align_up((size_t)B200_MAX_PEERS * s->D * 4, 256);
+    s->off_slots_dn = off; off += align_up((size_t)B200_MAX_PEERS * s->D * 4, 256);
+    s->off_flags = off;    off += 256;
+    s->off_am_val = off;   off += 128;
+    s->off_am_idx = off;   off += 128;
+    s->off_logits = off;   off += align_up((size_t)s->V * 4, 256);
+    s->comm_bytes = off;
+    s->comm = (char *)dev_zero(off);
+    if (!s->comm) goto fail;
+    s->peer[s->tp_rank] = s->comm;
+    s->connected = (k == 1);
+
+    CU_TRY(cudaMallocHost((void **)&s->h_logits, (size_t)s->V * 4), goto fail);
+    CU_TRY(cudaMallocHost((void **)&s->h_tok, 64), goto fail);
+    CU_TRY(cudaMallocHost((void **)&s->h_ctl, (size_t)(8 + max_seq + 2) * 4), goto fail);
+    for (int i = 0; i < 4; ++i) CU_TRY(cudaEventCreateWithFlags(&s->tok_ev[i], cudaEventDisableTiming), goto fail);
+    CU_TRY(cudaEventCreate(&s->ev_a), goto fail);
+    CU_TRY(cudaEventCreate(&s->ev_b), goto fail);
+    s->use_pdl = getenv("LLMB200_NO_PDL") ? 0 : 1;
+    return s;
+fail:
+    inference_state_free(s);
+    return NULL;
+}
+
+/* ------------------------------------------------------------ weights */
+
+static float *upload_gamma(const float *g, int n) { return g ? llmb200_upload_f32(g, (size_t)n) : NULL; }
+
+int llmb200_state_load_layer(InferenceState *s, int li, const LayerWeightRef *r, float rope_theta)
+{
+    if (!s || !r || li < 0 || li >= s->L) return B200_E_BADARG;
+    const int D = s->D, hd = s->hd, k = s->tp_rank;
+    const int Hq_hd = s->Hq * hd, Hkv_hd = s->Hkv * hd;
+    if (r->q_proj.rows != Hq_hd || r->q_proj.cols != D || r->k_proj.rows != Hkv_hd || r->k_proj.cols != D ||
+        r->v_proj.rows != Hkv_hd || r->v_proj.cols != D || r->o_proj.rows != D || r->o_proj.cols != Hq_hd ||
+        r->gate_proj.rows != s->IS || r->gate_proj.cols != D || r->up_proj.rows != s->IS || r->up_proj.cols != D ||
+        r->down_proj.rows != D || r->down_proj.cols != s->IS || !r->input_norm_g || !r->post_attn_norm_g) {
+        fprintf(stderr, "[FastGen] layer %d: weight shapes do not match the configuration\n", li);
+        return B200_E_BADARG;
+    }
+    Layer *ly = &s->layers[li];
+    const int wt = s->wtype;
+    const int ql = s->Hq_l * hd, kl = s->Hkv_l * hd, il = s->IS_l;
+    int rc = 0;
+    /* fused Q|K|V: this rank's query heads, then its key heads, then its value heads */
+    rc |= llmb200_upload_packed(wt, r->q_proj.data + (size_t)k * ql * D, D, ql, 0, D, ly->qkv.w, ly->qkv.stride, 0, 1);
+    rc |= llmb200_upload_packed(wt, r->k_proj.data + (size_t)k * kl * D, D, kl, 0, D, ly->qkv.w, ly->qkv.stride, ql, 1);
+    rc |= llmb200_upload_packed(wt, r->v_proj.data + (size_t)k * kl * D, D, kl, 0, D, ly->qkv.w, ly->qkv.stride, ql + kl, 1);
+    /* O: input columns of this rank's heads */
+    rc |= llmb200_upload_packed(wt, r->o_proj.data, Hq_hd, D, k * ql, ql, ly->o.w, ly->o.stride, 0, 1);
+    /* gate/up rows interleaved g0,u0,g1,u1,... so one warp finishes a (gate, up) pair */
+    rc |= llmb200_upload_packed(wt, r->gate_proj.data + (size_t)k * il * D, D, il, 0, D, ly->gateup.w, ly->gateup.stride, 0, 2);
+    rc |= llmb200_upload_packed(wt, r->up_proj.data + (size_t)k * il * D, D, il, 0, D, ly->gateup.w, ly->gateup.stride, 1, 2);
+    /* down: input columns of this rank's slice of the FFN */
+    rc |= llmb200_upload_packed(wt, r->down_proj.data, s->IS, D, k * il, il, ly->down.w, ly->down.stride, 0, 1);
+    if (rc) return rc;
+
+    ly->g_input = upload_gamma(r->input_norm_g, D);
+    ly->g_post_attn = upload_gamma(r->post_attn_norm_g, D);
+    ly->g_pre_ff = upload_gamma(r->pre_ff_norm_g, D);
+    ly->g_post_ff = upload_gamma(r->post_ff_norm_g, D);
+    ly->g_qn = upload_gamma(r->q_norm_g, hd);
+    ly->g_kn = upload_gamma(r->k_norm_g, hd);
+    if (!ly->g_input || !ly->g_post_attn) return -1;
+
+    /* RoPE frequencies exactly as the reference's CPU path forms them:
+     * 1.0f / powf(theta, (float)(2*d) / (float)hd)  (src/nn/attention.c:757-758) */
+    float *f = malloc((size_t)(hd / 2) * sizeof(float));
+    if (!f) return -1;
+    for (int d = 0; d < hd / 2; ++d) f[d] = 1.0f / powf(rope_theta, (float)(2 * d) / (float)hd);
+    ly->inv_freq = llmb200_upload_f32(f, (size_t)(hd / 2));
+    free(f);
+    if (!ly->inv_freq) return -1;
+    ly->loaded = 1;
+    return 0;
+}
+
+static void free_graphs(InferenceState *s)
+{
+    if (s->g_full) { cudaGraphExecDestroy(s->g_full); s->g_full = NULL; }
+    if (s->g_nolm) { cudaGraphExecDestroy(s->g_nolm); s->g_nolm = NULL; }
+}
+
+int llmb200_state_finish(InferenceState *s, const float *lm_head, const float *final_norm_gamma, const float *token_emb)
+{
+    if (!s || !lm_head || !final_norm_gamma || !token_emb) return B200_E_BADARG;
+    for (int i = 0; i < s->L; ++i)
+        if (!s->layers[i].loaded) { fprintf(stderr, "[FastGen] layer %d was never loaded\n", i); return B200_E_STATE; }
+    int rc = llmb200_upload_packed(s->wtype, lm_head + (size_t)s->tp_rank * s->V_l * s->D, s->D, s->V_l, 0, s->D,
+                                   s->lm.w, s->lm.stride, 0, 1);
+    if (rc) return rc;
+    s->g_final = llmb200_upload_f32(final_norm_gamma, (size_t)s->D);
+    s->emb = llmb200_upload_f32(token_emb, (size_t)s->V * s->D);
+    if (!s->g_final || !s->emb) return -1;
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1);
+    s->finished = 1;
+    return 0;
+}
+
+/* ------------------------------------------------------------ one token */
+
+static void prof_mark(InferenceState *s, int kind)
+{
+    if (!s->prof_on || s->prof_n >= s->prof_cap) return;
+    if (kind >= 0) {
+        s->prof_kind[s->prof_n / 2] = kind;
+        cudaEventRecord(s->prof_ev[s->prof_n++], g_rt.stream);
+    } else {
+        cudaEventRecord(s->prof_ev[s->prof_n++], g_rt.stream);
+    }
+}
+
+static unsigned *flags_of(InferenceState *s, int peer, int which) /* which: 0 o, 1 down, 2 argmax */
+{
+    return (unsigned *)(s->peer[peer] + s->off_flags) + which * B200_MAX_PEERS;
+}
+
+static void base_args(InferenceState *s, b200_matvec_args *a, const PackedMat *m, int pdl)
+{
+    memset(a, 0, sizeof(*a));
+    a->d_w = m->w; a->row_stride = m->stride; a->rows = m->rows; a->cols = m->cols; a->wtype = s->wtype;
+    a->eps = 1e-6f;                               /* hard-wired in the reference: src/nn/fast_inference.c:383 */
+    a->d_pos = s->d_pos; a->d_pos_rw = s->d_pos;
+    a->d_epoch = s->d_epoch; a->d_epoch_rw = s->d_epoch; a->d_err = s->d_err;
+    a->epoch_mul = s->L + 1;
+    a->use_pdl = pdl;
+}
+
+/* Enqueue every kernel of one token on the library stream. */
+static int enqueue_token(InferenceState *s, int with_lm, int pdl)
+{
+    const int k = s->tp_size, me = s->tp_rank, D = s->D, L = s->L;
+    const int gemma = s->mt == MODEL_GEMMA3;
+    float *slots_o = (float *)(s->comm + s->off_slots_o), *slots_dn = (float *)(s->comm + s->off_slots_dn);
+    b200_matvec_args a;
+    void *st = g_rt.stream;
+    for (int l = 0; l < L; ++l) {
+        Layer *ly = &s->layers[l];
+        /* --- qkv --- */
+        base_args(s, &a, &ly->qkv, pdl);
+        if (l == 0) {
+            a.in_mode = B200_IN_EMBED; a.d_emb = s->emb; a.d_tokens = s->d_tokens; a.emb_scale = s->emb_scale;
+            a.epoch_add = -1;                     /* previous token's last down signal */
+        } else {
+            a.in_mode = B200_IN_RESID; a.d_resid_in = s->resid[0];
+            a.d_slots = slots_dn; a.n_slots = k; a.slot_stride = D;
+            a.d_slot_norm_gamma = gemma ? s->layers[l - 1].g_post_ff : NULL;
+            a.epoch_add = l;                      /* down signal of layer l-1 */
+        }
+        if (k > 1) { a.d_wait_flags = flags_of(s, me, 1); a.n_wait = k; }
+        a.d_resid_out = s->resid[1];
+        a.d_norm_gamma = ly->g_input;
+        a.out_mode = B200_OUT_STORE; a.d_out[0] = s->qkv; a.n_out = 1;
+        prof_mark(s, K_QKV);
+        K_TRY(b200_matvec(&a, st), return -1);
+        prof_mark(s, -1);
+        /* --- attention --- */
+        b200_attn_args at;
+        memset(&at, 0, sizeof(at));
+        at.d_qkv = s->qkv; at.d_q_gamma = ly->g_qn; at.d_k_gamma = ly->g_kn; at.d_inv_freq = ly->inv_freq;
+        at.d_k_cache = ly->k_cache; at.d_v_cache = ly->v_cache;
+        at.d_out = s->attn_out; at.d_scratch = s->attn_scratch; at.d_tickets = s->attn_tickets; at.d_pos = s->d_pos;
+        at.n_q = s->Hq_l; at.n_kv = s->Hkv_l; at.hd = s->hd; at.max_seq = s->max_seq; at.n_split = s->n_split;
+        at.eps = 1e-6f; at.use_pdl = pdl;
+        prof_mark(s, K_ATTN);
+        K_TRY(b200_attn_decode(&at, st), return -1);
+        prof_mark(s, -1);
+        /* --- o: partial sums into slot `me` of every rank --- */
+        base_args(s, &a, &ly->o, pdl);
+        a.in_mode = B200_IN_VEC; a.d_in_vec = s->attn_out;
+        a.out_mode = B200_OUT_STORE; a.n_out = k;
+        for (int p = 0; p < k; ++p) a.d_out[p] = (float *)(s->peer[p] + s->off_slots_o) + (size_t)me * D;
+        if (k > 1) {
+            a.d_ticket = s->mv_ticket; a.n_signal = k; a.signal_index = me; a.epoch_add = l + 1;
+            for (int p = 0; p < k; ++p) a.d_signal_flags[p] = flags_of(s, p, 0);
+        }
+        prof_mark(s, K_O);
+        K_TRY(b200_matvec(&a, st), return -1);
+        prof_mark(s, -1);
+        /* --- gate/up --- */
+        base_args(s, &a, &ly->gateup, pdl);
+        a.in_mode = B200_IN_RESID; a.d_resid_in = s->resid[1]; a.d_resid_out = s->resid[0];
+        a.d_slots = slots_o; a.n_slots = k; a.slot_stride = D;
+        a.d_slot_norm_gamma = gemma ? ly->g_post_attn : NULL;
+        a.d_norm_gamma = gemma ? ly->g_pre_ff : ly->g_post_attn;
+        if (k > 1) { a.d_wait_flags = flags_of(s, me, 0); a.n_wait = k; a.epoch_add = l + 1; }
+        a.out_mode = B200_OUT_GLU; a.act = gemma ? 1 : 0; a.d_out[0] = s->act; a.n_out = 1;
+        prof_mark(s, K_GATEUP);
+        K_TRY(b200_matvec(&a, st), return -1);
+        prof_mark(s, -1);
+        /* --- down --- */
+        base_args(s, &a, &ly->down, pdl);
+        a.in_mode = B200_IN_VEC; a.d_in_vec = s->act;
+        a.out_mode = B200_OUT_STORE; a.n_out = k;
+        for (int p = 0; p < k; ++p) a.d_out[p] = (float *)(s->peer[p] + s->off_slots_dn) + (size_t)me * D;
+        if (k > 1) {
+            a.d_ticket = s->mv_ticket; a.n_signal = k; a.signal_index = me; a.epoch_add = l + 1;
+            for (int p = 0; p < k; ++p) a.d_signal_flags[p] = flags_of(s, p, 1);
+        }
+        if (!with_lm && l == L - 1) { a.d_ticket = s->mv_ticket; a.advance_pos = 1; a.advance_epoch = 1; }
+        prof_mark(s, K_DOWN);
+        K_TRY(b200_matvec(&a, st), return -1);
+        prof_mark(s, -1);
+    }
+    if (!with_lm) return 0;
+    /* --- final norm + LM head + greedy pick --- */
+    base_args(s, &a, &s->lm, pdl);
+    a.in_mode = B200_IN_RESID; a.d_resid_in = s->resid[0];
+    a.d_slots = slots_dn; a.n_slots = k; a.slot_stride = D;
+    a.d_slot_norm_gamma = gemma ? s->layers[L - 1].g_post_ff : NULL;
+    a.d_norm_gamma = s->g_final;
+    if (k > 1) { a.d_wait_flags = flags_of(s, me, 1); a.n_wait = k; a.epoch_add = L; }
+    a.out_mode = B200_OUT_STORE; a.n_out = k; a.out_offset = (long long)me * s->V_l;
+    for (int p = 0; p < k; ++p) a.d_out[p] = (float *)(s->peer[p] + s->off_logits);
+    a.d_ticket = s->mv_ticket; a.d_argmax_scratch = s->am_scratch;
+    a.n_argmax_out = k;
+    for (int p = 0; p < k; ++p) {
+        a.d_argmax_val[p] = (float *)(s->peer[p] + s->off_am_val) + me;
+        a.d_argmax_idx[p] = (int *)(s->peer[p] + s->off_am_idx) + me;
+    }
+    if (k == 1) {
+        a.d_next_token = s->d_tokens; a.d_prompt_len = s->d_prompt_len; a.advance_pos = 1; a.advance_epoch = 1;
+    } else {
+        a.n_signal = k; a.signal_index = me;
+        for (int p = 0; p < k; ++p) a.d_signal_flags[p] = flags_of(s, p, 2);
+        /* the wait above used epoch_add = L; the argmax flags carry L + 1 */
+    }
+    if (k > 1) {
+        /* one kernel cannot wait with one value and signal with another: the LM head
+         * waits on the down flags (value L) and signals the argmax flags with the
+         * same value L; the finalize kernel waits for that value. */
+        a.epoch_add = L;
+    }
+    prof_mark(s, K_LM);
+    K_TRY(b200_matvec(&a, st), return -1);
+    prof_mark(s, -1);
+    if (k > 1) {
+        K_TRY(b200_tp_argmax_finalize((const float *)(s->comm + s->off_am_val), (const int *)(s->comm + s->off_am_idx), k,
+                                      flags_of(s, me, 2), s->d_epoch, L + 1, L, s->d_tokens, s->d_pos, s->d_prompt_len,
+                                      s->d_epoch, s->d_err, pdl, st), return -1);
+    }
+    return 0;
+}
+
+static int capture(InferenceState *s, int with_lm, int pdl, cudaGraphExec_t *out)
+{
+    cudaGraph_t g = NULL;
+    CU_TRY(cudaStreamBeginCapture(g_rt.stream, cudaStreamCaptureModeThreadLocal), return -1);
+    int rc = enqueue_token(s, with_lm, pdl);
+    cudaError_t e = cudaStreamEndCapture(g_rt.stream, &g);
+    if (rc != 0 || e != cudaSuccess || !g) {
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+        return -1;
+    }
+    e = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) { cudaGetLastError(); *out = NULL; return -1; }
+    return 0;
+}
+
+static int ensure_graphs(InferenceState *s)
+{
+    if (s->g_full && s->g_nolm) return 0;
+    if (!s->finished) { fprintf(stderr, "[FastGen] state is not fully loaded\n"); return -1; }
+    if (!s->connected) { fprintf(stderr, "[FastGen] tensor-parallel peers are not connected (llmb200_state_connect)\n"); return -1; }
+    free_graphs(s);
+    if (capture(s, 1, s->use_pdl, &s->g_full) != 0 || capture(s, 0, s->use_pdl, &s->g_nolm) != 0) {
+        if (s->use_pdl) {
+            fprintf(stderr, "[FastGen] graph capture with programmatic dependent launch failed; retrying without\n");
+            free_graphs(s);
+            s->use_pdl = 0;
+            if (capture(s, 1, 0, &s->g_full) == 0 && capture(s, 0, 0, &s->g_nolm) == 0) return 0;
+        }
+        fprintf(stderr, "[FastGen] CUDA graph capture failed\n");
+        free_graphs(s);
+        return -1;
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------ TP plumbing */
+
+int llmb200_state_comm_handle(InferenceState *s, void *out)
+{
+    if (!s || !out) return B200_E_BADARG;
+    cudaIpcMemHandle_t h;
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1);
+    CU_TRY(cudaIpcGetMemHandle(&h, s->comm), return -1);
+    memset(out, 0, LLMB200_HANDLE_BYTES);
+    memcpy(out, &h, sizeof(h) < LLMB200_HANDLE_BYTES ? sizeof(h) : LLMB200_HANDLE_BYTES);
+    return 0;
+}
+
+int llmb200_state_connect(InferenceState *s, const void *handles, int world)
+{
+    if (!s || !handles || world != s->tp_size) return B200_E_BADARG;
+    for (int p = 0; p < world; ++p) {
+        if (p == s->tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)p * LLMB200_HANDLE_BYTES, sizeof(h));
+        void *ptr = NULL;
+        CU_TRY(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), return -1);
+        s->peer[p] = (char *)ptr;
+    }
+    s->connected = 1;
+    free_graphs(s);
+    return 0;
+}
+
+/* ------------------------------------------------------------ reference API */
+
+static void fill_refs_common(LayerWeightRef *r, llmb200_gqa *at, llmb200_linear *gate, llmb200_linear *up,
+                             llmb200_linear *down, int D, int Hq_hd, int Hkv_hd, int IS, int hd)
+{
+    r->q_proj = (WeightRef){at->q_proj->weight->data, Hq_hd, D};
+    r->k_proj = (WeightRef){at->k_proj->weight->data, Hkv_hd, D};
+    r->v_proj = (WeightRef){at->v_proj->weight->data, Hkv_hd, D};
+    r->o_proj = (WeightRef){at->o_proj->weight->data, D, Hq_hd};
+    r->gate_proj = (WeightRef){gate->weight->data, IS, D};
+    r->up_proj = (WeightRef){up->weight->data, IS, D};
+    r->down_proj = (WeightRef){down->weight->data, D, IS};
+    r->q_norm_g = at->q_norm ? at->q_norm->gamma->data : NULL;
+    r->k_norm_g = at->k_norm ? at->k_norm->gamma->data : NULL;
+    r->d_model = D; r->head_dim = hd;
+}
+
+InferenceState *inference_state_create(llmb200_qwen3_model *m, int max_seq_len, int use_fp16)
+{
+    if (!m) return NULL;
+    llmb200_config c = {MODEL_QWEN3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
+                        m->vocab_size, m->n_layers, max_seq_len, use_fp16};
+    InferenceState *s = llmb200_state_begin(&c);
+    if (!s) return NULL;
+    const char *mode = use_fp16 ? "F16" : "Q8_0";
+    fprintf(stderr, "[FastGen] Converting weights to %s + uploading to GPU...\n", mode);
+    const double t0 = now_ms();
+    for (int i = 0; i < m->n_layers; ++i) {
+        llmb200_qwen3_block *b = m->blocks[i];
+        LayerWeightRef r;
+        memset(&r, 0, sizeof(r));
+        fill_refs_common(&r, b->attn, b->gate_proj, b->up_proj, b->down_proj, m->d_model, m->n_q_heads * m->head_dim,
+                         m->n_kv_heads * m->head_dim, m->intermediate_size, m->head_dim);
+        r.input_norm_g = b->input_norm->gamma->data;
+        r.post_attn_norm_g = b->post_attn_norm->gamma->data;
+        if (llmb200_state_load_layer(s, i, &r, m->rope_theta) != 0) { inference_state_free(s); return NULL; }
+    }
+    if (llmb200_state_finish(s, m->lm_head->weight->data, m->final_norm->gamma->data, m->token_emb->weight->data) != 0) {
+        inference_state_free(s);
+        return NULL;
+    }
+    fprintf(stderr, "[FastGen] %s + GPU upload: %.0f ms\n", mode, now_ms() - t0);
+    return s;
+}
+
+InferenceState *inference_state_create_gemma3(llmb200_gemma3_model *m, int max_seq_len, int use_fp16)
+{
+    if (!m) return NULL;
+    llmb200_config c = {MODEL_GEMMA3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
+                        m->vocab_size, m->n_layers, max_seq_len, use_fp16};
+    InferenceState *s = llmb200_state_begin(&c);
+    if (!s) return NULL;
+    const char *mode = use_fp16 ? "F16" : "Q8_0";
+    fprintf(stderr, "[FastGen] Converting weights to %s + uploading to GPU...\n", mode);
+    const double t0 = now_ms();
+    for (int i = 0; i < m->n_layers; ++i) {
+        llmb200_gemma3_block *b = m->blocks[i];
+        LayerWeightRef r;
+        memset(&r, 0, sizeof(r));
+        fill_refs_common(&r, b->attn, b->gate_proj, b->up_proj, b->down_proj, m->d_model, m->n_q_heads * m->head_dim,
+                         m->n_kv_heads * m->head_dim, m->intermediate_size, m->head_dim);
+        r.input_norm_g = b->input_norm->gamma->data;
+        r.post_attn_norm_g = b->post_attn_norm->gamma->data;
+        r.pre_ff_norm_g = b->pre_ff_norm->gamma->data;
+        r.post_ff_norm_g = b->post_ff_norm->gamma->data;
+        const float theta = b->is_sliding ? m->local_rope_theta : m->global_rope_theta;
+        if (llmb200_state_load_layer(s, i, &r, theta) != 0) { inference_state_free(s); return NULL; }
+    }
+    /* tied embeddings: the LM head is the embedding table (src/nn/fast_inference.c:307-313) */
+    if (llmb200_state_finish(s, m->token_emb->weight->data, m->final_norm->gamma->data, m->token_emb->weight->data) != 0) {
+        inference_state_free(s);
+        return NULL;
+    }
+    fprintf(stderr, "[FastGen] %s + GPU upload: %.0f ms\n", mode, now_ms() - t0);
+    return s;
+}
+
+void inference_state_free(InferenceState *s)
+{
+    if (!s) return;
+    if (g_rt.refs > 0) cudaStreamSynchronize(g_rt.stream);
+    free_graphs(s);
+    if (s->layers) {
+        for (int i = 0; i < s->L; ++i) {
+            Layer *ly = &s->layers[i];
+            cudaFree(ly->qkv.w); cudaFree(ly->o.w); cudaFree(ly->gateup.w); cudaFree(ly->down.w);
+            cudaFree(ly->g_input); cudaFree(ly->g_post_attn); cudaFree(ly->g_pre_ff); cudaFree(ly->g_post_ff);
+            cudaFree(ly->g_qn); cudaFree(ly->g_kn); cudaFree(ly->inv_freq);
+            cudaFree(ly->k_cache); cudaFree(ly->v_cache);
+        }
+        free(s->layers);
+    }
+    cudaFree(s->lm.w); cudaFree(s->g_final); cudaFree(s->emb);
+    cudaFree(s->resid[0]); cudaFree(s->resid[1]); cudaFree(s->qkv); cudaFree(s->attn_out); cudaFree(s->act);
+    cudaFree(s->attn_scratch); cudaFree(s->am_scratch); cudaFree(s->attn_tickets); cudaFree(s->mv_ticket);
+    cudaFree(s->d_pos);
+    for (int p = 0; p < s->tp_size; ++p)
+        if (p != s->tp_rank && s->peer[p]) cudaIpcCloseMemHandle(s->peer[p]);
+    cudaFree(s->comm);
+    if (s->h_logits) cudaFreeHost(s->h_logits);
+    if (s->h_tok) cudaFreeHost(s->h_tok);
+    if (s->h_ctl) cudaFreeHost(s->h_ctl);
+    for (int i = 0; i < 4; ++i) if (s->tok_ev[i]) cudaEventDestroy(s->tok_ev[i]);
+    if (s->ev_a) cudaEventDestroy(s->ev_a);
+    if (s->ev_b) cudaEventDestroy(s->ev_b);
+    if (s->prof_ev) {
+        for (int i = 0; i < s->prof_cap; ++i) cudaEventDestroy(s->prof_ev[i]);
+        free(s->prof_ev); free(s->prof_kind);
+    }
+    free(s);
+    fast_metal_shutdown();
+}
+
+ModelType inference_state_model_type(InferenceState *s) { return s->mt; }
+int inference_state_vocab_size(InferenceState *s) { return s->V; }
+void inference_state_reset(InferenceState *s) { s->cur_len = 0; }
+int llmb200_state_position(InferenceState *s) { return s ? s->cur_len : -1; }
+unsigned long long llmb200_state_weight_bytes(InferenceState *s) { return s ? s->weight_bytes : 0; }
+double llmb200_last_decode_ms(InferenceState *s, int *n) { if (n) *n = s->last_n_decoded; return s->last_decode_ms; }
+double llmb200_last_prefill_ms(InferenceState *s) { return s->last_prefill_ms; }
+
+void llmb200_state_set_eos(InferenceState *s, const int *eos, int n)
+{
+    if (!s) return;
+    if (n < 0) n = 0;
+    if (n > 4) n = 4;
+    for (int i = 0; i < n; ++i) s->eos[i] = eos[i];
+    s->n_eos = n;
+}
+
+int llmb200_state_error(InferenceState *s)
+{
+    if (!s) return 1;
+    int err = 0;
+    if (cudaMemcpy(&err, s->d_err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 1;
+    return err;
+}
+
+/* Writes pos / prompt_len (and, when n_tok > 0, token ids starting at tok_at) into the control block. */
+static int set_control(InferenceState *s, int pos, int prompt_len, const uint32_t *tok, int tok_at, int n_tok)
+{
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1);   /* h_ctl may still be in flight */
+    s->h_ctl[0] = pos; s->h_ctl[1] = prompt_len;
+    CU_TRY(cudaMemcpyAsync(s->d_pos, s->h_ctl, 8, cudaMemcpyHostToDevice, g_rt.stream), return -1);
+    if (n_tok > 0) {
+        for (int i = 0; i < n_tok; ++i) s->h_ctl[8 + i] = (int)tok[i];
+        CU_TRY(cudaMemcpyAsync(s->d_tokens + tok_at, s->h_ctl + 8, (size_t)n_tok * 4, cudaMemcpyHostToDevice, g_rt.stream),
+               return -1);
+    }
+    return 0;
+}
+
+const float *inference_forward_token(InferenceState *s, int token)
+{
+    if (!s || ensure_graphs(s) != 0) return NULL;
+    if (s->cur_len >= s->max_seq) { fprintf(stderr, "[FastGen] KV cache is full (%d positions)\n", s->max_seq); return NULL; }
+    if (token < 0 || token >= s->V) { fprintf(stderr, "[FastGen] token id %d out of range\n", token); return NULL; }
+    uint32_t t = (uint32_t)token;
+    /* prompt_len beyond pos+1 keeps the graph from overwriting caller-supplied ids */
+    if (set_control(s, s->cur_len, s->max_seq + 2, &t, s->cur_len, 1) != 0) return NULL;
+    CU_TRY(cudaGraphLaunch(s->g_full, g_rt.stream), return NULL);
+    CU_TRY(cudaMemcpyAsync(s->h_logits, s->comm + s->off_logits, (size_t)s->V * 4, cudaMemcpyDeviceToHost, g_rt.stream),
+           return NULL);
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return NULL);
+    s->cur_len++;
+    return s->h_logits;
+}
+
+static int is_eos(const InferenceState *s, int tok)
+{
+    for (int e = 0; e < s->n_eos; ++e) if (tok == s->eos[e]) return 1;
+    return 0;
+}
+
+int inference_generate(InferenceState *s, const uint32_t *prompt, int prompt_len, uint32_t *out, int max_gen_len)
+{
+    if (!s || !prompt || !out || prompt_len <= 0 || max_gen_len <= 0) return 0;
+    if (ensure_graphs(s) != 0) return 0;
+    if (prompt_len > s->max_seq) {
+        fprintf(stderr, "[FastGen] prompt of %d tokens exceeds the KV cache (%d)\n", prompt_len, s->max_seq);
+        return 0;
+    }
+    for (int i = 0; i < prompt_len; ++i)
+        if (prompt[i] >= (uint32_t)s->V) { fprintf(stderr, "[FastGen] prompt token %u out of range\n", prompt[i]); return 0; }
+    s->cur_len = 0;
+    const int P = prompt_len;
+    if (set_control(s, 0, P, prompt, 0, P) != 0) return 0;
+
+    fprintf(stderr, "[FastGen] Prefilling %d tokens...\n", P);
+    double t0 = now_ms();
+    for (int i = 0; i < P - 1; ++i) CU_TRY(cudaGraphLaunch(s->g_nolm, g_rt.stream), return 0);
+    CU_TRY(cudaGraphLaunch(s->g_full, g_rt.stream), return 0);
+    CU_TRY(cudaMemcpyAsync(&s->h_tok[0], s->d_tokens + P, 4, cudaMemcpyDeviceToHost, g_rt.stream), return 0);
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return 0);
+    s->cur_len = P;
+    s->last_prefill_ms = now_ms() - t0;
+    fprintf(stderr, "[FastGen] Prefill: %.0f ms (%.1f tok/s)\n", s->last_prefill_ms, P * 1000.0 / s->last_prefill_ms);
+
+    int next = s->h_tok[0];
+    out[0] = (uint32_t)next;
+    int n_gen = 1;
+
+    fprintf(stderr, "[FastGen] Decoding...\n");
+    t0 = now_ms();
+    /* Forward number i (1-based) consumes the id at position P+i-1 and leaves the id
+     * for position P+i on the device. The host only needs ids to test for EOS, so it
+     * runs one forward ahead of the id it is waiting for. */
+    int max_fw = max_gen_len - 1;
+    if (max_fw > s->max_seq - P) max_fw = s->max_seq - P;
+    int launched = 0, done = 0;
+#define LAUNCH_FW()                                                                                          \
+    do {                                                                                                     \
+        CU_TRY(cudaGraphLaunch(s->g_full, g_rt.stream), return n_gen);                                       \
+        CU_TRY(cudaMemcpyAsync(&s->h_tok[4 + (launched & 3)], s->d_tokens + P + launched + 1, 4,             \
+                               cudaMemcpyDeviceToHost, g_rt.stream), return n_gen);                          \
+        CU_TRY(cudaEventRecord(s->tok_ev[launched & 3], g_rt.stream), return n_gen);                         \
+        launched++;                                                                                          \
+    } while (0)
+    if (!is_eos(s, next) && max_fw > 0) LAUNCH_FW();
+    while (done < launched) {
+        if (launched < max_fw && launched - done < 2) LAUNCH_FW();
+        CU_TRY(cudaEventSynchronize(s->tok_ev[done & 3]), return n_gen);
+        next = s->h_tok[4 + (done & 3)];
+        done++;
+        out[n_gen++] = (uint32_t)next;
+        if (n_gen % 10 == 0) {
+            double el = now_ms() - t0;
+            fprintf(stderr, "[FastGen]   %d tokens, %.1f tok/s\n", n_gen - 1, (n_gen - 1) * 1000.0 / el);
+        }
+        if (is_eos(s, next)) break;
+    }
+#undef LAUNCH_FW
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return n_gen);
+    s->cur_len = P + done;
+    s->last_decode_ms = now_ms() - t0;
+    s->last_n_decoded = n_gen - 1;
+    if (s->last_n_decoded > 0)
+        fprintf(stderr, "[FastGen] Decode: %d tokens in %.0f ms (%.1f tok/s, %.2f ms/tok)\n", s->last_n_decoded,
+                s->last_decode_ms, s->last_n_decoded * 1000.0 / s->last_decode_ms, s->last_decode_ms / s->last_n_decoded);
+    if (llmb200_state_error(s)) fprintf(stderr, "[FastGen] a device-side wait timed out; results are invalid\n");
+    return n_gen;
+}
+
+int qwen3_generate_fast(llmb200_qwen3_model *model, const uint32_t *prompt, int prompt_len, uint32_t *out,
+                        int max_gen_len, int max_seq_len, int use_fp16)
+{
+    InferenceState *s = inference_state_create(model, max_seq_len, use_fp16);
+    if (!s) return 0;
+    int n = inference_generate(s, prompt, prompt_len, out, max_gen_len);
+    inference_state_free(s);
+    return n;
+}
+
+/* eos_token_id from config.json: an int or an array of ints. */
+static int parse_eos(const char *model_path, int *eos, int max_eos)
+{
+    char path[700];
+    struct stat st;
+    if (stat(model_path, &st) == 0 && S_ISDIR(st.st_mode)) snprintf(path, sizeof(path), "%s/config.json", model_path);
+    else {
+        const char *sl = strrchr(model_path, '/');
+        if (sl) snprintf(path, sizeof(path), "%.*s/config.json", (int)(sl - model_path), model_path);
+        else snprintf(path, sizeof(path), "config.json");
+    }
+    FILE *fp = fopen(path, "r");
+    if (!fp) return 0;
+    char buf[4096];
+    size_t n = fread(buf, 1, sizeof(buf) - 1, fp);
+    buf[n] = 0;
+    fclose(fp);
+    const char *p = strstr(buf, "\"eos_token_id\"");
+    if (!p) return 0;
+    p += 14;
+    while (*p == ' ' || *p == ':' || *p == '\t') p++;
+    int cnt = 0;
+    if (*p == '[') {
+        p++;
+        while (*p && *p != ']' && cnt < max_eos) {
+            while (*p == ' ' || *p == ',' || *p == '\n') p++;
+            if (*p == ']') break;
+            char *end;
+            eos[cnt++] = (int)strtol(p, &end, 10);
+            if (end == p) break;
+            p = end;
+        }
+    } else {
+        eos[cnt++] = (int)strtol(p, NULL, 10);
+    }
+    return cnt;
+}
+
+void inference_state_load_eos(InferenceState *s, const char *model_path)
+{
+    if (!s || !model_path) return;
+    s->n_eos = parse_eos(model_path, s->eos, 4);
+    if (s->n_eos == 0) {
+        if (s->mt == MODEL_GEMMA3) { s->eos[0] = 1; s->eos[1] = 106; }
+        else { s->eos[0] = 151645; s->eos[1] = 151643; }
+        s->n_eos = 2;
+    }
+    fprintf(stderr, "[FastGen] EOS tokens (%d):", s->n_eos);
+    for (int i = 0; i < s->n_eos; ++i) fprintf(stderr, " %d", s->eos[i]);
+    fprintf(stderr, "\n");
+}
+
+/* ------------------------------------------------------------ measurement */
+
+float llmb200_state_run_device_steps(InferenceState *s, int n_steps)
+{
+    if (!s || n_steps <= 0 || ensure_graphs(s) != 0) return -1.0f;
+    if (s->cur_len + n_steps > s->max_seq) return -1.0f;
+    if (set_control(s, s->cur_len, 0, NULL, 0, 0) != 0) return -1.0f;
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1.0f);
+    CU_TRY(cudaEventRecord(s->ev_a, g_rt.stream), return -1.0f);
+    for (int i = 0; i < n_steps; ++i) CU_TRY(cudaGraphLaunch(s->g_full, g_rt.stream), return -1.0f);
+    CU_TRY(cudaEventRecord(s->ev_b, g_rt.stream), return -1.0f);
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1.0f);
+    float ms = -1.0f;
+    CU_TRY(cudaEventElapsedTime(&ms, s->ev_a, s->ev_b), return -1.0f);
+    s->cur_len += n_steps;
+    return ms;
+}
+
+int llmb200_state_profile_token(InferenceState *s, float *ms, int *launches)
+{
+    if (!s || !ms || !launches || ensure_graphs(s) != 0) return B200_E_BADARG;
+    if (s->cur_len + 1 > s->max_seq) return B200_E_STATE;
+    const int need = 2 * (5 * s->L + 1);
+    if (!s->prof_ev) {
+        s->prof_ev = calloc((size_t)need, sizeof(cudaEvent_t));
+        s->prof_kind = calloc((size_t)need / 2, sizeof(int));
+        if (!s->prof_ev || !s->prof_kind) return -1;
+        for (int i = 0; i < need; ++i) CU_TRY(cudaEventCreate(&s->prof_ev[i]), return -1);
+        s->prof_cap = need;
+    }
+    if (set_control(s, s->cur_len, 0, NULL, 0, 0) != 0) return -1;
+    s->prof_n = 0;
+    cudaEvent_t *ev = s->prof_ev;
+    s->prof_on = 1;
+    int rc = enqueue_token(s, 1, 0);
+    s->prof_on = 0;
+    const int n = s->prof_n;
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1);
+    if (rc != 0) return rc;
+    for (int i = 0; i < K_KINDS; ++i) { ms[i] = 0.0f; launches[i] = 0; }
+    for (int i = 0; i + 1 < n; i += 2) {
+        float t = 0.0f;
+        CU_TRY(cudaEventElapsedTime(&t, ev[i], ev[i + 1]), return -1);
+        ms[s->prof_kind[i / 2]] += t;
+        launches[s->prof_kind[i / 2]]++;
+    }
+    s->cur_len++;
+    return 0;
+}
+
+size_t llmb200_state_export_weight(InferenceState *s, int layer, int which, void *buf, size_t cap)
+{
+    if (!s) return 0;
+    const PackedMat *m = NULL;
+    if (which == 4) m = &s->lm;
+    else if (layer >= 0 && layer < s->L) {
+        Layer *ly = &s->layers[layer];
+        m = which == 0 ? &ly->qkv : which == 1 ? &ly->o : which == 2 ? &ly->gateup : which == 3 ? &ly->down : NULL;
+    }
+    if (!m) return 0;
+    const size_t bytes = s->wtype == B200_WT_Q8 ? (size_t)m->rows * (m->cols / 32) * 34 : (size_t)m->rows * m->cols * 2;
+    if (!buf) return bytes;
+    if (cap < bytes) return 0;
+    if (s->wtype == B200_WT_Q8) {
+        void *d = NULL;
+        CU_TRY(cudaMalloc(&d, bytes), return 0);
+        int rc = b200_q8_unpack_blocks(m->w, m->stride, m->rows, m->cols, d, g_rt.stream);
+        if (rc == 0) rc = (int)cudaMemcpyAsync(buf, d, bytes, cudaMemcpyDeviceToHost, g_rt.stream);
+        if (rc == 0) rc = (int)cudaStreamSynchronize(g_rt.stream);
+        cudaFree(d);
+        return rc == 0 ? bytes : 0;
+    }
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return 0);
+    CU_TRY(cudaMemcpy2D(buf, (size_t)m->cols * 2, m->w, (size_t)m->stride, (size_t)m->cols * 2, (size_t)m->rows,
+                        cudaMemcpyDeviceToHost), return 0);
+    return bytes;
+}

@@ -1,0 +1,70 @@
+/* Internal declarations shared by the C host files of libllmb200. */
+#ifndef LLMB200_INTERNAL_H
+#define LLMB200_INTERNAL_H
+
+#include <cuda_runtime_api.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/llmb200_kernels.h"
+#include "../../include/llmb200_wmat.h"
+
+enum { MB_SHARED = 0, MB_Q8 = 1, MB_F16 = 2, MB_DEVICE = 3 };
+
+struct MetalBuf {
+    void *dev;               /* device (or unified) pointer */
+    size_t size;             /* bytes at dev */
+    int kind;                /* MB_* */
+    int rows, cols;          /* packed weights only */
+    long long row_stride;
+    void *host_mirror;       /* canonical host copy of a packed weight, made on demand */
+};
+
+#define LLMB200_STAGE_BYTES ((size_t)64 << 20)
+
+typedef struct {
+    int refs;
+    int device;
+    cudaStream_t stream;
+    /* double-buffered upload staging: pinned host + device fp32 */
+    float *h_stage[2];
+    float *d_stage[2];
+    cudaEvent_t stage_done[2];
+    int stage_next;
+} llmb200_runtime;
+
+extern llmb200_runtime g_rt;
+
+#define CU_TRY(call, onfail)                                                          \
+    do {                                                                              \
+        cudaError_t e__ = (call);                                                     \
+        if (e__ != cudaSuccess) {                                                     \
+            fprintf(stderr, "[llmb200] %s failed: %s (%s:%d)\n", #call,               \
+                    cudaGetErrorString(e__), __FILE__, __LINE__);                     \
+            onfail;                                                                   \
+        }                                                                             \
+    } while (0)
+
+#define K_TRY(call, onfail)                                                           \
+    do {                                                                              \
+        int e__ = (call);                                                             \
+        if (e__ != 0) {                                                               \
+            fprintf(stderr, "[llmb200] %s failed: code %d%s%s (%s:%d)\n", #call, e__, \
+                    e__ > 0 ? " " : "", e__ > 0 ? cudaGetErrorString((cudaError_t)e__) : "", \
+                    __FILE__, __LINE__);                                              \
+            onfail;                                                                   \
+        }                                                                             \
+    } while (0)
+
+/* Convert the sub-matrix src[0..rows) x [col0, col0+cols) of a host fp32 matrix
+ * with leading dimension ld into packed rows dst_row0 + r*dst_row_step of a
+ * packed device matrix. Returns 0 on success. Asynchronous on g_rt.stream
+ * except for the host-side staging copies. */
+int llmb200_upload_packed(int wtype, const float *src, long long ld, int rows, int col0, int cols,
+                          void *d_dst, long long dst_row_stride, int dst_row0, int dst_row_step);
+
+/* Plain fp32 host -> new device allocation (returns NULL on failure). */
+float *llmb200_upload_f32(const float *src, size_t n);
+
+#endif
