@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Headline benchmark: Qwen3-4B-shaped Q8_0 batch-1 greedy decode, tokens per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one generate request of the workload (prompt 512, generate 512): a
+token-by-token prefill (untimed, as in the reference's own metric) followed by
+511 decode forwards (timed). Weights are seeded random N(0, 0.02) of the named
+architecture, quantised to Q8_0 on the GPU; token ids are uniform random.
+
+  value      decode tokens / second with every input resident in HBM: the
+             per-token CUDA graph replayed 511 times per step, timed with CUDA
+             events on the launching stream, max over ranks.
+  e2e        the same metric through the reference-facing call
+             inference_generate() with host buffers: prompt ids copied in,
+             every generated id copied back inside the timed region.
+  roofline   the dominant kernel (the gate/up Q8_0 matvec): algorithmic bytes
+             per launch / CUDA-event duration per launch, against the measured
+             HBM copy bandwidth.
+  cpu_baseline  the reference's own C code path (oracle/_ref) on one host
+             thread, on a bounded sample of the same workload.
+
+N > 1 runs the same model tensor-parallel over N GPUs (strong scaling).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+WORKLOADS = {
+    # name: (architecture, use_fp16, prompt, generate, max_seq)
+    "qwen3-4b-q8": ("qwen3-4b", 0, 512, 512, 4096),
+    "tiny-qwen3-q8": ("tiny-qwen3", 0, 16, 32, 64),
+}
+HBM_FALLBACK_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except Exception:
+                continue
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def gen_f32(S, n, seed, tid, std, threads, mean=0.0):
+    a = np.empty(n, dtype=np.float32)
+    S.llmb200_synth_normal(a.ctypes.data, n, seed, tid, mean, std, threads)
+    return a
+
+
+def build_state_streaming(pkg, L, S, sp, max_seq, use_fp16, threads):
+    """Layer-by-layer construction: at most one layer (plus the LM head) of fp32 weights is held on the host."""
+    cfg = pkg.config_of(sp, pkg.MODEL_QWEN3, max_seq, use_fp16)
+    st = L.llmb200_state_begin(C.byref(cfg))
+    if not st:
+        raise RuntimeError("llmb200_state_begin failed")
+    D, hd, IS, V = sp.d_model, sp.head_dim, sp.intermediate_size, sp.vocab_size
+    shapes = [(sp.n_q_heads * hd, D), (sp.n_kv_heads * hd, D), (sp.n_kv_heads * hd, D), (D, sp.n_q_heads * hd),
+              (IS, D), (IS, D), (D, IS)]
+    ones_d, ones_h = np.ones(D, dtype=np.float32), np.ones(hd, dtype=np.float32)
+    fp = pkg.c_float_p
+    for layer in range(sp.n_layers):
+        mats = [gen_f32(S, r * c, sp.seed, S.llmb200_synth_tensor_id(layer, w), sp.weight_std, threads)
+                for w, (r, c) in enumerate(shapes)]
+        ref = pkg.LayerWeightRef()
+        for name, m, (r, c) in zip(["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"], mats, shapes):
+            setattr(ref, name, pkg.WeightRef(m.ctypes.data_as(fp), r, c))
+        ref.input_norm_g = ones_d.ctypes.data_as(fp)
+        ref.post_attn_norm_g = ones_d.ctypes.data_as(fp)
+        ref.q_norm_g = ones_h.ctypes.data_as(fp)
+        ref.k_norm_g = ones_h.ctypes.data_as(fp)
+        ref.d_model, ref.head_dim = D, hd
+        if L.llmb200_state_load_layer(st, layer, C.byref(ref), C.c_float(sp.rope_theta)) != 0:
+            raise RuntimeError(f"loading layer {layer} failed")
+        L.metal_flush()                      # the staging copies read `mats`; keep them alive until done
+    lm = gen_f32(S, V * D, sp.seed, S.llmb200_synth_tensor_id(0, 101), sp.weight_std, threads)
+    emb = gen_f32(S, V * D, sp.seed, S.llmb200_synth_tensor_id(0, 100), sp.weight_std, threads)
+    if L.llmb200_state_finish(st, lm.ctypes.data_as(fp), ones_d.ctypes.data_as(fp), emb.ctypes.data_as(fp)) != 0:
+        raise RuntimeError("llmb200_state_finish failed")
+    return st
+
+
+def algorithmic_bytes_per_token(sp, n_attend, world=1):
+    """Bytes one decode token has to move per GPU: Q8_0 weights + gammas + F16 K/V rows + one embedding row."""
+    D, hd, IS, V, Lr = sp.d_model, sp.head_dim, sp.intermediate_size, sp.vocab_size, sp.n_layers
+    per_layer = ((sp.n_q_heads + 2 * sp.n_kv_heads) * hd * D + D * sp.n_q_heads * hd + 3 * IS * D) * 34 // 32
+    weights = (Lr * per_layer + V * D * 34 // 32) // world
+    gammas = (Lr * (2 * D + 2 * hd) + D) * 4
+    kv = Lr * 2 * (sp.n_kv_heads // world) * hd * 2 * n_attend
+    return weights + gammas + kv + D * 4
+
+
+def cpu_reference_sample(pkg, S, sp, threads):
+    """Times the reference's C path (oracle/_ref; else the oracle port) on a bounded sample.
+
+    Sample: models with 1 and with 3 of the architecture's layers plus the full LM head, 2 prompt + 2
+    generated tokens each; the per-layer and head times are separated by differencing and the full-depth
+    time per token is their linear combination.
+    """
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _oracle as O
+    use_ref = O.have_ref()
+    prompt = np.zeros(2, dtype=np.uint32)
+    S.llmb200_synth_tokens(prompt.ctypes.data, 2, 4321, sp.vocab_size)
+    per_tok = {}
+    for nl in (1, 3):
+        sub = pkg.SynthSpec.from_buffer_copy(sp)
+        sub.n_layers = nl
+        model = S.llmb200_synth_qwen3(C.byref(sub), threads)
+        out = np.zeros(2, dtype=np.uint32)
+        secs = np.zeros(2, dtype=np.float64)
+        if use_ref:
+            O.ref().ref_requant_qwen3(model, 0)
+            n = O.ref().ref_qwen3_generate(model, prompt.ctypes.data, 2, out.ctypes.data, 2, 8, None, 0, None, secs.ctypes.data)
+            tokens = 2 + (n - 1)
+            per_tok[nl] = float(secs[0] + secs[1]) / tokens
+        else:
+            om = O.model_qwen3(model, 0, 8, vocab=sp.vocab_size)
+            toks, _ = O.generate(om, prompt, 2)
+            per_tok[nl] = sum(O.generate.last_seconds) / (2 + len(toks) - 1)
+            del om
+        S.llmb200_synth_free_qwen3(model)
+    t_layer = max((per_tok[3] - per_tok[1]) / 2.0, 1e-9)
+    t_head = max(per_tok[1] - t_layer, 0.0)
+    t_full = sp.n_layers * t_layer + t_head
+    return {"value": 1.0 / t_full, "unit": "tok/s", "cores": 1, "kind": "reference" if use_ref else "port",
+            "sample": f"1- and 3-layer models of the architecture + full LM head, 4 forwards each (positions 0-3); "
+                      f"{t_layer * 1e3:.0f} ms/layer, {t_head * 1e3:.0f} ms head, extrapolated to {sp.n_layers} layers"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qwen3-4b-q8", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    arch, use_fp16, P, G, max_seq = WORKLOADS[args.workload]
+    pkg = entry.load_package()
+    S = pkg.synth()
+    sp = pkg.spec(arch)
+    threads = max(1, min(32, (os.cpu_count() or 8) // max(world, 1)))
+    config = {"workload": f"{arch} Q8_0 batch-1 greedy decode, prompt {P}, generate {G}, F16 KV cache {max_seq}",
+              "prompt_len": P, "gen_len": G, "kv_cache": "f16", "parallelism": f"tp{world}",
+              "l2": "inputs larger than L2 (weights streamed per token >> 126 MB); no flush needed"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        cb = cpu_reference_sample(pkg, S, sp, threads)
+        line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / cb["value"] * (G - 1),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = pkg.lib()
+    if L.llmb200_set_tp(rank, world) != 0:
+        raise RuntimeError("llmb200_set_tp failed")
+    t0 = time.time()
+    st = build_state_streaming(pkg, L, S, sp, max_seq, use_fp16, threads)
+    if world > 1:
+        h = (C.c_ubyte * pkg.LLMB200_HANDLE_BYTES)()
+        if L.llmb200_state_comm_handle(st, h) != 0:
+            raise RuntimeError("comm handle failed")
+        mine = torch.tensor(list(h), dtype=torch.uint8, device="cuda")
+        allh = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        table = bytes(torch.cat(allh).cpu().numpy().tobytes())
+        if L.llmb200_state_connect(st, table, world) != 0:
+            raise RuntimeError("connect failed")
+        dist.barrier()
+    build_s = time.time() - t0
+    L.llmb200_state_set_eos(st, None, 0)          # uniform random ids: never stop early
+
+    prompt = np.zeros(P, dtype=np.uint32)
+    S.llmb200_synth_tokens(prompt.ctypes.data, P, 4321, sp.vocab_size)
+    out = np.zeros(G, dtype=np.uint32)
+    pp, op = prompt.ctypes.data_as(pkg.c_u32_p), out.ctypes.data_as(pkg.c_u32_p)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def device_step():
+        # prefill + first token through the public call, then the decode forwards from device memory
+        if L.inference_generate(st, pp, P, op, 1) != 1:
+            raise RuntimeError("prefill failed")
+        barrier()
+        ms = L.llmb200_state_run_device_steps(st, G - 1)
+        if ms <= 0:
+            raise RuntimeError("device steps failed")
+        barrier()
+        return max_over_ranks(ms)
+
+    def e2e_step():
+        barrier()
+        n = L.inference_generate(st, pp, P, op, G)
+        nd = C.c_int(0)
+        ms = L.llmb200_last_decode_ms(st, C.byref(nd))
+        barrier()
+        if n != G:
+            raise RuntimeError(f"generate returned {n} tokens")
+        return max_over_ranks(ms), nd.value
+
+    for _ in range(args.warmup):
+        device_step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    step_ms = [device_step() for _ in range(args.steps)]
+    e2e = [e2e_step() for _ in range(args.steps)]
+    clocks = sampler.stop() if rank == 0 else None
+    first_tokens = out[:8].tolist()
+    if L.llmb200_state_error(st):
+        raise RuntimeError("a device-side wait timed out")
+
+    # instrumented pass for the per-kernel roofline (kernel by kernel, CUDA events around each launch)
+    L.inference_generate(st, pp, P, op, 1)
+    L.llmb200_state_run_device_steps(st, (G - 1) // 2)       # to the middle of the decode range
+    kms = (C.c_float * 6)()
+    kl = (C.c_int * 6)()
+    prof = {}
+    acc = np.zeros(6)
+    cnt = np.zeros(6)
+    for _ in range(8):
+        if L.llmb200_state_profile_token(st, kms, kl) != 0:
+            raise RuntimeError("profile pass failed")
+        acc += np.array(list(kms)); cnt += np.array(list(kl))
+    names = ["qkv_matvec", "attention", "o_matvec", "gateup_matvec", "down_matvec", "lm_head_matvec"]
+    for i, nme in enumerate(names):
+        prof[nme] = {"us_per_launch": 1e3 * acc[i] / max(cnt[i], 1), "launches_per_token": int(cnt[i] // 8)}
+    peak, peak_kind = measured_peaks()
+    D, IS = sp.d_model, sp.intermediate_size
+    gu_rows, gu_cols = 2 * IS // world, D
+    gu_bytes = gu_rows * gu_cols * 34 // 32 + 4 * gu_cols + 4 * (gu_rows // 2)
+    gu_s = 1e-6 * prof["gateup_matvec"]["us_per_launch"]
+    achieved = gu_bytes / gu_s / 1e9
+    roofline = {"bound": "hbm", "kernel": "matvec_kernel<Q8> gate/up (rows %d x cols %d)" % (gu_rows, gu_cols),
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                "traffic": None, "algorithmic_bytes_per_launch": gu_bytes}
+
+    n_tok = args.steps * (G - 1)
+    value = n_tok / (sum(step_ms) / 1e3)
+    e2e_ms = sum(m for m, _ in e2e)
+    e2e_tok = sum(n for _, n in e2e)
+    mean_bytes = float(np.mean([algorithmic_bytes_per_token(sp, n, world) for n in range(P + 1, P + G)]))
+    per_token_kernels = L.llmb200_state_graph_kernels(st, 1)
+    line = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sum(step_ms) / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32 accumulate over int8 (Q8_0) weights", "data": "synthetic", "config": config,
+        "e2e": {"value": e2e_tok / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": int(P * 4 + 8),
+                "d2h_bytes_per_step": int(G * 4)},
+        "gpu_launches": int(args.steps * (G - 1) * per_token_kernels),
+        "roofline": roofline,
+        "token_roofline": {"bytes_per_token_per_gpu": mean_bytes, "achieved_gbs": mean_bytes * value / 1e9,
+                           "frac_of_hbm": mean_bytes * value / 1e9 / peak, "peak_source": peak_kind},
+        "kernels": prof, "clocks": clocks, "ms_per_token": sum(step_ms) / n_tok, "build_seconds": build_s,
+        "first_tokens": first_tokens,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        if rank == 0:
+            line["cpu_baseline"] = cpu_reference_sample(pkg, S, sp, threads)
+    L.inference_state_free(st)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

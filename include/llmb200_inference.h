@@ -115,6 +115,8 @@ int llmb200_state_profile_token(InferenceState *state, float *ms, int *launches)
 /* Bytes of weights one token streams on this rank (all matrices + LM head). */
 unsigned long long llmb200_state_weight_bytes(InferenceState *state);
 int llmb200_state_position(InferenceState *state);
+/* Kernel nodes in the per-token graph (with or without the LM head launch). */
+int llmb200_state_graph_kernels(InferenceState *state, int with_lm_head);
 /* Copies the packed device weights of one matrix back as the reference's
  * canonical bytes (Q8_0 34-byte blocks or binary16), for parity checks.
  * which: 0 qkv (this rank's q rows, then k rows, then v rows), 1 o, 2 gate/up

@@ -83,6 +83,7 @@ struct InferenceState {
     cudaEvent_t tok_ev[4];
     cudaEvent_t ev_a, ev_b;
     cudaGraphExec_t g_full, g_nolm;
+    int kernels_full, kernels_nolm;   /* kernel nodes per graph */
     int use_pdl;
     int cur_len;
     double last_decode_ms, last_prefill_ms;
@@ -470,7 +471,10 @@ static int capture(InferenceState *s, int with_lm, int pdl, cudaGraphExec_t *out
 {
     cudaGraph_t g = NULL;
     CU_TRY(cudaStreamBeginCapture(g_rt.stream, cudaStreamCaptureModeThreadLocal), return -1);
+    const unsigned long long before = b200_launch_count(0);
     int rc = enqueue_token(s, with_lm, pdl);
+    if (with_lm) s->kernels_full = (int)(b200_launch_count(0) - before);
+    else s->kernels_nolm = (int)(b200_launch_count(0) - before);
     cudaError_t e = cudaStreamEndCapture(g_rt.stream, &g);
     if (rc != 0 || e != cudaSuccess || !g) {
         if (g) cudaGraphDestroy(g);
@@ -649,6 +653,11 @@ ModelType inference_state_model_type(InferenceState *s) { return s->mt; }
 int inference_state_vocab_size(InferenceState *s) { return s->V; }
 void inference_state_reset(InferenceState *s) { s->cur_len = 0; }
 int llmb200_state_position(InferenceState *s) { return s ? s->cur_len : -1; }
+int llmb200_state_graph_kernels(InferenceState *s, int with_lm_head)
+{
+    if (!s || ensure_graphs(s) != 0) return -1;
+    return with_lm_head ? s->kernels_full : s->kernels_nolm;
+}
 unsigned long long llmb200_state_weight_bytes(InferenceState *s) { return s ? s->weight_bytes : 0; }
 double llmb200_last_decode_ms(InferenceState *s, int *n) { if (n) *n = s->last_n_decoded; return s->last_decode_ms; }
 double llmb200_last_prefill_ms(InferenceState *s) { return s->last_prefill_ms; }

@@ -1,0 +1,227 @@
+"""End-to-end parity of the decode engine (through the reference-facing C API) against the CPU oracle.
+
+Bars (the north-star's): Q8_0 bytes on the device bit-exact; logits within 1e-2 of max|logit| at every
+step; greedy tokens identical over the first 32 generated.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import _oracle as O
+
+pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def make_prompt(synth, n, vocab, seed=4321):
+    p = np.zeros(n, dtype=np.uint32)
+    synth.llmb200_synth_tokens(p.ctypes.data, n, seed, vocab)
+    return p
+
+
+def gpu_generate(lib, pkg, state, prompt, max_gen):
+    out = np.zeros(max_gen, dtype=np.uint32)
+    n = lib.inference_generate(state, prompt.ctypes.data_as(pkg.c_u32_p), len(prompt), out.ctypes.data_as(pkg.c_u32_p), max_gen)
+    assert lib.llmb200_state_error(state) == 0
+    return out[:n]
+
+
+def gpu_logits_trace(lib, state, tokens, vocab):
+    """Feeds `tokens` one by one through inference_forward_token; returns logits [len(tokens), V]."""
+    lib.inference_state_reset(state)
+    rows = []
+    for t in tokens:
+        p = lib.inference_forward_token(state, int(t))
+        assert p
+        rows.append(np.ctypeslib.as_array(p, shape=(vocab,)).copy())
+    return np.stack(rows)
+
+
+def check_against_oracle(lib, pkg, synth, model, omodel, state, vocab, P, G, max_seq):
+    prompt = make_prompt(synth, P, vocab)
+    lib.llmb200_state_set_eos(state, None, 0)
+    got = gpu_generate(lib, pkg, state, prompt, G)
+    ref_tok, ref_lg = O.generate(omodel, prompt, G, vocab=vocab, want_logits=True)
+    assert len(got) == G == len(ref_tok)
+    # logits along the *reference's* token path, so a single flipped token cannot hide later errors
+    seq = np.concatenate([prompt, ref_tok[:-1]])
+    lg = gpu_logits_trace(lib, state, seq, vocab)[P - 1:]
+    rel = np.abs(lg - ref_lg).max(axis=1) / np.abs(ref_lg).max(axis=1)
+    assert rel.max() <= 1e-2, f"logit error {rel.max():.3e}"
+    if list(got) != list(ref_tok):
+        k = next(i for i in range(G) if got[i] != ref_tok[i])
+        top2 = np.sort(ref_lg[k])[-2:]
+        pytest.fail(f"greedy token {k} differs: gpu {got[k]} vs oracle {ref_tok[k]}; oracle top-2 gap {top2[1] - top2[0]:.3e}, "
+                    f"logit error at that step {np.abs(lg[k] - ref_lg[k]).max():.3e}")
+    return rel.max()
+
+
+@pytest.mark.parametrize("use_fp16", [0, 1])
+def test_tiny_qwen3_matches_oracle(lib, pkg, synth, use_fp16):
+    sp = pkg.spec("tiny-qwen3", gamma_jitter=0.1)
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 8)
+    state = lib.inference_state_create(model, 64, use_fp16)
+    assert state
+    try:
+        omodel = O.model_qwen3(model, use_fp16, 64, vocab=sp.vocab_size)
+        check_against_oracle(lib, pkg, synth, model, omodel, state, sp.vocab_size, 16, 32, 64)
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model)
+
+
+def test_tiny_qwen3_device_weights_bit_exact(lib, pkg, synth):
+    sp = pkg.spec("tiny-qwen3")
+    model_p = synth.llmb200_synth_qwen3(C.byref(sp), 8)
+    state = lib.inference_state_create(model_p, 32, 0)
+    assert state
+    try:
+        D, hd, IS = sp.d_model, sp.head_dim, sp.intermediate_size
+
+        def gen(layer, which, rows, cols):
+            w = np.empty((rows, cols), dtype=np.float32)
+            synth.llmb200_synth_normal(w.ctypes.data, w.size, sp.seed, synth.llmb200_synth_tensor_id(layer, which), 0.0, 0.02, 4)
+            return w
+
+        def export(layer, which):
+            n = lib.llmb200_state_export_weight(state, layer, which, None, 0)
+            buf = np.zeros(n, dtype=np.uint8)
+            assert lib.llmb200_state_export_weight(state, layer, which, buf.ctypes.data, n) == n
+            return buf
+        for layer in (0, sp.n_layers - 1):
+            q, k, v = gen(layer, 0, sp.n_q_heads * hd, D), gen(layer, 1, sp.n_kv_heads * hd, D), gen(layer, 2, sp.n_kv_heads * hd, D)
+            assert np.array_equal(export(layer, 0), O.q8_quantize(np.concatenate([q, k, v])))
+            assert np.array_equal(export(layer, 1), O.q8_quantize(gen(layer, 3, D, sp.n_q_heads * hd)))
+            g, u = gen(layer, 4, IS, D), gen(layer, 5, IS, D)
+            gu = np.empty((2 * IS, D), dtype=np.float32)
+            gu[0::2], gu[1::2] = g, u
+            assert np.array_equal(export(layer, 2), O.q8_quantize(gu))
+            assert np.array_equal(export(layer, 3), O.q8_quantize(gen(layer, 6, D, IS)))
+        lm = gen(0, 101, sp.vocab_size, D)
+        assert np.array_equal(export(0, 4), O.q8_quantize(lm))
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model_p)
+
+
+@pytest.mark.parametrize("use_fp16", [1, 0])
+def test_tiny_gemma3_matches_oracle(lib, pkg, synth, use_fp16):
+    sp = pkg.spec("tiny-gemma3", gamma_jitter=0.1)
+    model = synth.llmb200_synth_gemma3(C.byref(sp), 8)
+    state = lib.inference_state_create_gemma3(model, 96, use_fp16)
+    assert state
+    try:
+        assert lib.inference_state_model_type(state) == pkg.MODEL_GEMMA3
+        omodel = O.model_gemma3(model, use_fp16, 96, vocab=sp.vocab_size)
+        check_against_oracle(lib, pkg, synth, model, omodel, state, sp.vocab_size, 24, 32, 96)
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_gemma3(model)
+
+
+def test_generate_semantics(lib, pkg, synth):
+    """Count, EOS and cache-limit behaviour of inference_generate (src/nn/fast_inference.c:614-675)."""
+    sp = pkg.spec("tiny-qwen3")
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 8)
+    state = lib.inference_state_create(model, 40, 0)
+    assert state
+    try:
+        assert lib.inference_state_vocab_size(state) == sp.vocab_size
+        assert lib.inference_state_model_type(state) == pkg.MODEL_QWEN3
+        prompt = make_prompt(synth, 16, sp.vocab_size)
+        lib.llmb200_state_set_eos(state, None, 0)
+        full = gpu_generate(lib, pkg, state, prompt, 64)
+        # stops when the KV cache is full: 16 prompt + 24 forwards = 40 positions, 25 tokens out
+        assert len(full) == 25
+        again = gpu_generate(lib, pkg, state, prompt, 64)
+        assert list(full) == list(again)               # the request resets the state
+        # EOS: the EOS token is returned as the last token and nothing follows it
+        eos = (C.c_int * 1)(int(full[5]))
+        lib.llmb200_state_set_eos(state, eos, 1)
+        cut = gpu_generate(lib, pkg, state, prompt, 64)
+        first = list(full).index(full[5])
+        assert list(cut) == list(full[:first + 1])
+        # max_gen_len = 1: only the prefill argmax
+        lib.llmb200_state_set_eos(state, None, 0)
+        assert list(gpu_generate(lib, pkg, state, prompt, 1)) == [full[0]]
+        # one-token prompt
+        one = gpu_generate(lib, pkg, state, prompt[:1], 4)
+        om = O.model_qwen3(model, 0, 40, vocab=sp.vocab_size)
+        ref, _ = O.generate(om, prompt[:1], 4)
+        assert list(one) == list(ref)
+        # bad input is refused without touching the device
+        assert lib.inference_generate(state, prompt.ctypes.data_as(pkg.c_u32_p), 0, full.ctypes.data_as(pkg.c_u32_p), 4) == 0
+        big = np.full(41, 1, dtype=np.uint32)
+        assert lib.inference_generate(state, big.ctypes.data_as(pkg.c_u32_p), 41, full.ctypes.data_as(pkg.c_u32_p), 4) == 0
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model)
+
+
+def test_max_seq_is_clamped_and_long_context(lib, pkg, synth):
+    """max_seq_len > 4096 is clamped (src/nn/fast_inference.c:183-186); attention over a long cache stays exact."""
+    sp = pkg.spec("tiny-qwen3", n_layers=1, vocab_size=512)
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 8)
+    state = lib.inference_state_create(model, 5000, 0)
+    assert state
+    try:
+        P = 700
+        prompt = make_prompt(synth, P, sp.vocab_size)
+        lib.llmb200_state_set_eos(state, None, 0)
+        got = gpu_generate(lib, pkg, state, prompt, 8)
+        om = O.model_qwen3(model, 0, P + 8, vocab=sp.vocab_size)
+        ref, _ = O.generate(om, prompt, 8)
+        assert list(got) == list(ref)
+        big = np.zeros(4097, dtype=np.uint32)
+        out = np.zeros(2, dtype=np.uint32)
+        assert lib.inference_generate(state, big.ctypes.data_as(pkg.c_u32_p), 4097, out.ctypes.data_as(pkg.c_u32_p), 2) == 0
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model)
+
+
+def test_load_eos_from_config(lib, pkg, synth, tmp_path):
+    sp = pkg.spec("tiny-qwen3", n_layers=1, vocab_size=512)
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 4)
+    state = lib.inference_state_create(model, 32, 0)
+    assert state
+    try:
+        prompt = make_prompt(synth, 8, sp.vocab_size)
+        lib.llmb200_state_set_eos(state, None, 0)
+        full = gpu_generate(lib, pkg, state, prompt, 12)
+        (tmp_path / "config.json").write_text('{"model_type": "qwen3", "eos_token_id": [%d, 999999]}' % int(full[3]))
+        lib.inference_state_load_eos(state, str(tmp_path).encode())
+        cut = gpu_generate(lib, pkg, state, prompt, 12)
+        assert list(cut) == list(full[:list(full).index(full[3]) + 1])
+        (tmp_path / "config.json").write_text('{"eos_token_id": -1}')
+        lib.inference_state_load_eos(state, str(tmp_path / "model.safetensors").encode())
+        assert list(gpu_generate(lib, pkg, state, prompt, 12)) == list(full)
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model)
+
+
+def test_wmat_api_roundtrip(lib, pkg, synth):
+    """wmat_create_q8 / metal_buf_ptr give back the reference's canonical bytes (src/nn/wmat.c:47-75)."""
+    rows, cols = 96, 512
+    w = np.empty((rows, cols), dtype=np.float32)
+    synth.llmb200_synth_normal(w.ctypes.data, w.size, 1, 2, 0.0, 0.02, 1)
+    wm = lib.wmat_create_q8(w.ctypes.data_as(pkg.c_float_p), rows, cols)
+    assert wm and wm.contents.rows == rows and wm.contents.cols == cols and wm.contents.nb == cols // 32
+    p = lib.metal_buf_ptr(wm.contents.mbuf)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(rows * (cols // 32) * 34,)).copy()
+    assert np.array_equal(got, O.q8_quantize(w))
+    lib.wmat_free(wm)
+    wf = lib.wmat_convert(w.ctypes.data_as(pkg.c_float_p), rows, cols, 1)
+    assert wf and wf.contents.nb == 0
+    p = lib.metal_buf_ptr(wf.contents.mbuf)
+    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint16)), shape=(rows, cols)).copy()
+    assert np.array_equal(got, O.f16_bits(w))
+    lib.wmat_free(wf)
+    b = lib.metal_buf_from_data(w.ctypes.data, w.nbytes)
+    got = np.ctypeslib.as_array(C.cast(lib.metal_buf_ptr(b), C.POINTER(C.c_float)), shape=(rows, cols)).copy()
+    assert np.array_equal(got, w)
+    lib.metal_buf_free(b)
+    lib.metal_buf_free(None)
+    assert not lib.wmat_create_q8(w.ctypes.data_as(pkg.c_float_p), rows, 40)     # cols % 32 != 0
