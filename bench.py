@@ -193,17 +193,24 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-4b-q8", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (profiling runs)")
+    ap.add_argument("--gen-len", type=int, default=0, help="override the workload's generation length (profiling runs)")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (small ncu captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     arch, use_fp16, P, G, max_seq = WORKLOADS[args.workload]
+    P, G = args.prompt_len or P, args.gen_len or G
     pkg = entry.load_package()
     S = pkg.synth()
     sp = pkg.spec(arch)
+    if args.layers:
+        sp.n_layers = args.layers
     threads = max(1, min(32, (os.cpu_count() or 8) // max(world, 1)))
-    config = {"workload": f"{arch} Q8_0 batch-1 greedy decode, prompt {P}, generate {G}, F16 KV cache {max_seq}",
+    config = {"workload": f"{arch}{'' if not args.layers else f' cut to {args.layers} layers'} Q8_0 batch-1 greedy decode, "
+                          f"prompt {P}, generate {G}, F16 KV cache {max_seq}",
               "prompt_len": P, "gen_len": G, "kv_cache": "f16", "parallelism": f"tp{world}",
               "l2": "inputs larger than L2 (weights streamed per token >> 126 MB); no flush needed"}
 

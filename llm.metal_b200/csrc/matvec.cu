@@ -1,21 +1,31 @@
 // Fused weight-streaming matrix-vector product for batch-1 decode (sm_100a).
 //
-// Work split: a block owns a contiguous range of rows; its threads own fixed
-// 16-byte column slices (16 int8 quants or 8 halves) of every row. The input
-// vector slice of a thread therefore lives in registers for the whole kernel,
-// a warp reads 512 contiguous bytes of a row per load instruction, and a row's
-// dot product is completed by one pass over per-thread partials kept in shared
-// memory (fixed summation order, so results are reproducible run to run).
-// Grids are sized to a multiple of the SM count with all blocks resident.
+// One block per SM slot owns a contiguous range of rows. A producer warp
+// streams that range through a shared-memory ring with bulk asynchronous
+// copies (TMA, cp.async.bulk + mbarrier): rows of a packed matrix are
+// contiguous, so one copy instruction moves a whole stage (RB rows, 16-24 KB)
+// and the ring keeps ~100 KB per block in flight without holding registers.
+// Consumer threads own fixed 16-byte column slices (16 int8 quants or 8
+// halves) of every row, so their slice of the input vector stays in registers
+// for the whole kernel; consumer groups take stages round-robin, finish the RB
+// rows of a stage with one transposing shuffle reduction per warp plus a
+// fixed-order sum over the group's warps (reproducible run to run).
+//
+// The block is sized (<= ~100 KB shared memory, <= 32K registers) so that a
+// block of the NEXT kernel in the stream fits beside it: launched with
+// programmatic dependent launch, that block fills its own ring with weights
+// while this kernel is still running and only then waits for its input.
 //
 // The math is the reference's q8_matvec / f16_matvec
 // (shaders/q8_kernels.metal:10-42, 97-127): fp32 activations, integer quants
-// converted to fp32, fp32 multiply-accumulate, block sum scaled by the
-// binary16 block scale. Input assembly and the epilogues fold in rms_norm
+// converted to fp32, fp32 multiply-accumulate, partial block sums scaled by
+// the binary16 block scale. Input assembly and the epilogues fold in rms_norm
 // (:133-157), residual_add (:369-375), silu_mul / gelu_mul (:337-363), the
 // embedding copy (src/nn/fast_inference.c:386-392) and argmax (:469-476).
 #include "common.cuh"
 #include "../../include/llmb200_kernels.h"
+
+#include <stdlib.h>
 
 unsigned long long g_b200_launches = 0;
 
@@ -28,39 +38,98 @@ extern "C" unsigned long long b200_launch_count(int reset)
 
 namespace {
 
-// int8 -> fp32 through the 2^23 trick: byte b (biased by 128) is dropped into
-// the low mantissa byte of 0x4B000000 (= 8388608.0f); subtracting 8388736.0f
-// leaves the signed value exactly. One PRMT + one FADD per element.
-__device__ __forceinline__ float q8_to_f32(uint32_t biased_word, int k)
+// ---- mbarrier / bulk-copy primitives ------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *b, unsigned count)
 {
-    return __uint_as_float(__byte_perm(biased_word, 0x4B000000u, 0x7650u + k)) - 8388736.0f;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *b, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *b)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *b, unsigned parity)
+{
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after ~a second instead of hanging the GPU.
+__device__ __forceinline__ bool mbar_wait(uint64_t *b, unsigned parity)
+{
+    for (int it = 0; it < (1 << 22); ++it)
+        if (mbar_try_wait(b, parity)) return true;
+    return false;
+}
+// Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, unsigned bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint4 lds_128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// binary16 bits of a block scale (never negative) -> fp32 without the conversion unit: the bits moved
+// to the fp32 exponent/mantissa position are the value times 2^-112, exact for normals and subnormals.
+__device__ __forceinline__ float scale_f32(uint32_t h)
+{
+    float f = __uint_as_float(h << 13) * 5192296858534827628530496329220096.0f;   // 2^112
+    if ((h & 0x7c00u) == 0x7c00u) f = __half2float(__ushort_as_half((unsigned short)h));   // inf / nan
+    return f;
+}
+__device__ __forceinline__ void named_barrier(int id, int count)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// ---- arithmetic -----------------------------------------------------------
+// int8 -> fp32 through the 2^23 trick: a byte biased by 128 is dropped into the
+// low mantissa byte of 0x4B000000 (= 8388608.0f); subtracting 8388736.0f leaves
+// the signed value exactly. Conversion and multiply-add run two elements per
+// instruction on the packed fp32 pipe (add.f32x2 / fma.rn.f32x2).
+__device__ __forceinline__ float2 q8_pair(uint32_t biased_word, int k)
+{
+    float2 f;
+    f.x = __uint_as_float(__byte_perm(biased_word, 0x4B000000u, 0x7650u + k));
+    f.y = __uint_as_float(__byte_perm(biased_word, 0x4B000000u, 0x7651u + k));
+    return __fadd2_rn(f, make_float2(-8388736.0f, -8388736.0f));
 }
 
 __device__ __forceinline__ float dot16_q8(const uint4 &w, const float *x)
 {
     const uint32_t u[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        s0 = fmaf(q8_to_f32(u[i], 0), x[4 * i + 0], s0);
-        s1 = fmaf(q8_to_f32(u[i], 1), x[4 * i + 1], s1);
-        s2 = fmaf(q8_to_f32(u[i], 2), x[4 * i + 2], s2);
-        s3 = fmaf(q8_to_f32(u[i], 3), x[4 * i + 3], s3);
+        a = __ffma2_rn(q8_pair(u[i], 0), make_float2(x[4 * i + 0], x[4 * i + 1]), a);
+        b = __ffma2_rn(q8_pair(u[i], 2), make_float2(x[4 * i + 2], x[4 * i + 3]), b);
     }
-    return (s0 + s1) + (s2 + s3);
+    return (a.x + a.y) + (b.x + b.y);
 }
 
 __device__ __forceinline__ float dot8_f16(const uint4 &w, const float *x)
 {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-    float s0 = 0.f, s1 = 0.f;
+    float2 a = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[i]));
-        s0 = fmaf(f.x, x[2 * i + 0], s0);
-        s1 = fmaf(f.y, x[2 * i + 1], s1);
-    }
-    return s0 + s1;
+    for (int i = 0; i < 4; ++i)
+        a = __ffma2_rn(__half22float2(*reinterpret_cast<const __half2 *>(&u[i])), make_float2(x[2 * i], x[2 * i + 1]), a);
+    return a.x + a.y;
 }
 
 __device__ __forceinline__ float act_silu(float g) { return g / (1.0f + expf(-g)); }
@@ -76,56 +145,112 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi)
     return v > bv || (v == bv && i < bi);
 }
 
+// Sum of v over the T threads of one consumer group; every thread gets it.
+__device__ __forceinline__ float group_sum(float v, float *red, int bar_id, int T, int t)
+{
+    const int lane = t & 31, w = t >> 5, nw = T >> 5;
+    v = warp_sum(v);
+    named_barrier(bar_id, T);              // protect `red` from a previous use
+    if (lane == 0) red[w] = v;
+    named_barrier(bar_id, T);
+    float tot = 0.0f;
+    for (int i = 0; i < nw; ++i) tot += red[i];
+    return tot;
+}
+
+// v[j] holds this lane's partial of row j. Returns, in every lane, the warp
+// total of row (lane & (RB-1)): RB-1 exchanges fold the rows across lane bits,
+// the remaining log2(32/RB) butterflies add the lane groups.
+template <int RB>
+__device__ __forceinline__ float reduce_rows(float (&v)[RB], int lane)
+{
+#pragma unroll
+    for (int h = RB / 2; h >= 1; h >>= 1) {
+        const bool up = (lane & h) != 0;
+#pragma unroll
+        for (int j = 0; j < h; ++j) {
+            const float send = up ? v[j] : v[j + h];
+            const float keep = up ? v[j + h] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+        }
+    }
+    float tot = v[0];
+#pragma unroll
+    for (int o = RB; o < 32; o <<= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    return tot;
+}
+
+struct Geometry {
+    int T;              // threads per consumer group (a multiple of 32)
+    int NG;             // consumer groups
+    int nstage;         // ring slots
+    unsigned slot_bytes;  // bytes per slot (RB rows, rounded up to 128)
+    int dbg;            // diagnostics: 1 = no arithmetic, 2 = no waiting for data after the first ring fill
+};
+
+// blockDim.x = NG*T consumers + 32 producer threads.
 template <int WT, int SPT, int RB, int MAXT>
 __global__ void __launch_bounds__(MAXT)
-matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
+matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
 {
     constexpr int E = (WT == B200_WT_Q8) ? 16 : 8;       // elements per 16-byte slice
-    extern __shared__ __align__(16) float smem[];
-    const int T = blockDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = T >> 5;
-    float *part = smem;                  // [rmax][T]
-    float *red = smem + (size_t)rmax * T;  // 40 floats of reduction scratch, then argmax scratch
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int T = geo.T, NG = geo.NG, nstage = geo.nstage, nwg = T >> 5, nC = NG * T;
+    unsigned char *ring = smem_raw;
+    uint64_t *full = reinterpret_cast<uint64_t *>(ring + (size_t)nstage * geo.slot_bytes);
+    uint64_t *empty = full + nstage;
+    float *wpart = reinterpret_cast<float *>(empty + nstage);   // [NG][2][nwg][RB]
+    float *red = wpart + (size_t)NG * 2 * nwg * RB;             // [NG][32]
+    float *am_v = red + NG * 32;                                // [NG*RB]
+    int *am_i = reinterpret_cast<int *>(am_v + NG * RB);        // [NG*RB]
     __shared__ int s_last;
 
+    const int tid = threadIdx.x;
     const int ralign = (p.out_mode == B200_OUT_GLU) ? 2 : 1;
     const long long units = p.rows / ralign;
     const int r0 = (int)(units * blockIdx.x / gridDim.x) * ralign;
     const int r1 = (int)(units * (blockIdx.x + 1) / gridDim.x) * ralign;
+    const int nst = (r1 - r0 + RB - 1) / RB;
 
+    if (tid == 0) {
+        for (int i = 0; i < nstage; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], T); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // Every thread signals: the next kernel in the stream may be scheduled now and start
+    // filling its own ring beside this block.
+    pdl_launch_dependents();
+
+    // ---------------- producer warp: weights depend on no earlier kernel ----------------
+    if (tid >= nC) {
+        if (tid == nC) {
+            const unsigned char *wbase = static_cast<const unsigned char *>(p.d_w);
+            for (int i = 0; i < nst; ++i) {
+                const int slot = i % nstage;
+                if ((geo.dbg & 2) && i >= nstage) break;
+                if (i >= nstage && !mbar_wait(&empty[slot], ((i / nstage) - 1) & 1)) {
+                    if (p.d_err) *p.d_err = 2;
+                    break;
+                }
+                const int row0 = r0 + i * RB;
+                const int nr = min(RB, r1 - row0);
+                const unsigned bytes = (unsigned)nr * (unsigned)p.row_stride;
+                mbar_expect_tx(&full[slot], bytes);
+                bulk_load(ring + (size_t)slot * geo.slot_bytes, wbase + (long long)row0 * p.row_stride, bytes, &full[slot]);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int g = tid / T, t = tid - g * T, lane = t & 31, wg = t >> 5;
+    float *gred = red + g * 32;
     int col[SPT];
     bool on[SPT];
 #pragma unroll
-    for (int s = 0; s < SPT; ++s) { col[s] = (s * T + tid) * E; on[s] = col[s] < p.cols; }
+    for (int s = 0; s < SPT; ++s) { col[s] = (s * T + t) * E; on[s] = col[s] < p.cols; }
 
-    const uint8_t *wbase = static_cast<const uint8_t *>(p.d_w);
-    const long long scale_off = (long long)p.cols;        // Q8: scales follow the quants of a row
-
-    uint4 wq[RB][SPT];
-    unsigned short ws[RB][SPT];
-    auto load_batch = [&](int r, int rend) {
-#pragma unroll
-        for (int i = 0; i < RB; ++i) {
-            if (r + i < rend) {
-                const uint8_t *row = wbase + (long long)(r + i) * p.row_stride;
-#pragma unroll
-                for (int s = 0; s < SPT; ++s) {
-                    if (on[s]) {
-                        if (WT == B200_WT_Q8) {
-                            wq[i][s] = ldg_stream_16(row + col[s]);
-                            ws[i][s] = ldg_stream_u16(row + scale_off + (col[s] >> 5) * 2);
-                        } else {
-                            wq[i][s] = ldg_stream_16(row + (long long)col[s] * 2);
-                        }
-                    }
-                }
-            }
-        }
-    };
-
-    // Weights depend on no earlier kernel: start streaming them, and let the
-    // next kernel in the stream start doing the same, before waiting.
-    pdl_launch_dependents();
-    load_batch(r0, min(r0 + rmax, r1));
     pdl_wait();
 
     // Tensor parallel: every rank's partial vector must have landed in `slots`
@@ -136,18 +261,18 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
             const unsigned want = (*p.d_epoch) * (unsigned)p.epoch_mul + (unsigned)p.epoch_add;
             if (!wait_flag_ge(p.d_wait_flags + tid, want)) *p.d_err = 1;
         }
-        __syncthreads();
+        named_barrier(1, nC);
     }
 
-    // ---------------- input assembly ----------------
+    // ---------------- input assembly (each group builds the same vector) ----------------
     float x[SPT][E];
     if (p.in_mode == B200_IN_VEC) {
 #pragma unroll
         for (int s = 0; s < SPT; ++s)
 #pragma unroll
             for (int e = 0; e < E; e += 4) {
-                float4 t = on[s] ? *reinterpret_cast<const float4 *>(p.d_in_vec + col[s] + e) : make_float4(0, 0, 0, 0);
-                x[s][e] = t.x; x[s][e + 1] = t.y; x[s][e + 2] = t.z; x[s][e + 3] = t.w;
+                float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(p.d_in_vec + col[s] + e) : make_float4(0, 0, 0, 0);
+                x[s][e] = v4.x; x[s][e + 1] = v4.y; x[s][e + 2] = v4.z; x[s][e + 3] = v4.w;
             }
     } else {
         if (p.in_mode == B200_IN_EMBED) {
@@ -157,9 +282,9 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
             for (int s = 0; s < SPT; ++s)
 #pragma unroll
                 for (int e = 0; e < E; e += 4) {
-                    float4 t = on[s] ? *reinterpret_cast<const float4 *>(er + col[s] + e) : make_float4(0, 0, 0, 0);
-                    x[s][e] = t.x * p.emb_scale; x[s][e + 1] = t.y * p.emb_scale;
-                    x[s][e + 2] = t.z * p.emb_scale; x[s][e + 3] = t.w * p.emb_scale;
+                    float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(er + col[s] + e) : make_float4(0, 0, 0, 0);
+                    x[s][e] = v4.x * p.emb_scale; x[s][e + 1] = v4.y * p.emb_scale;
+                    x[s][e + 2] = v4.z * p.emb_scale; x[s][e + 3] = v4.w * p.emb_scale;
                 }
         } else {
             float sacc[SPT][E];
@@ -175,8 +300,8 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
                     for (int e = 0; e < E; e += 4) {
                         if (on[s]) {
                             // slots may be written by other GPUs: read them past L1
-                            float4 t = __ldcv(reinterpret_cast<const float4 *>(sl + col[s] + e));
-                            sacc[s][e] += t.x; sacc[s][e + 1] += t.y; sacc[s][e + 2] += t.z; sacc[s][e + 3] += t.w;
+                            float4 v4 = __ldcv(reinterpret_cast<const float4 *>(sl + col[s] + e));
+                            sacc[s][e] += v4.x; sacc[s][e + 1] += v4.y; sacc[s][e + 2] += v4.z; sacc[s][e + 3] += v4.w;
                         }
                     }
             }
@@ -186,7 +311,7 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
                 for (int s = 0; s < SPT; ++s)
 #pragma unroll
                     for (int e = 0; e < E; ++e) ss = fmaf(sacc[s][e], sacc[s][e], ss);
-                ss = block_sum(ss, red);
+                ss = group_sum(ss, gred, 2 + g, T, t);
                 const float inv = 1.0f / sqrtf(ss / (float)p.cols + p.eps);
 #pragma unroll
                 for (int s = 0; s < SPT; ++s)
@@ -198,12 +323,12 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
             for (int s = 0; s < SPT; ++s)
 #pragma unroll
                 for (int e = 0; e < E; e += 4) {
-                    float4 t = on[s] ? *reinterpret_cast<const float4 *>(p.d_resid_in + col[s] + e) : make_float4(0, 0, 0, 0);
-                    x[s][e] = t.x + sacc[s][e]; x[s][e + 1] = t.y + sacc[s][e + 1];
-                    x[s][e + 2] = t.z + sacc[s][e + 2]; x[s][e + 3] = t.w + sacc[s][e + 3];
+                    float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(p.d_resid_in + col[s] + e) : make_float4(0, 0, 0, 0);
+                    x[s][e] = v4.x + sacc[s][e]; x[s][e + 1] = v4.y + sacc[s][e + 1];
+                    x[s][e + 2] = v4.z + sacc[s][e + 2]; x[s][e + 3] = v4.w + sacc[s][e + 3];
                 }
         }
-        if (blockIdx.x == 0 && p.d_resid_out) {
+        if (blockIdx.x == 0 && g == 0 && p.d_resid_out) {
 #pragma unroll
             for (int s = 0; s < SPT; ++s)
 #pragma unroll
@@ -219,7 +344,7 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
         for (int s = 0; s < SPT; ++s)
 #pragma unroll
             for (int e = 0; e < E; ++e) ss = fmaf(x[s][e], x[s][e], ss);
-        ss = block_sum(ss, red);
+        ss = group_sum(ss, gred, 2 + g, T, t);
         const float inv = 1.0f / sqrtf(ss / (float)p.cols + p.eps);
 #pragma unroll
         for (int s = 0; s < SPT; ++s)
@@ -228,77 +353,95 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const int rmax)
                 if (on[s]) x[s][e] = p.d_norm_gamma[col[s] + e] * x[s][e] * inv;
     }
 
-    // ---------------- stream the rows ----------------
+    // ---------------- consume the ring: group g takes stages g, g+NG, ... ----------------
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int rb = r0; rb < r1; rb += rmax) {
-        const int rend = min(rb + rmax, r1);
-        for (int r = rb; r < rend; r += RB) {
-            if (r != r0) load_batch(r, rend);
+    // Byte offsets of this thread's slices inside a row. Threads past the end of the row read slice 0
+    // (valid memory) against a zero input slice and drop the result.
+    uint32_t qoff[SPT], soff[SPT];
 #pragma unroll
-            for (int i = 0; i < RB; ++i) {
-                if (r + i < rend) {
-                    float v = 0.0f;
+    for (int s = 0; s < SPT; ++s) {
+        const int c = on[s] ? col[s] : 0;
+        qoff[s] = (uint32_t)(WT == B200_WT_Q8 ? c : 2 * c);
+        soff[s] = (uint32_t)p.cols + (uint32_t)(c >> 5) * 2u;   // Q8: scales follow the quants of a row
+    }
+    const uint32_t ring_s = smem_u32(ring), stride = (uint32_t)p.row_stride;
+    for (int i = g, it = 0; i < nst; i += NG, ++it) {
+        const int slot = i % nstage;
+        if (!((geo.dbg & 2) && i >= nstage))
+        if (!mbar_wait(&full[slot], (i / nstage) & 1) && p.d_err) *p.d_err = 3;
+        if (geo.dbg & 1) { mbar_arrive(&empty[slot]); continue; }
+        const uint32_t sb = ring_s + (uint32_t)slot * geo.slot_bytes;
+        const int row0 = r0 + i * RB;
+        const int nr = min(RB, r1 - row0);
+        // Rows past nr hold stale bytes; they are computed like the others (no predicates in the
+        // hot loop), stay in their own reduction lane and are never emitted.
+        uint4 wq[RB][SPT];
+        uint32_t ws[RB][SPT];
 #pragma unroll
-                    for (int s = 0; s < SPT; ++s) {
-                        if (on[s]) {
-                            if (WT == B200_WT_Q8)
-                                v = fmaf(__half2float(__ushort_as_half(ws[i][s])), dot16_q8(wq[i][s], x[s]), v);
-                            else
-                                v += dot8_f16(wq[i][s], x[s]);
-                        }
-                    }
-                    part[(size_t)(r + i - rb) * T + tid] = v;
-                }
+        for (int j = 0; j < RB; ++j)
+#pragma unroll
+            for (int s = 0; s < SPT; ++s) {
+                wq[j][s] = lds_128(sb + (uint32_t)j * stride + qoff[s]);
+                if (WT == B200_WT_Q8) ws[j][s] = lds_u16(sb + (uint32_t)j * stride + soff[s]);
             }
+        float v[RB];
+#pragma unroll
+        for (int j = 0; j < RB; ++j) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int s = 0; s < SPT; ++s) {
+                float d;
+                if (WT == B200_WT_Q8) d = scale_f32(ws[j][s]) * dot16_q8(wq[j][s], x[s]);
+                else d = dot8_f16(wq[j][s], x[s]);
+                acc += on[s] ? d : 0.0f;
+            }
+            v[j] = acc;
         }
-        __syncthreads();
-        // one warp finishes one row (or one gate/up pair): fixed order over the T partials
-        const int nrows = rend - rb;
-        for (int lr = warp * ralign; lr < nrows; lr += nw * ralign) {
-            float v0 = 0.0f, v1 = 0.0f;
-            for (int t = lane; t < T; t += 32) v0 += part[(size_t)lr * T + t];
-            v0 = warp_sum(v0);
-            if (ralign == 2) {
-                for (int t = lane; t < T; t += 32) v1 += part[(size_t)(lr + 1) * T + t];
-                v1 = warp_sum(v1);
-            }
-            const int row = rb + lr;
+        mbar_arrive(&empty[slot]);             // this thread no longer reads the slot
+
+        const float tot = reduce_rows<RB>(v, lane);
+        float *wp = wpart + (size_t)((g * 2 + (it & 1)) * nwg) * RB;
+        if (lane < RB) wp[wg * RB + lane] = tot;
+        named_barrier(2 + g, T);
+        if (wg == 0) {
+            float y = 0.0f;
+            if (lane < RB)
+                for (int w = 0; w < nwg; ++w) y += wp[w * RB + lane];
+            const int row = row0 + lane;
             if (p.out_mode == B200_OUT_GLU) {
-                if (lane == 0) {
-                    const float a = p.act == 0 ? act_silu(v0) : act_gelu_tanh(v0);
-                    p.d_out[0][p.out_offset + (row >> 1)] = a * v1;
+                const float u = __shfl_down_sync(0xffffffffu, y, 1);
+                if (lane < nr && !(lane & 1)) {
+                    const float a = p.act == 0 ? act_silu(y) : act_gelu_tanh(y);
+                    p.d_out[0][p.out_offset + (row >> 1)] = a * u;
                 }
-            } else {
-                if (lane < p.n_out) p.d_out[lane][p.out_offset + row] = v0;
-                if (better(v0, row, best_v, best_i)) { best_v = v0; best_i = row; }
+            } else if (lane < nr) {
+                for (int q = 0; q < p.n_out; ++q) p.d_out[q][p.out_offset + row] = y;
+                if (better(y, row, best_v, best_i)) { best_v = y; best_i = row; }
             }
         }
-        __syncthreads();
     }
 
     if (!p.d_ticket) return;
 
     // ---------------- last-block bookkeeping ----------------
-    float *am_v = red + 40;                       // [32] per-warp best value
-    int *am_i = reinterpret_cast<int *>(red + 72);  // [32] per-warp best row
-    if (p.d_argmax_scratch) {
-        if (lane == 0) { am_v[warp] = best_v; am_i[warp] = best_i; }
-        __syncthreads();
-        if (tid == 0) {
+    if (p.d_argmax_scratch && wg == 0 && lane < RB) { am_v[g * RB + lane] = best_v; am_i[g * RB + lane] = best_i; }
+    __threadfence_system();
+    named_barrier(1, nC);
+    if (tid == 0) {
+        if (p.d_argmax_scratch) {
             float bv = am_v[0]; int bi = am_i[0];
-            for (int w = 1; w < nw; ++w) if (better(am_v[w], am_i[w], bv, bi)) { bv = am_v[w]; bi = am_i[w]; }
+            for (int k = 1; k < NG * RB; ++k) if (better(am_v[k], am_i[k], bv, bi)) { bv = am_v[k]; bi = am_i[k]; }
             p.d_argmax_scratch[2 * blockIdx.x] = bv;
             reinterpret_cast<int *>(p.d_argmax_scratch)[2 * blockIdx.x + 1] = bi;
+            __threadfence();
         }
+        s_last = (atomicAdd(p.d_ticket, 1u) == gridDim.x - 1);
     }
+    named_barrier(1, nC);
+    if (!s_last || tid >= 32) return;
     __threadfence_system();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(p.d_ticket, 1u) == gridDim.x - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence_system();
-    if (warp == 0) {
+    {
         float bv = -INFINITY; int bi = 0x7fffffff;
         if (p.d_argmax_scratch) {
             for (int b = lane; b < (int)gridDim.x; b += 32) {
@@ -344,18 +487,27 @@ int sm_count()
     return g_sm_count;
 }
 
-template <int WT, int SPT, int RB, int MAXT>
-int launch(const b200_matvec_args &a, int T, int grid, int rmax, cudaStream_t st)
+int env_int(const char *name, int dflt)
 {
-    const size_t smem = ((size_t)rmax * T + 40 + 64) * sizeof(float);
+    const char *e = getenv(name);
+    return e && *e ? atoi(e) : dflt;
+}
+
+template <int WT, int SPT, int RB, int MAXT>
+int launch(const b200_matvec_args &a, const Geometry &geo, int grid, cudaStream_t st)
+{
+    const int nwg = geo.T / 32;
+    const size_t smem = (size_t)geo.nstage * geo.slot_bytes + (size_t)geo.nstage * 16 +
+                        ((size_t)geo.NG * 2 * nwg * RB + (size_t)geo.NG * 32 + (size_t)geo.NG * RB * 2) * sizeof(float);
     auto kern = matvec_kernel<WT, SPT, RB, MAXT>;
+    if (smem > 220 * 1024) return B200_E_TOOLARGE;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(T);
+    cfg.blockDim = dim3(geo.NG * geo.T + 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -364,7 +516,26 @@ int launch(const b200_matvec_args &a, int T, int grid, int rmax, cudaStream_t st
     cfg.attrs = attr;
     cfg.numAttrs = a.use_pdl ? 1 : 0;
     ++g_b200_launches;
-    return (int)cudaLaunchKernelEx(&cfg, kern, a, rmax);
+    return (int)cudaLaunchKernelEx(&cfg, kern, a, geo);
+}
+
+template <int WT, int SPT, int RB>
+int launch_by_size(const b200_matvec_args &a, const Geometry &geo, int grid, cudaStream_t st)
+{
+    const int threads = geo.NG * geo.T + 32;
+    if (threads <= 672) return launch<WT, SPT, RB, 672>(a, geo, grid, st);
+    return launch<WT, SPT, RB, 1024>(a, geo, grid, st);
+}
+
+template <int WT, int SPT>
+int launch_by_rows(const b200_matvec_args &a, const Geometry &geo, int rb, int grid, cudaStream_t st)
+{
+    switch (rb) {
+    case 8: return launch_by_size<WT, SPT, 8>(a, geo, grid, st);
+    case 4: return launch_by_size<WT, SPT, 4>(a, geo, grid, st);
+    case 2: return launch_by_size<WT, SPT, 2>(a, geo, grid, st);
+    default: return launch_by_size<WT, SPT, 1>(a, geo, grid, st);
+    }
 }
 
 } // namespace
@@ -392,46 +563,47 @@ extern "C" int b200_matvec(const b200_matvec_args *ap, void *stream)
     if ((a.advance_pos || a.d_next_token) && !a.d_pos_rw) return B200_E_BADARG;
     if (a.d_next_token && (!a.d_prompt_len || !a.d_argmax_scratch)) return B200_E_BADARG;
     if (a.advance_epoch && (!a.d_epoch || !a.d_epoch_rw)) return B200_E_BADARG;
+    if (a.d_argmax_scratch && a.out_mode != B200_OUT_STORE) return B200_E_BADARG;
 
     const int E = a.wtype == B200_WT_Q8 ? 16 : 8;
     const int nsl = (a.cols + E - 1) / E;
-    const int spt = (nsl + 1023) / 1024;
-    if (spt > 2) return B200_E_TOOLARGE;
-    const int T = (((nsl + spt - 1) / spt) + 31) / 32 * 32;
+    // Up to two slices per thread: keeps a group at <= 320 threads for rows of up to 640 slices, so that
+    // two blocks (this kernel's and the next one's) fit on an SM; 960 consumers + the producer warp at most.
+    const int spt = nsl <= 320 ? 1 : 2;
+    if ((nsl + spt - 1) / spt > 960) return B200_E_TOOLARGE;
+    Geometry geo;
+    geo.T = (((nsl + spt - 1) / spt) + 31) / 32 * 32;
     const int ralign = a.out_mode == B200_OUT_GLU ? 2 : 1;
     const int units = a.rows / ralign;
 
+    // rows per stage: 16-24 KB per bulk copy
+    int rb = 8;
+    while (rb > 1 && (long long)rb * a.row_stride > 24576) rb >>= 1;
+    if (rb < ralign) rb = ralign;
+    geo.slot_bytes = (unsigned)(((long long)rb * a.row_stride + 127) / 128 * 128);
+    geo.dbg = env_int("LLMB200_MV_DBG", 0);
+    geo.NG = env_int("LLMB200_MV_GROUP_THREADS", 640) / geo.T;
+    if (geo.NG > 8) geo.NG = 8;
+    if (geo.NG < 1) geo.NG = 1;
+    // Ring slots: a multiple of the group count, so that a slot is always consumed by the same group.
+    // A group works through its stages in order, hence never waits on a slot whose previous phase is
+    // still open -- mbarrier parity waits cannot tell phase k from phase k-2.
+    const int ring_budget = env_int("LLMB200_MV_RING_KB", 192) * 1024;
+    while (geo.NG > 1 && (long long)geo.NG * geo.slot_bytes > ring_budget) --geo.NG;
+    int per_group = ring_budget / (int)(geo.NG * geo.slot_bytes);
+    if (per_group < 1) per_group = 1;
+    while (per_group > 1 && per_group * geo.NG > 12) --per_group;
+    geo.nstage = per_group * geo.NG;
+
     int grid = a.grid;
     if (grid <= 0) {
-        int per_sm = 640 / T;
-        if (per_sm < 1) per_sm = 1;
-        if (per_sm > 16) per_sm = 16;
-        grid = sm_count() * per_sm;
+        // one block per SM, leaving room for the next kernel's block; two for long streams
+        const long long bytes = (long long)a.rows * a.row_stride;
+        grid = sm_count() * (bytes / sm_count() > (long long)env_int("LLMB200_MV_TWO_BLOCK_KB", 1 << 20) * 1024 ? 2 : 1);
     }
     if (grid > units) grid = units;
-    const int RB = (spt == 1 && T <= 640) ? 8 : 4;
-    int rows_cta = ((units + grid - 1) / grid) * ralign;
-    int cap = (int)(40960 / (4 * (size_t)T)) / RB * RB;
-    if (cap < RB) cap = RB;
-    int rmax = (rows_cta + RB - 1) / RB * RB;
-    if (rmax > cap) rmax = cap;
     cudaStream_t st = (cudaStream_t)stream;
-
-#define B200_MV(WT_, SPT_, RB_, MAXT_) return launch<WT_, SPT_, RB_, MAXT_>(a, T, grid, rmax, st)
-    if (a.wtype == B200_WT_Q8) {
-        if (spt == 1) {
-            if (T <= 256) B200_MV(B200_WT_Q8, 1, 8, 256);
-            if (T <= 640) B200_MV(B200_WT_Q8, 1, 8, 640);
-            B200_MV(B200_WT_Q8, 1, 4, 1024);
-        }
-        B200_MV(B200_WT_Q8, 2, 4, 1024);
-    } else {
-        if (spt == 1) {
-            if (T <= 256) B200_MV(B200_WT_F16, 1, 8, 256);
-            if (T <= 640) B200_MV(B200_WT_F16, 1, 8, 640);
-            B200_MV(B200_WT_F16, 1, 4, 1024);
-        }
-        B200_MV(B200_WT_F16, 2, 4, 1024);
-    }
-#undef B200_MV
+    if (a.wtype == B200_WT_Q8)
+        return spt == 1 ? launch_by_rows<B200_WT_Q8, 1>(a, geo, rb, grid, st) : launch_by_rows<B200_WT_Q8, 2>(a, geo, rb, grid, st);
+    return spt == 1 ? launch_by_rows<B200_WT_F16, 1>(a, geo, rb, grid, st) : launch_by_rows<B200_WT_F16, 2>(a, geo, rb, grid, st);
 }
