@@ -100,6 +100,7 @@ typedef struct b200_matvec_args {
     const float *d_slots; int n_slots; long long slot_stride;   /* floats between slots */
     const float *d_slot_norm_gamma;
     const float *d_emb; const int *d_tokens; const int *d_pos; float emb_scale;
+    int emb_rows;                  /* rows of d_emb; an id outside [0, emb_rows) is read as id 0 */
     const float *d_norm_gamma; float eps;
     /* output */
     int out_mode, act;

@@ -37,6 +37,7 @@ class MatvecArgs(C.Structure):
         ("d_slots", C.c_void_p), ("n_slots", C.c_int), ("slot_stride", C.c_longlong),
         ("d_slot_norm_gamma", C.c_void_p),
         ("d_emb", C.c_void_p), ("d_tokens", C.c_void_p), ("d_pos", C.c_void_p), ("emb_scale", C.c_float),
+        ("emb_rows", C.c_int),
         ("d_norm_gamma", C.c_void_p), ("eps", C.c_float),
         ("out_mode", C.c_int), ("act", C.c_int),
         ("d_out", C.c_void_p * B200_MAX_PEERS), ("n_out", C.c_int), ("out_offset", C.c_longlong),

@@ -307,6 +307,7 @@ __global__ void tp_argmax_finalize_kernel(const float *vals, const int *idx, int
         const int i = __ldcv(idx + r);
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     }
+    if (bi == 0x7fffffff) bi = 0;
     const int pos = *pos_rw;
     if (pos + 1 >= *prompt_len) tokens[pos + 1] = bi;
     *pos_rw = pos + 1;

@@ -276,7 +276,8 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
             }
     } else {
         if (p.in_mode == B200_IN_EMBED) {
-            const long long tok = p.d_tokens[*p.d_pos];
+            long long tok = p.d_tokens[*p.d_pos];
+            if (tok < 0 || tok >= p.emb_rows) tok = 0;      // never index outside the table
             const float *er = p.d_emb + tok * (long long)p.cols;
 #pragma unroll
             for (int s = 0; s < SPT; ++s)
@@ -455,6 +456,7 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
                 const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
                 if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
             }
+            if (bi == 0x7fffffff) bi = 0;         // nothing compared greater (all NaN): index 0, as the reference's loop
             bi += (int)p.out_offset;              // global row index of a sharded matrix
             if (lane < p.n_argmax_out) { p.d_argmax_val[lane][0] = bv; p.d_argmax_idx[lane][0] = bi; }
         }
@@ -550,7 +552,7 @@ extern "C" int b200_matvec(const b200_matvec_args *ap, void *stream)
     if (a.row_stride < (long long)b200_packed_row_stride(a.wtype, a.cols)) return B200_E_BADARG;
     if (a.in_mode == B200_IN_VEC ? !a.d_in_vec
         : a.in_mode == B200_IN_RESID ? (!a.d_resid_in || a.n_slots < 0 || (a.n_slots > 0 && !a.d_slots))
-        : a.in_mode == B200_IN_EMBED ? (!a.d_emb || !a.d_tokens || !a.d_pos) : true)
+        : a.in_mode == B200_IN_EMBED ? (!a.d_emb || !a.d_tokens || !a.d_pos || a.emb_rows <= 0) : true)
         return B200_E_BADARG;
     if (a.out_mode == B200_OUT_GLU ? (a.rows % 2 || !a.d_out[0]) : (a.out_mode != B200_OUT_STORE || a.n_out < 1 || a.n_out > B200_MAX_PEERS))
         return B200_E_BADARG;

@@ -365,6 +365,7 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         base_args(s, &a, &ly->qkv, pdl);
         if (l == 0) {
             a.in_mode = B200_IN_EMBED; a.d_emb = s->emb; a.d_tokens = s->d_tokens; a.emb_scale = s->emb_scale;
+            a.emb_rows = s->V;
             a.epoch_add = -1;                     /* previous token's last down signal */
         } else {
             a.in_mode = B200_IN_RESID; a.d_resid_in = s->resid[0];
