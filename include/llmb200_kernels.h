@@ -156,6 +156,19 @@ typedef struct b200_attn_args {
 size_t b200_attn_scratch_floats(int n_q, int hd, int n_split);
 int    b200_attn_decode(const b200_attn_args *a, void *stream);
 
+/* No counterpart in the reference. b200_attn_decode for callers that cannot allocate device memory --
+ * a process whose GPU memory was carved up completely at start-up, or a loop that must not risk the
+ * device-wide synchronisation a cudaMalloc can cause. a->d_scratch and a->d_tickets are ignored; the
+ * partial results go to arrays built into the library (held by every GPU that loads it until the
+ * process exits). Limits: n_q * n_split * (hd + 2) <= B200_ATTN_STATIC_SCRATCH_FLOATS and
+ * n_kv <= B200_ATTN_STATIC_MAX_KV_HEADS; larger requests are refused with B200_E_TOOLARGE and a
+ * message on stderr. Calls no cudaMalloc/cudaFree. The first call on a device looks up the arrays'
+ * device addresses and should therefore come before any stream capture. All calls share the arrays:
+ * two calls whose kernels may overlap on the GPU (different streams) race with each other. */
+#define B200_ATTN_STATIC_SCRATCH_FLOATS (1 << 18)      /* 1 MiB */
+#define B200_ATTN_STATIC_MAX_KV_HEADS   64
+int b200_attn_decode_static(const b200_attn_args *a, void *stream);
+
 /* Last tensor-parallel step of a token: waits for every rank's (value, index)
  * pair, takes the largest (lowest index on ties), stores it as tokens[pos+1]
  * unless that position belongs to the prompt, and advances *pos. */

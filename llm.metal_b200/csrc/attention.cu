@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "../../include/llmb200_kernels.h"
 
+#include <stdio.h>
+
 extern unsigned long long g_b200_launches;
 
 namespace {
@@ -335,4 +337,65 @@ extern "C" int b200_tp_argmax_finalize(const float *d_vals, const int *d_idx, in
     ++g_b200_launches;
     return (int)cudaLaunchKernelEx(&cfg, tp_argmax_finalize_kernel, d_vals, d_idx, n_ranks, d_wait_flags, d_epoch,
                                    epoch_mul, epoch_add, d_tokens, d_pos, d_prompt_len, d_epoch_rw, d_err);
+}
+
+// ---------------------------------------------------------------------------
+// b200_attn_decode_static: the same attention launch for callers that can
+// neither allocate device memory themselves nor let a library do it for them
+// -- for instance a serving process whose device memory was handed out in full
+// at start-up, or a latency-critical loop in which a cudaMalloc (which may
+// synchronise the whole device) is not acceptable. The split-sequence partials
+// and the per-KV-head tickets, which b200_attn_decode takes from the caller,
+// live here in two arrays that are part of the library image. They exist once
+// per GPU that loads the library and stay there until the process exits.
+//
+// In host code the names of these arrays are only stand-ins; the kernel needs
+// their device addresses, which cudaGetSymbolAddress returns for the device
+// that is current at the time. That look-up happens on the first call on each
+// device, so that first call should be made before any stream capture.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) float g_attn_static_scratch[B200_ATTN_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) unsigned g_attn_static_tickets[B200_ATTN_STATIC_MAX_KV_HEADS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float *g_static_scratch_addr[kMaxDevices];
+unsigned *g_static_tickets_addr[kMaxDevices];
+bool g_static_ready[kMaxDevices];
+}
+
+extern "C" int b200_attn_decode_static(const b200_attn_args *ap, void *stream)
+{
+    if (!ap) return B200_E_BADARG;
+    const size_t need = b200_attn_scratch_floats(ap->n_q, ap->hd, ap->n_split);
+    if (need == 0 || ap->n_kv <= 0) return B200_E_BADARG;
+    if (need > (size_t)B200_ATTN_STATIC_SCRATCH_FLOATS || ap->n_kv > B200_ATTN_STATIC_MAX_KV_HEADS) {
+        fprintf(stderr, "[llmb200] b200_attn_decode_static: n_q*n_split*(hd+2) = %zu floats / %d KV heads exceed the built-in "
+                        "scratch (%d floats, %d KV heads); use b200_attn_decode with caller-provided scratch\n",
+                need, ap->n_kv, B200_ATTN_STATIC_SCRATCH_FLOATS, B200_ATTN_STATIC_MAX_KV_HEADS);
+        return B200_E_TOOLARGE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return B200_E_BADARG;
+    if (!g_static_ready[dev]) {
+        // once per device, with that device current: host-side symbol -> device address
+        void *ps = nullptr, *pt = nullptr;
+        e = cudaGetSymbolAddress(&ps, g_attn_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGetSymbolAddress(&pt, g_attn_static_tickets);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_addr[dev] = static_cast<float *>(ps);
+        g_static_tickets_addr[dev] = static_cast<unsigned *>(pt);
+        g_static_ready[dev] = true;
+    }
+    // The arrays keep whatever the last call left. The partials are fully rewritten by every launch;
+    // the tickets must start at zero, so they are cleared on the caller's stream first.
+    e = cudaMemsetAsync(g_static_tickets_addr[dev], 0, sizeof(unsigned) * (size_t)ap->n_kv, (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    b200_attn_args a = *ap;
+    a.d_scratch = g_static_scratch_addr[dev];
+    a.d_tickets = g_static_tickets_addr[dev];
+    return b200_attn_decode(&a, stream);
 }
