@@ -301,21 +301,19 @@ def main():
     if L.llmb200_state_error(st):
         raise RuntimeError("a device-side wait timed out")
 
-    # instrumented pass for the per-kernel roofline (kernel by kernel, CUDA events around each launch)
+    # per-kernel durations: each kind of kernel launched back to back over all layers (different weights
+    # every launch, so L2 cannot serve them) between two CUDA events on the library's stream
     L.inference_generate(st, pp, P, op, 1)
     L.llmb200_state_run_device_steps(st, (G - 1) // 2)       # to the middle of the decode range
-    kms = (C.c_float * 6)()
-    kl = (C.c_int * 6)()
-    prof = {}
-    acc = np.zeros(6)
-    cnt = np.zeros(6)
-    for _ in range(8):
-        if L.llmb200_state_profile_token(st, kms, kl) != 0:
-            raise RuntimeError("profile pass failed")
-        acc += np.array(list(kms)); cnt += np.array(list(kl))
     names = ["qkv_matvec", "attention", "o_matvec", "gateup_matvec", "down_matvec", "lm_head_matvec"]
+    prof = {}
     for i, nme in enumerate(names):
-        prof[nme] = {"us_per_launch": 1e3 * acc[i] / max(cnt[i], 1), "launches_per_token": int(cnt[i] // 8)}
+        nl = C.c_int(0)
+        ms = L.llmb200_state_time_kind(st, i, 8 if i < 5 else 24, C.byref(nl))
+        if ms <= 0 or nl.value <= 0:
+            raise RuntimeError("kernel timing failed")
+        prof[nme] = {"us_per_launch": 1e3 * ms / nl.value, "launches_timed": nl.value,
+                     "launches_per_token": sp.n_layers if i < 5 else 1}
     peak, peak_kind = measured_peaks()
     D, IS = sp.d_model, sp.intermediate_size
     gu_rows, gu_cols = 2 * IS // world, D

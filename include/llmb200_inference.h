@@ -112,6 +112,11 @@ float llmb200_state_run_device_steps(InferenceState *state, int n_steps);
  * 1 attention, 2 o matvec, 3 gate/up matvec, 4 down matvec, 5 LM head;
  * launches[6] the launch counts. The position advances by one. */
 int llmb200_state_profile_token(InferenceState *state, float *ms, int *launches);
+/* Times one kind of kernel (numbering as above) in isolation: `reps` passes over all layers' launches
+ * of that kind, back to back on the library stream between two CUDA events; every launch reads a
+ * different layer's weights, so nothing is served from L2. Returns the elapsed milliseconds for
+ * *launches launches (negative on error). The token state is left untouched. */
+float llmb200_state_time_kind(InferenceState *state, int kind, int reps, int *launches);
 /* Bytes of weights one token streams on this rank (all matrices + LM head). */
 unsigned long long llmb200_state_weight_bytes(InferenceState *state);
 int llmb200_state_position(InferenceState *state);

@@ -84,14 +84,6 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr)
     asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-// binary16 bits of a block scale (never negative) -> fp32 without the conversion unit: the bits moved
-// to the fp32 exponent/mantissa position are the value times 2^-112, exact for normals and subnormals.
-__device__ __forceinline__ float scale_f32(uint32_t h)
-{
-    float f = __uint_as_float(h << 13) * 5192296858534827628530496329220096.0f;   // 2^112
-    if ((h & 0x7c00u) == 0x7c00u) f = __half2float(__ushort_as_half((unsigned short)h));   // inf / nan
-    return f;
-}
 __device__ __forceinline__ void named_barrier(int id, int count)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -185,6 +177,7 @@ struct Geometry {
     int NG;             // consumer groups
     int nstage;         // ring slots
     unsigned slot_bytes;  // bytes per slot (RB rows, rounded up to 128)
+    int share_x;        // 1: group 0 assembles the input vector and hands it to the other groups through shared memory
     int dbg;            // diagnostics: 1 = no arithmetic, 2 = no waiting for data after the first ring fill
 };
 
@@ -203,6 +196,7 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
     float *red = wpart + (size_t)NG * 2 * nwg * RB;             // [NG][32]
     float *am_v = red + NG * 32;                                // [NG*RB]
     int *am_i = reinterpret_cast<int *>(am_v + NG * RB);        // [NG*RB]
+    float *xs = reinterpret_cast<float *>(am_i + NG * RB);      // [SPT*T*E] when geo.share_x
     __shared__ int s_last;
 
     const int tid = threadIdx.x;
@@ -264,8 +258,12 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
         named_barrier(1, nC);
     }
 
-    // ---------------- input assembly (each group builds the same vector) ----------------
+    // ---------------- input assembly ----------------
+    // Every SM needs the whole input vector. When it has to be assembled (slot sums, norms), one group
+    // per block does it and passes it on through shared memory: the few KB involved are read by all
+    // SMs at once, and every extra reader of the same L2 lines queues behind the others.
     float x[SPT][E];
+    if (!geo.share_x || g == 0) {
     if (p.in_mode == B200_IN_VEC) {
 #pragma unroll
         for (int s = 0; s < SPT; ++s)
@@ -300,8 +298,8 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
 #pragma unroll
                     for (int e = 0; e < E; e += 4) {
                         if (on[s]) {
-                            // slots may be written by other GPUs: read them past L1
-                            float4 v4 = __ldcv(reinterpret_cast<const float4 *>(sl + col[s] + e));
+                            // slots may be written by other GPUs: read them from L2, the point of coherence, never from L1
+                            float4 v4 = __ldcg(reinterpret_cast<const float4 *>(sl + col[s] + e));
                             sacc[s][e] += v4.x; sacc[s][e + 1] += v4.y; sacc[s][e + 2] += v4.z; sacc[s][e + 3] += v4.w;
                         }
                     }
@@ -340,6 +338,15 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
         }
     }
     if (p.d_norm_gamma) {
+        // gamma is fetched before the reduction so that its latency hides behind the barriers
+        float gm[SPT][E];
+#pragma unroll
+        for (int s = 0; s < SPT; ++s)
+#pragma unroll
+            for (int e = 0; e < E; e += 4) {
+                float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(p.d_norm_gamma + col[s] + e) : make_float4(0, 0, 0, 0);
+                gm[s][e] = v4.x; gm[s][e + 1] = v4.y; gm[s][e + 2] = v4.z; gm[s][e + 3] = v4.w;
+            }
         float ss = 0.0f;
 #pragma unroll
         for (int s = 0; s < SPT; ++s)
@@ -350,8 +357,27 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
 #pragma unroll
         for (int s = 0; s < SPT; ++s)
 #pragma unroll
-            for (int e = 0; e < E; ++e)
-                if (on[s]) x[s][e] = p.d_norm_gamma[col[s] + e] * x[s][e] * inv;
+            for (int e = 0; e < E; ++e) x[s][e] = gm[s][e] * x[s][e] * inv;
+    }
+    }
+    if (geo.share_x) {
+        if (g == 0) {
+#pragma unroll
+            for (int s = 0; s < SPT; ++s)
+#pragma unroll
+                for (int e = 0; e < E; e += 4)
+                    *reinterpret_cast<float4 *>(xs + (size_t)(s * T + t) * E + e) = make_float4(x[s][e], x[s][e + 1], x[s][e + 2], x[s][e + 3]);
+        }
+        named_barrier(1, nC);
+        if (g != 0) {
+#pragma unroll
+            for (int s = 0; s < SPT; ++s)
+#pragma unroll
+                for (int e = 0; e < E; e += 4) {
+                    const float4 v4 = *reinterpret_cast<const float4 *>(xs + (size_t)(s * T + t) * E + e);
+                    x[s][e] = v4.x; x[s][e + 1] = v4.y; x[s][e + 2] = v4.z; x[s][e + 3] = v4.w;
+                }
+        }
     }
 
     // ---------------- consume the ring: group g takes stages g, g+NG, ... ----------------
@@ -393,9 +419,9 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
 #pragma unroll
             for (int s = 0; s < SPT; ++s) {
                 float d;
-                if (WT == B200_WT_Q8) d = scale_f32(ws[j][s]) * dot16_q8(wq[j][s], x[s]);
+                if (WT == B200_WT_Q8) d = __half2float(__ushort_as_half((unsigned short)ws[j][s])) * dot16_q8(wq[j][s], x[s]);
                 else d = dot8_f16(wq[j][s], x[s]);
-                acc += on[s] ? d : 0.0f;
+                acc += d;                      // threads past the end of the row hold a zero input slice
             }
             v[j] = acc;
         }
@@ -500,7 +526,8 @@ int launch(const b200_matvec_args &a, const Geometry &geo, int grid, cudaStream_
 {
     const int nwg = geo.T / 32;
     const size_t smem = (size_t)geo.nstage * geo.slot_bytes + (size_t)geo.nstage * 16 +
-                        ((size_t)geo.NG * 2 * nwg * RB + (size_t)geo.NG * 32 + (size_t)geo.NG * RB * 2) * sizeof(float);
+                        ((size_t)geo.NG * 2 * nwg * RB + (size_t)geo.NG * 32 + (size_t)geo.NG * RB * 2) * sizeof(float) +
+                        (geo.share_x ? (size_t)SPT * geo.T * (WT == B200_WT_Q8 ? 16 : 8) * sizeof(float) : 0);
     auto kern = matvec_kernel<WT, SPT, RB, MAXT>;
     if (smem > 220 * 1024) return B200_E_TOOLARGE;
     if (smem > 48 * 1024) {
@@ -596,6 +623,7 @@ extern "C" int b200_matvec(const b200_matvec_args *ap, void *stream)
     if (per_group < 1) per_group = 1;
     while (per_group > 1 && per_group * geo.NG > 12) --per_group;
     geo.nstage = per_group * geo.NG;
+    geo.share_x = geo.NG > 1 && (a.in_mode != B200_IN_VEC || a.d_norm_gamma) && (size_t)spt * geo.T * E * 4 <= 16384;
 
     int grid = a.grid;
     if (grid <= 0) {

@@ -92,6 +92,7 @@ struct InferenceState {
     /* instrumentation */
     cudaEvent_t *prof_ev;
     int prof_n, prof_cap, prof_on;
+    int only_kind;           /* >= 0: enqueue_token launches only this kind of kernel (timing loops) */
     int *prof_kind;
 };
 
@@ -241,6 +242,7 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
     CU_TRY(cudaEventCreate(&s->ev_a), goto fail);
     CU_TRY(cudaEventCreate(&s->ev_b), goto fail);
     s->use_pdl = getenv("LLMB200_NO_PDL") ? 0 : 1;
+    s->only_kind = -1;
     return s;
 fail:
     inference_state_free(s);
@@ -351,6 +353,18 @@ static void base_args(InferenceState *s, b200_matvec_args *a, const PackedMat *m
     a->use_pdl = pdl;
 }
 
+/* Timing loops launch one kind of kernel only; such launches must not touch the token state. */
+static int want(InferenceState *s, int kind, b200_matvec_args *a)
+{
+    if (s->only_kind < 0) return 1;
+    if (s->only_kind != kind) return 0;
+    if (a) {
+        a->n_wait = 0; a->n_signal = 0; a->advance_pos = 0; a->advance_epoch = 0; a->d_next_token = NULL;
+        if (!a->d_argmax_scratch) a->d_ticket = NULL;
+    }
+    return 1;
+}
+
 /* Enqueue every kernel of one token on the library stream. */
 static int enqueue_token(InferenceState *s, int with_lm, int pdl)
 {
@@ -378,7 +392,7 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         a.d_norm_gamma = ly->g_input;
         a.out_mode = B200_OUT_STORE; a.d_out[0] = s->qkv; a.n_out = 1;
         prof_mark(s, K_QKV);
-        K_TRY(b200_matvec(&a, st), return -1);
+        if (want(s, K_QKV, &a)) K_TRY(b200_matvec(&a, st), return -1);
         prof_mark(s, -1);
         /* --- attention --- */
         b200_attn_args at;
@@ -389,7 +403,7 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         at.n_q = s->Hq_l; at.n_kv = s->Hkv_l; at.hd = s->hd; at.max_seq = s->max_seq; at.n_split = s->n_split;
         at.eps = 1e-6f; at.use_pdl = pdl;
         prof_mark(s, K_ATTN);
-        K_TRY(b200_attn_decode(&at, st), return -1);
+        if (want(s, K_ATTN, NULL)) K_TRY(b200_attn_decode(&at, st), return -1);
         prof_mark(s, -1);
         /* --- o: partial sums into slot `me` of every rank --- */
         base_args(s, &a, &ly->o, pdl);
@@ -401,7 +415,7 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
             for (int p = 0; p < k; ++p) a.d_signal_flags[p] = flags_of(s, p, 0);
         }
         prof_mark(s, K_O);
-        K_TRY(b200_matvec(&a, st), return -1);
+        if (want(s, K_O, &a)) K_TRY(b200_matvec(&a, st), return -1);
         prof_mark(s, -1);
         /* --- gate/up --- */
         base_args(s, &a, &ly->gateup, pdl);
@@ -412,7 +426,7 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         if (k > 1) { a.d_wait_flags = flags_of(s, me, 0); a.n_wait = k; a.epoch_add = l + 1; }
         a.out_mode = B200_OUT_GLU; a.act = gemma ? 1 : 0; a.d_out[0] = s->act; a.n_out = 1;
         prof_mark(s, K_GATEUP);
-        K_TRY(b200_matvec(&a, st), return -1);
+        if (want(s, K_GATEUP, &a)) K_TRY(b200_matvec(&a, st), return -1);
         prof_mark(s, -1);
         /* --- down --- */
         base_args(s, &a, &ly->down, pdl);
@@ -425,7 +439,7 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         }
         if (!with_lm && l == L - 1) { a.d_ticket = s->mv_ticket; a.advance_pos = 1; a.advance_epoch = 1; }
         prof_mark(s, K_DOWN);
-        K_TRY(b200_matvec(&a, st), return -1);
+        if (want(s, K_DOWN, &a)) K_TRY(b200_matvec(&a, st), return -1);
         prof_mark(s, -1);
     }
     if (!with_lm) return 0;
@@ -458,9 +472,9 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         a.epoch_add = L;
     }
     prof_mark(s, K_LM);
-    K_TRY(b200_matvec(&a, st), return -1);
+    if (want(s, K_LM, &a)) K_TRY(b200_matvec(&a, st), return -1);
     prof_mark(s, -1);
-    if (k > 1) {
+    if (k > 1 && s->only_kind < 0) {
         K_TRY(b200_tp_argmax_finalize((const float *)(s->comm + s->off_am_val), (const int *)(s->comm + s->off_am_idx), k,
                                       flags_of(s, me, 2), s->d_epoch, L + 1, L, s->d_tokens, s->d_pos, s->d_prompt_len,
                                       s->d_epoch, s->d_err, pdl, st), return -1);
@@ -862,6 +876,26 @@ float llmb200_state_run_device_steps(InferenceState *s, int n_steps)
     float ms = -1.0f;
     CU_TRY(cudaEventElapsedTime(&ms, s->ev_a, s->ev_b), return -1.0f);
     s->cur_len += n_steps;
+    return ms;
+}
+
+float llmb200_state_time_kind(InferenceState *s, int kind, int reps, int *launches)
+{
+    if (!s || kind < 0 || kind >= K_KINDS || reps <= 0 || ensure_graphs(s) != 0) return -1.0f;
+    if (s->cur_len >= s->max_seq) return -1.0f;
+    if (set_control(s, s->cur_len, 0, NULL, 0, 0) != 0) return -1.0f;
+    s->only_kind = kind;
+    int rc = enqueue_token(s, kind == K_LM, 0);                 /* warm-up pass, untimed */
+    const unsigned long long before = b200_launch_count(0);
+    if (rc == 0) rc = (int)cudaEventRecord(s->ev_a, g_rt.stream);
+    for (int i = 0; i < reps && rc == 0; ++i) rc = enqueue_token(s, kind == K_LM, 0);
+    if (rc == 0) rc = (int)cudaEventRecord(s->ev_b, g_rt.stream);
+    s->only_kind = -1;
+    if (launches) *launches = (int)(b200_launch_count(0) - before);
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1.0f);
+    if (rc != 0) return -1.0f;
+    float ms = -1.0f;
+    CU_TRY(cudaEventElapsedTime(&ms, s->ev_a, s->ev_b), return -1.0f);
     return ms;
 }
 
