@@ -178,6 +178,67 @@ int b200_tp_argmax_finalize(const float *d_vals, const int *d_idx, int n_ranks,
                             int *d_tokens, int *d_pos, const int *d_prompt_len,
                             unsigned *d_epoch_rw, int *d_err, int use_pdl, void *stream);
 
+/* ------------------------------------------------------------------------
+ * Whole-token kernel: every matvec and attention step of one token in ONE
+ * persistent launch (one block per SM, cooperative). Replaces the reference's
+ * single command buffer with its barrier after every dispatch
+ * (src/nn/fast_metal.m:223-247; op sequence src/nn/fast_inference.c:394-466):
+ * here the steps are separated by device-wide barriers inside the kernel,
+ * while a producer warp keeps streaming the weights of the coming steps into
+ * the shared-memory ring, so HBM stays busy across step boundaries.
+ *
+ * The caller describes the token as an array of b200_op in device memory
+ * (same field meaning as b200_matvec_args / b200_attn_args); geometry fields
+ * are filled by b200_op_plan_matvec. All matrices of a plan share one wtype.
+ * ---------------------------------------------------------------------- */
+enum { B200_OP_MATVEC = 0, B200_OP_ATTN = 1 };
+
+typedef struct b200_op {
+    int type;
+    /* matvec: weights + geometry */
+    const void *d_w; long long row_stride; int rows, cols;
+    int rb, T, NG, spt;
+    /* matvec: input assembly */
+    int in_mode;
+    const float *d_in_vec; const float *d_resid_in; float *d_resid_out;
+    const float *d_slots; int n_slots; long long slot_stride;
+    const float *d_slot_norm_gamma; const float *d_norm_gamma;
+    /* matvec: output */
+    int out_mode, act;
+    float *d_out[B200_MAX_PEERS]; int n_out; long long out_offset;
+    int argmax;                                   /* 1: this step picks the next token id (LM head) */
+    /* tensor-parallel hand-shake around this step */
+    const unsigned *d_wait_flags; int n_wait, wait_add;
+    unsigned *d_signal_flags[B200_MAX_PEERS]; int n_signal, signal_index, signal_add;
+    /* attention */
+    const float *d_qkv; const float *d_q_gamma; const float *d_k_gamma; const float *d_inv_freq;
+    void *d_k_cache; void *d_v_cache; float *d_attn_out;
+} b200_op;
+
+/* Fills rb, T, NG, spt of a matvec step from rows/cols/row_stride/out_mode. Returns 0, or
+ * B200_E_TOOLARGE when a row does not fit the kernel's thread/ring budget. */
+int b200_op_plan_matvec(b200_op *op, int wtype);
+
+typedef struct b200_token_args {
+    const b200_op *d_ops; int n_ops; int wtype;
+    int wide;                                     /* 1 when any step was planned with spt == 2 */
+    /* model constants */
+    const float *d_emb; int emb_rows; float emb_scale, eps;
+    int n_q, n_kv, hd, max_seq, n_split;
+    /* device control words */
+    int *d_pos; int *d_tokens; const int *d_prompt_len; unsigned *d_epoch; int epoch_mul; int *d_err;
+    /* scratch */
+    float *d_attn_scratch; unsigned *d_attn_tickets; float *d_argmax_scratch;
+    unsigned *d_grid_barrier;                     /* 2 zero-initialised words */
+    /* what the last block does when the steps are done */
+    int pick_token;                               /* tokens[pos+1] = argmax unless pos+1 < *prompt_len */
+    float *d_argmax_val[B200_MAX_PEERS]; int *d_argmax_idx[B200_MAX_PEERS]; int n_ranks, rank;
+    const float *d_rank_vals; const int *d_rank_idx;   /* [n_ranks] pairs pushed by the ranks (TP) */
+    const unsigned *d_argmax_wait_flags; unsigned *d_argmax_signal_flags[B200_MAX_PEERS]; int argmax_add;
+} b200_token_args;
+
+int b200_decode_token(const b200_token_args *a, void *stream);
+
 /* Number of kernel launches issued through this ABI since the last reset
  * (what bench.py reports as gpu_launches). */
 unsigned long long b200_launch_count(int reset);

@@ -92,6 +92,8 @@ struct InferenceState {
     /* instrumentation */
     cudaEvent_t *prof_ev;
     int prof_n, prof_cap, prof_on;
+    /* whole-token kernel: step list on the device, barrier words, launch arguments */
+    b200_op *d_ops; unsigned *d_gbar; int n_ops, fused, plan_wide;
     int only_kind;           /* >= 0: enqueue_token launches only this kind of kernel (timing loops) */
     int *prof_kind;
 };
@@ -482,12 +484,105 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
     return 0;
 }
 
+/* ------------------------------------------------------------ whole-token kernel */
+
+/* Builds the step list of one token (the same sequence enqueue_token launches kernel by kernel) and
+ * copies it to the device. Returns 0 when the whole-token kernel can run this model, 1 when it cannot
+ * (head grouping, row length or attention scratch outside its limits), -1 on a CUDA error. */
+static int build_plan(InferenceState *s)
+{
+    const int k = s->tp_size, me = s->tp_rank, D = s->D, L = s->L, gemma = s->mt == MODEL_GEMMA3;
+    if (s->Hq_l != 4 * s->Hkv_l) return 1;
+    const int n = 5 * L + 1;
+    b200_op *ops = calloc((size_t)n, sizeof(b200_op));
+    if (!ops) return -1;
+    float *slots_o = (float *)(s->comm + s->off_slots_o), *slots_dn = (float *)(s->comm + s->off_slots_dn);
+    int rc = 0, wide = 0, i = 0;
+#define MV(dst, m) do { (dst)->type = B200_OP_MATVEC; (dst)->d_w = (m)->w; (dst)->row_stride = (m)->stride; (dst)->rows = (m)->rows; (dst)->cols = (m)->cols; } while (0)
+    for (int l = 0; l < L; ++l) {
+        Layer *ly = &s->layers[l];
+        b200_op *o = &ops[i++];                                  /* qkv */
+        MV(o, &ly->qkv);
+        if (l == 0) { o->in_mode = B200_IN_EMBED; o->wait_add = -1; }
+        else {
+            o->in_mode = B200_IN_RESID; o->d_resid_in = s->resid[0]; o->d_slots = slots_dn; o->n_slots = k; o->slot_stride = D;
+            o->d_slot_norm_gamma = gemma ? s->layers[l - 1].g_post_ff : NULL; o->wait_add = l;
+        }
+        if (k > 1) { o->d_wait_flags = flags_of(s, me, 1); o->n_wait = k; }
+        o->d_resid_out = s->resid[1]; o->d_norm_gamma = ly->g_input;
+        o->out_mode = B200_OUT_STORE; o->d_out[0] = s->qkv; o->n_out = 1;
+        o = &ops[i++];                                           /* attention */
+        o->type = B200_OP_ATTN;
+        o->d_qkv = s->qkv; o->d_q_gamma = ly->g_qn; o->d_k_gamma = ly->g_kn; o->d_inv_freq = ly->inv_freq;
+        o->d_k_cache = ly->k_cache; o->d_v_cache = ly->v_cache; o->d_attn_out = s->attn_out;
+        o = &ops[i++];                                           /* o */
+        MV(o, &ly->o);
+        o->in_mode = B200_IN_VEC; o->d_in_vec = s->attn_out; o->out_mode = B200_OUT_STORE; o->n_out = k;
+        for (int p = 0; p < k; ++p) o->d_out[p] = (float *)(s->peer[p] + s->off_slots_o) + (size_t)me * D;
+        if (k > 1) { o->n_signal = k; o->signal_index = me; o->signal_add = l + 1; for (int p = 0; p < k; ++p) o->d_signal_flags[p] = flags_of(s, p, 0); }
+        o = &ops[i++];                                           /* gate/up */
+        MV(o, &ly->gateup);
+        o->in_mode = B200_IN_RESID; o->d_resid_in = s->resid[1]; o->d_resid_out = s->resid[0];
+        o->d_slots = slots_o; o->n_slots = k; o->slot_stride = D;
+        o->d_slot_norm_gamma = gemma ? ly->g_post_attn : NULL; o->d_norm_gamma = gemma ? ly->g_pre_ff : ly->g_post_attn;
+        if (k > 1) { o->d_wait_flags = flags_of(s, me, 0); o->n_wait = k; o->wait_add = l + 1; }
+        o->out_mode = B200_OUT_GLU; o->act = gemma ? 1 : 0; o->d_out[0] = s->act; o->n_out = 1;
+        o = &ops[i++];                                           /* down */
+        MV(o, &ly->down);
+        o->in_mode = B200_IN_VEC; o->d_in_vec = s->act; o->out_mode = B200_OUT_STORE; o->n_out = k;
+        for (int p = 0; p < k; ++p) o->d_out[p] = (float *)(s->peer[p] + s->off_slots_dn) + (size_t)me * D;
+        if (k > 1) { o->n_signal = k; o->signal_index = me; o->signal_add = l + 1; for (int p = 0; p < k; ++p) o->d_signal_flags[p] = flags_of(s, p, 1); }
+    }
+    b200_op *o = &ops[i++];                                      /* final norm + LM head */
+    MV(o, &s->lm);
+    o->in_mode = B200_IN_RESID; o->d_resid_in = s->resid[0]; o->d_slots = slots_dn; o->n_slots = k; o->slot_stride = D;
+    o->d_slot_norm_gamma = gemma ? s->layers[L - 1].g_post_ff : NULL; o->d_norm_gamma = s->g_final;
+    if (k > 1) { o->d_wait_flags = flags_of(s, me, 1); o->n_wait = k; o->wait_add = L; }
+    o->out_mode = B200_OUT_STORE; o->n_out = k; o->out_offset = (long long)me * s->V_l; o->argmax = 1;
+    for (int p = 0; p < k; ++p) o->d_out[p] = (float *)(s->peer[p] + s->off_logits);
+#undef MV
+    for (int j = 0; j < n && rc == 0; ++j)
+        if (ops[j].type == B200_OP_MATVEC) { rc = b200_op_plan_matvec(&ops[j], s->wtype); if (ops[j].spt == 2) wide = 1; }
+    if (rc != 0) { free(ops); return 1; }
+    if (!s->d_ops) CU_TRY(cudaMalloc((void **)&s->d_ops, (size_t)n * sizeof(b200_op)), { free(ops); return -1; });
+    if (!s->d_gbar) { s->d_gbar = (unsigned *)dev_zero(8); if (!s->d_gbar) { free(ops); return -1; } }
+    CU_TRY(cudaMemcpy(s->d_ops, ops, (size_t)n * sizeof(b200_op), cudaMemcpyHostToDevice), { free(ops); return -1; });
+    free(ops);
+    s->n_ops = n; s->plan_wide = wide;
+    return 0;
+}
+
+static int enqueue_token_fused(InferenceState *s, int with_lm)
+{
+    const int k = s->tp_size, me = s->tp_rank;
+    b200_token_args a;
+    memset(&a, 0, sizeof(a));
+    a.d_ops = s->d_ops; a.n_ops = with_lm ? s->n_ops : s->n_ops - 1; a.wtype = s->wtype; a.wide = s->plan_wide;
+    a.d_emb = s->emb; a.emb_rows = s->V; a.emb_scale = s->emb_scale; a.eps = 1e-6f;
+    a.n_q = s->Hq_l; a.n_kv = s->Hkv_l; a.hd = s->hd; a.max_seq = s->max_seq; a.n_split = s->n_split;
+    a.d_pos = s->d_pos; a.d_tokens = s->d_tokens; a.d_prompt_len = s->d_prompt_len; a.d_epoch = s->d_epoch;
+    a.epoch_mul = s->L + 1; a.d_err = s->d_err;
+    a.d_attn_scratch = s->attn_scratch; a.d_attn_tickets = s->attn_tickets; a.d_argmax_scratch = s->am_scratch;
+    a.d_grid_barrier = s->d_gbar;
+    a.pick_token = with_lm; a.n_ranks = k; a.rank = me; a.argmax_add = s->L;
+    for (int p = 0; p < k; ++p) {
+        a.d_argmax_val[p] = (float *)(s->peer[p] + s->off_am_val) + me;
+        a.d_argmax_idx[p] = (int *)(s->peer[p] + s->off_am_idx) + me;
+        a.d_argmax_signal_flags[p] = flags_of(s, p, 2);
+    }
+    a.d_rank_vals = (const float *)(s->comm + s->off_am_val);
+    a.d_rank_idx = (const int *)(s->comm + s->off_am_idx);
+    a.d_argmax_wait_flags = flags_of(s, me, 2);
+    K_TRY(b200_decode_token(&a, g_rt.stream), return -1);
+    return 0;
+}
+
 static int capture(InferenceState *s, int with_lm, int pdl, cudaGraphExec_t *out)
 {
     cudaGraph_t g = NULL;
     CU_TRY(cudaStreamBeginCapture(g_rt.stream, cudaStreamCaptureModeThreadLocal), return -1);
     const unsigned long long before = b200_launch_count(0);
-    int rc = enqueue_token(s, with_lm, pdl);
+    int rc = s->fused ? enqueue_token_fused(s, with_lm) : enqueue_token(s, with_lm, pdl);
     if (with_lm) s->kernels_full = (int)(b200_launch_count(0) - before);
     else s->kernels_nolm = (int)(b200_launch_count(0) - before);
     cudaError_t e = cudaStreamEndCapture(g_rt.stream, &g);
@@ -508,6 +603,21 @@ static int ensure_graphs(InferenceState *s)
     if (!s->finished) { fprintf(stderr, "[FastGen] state is not fully loaded\n"); return -1; }
     if (!s->connected) { fprintf(stderr, "[FastGen] tensor-parallel peers are not connected (llmb200_state_connect)\n"); return -1; }
     free_graphs(s);
+    /* Preferred: the whole token as one persistent kernel. Falls back to the kernel-per-step graph when
+     * the model is outside that kernel's limits, when LLMB200_TOKEN_KERNEL=0, or when its capture fails. */
+    s->fused = 0;
+    const char *tk = getenv("LLMB200_TOKEN_KERNEL");
+    if (!(tk && tk[0] == '0')) {
+        int pr = build_plan(s);
+        if (pr < 0) return -1;
+        if (pr == 0) {
+            s->fused = 1;
+            if (capture(s, 1, 0, &s->g_full) == 0 && capture(s, 0, 0, &s->g_nolm) == 0) return 0;
+            fprintf(stderr, "[FastGen] whole-token kernel could not be captured; using one kernel per step\n");
+            free_graphs(s);
+            s->fused = 0;
+        }
+    }
     if (capture(s, 1, s->use_pdl, &s->g_full) != 0 || capture(s, 0, s->use_pdl, &s->g_nolm) != 0) {
         if (s->use_pdl) {
             fprintf(stderr, "[FastGen] graph capture with programmatic dependent launch failed; retrying without\n");
@@ -645,6 +755,7 @@ void inference_state_free(InferenceState *s)
     }
     cudaFree(s->lm.w); cudaFree(s->g_final); cudaFree(s->emb);
     cudaFree(s->resid[0]); cudaFree(s->resid[1]); cudaFree(s->qkv); cudaFree(s->attn_out); cudaFree(s->act);
+    cudaFree(s->d_ops); cudaFree(s->d_gbar);
     cudaFree(s->attn_scratch); cudaFree(s->am_scratch); cudaFree(s->attn_tickets); cudaFree(s->mv_ticket);
     cudaFree(s->d_pos);
     for (int p = 0; p < s->tp_size; ++p)
