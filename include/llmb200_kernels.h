@@ -235,6 +235,9 @@ typedef struct b200_token_args {
     float *d_argmax_val[B200_MAX_PEERS]; int *d_argmax_idx[B200_MAX_PEERS]; int n_ranks, rank;
     const float *d_rank_vals; const int *d_rank_idx;   /* [n_ranks] pairs pushed by the ranks (TP) */
     const unsigned *d_argmax_wait_flags; unsigned *d_argmax_signal_flags[B200_MAX_PEERS]; int argmax_add;
+    /* optional trace, 4 words per step written by block 0: nanosecond timer when step i starts [4i], is
+     * done [4i+1], has its input vector [4i+2], gets its first weights [4i+3]; 4*n_ops words, or NULL */
+    unsigned long long *d_step_ns;
 } b200_token_args;
 
 int b200_decode_token(const b200_token_args *a, void *stream);

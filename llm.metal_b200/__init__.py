@@ -117,7 +117,7 @@ SYMBOLS_MAIN = {
                             "llmb200_state_begin", "llmb200_state_load_layer", "llmb200_state_finish",
                             "llmb200_state_set_eos", "llmb200_last_decode_ms", "llmb200_last_prefill_ms",
                             "llmb200_state_error", "llmb200_state_run_device_steps", "llmb200_state_profile_token",
-                            "llmb200_state_time_kind",
+                            "llmb200_state_time_kind", "llmb200_state_step_trace",
                             "llmb200_state_weight_bytes", "llmb200_state_position", "llmb200_state_graph_kernels",
                             "llmb200_state_export_weight"],
 }
@@ -174,6 +174,7 @@ def lib():
         "llmb200_state_error": (i, [vp]), "llmb200_state_run_device_steps": (C.c_float, [vp, i]),
         "llmb200_state_profile_token": (i, [vp, c_float_p, c_int_p]),
         "llmb200_state_time_kind": (C.c_float, [vp, i, i, c_int_p]),
+        "llmb200_state_step_trace": (i, [vp, C.POINTER(C.c_ulonglong), i]),
         "llmb200_state_weight_bytes": (C.c_ulonglong, [vp]), "llmb200_state_position": (i, [vp]),
         "llmb200_state_graph_kernels": (i, [vp, i]),
         "llmb200_state_export_weight": (sz, [vp, i, i, vp, sz]),

@@ -36,24 +36,34 @@ __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
     }
 }
 
+// Thread layout: the block's 256 threads are split into G head groups; a head group is KL key lanes of
+// 8 threads; the 8 threads of a key lane split the head dimension (DPT = HD/8 values each). A key lane
+// walks keys kl, kl+KL, ... of the block's slice with its own online softmax (running max, sum and
+// output), so nothing is exchanged between threads while keys stream in; K and V rows are prefetched
+// two keys ahead, the first ones before the query is even normalised. At the end the key lanes of a
+// head are merged (shuffles inside a warp, shared memory across warps).
 template <int HD, int G>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap)
 {
-    constexpr int TPK = HD / 8;                 // threads that share one key row in the PV pass
-    constexpr int KG = ATT_THREADS / TPK;       // key rows processed side by side
+    constexpr int DPT = HD / 8;                 // head-dim values per thread
+    constexpr int NV = DPT / 8;                 // 16-byte loads per K (and per V) row per thread
+    constexpr int TPH = ATT_THREADS / G;        // threads per head group
+    constexpr int KL = TPH / 8;                 // key lanes per head
+    constexpr int WPH = TPH / 32;               // warps per head
     constexpr int HALF = HD / 2;
+    constexpr int PF = 2;                       // keys in flight per key lane
     extern __shared__ __align__(16) float sm[];
     float *q_s = sm;                            // [G][HD]
     float *k_new = q_s + G * HD;                // [HD]
     float *v_new = k_new + HD;                  // [HD]
-    float *ml = v_new + HD;                     // [2*G] running max, sum
-    float *scores = ml + 2 * G;                 // [G][chunk_cap]
-    float *ored = scores + (size_t)G * chunk_cap;  // [KG][G][HD]
+    float *mrg = v_new + HD;                    // [G][WPH][HD + 2] merge buffer across warps
     __shared__ int s_last;
+    (void)chunk_cap;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = ATT_THREADS / 32;
     const int split = blockIdx.x, kvh = blockIdx.y;
+    const int g = tid / TPH, r = tid - g * TPH, kl = r >> 3, dl = r & 7;
 
     pdl_launch_dependents();
     pdl_wait();
@@ -62,10 +72,23 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap
     const int n = pos + 1;
     const int chunk = (n + p.n_split - 1) / p.n_split;
     const int j0 = min(split * chunk, n), j1 = min(j0 + chunk, n);
-    const int len = j1 - j0;
 
     __half *kc = static_cast<__half *>(p.d_k_cache) + (size_t)kvh * p.max_seq * HD;
     __half *vc = static_cast<__half *>(p.d_v_cache) + (size_t)kvh * p.max_seq * HD;
+
+    // ---- start the first K/V rows of this key lane on their way ----
+    static_assert(PF == 2, "the key loop below is unrolled for two slots");
+    uint4 kq0[NV], vq0[NV], kq1[NV], vq1[NV];
+    auto fetch = [&](uint4 (&kq)[NV], uint4 (&vq)[NV], int j) {
+        if (j < j1 && j != pos) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * HD + dl * DPT);
+            const uint4 *vr = reinterpret_cast<const uint4 *>(vc + (size_t)j * HD + dl * DPT);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) { kq[i] = kr[i]; vq[i] = vr[i]; }
+        }
+    };
+    fetch(kq0, vq0, j0 + kl);
+    fetch(kq1, vq1, j0 + kl + KL);
 
     // ---- normalise + rotate the G query heads and the new key; fetch the new value ----
     for (int vi = warp; vi <= G; vi += nw) {
@@ -73,7 +96,7 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap
         const float *src = is_k ? p.d_qkv + (size_t)p.n_q * HD + (size_t)kvh * HD
                                 : p.d_qkv + (size_t)(kvh * G + vi) * HD;
         const float *gamma = is_k ? p.d_k_gamma : p.d_q_gamma;
-        float a[HALF / 32 > 0 ? HALF / 32 : 1], b[HALF / 32 > 0 ? HALF / 32 : 1];
+        float a[HALF / 32], b[HALF / 32];
         float ss = 0.0f;
 #pragma unroll
         for (int j = 0; j < HALF / 32; ++j) {
@@ -93,9 +116,8 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap
 #pragma unroll
         for (int j = 0; j < HALF / 32; ++j) {
             const int d = lane + 32 * j;
-            const float ang = (float)pos * p.d_inv_freq[d];
             float sn, cs;
-            sincosf(ang, &sn, &cs);
+            sincosf((float)pos * p.d_inv_freq[d], &sn, &cs);
             const float r0 = a[j] * cs - b[j] * sn;
             const float r1 = a[j] * sn + b[j] * cs;
             if (is_k) {
@@ -117,93 +139,89 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap
     }
     __syncthreads();
 
-    // ---- scores: one thread per key row ----
+    // ---- stream the keys of this lane: online softmax in registers ----
+    float q[DPT], acc[DPT];
+#pragma unroll
+    for (int e = 0; e < DPT; ++e) { q[e] = q_s[g * HD + dl * DPT + e]; acc[e] = 0.0f; }
     const float scale = 1.0f / sqrtf((float)HD);
-    for (int j = j0 + tid; j < j1; j += ATT_THREADS) {
-        float acc[G];
+    float m = -INFINITY, l = 0.0f;
+    auto one_key = [&](uint4 (&kq)[NV], uint4 (&vq)[NV], int j) {
+        const bool valid = j < j1;              // every lane of the warp runs the shuffles; only valid keys count
+        float kf[DPT], vf[DPT];
+        if (!valid) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) acc[g] = 0.0f;
-        if (j == pos) {
-            for (int d = 0; d < HD; ++d) {
-                const float kv = k_new[d];
+            for (int e = 0; e < DPT; ++e) { kf[e] = 0.0f; vf[e] = 0.0f; }
+        } else if (j == pos) {
 #pragma unroll
-                for (int g = 0; g < G; ++g) acc[g] = fmaf(q_s[g * HD + d], kv, acc[g]);
-            }
+            for (int e = 0; e < DPT; ++e) { kf[e] = k_new[dl * DPT + e]; vf[e] = v_new[dl * DPT + e]; }
         } else {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * HD);
-#pragma unroll 4
-            for (int c = 0; c < HD / 8; ++c) {
-                float kf[8];
-                halves8_to_float(kr[c], kf);
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(q_s + g * HD + 8 * c);
-                    const float4 qb = *reinterpret_cast<const float4 *>(q_s + g * HD + 8 * c + 4);
-                    float t = acc[g];
-                    t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t); t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
-                    t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t); t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
-                    acc[g] = t;
-                }
+            for (int i = 0; i < NV; ++i) {
+                halves8_to_float(kq[i], kf + 8 * i);
+                halves8_to_float(vq[i], vf + 8 * i);
             }
         }
+        fetch(kq, vq, j + PF * KL);             // refill these registers with the key two rounds ahead
+        float s = 0.0f;
 #pragma unroll
-        for (int g = 0; g < G; ++g) scores[(size_t)g * chunk_cap + (j - j0)] = acc[g] * scale;
-    }
-    __syncthreads();
-
-    // ---- per head: max, exponentials, sum ----
-    for (int g = warp; g < G; g += nw) {
-        float *sc = scores + (size_t)g * chunk_cap;
-        float m = -INFINITY;
-        for (int i = lane; i < len; i += 32) m = fmaxf(m, sc[i]);
-        m = warp_max(m);
-        float l = 0.0f;
-        for (int i = lane; i < len; i += 32) { const float e = expf(sc[i] - m); sc[i] = e; l += e; }
-        l = warp_sum(l);
-        if (lane == 0) { ml[2 * g] = m; ml[2 * g + 1] = l; }
-    }
-    __syncthreads();
-
-    // ---- unnormalised output: KG key rows side by side, 8 dims per thread ----
-    {
-        const int kg = tid / TPK, dl = tid % TPK;
-        float acc[G][8];
+        for (int e = 0; e < DPT; ++e) s = fmaf(q[e], kf[e], s);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s *= scale;
+        if (valid) {
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn), pj = expf(s - mn);
+            l = fmaf(l, corr, pj);
 #pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[g][e] = 0.0f;
-        for (int j = j0 + kg; j < j1; j += KG) {
-            float vf[8];
-            if (j == pos) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) vf[e] = v_new[8 * dl + e];
-            } else {
-                halves8_to_float(reinterpret_cast<const uint4 *>(vc + (size_t)j * HD)[dl], vf);
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pj = scores[(size_t)g * chunk_cap + (j - j0)];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
-            }
+            for (int e = 0; e < DPT; ++e) acc[e] = fmaf(acc[e], corr, pj * vf[e]);
+            m = mn;
         }
+    };
+    // same trip count for every key lane of the block, so that the warp-wide shuffles stay convergent
+    const int rounds = (j1 - j0 + PF * KL - 1) / (PF * KL);
+    for (int it = 0, j = j0 + kl; it < rounds; ++it, j += PF * KL) {
+        one_key(kq0, vq0, j);
+        one_key(kq1, vq1, j + KL);
+    }
+
+    // ---- merge the key lanes of a head: inside the warp, then across the head's warps ----
 #pragma unroll
-        for (int g = 0; g < G; ++g)
+    for (int o = 8; o < 32; o <<= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
+        const float mn = fmaxf(m, mo);
+        const float ca = (m == -INFINITY) ? 0.0f : expf(m - mn), cb = (mo == -INFINITY) ? 0.0f : expf(mo - mn);
+        l = l * ca + lo * cb;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) ored[((size_t)kg * G + g) * HD + 8 * dl + e] = acc[g][e];
+        for (int e = 0; e < DPT; ++e) acc[e] = acc[e] * ca + __shfl_xor_sync(0xffffffffu, acc[e], o) * cb;
+        m = mn;
+    }
+    const int wh = r >> 5;                      // warp index inside the head group
+    if ((r & 31) < 8) {                         // key lane 0 of each warp holds the warp's state
+        float *dst = mrg + ((size_t)g * WPH + wh) * (HD + 2);
+#pragma unroll
+        for (int e = 0; e < DPT; ++e) dst[dl * DPT + e] = acc[e];
+        if (dl == 0) { dst[HD] = m; dst[HD + 1] = l; }
     }
     __syncthreads();
-    // scratch: [n_q][n_split][HD + 2]
-    for (int o = tid; o < G * HD; o += ATT_THREADS) {
-        const int g = o / HD, d = o % HD;
+    // scratch: [n_q][n_split][HD + 2] = unnormalised output, running max, sum
+    for (int o = tid; o < G * (HD + 2); o += ATT_THREADS) {
+        const int gg = o / (HD + 2), d = o - gg * (HD + 2);
+        const float *src = mrg + (size_t)gg * WPH * (HD + 2);
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WPH; ++w) M = fmaxf(M, src[w * (HD + 2) + HD]);
         float v = 0.0f;
-#pragma unroll 4
-        for (int k = 0; k < KG; ++k) v += ored[((size_t)k * G + g) * HD + d];
-        p.d_scratch[((size_t)(kvh * G + g) * p.n_split + split) * (HD + 2) + d] = v;
-    }
-    if (tid < 2 * G) {
-        const int g = tid >> 1;
-        p.d_scratch[((size_t)(kvh * G + g) * p.n_split + split) * (HD + 2) + HD + (tid & 1)] = ml[tid];
+        if (d == HD) v = M;
+        else {
+#pragma unroll
+            for (int w = 0; w < WPH; ++w) {
+                const float mw = src[w * (HD + 2) + HD];
+                const float c = (mw == -INFINITY) ? 0.0f : expf(mw - M);
+                v = fmaf(src[w * (HD + 2) + (d == HD + 1 ? HD + 1 : d)], c, v);
+            }
+        }
+        p.d_scratch[((size_t)(kvh * G + gg) * p.n_split + split) * (HD + 2) + d] = v;
     }
 
     // ---- the last block of this KV head merges the splits ----
@@ -213,22 +231,37 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int o = tid; o < G * HD; o += ATT_THREADS) {
-        const int g = o / HD, d = o % HD;
-        const float *base = p.d_scratch + (size_t)(kvh * G + g) * p.n_split * (HD + 2);
-        float M = -INFINITY;
-        for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, __ldcg(base + (size_t)s * (HD + 2) + HD));
-        float L = 0.0f, acc = 0.0f;
+    // Two short passes instead of one long dependent loop per output: first all (max, sum) pairs are
+    // fetched at once and turned into one weight per (head, split) in shared memory, then every output
+    // is a weighted sum whose loads do not depend on anything and can all be in flight together.
+    float *m_sm = mrg, *w_sm = mrg + G * p.n_split;
+    for (int i = tid; i < G * p.n_split; i += ATT_THREADS) {
+        const int gg = i / p.n_split, s = i - gg * p.n_split;
+        const float *rec = p.d_scratch + ((size_t)(kvh * G + gg) * p.n_split + s) * (HD + 2) + HD;
+        m_sm[i] = __ldcg(rec);
+        w_sm[i] = __ldcg(rec + 1);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float M = -INFINITY, L = 0.0f;
+        for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, m_sm[tid * p.n_split + s]);
         for (int s = 0; s < p.n_split; ++s) {
-            const float m = __ldcg(base + (size_t)s * (HD + 2) + HD);
-            const float l = __ldcg(base + (size_t)s * (HD + 2) + HD + 1);
-            if (l > 0.0f) {
-                const float w = expf(m - M);
-                L = fmaf(l, w, L);
-                acc = fmaf(__ldcg(base + (size_t)s * (HD + 2) + d), w, acc);
-            }
+            const float ls = w_sm[tid * p.n_split + s];
+            const float w = ls > 0.0f ? expf(m_sm[tid * p.n_split + s] - M) : 0.0f;
+            L = fmaf(ls, w, L);
+            w_sm[tid * p.n_split + s] = w;
         }
-        p.d_out[(size_t)(kvh * G + g) * HD + d] = acc / L;
+        const float inv = 1.0f / L;
+        for (int s = 0; s < p.n_split; ++s) w_sm[tid * p.n_split + s] *= inv;
+    }
+    __syncthreads();
+    for (int o = tid; o < G * HD; o += ATT_THREADS) {
+        const int gg = o / HD, d = o % HD;
+        const float *base = p.d_scratch + (size_t)(kvh * G + gg) * p.n_split * (HD + 2) + d;
+        float acc2 = 0.0f;
+#pragma unroll 8
+        for (int s = 0; s < p.n_split; ++s) acc2 = fmaf(__ldcg(base + (size_t)s * (HD + 2)), w_sm[gg * p.n_split + s], acc2);
+        p.d_out[(size_t)(kvh * G + gg) * HD + d] = acc2;
     }
     if (tid == 0) p.d_tickets[kvh] = 0u;
 }
@@ -237,8 +270,10 @@ template <int HD, int G>
 int launch_attn(const b200_attn_args &a, cudaStream_t st)
 {
     const int chunk_cap = (a.max_seq + a.n_split - 1) / a.n_split;
-    const int KG = ATT_THREADS / (HD / 8);
-    const size_t smem = ((size_t)G * HD + 2 * HD + 2 * G + (size_t)G * chunk_cap + (size_t)KG * G * HD) * sizeof(float);
+    const int WPH = ATT_THREADS / G / 32;
+    size_t mrg_floats = (size_t)G * WPH * (HD + 2);
+    if (mrg_floats < (size_t)2 * G * a.n_split) mrg_floats = (size_t)2 * G * a.n_split;
+    const size_t smem = ((size_t)G * HD + 2 * HD + mrg_floats) * sizeof(float);
     auto kern = attn_decode_kernel<HD, G>;
     if (smem > 200 * 1024) return B200_E_TOOLARGE;
     if (smem > 48 * 1024) {

@@ -35,9 +35,10 @@ constexpr int ATT_T = 256;                           // consumer threads that wo
 struct Smem {
     unsigned char *ring;
     uint64_t *full, *empty;
-    float *wpart;        // [2][TK_MAX_WARPS][8]
+    float *wpart;        // [TK_SLOTS][TK_MAX_WARPS][8] partial row sums of the stage in each slot
+    int *cnt;            // [TK_SLOTS] warps that have delivered their partials
     float *red;          // [8][32]
-    float *am_v; int *am_i;   // [64] each
+    float *am_v; int *am_i;   // [TK_MAX_WARPS * 8] each
     int *flags;          // [0] abort, [1] last-block
     float *att;          // TK_ATT_BYTES, also xs
 };
@@ -49,16 +50,18 @@ __device__ __forceinline__ Smem carve(unsigned char *base)
     unsigned char *p = base + (size_t)TK_SLOTS * TK_SLOT_BYTES;
     s.full = reinterpret_cast<uint64_t *>(p); p += TK_SLOTS * 8;
     s.empty = reinterpret_cast<uint64_t *>(p); p += TK_SLOTS * 8;
-    s.wpart = reinterpret_cast<float *>(p); p += 2 * TK_MAX_WARPS * 8 * 4;
+    s.wpart = reinterpret_cast<float *>(p); p += TK_SLOTS * TK_MAX_WARPS * 8 * 4;
+    s.cnt = reinterpret_cast<int *>(p); p += TK_SLOTS * 4 + 32;
     s.red = reinterpret_cast<float *>(p); p += 8 * 32 * 4;
-    s.am_v = reinterpret_cast<float *>(p); p += 64 * 4;
-    s.am_i = reinterpret_cast<int *>(p); p += 64 * 4;
+    s.am_v = reinterpret_cast<float *>(p); p += TK_MAX_WARPS * 8 * 4;
+    s.am_i = reinterpret_cast<int *>(p); p += TK_MAX_WARPS * 8 * 4;
     s.flags = reinterpret_cast<int *>(p); p += 64;
     s.att = reinterpret_cast<float *>(p);
     return s;
 }
-constexpr size_t TK_SMEM_BYTES = (size_t)TK_SLOTS * TK_SLOT_BYTES + TK_SLOTS * 16 + 2 * TK_MAX_WARPS * 8 * 4 + 8 * 32 * 4 +
-                                 64 * 8 + 64 + TK_ATT_BYTES;
+constexpr size_t TK_SMEM_BYTES = (size_t)TK_SLOTS * TK_SLOT_BYTES + TK_SLOTS * 16 + TK_SLOTS * TK_MAX_WARPS * 8 * 4 + (TK_SLOTS * 4 + 32) +
+                                 8 * 32 * 4 + TK_MAX_WARPS * 8 * 8 + 64 + TK_ATT_BYTES;
+static_assert(TK_SMEM_BYTES <= 232448, "more shared memory than an sm_100 block can have");
 
 // Rows of a step owned by this block, and by each of its consumer groups.
 struct RowSplit { int r0, r1; };
@@ -79,6 +82,13 @@ __device__ __forceinline__ RowSplit group_rows(const b200_op &op, const RowSplit
     r.r0 = b.r0 + (int)((long long)units * g / op.NG) * ralign;
     r.r1 = b.r0 + (int)((long long)units * (g + 1) / op.NG) * ralign;
     return r;
+}
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
 }
 
 // mbarrier wait that also ends as soon as the block's abort flag is up, so that after one failed wait
@@ -119,7 +129,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned *counter, unsigned target,
 // ---------------------------------------------------------------------------
 template <int WT, int SPT, int RB>
 __device__ __forceinline__ void matvec_step(const b200_op &op, const b200_token_args &p, const Smem &sm, int tid, int pos,
-                                            unsigned &fill_parity, float &best_v, int &best_i)
+                                            unsigned &fill_parity, float &best_v, int &best_i, unsigned long long *trace)
 {
     constexpr int E = (WT == B200_WT_Q8) ? 16 : 8;
     const int T = op.T, NG = op.NG, spg = TK_SLOTS / NG;
@@ -253,6 +263,7 @@ __device__ __forceinline__ void matvec_step(const b200_op &op, const b200_token_
             }
         }
 
+        if (trace && tid == 0) trace[2] = global_ns();
         // ---------------- this group's stages ----------------
         uint32_t qoff[SPT], soff[SPT];
 #pragma unroll
@@ -264,11 +275,11 @@ __device__ __forceinline__ void matvec_step(const b200_op &op, const b200_token_
         const uint32_t ring_s = smem_u32(sm.ring), stride = (uint32_t)op.row_stride;
         const RowSplit gr = group_rows(op, br, g);
         const int nst = (gr.r1 - gr.r0 + RB - 1) / RB;
-        float *wp_base = sm.wpart + (size_t)(g * nwg) * 8;          // this group's warps; 2 buffers of TK_MAX_WARPS*8 apart
         for (int k = 0; k < nst; ++k) {
             const int slot = g * spg + (k % spg);
             const unsigned par = ((fill_parity >> slot) + (unsigned)(k / spg)) & 1u;
             if (!mbar_wait_or_abort(&sm.full[slot], par, sm.flags)) { sm.flags[0] = 1; if (p.d_err) *p.d_err = 3; }
+            if (trace && tid == 0 && k == 0) trace[3] = global_ns();
             const uint32_t sb = ring_s + (uint32_t)slot * TK_SLOT_BYTES;
             const int row0 = gr.r0 + k * RB;
             const int nr = min(RB, gr.r1 - row0);
@@ -299,15 +310,23 @@ __device__ __forceinline__ void matvec_step(const b200_op &op, const b200_token_
                     v[jb + j] = acc;
                 }
             }
+            // Warps run free of each other: each leaves its partial sums of the stage's rows in shared memory
+            // and counts itself in; the warp that arrives last (no waiting involved) adds the partials in warp
+            // order, emits the rows and hands the slot back to the producer.
             const float tot = reduce_rows<RB>(v, lane);
-            float *wp = wp_base + (size_t)(k & 1) * TK_MAX_WARPS * 8;
+            float *wp = sm.wpart + (size_t)slot * TK_MAX_WARPS * 8;
             if (lane < RB) wp[wg * 8 + lane] = tot;
-            named_barrier(2 + g, T);                    // every thread of the group is done with the slot
-            if (wg == 0) {
-                if (lane == 0) mbar_arrive(&sm.empty[slot]);
+            __threadfence_block();
+            int last = 0;
+            if (lane == 0) last = (atomicAdd(&sm.cnt[slot], 1) == nwg - 1);
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_block();
                 float y = 0.0f;
                 if (lane < RB)
                     for (int w = 0; w < nwg; ++w) y += wp[w * 8 + lane];
+                __syncwarp();
+                if (lane == 0) { sm.cnt[slot] = 0; mbar_arrive(&sm.empty[slot]); }
                 const int row = row0 + lane;
                 if (op.out_mode == B200_OUT_GLU) {
                     const float u = __shfl_down_sync(0xffffffffu, y, 1);
@@ -556,7 +575,8 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
 
     if (tid == 0) {
         for (int i = 0; i < TK_SLOTS; ++i) { mbar_init(&sm.full[i], 1); mbar_init(&sm.empty[i], 1); }
-        sm.flags[0] = 0; sm.flags[1] = 0;
+        sm.flags[0] = 0; sm.flags[1] = 0; sm.flags[2] = 0; sm.flags[3] = 0;
+        for (int i = 0; i < TK_SLOTS; ++i) sm.cnt[i] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -573,25 +593,27 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
                 if (op.type != B200_OP_MATVEC) continue;
                 const int rb = op.rb, NG = op.NG, spg = TK_SLOTS / NG;
                 const RowSplit br = block_rows(op);
-                int maxk = 0;
+                // per-group row ranges once per step: the issue loop below must stay a handful of instructions per copy
+                int g0[TK_SLOTS], g1[TK_SLOTS], maxk = 0;
                 for (int g = 0; g < NG; ++g) {
                     const RowSplit gr = group_rows(op, br, g);
+                    g0[g] = gr.r0; g1[g] = gr.r1;
                     maxk = max(maxk, (gr.r1 - gr.r0 + rb - 1) / rb);
                 }
                 const unsigned char *wbase = static_cast<const unsigned char *>(op.d_w);
+                const unsigned stride = (unsigned)op.row_stride;
                 for (int k = 0; k < maxk && !dead; ++k) {
                     for (int g = 0; g < NG; ++g) {
-                        const RowSplit gr = group_rows(op, br, g);
-                        const int row0 = gr.r0 + k * rb;
-                        if (row0 >= gr.r1) continue;
+                        const int row0 = g0[g] + k * rb;
+                        if (row0 >= g1[g]) continue;
                         const int slot = g * spg + (k % spg);
                         if (fills[slot] > 0 && !mbar_wait_or_abort(&sm.empty[slot], (unsigned)(fills[slot] - 1) & 1u, sm.flags)) {
                             sm.flags[0] = 1; if (p.d_err) *p.d_err = 2; dead = true; break;
                         }
                         if (*(volatile int *)sm.flags) { dead = true; break; }
-                        const unsigned bytes = (unsigned)min(rb, gr.r1 - row0) * (unsigned)op.row_stride;
+                        const unsigned bytes = (unsigned)min(rb, g1[g] - row0) * stride;
                         mbar_expect_tx(&sm.full[slot], bytes);
-                        bulk_load(sm.ring + (size_t)slot * TK_SLOT_BYTES, wbase + (long long)row0 * op.row_stride, bytes, &sm.full[slot]);
+                        bulk_load(sm.ring + (size_t)slot * TK_SLOT_BYTES, wbase + (size_t)row0 * stride, bytes, &sm.full[slot]);
                         ++fills[slot];
                     }
                 }
@@ -633,8 +655,10 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
             named_barrier(1, TK_CONSUMERS);
         }
         if (sm.flags[2]) break;
+        unsigned long long *trace = (p.d_step_ns && blockIdx.x == 0) ? p.d_step_ns + 4 * oi : nullptr;
+        if (trace && tid == 0) trace[0] = global_ns();
         if (s_op.type == B200_OP_MATVEC) {
-#define TK_MV(SPT_, RB_) matvec_step<WT, SPT_, RB_>(s_op, p, sm, tid, pos, fill_parity, best_v, best_i)
+#define TK_MV(SPT_, RB_) matvec_step<WT, SPT_, RB_>(s_op, p, sm, tid, pos, fill_parity, best_v, best_i, trace)
             if (s_op.spt == 1) {
                 switch (s_op.rb) {
                 case 8: TK_MV(1, 8); break;
@@ -653,14 +677,19 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
             else attention_step<256, 4>(s_op, p, sm, tid, pos);
             __threadfence();
         }
+        if (trace && tid == 0) trace[1] = global_ns();
         if (oi == p.n_ops - 1 && p.pick_token) {
             // this block's best row of the last step -> scratch, before the closing barrier
             const int T = s_op.T, g = tid / T, t = tid - g * T;
-            if (g < s_op.NG && (t >> 5) == 0 && (t & 31) < 8) { sm.am_v[g * 8 + (t & 31)] = best_v; sm.am_i[g * 8 + (t & 31)] = best_i; }
+            if ((tid & 31) < 8) {
+                const bool act = g < s_op.NG;
+                sm.am_v[(tid >> 5) * 8 + (tid & 31)] = act ? best_v : -INFINITY;
+                sm.am_i[(tid >> 5) * 8 + (tid & 31)] = act ? best_i : 0x7fffffff;
+            }
             named_barrier(1, TK_CONSUMERS);
             if (tid == 0) {
                 float bv = -INFINITY; int bi = 0x7fffffff;
-                for (int k = 0; k < s_op.NG * 8; ++k) if (better(sm.am_v[k], sm.am_i[k], bv, bi)) { bv = sm.am_v[k]; bi = sm.am_i[k]; }
+                for (int k = 0; k < TK_MAX_WARPS * 8; ++k) if (better(sm.am_v[k], sm.am_i[k], bv, bi)) { bv = sm.am_v[k]; bi = sm.am_i[k]; }
                 p.d_argmax_scratch[2 * blockIdx.x] = bv;
                 reinterpret_cast<int *>(p.d_argmax_scratch)[2 * blockIdx.x + 1] = bi;
                 __threadfence();

@@ -94,6 +94,7 @@ struct InferenceState {
     int prof_n, prof_cap, prof_on;
     /* whole-token kernel: step list on the device, barrier words, launch arguments */
     b200_op *d_ops; unsigned *d_gbar; int n_ops, fused, plan_wide;
+    unsigned long long *d_step_ns;   /* step trace of the whole-token kernel (LLMB200_TRACE=1) */
     int only_kind;           /* >= 0: enqueue_token launches only this kind of kernel (timing loops) */
     int *prof_kind;
 };
@@ -549,6 +550,7 @@ static int build_plan(InferenceState *s)
     CU_TRY(cudaMemcpy(s->d_ops, ops, (size_t)n * sizeof(b200_op), cudaMemcpyHostToDevice), { free(ops); return -1; });
     free(ops);
     s->n_ops = n; s->plan_wide = wide;
+    if (getenv("LLMB200_TRACE") && !s->d_step_ns) s->d_step_ns = (unsigned long long *)dev_zero((size_t)4 * n * 8);
     return 0;
 }
 
@@ -564,6 +566,7 @@ static int enqueue_token_fused(InferenceState *s, int with_lm)
     a.epoch_mul = s->L + 1; a.d_err = s->d_err;
     a.d_attn_scratch = s->attn_scratch; a.d_attn_tickets = s->attn_tickets; a.d_argmax_scratch = s->am_scratch;
     a.d_grid_barrier = s->d_gbar;
+    a.d_step_ns = s->d_step_ns;
     a.pick_token = with_lm; a.n_ranks = k; a.rank = me; a.argmax_add = s->L;
     for (int p = 0; p < k; ++p) {
         a.d_argmax_val[p] = (float *)(s->peer[p] + s->off_am_val) + me;
@@ -603,11 +606,12 @@ static int ensure_graphs(InferenceState *s)
     if (!s->finished) { fprintf(stderr, "[FastGen] state is not fully loaded\n"); return -1; }
     if (!s->connected) { fprintf(stderr, "[FastGen] tensor-parallel peers are not connected (llmb200_state_connect)\n"); return -1; }
     free_graphs(s);
-    /* Preferred: the whole token as one persistent kernel. Falls back to the kernel-per-step graph when
-     * the model is outside that kernel's limits, when LLMB200_TOKEN_KERNEL=0, or when its capture fails. */
+    /* LLMB200_TOKEN_KERNEL=1 selects the whole-token persistent kernel (one launch per token, device-wide
+     * barriers between steps). It is measured slower than the kernel-per-step graph at present -- its steps
+     * pay a device-wide barrier plus an input broadcast each -- so the graph of per-step kernels is the default. */
     s->fused = 0;
     const char *tk = getenv("LLMB200_TOKEN_KERNEL");
-    if (!(tk && tk[0] == '0')) {
+    if (tk && tk[0] == '1') {
         int pr = build_plan(s);
         if (pr < 0) return -1;
         if (pr == 0) {
@@ -783,6 +787,16 @@ int llmb200_state_graph_kernels(InferenceState *s, int with_lm_head)
 {
     if (!s || ensure_graphs(s) != 0) return -1;
     return with_lm_head ? s->kernels_full : s->kernels_nolm;
+}
+/* Step trace of the last whole-token launch (needs LLMB200_TRACE=1 at create time): 2*n words of the
+ * nanosecond timer, start and end of each step on block 0. Returns the number of steps copied. */
+int llmb200_state_step_trace(InferenceState *s, unsigned long long *out, int cap_steps)
+{
+    if (!s || !s->d_step_ns || !out) return 0;
+    int n = s->n_ops < cap_steps ? s->n_ops : cap_steps;
+    if (cudaStreamSynchronize(g_rt.stream) != cudaSuccess) return 0;
+    if (cudaMemcpy(out, s->d_step_ns, (size_t)4 * n * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    return n;
 }
 unsigned long long llmb200_state_weight_bytes(InferenceState *s) { return s ? s->weight_bytes : 0; }
 double llmb200_last_decode_ms(InferenceState *s, int *n) { if (n) *n = s->last_n_decoded; return s->last_decode_ms; }

@@ -225,3 +225,24 @@ def test_wmat_api_roundtrip(lib, pkg, synth):
     lib.metal_buf_free(b)
     lib.metal_buf_free(None)
     assert not lib.wmat_create_q8(w.ctypes.data_as(pkg.c_float_p), rows, 40)     # cols % 32 != 0
+
+
+def test_whole_token_kernel_gives_the_same_tokens(lib, pkg, synth, monkeypatch):
+    """The opt-in persistent whole-token kernel (LLMB200_TOKEN_KERNEL=1) must reproduce the per-step graph exactly."""
+    sp = pkg.spec("tiny-qwen3", gamma_jitter=0.1)
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 8)
+    prompt = make_prompt(synth, 16, sp.vocab_size)
+    outs = []
+    try:
+        for flag in ("0", "1"):
+            monkeypatch.setenv("LLMB200_TOKEN_KERNEL", flag)
+            state = lib.inference_state_create(model, 64, 0)
+            assert state
+            lib.llmb200_state_set_eos(state, None, 0)
+            outs.append(list(gpu_generate(lib, pkg, state, prompt, 32)))
+            assert lib.llmb200_state_graph_kernels(state, 1) == (1 if flag == "1" else 5 * sp.n_layers + 1)
+            lib.inference_state_free(state)
+    finally:
+        synth.llmb200_synth_free_qwen3(model)
+    assert outs[0] == outs[1]
+    om = O.model_qwen3(model, 0, 64, vocab=sp.vocab_size) if False else None
