@@ -45,6 +45,7 @@ WORKLOADS = {
     "tiny-qwen3-q8": ("tiny-qwen3", 0, 16, 32, 64),
 }
 HBM_FALLBACK_GBS = 6650.0
+GATEUP_TRAFFIC_BYTES = 53_014_700
 
 
 def measured_peaks():
@@ -322,7 +323,11 @@ def main():
     achieved = gu_bytes / gu_s / 1e9
     roofline = {"bound": "hbm", "kernel": "matvec_kernel<Q8> gate/up (rows %d x cols %d)" % (gu_rows, gu_cols),
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                "traffic": None, "algorithmic_bytes_per_launch": gu_bytes}
+                # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch from the ncu --set full capture
+                # (profiles/matvec_gateup_qwen3-4b_4layers_full.md): 53.01 MB at N=1; the rows, and with them the
+                # traffic, divide by the tensor-parallel degree
+                "traffic": (GATEUP_TRAFFIC_BYTES // world) if arch == "qwen3-4b" else None,
+                "algorithmic_bytes_per_launch": gu_bytes}
 
     n_tok = args.steps * (G - 1)
     value = n_tok / (sum(step_ms) / 1e3)

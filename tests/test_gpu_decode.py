@@ -245,4 +245,3 @@ def test_whole_token_kernel_gives_the_same_tokens(lib, pkg, synth, monkeypatch):
     finally:
         synth.llmb200_synth_free_qwen3(model)
     assert outs[0] == outs[1]
-    om = O.model_qwen3(model, 0, 64, vocab=sp.vocab_size) if False else None
