@@ -109,7 +109,8 @@ SYMBOLS_MAIN = {
                        "metal_buf_free", "metal_buf_ptr", "wmat_create_q8", "wmat_create_f16", "wmat_free", "wmat_convert",
                        "norm_upload", "layers_convert_upload", "layers_free"],
     "llmb200_kernels.h": ["b200_packed_row_stride", "b200_q8_pack", "b200_f16_pack", "b200_q8_unpack_blocks", "b200_matvec",
-                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_launch_count"],
+                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_op_plan_matvec", "b200_decode_token",
+                          "b200_launch_count"],
     "llmb200_inference.h": ["inference_state_create", "inference_state_create_gemma3", "inference_state_free",
                             "inference_generate", "inference_state_model_type", "inference_state_vocab_size",
                             "inference_state_reset", "inference_forward_token", "inference_state_load_eos",
@@ -156,6 +157,7 @@ def lib():
         "b200_attn_scratch_floats": (sz, [i, i, i]), "b200_attn_decode": (i, [C.POINTER(AttnArgs), vp]),
         "b200_attn_decode_static": (i, [C.POINTER(AttnArgs), vp]),
         "b200_tp_argmax_finalize": (i, [vp, vp, i, vp, vp, i, i, vp, vp, vp, vp, vp, i, vp]),
+        "b200_op_plan_matvec": (i, [vp, vp]), "b200_decode_token": (i, [vp, vp]),
         "b200_launch_count": (C.c_ulonglong, [i]),
         "inference_state_create": (vp, [vp, i, i]), "inference_state_create_gemma3": (vp, [vp, i, i]),
         "inference_state_free": (None, [vp]),
