@@ -89,6 +89,15 @@ class LayerWeightRef(C.Structure):
                 ("d_model", C.c_int), ("head_dim", C.c_int)]
 
 
+class GemmArgs(C.Structure):
+    """b200_gemm_args (include/llmb200_train_kernels.h)."""
+    _fields_ = [("A", C.c_void_p), ("a_row", C.c_longlong), ("a_col", C.c_longlong),
+                ("B", C.c_void_p), ("b_row", C.c_longlong), ("b_col", C.c_longlong),
+                ("C", C.c_void_p), ("ldc", C.c_longlong),
+                ("R", C.c_void_p), ("ldr", C.c_longlong),
+                ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("alpha", C.c_float)]
+
+
 class WMat(C.Structure):
     _fields_ = [("mbuf", C.c_void_p), ("rows", C.c_int), ("cols", C.c_int), ("nb", C.c_int)]
 
@@ -121,6 +130,22 @@ SYMBOLS_MAIN = {
                             "llmb200_state_time_kind", "llmb200_state_step_trace",
                             "llmb200_state_weight_bytes", "llmb200_state_position", "llmb200_state_graph_kernels",
                             "llmb200_state_export_weight"],
+    "llmb200_train_kernels.h": ["b200_gemm_f32", "b200_gemm_tf32", "b200_embed_rows", "b200_round_f16",
+                                "b200_transpose_f32", "b200_rms_norm_rows", "b200_rms_norm_bwd_rows",
+                                "b200_qk_norm_rope", "b200_qk_norm_rope_bwd", "b200_attn_train_fwd",
+                                "b200_attn_train_bwd", "b200_silu_mul_rows", "b200_silu_mul_bwd_rows", "b200_lora_add",
+                                "b200_softmax_ce_rows", "b200_sumsq_partials", "b200_clip_adamw"],
+    "llmb200_sft.h": ["sft_state_create", "sft_state_free", "sft_train_step", "forward_to_logits", "sft_backward",
+                      "sft_get_logits", "sft_get_dlogits", "sft_get_x_cpu", "sft_get_losses_cpu", "sft_get_seq_len",
+                      "sft_get_vocab_size", "sft_get_d_model", "sft_get_lora_rank", "sft_get_n_layers",
+                      "sft_get_emb_scale", "sft_get_token_emb", "sft_get_step_count", "sft_set_step_count",
+                      "sft_get_n_lora_grad_bufs", "sft_get_lora_grad_ptr", "sft_set_lora_grad", "sft_lora_update",
+                      "sft_save_lora", "sft_get_lora_weight_buf", "sft_get_lora_scaling", "sft_sync_lora_to_model",
+                      "llmb200_sft_begin", "llmb200_sft_load_layer", "llmb200_sft_finish",
+                      "llmb200_sft_forward_backward", "llmb200_sft_apply_update", "llmb200_sft_train_batch",
+                      "llmb200_sft_grad_vector", "llmb200_sft_param_vector", "llmb200_sft_last_grad_norm",
+                      "llmb200_sft_last_step_ms", "llmb200_sft_use_tensor_cores", "llmb200_sft_error",
+                      "llmb200_sft_export"],
 }
 SYMBOLS_SYNTH = {
     "llmb200_synth.h": ["llmb200_synth_tensor_id", "llmb200_synth_normal_range", "llmb200_synth_normal",
@@ -141,7 +166,7 @@ def lib():
     if not os.path.exists(path):
         _build.build_main()
     L = C.CDLL(path)
-    vp, i, ll, sz = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
+    vp, i, ll, sz, fl = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t, C.c_float
     sig = {
         "fast_metal_init": (i, []), "fast_metal_shutdown": (None, []), "metal_flush": (None, []),
         "metal_buf_create": (vp, [sz]), "metal_buf_from_data": (vp, [vp, sz]), "metal_buf_free": (None, [vp]),
@@ -180,6 +205,44 @@ def lib():
         "llmb200_state_weight_bytes": (C.c_ulonglong, [vp]), "llmb200_state_position": (i, [vp]),
         "llmb200_state_graph_kernels": (i, [vp, i]),
         "llmb200_state_export_weight": (sz, [vp, i, i, vp, sz]),
+        # ---- llmb200_train_kernels.h
+        "b200_gemm_f32": (i, [C.POINTER(GemmArgs), vp]), "b200_gemm_tf32": (i, [C.POINTER(GemmArgs), vp]),
+        "b200_embed_rows": (i, [vp, vp, i, i, i, fl, vp, vp]),
+        "b200_round_f16": (i, [vp, sz, vp]), "b200_transpose_f32": (i, [vp, i, i, vp, vp]),
+        "b200_rms_norm_rows": (i, [vp, vp, vp, i, i, fl, vp]),
+        "b200_rms_norm_bwd_rows": (i, [vp, vp, vp, vp, i, i, fl, i, fl, vp]),
+        "b200_qk_norm_rope": (i, [vp, ll, vp, vp, vp, i, i, i, i, i, fl, vp, vp, vp]),
+        "b200_qk_norm_rope_bwd": (i, [vp, vp, ll, vp, vp, vp, i, i, i, i, i, fl, vp]),
+        "b200_attn_train_fwd": (i, [vp, vp, vp, ll, i, i, i, i, i, fl, vp, vp, vp]),
+        "b200_attn_train_bwd": (i, [vp, vp, vp, vp, vp, ll, i, i, i, i, i, fl, vp, vp, ll, vp]),
+        "b200_silu_mul_rows": (i, [vp, i, i, vp, vp]), "b200_silu_mul_bwd_rows": (i, [vp, vp, i, i, vp, vp]),
+        "b200_lora_add": (i, [vp, ll, i, i, vp, vp, i, fl, i, vp]),
+        "b200_softmax_ce_rows": (i, [vp, vp, i, i, fl, vp, vp, vp]),
+        "b200_sumsq_partials": (i, [vp, sz, vp, i, vp]),
+        "b200_clip_adamw": (i, [vp, vp, vp, vp, sz, vp, i, fl, fl, fl, fl, fl, fl, fl, fl, i, vp, vp]),
+        # ---- llmb200_sft.h
+        "sft_state_create": (vp, [vp, i, i, fl]), "sft_state_free": (None, [vp]),
+        "sft_train_step": (fl, [vp, c_u32_p, c_u32_p, fl]),
+        "forward_to_logits": (None, [vp]), "sft_backward": (None, [vp]),
+        "sft_get_logits": (vp, [vp]), "sft_get_dlogits": (vp, [vp]),
+        "sft_get_x_cpu": (c_float_p, [vp]), "sft_get_losses_cpu": (c_float_p, [vp]),
+        "sft_get_seq_len": (i, [vp]), "sft_get_vocab_size": (i, [vp]), "sft_get_d_model": (i, [vp]),
+        "sft_get_lora_rank": (i, [vp]), "sft_get_n_layers": (i, [vp]), "sft_get_emb_scale": (fl, [vp]),
+        "sft_get_token_emb": (c_float_p, [vp]), "sft_get_step_count": (i, [vp]), "sft_set_step_count": (None, [vp, i]),
+        "sft_get_n_lora_grad_bufs": (i, [vp]), "sft_get_lora_grad_ptr": (c_float_p, [vp, i, c_int_p]),
+        "sft_set_lora_grad": (None, [vp, i, c_float_p, i]), "sft_lora_update": (None, [vp, fl]),
+        "sft_save_lora": (None, [vp, C.c_char_p]), "sft_get_lora_weight_buf": (vp, [vp, i, i]),
+        "sft_get_lora_scaling": (fl, [vp]), "sft_sync_lora_to_model": (None, [vp, vp]),
+        "llmb200_sft_begin": (vp, [C.POINTER(Config), i, i, i, fl]),
+        "llmb200_sft_load_layer": (i, [vp, i, C.POINTER(LayerWeightRef), fl, C.POINTER(c_float_p * 4)]),
+        "llmb200_sft_finish": (i, [vp, c_float_p, c_float_p, c_float_p, i]),
+        "llmb200_sft_forward_backward": (fl, [vp, c_u32_p, c_u32_p]),
+        "llmb200_sft_apply_update": (None, [vp, fl]),
+        "llmb200_sft_train_batch": (fl, [vp, c_u32_p, c_u32_p, fl]),
+        "llmb200_sft_grad_vector": (sz, [vp, C.POINTER(vp)]), "llmb200_sft_param_vector": (sz, [vp, C.POINTER(vp)]),
+        "llmb200_sft_last_grad_norm": (fl, [vp]), "llmb200_sft_last_step_ms": (fl, [vp, c_float_p]),
+        "llmb200_sft_use_tensor_cores": (i, [vp, i]), "llmb200_sft_error": (i, [vp]),
+        "llmb200_sft_export": (sz, [vp, i, i, vp, sz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

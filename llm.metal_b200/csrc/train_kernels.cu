@@ -1,0 +1,672 @@
+// Row-wise and attention kernels of the LoRA-SFT step (everything but the GEMMs).
+//
+// Arithmetic follows shaders/q8_kernels.metal: rms_norm :133-158,
+// rms_norm_train_backward :584-624, rope_train :495-538, rope_train_bwd
+// :997-1040, attn_train_fwd :769-851, attn_bwd_dq :857-925, attn_bwd_dkv
+// :931-968, repeat_kv / repeat_kv_bwd :476-492 / :973-992 (folded into the
+// indexing), silu_mul :337-348, silu_mul_backward :540-556, softmax_ce_train
+// :646-690, scale_tensor :627-633, clamp_tensor :1155-1161; the optimiser
+// follows src/nn/fast_sft.c:1045-1107. All fp32 (the gradient norm in double).
+//
+// These kernels move little data next to the projections (a few MB per layer
+// against hundreds of MB of weights); they are written for fusion -- no
+// transposed or repeated copies, residual adds and scalings folded in -- rather
+// than for peak bandwidth.
+#include "common.cuh"
+#include "../../include/llmb200_train_kernels.h"
+
+extern unsigned long long g_b200_launches;
+
+namespace {
+
+__device__ __forceinline__ float block_sum_f(float v, float *sh)
+{
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; ++i) t += sh[i];      // fixed order
+    return t;
+}
+
+__device__ __forceinline__ float block_max_f(float v, float *sh)
+{
+    v = warp_max(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float t = sh[0];
+    for (int i = 1; i < nw; ++i) t = fmaxf(t, sh[i]);
+    return t;
+}
+
+// ---- embedding -----------------------------------------------------------------------------
+__global__ void embed_rows_kernel(const float *emb, const uint32_t *tokens, int dim, int vocab, float scale, float *x)
+{
+    const int m = blockIdx.x;
+    uint32_t t = tokens[m];
+    if (t >= (uint32_t)vocab) t = 0;                                  // never read outside the table
+    const float *src = emb + (size_t)t * dim;
+    float *dst = x + (size_t)m * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = src[i] * scale;
+}
+
+// ---- RMSNorm over rows: one warp per row ----------------------------------------------------
+__global__ void rms_norm_rows_kernel(const float *x, const float *gamma, float *out, int rows, int dim, float eps)
+{
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int l = threadIdx.x & 31;
+    const float *xr = x + (size_t)row * dim;
+    float ss = 0.f;
+    for (int i = l; i < dim; i += 32) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    float *o = out + (size_t)row * dim;
+    for (int i = l; i < dim; i += 32) o[i] = xr[i] * inv * gamma[i];
+}
+
+__global__ void rms_norm_bwd_rows_kernel(const float *x, const float *dy, const float *gamma, float *dx, int rows,
+                                         int dim, float eps, int accumulate, float clamp)
+{
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int l = threadIdx.x & 31;
+    const float *xr = x + (size_t)row * dim, *dr = dy + (size_t)row * dim;
+    float ss = 0.f, dot = 0.f;
+    for (int i = l; i < dim; i += 32) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+        dot = fmaf(dr[i] * gamma[i], v, dot);
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    const float coeff = dot * inv * inv / (float)dim;
+    float *o = dx + (size_t)row * dim;
+    for (int i = l; i < dim; i += 32) {
+        float v = (gamma[i] * dr[i] - coeff * xr[i]) * inv;
+        if (accumulate) v += o[i];
+        if (clamp > 0.f) v = fminf(fmaxf(v, -clamp), clamp);
+        o[i] = v;
+    }
+}
+
+// ---- QK-norm + RoPE: one warp per (row, head) -----------------------------------------------
+// Heads 0..n_q-1 are q heads, n_q..n_q+n_kv-1 the k heads; both sit in qkv at column head*hd.
+template <int HD>
+__global__ void qk_norm_rope_kernel(const float *qkv, long long ld, const float *qg, const float *kg,
+                                    const float *inv_freq, int rows, int seq_len, int n_q, int n_kv, float eps,
+                                    float *q_out, float *k_out)
+{
+    constexpr int PER = HD / 64;                       // rotation pairs per lane
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int nh = n_q + n_kv;
+    if (unit >= rows * nh) return;
+    const int row = unit / nh, h = unit % nh, l = threadIdx.x & 31;
+    const float *src = qkv + (size_t)row * ld + (size_t)h * HD;
+    const float *g = h < n_q ? qg : kg;
+    float *dst = h < n_q ? q_out + ((size_t)row * n_q + h) * HD : k_out + ((size_t)row * n_kv + (h - n_q)) * HD;
+    float a[PER], b[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < PER; ++c) {
+        a[c] = src[l + 32 * c];
+        b[c] = src[l + 32 * c + HD / 2];
+        ss = fmaf(a[c], a[c], ss);
+        ss = fmaf(b[c], b[c], ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)HD + eps);
+    const float pos = (float)(row % seq_len);
+#pragma unroll
+    for (int c = 0; c < PER; ++c) {
+        const int d = l + 32 * c;
+        const float x0 = a[c] * inv * g[d], x1 = b[c] * inv * g[d + HD / 2];
+        float sn, cs;
+        sincosf(pos * inv_freq[d], &sn, &cs);
+        dst[d] = x0 * cs - x1 * sn;
+        dst[d + HD / 2] = x0 * sn + x1 * cs;
+    }
+}
+
+template <int HD>
+__global__ void qk_norm_rope_bwd_kernel(float *dqkv, const float *qkv, long long ld, const float *qg, const float *kg,
+                                        const float *inv_freq, int rows, int seq_len, int n_q, int n_kv, float eps)
+{
+    constexpr int PER = HD / 64;
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int nh = n_q + n_kv;
+    if (unit >= rows * nh) return;
+    const int row = unit / nh, h = unit % nh, l = threadIdx.x & 31;
+    const float *x = qkv + (size_t)row * ld + (size_t)h * HD;
+    float *d = dqkv + (size_t)row * ld + (size_t)h * HD;
+    const float *g = h < n_q ? qg : kg;
+    const float pos = (float)(row % seq_len);
+    float xa[PER], xb[PER], ga[PER], gb[PER];
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < PER; ++c) {
+        const int i = l + 32 * c;
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        const float y0 = d[i], y1 = d[i + HD / 2];
+        ga[c] = y0 * cs + y1 * sn;                     // rotation by -angle
+        gb[c] = -y0 * sn + y1 * cs;
+        xa[c] = x[i];
+        xb[c] = x[i + HD / 2];
+        ss = fmaf(xa[c], xa[c], ss);
+        ss = fmaf(xb[c], xb[c], ss);
+        dot = fmaf(ga[c] * g[i], xa[c], dot);
+        dot = fmaf(gb[c] * g[i + HD / 2], xb[c], dot);
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float inv = rsqrtf(ss / (float)HD + eps);
+    const float coeff = dot * inv * inv / (float)HD;
+#pragma unroll
+    for (int c = 0; c < PER; ++c) {
+        const int i = l + 32 * c;
+        d[i] = (g[i] * ga[c] - coeff * xa[c]) * inv;
+        d[i + HD / 2] = (g[i + HD / 2] * gb[c] - coeff * xb[c]) * inv;
+    }
+}
+
+// ---- causal attention, training form: one warp per (sequence, head, query) ---------------------
+// Dynamic shared memory per warp: HD floats (the query or d_out row) + N floats (the score row).
+constexpr int ATT_WARPS = 4;
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_train_fwd_kernel(const float *q, const float *k, const float *v, long long v_ld, int n_seq, int N, int n_q,
+                      int n_kv, float scale, float *probs, float *out)
+{
+    extern __shared__ float sh[];
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    float *qs = sh + (size_t)w * (HD + N), *sc = qs + HD;
+    const long long unit = (long long)blockIdx.x * ATT_WARPS + w;
+    if (unit >= (long long)n_seq * n_q * N) return;
+    const int i = (int)(unit % N), h = (int)((unit / N) % n_q), s = (int)(unit / ((long long)N * n_q));
+    const int kvh = h / (n_q / n_kv);
+    const size_t row0 = (size_t)s * N;
+    const float *qr = q + ((row0 + i) * n_q + h) * HD;
+    for (int d = l; d < HD; d += 32) qs[d] = qr[d];
+    __syncwarp();
+
+    float mx = -1e30f;
+    for (int j = l; j <= i; j += 32) {
+        const float4 *kr = reinterpret_cast<const float4 *>(k + ((row0 + j) * n_kv + kvh) * HD);
+        float dot = 0.f;
+#pragma unroll 8
+        for (int d4 = 0; d4 < HD / 4; ++d4) {
+            const float4 kk = kr[d4];
+            dot = fmaf(qs[4 * d4], kk.x, dot);
+            dot = fmaf(qs[4 * d4 + 1], kk.y, dot);
+            dot = fmaf(qs[4 * d4 + 2], kk.z, dot);
+            dot = fmaf(qs[4 * d4 + 3], kk.w, dot);
+        }
+        dot *= scale;
+        sc[j] = dot;
+        mx = fmaxf(mx, dot);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int j = l; j <= i; j += 32) {
+        const float e = expf(sc[j] - mx);
+        sc[j] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    float *pr = probs + (((size_t)s * n_q + h) * N + i) * N;
+    for (int j = l; j < N; j += 32) {
+        const float p = j <= i ? sc[j] * inv : 0.f;
+        if (j <= i) sc[j] = p;
+        pr[j] = p;
+    }
+    __syncwarp();
+    float *o = out + ((row0 + i) * n_q + h) * HD;
+    for (int d = l; d < HD; d += 32) {
+        float acc = 0.f;
+        for (int j = 0; j <= i; ++j) acc = fmaf(sc[j], v[(row0 + j) * v_ld + (size_t)kvh * HD + d], acc);
+        o[d] = acc;
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_bwd_dq_kernel(const float *d_out, const float *probs, const float *k, const float *v, long long v_ld, int n_seq,
+                   int N, int n_q, int n_kv, float scale, float *d_score, float *dqkv, long long ld)
+{
+    extern __shared__ float sh[];
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    float *os = sh + (size_t)w * (HD + N), *ds = os + HD;
+    const long long unit = (long long)blockIdx.x * ATT_WARPS + w;
+    if (unit >= (long long)n_seq * n_q * N) return;
+    const int i = (int)(unit % N), h = (int)((unit / N) % n_q), s = (int)(unit / ((long long)N * n_q));
+    const int kvh = h / (n_q / n_kv);
+    const size_t row0 = (size_t)s * N;
+    const float *dor = d_out + ((row0 + i) * n_q + h) * HD;
+    for (int d = l; d < HD; d += 32) os[d] = dor[d];
+    __syncwarp();
+    const float *pr = probs + (((size_t)s * n_q + h) * N + i) * N;
+    float dp = 0.f;
+    for (int j = l; j <= i; j += 32) {
+        const float4 *vr = reinterpret_cast<const float4 *>(v + (row0 + j) * v_ld + (size_t)kvh * HD);
+        float dot = 0.f;
+#pragma unroll 8
+        for (int d4 = 0; d4 < HD / 4; ++d4) {
+            const float4 vv = vr[d4];
+            dot = fmaf(os[4 * d4], vv.x, dot);
+            dot = fmaf(os[4 * d4 + 1], vv.y, dot);
+            dot = fmaf(os[4 * d4 + 2], vv.z, dot);
+            dot = fmaf(os[4 * d4 + 3], vv.w, dot);
+        }
+        ds[j] = dot;
+        dp = fmaf(pr[j], dot, dp);
+    }
+    dp = warp_sum(dp);
+    float *dsr = d_score + (((size_t)s * n_q + h) * N + i) * N;
+    for (int j = l; j < N; j += 32) {
+        const float g = j <= i ? pr[j] * (ds[j] - dp) * scale : 0.f;
+        if (j <= i) ds[j] = g;
+        dsr[j] = g;
+    }
+    __syncwarp();
+    float *dq = dqkv + (row0 + i) * ld + (size_t)h * HD;
+    for (int d = l; d < HD; d += 32) {
+        float acc = 0.f;
+        for (int j = 0; j <= i; ++j) acc = fmaf(ds[j], k[((row0 + j) * n_kv + kvh) * HD + d], acc);
+        dq[d] = acc;
+    }
+}
+
+// One warp per (sequence, kv head, key): dK and dV summed over the later queries of each q head
+// of the group, then over the group in head order (attn_bwd_dkv followed by repeat_kv_bwd).
+template <int HD>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_bwd_dkv_kernel(const float *d_score, const float *probs, const float *q, const float *d_out, int n_seq, int N,
+                    int n_q, int n_kv, float *dqkv, long long ld)
+{
+    constexpr int PER = HD / 32;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * ATT_WARPS + w;
+    if (unit >= (long long)n_seq * n_kv * N) return;
+    const int j = (int)(unit % N), kvh = (int)((unit / N) % n_kv), s = (int)(unit / ((long long)N * n_kv));
+    const int G = n_q / n_kv;
+    const size_t row0 = (size_t)s * N;
+    float dk[PER], dv[PER];
+#pragma unroll
+    for (int c = 0; c < PER; ++c) dk[c] = dv[c] = 0.f;
+    for (int g = 0; g < G; ++g) {
+        const int h = kvh * G + g;
+        const float *dsc = d_score + ((size_t)s * n_q + h) * N * N;
+        const float *prc = probs + ((size_t)s * n_q + h) * N * N;
+        float hk[PER], hv[PER];
+#pragma unroll
+        for (int c = 0; c < PER; ++c) hk[c] = hv[c] = 0.f;
+        for (int i = j; i < N; ++i) {
+            const float dsv = dsc[(size_t)i * N + j], pv = prc[(size_t)i * N + j];
+            const float *qr = q + ((row0 + i) * n_q + h) * HD;
+            const float *dor = d_out + ((row0 + i) * n_q + h) * HD;
+#pragma unroll
+            for (int c = 0; c < PER; ++c) {
+                hk[c] = fmaf(dsv, qr[l + 32 * c], hk[c]);
+                hv[c] = fmaf(pv, dor[l + 32 * c], hv[c]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < PER; ++c) { dk[c] += hk[c]; dv[c] += hv[c]; }
+    }
+    float *dkr = dqkv + (row0 + j) * ld + (size_t)(n_q + kvh) * HD;
+    float *dvr = dqkv + (row0 + j) * ld + (size_t)(n_q + n_kv + kvh) * HD;
+#pragma unroll
+    for (int c = 0; c < PER; ++c) { dkr[l + 32 * c] = dk[c]; dvr[l + 32 * c] = dv[c]; }
+}
+
+// ---- SwiGLU ------------------------------------------------------------------------------------
+__global__ void silu_mul_rows_kernel(const float *gu, int inter, float *act, size_t total)
+{
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = e / inter, i = e % inter;
+        const float g = gu[m * 2 * inter + i], u = gu[m * 2 * inter + inter + i];
+        act[e] = g / (1.0f + expf(-g)) * u;
+    }
+}
+
+__global__ void silu_mul_bwd_rows_kernel(const float *d_act, const float *gu, int inter, float *d_gu, size_t total)
+{
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = e / inter, i = e % inter;
+        const float g = gu[m * 2 * inter + i], u = gu[m * 2 * inter + inter + i], dy = d_act[e];
+        const float sig = 1.0f / (1.0f + expf(-g));
+        d_gu[m * 2 * inter + i] = dy * u * (sig * (1.0f + g * (1.0f - sig)));
+        d_gu[m * 2 * inter + inter + i] = dy * (g * sig);
+    }
+}
+
+// ---- LoRA up-projection added into the base projection -------------------------------------------
+template <int MAXR>
+__global__ void lora_add_kernel(float *y, long long ld, int col0, int n_cols, const float *mid, const float *B, int rank,
+                                float sc, int rows)
+{
+    __shared__ float ms[MAXR];
+    const int m = blockIdx.y;
+    if (threadIdx.x < rank) ms[threadIdx.x] = mid[(size_t)m * rank + threadIdx.x];
+    __syncthreads();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_cols) return;
+    const float *br = B + (size_t)c * rank;
+    float acc = 0.f;
+    for (int r = 0; r < rank; ++r) acc = fmaf(ms[r], br[r], acc);
+    y[(size_t)m * ld + col0 + c] += sc * acc;
+}
+
+// ---- softmax cross-entropy: one block per row ----------------------------------------------------
+__global__ void __launch_bounds__(1024)
+softmax_ce_rows_kernel(const float *logits, const uint32_t *targets, int vocab, float grad_scale, float *losses,
+                       float *dlogits)
+{
+    __shared__ float sh[32];
+    const size_t off = (size_t)blockIdx.x * vocab;
+    const float *lr = logits + off;
+    uint32_t tgt = targets[blockIdx.x];
+    if (tgt >= (uint32_t)vocab) tgt = 0;
+    float mx = -1e30f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, lr[i]);
+    mx = block_max_f(mx, sh);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(lr[i] - mx);
+    sum = block_sum_f(sum, sh);
+    const float lse = logf(sum) + mx;
+    if (threadIdx.x == 0) losses[blockIdx.x] = lse - lr[tgt];
+    float *dr = dlogits + off;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float p = expf(lr[i] - lse);
+        dr[i] = (p - ((uint32_t)i == tgt ? 1.0f : 0.0f)) * grad_scale;
+    }
+}
+
+// ---- frozen weights: binary16 values held as fp32, and their transposes ---------------------------
+__global__ void round_f16_kernel(float *w, size_t n)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        w[i] = __half2float(__float2half_rn(w[i]));
+}
+
+// dst[c, r] = src[r, c]; 32 x 32 tiles through shared memory so that both sides coalesce.
+__global__ void transpose_f32_kernel(const float *src, int rows, int cols, float *dst)
+{
+    __shared__ float t[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int r = r0 + i, c = c0 + threadIdx.x;
+        t[i][threadIdx.x] = (r < rows && c < cols) ? src[(size_t)r * cols + c] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int c = c0 + i, r = r0 + threadIdx.x;
+        if (c < cols && r < rows) dst[(size_t)c * rows + r] = t[threadIdx.x][i];
+    }
+}
+
+// ---- gradient norm, clip, AdamW ------------------------------------------------------------------
+__global__ void __launch_bounds__(256) sumsq_partials_kernel(const float *g, size_t n, double *partials)
+{
+    __shared__ double sh[8];
+    double acc = 0.0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const double v = (double)g[i];
+        acc += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < 8; ++i) t += sh[i];
+        partials[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+clip_adamw_kernel(float *p, float *g, float *m, float *v, size_t n, const double *partials, int n_partials,
+                  float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                  int apply_update, float *norm_out)
+{
+    __shared__ float s_scale;
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < n_partials; ++i) t += partials[i];          // same order in every block
+        const float norm = (float)sqrt(t);
+        s_scale = norm > max_norm ? max_norm / norm : 1.0f;
+        if (blockIdx.x == 0 && norm_out) norm_out[0] = norm;
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float gr = g[i];
+        if (scale != 1.0f) { gr *= scale; g[i] = gr; }
+        if (apply_update) {
+            const float mi = beta1 * m[i] + (1.0f - beta1) * gr;
+            const float vi = beta2 * v[i] + (1.0f - beta2) * gr * gr;
+            m[i] = mi;
+            v[i] = vi;
+            const float pi = p[i];
+            p[i] = pi - lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * pi);
+        }
+    }
+}
+
+inline int done()
+{
+    ++g_b200_launches;
+    return (int)cudaGetLastError();
+}
+
+template <typename K>
+int opt_in_smem(K kern, size_t bytes)
+{
+    if (bytes <= 48 * 1024) return 0;
+    if (bytes > 200 * 1024) return B200_E_TOOLARGE;
+    return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+}  // namespace
+
+// ================================== C ABI =========================================================
+
+extern "C" int b200_round_f16(float *w, size_t n, void *stream)
+{
+    if (!w || n == 0) return B200_E_BADARG;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    round_f16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w, n);
+    return done();
+}
+
+extern "C" int b200_transpose_f32(const float *src, int rows, int cols, float *dst, void *stream)
+{
+    if (!src || !dst || rows <= 0 || cols <= 0 || (rows + 31) / 32 > 65535) return B200_E_BADARG;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+    transpose_f32_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, rows, cols, dst);
+    return done();
+}
+
+extern "C" int b200_embed_rows(const float *emb, const uint32_t *tokens, int rows, int dim, int vocab, float scale,
+                               float *x, void *stream)
+{
+    if (!emb || !tokens || !x || rows <= 0 || dim <= 0 || vocab <= 0) return B200_E_BADARG;
+    embed_rows_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(emb, tokens, dim, vocab, scale, x);
+    return done();
+}
+
+extern "C" int b200_rms_norm_rows(const float *x, const float *gamma, float *out, int rows, int dim, float eps,
+                                  void *stream)
+{
+    if (!x || !gamma || !out || rows <= 0 || dim <= 0) return B200_E_BADARG;
+    rms_norm_rows_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, gamma, out, rows, dim, eps);
+    return done();
+}
+
+extern "C" int b200_rms_norm_bwd_rows(const float *x, const float *dy, const float *gamma, float *dx, int rows, int dim,
+                                      float eps, int accumulate, float clamp, void *stream)
+{
+    if (!x || !dy || !gamma || !dx || rows <= 0 || dim <= 0) return B200_E_BADARG;
+    rms_norm_bwd_rows_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, dy, gamma, dx, rows, dim, eps,
+                                                                              accumulate, clamp);
+    return done();
+}
+
+extern "C" int b200_qk_norm_rope(const float *qkv, long long ld, const float *q_gamma, const float *k_gamma,
+                                 const float *inv_freq, int rows, int seq_len, int n_q, int n_kv, int hd, float eps,
+                                 float *q_out, float *k_out, void *stream)
+{
+    if (!qkv || !q_gamma || !k_gamma || !inv_freq || !q_out || !k_out || rows <= 0 || seq_len <= 0) return B200_E_BADARG;
+    const long long units = (long long)rows * (n_q + n_kv);
+    const unsigned grid = (unsigned)((units + 7) / 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (hd) {
+    case 64: qk_norm_rope_kernel<64><<<grid, 256, 0, st>>>(qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps, q_out, k_out); break;
+    case 128: qk_norm_rope_kernel<128><<<grid, 256, 0, st>>>(qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps, q_out, k_out); break;
+    case 256: qk_norm_rope_kernel<256><<<grid, 256, 0, st>>>(qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps, q_out, k_out); break;
+    default: return B200_E_BADARG;
+    }
+    return done();
+}
+
+extern "C" int b200_qk_norm_rope_bwd(float *dqkv, const float *qkv, long long ld, const float *q_gamma,
+                                     const float *k_gamma, const float *inv_freq, int rows, int seq_len, int n_q,
+                                     int n_kv, int hd, float eps, void *stream)
+{
+    if (!dqkv || !qkv || !q_gamma || !k_gamma || !inv_freq || rows <= 0 || seq_len <= 0) return B200_E_BADARG;
+    const long long units = (long long)rows * (n_q + n_kv);
+    const unsigned grid = (unsigned)((units + 7) / 8);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (hd) {
+    case 64: qk_norm_rope_bwd_kernel<64><<<grid, 256, 0, st>>>(dqkv, qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
+    case 128: qk_norm_rope_bwd_kernel<128><<<grid, 256, 0, st>>>(dqkv, qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
+    case 256: qk_norm_rope_bwd_kernel<256><<<grid, 256, 0, st>>>(dqkv, qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
+    default: return B200_E_BADARG;
+    }
+    return done();
+}
+
+static bool attn_shape_ok(int n_seq, int seq_len, int n_q, int n_kv, int hd)
+{
+    return n_seq > 0 && seq_len > 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0 && (hd == 64 || hd == 128 || hd == 256);
+}
+
+template <int HD>
+static int attn_fwd_launch(const float *q, const float *k, const float *v, long long v_ld, int n_seq, int N, int n_q,
+                           int n_kv, float scale, float *probs, float *out, cudaStream_t st)
+{
+    const size_t smem = (size_t)ATT_WARPS * (HD + N) * sizeof(float);
+    int rc = opt_in_smem(attn_train_fwd_kernel<HD>, smem);
+    if (rc) return rc;
+    const long long units = (long long)n_seq * n_q * N;
+    attn_train_fwd_kernel<HD><<<(unsigned)((units + ATT_WARPS - 1) / ATT_WARPS), ATT_WARPS * 32, smem, st>>>(
+        q, k, v, v_ld, n_seq, N, n_q, n_kv, scale, probs, out);
+    return done();
+}
+
+extern "C" int b200_attn_train_fwd(const float *q, const float *k, const float *v, long long v_ld, int n_seq,
+                                   int seq_len, int n_q, int n_kv, int hd, float scale, float *probs, float *out,
+                                   void *stream)
+{
+    if (!q || !k || !v || !probs || !out || !attn_shape_ok(n_seq, seq_len, n_q, n_kv, hd)) return B200_E_BADARG;
+    if ((v_ld & 3) || ((uintptr_t)v & 15) || ((uintptr_t)k & 15)) return B200_E_BADARG;     // 16-byte row loads
+    cudaStream_t st = (cudaStream_t)stream;
+    if (hd == 64) return attn_fwd_launch<64>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, st);
+    if (hd == 128) return attn_fwd_launch<128>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, st);
+    return attn_fwd_launch<256>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, st);
+}
+
+template <int HD>
+static int attn_bwd_launch(const float *d_out, const float *probs, const float *q, const float *k, const float *v,
+                           long long v_ld, int n_seq, int N, int n_q, int n_kv, float scale, float *d_score,
+                           float *dqkv, long long ld, cudaStream_t st)
+{
+    const size_t smem = (size_t)ATT_WARPS * (HD + N) * sizeof(float);
+    int rc = opt_in_smem(attn_bwd_dq_kernel<HD>, smem);
+    if (rc) return rc;
+    const long long uq = (long long)n_seq * n_q * N, uk = (long long)n_seq * n_kv * N;
+    attn_bwd_dq_kernel<HD><<<(unsigned)((uq + ATT_WARPS - 1) / ATT_WARPS), ATT_WARPS * 32, smem, st>>>(
+        d_out, probs, k, v, v_ld, n_seq, N, n_q, n_kv, scale, d_score, dqkv, ld);
+    rc = done();
+    if (rc) return rc;
+    attn_bwd_dkv_kernel<HD><<<(unsigned)((uk + ATT_WARPS - 1) / ATT_WARPS), ATT_WARPS * 32, 0, st>>>(
+        d_score, probs, q, d_out, n_seq, N, n_q, n_kv, dqkv, ld);
+    return done();
+}
+
+extern "C" int b200_attn_train_bwd(const float *d_out, const float *probs, const float *q, const float *k,
+                                   const float *v, long long v_ld, int n_seq, int seq_len, int n_q, int n_kv, int hd,
+                                   float scale, float *d_score, float *dqkv, long long ld, void *stream)
+{
+    if (!d_out || !probs || !q || !k || !v || !d_score || !dqkv || !attn_shape_ok(n_seq, seq_len, n_q, n_kv, hd))
+        return B200_E_BADARG;
+    if ((v_ld & 3) || ((uintptr_t)v & 15)) return B200_E_BADARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (hd == 64) return attn_bwd_launch<64>(d_out, probs, q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, d_score, dqkv, ld, st);
+    if (hd == 128) return attn_bwd_launch<128>(d_out, probs, q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, d_score, dqkv, ld, st);
+    return attn_bwd_launch<256>(d_out, probs, q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, d_score, dqkv, ld, st);
+}
+
+extern "C" int b200_silu_mul_rows(const float *gu, int rows, int inter, float *act, void *stream)
+{
+    if (!gu || !act || rows <= 0 || inter <= 0) return B200_E_BADARG;
+    const size_t total = (size_t)rows * inter;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    silu_mul_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gu, inter, act, total);
+    return done();
+}
+
+extern "C" int b200_silu_mul_bwd_rows(const float *d_act, const float *gu, int rows, int inter, float *d_gu,
+                                      void *stream)
+{
+    if (!d_act || !gu || !d_gu || rows <= 0 || inter <= 0) return B200_E_BADARG;
+    const size_t total = (size_t)rows * inter;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    silu_mul_bwd_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_act, gu, inter, d_gu, total);
+    return done();
+}
+
+extern "C" int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, const float *B, int rank,
+                             float sc, int rows, void *stream)
+{
+    if (!y || !mid || !B || rank <= 0 || rank > 64 || rows <= 0 || n_cols <= 0 || rows > 65535) return B200_E_BADARG;
+    dim3 grid((n_cols + 255) / 256, rows);
+    lora_add_kernel<64><<<grid, 256, 0, (cudaStream_t)stream>>>(y, ld, col0, n_cols, mid, B, rank, sc, rows);
+    return done();
+}
+
+extern "C" int b200_softmax_ce_rows(const float *logits, const uint32_t *targets, int rows, int vocab,
+                                    float grad_scale, float *losses, float *dlogits, void *stream)
+{
+    if (!logits || !targets || !losses || !dlogits || rows <= 0 || vocab <= 0) return B200_E_BADARG;
+    softmax_ce_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, targets, vocab, grad_scale, losses, dlogits);
+    return done();
+}
+
+extern "C" int b200_sumsq_partials(const float *g, size_t n, double *partials, int n_partials, void *stream)
+{
+    if (!g || !partials || n == 0 || n_partials <= 0 || n_partials > 4096) return B200_E_BADARG;
+    sumsq_partials_kernel<<<n_partials, 256, 0, (cudaStream_t)stream>>>(g, n, partials);
+    return done();
+}
+
+extern "C" int b200_clip_adamw(float *p, float *g, float *m, float *v, size_t n, const double *partials,
+                               int n_partials, float max_norm, float lr, float beta1, float beta2, float eps, float wd,
+                               float bc1, float bc2, int apply_update, float *norm_out, void *stream)
+{
+    if (!g || !partials || n == 0 || n_partials <= 0) return B200_E_BADARG;
+    if (apply_update && (!p || !m || !v)) return B200_E_BADARG;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    clip_adamw_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, n, partials, n_partials, max_norm, lr, beta1,
+                                                             beta2, eps, wd, bc1, bc2, apply_update, norm_out);
+    return done();
+}

@@ -19,6 +19,7 @@ struct MetalBuf {
     int rows, cols;          /* packed weights only */
     long long row_stride;
     void *host_mirror;       /* canonical host copy of a packed weight, made on demand */
+    int borrowed;            /* dev belongs to someone else: metal_buf_free leaves it alone */
 };
 
 #define LLMB200_STAGE_BYTES ((size_t)64 << 20)
@@ -66,5 +67,10 @@ int llmb200_upload_packed(int wtype, const float *src, long long ld, int rows, i
 
 /* Plain fp32 host -> new device allocation (returns NULL on failure). */
 float *llmb200_upload_f32(const float *src, size_t n);
+/* Plain fp32 host -> existing device memory through the staging buffers. */
+int llmb200_upload_f32_into(float *d_dst, const float *src, size_t n);
+/* A MetalBuf handle over device memory the caller keeps owning. metal_buf_ptr
+ * on it returns a host copy refreshed by every call. */
+MetalBuf *llmb200_buf_wrap(void *dev, size_t size);
 
 #endif

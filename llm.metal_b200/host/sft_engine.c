@@ -1,0 +1,795 @@
+/*
+ * LoRA-SFT engine of libllmb200 (host side, C).
+ *
+ * Stands in for src/nn/fast_sft.c (LoRA branch, Qwen3 block order): state
+ * creation :171-278, forward_to_logits :616-752, sft_apply_ce_loss :754-760,
+ * sft_backward_ex :766-982, clip_grad_norm / adamw_update / lora_update
+ * :1045-1107, sft_train_step :1113-1157, accessors :1206-1285.
+ *
+ * Differences in structure, not in arithmetic:
+ *  - S sequences of N tokens are one [S*N, .] activation matrix, so every
+ *    frozen projection is ONE matrix product per layer and pass (the reference
+ *    runs one sequence per step). Q/K/V and gate/up are fused row-wise.
+ *  - No transposed, repeated or copied activations: kernels index heads and
+ *    KV groups in place; residual adds ride on the product's epilogue; saved
+ *    activations are the buffers the forward wrote, not copies.
+ *  - The frozen weights are fp32 copies of their binary16 values (every product
+ *    equals the reference's float(half) * float); with tensor cores on, a
+ *    transposed copy serves the backward product so that both passes read
+ *    operands contiguous along the contraction.
+ *  - Clip + AdamW run on the device over one flat parameter vector.
+ */
+#include "internal.h"
+#include "../../include/llmb200_sft.h"
+#include "../../include/llmb200_train_kernels.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+
+typedef struct {
+    float *w;        /* [rows, cols] */
+    float *wt;       /* [cols, rows] or NULL */
+    int rows, cols;
+} SftMat;
+
+typedef struct {
+    SftMat qkv, o, gu, down;
+    float *g_in, *g_post, *g_q, *g_k;   /* norm gammas */
+    float *inv_freq;                    /* [hd/2] */
+    /* saved activations */
+    float *x_in, *ln1, *qkv_out, *q_f, *k_f, *probs, *x_mid, *ln2, *gu_out, *mid_q, *mid_v;
+    size_t lora_off;                    /* offset of this layer in the flat LoRA vectors */
+    MetalBuf *lora_buf[4];              /* handles made on demand by sft_get_lora_weight_buf */
+    int loaded;
+} SftLayer;
+
+struct SFTState {
+    int D, Hq, Hkv, hd, IS, V, NL, N, S, M, QKV;
+    int Hq_hd, Hkv_hd;
+    float eps, lora_scaling, emb_scale;
+    int lora_rank, step_count, model_type;
+    int use_tc, err, finished;
+    float *rope_thetas;
+
+    SftLayer *layers;
+    SftMat lm_head;
+    float *final_g, *d_emb;
+    float *token_emb_host;
+
+    /* flat LoRA vectors (device) + pinned mirror of the gradients */
+    size_t n_lora, per_layer, sizes[4], sub_off[4];
+    float *lora_p, *lora_g, *lora_m, *lora_v;
+    float *h_grad;
+
+    /* scratch */
+    float *x_final, *ln_final, *att, *act, *logits, *dlogits, *losses;
+    float *dx, *d_ln, *d_act, *d_gu, *d_att, *dqkv, *d_score, *tmp_q, *tmp_v;
+    uint32_t *tokens, *targets;
+    double *partials;
+    float *d_norm;
+    float *x_shared;            /* managed [M, D]: sft_get_x_cpu */
+    float *losses_shared;       /* managed [M]:    sft_get_losses_cpu */
+    uint32_t *h_tok;            /* pinned [2*M] */
+    float *h_loss;              /* pinned [M + 1] */
+    MetalBuf *mb_logits, *mb_dlogits;
+
+    cudaEvent_t ev[4];
+    float last_step_ms, last_update_ms, last_norm;
+};
+
+#define N_PARTIALS 1024
+
+#define S_TRY(s, call)                                                                     \
+    do {                                                                                   \
+        int e__ = (call);                                                                  \
+        if (e__ != 0 && !(s)->err) {                                                       \
+            (s)->err = e__;                                                                \
+            fprintf(stderr, "[llmb200] sft: %s failed: code %d%s%s (%s:%d)\n", #call, e__, \
+                    e__ > 0 ? " " : "", e__ > 0 ? cudaGetErrorString((cudaError_t)e__) : "", \
+                    __FILE__, __LINE__);                                                   \
+        }                                                                                  \
+    } while (0)
+
+static float *dalloc(SFTState *s, size_t n_floats)
+{
+    float *p = NULL;
+    cudaError_t e = cudaMalloc((void **)&p, (n_floats ? n_floats : 1) * sizeof(float));
+    if (e != cudaSuccess) {
+        fprintf(stderr, "[llmb200] sft: allocating %zu floats failed: %s\n", n_floats, cudaGetErrorString(e));
+        if (!s->err) s->err = (int)e;
+        return NULL;
+    }
+    return p;
+}
+
+/* ---------------------------------------------------------------- weights */
+
+/* rows of `src` ([rows, cols] fp32, host) into dst rows row0.. of a [*, cols] device matrix */
+static int mat_put(SFTState *s, SftMat *m, int row0, const float *src, int rows)
+{
+    if (!src) return B200_E_BADARG;
+    int rc = llmb200_upload_f32_into(m->w + (size_t)row0 * m->cols, src, (size_t)rows * m->cols);
+    if (rc) return rc;
+    return b200_round_f16(m->w + (size_t)row0 * m->cols, (size_t)rows * m->cols, g_rt.stream);
+}
+
+static int mat_alloc(SFTState *s, SftMat *m, int rows, int cols)
+{
+    m->rows = rows;
+    m->cols = cols;
+    m->w = dalloc(s, (size_t)rows * cols);
+    m->wt = s->use_tc ? dalloc(s, (size_t)rows * cols) : NULL;
+    return (m->w && (!s->use_tc || m->wt)) ? 0 : -1;
+}
+
+static int mat_finish(SFTState *s, SftMat *m)
+{
+    if (!m->wt) return 0;
+    return b200_transpose_f32(m->w, m->rows, m->cols, m->wt, g_rt.stream);
+}
+
+static void mat_free(SftMat *m)
+{
+    cudaFree(m->w);
+    cudaFree(m->wt);
+    m->w = m->wt = NULL;
+}
+
+/* C[M, W.rows] = A[M, W.cols] * W^T (+ R): the reference's f16_matmul. */
+static void gemm_fwd(SFTState *s, const float *A, const SftMat *W, float *C, const float *R)
+{
+    b200_gemm_args g = {0};
+    g.A = A; g.a_row = W->cols; g.a_col = 1;
+    g.B = W->w; g.b_row = 1; g.b_col = W->cols;
+    g.C = C; g.ldc = W->rows;
+    g.R = R; g.ldr = W->rows;
+    g.M = s->M; g.N = W->rows; g.K = W->cols;
+    g.alpha = 1.0f;
+    if (s->use_tc) {
+        int rc = b200_gemm_tf32(&g, g_rt.stream);
+        if (rc == 0) return;
+        if (rc != B200_E_UNSUPPORTED) { S_TRY(s, rc); return; }
+    }
+    S_TRY(s, b200_gemm_f32(&g, g_rt.stream));
+}
+
+/* C[M, W.cols] = A[M, W.rows] * W: the reference's f16_matmul_nt. */
+static void gemm_bwd(SFTState *s, const float *A, const SftMat *W, float *C)
+{
+    b200_gemm_args g = {0};
+    g.A = A; g.a_row = W->rows; g.a_col = 1;
+    g.C = C; g.ldc = W->cols;
+    g.M = s->M; g.N = W->cols; g.K = W->rows;
+    g.alpha = 1.0f;
+    if (s->use_tc && W->wt) {
+        g.B = W->wt; g.b_row = 1; g.b_col = W->rows;
+        int rc = b200_gemm_tf32(&g, g_rt.stream);
+        if (rc == 0) return;
+        if (rc != B200_E_UNSUPPORTED) { S_TRY(s, rc); return; }
+    }
+    g.B = W->w; g.b_row = W->cols; g.b_col = 1;
+    S_TRY(s, b200_gemm_f32(&g, g_rt.stream));
+}
+
+/* generic small product on the CUDA cores */
+static void gemm_small(SFTState *s, const float *A, long long a_row, long long a_col, const float *B, long long b_row,
+                       long long b_col, float *C, long long ldc, const float *R, int M, int N, int K, float alpha)
+{
+    b200_gemm_args g = {0};
+    g.A = A; g.a_row = a_row; g.a_col = a_col;
+    g.B = B; g.b_row = b_row; g.b_col = b_col;
+    g.C = C; g.ldc = ldc; g.R = R; g.ldr = ldc;
+    g.M = M; g.N = N; g.K = K; g.alpha = alpha;
+    S_TRY(s, b200_gemm_f32(&g, g_rt.stream));
+}
+
+/* ---------------------------------------------------------------- create */
+
+SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, int lora_rank, float lora_alpha)
+{
+    if (!cfg || seq_len <= 0 || n_seq <= 0 || lora_rank <= 0 || lora_rank > 64) {
+        fprintf(stderr, "[FastSFT] bad arguments (seq_len %d, sequences %d, rank %d; rank must be 1..64)\n", seq_len,
+                n_seq, lora_rank);
+        return NULL;
+    }
+    if (cfg->model_type != MODEL_QWEN3) {
+        fprintf(stderr, "[FastSFT] only the Qwen3 block order is implemented\n");
+        return NULL;
+    }
+    if (cfg->n_kv_heads <= 0 || cfg->n_q_heads % cfg->n_kv_heads ||
+        (cfg->head_dim != 64 && cfg->head_dim != 128 && cfg->head_dim != 256)) {
+        fprintf(stderr, "[FastSFT] unsupported head layout (%d q, %d kv, head_dim %d)\n", cfg->n_q_heads,
+                cfg->n_kv_heads, cfg->head_dim);
+        return NULL;
+    }
+    if (fast_metal_init() != 0) {
+        fprintf(stderr, "[FastSFT] device init failed\n");
+        return NULL;
+    }
+    SFTState *s = calloc(1, sizeof(SFTState));
+    if (!s) { fast_metal_shutdown(); return NULL; }
+    s->model_type = MODEL_QWEN3;
+    s->D = cfg->d_model; s->Hq = cfg->n_q_heads; s->Hkv = cfg->n_kv_heads; s->hd = cfg->head_dim;
+    s->IS = cfg->intermediate_size; s->V = cfg->vocab_size; s->NL = cfg->n_layers;
+    s->N = seq_len; s->S = n_seq; s->M = seq_len * n_seq;
+    s->Hq_hd = s->Hq * s->hd; s->Hkv_hd = s->Hkv * s->hd; s->QKV = s->Hq_hd + 2 * s->Hkv_hd;
+    s->emb_scale = 1.0f;
+    s->eps = 1e-6f;
+    s->lora_rank = lora_rank;
+    s->lora_scaling = lora_alpha / (float)lora_rank;
+    const char *tc = getenv("LLMB200_SFT_TC");
+    s->use_tc = !(tc && tc[0] == '0');
+    s->rope_thetas = calloc(s->NL, sizeof(float));
+    s->layers = calloc(s->NL, sizeof(SftLayer));
+
+    const int R = lora_rank, M = s->M;
+    s->sizes[0] = (size_t)R * s->D; s->sizes[1] = (size_t)s->Hq_hd * R;
+    s->sizes[2] = (size_t)R * s->D; s->sizes[3] = (size_t)s->Hkv_hd * R;
+    s->sub_off[0] = 0;
+    for (int i = 1; i < 4; ++i) s->sub_off[i] = s->sub_off[i - 1] + s->sizes[i - 1];
+    s->per_layer = s->sub_off[3] + s->sizes[3];
+    s->n_lora = s->per_layer * s->NL;
+    s->lora_p = dalloc(s, s->n_lora); s->lora_g = dalloc(s, s->n_lora);
+    s->lora_m = dalloc(s, s->n_lora); s->lora_v = dalloc(s, s->n_lora);
+    if (!s->err) {
+        cudaMemsetAsync(s->lora_p, 0, s->n_lora * 4, g_rt.stream);
+        cudaMemsetAsync(s->lora_g, 0, s->n_lora * 4, g_rt.stream);
+        cudaMemsetAsync(s->lora_m, 0, s->n_lora * 4, g_rt.stream);
+        cudaMemsetAsync(s->lora_v, 0, s->n_lora * 4, g_rt.stream);
+    }
+    if (cudaMallocHost((void **)&s->h_grad, s->n_lora * 4) != cudaSuccess) s->err = -10;
+
+    for (int L = 0; L < s->NL && !s->err; ++L) {
+        SftLayer *l = &s->layers[L];
+        l->lora_off = s->per_layer * L;
+        mat_alloc(s, &l->qkv, s->QKV, s->D);
+        mat_alloc(s, &l->o, s->D, s->Hq_hd);
+        mat_alloc(s, &l->gu, 2 * s->IS, s->D);
+        mat_alloc(s, &l->down, s->D, s->IS);
+        l->g_in = dalloc(s, s->D); l->g_post = dalloc(s, s->D);
+        l->g_q = dalloc(s, s->hd); l->g_k = dalloc(s, s->hd);
+        l->inv_freq = dalloc(s, s->hd / 2);
+        l->x_in = dalloc(s, (size_t)M * s->D); l->ln1 = dalloc(s, (size_t)M * s->D);
+        l->qkv_out = dalloc(s, (size_t)M * s->QKV);
+        l->q_f = dalloc(s, (size_t)M * s->Hq_hd); l->k_f = dalloc(s, (size_t)M * s->Hkv_hd);
+        l->probs = dalloc(s, (size_t)s->S * s->Hq * s->N * s->N);
+        l->x_mid = dalloc(s, (size_t)M * s->D); l->ln2 = dalloc(s, (size_t)M * s->D);
+        l->gu_out = dalloc(s, (size_t)M * 2 * s->IS);
+        l->mid_q = dalloc(s, (size_t)M * R); l->mid_v = dalloc(s, (size_t)M * R);
+    }
+    mat_alloc(s, &s->lm_head, s->V, s->D);
+    s->final_g = dalloc(s, s->D);
+    s->d_emb = dalloc(s, (size_t)s->V * s->D);
+
+    s->x_final = dalloc(s, (size_t)M * s->D); s->ln_final = dalloc(s, (size_t)M * s->D);
+    s->att = dalloc(s, (size_t)M * s->Hq_hd); s->act = dalloc(s, (size_t)M * s->IS);
+    s->logits = dalloc(s, (size_t)M * s->V); s->dlogits = dalloc(s, (size_t)M * s->V);
+    s->losses = dalloc(s, M);
+    s->dx = dalloc(s, (size_t)M * s->D); s->d_ln = dalloc(s, (size_t)M * s->D);
+    s->d_act = dalloc(s, (size_t)M * s->IS); s->d_gu = dalloc(s, (size_t)M * 2 * s->IS);
+    s->d_att = dalloc(s, (size_t)M * s->Hq_hd); s->dqkv = dalloc(s, (size_t)M * s->QKV);
+    s->d_score = dalloc(s, (size_t)s->S * s->Hq * s->N * s->N);
+    s->tmp_q = dalloc(s, (size_t)M * R); s->tmp_v = dalloc(s, (size_t)M * R);
+    s->tokens = (uint32_t *)dalloc(s, M); s->targets = (uint32_t *)dalloc(s, M);
+    s->partials = (double *)dalloc(s, 2 * N_PARTIALS);
+    s->d_norm = dalloc(s, 1);
+    if (!s->err) {
+        if (cudaMallocManaged((void **)&s->x_shared, (size_t)M * s->D * 4, cudaMemAttachGlobal) != cudaSuccess ||
+            cudaMallocManaged((void **)&s->losses_shared, (size_t)M * 4, cudaMemAttachGlobal) != cudaSuccess ||
+            cudaMallocHost((void **)&s->h_tok, (size_t)2 * M * 4) != cudaSuccess ||
+            cudaMallocHost((void **)&s->h_loss, (size_t)(M + 1) * 4) != cudaSuccess)
+            s->err = -11;
+    }
+    if (!s->err) {
+        memset(s->x_shared, 0, (size_t)M * s->D * 4);
+        memset(s->losses_shared, 0, (size_t)M * 4);
+        s->mb_logits = llmb200_buf_wrap(s->logits, (size_t)M * s->V * 4);
+        s->mb_dlogits = llmb200_buf_wrap(s->dlogits, (size_t)M * s->V * 4);
+        for (int i = 0; i < 4; ++i)
+            if (cudaEventCreate(&s->ev[i]) != cudaSuccess) s->err = -12;
+    }
+    if (s->err) {
+        fprintf(stderr, "[FastSFT] state allocation failed\n");
+        sft_state_free(s);
+        return NULL;
+    }
+    return s;
+}
+
+static int upload_small(float *d, const float *src, size_t n)
+{
+    return src ? llmb200_upload_f32_into(d, src, n) : B200_E_BADARG;
+}
+
+int llmb200_sft_load_layer(SFTState *s, int L, const LayerWeightRef *r, float rope_theta, const float *const lora[4])
+{
+    if (!s || !r || L < 0 || L >= s->NL) return B200_E_BADARG;
+    SftLayer *l = &s->layers[L];
+    if (r->q_proj.rows != s->Hq_hd || r->q_proj.cols != s->D || r->k_proj.rows != s->Hkv_hd ||
+        r->v_proj.rows != s->Hkv_hd || r->o_proj.rows != s->D || r->o_proj.cols != s->Hq_hd ||
+        r->gate_proj.rows != s->IS || r->up_proj.rows != s->IS || r->down_proj.rows != s->D ||
+        r->down_proj.cols != s->IS) {
+        fprintf(stderr, "[FastSFT] layer %d: matrix shapes do not match the configuration\n", L);
+        return B200_E_BADARG;
+    }
+    int rc = 0;
+    if (!rc) rc = mat_put(s, &l->qkv, 0, r->q_proj.data, s->Hq_hd);
+    if (!rc) rc = mat_put(s, &l->qkv, s->Hq_hd, r->k_proj.data, s->Hkv_hd);
+    if (!rc) rc = mat_put(s, &l->qkv, s->Hq_hd + s->Hkv_hd, r->v_proj.data, s->Hkv_hd);
+    if (!rc) rc = mat_put(s, &l->o, 0, r->o_proj.data, s->D);
+    if (!rc) rc = mat_put(s, &l->gu, 0, r->gate_proj.data, s->IS);
+    if (!rc) rc = mat_put(s, &l->gu, s->IS, r->up_proj.data, s->IS);
+    if (!rc) rc = mat_put(s, &l->down, 0, r->down_proj.data, s->D);
+    if (!rc) rc = mat_finish(s, &l->qkv);
+    if (!rc) rc = mat_finish(s, &l->o);
+    if (!rc) rc = mat_finish(s, &l->gu);
+    if (!rc) rc = mat_finish(s, &l->down);
+    if (!rc) rc = upload_small(l->g_in, r->input_norm_g, s->D);
+    if (!rc) rc = upload_small(l->g_post, r->post_attn_norm_g, s->D);
+    if (!rc) rc = upload_small(l->g_q, r->q_norm_g, s->hd);
+    if (!rc) rc = upload_small(l->g_k, r->k_norm_g, s->hd);
+    if (rc) return rc;
+
+    /* 1 / pow(theta, 2d/hd) as the shader computes it per element (q8_kernels.metal:531) */
+    const int half = s->hd / 2;
+    float *f = malloc(half * sizeof(float));
+    for (int d = 0; d < half; ++d) f[d] = 1.0f / powf(rope_theta, (float)(2 * d) / (float)s->hd);
+    rc = llmb200_upload_f32_into(l->inv_freq, f, half);
+    free(f);
+    s->rope_thetas[L] = rope_theta;
+    if (rc) return rc;
+
+    /* LoRA init (src/nn/fast_sft.c:96-122): supplied matrices, else A uniform(+-1/sqrt(D)) from rand(), B = 0 */
+    for (int sub = 0; sub < 4 && !rc; ++sub) {
+        float *dst = s->lora_p + l->lora_off + s->sub_off[sub];
+        const size_t n = s->sizes[sub];
+        if (lora && lora[sub]) {
+            rc = llmb200_upload_f32_into(dst, lora[sub], n);
+        } else if (sub == 0 || sub == 2) {
+            float *tmp = malloc(n * sizeof(float));
+            const float std_a = 1.0f / sqrtf((float)s->D);
+            for (size_t j = 0; j < n; ++j) tmp[j] = ((float)rand() / (float)RAND_MAX - 0.5f) * 2.0f * std_a;
+            rc = llmb200_upload_f32_into(dst, tmp, n);
+            free(tmp);
+        } else {
+            rc = (int)cudaMemsetAsync(dst, 0, n * 4, g_rt.stream);
+        }
+    }
+    l->loaded = 1;
+    return rc;
+}
+
+int llmb200_sft_finish(SFTState *s, const float *lm_head, const float *final_norm_gamma, const float *token_emb,
+                       int keep_host_emb)
+{
+    if (!s || !lm_head || !final_norm_gamma || !token_emb) return B200_E_BADARG;
+    for (int L = 0; L < s->NL; ++L)
+        if (!s->layers[L].loaded) {
+            fprintf(stderr, "[FastSFT] layer %d was never loaded\n", L);
+            return B200_E_STATE;
+        }
+    int rc = mat_put(s, &s->lm_head, 0, lm_head, s->V);
+    if (!rc) rc = mat_finish(s, &s->lm_head);
+    if (!rc) rc = llmb200_upload_f32_into(s->final_g, final_norm_gamma, s->D);
+    if (!rc) rc = llmb200_upload_f32_into(s->d_emb, token_emb, (size_t)s->V * s->D);
+    if (!rc && keep_host_emb) {
+        s->token_emb_host = malloc((size_t)s->V * s->D * sizeof(float));
+        if (s->token_emb_host) memcpy(s->token_emb_host, token_emb, (size_t)s->V * s->D * sizeof(float));
+    }
+    if (!rc) rc = (int)cudaStreamSynchronize(g_rt.stream);
+    s->finished = rc == 0;
+    return rc;
+}
+
+SFTState *sft_state_create(llmb200_qwen3_model *m, int seq_len, int lora_rank, float lora_alpha)
+{
+    if (!m) return NULL;
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    printf("[FastSFT] Converting weights to F16...\n");
+    llmb200_config cfg = { MODEL_QWEN3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
+                           m->vocab_size, m->n_layers, seq_len, 1 };
+    SFTState *s = llmb200_sft_begin(&cfg, seq_len, 1, lora_rank, lora_alpha);
+    if (!s) return NULL;
+    const int Hq_hd = s->Hq_hd, Hkv_hd = s->Hkv_hd;
+    for (int i = 0; i < s->NL; ++i) {
+        llmb200_qwen3_block *b = m->blocks[i];
+        LayerWeightRef r;
+        memset(&r, 0, sizeof(r));
+        r.q_proj = (WeightRef){ b->attn->q_proj->weight->data, Hq_hd, s->D };
+        r.k_proj = (WeightRef){ b->attn->k_proj->weight->data, Hkv_hd, s->D };
+        r.v_proj = (WeightRef){ b->attn->v_proj->weight->data, Hkv_hd, s->D };
+        r.o_proj = (WeightRef){ b->attn->o_proj->weight->data, s->D, Hq_hd };
+        r.gate_proj = (WeightRef){ b->gate_proj->weight->data, s->IS, s->D };
+        r.up_proj = (WeightRef){ b->up_proj->weight->data, s->IS, s->D };
+        r.down_proj = (WeightRef){ b->down_proj->weight->data, s->D, s->IS };
+        r.input_norm_g = b->input_norm->gamma->data;
+        r.post_attn_norm_g = b->post_attn_norm->gamma->data;
+        r.q_norm_g = b->attn->q_norm->gamma->data;
+        r.k_norm_g = b->attn->k_norm->gamma->data;
+        r.d_model = s->D;
+        r.head_dim = s->hd;
+        const float *lora[4] = { NULL, NULL, NULL, NULL };
+        if (m->q_loras && m->q_loras[i]) { lora[0] = m->q_loras[i]->lora_A->data; lora[1] = m->q_loras[i]->lora_B->data; }
+        if (m->v_loras && m->v_loras[i]) { lora[2] = m->v_loras[i]->lora_A->data; lora[3] = m->v_loras[i]->lora_B->data; }
+        if (llmb200_sft_load_layer(s, i, &r, m->rope_theta, lora) != 0) { sft_state_free(s); return NULL; }
+    }
+    if (llmb200_sft_finish(s, m->lm_head->weight->data, m->final_norm->gamma->data, m->token_emb->weight->data, 1) != 0) {
+        sft_state_free(s);
+        return NULL;
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    const double ms = (t1.tv_sec - t0.tv_sec) * 1000.0 + (t1.tv_nsec - t0.tv_nsec) / 1e6;
+    printf("[FastSFT] Init: %.0f ms, seq=%d, lora_rank=%d\n", ms, seq_len, lora_rank);
+    return s;
+}
+
+void sft_state_free(SFTState *s)
+{
+    if (!s) return;
+    if (g_rt.refs > 0) cudaStreamSynchronize(g_rt.stream);
+    for (int L = 0; L < s->NL && s->layers; ++L) {
+        SftLayer *l = &s->layers[L];
+        mat_free(&l->qkv); mat_free(&l->o); mat_free(&l->gu); mat_free(&l->down);
+        float *bufs[] = { l->g_in, l->g_post, l->g_q, l->g_k, l->inv_freq, l->x_in, l->ln1, l->qkv_out, l->q_f, l->k_f,
+                          l->probs, l->x_mid, l->ln2, l->gu_out, l->mid_q, l->mid_v };
+        for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
+        for (int i = 0; i < 4; ++i) metal_buf_free(l->lora_buf[i]);
+    }
+    mat_free(&s->lm_head);
+    void *bufs[] = { s->final_g, s->d_emb, s->lora_p, s->lora_g, s->lora_m, s->lora_v, s->x_final, s->ln_final, s->att,
+                     s->act, s->logits, s->dlogits, s->losses, s->dx, s->d_ln, s->d_act, s->d_gu, s->d_att, s->dqkv,
+                     s->d_score, s->tmp_q, s->tmp_v, s->tokens, s->targets, s->partials, s->d_norm, s->x_shared,
+                     s->losses_shared };
+    for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
+    cudaFreeHost(s->h_grad); cudaFreeHost(s->h_tok); cudaFreeHost(s->h_loss);
+    metal_buf_free(s->mb_logits); metal_buf_free(s->mb_dlogits);
+    for (int i = 0; i < 4; ++i) if (s->ev[i]) cudaEventDestroy(s->ev[i]);
+    free(s->token_emb_host);
+    free(s->rope_thetas);
+    free(s->layers);
+    free(s);
+    fast_metal_shutdown();
+}
+
+/* ---------------------------------------------------------------- forward */
+
+static float *layer_out(SFTState *s, int L) { return L + 1 < s->NL ? s->layers[L + 1].x_in : s->x_final; }
+
+/* x of layer 0 must be in layers[0].x_in */
+static void forward_device(SFTState *s)
+{
+    cudaStream_t st = g_rt.stream;
+    const int M = s->M, R = s->lora_rank;
+    const float sc = s->lora_scaling, attn_scale = 1.0f / sqrtf((float)s->hd);
+    for (int L = 0; L < s->NL; ++L) {
+        SftLayer *l = &s->layers[L];
+        float *pA_q = s->lora_p + l->lora_off + s->sub_off[0], *pB_q = s->lora_p + l->lora_off + s->sub_off[1];
+        float *pA_v = s->lora_p + l->lora_off + s->sub_off[2], *pB_v = s->lora_p + l->lora_off + s->sub_off[3];
+        S_TRY(s, b200_rms_norm_rows(l->x_in, l->g_in, l->ln1, M, s->D, s->eps, st));
+        gemm_fwd(s, l->ln1, &l->qkv, l->qkv_out, NULL);
+        /* q += sc * (ln1 A_q^T) B_q^T, v likewise (:639-643, :652-656) */
+        gemm_small(s, l->ln1, s->D, 1, pA_q, 1, s->D, l->mid_q, R, NULL, M, R, s->D, 1.0f);
+        S_TRY(s, b200_lora_add(l->qkv_out, s->QKV, 0, s->Hq_hd, l->mid_q, pB_q, R, sc, M, st));
+        gemm_small(s, l->ln1, s->D, 1, pA_v, 1, s->D, l->mid_v, R, NULL, M, R, s->D, 1.0f);
+        S_TRY(s, b200_lora_add(l->qkv_out, s->QKV, s->Hq_hd + s->Hkv_hd, s->Hkv_hd, l->mid_v, pB_v, R, sc, M, st));
+        S_TRY(s, b200_qk_norm_rope(l->qkv_out, s->QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv, s->hd,
+                                   s->eps, l->q_f, l->k_f, st));
+        S_TRY(s, b200_attn_train_fwd(l->q_f, l->k_f, l->qkv_out + s->Hq_hd + s->Hkv_hd, s->QKV, s->S, s->N, s->Hq,
+                                     s->Hkv, s->hd, attn_scale, l->probs, s->att, st));
+        gemm_fwd(s, s->att, &l->o, l->x_mid, l->x_in);                       /* + residual (:686) */
+        S_TRY(s, b200_rms_norm_rows(l->x_mid, l->g_post, l->ln2, M, s->D, s->eps, st));
+        gemm_fwd(s, l->ln2, &l->gu, l->gu_out, NULL);
+        S_TRY(s, b200_silu_mul_rows(l->gu_out, M, s->IS, s->act, st));
+        gemm_fwd(s, s->act, &l->down, layer_out(s, L), l->x_mid);            /* + residual (:738) */
+    }
+    S_TRY(s, b200_rms_norm_rows(s->x_final, s->final_g, s->ln_final, M, s->D, s->eps, st));
+    gemm_fwd(s, s->ln_final, &s->lm_head, s->logits, NULL);
+}
+
+static void loss_device(SFTState *s)
+{
+    /* 1/N per sequence (:759), and the mean over the S sequences of a step */
+    const float gs = 1.0f / ((float)s->N * (float)s->S);
+    S_TRY(s, b200_softmax_ce_rows(s->logits, s->targets, s->M, s->V, gs, s->losses, s->dlogits, g_rt.stream));
+}
+
+/* ---------------------------------------------------------------- backward */
+
+static void backward_device(SFTState *s)
+{
+    cudaStream_t st = g_rt.stream;
+    const int M = s->M, R = s->lora_rank, QKV = s->QKV;
+    const float sc = s->lora_scaling, attn_scale = 1.0f / sqrtf((float)s->hd);
+    gemm_bwd(s, s->dlogits, &s->lm_head, s->d_ln);                                           /* :777 */
+    S_TRY(s, b200_rms_norm_bwd_rows(s->x_final, s->d_ln, s->final_g, s->dx, M, s->D, s->eps, 0, 0.f, st));
+    for (int L = s->NL - 1; L >= 0; --L) {
+        SftLayer *l = &s->layers[L];
+        float *pA_q = s->lora_p + l->lora_off + s->sub_off[0], *pB_q = s->lora_p + l->lora_off + s->sub_off[1];
+        float *pA_v = s->lora_p + l->lora_off + s->sub_off[2], *pB_v = s->lora_p + l->lora_off + s->sub_off[3];
+        float *gA_q = s->lora_g + l->lora_off + s->sub_off[0], *gB_q = s->lora_g + l->lora_off + s->sub_off[1];
+        float *gA_v = s->lora_g + l->lora_off + s->sub_off[2], *gB_v = s->lora_g + l->lora_off + s->sub_off[3];
+        /* FFN (:841-872) */
+        gemm_bwd(s, s->dx, &l->down, s->d_act);
+        S_TRY(s, b200_silu_mul_bwd_rows(s->d_act, l->gu_out, M, s->IS, s->d_gu, st));
+        gemm_bwd(s, s->d_gu, &l->gu, s->d_ln);
+        S_TRY(s, b200_rms_norm_bwd_rows(l->x_mid, s->d_ln, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, st));
+        /* attention (:889-918) */
+        gemm_bwd(s, s->dx, &l->o, s->d_att);
+        const float *v = l->qkv_out + s->Hq_hd + s->Hkv_hd;
+        S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, QKV, s->S, s->N, s->Hq, s->Hkv, s->hd,
+                                     attn_scale, s->d_score, s->dqkv, QKV, st));
+        S_TRY(s, b200_qk_norm_rope_bwd(s->dqkv, l->qkv_out, QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv,
+                                       s->hd, s->eps, st));
+        const float *dq = s->dqkv, *dv = s->dqkv + s->Hq_hd + s->Hkv_hd;
+        /* LoRA Q (:946-952): dB = sc dq^T mid, tmp = sc dq B, dA = tmp^T ln1 */
+        gemm_small(s, dq, 1, QKV, l->mid_q, R, 1, gB_q, R, NULL, s->Hq_hd, R, M, sc);
+        gemm_small(s, dq, QKV, 1, pB_q, R, 1, s->tmp_q, R, NULL, M, R, s->Hq_hd, sc);
+        gemm_small(s, s->tmp_q, 1, R, l->ln1, s->D, 1, gA_q, s->D, NULL, R, s->D, M, 1.0f);
+        /* LoRA V (:961-966) */
+        gemm_small(s, dv, 1, QKV, l->mid_v, R, 1, gB_v, R, NULL, s->Hkv_hd, R, M, sc);
+        gemm_small(s, dv, QKV, 1, pB_v, R, 1, s->tmp_v, R, NULL, M, R, s->Hkv_hd, sc);
+        gemm_small(s, s->tmp_v, 1, R, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
+        /* through the frozen q, k, v projections and the two LoRA down-projections (:953-970) */
+        gemm_bwd(s, s->dqkv, &l->qkv, s->d_ln);
+        gemm_small(s, s->tmp_q, R, 1, pA_q, s->D, 1, s->d_ln, s->D, s->d_ln, M, s->D, R, 1.0f);
+        gemm_small(s, s->tmp_v, R, 1, pA_v, s->D, 1, s->d_ln, s->D, s->d_ln, M, s->D, R, 1.0f);
+        /* input norm + residual + clamp (:974-979) */
+        S_TRY(s, b200_rms_norm_bwd_rows(l->x_in, s->d_ln, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, st));
+    }
+}
+
+/* ---------------------------------------------------------------- update */
+
+static void update_device(SFTState *s, float lr, int step)
+{
+    const float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, wd = 0.01f;
+    const float bc1 = 1.0f - powf(beta1, (float)step), bc2 = 1.0f - powf(beta2, (float)step);
+    cudaStream_t st = g_rt.stream;
+    cudaEventRecord(s->ev[2], st);
+    S_TRY(s, b200_sumsq_partials(s->lora_g, s->n_lora, s->partials, N_PARTIALS, st));
+    S_TRY(s, b200_clip_adamw(s->lora_p, s->lora_g, s->lora_m, s->lora_v, s->n_lora, s->partials, N_PARTIALS, 1.0f, lr,
+                             beta1, beta2, eps, wd, bc1, bc2, 1, s->d_norm, st));
+    cudaEventRecord(s->ev[3], st);
+    S_TRY(s, (int)cudaMemcpyAsync(&s->h_loss[s->M], s->d_norm, 4, cudaMemcpyDeviceToHost, st));
+    S_TRY(s, (int)cudaStreamSynchronize(st));
+    s->last_norm = s->h_loss[s->M];
+    cudaEventElapsedTime(&s->last_update_ms, s->ev[2], s->ev[3]);
+}
+
+static float mean_loss_host(SFTState *s)
+{
+    /* summed on the host in position order like the reference (:1142-1144) */
+    S_TRY(s, (int)cudaMemcpyAsync(s->h_loss, s->losses, (size_t)s->M * 4, cudaMemcpyDeviceToHost, g_rt.stream));
+    S_TRY(s, (int)cudaStreamSynchronize(g_rt.stream));
+    float total = 0.f;
+    for (int i = 0; i < s->M; ++i) total += s->h_loss[i];
+    return total / (float)s->M;
+}
+
+float llmb200_sft_forward_backward(SFTState *s, const uint32_t *inputs, const uint32_t *targets)
+{
+    if (!s || !s->finished || !inputs || !targets) return NAN;
+    cudaStream_t st = g_rt.stream;
+    memcpy(s->h_tok, inputs, (size_t)s->M * 4);
+    memcpy(s->h_tok + s->M, targets, (size_t)s->M * 4);
+    S_TRY(s, (int)cudaMemcpyAsync(s->tokens, s->h_tok, (size_t)s->M * 4, cudaMemcpyHostToDevice, st));
+    S_TRY(s, (int)cudaMemcpyAsync(s->targets, s->h_tok + s->M, (size_t)s->M * 4, cudaMemcpyHostToDevice, st));
+    cudaEventRecord(s->ev[0], st);
+    S_TRY(s, b200_embed_rows(s->d_emb, s->tokens, s->M, s->D, s->V, s->emb_scale, s->layers[0].x_in, st));
+    forward_device(s);
+    loss_device(s);
+    backward_device(s);
+    cudaEventRecord(s->ev[1], st);
+    const float loss = mean_loss_host(s);
+    cudaEventElapsedTime(&s->last_step_ms, s->ev[0], s->ev[1]);
+    return s->err ? NAN : loss;
+}
+
+void llmb200_sft_apply_update(SFTState *s, float lr)
+{
+    if (!s || !s->finished) return;
+    s->step_count++;
+    update_device(s, lr, s->step_count);
+}
+
+float llmb200_sft_train_batch(SFTState *s, const uint32_t *inputs, const uint32_t *targets, float lr)
+{
+    const float loss = llmb200_sft_forward_backward(s, inputs, targets);
+    llmb200_sft_apply_update(s, lr);
+    return loss;
+}
+
+float sft_train_step(SFTState *s, const uint32_t *input_tokens, const uint32_t *target_tokens, float lr)
+{
+    return llmb200_sft_train_batch(s, input_tokens, target_tokens, lr);
+}
+
+void forward_to_logits(SFTState *s)
+{
+    if (!s || !s->finished) return;
+    /* the caller wrote the embeddings into the shared x buffer */
+    S_TRY(s, (int)cudaMemcpyAsync(s->layers[0].x_in, s->x_shared, (size_t)s->M * s->D * 4, cudaMemcpyDefault,
+                                  g_rt.stream));
+    forward_device(s);
+}
+
+void sft_backward(SFTState *s)
+{
+    if (!s || !s->finished) return;
+    backward_device(s);
+}
+
+void sft_lora_update(SFTState *s, float lr)
+{
+    /* The reference clips here and once more inside lora_update (:1248-1251, :1094); the second
+     * clip sees a norm of 1 and changes nothing beyond rounding, so one clip is applied. */
+    if (!s || !s->finished) return;
+    update_device(s, lr, s->step_count);
+}
+
+/* ---------------------------------------------------------------- accessors */
+
+MetalBuf *sft_get_logits(SFTState *s) { return s ? s->mb_logits : NULL; }
+MetalBuf *sft_get_dlogits(SFTState *s) { return s ? s->mb_dlogits : NULL; }
+float *sft_get_x_cpu(SFTState *s) { if (!s) return NULL; metal_flush(); return s->x_shared; }
+float *sft_get_losses_cpu(SFTState *s)
+{
+    if (!s) return NULL;
+    cudaMemcpyAsync(s->losses_shared, s->losses, (size_t)s->M * 4, cudaMemcpyDefault, g_rt.stream);
+    metal_flush();
+    return s->losses_shared;
+}
+int sft_get_seq_len(SFTState *s) { return s->N; }
+int sft_get_vocab_size(SFTState *s) { return s->V; }
+int sft_get_d_model(SFTState *s) { return s->D; }
+int sft_get_lora_rank(SFTState *s) { return s->lora_rank; }
+int sft_get_n_layers(SFTState *s) { return s->NL; }
+float sft_get_emb_scale(SFTState *s) { return s->emb_scale; }
+const float *sft_get_token_emb(SFTState *s) { return s->token_emb_host; }
+int sft_get_step_count(SFTState *s) { return s->step_count; }
+void sft_set_step_count(SFTState *s, int step) { s->step_count = step; }
+int sft_get_n_lora_grad_bufs(SFTState *s) { return s->NL * 4; }
+float sft_get_lora_scaling(SFTState *s) { return s->lora_scaling; }
+
+float *sft_get_lora_grad_ptr(SFTState *s, int idx, int *out_size)
+{
+    if (!s || idx < 0 || idx >= s->NL * 4) return NULL;
+    const int L = idx / 4, sub = idx % 4;
+    const size_t off = s->layers[L].lora_off + s->sub_off[sub];
+    if (out_size) *out_size = (int)s->sizes[sub];
+    cudaMemcpyAsync(s->h_grad + off, s->lora_g + off, s->sizes[sub] * 4, cudaMemcpyDeviceToHost, g_rt.stream);
+    metal_flush();
+    return s->h_grad + off;
+}
+
+void sft_set_lora_grad(SFTState *s, int idx, const float *data, int size)
+{
+    if (!s || !data || idx < 0 || idx >= s->NL * 4) return;
+    const int L = idx / 4, sub = idx % 4;
+    if (size < 0 || (size_t)size > s->sizes[sub]) return;
+    const size_t off = s->layers[L].lora_off + s->sub_off[sub];
+    if (data != s->h_grad + off) memcpy(s->h_grad + off, data, (size_t)size * 4);
+    cudaMemcpyAsync(s->lora_g + off, s->h_grad + off, (size_t)size * 4, cudaMemcpyHostToDevice, g_rt.stream);
+    metal_flush();
+}
+
+MetalBuf *sft_get_lora_weight_buf(SFTState *s, int layer, int sub)
+{
+    if (!s || layer < 0 || layer >= s->NL || sub < 0 || sub > 3) return NULL;
+    SftLayer *l = &s->layers[layer];
+    if (!l->lora_buf[sub])
+        l->lora_buf[sub] = llmb200_buf_wrap(s->lora_p + l->lora_off + s->sub_off[sub], s->sizes[sub] * 4);
+    return l->lora_buf[sub];
+}
+
+static float *lora_params_host(SFTState *s)
+{
+    float *h = malloc(s->n_lora * sizeof(float));
+    if (!h) return NULL;
+    metal_flush();
+    if (cudaMemcpy(h, s->lora_p, s->n_lora * 4, cudaMemcpyDeviceToHost) != cudaSuccess) { free(h); return NULL; }
+    return h;
+}
+
+void sft_save_lora(SFTState *s, const char *path)
+{
+    if (!s || !path) return;
+    FILE *fp = fopen(path, "wb");
+    if (!fp) {
+        fprintf(stderr, "[FastSFT] Failed to open %s for writing\n", path);
+        return;
+    }
+    float *h = lora_params_host(s);
+    if (!h) { fclose(fp); fprintf(stderr, "[FastSFT] reading the LoRA weights back failed\n"); return; }
+    const uint32_t magic = 0x4C4F5241u;
+    const int32_t n_layers = s->NL, rank = s->lora_rank;
+    fwrite(&magic, 4, 1, fp);
+    fwrite(&n_layers, 4, 1, fp);
+    fwrite(&rank, 4, 1, fp);
+    fwrite(h, sizeof(float), s->n_lora, fp);        /* the flat vector is already in file order */
+    fclose(fp);
+    free(h);
+    printf("[FastSFT] LoRA saved to %s (rank=%d, %.2f MB)\n", path, rank,
+           (float)(s->n_lora * sizeof(float)) / (1024.0f * 1024.0f));
+}
+
+void sft_sync_lora_to_model(SFTState *s, llmb200_qwen3_model *m)
+{
+    if (!s || !m || !m->q_loras || !m->v_loras) return;
+    float *h = lora_params_host(s);
+    if (!h) return;
+    for (int L = 0; L < s->NL; ++L) {
+        const float *base = h + s->layers[L].lora_off;
+        if (m->q_loras[L]) {
+            memcpy(m->q_loras[L]->lora_A->data, base + s->sub_off[0], s->sizes[0] * 4);
+            memcpy(m->q_loras[L]->lora_B->data, base + s->sub_off[1], s->sizes[1] * 4);
+        }
+        if (m->v_loras[L]) {
+            memcpy(m->v_loras[L]->lora_A->data, base + s->sub_off[2], s->sizes[2] * 4);
+            memcpy(m->v_loras[L]->lora_B->data, base + s->sub_off[3], s->sizes[3] * 4);
+        }
+    }
+    free(h);
+}
+
+size_t llmb200_sft_grad_vector(SFTState *s, void **p) { if (!s) return 0; if (p) *p = s->lora_g; return s->n_lora; }
+size_t llmb200_sft_param_vector(SFTState *s, void **p) { if (!s) return 0; if (p) *p = s->lora_p; return s->n_lora; }
+float llmb200_sft_last_grad_norm(SFTState *s) { return s ? s->last_norm : NAN; }
+float llmb200_sft_last_step_ms(SFTState *s, float *update_ms)
+{
+    if (!s) return -1.f;
+    if (update_ms) *update_ms = s->last_update_ms;
+    return s->last_step_ms;
+}
+int llmb200_sft_use_tensor_cores(SFTState *s, int on)
+{
+    if (!s) return 0;
+    const int prev = s->use_tc;
+    /* the transposed copies exist only when the state was created with tensor cores on */
+    s->use_tc = on && s->lm_head.wt != NULL;
+    return prev;
+}
+int llmb200_sft_error(SFTState *s) { return s ? s->err : -1; }
+
+size_t llmb200_sft_export(SFTState *s, int what, int layer, float *dst, size_t cap)
+{
+    if (!s || !dst) return 0;
+    const float *src = NULL;
+    size_t n = 0;
+    const size_t M = s->M;
+    if (what < 100) {
+        if (layer < 0 || layer >= s->NL) return 0;
+        SftLayer *l = &s->layers[layer];
+        switch (what) {
+        case LLMB200_SFT_X_IN: src = l->x_in; n = M * s->D; break;
+        case LLMB200_SFT_LN1: src = l->ln1; n = M * s->D; break;
+        case LLMB200_SFT_QKV: src = l->qkv_out; n = M * s->QKV; break;
+        case LLMB200_SFT_Q_FINAL: src = l->q_f; n = M * s->Hq_hd; break;
+        case LLMB200_SFT_K_FINAL: src = l->k_f; n = M * s->Hkv_hd; break;
+        case LLMB200_SFT_PROBS: src = l->probs; n = (size_t)s->S * s->Hq * s->N * s->N; break;
+        case LLMB200_SFT_X_MID: src = l->x_mid; n = M * s->D; break;
+        case LLMB200_SFT_LN2: src = l->ln2; n = M * s->D; break;
+        case LLMB200_SFT_GATE_UP: src = l->gu_out; n = M * 2 * s->IS; break;
+        case LLMB200_SFT_MID_Q: src = l->mid_q; n = M * s->lora_rank; break;
+        case LLMB200_SFT_MID_V: src = l->mid_v; n = M * s->lora_rank; break;
+        default: return 0;
+        }
+    } else {
+        switch (what) {
+        case LLMB200_SFT_LOGITS: src = s->logits; n = M * s->V; break;
+        case LLMB200_SFT_DLOGITS: src = s->dlogits; n = M * s->V; break;
+        case LLMB200_SFT_LOSSES: src = s->losses; n = M; break;
+        case LLMB200_SFT_X_FINAL: src = s->x_final; n = M * s->D; break;
+        case LLMB200_SFT_LORA_GRADS: src = s->lora_g; n = s->n_lora; break;
+        case LLMB200_SFT_LORA_PARAMS: src = s->lora_p; n = s->n_lora; break;
+        default: return 0;
+        }
+    }
+    if (n > cap) return 0;
+    metal_flush();
+    if (cudaMemcpy(dst, src, n * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    return n;
+}

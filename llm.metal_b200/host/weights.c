@@ -94,7 +94,7 @@ MetalBuf *metal_buf_from_data(const void *data, size_t sz)
 void metal_buf_free(MetalBuf *b)
 {
     if (!b) return;
-    if (b->dev) cudaFree(b->dev);
+    if (b->dev && !b->borrowed) cudaFree(b->dev);
     free(b->host_mirror);
     free(b);
 }
@@ -107,7 +107,7 @@ void *metal_buf_ptr(MetalBuf *b)
         metal_flush();
         return b->dev;
     }
-    if (b->host_mirror) return b->host_mirror;
+    if (b->host_mirror && b->kind != MB_DEVICE) return b->host_mirror;
     if (b->kind == MB_Q8) {
         /* rebuild the reference's 34-byte block stream from the packed rows */
         size_t bytes = (size_t)b->rows * (b->cols / 32) * 34;
@@ -131,7 +131,9 @@ void *metal_buf_ptr(MetalBuf *b)
         if (e != cudaSuccess) { free(b->host_mirror); b->host_mirror = NULL; }
         return b->host_mirror;
     }
-    b->host_mirror = malloc(b->size ? b->size : 1);
+    /* plain device memory: the copy is refreshed on every call */
+    metal_flush();
+    if (!b->host_mirror) b->host_mirror = malloc(b->size ? b->size : 1);
     if (b->host_mirror && cudaMemcpy(b->host_mirror, b->dev, b->size, cudaMemcpyDeviceToHost) != cudaSuccess) {
         free(b->host_mirror);
         b->host_mirror = NULL;
@@ -173,22 +175,39 @@ int llmb200_upload_packed(int wtype, const float *src, long long ld, int rows, i
     return 0;
 }
 
-float *llmb200_upload_f32(const float *src, size_t n)
+int llmb200_upload_f32_into(float *d, const float *src, size_t n)
 {
-    float *d = NULL;
-    CU_TRY(cudaMalloc((void **)&d, (n ? n : 1) * sizeof(float)), return NULL);
     const size_t chunk = LLMB200_STAGE_BYTES / sizeof(float);
     for (size_t o = 0; o < n; o += chunk) {
         const size_t m = (n - o) < chunk ? (n - o) : chunk;
         const int sb = g_rt.stage_next;
         g_rt.stage_next ^= 1;
-        CU_TRY(cudaEventSynchronize(g_rt.stage_done[sb]), { cudaFree(d); return NULL; });
+        CU_TRY(cudaEventSynchronize(g_rt.stage_done[sb]), return -100);
         memcpy(g_rt.h_stage[sb], src + o, m * sizeof(float));
         CU_TRY(cudaMemcpyAsync(d + o, g_rt.h_stage[sb], m * sizeof(float), cudaMemcpyHostToDevice, g_rt.stream),
-               { cudaFree(d); return NULL; });
-        CU_TRY(cudaEventRecord(g_rt.stage_done[sb], g_rt.stream), { cudaFree(d); return NULL; });
+               return -101);
+        CU_TRY(cudaEventRecord(g_rt.stage_done[sb], g_rt.stream), return -102);
     }
+    return 0;
+}
+
+float *llmb200_upload_f32(const float *src, size_t n)
+{
+    float *d = NULL;
+    CU_TRY(cudaMalloc((void **)&d, (n ? n : 1) * sizeof(float)), return NULL);
+    if (llmb200_upload_f32_into(d, src, n) != 0) { cudaFree(d); return NULL; }
     return d;
+}
+
+MetalBuf *llmb200_buf_wrap(void *dev, size_t size)
+{
+    MetalBuf *b = calloc(1, sizeof(MetalBuf));
+    if (!b) return NULL;
+    b->kind = MB_DEVICE;
+    b->dev = dev;
+    b->size = size;
+    b->borrowed = 1;
+    return b;
 }
 
 /* ---------------------------------------------------------------- WMat */
