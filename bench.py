@@ -186,13 +186,268 @@ def cpu_reference_sample(pkg, S, sp, threads):
                       f"{t_layer * 1e3:.0f} ms/layer, {t_head * 1e3:.0f} ms head, extrapolated to {sp.n_layers} layers"}
 
 
+SFT_WORKLOADS = {
+    # name: (architecture, seq_len, sequences per GPU, LoRA rank, alpha)
+    "qwen3-4b-sft-lora": ("qwen3-4b", 64, 8, 16, 32.0),
+    "tiny-qwen3-sft-lora": ("tiny-qwen3", 64, 8, 16, 32.0),
+}
+T_LORA = 50          # tensor ids of the seeded LoRA A matrices (+0: A_q, +2: A_v)
+
+
+class _DeviceVector:
+    """A flat fp32 device vector owned by the library, exposed to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def build_sft_streaming(pkg, L, S, sp, seq, n_seq, rank, alpha, threads):
+    cfg = pkg.config_of(sp, pkg.MODEL_QWEN3, seq, 1)
+    st = L.llmb200_sft_begin(C.byref(cfg), seq, n_seq, rank, alpha)
+    if not st:
+        raise RuntimeError("llmb200_sft_begin failed")
+    D, hd, IS, V = sp.d_model, sp.head_dim, sp.intermediate_size, sp.vocab_size
+    shapes = [(sp.n_q_heads * hd, D), (sp.n_kv_heads * hd, D), (sp.n_kv_heads * hd, D), (D, sp.n_q_heads * hd),
+              (IS, D), (IS, D), (D, IS)]
+    ones_d, ones_h = np.ones(D, dtype=np.float32), np.ones(hd, dtype=np.float32)
+    zb_q = np.zeros(sp.n_q_heads * hd * rank, dtype=np.float32)
+    zb_v = np.zeros(sp.n_kv_heads * hd * rank, dtype=np.float32)
+    fp = pkg.c_float_p
+    for layer in range(sp.n_layers):
+        mats = [gen_f32(S, r * c, sp.seed, S.llmb200_synth_tensor_id(layer, w), sp.weight_std, threads)
+                for w, (r, c) in enumerate(shapes)]
+        ref = pkg.LayerWeightRef()
+        for name, m, (r, c) in zip(["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"], mats, shapes):
+            setattr(ref, name, pkg.WeightRef(m.ctypes.data_as(fp), r, c))
+        ref.input_norm_g = ones_d.ctypes.data_as(fp)
+        ref.post_attn_norm_g = ones_d.ctypes.data_as(fp)
+        ref.q_norm_g = ones_h.ctypes.data_as(fp)
+        ref.k_norm_g = ones_h.ctypes.data_as(fp)
+        ref.d_model, ref.head_dim = D, hd
+        # LoRA as configured: A ~ N(0, 0.01), B = 0
+        a_q = gen_f32(S, rank * D, 77, S.llmb200_synth_tensor_id(layer, T_LORA + 0), 0.01, threads)
+        a_v = gen_f32(S, rank * D, 77, S.llmb200_synth_tensor_id(layer, T_LORA + 2), 0.01, threads)
+        lora = (fp * 4)(a_q.ctypes.data_as(fp), zb_q.ctypes.data_as(fp), a_v.ctypes.data_as(fp), zb_v.ctypes.data_as(fp))
+        if L.llmb200_sft_load_layer(st, layer, C.byref(ref), C.c_float(sp.rope_theta), C.byref(lora)) != 0:
+            raise RuntimeError(f"loading layer {layer} failed")
+        L.metal_flush()
+    lm = gen_f32(S, V * D, sp.seed, S.llmb200_synth_tensor_id(0, 101), sp.weight_std, threads)
+    emb = gen_f32(S, V * D, sp.seed, S.llmb200_synth_tensor_id(0, 100), sp.weight_std, threads)
+    if L.llmb200_sft_finish(st, lm.ctypes.data_as(fp), ones_d.ctypes.data_as(fp), emb.ctypes.data_as(fp), 0) != 0:
+        raise RuntimeError("llmb200_sft_finish failed")
+    return st
+
+
+def sft_flops_per_token(sp):
+    """Forward 2P + backward through the frozen weights 2P multiply-adds per token (LoRA and attention < 1 %)."""
+    D, hd, IS, V = sp.d_model, sp.head_dim, sp.intermediate_size, sp.vocab_size
+    per_layer = (sp.n_q_heads + 2 * sp.n_kv_heads) * hd * D + D * sp.n_q_heads * hd + 3 * IS * D
+    return 4.0 * (per_layer * sp.n_layers + V * D)
+
+
+def sft_cpu_port_sample(sp, seq, rank, alpha):
+    """The CPU restatement (oracle/sft_oracle.py, numpy) timed on one sequence per step, as the reference
+    trains: 1- and 2-layer cuts of the architecture with the full LM head, extrapolated to all layers."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("sft_oracle", os.path.join(ROOT, "oracle", "sft_oracle.py"))
+    o = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(o)
+    rng = np.random.default_rng(0)
+    D, hd, IS, V = sp.d_model, sp.head_dim, sp.intermediate_size, sp.vocab_size
+    Hq, Hkv = sp.n_q_heads, sp.n_kv_heads
+
+    def mat(r, c):
+        return o.f16_round((rng.standard_normal((r, c)) * 0.02).astype(np.float32))
+
+    layer = dict(q=mat(Hq * hd, D), k=mat(Hkv * hd, D), v=mat(Hkv * hd, D), o=mat(D, Hq * hd), gate=mat(IS, D),
+                 up=mat(IS, D), down=mat(D, IS), input_norm=np.ones(D, np.float32), post_attn_norm=np.ones(D, np.float32),
+                 q_norm=np.ones(hd, np.float32), k_norm=np.ones(hd, np.float32))
+    lm, emb = mat(V, D), mat(V, D)
+    lor = dict(A_q=(rng.standard_normal((rank, D)) * 0.01).astype(np.float32), B_q=np.zeros((Hq * hd, rank), np.float32),
+               A_v=(rng.standard_normal((rank, D)) * 0.01).astype(np.float32), B_v=np.zeros((Hkv * hd, rank), np.float32))
+    toks = rng.integers(0, V, seq + 1)
+    times = []
+    for nl in (1, 2):
+        cfg = dict(d_model=D, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=hd, intermediate_size=IS, vocab_size=V, n_layers=nl,
+                   rope_theta=sp.rope_theta, eps=1e-6)
+        w = o.Weights(cfg, [layer] * nl, lm, np.ones(D, np.float32), emb)
+        lora = o.LoRA([lor] * nl, rank, alpha)
+        o.train_step(w, lora, toks[:-1], toks[1:], 1e-4)
+        t0 = time.time()
+        o.train_step(w, lora, toks[:-1], toks[1:], 1e-4)
+        times.append(time.time() - t0)
+    t_layer = max(times[1] - times[0], 1e-6)
+    t_head = max(times[0] - t_layer, 0.0)
+    total = t_head + t_layer * sp.n_layers
+    return {"value": seq / total, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"numpy restatement, one sequence of {seq} tokens per step: 1- and 2-layer cuts + full LM head, "
+                      f"{t_layer * 1e3:.0f} ms/layer, {t_head * 1e3:.0f} ms head+loss, extrapolated to {sp.n_layers} layers"}
+
+
+def sft_main(args, rank, local_rank, world):
+    arch, seq, n_seq, lrank, alpha = SFT_WORKLOADS[args.workload]
+    pkg = entry.load_package()
+    S = pkg.synth()
+    sp = pkg.spec(arch)
+    if args.layers:
+        sp.n_layers = args.layers
+    threads = max(1, min(32, (os.cpu_count() or 8) // max(world, 1)))
+    M = seq * n_seq
+    config = {"workload": f"{arch}{'' if not args.layers else f' cut to {args.layers} layers'} LoRA SFT step, frozen F16-valued "
+                          f"base, rank {lrank} alpha {alpha:g} on Q and V, seq {seq}, {n_seq} sequences per GPU, AdamW lr 1e-4",
+              "seq_len": seq, "sequences_per_gpu": n_seq, "global_batch": n_seq * world, "parallelism": f"dp{world}",
+              "l2": "inputs larger than L2 (every step streams all frozen weights, >> 126 MB); no flush needed"}
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        cb = sft_cpu_port_sample(sp, seq, lrank, alpha)
+        print(json.dumps({"impl": "reference", "metric": "sft_tokens_per_s", "value": cb["value"], "unit": "tok/s",
+                          "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": 1000.0 * seq / cb["value"], "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "cpu_baseline": cb,
+                          "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = pkg.lib()
+    t0 = time.time()
+    st = build_sft_streaming(pkg, L, S, sp, seq, n_seq, lrank, alpha, threads)
+    build_s = time.time() - t0
+    gp = C.c_void_p()
+    n_grad = L.llmb200_sft_grad_vector(st, C.byref(gp))
+    grads = torch.as_tensor(_DeviceVector(gp.value, n_grad), device="cuda") if world > 1 else None
+
+    n_batches = args.steps + args.warmup
+    toks = np.zeros((n_batches, n_seq, seq + 1), dtype=np.uint32)
+    S.llmb200_synth_tokens(toks.ctypes.data, toks.size, 4321 + rank, sp.vocab_size)    # every rank its own sequences
+    xs = np.ascontiguousarray(toks[:, :, :-1]).reshape(n_batches, M)
+    ys = np.ascontiguousarray(toks[:, :, 1:]).reshape(n_batches, M)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    losses = []
+
+    def step(i):
+        """One optimizer step through the public calls; returns (device ms, wall ms)."""
+        barrier()
+        w0 = time.perf_counter()
+        loss = L.llmb200_sft_forward_backward(st, xs[i].ctypes.data_as(pkg.c_u32_p), ys[i].ctypes.data_as(pkg.c_u32_p))
+        ar_ms = 0.0
+        if world > 1:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dist.all_reduce(grads, op=dist.ReduceOp.SUM)       # LoRA-gradient exchange: sum, then the mean
+            grads.mul_(1.0 / world)
+            e1.record()
+            torch.cuda.synchronize()
+            ar_ms = e0.elapsed_time(e1)
+        L.llmb200_sft_apply_update(st, 1e-4)
+        wall = (time.perf_counter() - w0) * 1e3
+        upd = C.c_float(0)
+        dev = L.llmb200_sft_last_step_ms(st, C.byref(upd)) + upd.value + ar_ms
+        barrier()
+        losses.append(loss)
+        return max_over_ranks(dev), max_over_ranks(wall)
+
+    for i in range(args.warmup):
+        step(i)
+    L.b200_launch_count(1)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    timed = [step(args.warmup + i) for i in range(args.steps)]
+    clocks = sampler.stop() if rank == 0 else None
+    launches = int(L.b200_launch_count(0))
+    if L.llmb200_sft_error(st):
+        raise RuntimeError("the SFT engine reported an error")
+    dev_ms = sum(d for d, _ in timed)
+    wall_ms = sum(w for _, w in timed)
+    tok = args.steps * M * world
+    value, e2e_v = tok / (dev_ms / 1e3), tok / (wall_ms / 1e3)
+
+    # dominant kernel alone: the gate/up forward product [M, 2*IS] = [M, D] x [2*IS, D]^T on the tensor cores
+    D, IS = sp.d_model, sp.intermediate_size
+    a = torch.randn(M, D, device="cuda")
+    ws = [torch.randn(2 * IS, D, device="cuda").half().float() * 0.02 for _ in range(3)]
+    cbuf = torch.empty(M, 2 * IS, device="cuda")
+    errw = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def one(wt):
+        g = pkg.GemmArgs()
+        g.A, g.a_row, g.a_col = a.data_ptr(), D, 1
+        g.B, g.b_row, g.b_col = wt.data_ptr(), 1, D
+        g.C, g.ldc, g.M, g.N, g.K, g.alpha, g.d_err = cbuf.data_ptr(), 2 * IS, M, 2 * IS, D, 1.0, errw.data_ptr()
+        return L.b200_gemm_tf32(C.byref(g), C.c_void_p(stream))
+
+    tc_ok = one(ws[0]) == 0
+    roofline = None
+    if tc_ok:
+        for i in range(3):
+            one(ws[i % 3])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 30
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            one(ws[i % 3])
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / 1e3 / reps
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peak, peak_kind = float(json.load(f)["bf16_tflops"]), "measured (cuBLAS bf16 burst; TF32 runs at half that rate)"
+        except Exception:
+            peak, peak_kind = 1590.0, "fallback"
+        ach = 2.0 * M * 2 * IS * D / sec / 1e12
+        roofline = {"bound": "tensor", "kernel": f"gemm_tf32_kernel gate/up forward (M {M}, N {2 * IS}, K {D})",
+                    "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "peak_source": peak_kind,
+                    "traffic": None, "us_per_launch": sec * 1e6}
+    step_flops = sft_flops_per_token(sp) * M
+    line = {
+        "metric": "sft_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "tf32 tensor-core products over binary16-valued weights, fp32 accumulate and elsewhere",
+        "data": "synthetic", "config": config,
+        "e2e": {"value": e2e_v, "unit": "tok/s", "h2d_bytes_per_step": int(2 * M * 4), "d2h_bytes_per_step": int(M * 4 + 8)},
+        "gpu_launches": launches, "roofline": roofline,
+        "step_tflops_per_gpu": step_flops / (dev_ms / args.steps / 1e3) / 1e12,
+        "clocks": clocks, "build_seconds": build_s, "losses": [float(x) for x in losses],
+        "grad_norm_last": float(L.llmb200_sft_last_grad_norm(st)),
+    }
+    if world == 1 and not args.no_cpu_baseline and rank == 0:
+        line["cpu_baseline"] = sft_cpu_port_sample(sp, seq, lrank, alpha)
+    L.sft_state_free(st)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="qwen3-4b-q8", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="qwen3-4b-q8", choices=sorted(WORKLOADS) + sorted(SFT_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (profiling runs)")
     ap.add_argument("--gen-len", type=int, default=0, help="override the workload's generation length (profiling runs)")
@@ -202,6 +457,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload in SFT_WORKLOADS:
+        return sft_main(args, rank, local_rank, world)
     arch, use_fp16, P, G, max_seq = WORKLOADS[args.workload]
     P, G = args.prompt_len or P, args.gen_len or G
     pkg = entry.load_package()

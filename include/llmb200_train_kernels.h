@@ -36,6 +36,8 @@ typedef struct {
     const float *R; long long ldr;
     int M, N, K;
     float alpha;
+    unsigned *d_err;     /* optional device word; the tensor-core kernel stores a non-zero code there when a
+                            bounded wait runs out (the product is then incomplete) */
 } b200_gemm_args;
 
 /* CUDA-core version: any shape, any of the stride combinations above. */

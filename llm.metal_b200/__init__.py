@@ -95,7 +95,7 @@ class GemmArgs(C.Structure):
                 ("B", C.c_void_p), ("b_row", C.c_longlong), ("b_col", C.c_longlong),
                 ("C", C.c_void_p), ("ldc", C.c_longlong),
                 ("R", C.c_void_p), ("ldr", C.c_longlong),
-                ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("alpha", C.c_float)]
+                ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("alpha", C.c_float), ("d_err", C.c_void_p)]
 
 
 class WMat(C.Structure):

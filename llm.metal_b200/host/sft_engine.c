@@ -147,6 +147,7 @@ static void gemm_fwd(SFTState *s, const float *A, const SftMat *W, float *C, con
     g.R = R; g.ldr = W->rows;
     g.M = s->M; g.N = W->rows; g.K = W->cols;
     g.alpha = 1.0f;
+    g.d_err = (unsigned *)s->d_norm + 1;
     if (s->use_tc) {
         int rc = b200_gemm_tf32(&g, g_rt.stream);
         if (rc == 0) return;
@@ -163,6 +164,7 @@ static void gemm_bwd(SFTState *s, const float *A, const SftMat *W, float *C)
     g.C = C; g.ldc = W->cols;
     g.M = s->M; g.N = W->cols; g.K = W->rows;
     g.alpha = 1.0f;
+    g.d_err = (unsigned *)s->d_norm + 1;
     if (s->use_tc && W->wt) {
         g.B = W->wt; g.b_row = 1; g.b_col = W->rows;
         int rc = b200_gemm_tf32(&g, g_rt.stream);
@@ -274,7 +276,8 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->tmp_q = dalloc(s, (size_t)M * R); s->tmp_v = dalloc(s, (size_t)M * R);
     s->tokens = (uint32_t *)dalloc(s, M); s->targets = (uint32_t *)dalloc(s, M);
     s->partials = (double *)dalloc(s, 2 * N_PARTIALS);
-    s->d_norm = dalloc(s, 1);
+    s->d_norm = dalloc(s, 2);                 /* [0] gradient norm, [1] error word of the tensor-core products */
+    if (s->d_norm) cudaMemsetAsync(s->d_norm, 0, 8, g_rt.stream);
     if (!s->err) {
         if (cudaMallocManaged((void **)&s->x_shared, (size_t)M * s->D * 4, cudaMemAttachGlobal) != cudaSuccess ||
             cudaMallocManaged((void **)&s->losses_shared, (size_t)M * 4, cudaMemAttachGlobal) != cudaSuccess ||
@@ -563,7 +566,14 @@ static float mean_loss_host(SFTState *s)
 {
     /* summed on the host in position order like the reference (:1142-1144) */
     S_TRY(s, (int)cudaMemcpyAsync(s->h_loss, s->losses, (size_t)s->M * 4, cudaMemcpyDeviceToHost, g_rt.stream));
+    S_TRY(s, (int)cudaMemcpyAsync(&s->h_loss[s->M], s->d_norm + 1, 4, cudaMemcpyDeviceToHost, g_rt.stream));
     S_TRY(s, (int)cudaStreamSynchronize(g_rt.stream));
+    unsigned gemm_err;
+    memcpy(&gemm_err, &s->h_loss[s->M], 4);
+    if (gemm_err && !s->err) {
+        s->err = (int)gemm_err;
+        fprintf(stderr, "[llmb200] sft: a tensor-core product gave up waiting (code 0x%x)\n", gemm_err);
+    }
     float total = 0.f;
     for (int i = 0; i < s->M; ++i) total += s->h_loss[i];
     return total / (float)s->M;
