@@ -67,8 +67,8 @@ int b200_rms_norm_rows(const float *x, const float *gamma, float *out, int rows,
 /* dx (+)= rms_norm backward of dy through x (rms_norm_train_backward :584-624);
  * accumulate != 0 adds into dx (the reference's residual_add that follows);
  * clamp > 0 clips the result to +-clamp afterwards (clamp_tensor :1155-1161). */
-int b200_rms_norm_bwd_rows(const float *x, const float *dy, const float *gamma, float *dx, int rows, int dim,
-                           float eps, int accumulate, float clamp, void *stream);
+int b200_rms_norm_bwd_rows(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx, int rows,
+                           int dim, float eps, int accumulate, float clamp, void *stream);
 
 /* Per-head RMSNorm then rotary embedding of the q and k column blocks of the
  * fused projection output qkv [rows, ld] (q heads first, then kv heads of k,
@@ -79,10 +79,10 @@ int b200_rms_norm_bwd_rows(const float *x, const float *dy, const float *gamma, 
 int b200_qk_norm_rope(const float *qkv, long long ld, const float *q_gamma, const float *k_gamma,
                       const float *inv_freq, int rows, int seq_len, int n_q, int n_kv, int hd, float eps,
                       float *q_out, float *k_out, void *stream);
-/* Backward of the above, in place on the q and k blocks of dqkv [rows, ld]:
+/* Backward of the above, in place on the q and k blocks of dqkv [rows, dld]:
  * inverse rotation (rope_train_bwd :997-1040) then RMSNorm backward through
- * the saved pre-norm values in qkv. */
-int b200_qk_norm_rope_bwd(float *dqkv, const float *qkv, long long ld, const float *q_gamma, const float *k_gamma,
+ * the saved pre-norm values in qkv [rows, ld]. */
+int b200_qk_norm_rope_bwd(float *dqkv, const float *qkv, long long ld, long long dld, const float *q_gamma, const float *k_gamma,
                           const float *inv_freq, int rows, int seq_len, int n_q, int n_kv, int hd, float eps,
                           void *stream);
 
@@ -105,10 +105,19 @@ int b200_silu_mul_rows(const float *gu, int rows, int inter, float *act, void *s
 /* silu_mul_backward (:540-556): d_act [rows, inter] -> d_gu [rows, 2*inter]. */
 int b200_silu_mul_bwd_rows(const float *d_act, const float *gu, int rows, int inter, float *d_gu, void *stream);
 
-/* y[m, col0+c] += sc * sum_r mid[m,r] * B[c,r] for c < n_cols (float_matmul
- * with K = rank + add_scaled, src/nn/fast_sft.c:639-643). rank <= 64. */
-int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, const float *B, int rank,
-                  float sc, int rows, void *stream);
+/* y[m, col0+c] += sc * sum_r mid[m*mid_ld + r] * B[c,r] for c < n_cols
+ * (float_matmul with K = rank + add_scaled, src/nn/fast_sft.c:639-643). rank <= 64. */
+int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, long long mid_ld, const float *B,
+                  int rank, float sc, int rows, void *stream);
+/* Refreshes the LoRA rows appended to the fused q/k/v weight and to its
+ * transposed copy, so that the two big products of a layer also deliver the
+ * rank-R intermediates of fast_sft.c:639-641 (ln1 A^T) and :948-949, :963-964
+ * (sc dq B_q, sc dv B_v):
+ *   w_ext  [q_cols + 2 kv_cols + xr, d]: extra rows 0..R-1 = A_q, R..2R-1 = A_v, rest 0
+ *   wt_ext [d + xr, q_cols + 2 kv_cols]: extra row r = sc B_q[:, r] over the q columns,
+ *                                        extra row R+r = sc B_v[:, r] over the v columns, rest 0 */
+int b200_lora_pack(float *w_ext, float *wt_ext, const float *A_q, const float *B_q, const float *A_v,
+                   const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc, void *stream);
 
 /* softmax_ce_train (:646-690) followed by scale_tensor(grad_scale):
  * losses[m] = logsumexp - logit[target]; dlogits = (softmax - onehot) * grad_scale. */

@@ -54,40 +54,63 @@ __global__ void embed_rows_kernel(const float *emb, const uint32_t *tokens, int 
     for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = src[i] * scale;
 }
 
-// ---- RMSNorm over rows: one warp per row ----------------------------------------------------
-__global__ void rms_norm_rows_kernel(const float *x, const float *gamma, float *out, int rows, int dim, float eps)
+// ---- RMSNorm over rows: a group of G threads per row (G = 32 for short rows, 256 for long ones) -----
+template <int G>
+__device__ __forceinline__ float group_sum_f(float v, float *sh)
 {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const int l = threadIdx.x & 31;
-    const float *xr = x + (size_t)row * dim;
-    float ss = 0.f;
-    for (int i = l; i < dim; i += 32) { const float v = xr[i]; ss = fmaf(v, v, ss); }
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)dim + eps);
-    float *o = out + (size_t)row * dim;
-    for (int i = l; i < dim; i += 32) o[i] = xr[i] * inv * gamma[i];
+    v = warp_sum(v);
+    if (G == 32) return v;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < G / 32; ++i) t += sh[i];
+    return t;
 }
 
-__global__ void rms_norm_bwd_rows_kernel(const float *x, const float *dy, const float *gamma, float *dx, int rows,
-                                         int dim, float eps, int accumulate, float clamp)
+template <int G>
+__global__ void __launch_bounds__(256)
+rms_norm_rows_kernel(const float *x, const float *gamma, float *out, int rows, int dim, float eps)
 {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const int l = threadIdx.x & 31;
-    const float *xr = x + (size_t)row * dim, *dr = dy + (size_t)row * dim;
+    __shared__ float sh[8];
+    const int row = blockIdx.x * (256 / G) + threadIdx.x / G;
+    const int l = threadIdx.x % G;
+    const bool on = row < rows;
+    const float *xr = x + (size_t)(on ? row : 0) * dim;
+    float ss = 0.f;
+    if (on) for (int i = l; i < dim; i += G) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = group_sum_f<G>(ss, sh);
+    if (!on) return;
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    float *o = out + (size_t)row * dim;
+    for (int i = l; i < dim; i += G) o[i] = xr[i] * inv * gamma[i];
+}
+
+template <int G>
+__global__ void __launch_bounds__(256)
+rms_norm_bwd_rows_kernel(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx, int rows,
+                         int dim, float eps, int accumulate, float clamp)
+{
+    __shared__ float sh[8];
+    const int row = blockIdx.x * (256 / G) + threadIdx.x / G;
+    const int l = threadIdx.x % G;
+    const bool on = row < rows;
+    const float *xr = x + (size_t)(on ? row : 0) * dim, *dr = dy + (size_t)(on ? row : 0) * dy_ld;
     float ss = 0.f, dot = 0.f;
-    for (int i = l; i < dim; i += 32) {
+    if (on) for (int i = l; i < dim; i += G) {
         const float v = xr[i];
         ss = fmaf(v, v, ss);
         dot = fmaf(dr[i] * gamma[i], v, dot);
     }
-    ss = warp_sum(ss);
-    dot = warp_sum(dot);
+    ss = group_sum_f<G>(ss, sh);
+    dot = group_sum_f<G>(dot, sh);
+    if (!on) return;
     const float inv = rsqrtf(ss / (float)dim + eps);
     const float coeff = dot * inv * inv / (float)dim;
     float *o = dx + (size_t)row * dim;
-    for (int i = l; i < dim; i += 32) {
+    for (int i = l; i < dim; i += G) {
         float v = (gamma[i] * dr[i] - coeff * xr[i]) * inv;
         if (accumulate) v += o[i];
         if (clamp > 0.f) v = fminf(fmaxf(v, -clamp), clamp);
@@ -134,7 +157,7 @@ __global__ void qk_norm_rope_kernel(const float *qkv, long long ld, const float 
 }
 
 template <int HD>
-__global__ void qk_norm_rope_bwd_kernel(float *dqkv, const float *qkv, long long ld, const float *qg, const float *kg,
+__global__ void qk_norm_rope_bwd_kernel(float *dqkv, const float *qkv, long long ld, long long dld, const float *qg, const float *kg,
                                         const float *inv_freq, int rows, int seq_len, int n_q, int n_kv, float eps)
 {
     constexpr int PER = HD / 64;
@@ -143,7 +166,7 @@ __global__ void qk_norm_rope_bwd_kernel(float *dqkv, const float *qkv, long long
     if (unit >= rows * nh) return;
     const int row = unit / nh, h = unit % nh, l = threadIdx.x & 31;
     const float *x = qkv + (size_t)row * ld + (size_t)h * HD;
-    float *d = dqkv + (size_t)row * ld + (size_t)h * HD;
+    float *d = dqkv + (size_t)row * dld + (size_t)h * HD;
     const float *g = h < n_q ? qg : kg;
     const float pos = (float)(row % seq_len);
     float xa[PER], xb[PER], ga[PER], gb[PER];
@@ -349,20 +372,62 @@ __global__ void silu_mul_bwd_rows_kernel(const float *d_act, const float *gu, in
 }
 
 // ---- LoRA up-projection added into the base projection -------------------------------------------
+// One thread per output column keeps its row of B in registers and walks LORA_ROWS token rows whose
+// mid vectors sit in shared memory.
+constexpr int LORA_ROWS = 8;
 template <int MAXR>
-__global__ void lora_add_kernel(float *y, long long ld, int col0, int n_cols, const float *mid, const float *B, int rank,
-                                float sc, int rows)
+__global__ void __launch_bounds__(256)
+lora_add_kernel(float *y, long long ld, int col0, int n_cols, const float *mid, long long mid_ld, const float *B,
+                int rank, float sc, int rows)
 {
-    __shared__ float ms[MAXR];
-    const int m = blockIdx.y;
-    if (threadIdx.x < rank) ms[threadIdx.x] = mid[(size_t)m * rank + threadIdx.x];
+    __shared__ float ms[LORA_ROWS][MAXR];
+    const int m0 = blockIdx.y * LORA_ROWS;
+    for (int e = threadIdx.x; e < LORA_ROWS * MAXR; e += blockDim.x) {
+        const int i = e / MAXR, r = e % MAXR;
+        ms[i][r] = (r < rank && m0 + i < rows) ? mid[(size_t)(m0 + i) * mid_ld + r] : 0.f;   // zero beyond the rank
+    }
     __syncthreads();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= n_cols) return;
-    const float *br = B + (size_t)c * rank;
-    float acc = 0.f;
-    for (int r = 0; r < rank; ++r) acc = fmaf(ms[r], br[r], acc);
-    y[(size_t)m * ld + col0 + c] += sc * acc;
+    float b[MAXR];
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) b[r] = r < rank ? B[(size_t)c * rank + r] : 0.f;
+#pragma unroll
+    for (int i = 0; i < LORA_ROWS; ++i) {
+        if (m0 + i >= rows) break;
+        float acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAXR; ++r) acc = fmaf(ms[i][r], b[r], acc);
+        y[(size_t)(m0 + i) * ld + col0 + c] += sc * acc;
+    }
+}
+
+// Refreshes the LoRA rows appended to the fused q/k/v weight and to its transposed copy.
+//   w_ext  [qkv + xr, d]: rows qkv..qkv+R = A_q, rows qkv+R..qkv+2R = A_v
+//   wt_ext [d + xr, qkv]: row d+r = sc * B_q[:, r] over the q columns, row d+R+r = sc * B_v[:, r] over the
+//                         v columns, zero elsewhere
+// so that the forward product also yields ln1 A^T and the backward product also yields sc * dq B_q and
+// sc * dv B_v (src/nn/fast_sft.c:639-641, 948-949, 963-964) at no extra pass over the activations.
+__global__ void lora_pack_kernel(float *w_ext, float *wt_ext, const float *A_q, const float *B_q, const float *A_v,
+                                 const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc)
+{
+    const int qkv = q_cols + 2 * kv_cols;
+    const int row = blockIdx.y;                                    // 0 .. xr-1
+    const int width = d > qkv ? d : qkv;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+        if (c < d) {
+            float v = 0.f;
+            if (row < rank) v = A_q[(size_t)row * d + c];
+            else if (row < 2 * rank) v = A_v[(size_t)(row - rank) * d + c];
+            w_ext[(size_t)(qkv + row) * d + c] = v;
+        }
+        if (c < qkv) {
+            float v = 0.f;
+            if (row < rank) { if (c < q_cols) v = sc * B_q[(size_t)c * rank + row]; }
+            else if (row < 2 * rank) { if (c >= q_cols + kv_cols) v = sc * B_v[(size_t)(c - q_cols - kv_cols) * rank + (row - rank)]; }
+            wt_ext[(size_t)(d + row) * qkv + c] = v;
+        }
+    }
 }
 
 // ---- softmax cross-entropy: one block per row ----------------------------------------------------
@@ -508,16 +573,21 @@ extern "C" int b200_rms_norm_rows(const float *x, const float *gamma, float *out
                                   void *stream)
 {
     if (!x || !gamma || !out || rows <= 0 || dim <= 0) return B200_E_BADARG;
-    rms_norm_rows_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, gamma, out, rows, dim, eps);
+    if (dim >= 1024) rms_norm_rows_kernel<256><<<rows, 256, 0, (cudaStream_t)stream>>>(x, gamma, out, rows, dim, eps);
+    else rms_norm_rows_kernel<32><<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, gamma, out, rows, dim, eps);
     return done();
 }
 
-extern "C" int b200_rms_norm_bwd_rows(const float *x, const float *dy, const float *gamma, float *dx, int rows, int dim,
-                                      float eps, int accumulate, float clamp, void *stream)
+extern "C" int b200_rms_norm_bwd_rows(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx,
+                                      int rows, int dim, float eps, int accumulate, float clamp, void *stream)
 {
-    if (!x || !dy || !gamma || !dx || rows <= 0 || dim <= 0) return B200_E_BADARG;
-    rms_norm_bwd_rows_kernel<<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, dy, gamma, dx, rows, dim, eps,
-                                                                              accumulate, clamp);
+    if (!x || !dy || !gamma || !dx || rows <= 0 || dim <= 0 || dy_ld < dim) return B200_E_BADARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dim >= 1024)
+        rms_norm_bwd_rows_kernel<256><<<rows, 256, 0, st>>>(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate, clamp);
+    else
+        rms_norm_bwd_rows_kernel<32><<<(rows + 7) / 8, 256, 0, st>>>(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate,
+                                                                    clamp);
     return done();
 }
 
@@ -538,7 +608,7 @@ extern "C" int b200_qk_norm_rope(const float *qkv, long long ld, const float *q_
     return done();
 }
 
-extern "C" int b200_qk_norm_rope_bwd(float *dqkv, const float *qkv, long long ld, const float *q_gamma,
+extern "C" int b200_qk_norm_rope_bwd(float *dqkv, const float *qkv, long long ld, long long dld, const float *q_gamma,
                                      const float *k_gamma, const float *inv_freq, int rows, int seq_len, int n_q,
                                      int n_kv, int hd, float eps, void *stream)
 {
@@ -547,9 +617,9 @@ extern "C" int b200_qk_norm_rope_bwd(float *dqkv, const float *qkv, long long ld
     const unsigned grid = (unsigned)((units + 7) / 8);
     cudaStream_t st = (cudaStream_t)stream;
     switch (hd) {
-    case 64: qk_norm_rope_bwd_kernel<64><<<grid, 256, 0, st>>>(dqkv, qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
-    case 128: qk_norm_rope_bwd_kernel<128><<<grid, 256, 0, st>>>(dqkv, qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
-    case 256: qk_norm_rope_bwd_kernel<256><<<grid, 256, 0, st>>>(dqkv, qkv, ld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
+    case 64: qk_norm_rope_bwd_kernel<64><<<grid, 256, 0, st>>>(dqkv, qkv, ld, dld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
+    case 128: qk_norm_rope_bwd_kernel<128><<<grid, 256, 0, st>>>(dqkv, qkv, ld, dld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
+    case 256: qk_norm_rope_bwd_kernel<256><<<grid, 256, 0, st>>>(dqkv, qkv, ld, dld, q_gamma, k_gamma, inv_freq, rows, seq_len, n_q, n_kv, eps); break;
     default: return B200_E_BADARG;
     }
     return done();
@@ -635,12 +705,28 @@ extern "C" int b200_silu_mul_bwd_rows(const float *d_act, const float *gu, int r
     return done();
 }
 
-extern "C" int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, const float *B, int rank,
-                             float sc, int rows, void *stream)
+extern "C" int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, long long mid_ld,
+                             const float *B, int rank, float sc, int rows, void *stream)
 {
-    if (!y || !mid || !B || rank <= 0 || rank > 64 || rows <= 0 || n_cols <= 0 || rows > 65535) return B200_E_BADARG;
-    dim3 grid((n_cols + 255) / 256, rows);
-    lora_add_kernel<64><<<grid, 256, 0, (cudaStream_t)stream>>>(y, ld, col0, n_cols, mid, B, rank, sc, rows);
+    if (!y || !mid || !B || rank <= 0 || rank > 64 || rows <= 0 || n_cols <= 0 || mid_ld < rank) return B200_E_BADARG;
+    if ((rows + LORA_ROWS - 1) / LORA_ROWS > 65535) return B200_E_TOOLARGE;
+    dim3 grid((n_cols + 255) / 256, (rows + LORA_ROWS - 1) / LORA_ROWS);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rank <= 16) lora_add_kernel<16><<<grid, 256, 0, st>>>(y, ld, col0, n_cols, mid, mid_ld, B, rank, sc, rows);
+    else lora_add_kernel<64><<<grid, 256, 0, st>>>(y, ld, col0, n_cols, mid, mid_ld, B, rank, sc, rows);
+    return done();
+}
+
+extern "C" int b200_lora_pack(float *w_ext, float *wt_ext, const float *A_q, const float *B_q, const float *A_v,
+                              const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc, void *stream)
+{
+    if (!w_ext || !wt_ext || !A_q || !B_q || !A_v || !B_v || d <= 0 || q_cols <= 0 || kv_cols <= 0 || rank <= 0 ||
+        xr < 2 * rank)
+        return B200_E_BADARG;
+    const int width = d > q_cols + 2 * kv_cols ? d : q_cols + 2 * kv_cols;
+    dim3 grid((width + 255) / 256, xr);
+    lora_pack_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w_ext, wt_ext, A_q, B_q, A_v, B_v, d, q_cols, kv_cols, rank,
+                                                            xr, sc);
     return done();
 }
 

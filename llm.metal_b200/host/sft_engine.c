@@ -39,7 +39,8 @@ typedef struct {
     float *g_in, *g_post, *g_q, *g_k;   /* norm gammas */
     float *inv_freq;                    /* [hd/2] */
     /* saved activations */
-    float *x_in, *ln1, *qkv_out, *q_f, *k_f, *probs, *x_mid, *ln2, *gu_out, *mid_q, *mid_v;
+    float *x_in, *ln1, *qkv_out, *q_f, *k_f, *probs, *x_mid, *ln2, *gu_out;
+    float *mid_q, *mid_v;               /* columns QKV.. of qkv_out (row stride QKVX), not separate buffers */
     size_t lora_off;                    /* offset of this layer in the flat LoRA vectors */
     MetalBuf *lora_buf[4];              /* handles made on demand by sft_get_lora_weight_buf */
     int loaded;
@@ -47,6 +48,7 @@ typedef struct {
 
 struct SFTState {
     int D, Hq, Hkv, hd, IS, V, NL, N, S, M, QKV;
+    int XR, QKVX;               /* LoRA columns appended to the fused q/k/v product (2R rounded up to 4) */
     int Hq_hd, Hkv_hd;
     float eps, lora_scaling, emb_scale;
     int lora_rank, step_count, model_type;
@@ -65,7 +67,7 @@ struct SFTState {
 
     /* scratch */
     float *x_final, *ln_final, *att, *act, *logits, *dlogits, *losses;
-    float *dx, *d_ln, *d_act, *d_gu, *d_att, *dqkv, *d_score, *tmp_q, *tmp_v;
+    float *dx, *d_ln, *d_lnx, *d_act, *d_gu, *d_att, *dqkv, *d_score;
     uint32_t *tokens, *targets;
     double *partials;
     float *d_norm;
@@ -122,6 +124,19 @@ static int mat_alloc(SFTState *s, SftMat *m, int rows, int cols)
     m->w = dalloc(s, (size_t)rows * cols);
     m->wt = s->use_tc ? dalloc(s, (size_t)rows * cols) : NULL;
     return (m->w && (!s->use_tc || m->wt)) ? 0 : -1;
+}
+
+/* The fused q/k/v matrix carries XR extra rows (the LoRA A matrices) and always has a transposed copy
+ * [D + XR, QKV] whose extra rows hold sc * B (see b200_lora_pack). */
+static int qkv_alloc(SFTState *s, SftMat *m)
+{
+    m->rows = s->QKVX;
+    m->cols = s->D;
+    m->w = dalloc(s, (size_t)s->QKVX * s->D);
+    m->wt = dalloc(s, (size_t)(s->D + s->XR) * s->QKV);
+    if (m->w) cudaMemsetAsync(m->w, 0, (size_t)s->QKVX * s->D * 4, g_rt.stream);
+    if (m->wt) cudaMemsetAsync(m->wt, 0, (size_t)(s->D + s->XR) * s->QKV * 4, g_rt.stream);
+    return (m->w && m->wt) ? 0 : -1;
 }
 
 static int mat_finish(SFTState *s, SftMat *m)
@@ -217,6 +232,8 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->IS = cfg->intermediate_size; s->V = cfg->vocab_size; s->NL = cfg->n_layers;
     s->N = seq_len; s->S = n_seq; s->M = seq_len * n_seq;
     s->Hq_hd = s->Hq * s->hd; s->Hkv_hd = s->Hkv * s->hd; s->QKV = s->Hq_hd + 2 * s->Hkv_hd;
+    s->XR = (2 * lora_rank + 3) & ~3;
+    s->QKVX = s->QKV + s->XR;
     s->emb_scale = 1.0f;
     s->eps = 1e-6f;
     s->lora_rank = lora_rank;
@@ -246,7 +263,7 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     for (int L = 0; L < s->NL && !s->err; ++L) {
         SftLayer *l = &s->layers[L];
         l->lora_off = s->per_layer * L;
-        mat_alloc(s, &l->qkv, s->QKV, s->D);
+        qkv_alloc(s, &l->qkv);
         mat_alloc(s, &l->o, s->D, s->Hq_hd);
         mat_alloc(s, &l->gu, 2 * s->IS, s->D);
         mat_alloc(s, &l->down, s->D, s->IS);
@@ -254,12 +271,12 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
         l->g_q = dalloc(s, s->hd); l->g_k = dalloc(s, s->hd);
         l->inv_freq = dalloc(s, s->hd / 2);
         l->x_in = dalloc(s, (size_t)M * s->D); l->ln1 = dalloc(s, (size_t)M * s->D);
-        l->qkv_out = dalloc(s, (size_t)M * s->QKV);
+        l->qkv_out = dalloc(s, (size_t)M * s->QKVX);
+        if (l->qkv_out) { l->mid_q = l->qkv_out + s->QKV; l->mid_v = l->mid_q + R; }
         l->q_f = dalloc(s, (size_t)M * s->Hq_hd); l->k_f = dalloc(s, (size_t)M * s->Hkv_hd);
         l->probs = dalloc(s, (size_t)s->S * s->Hq * s->N * s->N);
         l->x_mid = dalloc(s, (size_t)M * s->D); l->ln2 = dalloc(s, (size_t)M * s->D);
         l->gu_out = dalloc(s, (size_t)M * 2 * s->IS);
-        l->mid_q = dalloc(s, (size_t)M * R); l->mid_v = dalloc(s, (size_t)M * R);
     }
     mat_alloc(s, &s->lm_head, s->V, s->D);
     s->final_g = dalloc(s, s->D);
@@ -270,10 +287,10 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->logits = dalloc(s, (size_t)M * s->V); s->dlogits = dalloc(s, (size_t)M * s->V);
     s->losses = dalloc(s, M);
     s->dx = dalloc(s, (size_t)M * s->D); s->d_ln = dalloc(s, (size_t)M * s->D);
+    s->d_lnx = dalloc(s, (size_t)M * (s->D + s->XR));
     s->d_act = dalloc(s, (size_t)M * s->IS); s->d_gu = dalloc(s, (size_t)M * 2 * s->IS);
     s->d_att = dalloc(s, (size_t)M * s->Hq_hd); s->dqkv = dalloc(s, (size_t)M * s->QKV);
     s->d_score = dalloc(s, (size_t)s->S * s->Hq * s->N * s->N);
-    s->tmp_q = dalloc(s, (size_t)M * R); s->tmp_v = dalloc(s, (size_t)M * R);
     s->tokens = (uint32_t *)dalloc(s, M); s->targets = (uint32_t *)dalloc(s, M);
     s->partials = (double *)dalloc(s, 2 * N_PARTIALS);
     s->d_norm = dalloc(s, 2);                 /* [0] gradient norm, [1] error word of the tensor-core products */
@@ -325,7 +342,7 @@ int llmb200_sft_load_layer(SFTState *s, int L, const LayerWeightRef *r, float ro
     if (!rc) rc = mat_put(s, &l->gu, 0, r->gate_proj.data, s->IS);
     if (!rc) rc = mat_put(s, &l->gu, s->IS, r->up_proj.data, s->IS);
     if (!rc) rc = mat_put(s, &l->down, 0, r->down_proj.data, s->D);
-    if (!rc) rc = mat_finish(s, &l->qkv);
+    if (!rc) rc = b200_transpose_f32(l->qkv.w, s->QKV, s->D, l->qkv.wt, g_rt.stream);   /* rows 0..D-1 of wt */
     if (!rc) rc = mat_finish(s, &l->o);
     if (!rc) rc = mat_finish(s, &l->gu);
     if (!rc) rc = mat_finish(s, &l->down);
@@ -437,14 +454,14 @@ void sft_state_free(SFTState *s)
         SftLayer *l = &s->layers[L];
         mat_free(&l->qkv); mat_free(&l->o); mat_free(&l->gu); mat_free(&l->down);
         float *bufs[] = { l->g_in, l->g_post, l->g_q, l->g_k, l->inv_freq, l->x_in, l->ln1, l->qkv_out, l->q_f, l->k_f,
-                          l->probs, l->x_mid, l->ln2, l->gu_out, l->mid_q, l->mid_v };
+                          l->probs, l->x_mid, l->ln2, l->gu_out };
         for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
         for (int i = 0; i < 4; ++i) metal_buf_free(l->lora_buf[i]);
     }
     mat_free(&s->lm_head);
     void *bufs[] = { s->final_g, s->d_emb, s->lora_p, s->lora_g, s->lora_m, s->lora_v, s->x_final, s->ln_final, s->att,
                      s->act, s->logits, s->dlogits, s->losses, s->dx, s->d_ln, s->d_act, s->d_gu, s->d_att, s->dqkv,
-                     s->d_score, s->tmp_q, s->tmp_v, s->tokens, s->targets, s->partials, s->d_norm, s->x_shared,
+                     s->d_score, s->d_lnx, s->tokens, s->targets, s->partials, s->d_norm, s->x_shared,
                      s->losses_shared };
     for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
     cudaFreeHost(s->h_grad); cudaFreeHost(s->h_tok); cudaFreeHost(s->h_loss);
@@ -472,15 +489,16 @@ static void forward_device(SFTState *s)
         float *pA_q = s->lora_p + l->lora_off + s->sub_off[0], *pB_q = s->lora_p + l->lora_off + s->sub_off[1];
         float *pA_v = s->lora_p + l->lora_off + s->sub_off[2], *pB_v = s->lora_p + l->lora_off + s->sub_off[3];
         S_TRY(s, b200_rms_norm_rows(l->x_in, l->g_in, l->ln1, M, s->D, s->eps, st));
+        /* the LoRA matrices ride along with the frozen q/k/v weight: the product below also yields
+         * mid_q = ln1 A_q^T and mid_v = ln1 A_v^T in the last columns of qkv_out (:639, :652) */
+        S_TRY(s, b200_lora_pack(l->qkv.w, l->qkv.wt, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR, sc, st));
         gemm_fwd(s, l->ln1, &l->qkv, l->qkv_out, NULL);
-        /* q += sc * (ln1 A_q^T) B_q^T, v likewise (:639-643, :652-656) */
-        gemm_small(s, l->ln1, s->D, 1, pA_q, 1, s->D, l->mid_q, R, NULL, M, R, s->D, 1.0f);
-        S_TRY(s, b200_lora_add(l->qkv_out, s->QKV, 0, s->Hq_hd, l->mid_q, pB_q, R, sc, M, st));
-        gemm_small(s, l->ln1, s->D, 1, pA_v, 1, s->D, l->mid_v, R, NULL, M, R, s->D, 1.0f);
-        S_TRY(s, b200_lora_add(l->qkv_out, s->QKV, s->Hq_hd + s->Hkv_hd, s->Hkv_hd, l->mid_v, pB_v, R, sc, M, st));
-        S_TRY(s, b200_qk_norm_rope(l->qkv_out, s->QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv, s->hd,
+        /* q += sc * mid_q B_q^T, v += sc * mid_v B_v^T (:641-643, :654-656) */
+        S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, 0, s->Hq_hd, l->mid_q, s->QKVX, pB_q, R, sc, M, st));
+        S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, s->Hq_hd + s->Hkv_hd, s->Hkv_hd, l->mid_v, s->QKVX, pB_v, R, sc, M, st));
+        S_TRY(s, b200_qk_norm_rope(l->qkv_out, s->QKVX, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv, s->hd,
                                    s->eps, l->q_f, l->k_f, st));
-        S_TRY(s, b200_attn_train_fwd(l->q_f, l->k_f, l->qkv_out + s->Hq_hd + s->Hkv_hd, s->QKV, s->S, s->N, s->Hq,
+        S_TRY(s, b200_attn_train_fwd(l->q_f, l->k_f, l->qkv_out + s->Hq_hd + s->Hkv_hd, s->QKVX, s->S, s->N, s->Hq,
                                      s->Hkv, s->hd, attn_scale, l->probs, s->att, st));
         gemm_fwd(s, s->att, &l->o, l->x_mid, l->x_in);                       /* + residual (:686) */
         S_TRY(s, b200_rms_norm_rows(l->x_mid, l->g_post, l->ln2, M, s->D, s->eps, st));
@@ -507,7 +525,7 @@ static void backward_device(SFTState *s)
     const int M = s->M, R = s->lora_rank, QKV = s->QKV;
     const float sc = s->lora_scaling, attn_scale = 1.0f / sqrtf((float)s->hd);
     gemm_bwd(s, s->dlogits, &s->lm_head, s->d_ln);                                           /* :777 */
-    S_TRY(s, b200_rms_norm_bwd_rows(s->x_final, s->d_ln, s->final_g, s->dx, M, s->D, s->eps, 0, 0.f, st));
+    S_TRY(s, b200_rms_norm_bwd_rows(s->x_final, s->d_ln, s->D, s->final_g, s->dx, M, s->D, s->eps, 0, 0.f, st));
     for (int L = s->NL - 1; L >= 0; --L) {
         SftLayer *l = &s->layers[L];
         float *pA_q = s->lora_p + l->lora_off + s->sub_off[0], *pB_q = s->lora_p + l->lora_off + s->sub_off[1];
@@ -518,29 +536,40 @@ static void backward_device(SFTState *s)
         gemm_bwd(s, s->dx, &l->down, s->d_act);
         S_TRY(s, b200_silu_mul_bwd_rows(s->d_act, l->gu_out, M, s->IS, s->d_gu, st));
         gemm_bwd(s, s->d_gu, &l->gu, s->d_ln);
-        S_TRY(s, b200_rms_norm_bwd_rows(l->x_mid, s->d_ln, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, st));
+        S_TRY(s, b200_rms_norm_bwd_rows(l->x_mid, s->d_ln, s->D, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, st));
         /* attention (:889-918) */
         gemm_bwd(s, s->dx, &l->o, s->d_att);
         const float *v = l->qkv_out + s->Hq_hd + s->Hkv_hd;
-        S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, QKV, s->S, s->N, s->Hq, s->Hkv, s->hd,
+        S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd,
                                      attn_scale, s->d_score, s->dqkv, QKV, st));
-        S_TRY(s, b200_qk_norm_rope_bwd(s->dqkv, l->qkv_out, QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv,
-                                       s->hd, s->eps, st));
+        S_TRY(s, b200_qk_norm_rope_bwd(s->dqkv, l->qkv_out, s->QKVX, QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq,
+                                       s->Hkv, s->hd, s->eps, st));
         const float *dq = s->dqkv, *dv = s->dqkv + s->Hq_hd + s->Hkv_hd;
-        /* LoRA Q (:946-952): dB = sc dq^T mid, tmp = sc dq B, dA = tmp^T ln1 */
-        gemm_small(s, dq, 1, QKV, l->mid_q, R, 1, gB_q, R, NULL, s->Hq_hd, R, M, sc);
-        gemm_small(s, dq, QKV, 1, pB_q, R, 1, s->tmp_q, R, NULL, M, R, s->Hq_hd, sc);
-        gemm_small(s, s->tmp_q, 1, R, l->ln1, s->D, 1, gA_q, s->D, NULL, R, s->D, M, 1.0f);
-        /* LoRA V (:961-966) */
-        gemm_small(s, dv, 1, QKV, l->mid_v, R, 1, gB_v, R, NULL, s->Hkv_hd, R, M, sc);
-        gemm_small(s, dv, QKV, 1, pB_v, R, 1, s->tmp_v, R, NULL, M, R, s->Hkv_hd, sc);
-        gemm_small(s, s->tmp_v, 1, R, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
-        /* through the frozen q, k, v projections and the two LoRA down-projections (:953-970) */
-        gemm_bwd(s, s->dqkv, &l->qkv, s->d_ln);
-        gemm_small(s, s->tmp_q, R, 1, pA_q, s->D, 1, s->d_ln, s->D, s->d_ln, M, s->D, R, 1.0f);
-        gemm_small(s, s->tmp_v, R, 1, pA_v, s->D, 1, s->d_ln, s->D, s->d_ln, M, s->D, R, 1.0f);
+        /* Through the frozen q, k, v projections (:955-958, :968-970). The transposed weight carries sc*B_q and
+         * sc*B_v as extra rows, so the same product leaves tmp_q = sc dq B_q and tmp_v = sc dv B_v (:948-949,
+         * :963-964) in columns D.. of d_lnx. */
+        const int DX = s->D + s->XR;
+        {
+            b200_gemm_args g = {0};
+            g.A = s->dqkv; g.a_row = QKV; g.a_col = 1;
+            g.B = l->qkv.wt; g.b_row = 1; g.b_col = QKV;
+            g.C = s->d_lnx; g.ldc = DX;
+            g.M = M; g.N = DX; g.K = QKV; g.alpha = 1.0f;
+            g.d_err = (unsigned *)s->d_norm + 1;
+            int rc = s->use_tc ? b200_gemm_tf32(&g, st) : B200_E_UNSUPPORTED;
+            if (rc == B200_E_UNSUPPORTED) rc = b200_gemm_f32(&g, st);
+            S_TRY(s, rc);
+        }
+        const float *tmp_q = s->d_lnx + s->D, *tmp_v = tmp_q + R;
+        /* dB = sc dq^T mid (:946-947, :961-962); dA = tmp^T ln1 (:950, :965) */
+        gemm_small(s, dq, 1, QKV, l->mid_q, s->QKVX, 1, gB_q, R, NULL, s->Hq_hd, R, M, sc);
+        gemm_small(s, tmp_q, 1, DX, l->ln1, s->D, 1, gA_q, s->D, NULL, R, s->D, M, 1.0f);
+        gemm_small(s, dv, 1, QKV, l->mid_v, s->QKVX, 1, gB_v, R, NULL, s->Hkv_hd, R, M, sc);
+        gemm_small(s, tmp_v, 1, DX, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
+        /* d_ln += tmp_q A_q + tmp_v A_v (:951-953, :966, :970): one product over the 2R packed rows of the weight */
+        gemm_small(s, tmp_q, DX, 1, l->qkv.w + (size_t)QKV * s->D, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, 2 * R, 1.0f);
         /* input norm + residual + clamp (:974-979) */
-        S_TRY(s, b200_rms_norm_bwd_rows(l->x_in, s->d_ln, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, st));
+        S_TRY(s, b200_rms_norm_bwd_rows(l->x_in, s->d_lnx, DX, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, st));
     }
 }
 
@@ -776,15 +805,22 @@ size_t llmb200_sft_export(SFTState *s, int what, int layer, float *dst, size_t c
         switch (what) {
         case LLMB200_SFT_X_IN: src = l->x_in; n = M * s->D; break;
         case LLMB200_SFT_LN1: src = l->ln1; n = M * s->D; break;
-        case LLMB200_SFT_QKV: src = l->qkv_out; n = M * s->QKV; break;
+        case LLMB200_SFT_QKV: src = l->qkv_out; n = M * s->QKVX; break;
         case LLMB200_SFT_Q_FINAL: src = l->q_f; n = M * s->Hq_hd; break;
         case LLMB200_SFT_K_FINAL: src = l->k_f; n = M * s->Hkv_hd; break;
         case LLMB200_SFT_PROBS: src = l->probs; n = (size_t)s->S * s->Hq * s->N * s->N; break;
         case LLMB200_SFT_X_MID: src = l->x_mid; n = M * s->D; break;
         case LLMB200_SFT_LN2: src = l->ln2; n = M * s->D; break;
         case LLMB200_SFT_GATE_UP: src = l->gu_out; n = M * 2 * s->IS; break;
-        case LLMB200_SFT_MID_Q: src = l->mid_q; n = M * s->lora_rank; break;
-        case LLMB200_SFT_MID_V: src = l->mid_v; n = M * s->lora_rank; break;
+        case LLMB200_SFT_MID_Q:
+        case LLMB200_SFT_MID_V:
+            n = M * s->lora_rank;
+            if (n > cap) return 0;
+            metal_flush();
+            if (cudaMemcpy2D(dst, (size_t)s->lora_rank * 4, what == LLMB200_SFT_MID_Q ? l->mid_q : l->mid_v,
+                             (size_t)s->QKVX * 4, (size_t)s->lora_rank * 4, M, cudaMemcpyDeviceToHost) != cudaSuccess)
+                return 0;
+            return n;
         default: return 0;
         }
     } else {

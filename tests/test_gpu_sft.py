@@ -108,9 +108,10 @@ def test_round_f16_is_bit_exact_and_transpose(pkg, lib):
     assert np.array_equal(host(t), got.T)
 
 
-def test_rms_norm_rows_forward_and_backward(lib):
+@pytest.mark.parametrize("rows,dim", [(37, 200), (19, 2560)])
+def test_rms_norm_rows_forward_and_backward(lib, rows, dim):
     rng = np.random.default_rng(4)
-    rows, dim, eps = 37, 200, 1e-6
+    eps = 1e-6
     x = rng.standard_normal((rows, dim)).astype(np.float32)
     dy = rng.standard_normal((rows, dim)).astype(np.float32)
     g = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
@@ -119,11 +120,11 @@ def test_rms_norm_rows_forward_and_backward(lib):
     assert lib.b200_rms_norm_rows(dx.data_ptr(), dg.data_ptr(), dout.data_ptr(), rows, dim, eps, None) == 0
     assert sc.rel_err(host(dout), o.rms_norm(x, g, eps)) < 1e-5
     ddy, dacc = dev(dy), dev(dx0)
-    assert lib.b200_rms_norm_bwd_rows(dx.data_ptr(), ddy.data_ptr(), dg.data_ptr(), dacc.data_ptr(), rows, dim, eps, 1,
-                                      0.0, None) == 0
+    assert lib.b200_rms_norm_bwd_rows(dx.data_ptr(), ddy.data_ptr(), dim, dg.data_ptr(), dacc.data_ptr(), rows, dim, eps,
+                                      1, 0.0, None) == 0
     assert sc.rel_err(host(dacc), dx0 + o.rms_norm_backward(x, dy, g, eps)) < 1e-5
-    assert lib.b200_rms_norm_bwd_rows(dx.data_ptr(), ddy.data_ptr(), dg.data_ptr(), dacc.data_ptr(), rows, dim, eps, 0,
-                                      0.5, None) == 0
+    assert lib.b200_rms_norm_bwd_rows(dx.data_ptr(), ddy.data_ptr(), dim, dg.data_ptr(), dacc.data_ptr(), rows, dim, eps,
+                                      0, 0.5, None) == 0
     assert sc.rel_err(host(dacc), np.clip(o.rms_norm_backward(x, dy, g, eps), -0.5, 0.5)) < 1e-5
 
 
@@ -185,7 +186,7 @@ def test_qk_norm_rope_and_attention(lib, hd):
     ddo = dev(d_out)
     assert lib.b200_attn_train_bwd(ddo.data_ptr(), probs.data_ptr(), dq_f.data_ptr(), dk_f.data_ptr(), v_ptr, QKV, S, N,
                                    Hq, Hkv, hd, float(scale), d_score.data_ptr(), dgrad.data_ptr(), QKV, None) == 0
-    assert lib.b200_qk_norm_rope_bwd(dgrad.data_ptr(), dqkv_in.data_ptr(), QKV, dqg.data_ptr(), dkg.data_ptr(),
+    assert lib.b200_qk_norm_rope_bwd(dgrad.data_ptr(), dqkv_in.data_ptr(), QKV, QKV, dqg.data_ptr(), dkg.data_ptr(),
                                      dfr.data_ptr(), M, N, Hq, Hkv, hd, eps, None) == 0
     assert sc.rel_err(host(dgrad), dqkv_want) < 5e-5
 
@@ -203,15 +204,17 @@ def test_silu_lora_add_softmax_ce(lib):
     dg, du = o.silu_mul_backward(dy, gu[:, :inter], gu[:, inter:])
     assert sc.rel_err(host(dd), np.concatenate([dg, du], axis=1)) < 1e-5
 
-    ld, col0, n_cols, R = 300, 40, 130, 16
-    y = rng.standard_normal((rows, ld)).astype(np.float32)
-    mid = rng.standard_normal((rows, R)).astype(np.float32)
-    B = rng.standard_normal((n_cols, R)).astype(np.float32)
-    dyy, dmid, dB = dev(y), dev(mid), dev(B)
-    assert lib.b200_lora_add(dyy.data_ptr(), ld, col0, n_cols, dmid.data_ptr(), dB.data_ptr(), R, 2.0, rows, None) == 0
-    want = y.copy()
-    want[:, col0:col0 + n_cols] += 2.0 * (mid @ B.T)
-    assert sc.rel_err(host(dyy), want) < 1e-5
+    for R in (16, 8, 40):                       # ranks below the kernel's register tile read no stale shared memory
+        ld, col0, n_cols = 300, 40, 130
+        y = rng.standard_normal((rows, ld)).astype(np.float32)
+        mid = rng.standard_normal((rows, R + 3)).astype(np.float32)          # strided rows
+        B = rng.standard_normal((n_cols, R)).astype(np.float32)
+        dyy, dmid, dB = dev(y), dev(mid), dev(B)
+        assert lib.b200_lora_add(dyy.data_ptr(), ld, col0, n_cols, dmid.data_ptr(), R + 3, dB.data_ptr(), R, 2.0, rows,
+                                 None) == 0
+        want = y.copy()
+        want[:, col0:col0 + n_cols] += 2.0 * (mid[:, :R] @ B.T)
+        assert sc.rel_err(host(dyy), want) < 1e-5
 
     V = 5000
     logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
