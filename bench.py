@@ -45,6 +45,17 @@ WORKLOADS = {
     "tiny-qwen3-q8": ("tiny-qwen3", 0, 16, 32, 64),
 }
 HBM_FALLBACK_GBS = 6650.0
+
+# Libraries (NCCL's version banner, the engine's progress lines) write to file descriptor 1 too; the
+# contract is ONE JSON line on stdout, so everything else is sent to stderr and the line goes to the
+# original descriptor.
+_JSON_FD = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(text):
+    os.write(_JSON_FD, (text + "\n").encode())
+
 GATEUP_TRAFFIC_BYTES = 53_014_700
 
 
@@ -301,7 +312,7 @@ def sft_main(args, rank, local_rank, world):
         if rank != 0:
             return 0
         cb = sft_cpu_port_sample(sp, seq, lrank, alpha)
-        print(json.dumps({"impl": "reference", "metric": "sft_tokens_per_s", "value": cb["value"], "unit": "tok/s",
+        emit(json.dumps({"impl": "reference", "metric": "sft_tokens_per_s", "value": cb["value"], "unit": "tok/s",
                           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
                           "ms_per_step": 1000.0 * seq / cb["value"], "higher_is_better": True, "scaling": "weak",
                           "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "cpu_baseline": cb,
@@ -437,7 +448,7 @@ def sft_main(args, rank, local_rank, world):
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line))
+        emit(json.dumps(line))
     return 0
 
 
@@ -482,7 +493,7 @@ def main():
                 "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
-        print(json.dumps(line))
+        emit(json.dumps(line))
         return 0
 
     import torch
@@ -613,7 +624,7 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line))
+        emit(json.dumps(line))
     return 0
 
 
