@@ -9,7 +9,7 @@
 // core reads them as TF32 (10-bit mantissa): weights holding binary16 values
 // are exact, activations are rounded once per product, accumulation is fp32.
 //
-// Structure per CTA (one 128 x BN output tile, 192 threads):
+// Structure per CTA (one 128 x bn output tile, bn chosen per launch; 192 threads):
 //   warp 0      producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle) of a 128 x 32 A tile and a
 //               BN x 32 B tile per stage into a ring guarded by full/empty mbarriers
 //   warp 1      allocates BN columns of tensor memory; one lane issues tcgen05.mma
@@ -22,6 +22,8 @@
 #include "../../include/llmb200_train_kernels.h"
 
 #include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
 
 extern unsigned long long g_b200_launches;
 
@@ -38,7 +40,29 @@ struct EpiArgs {
     int M, N, K;
     float alpha;
     unsigned *d_err;
+    int bn;            // columns of the output tile = N of one tcgen05.mma (a multiple of 16, 64..256)
+    int stages;        // ring slots
+    int tmem_cols;     // tensor-memory columns to allocate: the power of two >= bn
+    int ksub;          // 32-element k sub-tiles per ring slot (each its own 128-byte-swizzled block)
+    int splits;        // CTAs sharing one output tile along k (gridDim.z); 1 = none
+    unsigned *flags;   // one turn counter per output tile, zero between launches
 };
+
+// Turn counters of the serial split-k epilogue (see the kernel): one word per output tile.
+constexpr int MAX_SPLIT_TILES = 1024;
+__device__ unsigned g_split_flags[MAX_SPLIT_TILES];
+
+// Timeline of CTA (0,0,0) of the last launch, in globaltimer nanoseconds: 0 start, 1 first operands landed,
+// 2 accumulator complete, 3 this CTA's turn to store (split-k), 4 epilogue done. Diagnostics only.
+__device__ unsigned long long g_gemm_trace[8];
+__device__ __forceinline__ unsigned long long now_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+constexpr int MAX_STAGES = 8;
 
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
 {
@@ -94,13 +118,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, unsigned parity, vo
     return false;
 }
 
-template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const EpiArgs p)
 {
-    constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t A_BYTES = BM * BK * 4;
+    const int BN = p.bn, STAGES = p.stages;
+    const int KSUB = p.ksub;
+    const uint32_t B_BYTES = (uint32_t)BN * BK * 4;                                     // both multiples of 1024
+    const uint32_t STAGE_BYTES = (A_BYTES + B_BYTES) * KSUB;                            // [A_0 .. A_ksub-1][B_0 .. B_ksub-1]
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_bar;
     __shared__ uint32_t tmem_base_sh;
     __shared__ int abort_sh;
 
@@ -108,10 +135,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-    const int nkb = (p.K + BK - 1) / BK;
+    // k-blocks of this CTA: the whole contraction, or its share when several CTAs split one tile along k
+    const int nkb_all = (p.K + BK * KSUB - 1) / (BK * KSUB);
+    const int per_split = (nkb_all + p.splits - 1) / p.splits;
+    const int kb0 = blockIdx.z * per_split;
+    const int nkb = min(per_split, nkb_all - kb0);               // > 0: the host never launches an empty split
     volatile int *abort_flag = &abort_sh;
+    const bool traced = (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
 
     if (threadIdx.x == 0) {
+        if (traced) g_gemm_trace[0] = now_ns();
         abort_sh = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
@@ -119,7 +152,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_sh)), "r"((uint32_t)BN) : "memory");
+                     ::"r"(smem_u32(&tmem_base_sh)), "r"((uint32_t)p.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -135,10 +168,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!*abort_flag) { *abort_flag = 1; if (p.d_err) atomicExch(p.d_err, 0x7101u); }
                     break;
                 }
-                uint8_t *a_dst = tiles + (size_t)s * STAGE_BYTES, *b_dst = a_dst + A_BYTES;
+                uint8_t *a_dst = tiles + (size_t)s * STAGE_BYTES, *b_dst = a_dst + A_BYTES * KSUB;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kb * BK, m0, &full_bar[s]);
-                tma_load_2d(b_dst, &map_b, kb * BK, n0, &full_bar[s]);
+                for (int u = 0; u < KSUB; ++u) {     // a sub-tile past the end of k is all fill (zeros)
+                    const int x = ((kb0 + kb) * KSUB + u) * BK;
+                    tma_load_2d(a_dst + (size_t)u * A_BYTES, &map_a, x, m0, &full_bar[s]);
+                    tma_load_2d(b_dst + (size_t)u * B_BYTES, &map_b, x, n0, &full_bar[s]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -154,11 +190,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
-                const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(b_addr);
+                if (traced && kb == 0) g_gemm_trace[1] = now_ns();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES * KSUB;
+                for (int u = 0; u < KSUB; ++u) {
+                    const uint64_t adesc = smem_desc_sw128(a_addr + u * A_BYTES), bdesc = smem_desc_sw128(b_addr + u * B_BYTES);
 #pragma unroll
-                for (int j = 0; j < BK / UMMA_K; ++j)           // 32 bytes along k per step: +2 in 16-byte units
-                    umma_tf32(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+                    for (int j = 0; j < BK / UMMA_K; ++j)       // 32 bytes along k per step: +2 in 16-byte units
+                        umma_tf32(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | u | j) != 0);
+                }
                 umma_commit(&empty_bar[s]);                     // slot reusable once these MMAs have read it
             }
             if (ok) umma_commit(&acc_bar);                      // accumulator complete
@@ -173,23 +212,50 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (lane == 0 && !*abort_flag) { *abort_flag = 1; if (p.d_err) atomicExch(p.d_err, 0x7103u); }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (traced && threadIdx.x == 64) g_gemm_trace[2] = now_ns();
+            // Serial split-k: the CTAs of a tile add their partial sums into C one after the other, in split
+            // order (deterministic), handing over through a turn counter. All of them are resident at once
+            // (the host keeps tiles * splits <= SMs), so the wait cannot deadlock; it is bounded anyway.
+            const int split = blockIdx.z;
+            unsigned *turn = p.flags + (blockIdx.y * gridDim.x + blockIdx.x);
+            if (p.splits > 1 && split > 0) {
+                bool mine = true;
+                if (lane == 0) {
+                    mine = false;
+                    for (int it = 0; it < (1 << 22); ++it) {
+                        unsigned v;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(turn) : "memory");
+                        if (v == (unsigned)split) { mine = true; break; }
+                        if ((it & 63) == 63 && *abort_flag) break;
+                    }
+                }
+                mine = __shfl_sync(0xffffffffu, mine, 0);
+                if (!mine) {
+                    if (lane == 0 && !*abort_flag) { *abort_flag = 1; if (p.d_err) atomicExch(p.d_err, 0x7104u); }
+                    ok = false;
+                }
+            }
+            if (traced && threadIdx.x == 64) g_gemm_trace[3] = now_ns();
+            const bool first = split == 0;
             float *crow = p.C + (long long)row * p.ldc;
-            const float *rrow = p.R ? p.R + (long long)row * p.ldr : nullptr;
+            // split 0 adds the residual; later splits add what is already in C
+            const float *rrow = !first ? crow : p.R ? p.R + (long long)row * p.ldr : nullptr;
             const bool vec = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                              (!p.R || (((p.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0)));
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int c = 0; ok && c < BN; c += 32) {
                 if (n0 + c >= p.N) break;                       // uniform across the warp
+                const int cw = min(32, BN - c);                 // columns of this chunk that belong to the tile
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c, r);
                 if (row < p.M) {
-                    if (vec && n0 + c + 32 <= p.N) {
+                    if (vec && cw == 32 && n0 + c + 32 <= p.N) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
                             float4 v = make_float4(p.alpha * __uint_as_float(r[j]), p.alpha * __uint_as_float(r[j + 1]),
                                                    p.alpha * __uint_as_float(r[j + 2]), p.alpha * __uint_as_float(r[j + 3]));
                             if (rrow) {
-                                const float4 q = *reinterpret_cast<const float4 *>(rrow + n0 + c + j);
+                                const float4 q = __ldcg(reinterpret_cast<const float4 *>(rrow + n0 + c + j));
                                 v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
                             }
                             *reinterpret_cast<float4 *>(crow + n0 + c + j) = v;
@@ -198,14 +264,26 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int n = n0 + c + j;
-                            if (n < p.N) {
+                            if (j < cw && n < p.N) {
                                 float v = p.alpha * __uint_as_float(r[j]);
-                                if (rrow) v += rrow[n];
+                                if (rrow) v += __ldcg(rrow + n);
                                 crow[n] = v;
                             }
                         }
                     }
                 }
+            }
+        }
+        if (traced && threadIdx.x == 64) g_gemm_trace[4] = now_ns();
+        if (p.splits > 1) {
+            // every epilogue warp comes here on every path, so the barrier always has its 128 threads
+            named_barrier(1, 128);                              // the four warps have stored their rows
+            if (threadIdx.x == 64 && !*abort_flag) {
+                __threadfence();
+                const int split = blockIdx.z;
+                unsigned *turn = p.flags + (blockIdx.y * gridDim.x + blockIdx.x);
+                const unsigned next = split + 1 == p.splits ? 0u : (unsigned)(split + 1);
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(turn), "r"(next) : "memory");
             }
         }
     }
@@ -219,7 +297,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
     }
 }
 
@@ -258,19 +336,74 @@ bool make_map(CUtensorMap *map, const float *base, long long rows, long long K, 
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES>
-int launch(const CUtensorMap &ma, const CUtensorMap &mb, const EpiArgs &e, cudaStream_t st)
+int sm_count_tc()
 {
-    constexpr size_t smem = (size_t)STAGES * (BM + BN) * BK * 4 + 1024;
-    static bool set = false;
-    if (!set) {
-        cudaError_t rc = cudaFuncSetAttribute(gemm_tf32_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)smem);
-        if (rc != cudaSuccess) return (int)rc;
-        set = true;
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
     }
-    dim3 grid((e.M + BM - 1) / BM, (e.N + BN - 1) / BN);
-    gemm_tf32_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, e);
+    return n;
+}
+
+// Tile choice, from measurements on B200. A CTA stages (128 + bn) * 128 bytes per 32 elements of k; an SM
+// takes them in at <= ~117 GB/s (its 64 B/clk L2 port) and all SMs together at <= ~12 TB/s, and that, not
+// the tensor pipe, bounds the kernel -- fewer bytes per flop (wide tiles) win as long as the tiles fill the
+// machine.
+//  * 128-wide tiles fit in one wave: take them, with two k sub-tiles per ring slot (three 64 KB slots
+//    hide the per-slot hand-over better than six 32 KB ones: 0.27 us instead of 0.40 us per 32 of k).
+//    With a very long contraction on top (the LM-head backward, K = vocabulary), three CTAs split a
+//    256-wide tile along k; their epilogues run one after the other, which only pays when k is long.
+//  * otherwise the width (a multiple of 16 up to 256) that minimises waves * (128 + bn).
+void pick_tile(int M, int N, int K, int *bn_out, int *ksub_out, int *splits_out)
+{
+    const int mt = (M + BM - 1) / BM, sms = sm_count_tc(), nkb = (K + BK - 1) / BK;
+    *splits_out = 1;
+    if ((long long)mt * ((N + 127) / 128) <= sms) {
+        const long long tiles256 = (long long)mt * ((N + 255) / 256);
+        if (nkb >= 1024 && tiles256 * 3 <= sms && tiles256 <= MAX_SPLIT_TILES) {
+            *bn_out = 256; *ksub_out = 1; *splits_out = 3;
+        } else {
+            *bn_out = 128; *ksub_out = 2;
+        }
+        return;
+    }
+    long long best = -1;
+    for (int bn = 144; bn <= 256; bn += 16) {
+        const long long tiles = (long long)mt * ((N + bn - 1) / bn);
+        const long long cost = ((tiles + sms - 1) / sms) * (BM + bn);
+        if (best < 0 || cost < best || (cost == best && bn > *bn_out)) { best = cost; *bn_out = bn; }
+    }
+    *ksub_out = 1;
+}
+
+int launch(const CUtensorMap &ma, const CUtensorMap &mb, EpiArgs e, cudaStream_t st)
+{
+    static int ksub_env = -1;
+    if (ksub_env < 0) {
+        const char *t = getenv("LLMB200_GEMM_KSUB");
+        ksub_env = t ? atoi(t) : 0;
+        if (ksub_env < 0 || ksub_env > 4) ksub_env = 0;
+    }
+    if (ksub_env) e.ksub = ksub_env;
+    while (e.ksub > 1 && (size_t)(BM + e.bn) * BK * 4 * e.ksub * 2 > 200 * 1024) --e.ksub;
+    const size_t stage = (size_t)(BM + e.bn) * BK * 4 * e.ksub;
+    int stages = (int)((200 * 1024) / stage);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) return B200_E_UNSUPPORTED;
+    e.stages = stages;
+    e.tmem_cols = e.bn <= 64 ? 64 : e.bn <= 128 ? 128 : 256;
+    const size_t smem = stage * stages + 1024;
+    static size_t attr_set = 0;
+    if (smem > attr_set) {
+        cudaError_t rc = cudaFuncSetAttribute(gemm_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (rc != cudaSuccess) return (int)rc;
+        attr_set = smem;
+    }
+    if (cudaGetSymbolAddress((void **)&e.flags, g_split_flags) != cudaSuccess) return B200_E_UNSUPPORTED;
+    dim3 grid((e.M + BM - 1) / BM, (e.N + e.bn - 1) / e.bn, e.splits);
+    gemm_tf32_kernel<<<grid, GEMM_THREADS, smem, st>>>(ma, mb, e);
     ++g_b200_launches;
     return (int)cudaGetLastError();
 }
@@ -285,11 +418,29 @@ extern "C" int b200_gemm_tf32(const b200_gemm_args *a, void *stream)
     if ((a->K & 3) || (lda & 3) || (ldb & 3) || lda < a->K || ldb < a->K) return B200_E_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15)) return B200_E_UNSUPPORTED;
     if (a->N < 64 || a->M < 16) return B200_E_UNSUPPORTED;        // the CUDA-core kernel is the better fit
-    if ((a->M + BM - 1) / BM > 2147483647 || (a->N + 127) / 128 > 65535) return B200_E_UNSUPPORTED;
+    if ((a->N + 63) / 64 > 65535) return B200_E_UNSUPPORTED;
 
     CUtensorMap ma, mb;
-    EpiArgs e = {a->C, a->ldc, a->R, a->ldr, a->M, a->N, a->K, a->alpha, a->d_err};
+    EpiArgs e = {a->C, a->ldc, a->R, a->ldr, a->M, a->N, a->K, a->alpha, a->d_err, 128, 0, 0, 1, 1, nullptr};
     if (!make_map(&ma, a->A, a->M, a->K, lda, BM)) return B200_E_UNSUPPORTED;
-    if (!make_map(&mb, a->B, a->N, a->K, ldb, 128)) return B200_E_UNSUPPORTED;
-    return launch<128, 6>(ma, mb, e, (cudaStream_t)stream);
+    // LLMB200_GEMM_BN=<n> overrides the tile width for experiments
+    static int forced = -1;
+    if (forced < 0) {
+        const char *t = getenv("LLMB200_GEMM_BN");
+        forced = t ? atoi(t) : 0;
+        if (forced < 0 || forced > 256 || (forced % 16)) forced = 0;
+    }
+    pick_tile(a->M, a->N, a->K, &e.bn, &e.ksub, &e.splits);
+    if (forced >= 64) { e.bn = forced; e.splits = 1; }
+    if (!make_map(&mb, a->B, a->N, a->K, ldb, e.bn)) return B200_E_UNSUPPORTED;
+    return launch(ma, mb, e, (cudaStream_t)stream);
+}
+
+// Diagnostics: the timeline of CTA (0,0,0) of the last launch (see g_gemm_trace). Synchronises the device.
+extern "C" int b200_gemm_tf32_trace(unsigned long long *out8)
+{
+    if (!out8) return B200_E_BADARG;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out8, g_gemm_trace, 8 * sizeof(unsigned long long));
+    return (int)e;
 }

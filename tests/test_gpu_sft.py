@@ -58,7 +58,11 @@ def test_gemm_f32_all_orientations(pkg, lib, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 32), (128, 128, 256), (70, 200, 100), (512, 384, 1024), (64, 640, 2560),
-                                   (300, 64, 36)])
+                                   (300, 64, 36),
+                                   # tile widths the wave-aware choice picks for the SFT shapes: 80, 176, 112, 144
+                                   (512, 2560, 128), (512, 6176, 64), (512, 4096, 96), (512, 9728, 32),
+                                   # few tiles: several CTAs split a tile along k and add in turn (3 and 8 splits)
+                                   (512, 2560, 4096), (128, 256, 2048), (100, 300, 1000)])
 def test_gemm_tf32_tensor_cores(pkg, lib, M, N, K):
     """A = activations (rounded to TF32 by the tensor core), B = weights holding binary16 values
     (exact in TF32): the error is that of rounding A once, ~2^-11 relative per product."""
