@@ -94,7 +94,8 @@ int b200_attn_train_fwd(const float *q, const float *k, const float *v, long lon
                         int n_q, int n_kv, int hd, float scale, float *probs, float *out, void *stream);
 /* attn_bwd_dq (:857-925), attn_bwd_dkv (:931-968) and repeat_kv_bwd (:973-992):
  * d_out [rows, n_q*hd] -> dq, dk, dv written into the q, k, v column blocks of
- * dqkv [rows, ld]. d_score [S, n_q, N, N] is scratch. */
+ * dqkv [rows, ld]. d_score is scratch of S*n_q*N*max(N, 2*hd) floats (the
+ * score gradients, or per-head dK/dV partial sums for short sequences). */
 int b200_attn_train_bwd(const float *d_out, const float *probs, const float *q, const float *k, const float *v,
                         long long v_ld, int n_seq, int seq_len, int n_q, int n_kv, int hd, float scale,
                         float *d_score, float *dqkv, long long ld, void *stream);

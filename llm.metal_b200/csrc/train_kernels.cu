@@ -350,6 +350,242 @@ attn_bwd_dkv_kernel(const float *d_score, const float *probs, const float *q, co
     for (int c = 0; c < PER; ++c) { dkr[l + 32 * c] = dk[c]; dvr[l + 32 * c] = dv[c]; }
 }
 
+// ---- causal attention for short sequences (N <= 64): one block per (sequence, head) ----------------
+// The whole 64 x 64 score tile of a head lives in shared memory and every product is a register-tiled
+// shared-memory matmul (256 threads, 4 x 4 or 4 x HD/16 outputs each) instead of one warp walking the keys.
+// Same arithmetic as the per-query kernels above (fp32 FMA, softmax with max subtraction).
+constexpr int AT = 64;            // tile edge: queries and keys
+constexpr int ATP = AT + 4;       // padded row of a transposed operand (keeps float4 reads aligned)
+
+// dst[d][i] = src[i][d] for i < n (zero beyond), src rows `ld` floats apart. HD columns.
+template <int HD>
+__device__ __forceinline__ void load_transposed(float *dst, const float *src, long long ld, int n)
+{
+    for (int e = threadIdx.x; e < AT * HD; e += blockDim.x) {
+        const int i = e / HD, d = e % HD;
+        dst[d * ATP + i] = i < n ? src[(size_t)i * ld + d] : 0.f;
+    }
+}
+template <int HD>
+__device__ __forceinline__ void load_rows(float *dst, const float *src, long long ld, int n)
+{
+    for (int e = threadIdx.x; e < AT * HD; e += blockDim.x) {
+        const int i = e / HD, d = e % HD;
+        dst[i * HD + d] = i < n ? src[(size_t)i * ld + d] : 0.f;
+    }
+}
+
+// acc[a][b] = sum_d At[d][4*ty + a] * Bt[d][4*tx + b]   (both operands transposed, ATP-padded)
+template <int HD>
+__device__ __forceinline__ void tile_abt(const float *At, const float *Bt, int ty, int tx, float (&acc)[4][4])
+{
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+#pragma unroll 4
+    for (int d = 0; d < HD; ++d) {
+        const float4 av = *reinterpret_cast<const float4 *>(At + d * ATP + 4 * ty);
+        const float4 bv = *reinterpret_cast<const float4 *>(Bt + d * ATP + 4 * tx);
+        const float a4[4] = {av.x, av.y, av.z, av.w}, b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(a4[a], b4[b], acc[a][b]);
+    }
+}
+
+// out[4*ty + a][CW*tx + c] = sum_j W(j, 4*ty + a) * B[j][CW*tx + c], j < n; W(j, r) = Wm[r*ATP + j] when
+// !WT (the weight matrix is indexed [row][j]) or Wm[j*ATP + r] when WT (indexed [j][row]). B row-major [AT][HD].
+template <int HD, bool WT>
+__device__ __forceinline__ void tile_wb(const float *Wm, const float *B, int n, int ty, int tx, float (&acc)[4][HD / 16])
+{
+    constexpr int CW = HD / 16;
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < CW; ++c) acc[a][c] = 0.f;
+    for (int j = 0; j < n; ++j) {
+        float w[4];
+        if (WT) {
+            const float4 wv = *reinterpret_cast<const float4 *>(Wm + j * ATP + 4 * ty);
+            w[0] = wv.x; w[1] = wv.y; w[2] = wv.z; w[3] = wv.w;
+        } else {
+#pragma unroll
+            for (int a = 0; a < 4; ++a) w[a] = Wm[(4 * ty + a) * ATP + j];
+        }
+        float bv[CW];
+#pragma unroll
+        for (int c4 = 0; c4 < CW / 4; ++c4) {
+            const float4 t = *reinterpret_cast<const float4 *>(B + j * HD + CW * tx + 4 * c4);
+            bv[4 * c4] = t.x; bv[4 * c4 + 1] = t.y; bv[4 * c4 + 2] = t.z; bv[4 * c4 + 3] = t.w;
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < CW; ++c) acc[a][c] = fmaf(w[a], bv[c], acc[a][c]);
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256)
+attn_fwd_tile_kernel(const float *q, const float *k, const float *v, long long v_ld, int N, int n_q, int n_kv,
+                     float scale, float *probs, float *out)
+{
+    extern __shared__ __align__(16) float sh[];
+    float *Qt = sh, *Kt = Qt + HD * ATP, *Vs = Kt + HD * ATP, *P = Vs + AT * HD;     // P [AT][ATP]
+    const int h = blockIdx.x % n_q, s = blockIdx.x / n_q, kvh = h / (n_q / n_kv);
+    const size_t row0 = (size_t)s * N;
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    load_transposed<HD>(Qt, q + (row0 * n_q + h) * HD, (long long)n_q * HD, N);
+    load_transposed<HD>(Kt, k + (row0 * n_kv + kvh) * HD, (long long)n_kv * HD, N);
+    load_rows<HD>(Vs, v + row0 * v_ld + (size_t)kvh * HD, v_ld, N);
+    __syncthreads();
+    float acc[4][4];
+    tile_abt<HD>(Qt, Kt, ty, tx, acc);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = 4 * ty + a, j = 4 * tx + b;
+            P[i * ATP + j] = (j <= i && i < N) ? acc[a][b] * scale : -1e30f;
+        }
+    __syncthreads();
+    {   // softmax: four threads per row, 16 columns each
+        const int i = threadIdx.x / 4, part = threadIdx.x % 4;
+        float *pr = P + i * ATP + 16 * part;
+        float mx = -1e30f;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) mx = fmaxf(mx, pr[c]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        float e[16], sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const int j = 16 * part + c;
+            e[c] = (j <= i && i < N) ? expf(pr[c] - mx) : 0.f;
+            sum += e[c];
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float inv = i < N ? 1.0f / sum : 0.f;
+        float *gp = probs + (((size_t)s * n_q + h) * N + i) * N;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const int j = 16 * part + c;
+            const float p = e[c] * inv;
+            pr[c] = p;
+            if (i < N && j < N) gp[j] = p;
+        }
+    }
+    __syncthreads();
+    float o[4][HD / 16];
+    tile_wb<HD, false>(P, Vs, N, ty, tx, o);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = 4 * ty + a;
+        if (i >= N) continue;
+        float *dst = out + ((row0 + i) * n_q + h) * HD + (HD / 16) * tx;
+#pragma unroll
+        for (int c = 0; c < HD / 16; ++c) dst[c] = o[a][c];
+    }
+}
+
+// Backward of one (sequence, head): dq into dqkv, this head's dK and dV into part[s][h][N][2][HD].
+template <int HD>
+__global__ void __launch_bounds__(256)
+attn_bwd_tile_kernel(const float *d_out, const float *probs, const float *q, const float *k, const float *v,
+                     long long v_ld, int N, int n_q, int n_kv, float scale, float *dqkv, long long ld, float *part)
+{
+    extern __shared__ __align__(16) float sh[];
+    float *dOt = sh, *Vt = dOt + HD * ATP, *dOs = Vt + HD * ATP, *Ks = dOs + AT * HD, *Qs = Ks + AT * HD;
+    float *P = Qs + AT * HD, *dS = P + AT * ATP;
+    const int h = blockIdx.x % n_q, s = blockIdx.x / n_q, kvh = h / (n_q / n_kv);
+    const size_t row0 = (size_t)s * N;
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+    const float *dop = d_out + (row0 * n_q + h) * HD;
+    load_transposed<HD>(dOt, dop, (long long)n_q * HD, N);
+    load_rows<HD>(dOs, dop, (long long)n_q * HD, N);
+    load_transposed<HD>(Vt, v + row0 * v_ld + (size_t)kvh * HD, v_ld, N);
+    load_rows<HD>(Ks, k + (row0 * n_kv + kvh) * HD, (long long)n_kv * HD, N);
+    load_rows<HD>(Qs, q + (row0 * n_q + h) * HD, (long long)n_q * HD, N);
+    const float *gp = probs + ((size_t)s * n_q + h) * N * N;
+    for (int e = threadIdx.x; e < AT * AT; e += blockDim.x) {
+        const int i = e / AT, j = e % AT;
+        P[i * ATP + j] = (i < N && j < N) ? gp[(size_t)i * N + j] : 0.f;
+    }
+    __syncthreads();
+    float acc[4][4];
+    tile_abt<HD>(dOt, Vt, ty, tx, acc);                       // d_raw[i][j] = dO_i . V_j
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = 4 * ty + a, j = 4 * tx + b;
+            dS[i * ATP + j] = (j <= i && i < N) ? acc[a][b] : 0.f;
+        }
+    __syncthreads();
+    {   // d_score = p * (d_raw - sum_k p_k d_raw_k) * scale, four threads per row
+        const int i = threadIdx.x / 4, part4 = threadIdx.x % 4;
+        float *dr = dS + i * ATP + 16 * part4;
+        const float *pr = P + i * ATP + 16 * part4;
+        float dp = 0.f;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) dp = fmaf(pr[c], dr[c], dp);
+        dp += __shfl_xor_sync(0xffffffffu, dp, 1);
+        dp += __shfl_xor_sync(0xffffffffu, dp, 2);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) dr[c] = pr[c] * (dr[c] - dp) * scale;     // p is zero above the diagonal
+    }
+    __syncthreads();
+    float o[4][HD / 16];
+    tile_wb<HD, false>(dS, Ks, N, ty, tx, o);                 // dQ_i = sum_j dS[i][j] K_j
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = 4 * ty + a;
+        if (i >= N) continue;
+        float *dst = dqkv + (row0 + i) * ld + (size_t)h * HD + (HD / 16) * tx;
+#pragma unroll
+        for (int c = 0; c < HD / 16; ++c) dst[c] = o[a][c];
+    }
+    float *pk = part + (((size_t)s * n_q + h) * N) * 2 * HD;
+    tile_wb<HD, true>(dS, Qs, N, ty, tx, o);                  // dK_j = sum_i dS[i][j] Q_i
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int j = 4 * ty + a;
+        if (j >= N) continue;
+#pragma unroll
+        for (int c = 0; c < HD / 16; ++c) pk[(size_t)j * 2 * HD + (HD / 16) * tx + c] = o[a][c];
+    }
+    tile_wb<HD, true>(P, dOs, N, ty, tx, o);                  // dV_j = sum_i P[i][j] dO_i
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int j = 4 * ty + a;
+        if (j >= N) continue;
+#pragma unroll
+        for (int c = 0; c < HD / 16; ++c) pk[(size_t)j * 2 * HD + HD + (HD / 16) * tx + c] = o[a][c];
+    }
+}
+
+// dK, dV of a KV head = sum over its query heads in head order (repeat_kv_bwd), into the k and v blocks of dqkv.
+__global__ void attn_bwd_reduce_kernel(const float *part, int n_seq, int N, int n_q, int n_kv, int hd, float *dqkv,
+                                       long long ld)
+{
+    const int G = n_q / n_kv;
+    const size_t total = (size_t)n_seq * N * n_kv * 2 * hd;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(e % hd);
+        const int which = (int)((e / hd) % 2);
+        const int kvh = (int)((e / (2 * hd)) % n_kv);
+        const size_t row = e / ((size_t)2 * hd * n_kv);            // s*N + j
+        const int s = (int)(row / N), j = (int)(row % N);
+        float sum = 0.f;
+        for (int g = 0; g < G; ++g)
+            sum += part[((((size_t)s * n_q + kvh * G + g) * N + j) * 2 + which) * hd + d];
+        dqkv[row * ld + (size_t)(n_q + (which ? n_kv : 0) + kvh) * hd + d] = sum;
+    }
+}
+
 // ---- SwiGLU ------------------------------------------------------------------------------------
 __global__ void silu_mul_rows_kernel(const float *gu, int inter, float *act, size_t total)
 {
@@ -634,6 +870,13 @@ template <int HD>
 static int attn_fwd_launch(const float *q, const float *k, const float *v, long long v_ld, int n_seq, int N, int n_q,
                            int n_kv, float scale, float *probs, float *out, cudaStream_t st)
 {
+    if constexpr (HD <= 128) if (N <= AT) {                   // short sequences: one block per (sequence, head)
+        const size_t tsm = ((size_t)2 * HD * ATP + (size_t)AT * HD + (size_t)AT * ATP) * sizeof(float);
+        int rc = opt_in_smem(attn_fwd_tile_kernel<HD>, tsm);
+        if (rc) return rc;
+        attn_fwd_tile_kernel<HD><<<n_seq * n_q, 256, tsm, st>>>(q, k, v, v_ld, N, n_q, n_kv, scale, probs, out);
+        return done();
+    }
     const size_t smem = (size_t)ATT_WARPS * (HD + N) * sizeof(float);
     int rc = opt_in_smem(attn_train_fwd_kernel<HD>, smem);
     if (rc) return rc;
@@ -660,6 +903,20 @@ static int attn_bwd_launch(const float *d_out, const float *probs, const float *
                            long long v_ld, int n_seq, int N, int n_q, int n_kv, float scale, float *d_score,
                            float *dqkv, long long ld, cudaStream_t st)
 {
+    if constexpr (HD <= 128) if (N <= AT) {
+        // d_score is used as the per-head dK/dV scratch [S][n_q][N][2][HD] here
+        const size_t tsm = ((size_t)2 * HD * ATP + (size_t)3 * AT * HD + (size_t)2 * AT * ATP) * sizeof(float);
+        int rc = opt_in_smem(attn_bwd_tile_kernel<HD>, tsm);
+        if (rc) return rc;
+        attn_bwd_tile_kernel<HD><<<n_seq * n_q, 256, tsm, st>>>(d_out, probs, q, k, v, v_ld, N, n_q, n_kv, scale, dqkv, ld,
+                                                                d_score);
+        rc = done();
+        if (rc) return rc;
+        const size_t total = (size_t)n_seq * N * n_kv * 2 * HD;
+        const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+        attn_bwd_reduce_kernel<<<grid, 256, 0, st>>>(d_score, n_seq, N, n_q, n_kv, HD, dqkv, ld);
+        return done();
+    }
     const size_t smem = (size_t)ATT_WARPS * (HD + N) * sizeof(float);
     int rc = opt_in_smem(attn_bwd_dq_kernel<HD>, smem);
     if (rc) return rc;

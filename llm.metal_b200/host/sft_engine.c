@@ -290,7 +290,7 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->d_lnx = dalloc(s, (size_t)M * (s->D + s->XR));
     s->d_act = dalloc(s, (size_t)M * s->IS); s->d_gu = dalloc(s, (size_t)M * 2 * s->IS);
     s->d_att = dalloc(s, (size_t)M * s->Hq_hd); s->dqkv = dalloc(s, (size_t)M * s->QKV);
-    s->d_score = dalloc(s, (size_t)s->S * s->Hq * s->N * s->N);
+    s->d_score = dalloc(s, (size_t)s->S * s->Hq * s->N * (s->N > 2 * s->hd ? s->N : 2 * s->hd));
     s->tokens = (uint32_t *)dalloc(s, M); s->targets = (uint32_t *)dalloc(s, M);
     s->partials = (double *)dalloc(s, 2 * N_PARTIALS);
     s->d_norm = dalloc(s, 2);                 /* [0] gradient norm, [1] error word of the tensor-core products */

@@ -132,10 +132,11 @@ def test_rms_norm_rows_forward_and_backward(lib, rows, dim):
     assert sc.rel_err(host(dacc), np.clip(o.rms_norm_backward(x, dy, g, eps), -0.5, 0.5)) < 1e-5
 
 
-@pytest.mark.parametrize("hd", [64, 128, 256])
-def test_qk_norm_rope_and_attention(lib, hd):
-    rng = np.random.default_rng(hd)
-    S, N, Hq, Hkv, eps, theta = 2, 9, 4, 2, 1e-6, 1e6
+@pytest.mark.parametrize("hd,N", [(64, 9), (128, 9), (256, 9), (128, 64), (64, 33), (128, 70)])
+def test_qk_norm_rope_and_attention(lib, hd, N):
+    """N <= 64 with head_dim <= 128 takes the one-block-per-head kernels, the rest the per-query kernels."""
+    rng = np.random.default_rng(hd + N)
+    S, Hq, Hkv, eps, theta = 2, 4, 2, 1e-6, 1e6
     M, QKV = S * N, (Hq + 2 * Hkv) * hd
     qkv = rng.standard_normal((M, QKV)).astype(np.float32)
     qg = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
@@ -185,7 +186,7 @@ def test_qk_norm_rope_and_attention(lib, hd):
                                    probs.data_ptr(), out.data_ptr(), None) == 0
     assert np.abs(host(probs) - probs_want).max() < 2e-6
     assert sc.rel_err(host(out), out_want) < 2e-5
-    d_score = torch.zeros(S, Hq, N, N, device="cuda")
+    d_score = torch.zeros(S * Hq * N * max(N, 2 * hd), device="cuda")
     dgrad = torch.zeros(M, QKV, device="cuda")
     ddo = dev(d_out)
     assert lib.b200_attn_train_bwd(ddo.data_ptr(), probs.data_ptr(), dq_f.data_ptr(), dk_f.data_ptr(), v_ptr, QKV, S, N,
