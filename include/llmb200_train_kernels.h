@@ -120,6 +120,14 @@ int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid
 int b200_lora_pack(float *w_ext, float *wt_ext, const float *A_q, const float *B_q, const float *A_v,
                    const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc, void *stream);
 
+/* C(p, r) = alpha * sum_m X[m*ld_x + p] * Y[m*ld_y + r] for p < P, r < R <= 16
+ * (B200_E_UNSUPPORTED for wider ranks: use b200_gemm_f32),
+ * stored at C[p*c_p + r*c_r]: float_matmul_tn (:1070-1094) for the rank-R LoRA
+ * gradients dB = sc dY^T mid (c_p = R, c_r = 1) and dA = tmp^T ln1 (c_p = 1,
+ * c_r = P), src/nn/fast_sft.c:946-950, 961-965. Row order of the sum is fixed. */
+int b200_xty_skinny(const float *X, long long ld_x, const float *Y, long long ld_y, int rows, int P, int R,
+                    float alpha, float *C, long long c_p, long long c_r, void *stream);
+
 /* softmax_ce_train (:646-690) followed by scale_tensor(grad_scale):
  * losses[m] = logsumexp - logit[target]; dlogits = (softmax - onehot) * grad_scale. */
 int b200_softmax_ce_rows(const float *logits, const uint32_t *targets, int rows, int vocab, float grad_scale,

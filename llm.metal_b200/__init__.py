@@ -133,7 +133,7 @@ SYMBOLS_MAIN = {
     "llmb200_train_kernels.h": ["b200_gemm_f32", "b200_gemm_tf32", "b200_embed_rows", "b200_round_f16",
                                 "b200_transpose_f32", "b200_rms_norm_rows", "b200_rms_norm_bwd_rows",
                                 "b200_qk_norm_rope", "b200_qk_norm_rope_bwd", "b200_attn_train_fwd",
-                                "b200_attn_train_bwd", "b200_silu_mul_rows", "b200_silu_mul_bwd_rows", "b200_lora_add", "b200_lora_pack",
+                                "b200_attn_train_bwd", "b200_silu_mul_rows", "b200_silu_mul_bwd_rows", "b200_lora_add", "b200_lora_pack", "b200_xty_skinny",
                                 "b200_softmax_ce_rows", "b200_sumsq_partials", "b200_clip_adamw"],
     "llmb200_sft.h": ["sft_state_create", "sft_state_free", "sft_train_step", "forward_to_logits", "sft_backward",
                       "sft_get_logits", "sft_get_dlogits", "sft_get_x_cpu", "sft_get_losses_cpu", "sft_get_seq_len",
@@ -218,6 +218,7 @@ def lib():
         "b200_silu_mul_rows": (i, [vp, i, i, vp, vp]), "b200_silu_mul_bwd_rows": (i, [vp, vp, i, i, vp, vp]),
         "b200_lora_add": (i, [vp, ll, i, i, vp, ll, vp, i, fl, i, vp]),
         "b200_lora_pack": (i, [vp, vp, vp, vp, vp, vp, i, i, i, i, i, fl, vp]),
+        "b200_xty_skinny": (i, [vp, ll, vp, ll, i, i, i, fl, vp, ll, ll, vp]),
         "b200_softmax_ce_rows": (i, [vp, vp, i, i, fl, vp, vp, vp]),
         "b200_sumsq_partials": (i, [vp, sz, vp, i, vp]),
         "b200_clip_adamw": (i, [vp, vp, vp, vp, sz, vp, i, fl, fl, fl, fl, fl, fl, fl, fl, i, vp, vp]),

@@ -666,6 +666,73 @@ __global__ void lora_pack_kernel(float *w_ext, float *wt_ext, const float *A_q, 
     }
 }
 
+// ---- rank-R LoRA gradients: C(p, r) = alpha * sum_m X[m, p] * Y[m, r], X wide, Y narrow (R <= MAXR) ------
+// float_matmul_tn of the reference (shaders/q8_kernels.metal:1070-1094) for dB = sc * dY^T mid and
+// dA = tmp^T ln1 (src/nn/fast_sft.c:946-950, 961-965). A block owns 32 columns p; its eight warps take
+// every eighth row m and are summed in warp order through shared memory, so the result does not depend on
+// scheduling. A thread keeps its R sums in registers; the rows of Y are staged in shared memory 4096/MAXR
+// at a time and read as broadcasts; four X loads are in flight per thread.
+template <int MAXR>
+__global__ void __launch_bounds__(256)
+xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y, int rows, int P, int R, float alpha,
+                  float *C, long long c_p, long long c_r)
+{
+    constexpr int CH = 4096 / MAXR;                      // rows of Y per shared-memory chunk
+    __shared__ float ys[CH * MAXR];
+    __shared__ float red[7 * 32 * (MAXR + 1) > 4096 ? 1 : 7 * 32 * (MAXR + 1)];
+    static_assert(MAXR <= 16, "the cross-warp buffer is sized for MAXR <= 16");
+    const int pl = threadIdx.x & 31, mg = threadIdx.x >> 5;
+    const int p = blockIdx.x * 32 + pl;
+    const bool on = p < P;
+    float acc[MAXR];
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) acc[r] = 0.f;
+    for (int c0 = 0; c0 < rows; c0 += CH) {
+        const int cn = min(CH, rows - c0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < cn * MAXR; e += 256) {
+            const int m = e / MAXR, r = e % MAXR;
+            ys[e] = r < R ? Y[(size_t)(c0 + m) * ld_y + r] : 0.f;
+        }
+        __syncthreads();
+        if (on) {
+            int m = mg;
+            for (; m + 24 < cn; m += 32) {               // four rows of this warp in flight
+                const float x0 = X[(size_t)(c0 + m) * ld_x + p], x1 = X[(size_t)(c0 + m + 8) * ld_x + p];
+                const float x2 = X[(size_t)(c0 + m + 16) * ld_x + p], x3 = X[(size_t)(c0 + m + 24) * ld_x + p];
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r) {
+                    acc[r] = fmaf(x0, ys[m * MAXR + r], acc[r]);
+                    acc[r] = fmaf(x1, ys[(m + 8) * MAXR + r], acc[r]);
+                    acc[r] = fmaf(x2, ys[(m + 16) * MAXR + r], acc[r]);
+                    acc[r] = fmaf(x3, ys[(m + 24) * MAXR + r], acc[r]);
+                }
+            }
+            for (; m < cn; m += 8) {
+                const float x0 = X[(size_t)(c0 + m) * ld_x + p];
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r) acc[r] = fmaf(x0, ys[m * MAXR + r], acc[r]);
+            }
+        }
+    }
+    if (mg > 0) {
+#pragma unroll
+        for (int r = 0; r < MAXR; ++r) red[((mg - 1) * 32 + pl) * (MAXR + 1) + r] = acc[r];
+    }
+    __syncthreads();
+    if (mg == 0 && on) {
+#pragma unroll
+        for (int r = 0; r < MAXR; ++r) {
+            if (r < R) {
+                float v = acc[r];
+#pragma unroll
+                for (int g = 0; g < 7; ++g) v += red[(g * 32 + pl) * (MAXR + 1) + r];
+                C[(size_t)p * c_p + (size_t)r * c_r] = alpha * v;
+            }
+        }
+    }
+}
+
 // ---- softmax cross-entropy: one block per row ----------------------------------------------------
 __global__ void __launch_bounds__(1024)
 softmax_ce_rows_kernel(const float *logits, const uint32_t *targets, int vocab, float grad_scale, float *losses,
@@ -984,6 +1051,16 @@ extern "C" int b200_lora_pack(float *w_ext, float *wt_ext, const float *A_q, con
     dim3 grid((width + 255) / 256, xr);
     lora_pack_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w_ext, wt_ext, A_q, B_q, A_v, B_v, d, q_cols, kv_cols, rank,
                                                             xr, sc);
+    return done();
+}
+
+extern "C" int b200_xty_skinny(const float *X, long long ld_x, const float *Y, long long ld_y, int rows, int P, int R,
+                               float alpha, float *C, long long c_p, long long c_r, void *stream)
+{
+    if (!X || !Y || !C || rows <= 0 || P <= 0 || R <= 0 || ld_x < P || ld_y < R) return B200_E_BADARG;
+    if (R > 16) return B200_E_UNSUPPORTED;               // wider ranks go through b200_gemm_f32
+    xty_skinny_kernel<16><<<(unsigned)((P + 31) / 32), 256, 0, (cudaStream_t)stream>>>(X, ld_x, Y, ld_y, rows, P, R, alpha,
+                                                                                        C, c_p, c_r);
     return done();
 }
 

@@ -562,10 +562,17 @@ static void backward_device(SFTState *s)
         }
         const float *tmp_q = s->d_lnx + s->D, *tmp_v = tmp_q + R;
         /* dB = sc dq^T mid (:946-947, :961-962); dA = tmp^T ln1 (:950, :965) */
-        gemm_small(s, dq, 1, QKV, l->mid_q, s->QKVX, 1, gB_q, R, NULL, s->Hq_hd, R, M, sc);
-        gemm_small(s, tmp_q, 1, DX, l->ln1, s->D, 1, gA_q, s->D, NULL, R, s->D, M, 1.0f);
-        gemm_small(s, dv, 1, QKV, l->mid_v, s->QKVX, 1, gB_v, R, NULL, s->Hkv_hd, R, M, sc);
-        gemm_small(s, tmp_v, 1, DX, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
+        if (R <= 16) {
+            S_TRY(s, b200_xty_skinny(dq, QKV, l->mid_q, s->QKVX, M, s->Hq_hd, R, sc, gB_q, R, 1, st));
+            S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_q, DX, M, s->D, R, 1.0f, gA_q, 1, s->D, st));
+            S_TRY(s, b200_xty_skinny(dv, QKV, l->mid_v, s->QKVX, M, s->Hkv_hd, R, sc, gB_v, R, 1, st));
+            S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_v, DX, M, s->D, R, 1.0f, gA_v, 1, s->D, st));
+        } else {
+            gemm_small(s, dq, 1, QKV, l->mid_q, s->QKVX, 1, gB_q, R, NULL, s->Hq_hd, R, M, sc);
+            gemm_small(s, tmp_q, 1, DX, l->ln1, s->D, 1, gA_q, s->D, NULL, R, s->D, M, 1.0f);
+            gemm_small(s, dv, 1, QKV, l->mid_v, s->QKVX, 1, gB_v, R, NULL, s->Hkv_hd, R, M, sc);
+            gemm_small(s, tmp_v, 1, DX, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
+        }
         /* d_ln += tmp_q A_q + tmp_v A_v (:951-953, :966, :970): one product over the 2R packed rows of the weight */
         gemm_small(s, tmp_q, DX, 1, l->qkv.w + (size_t)QKV * s->D, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, 2 * R, 1.0f);
         /* input norm + residual + clamp (:974-979) */

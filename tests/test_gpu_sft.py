@@ -233,6 +233,21 @@ def test_silu_lora_add_softmax_ce(lib):
     assert np.abs(host(dlog) - 0.25 * wd).max() < 1e-6
 
 
+@pytest.mark.parametrize("rows,P,R", [(512, 4096, 16), (37, 130, 8), (300, 2560, 16), (64, 2560, 3)])
+def test_xty_skinny_lora_gradients(lib, rows, P, R):
+    rng = np.random.default_rng(P + R)
+    X = rng.standard_normal((rows, P + 5)).astype(np.float32)
+    Y = rng.standard_normal((rows, R + 3)).astype(np.float32)
+    dX, dY = dev(X), dev(Y)
+    want = 0.5 * (X[:, :P].astype(np.float64).T @ Y[:, :R].astype(np.float64))
+    c1 = torch.zeros(P, R, device="cuda")
+    assert lib.b200_xty_skinny(dX.data_ptr(), P + 5, dY.data_ptr(), R + 3, rows, P, R, 0.5, c1.data_ptr(), R, 1, None) == 0
+    assert sc.rel_err(host(c1), want) < 1e-5
+    c2 = torch.zeros(R, P, device="cuda")
+    assert lib.b200_xty_skinny(dX.data_ptr(), P + 5, dY.data_ptr(), R + 3, rows, P, R, 0.5, c2.data_ptr(), 1, P, None) == 0
+    assert sc.rel_err(host(c2), want.T) < 1e-5
+
+
 def test_clip_and_adamw_kernels(lib):
     rng = np.random.default_rng(9)
     n = 100003
