@@ -393,8 +393,8 @@ def sft_main(args, rank, local_rank, world):
 
     # dominant kernel alone: the gate/up forward product [M, 2*IS] = [M, D] x [2*IS, D]^T on the tensor cores
     D, IS = sp.d_model, sp.intermediate_size
-    a = torch.randn(M, D, device="cuda")
-    ws = [torch.randn(2 * IS, D, device="cuda").half().float() * 0.02 for _ in range(3)]
+    a = torch.randn(M, D, device="cuda").half()
+    ws = [(torch.randn(2 * IS, D, device="cuda") * 0.02).half() for _ in range(3)]
     cbuf = torch.empty(M, 2 * IS, device="cuda")
     errw = torch.zeros(1, dtype=torch.int32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
@@ -404,7 +404,7 @@ def sft_main(args, rank, local_rank, world):
         g.A, g.a_row, g.a_col = a.data_ptr(), D, 1
         g.B, g.b_row, g.b_col = wt.data_ptr(), 1, D
         g.C, g.ldc, g.M, g.N, g.K, g.alpha, g.d_err = cbuf.data_ptr(), 2 * IS, M, 2 * IS, D, 1.0, errw.data_ptr()
-        return L.b200_gemm_tf32(C.byref(g), C.c_void_p(stream))
+        return L.b200_gemm_f16(C.byref(g), C.c_void_p(stream))
 
     tc_ok = one(ws[0]) == 0
     roofline = None
@@ -422,18 +422,18 @@ def sft_main(args, rank, local_rank, world):
         sec = e0.elapsed_time(e1) / 1e3 / reps
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peak, peak_kind = float(json.load(f)["bf16_tflops"]), "measured (cuBLAS bf16 burst; TF32 runs at half that rate)"
+                peak, peak_kind = float(json.load(f)["bf16_tflops"]), "measured (cuBLAS bf16 burst)"
         except Exception:
             peak, peak_kind = 1590.0, "fallback"
         ach = 2.0 * M * 2 * IS * D / sec / 1e12
-        roofline = {"bound": "tensor", "kernel": f"gemm_tf32_kernel gate/up forward (M {M}, N {2 * IS}, K {D})",
+        roofline = {"bound": "tensor", "kernel": f"gemm_tf32_kernel, binary16 operands: gate/up forward (M {M}, N {2 * IS}, K {D})",
                     "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "peak_source": peak_kind,
                     "traffic": None, "us_per_launch": sec * 1e6}
     step_flops = sft_flops_per_token(sp) * M
     line = {
         "metric": "sft_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "tf32 tensor-core products over binary16-valued weights, fp32 accumulate and elsewhere",
+        "vs_baseline": None, "dtype": "binary16 tensor-core operands (weights exact, activations rounded), fp32 accumulate; fp32 elsewhere",
         "data": "synthetic", "config": config,
         "e2e": {"value": e2e_v, "unit": "tok/s", "h2d_bytes_per_step": int(2 * M * 4), "d2h_bytes_per_step": int(M * 4 + 8)},
         "gpu_launches": launches, "roofline": roofline,

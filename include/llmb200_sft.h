@@ -119,9 +119,11 @@ float llmb200_sft_last_grad_norm(SFTState *state);
 /* Device milliseconds (CUDA events) of the last forward+loss+backward and of
  * the last clip+AdamW. */
 float llmb200_sft_last_step_ms(SFTState *state, float *update_ms);
-/* 0: CUDA-core GEMM for every product; 1: tensor-core GEMM for the frozen
- * projections when the shape allows it (default; LLMB200_SFT_TC=0 also turns
- * it off). Returns the previous setting. */
+/* Returns 1 when the state runs the frozen projections on the tensor cores
+ * (binary16 operands, fp32 accumulate; the default when the dimensions allow
+ * it), 0 when every product runs on the CUDA cores in fp32 (LLMB200_SFT_TC=0
+ * at creation). The mode is fixed when the state is created -- the weights are
+ * stored for it -- so `on` is ignored. */
 int llmb200_sft_use_tensor_cores(SFTState *state, int on);
 /* Non-zero once a launch or copy has failed. */
 int llmb200_sft_error(SFTState *state);

@@ -49,6 +49,16 @@ int b200_gemm_f32(const b200_gemm_args *a, void *stream);
  * by the tensor core (weights holding binary16 values stay exact).
  * Returns B200_E_UNSUPPORTED when a condition does not hold. */
 int b200_gemm_tf32(const b200_gemm_args *a, void *stream);
+/* The same kernel on binary16 operands (tcgen05.mma kind::f16): A and B point
+ * to binary16 data (strides in elements, K and the row strides multiples of
+ * 8), C and R stay fp32, accumulation is fp32. Half the operand bytes of the
+ * TF32 form, which is what bounds the kernel. */
+int b200_gemm_f16(const b200_gemm_args *a, void *stream);
+/* dst[i] = binary16(src[i] * scale), round to nearest even: the operand copies
+ * b200_gemm_f16 reads (gradients are scaled by a power of two into binary16's
+ * range and the product scaled back through alpha). */
+int b200_f32_to_f16(const float *src, size_t n, float scale, void *dst, void *stream);
+int b200_transpose_f16(const void *src, int rows, int cols, void *dst, void *stream);
 
 /* x[m,:] = scale * emb[tokens[m],:]  (src/nn/fast_sft.c:1118-1126). */
 int b200_embed_rows(const float *emb, const uint32_t *tokens, int rows, int dim, int vocab, float scale,
@@ -119,6 +129,9 @@ int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid
  *                                        extra row R+r = sc B_v[:, r] over the v columns, rest 0 */
 int b200_lora_pack(float *w_ext, float *wt_ext, const float *A_q, const float *B_q, const float *A_v,
                    const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc, void *stream);
+/* The same with binary16 destinations. */
+int b200_lora_pack_f16(void *w_ext, void *wt_ext, const float *A_q, const float *B_q, const float *A_v,
+                       const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc, void *stream);
 
 /* C(p, r) = alpha * sum_m X[m*ld_x + p] * Y[m*ld_y + r] for p < P, r < R <= 16
  * (B200_E_UNSUPPORTED for wider ranks: use b200_gemm_f32),

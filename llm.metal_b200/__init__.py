@@ -130,7 +130,7 @@ SYMBOLS_MAIN = {
                             "llmb200_state_time_kind", "llmb200_state_step_trace",
                             "llmb200_state_weight_bytes", "llmb200_state_position", "llmb200_state_graph_kernels",
                             "llmb200_state_export_weight"],
-    "llmb200_train_kernels.h": ["b200_gemm_f32", "b200_gemm_tf32", "b200_embed_rows", "b200_round_f16",
+    "llmb200_train_kernels.h": ["b200_gemm_f32", "b200_gemm_tf32", "b200_gemm_f16", "b200_f32_to_f16", "b200_transpose_f16", "b200_lora_pack_f16", "b200_embed_rows", "b200_round_f16",
                                 "b200_transpose_f32", "b200_rms_norm_rows", "b200_rms_norm_bwd_rows",
                                 "b200_qk_norm_rope", "b200_qk_norm_rope_bwd", "b200_attn_train_fwd",
                                 "b200_attn_train_bwd", "b200_silu_mul_rows", "b200_silu_mul_bwd_rows", "b200_lora_add", "b200_lora_pack", "b200_xty_skinny",
@@ -207,6 +207,9 @@ def lib():
         "llmb200_state_export_weight": (sz, [vp, i, i, vp, sz]),
         # ---- llmb200_train_kernels.h
         "b200_gemm_f32": (i, [C.POINTER(GemmArgs), vp]), "b200_gemm_tf32": (i, [C.POINTER(GemmArgs), vp]),
+        "b200_gemm_f16": (i, [C.POINTER(GemmArgs), vp]), "b200_f32_to_f16": (i, [vp, sz, fl, vp, vp]),
+        "b200_transpose_f16": (i, [vp, i, i, vp, vp]),
+        "b200_lora_pack_f16": (i, [vp, vp, vp, vp, vp, vp, i, i, i, i, i, fl, vp]),
         "b200_embed_rows": (i, [vp, vp, i, i, i, fl, vp, vp]),
         "b200_round_f16": (i, [vp, sz, vp]), "b200_transpose_f32": (i, [vp, i, i, vp, vp]),
         "b200_rms_norm_rows": (i, [vp, vp, vp, i, i, fl, vp]),

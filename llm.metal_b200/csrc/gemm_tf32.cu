@@ -43,7 +43,8 @@ struct EpiArgs {
     int bn;            // columns of the output tile = N of one tcgen05.mma (a multiple of 16, 64..256)
     int stages;        // ring slots
     int tmem_cols;     // tensor-memory columns to allocate: the power of two >= bn
-    int ksub;          // 32-element k sub-tiles per ring slot (each its own 128-byte-swizzled block)
+    int f16;           // 0: fp32 operands read as TF32 (32 per 128-byte row); 1: binary16 operands (64 per row)
+    int ksub;          // 128-byte-wide k sub-tiles per ring slot (each its own 128-byte-swizzled block)
     int splits;        // CTAs sharing one output tile along k (gridDim.z); 1 = none
     unsigned *flags;   // one turn counter per output tile, zero between launches
 };
@@ -87,6 +88,13 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
 {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
 }
 
@@ -136,7 +144,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     // k-blocks of this CTA: the whole contraction, or its share when several CTAs split one tile along k
-    const int nkb_all = (p.K + BK * KSUB - 1) / (BK * KSUB);
+    const int BKE = p.f16 ? 2 * BK : BK;                         // elements per 128-byte operand row
+    const int nkb_all = (p.K + BKE * KSUB - 1) / (BKE * KSUB);
     const int per_split = (nkb_all + p.splits - 1) / p.splits;
     const int kb0 = blockIdx.z * per_split;
     const int nkb = min(per_split, nkb_all - kb0);               // > 0: the host never launches an empty split
@@ -171,7 +180,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 uint8_t *a_dst = tiles + (size_t)s * STAGE_BYTES, *b_dst = a_dst + A_BYTES * KSUB;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 for (int u = 0; u < KSUB; ++u) {     // a sub-tile past the end of k is all fill (zeros)
-                    const int x = ((kb0 + kb) * KSUB + u) * BK;
+                    const int x = ((kb0 + kb) * KSUB + u) * BKE;
                     tma_load_2d(a_dst + (size_t)u * A_BYTES, &map_a, x, m0, &full_bar[s]);
                     tma_load_2d(b_dst + (size_t)u * B_BYTES, &map_b, x, n0, &full_bar[s]);
                 }
@@ -180,7 +189,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: D fp32, A and B TF32, both K-major, N = BN, M = 128
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // (operand format field: 2 = TF32, 0 = F16; an MMA covers 32 bytes of k either way: 8 or 16 elements)
+            const uint32_t fmt = p.f16 ? 0u : 2u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % STAGES, it = kb / STAGES;
@@ -195,8 +206,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int u = 0; u < KSUB; ++u) {
                     const uint64_t adesc = smem_desc_sw128(a_addr + u * A_BYTES), bdesc = smem_desc_sw128(b_addr + u * B_BYTES);
 #pragma unroll
-                    for (int j = 0; j < BK / UMMA_K; ++j)       // 32 bytes along k per step: +2 in 16-byte units
-                        umma_tf32(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | u | j) != 0);
+                    for (int j = 0; j < BK / UMMA_K; ++j) {     // 32 bytes along k per step: +2 in 16-byte units
+                        if (p.f16) umma_f16(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | u | j) != 0);
+                        else umma_tf32(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | u | j) != 0);
+                    }
                 }
                 umma_commit(&empty_bar[s]);                     // slot reusable once these MMAs have read it
             }
@@ -323,15 +336,16 @@ encode_fn_t encode_fn()
 }
 
 // [rows, K] fp32 matrix with row stride ld elements; box = 32 x box_rows, 128-byte swizzle, zero fill outside.
-bool make_map(CUtensorMap *map, const float *base, long long rows, long long K, long long ld, int box_rows)
+bool make_map(CUtensorMap *map, const void *base, long long rows, long long K, long long ld, int box_rows, int f16)
 {
     encode_fn_t enc = encode_fn();
     if (!enc) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * (f16 ? 2 : 4)};
+    const cuuint32_t box[2] = {(cuuint32_t)(f16 ? 2 * BK : BK), (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+    return enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base),
+               dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -356,9 +370,10 @@ int sm_count_tc()
 //    With a very long contraction on top (the LM-head backward, K = vocabulary), three CTAs split a
 //    256-wide tile along k; their epilogues run one after the other, which only pays when k is long.
 //  * otherwise the width (a multiple of 16 up to 256) that minimises waves * (128 + bn).
-void pick_tile(int M, int N, int K, int *bn_out, int *ksub_out, int *splits_out)
+void pick_tile(int M, int N, int K, int f16, int *bn_out, int *ksub_out, int *splits_out)
 {
-    const int mt = (M + BM - 1) / BM, sms = sm_count_tc(), nkb = (K + BK - 1) / BK;
+    const int bke = f16 ? 2 * BK : BK;
+    const int mt = (M + BM - 1) / BM, sms = sm_count_tc(), nkb = (K + bke - 1) / bke;
     *splits_out = 1;
     if ((long long)mt * ((N + 127) / 128) <= sms) {
         const long long tiles256 = (long long)mt * ((N + 255) / 256);
@@ -410,19 +425,19 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, EpiArgs e, cudaStream_t
 
 }  // namespace
 
-extern "C" int b200_gemm_tf32(const b200_gemm_args *a, void *stream)
+static int gemm_tc(const b200_gemm_args *a, int f16, void *stream)
 {
     if (!a || !a->A || !a->B || !a->C || a->M <= 0 || a->N <= 0 || a->K <= 0) return B200_E_BADARG;
     if (a->a_col != 1 || a->b_row != 1) return B200_E_UNSUPPORTED;
     const long long lda = a->a_row, ldb = a->b_col;
-    if ((a->K & 3) || (lda & 3) || (ldb & 3) || lda < a->K || ldb < a->K) return B200_E_UNSUPPORTED;
+    const int gran = f16 ? 7 : 3;                                  // 16-byte granularity of rows and of k
+    if ((a->K & gran) || (lda & gran) || (ldb & gran) || lda < a->K || ldb < a->K) return B200_E_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15)) return B200_E_UNSUPPORTED;
     if (a->N < 64 || a->M < 16) return B200_E_UNSUPPORTED;        // the CUDA-core kernel is the better fit
     if ((a->N + 63) / 64 > 65535) return B200_E_UNSUPPORTED;
 
     CUtensorMap ma, mb;
-    EpiArgs e = {a->C, a->ldc, a->R, a->ldr, a->M, a->N, a->K, a->alpha, a->d_err, 128, 0, 0, 1, 1, nullptr};
-    if (!make_map(&ma, a->A, a->M, a->K, lda, BM)) return B200_E_UNSUPPORTED;
+    EpiArgs e = {a->C, a->ldc, a->R, a->ldr, a->M, a->N, a->K, a->alpha, a->d_err, 128, 0, 0, f16, 1, 1, nullptr};
     // LLMB200_GEMM_BN=<n> overrides the tile width for experiments
     static int forced = -1;
     if (forced < 0) {
@@ -430,11 +445,15 @@ extern "C" int b200_gemm_tf32(const b200_gemm_args *a, void *stream)
         forced = t ? atoi(t) : 0;
         if (forced < 0 || forced > 256 || (forced % 16)) forced = 0;
     }
-    pick_tile(a->M, a->N, a->K, &e.bn, &e.ksub, &e.splits);
+    pick_tile(a->M, a->N, a->K, f16, &e.bn, &e.ksub, &e.splits);
     if (forced >= 64) { e.bn = forced; e.splits = 1; }
-    if (!make_map(&mb, a->B, a->N, a->K, ldb, e.bn)) return B200_E_UNSUPPORTED;
+    if (!make_map(&ma, a->A, a->M, a->K, lda, BM, f16)) return B200_E_UNSUPPORTED;
+    if (!make_map(&mb, a->B, a->N, a->K, ldb, e.bn, f16)) return B200_E_UNSUPPORTED;
     return launch(ma, mb, e, (cudaStream_t)stream);
 }
+
+extern "C" int b200_gemm_tf32(const b200_gemm_args *a, void *stream) { return gemm_tc(a, 0, stream); }
+extern "C" int b200_gemm_f16(const b200_gemm_args *a, void *stream) { return gemm_tc(a, 1, stream); }
 
 // Diagnostics: the timeline of CTA (0,0,0) of the last launch (see g_gemm_trace). Synchronises the device.
 extern "C" int b200_gemm_tf32_trace(unsigned long long *out8)

@@ -644,7 +644,11 @@ lora_add_kernel(float *y, long long ld, int col0, int n_cols, const float *mid, 
 //                         v columns, zero elsewhere
 // so that the forward product also yields ln1 A^T and the backward product also yields sc * dq B_q and
 // sc * dv B_v (src/nn/fast_sft.c:639-641, 948-949, 963-964) at no extra pass over the activations.
-__global__ void lora_pack_kernel(float *w_ext, float *wt_ext, const float *A_q, const float *B_q, const float *A_v,
+__device__ __forceinline__ void store_as(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store_as(__half *p, float v) { *p = __float2half_rn(v); }
+
+template <typename T>
+__global__ void lora_pack_kernel(T *w_ext, T *wt_ext, const float *A_q, const float *B_q, const float *A_v,
                                  const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc)
 {
     const int qkv = q_cols + 2 * kv_cols;
@@ -655,13 +659,13 @@ __global__ void lora_pack_kernel(float *w_ext, float *wt_ext, const float *A_q, 
             float v = 0.f;
             if (row < rank) v = A_q[(size_t)row * d + c];
             else if (row < 2 * rank) v = A_v[(size_t)(row - rank) * d + c];
-            w_ext[(size_t)(qkv + row) * d + c] = v;
+            store_as(w_ext + (size_t)(qkv + row) * d + c, v);
         }
         if (c < qkv) {
             float v = 0.f;
             if (row < rank) { if (c < q_cols) v = sc * B_q[(size_t)c * rank + row]; }
             else if (row < 2 * rank) { if (c >= q_cols + kv_cols) v = sc * B_v[(size_t)(c - q_cols - kv_cols) * rank + (row - rank)]; }
-            wt_ext[(size_t)(d + row) * qkv + c] = v;
+            store_as(wt_ext + (size_t)(d + row) * qkv + c, v);
         }
     }
 }
@@ -773,6 +777,37 @@ __global__ void transpose_f32_kernel(const float *src, int rows, int cols, float
     for (int i = threadIdx.y; i < 32; i += 8) {
         const int r = r0 + i, c = c0 + threadIdx.x;
         t[i][threadIdx.x] = (r < rows && c < cols) ? src[(size_t)r * cols + c] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int c = c0 + i, r = r0 + threadIdx.x;
+        if (c < cols && r < rows) dst[(size_t)c * rows + r] = t[threadIdx.x][i];
+    }
+}
+
+// ---- binary16 operand copies for the tensor-core products --------------------------------------------
+// dst = half(src * scale), four elements per thread (n a multiple of 4 is the fast path).
+__global__ void f32_to_f16_kernel(const float *src, size_t n, float scale, __half *dst)
+{
+    const size_t n4 = n / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = reinterpret_cast<const float4 *>(src)[i];
+        __half2 a = __floats2half2_rn(v.x * scale, v.y * scale), b = __floats2half2_rn(v.z * scale, v.w * scale);
+        uint2 o;
+        o.x = *reinterpret_cast<unsigned *>(&a);
+        o.y = *reinterpret_cast<unsigned *>(&b);
+        reinterpret_cast<uint2 *>(dst)[i] = o;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) dst[n4 * 4 + threadIdx.x] = __float2half_rn(src[n4 * 4 + threadIdx.x] * scale);
+}
+
+__global__ void transpose_f16_kernel(const __half *src, int rows, int cols, __half *dst)
+{
+    __shared__ __half t[32][34];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += 8) {
+        const int r = r0 + i, c = c0 + threadIdx.x;
+        t[i][threadIdx.x] = (r < rows && c < cols) ? src[(size_t)r * cols + c] : __float2half(0.f);
     }
     __syncthreads();
     for (int i = threadIdx.y; i < 32; i += 8) {
@@ -1049,8 +1084,40 @@ extern "C" int b200_lora_pack(float *w_ext, float *wt_ext, const float *A_q, con
         return B200_E_BADARG;
     const int width = d > q_cols + 2 * kv_cols ? d : q_cols + 2 * kv_cols;
     dim3 grid((width + 255) / 256, xr);
-    lora_pack_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w_ext, wt_ext, A_q, B_q, A_v, B_v, d, q_cols, kv_cols, rank,
-                                                            xr, sc);
+    lora_pack_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(w_ext, wt_ext, A_q, B_q, A_v, B_v, d, q_cols, kv_cols,
+                                                                   rank, xr, sc);
+    return done();
+}
+
+extern "C" int b200_lora_pack_f16(void *w_ext, void *wt_ext, const float *A_q, const float *B_q, const float *A_v,
+                                  const float *B_v, int d, int q_cols, int kv_cols, int rank, int xr, float sc,
+                                  void *stream)
+{
+    if (!w_ext || !wt_ext || !A_q || !B_q || !A_v || !B_v || d <= 0 || q_cols <= 0 || kv_cols <= 0 || rank <= 0 ||
+        xr < 2 * rank)
+        return B200_E_BADARG;
+    const int width = d > q_cols + 2 * kv_cols ? d : q_cols + 2 * kv_cols;
+    dim3 grid((width + 255) / 256, xr);
+    lora_pack_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(static_cast<__half *>(w_ext), static_cast<__half *>(wt_ext),
+                                                                    A_q, B_q, A_v, B_v, d, q_cols, kv_cols, rank, xr, sc);
+    return done();
+}
+
+extern "C" int b200_f32_to_f16(const float *src, size_t n, float scale, void *dst, void *stream)
+{
+    if (!src || !dst || n == 0 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 7)) return B200_E_BADARG;
+    const size_t n4 = (n + 3) / 4;
+    const unsigned grid = (unsigned)((n4 + 255) / 256 < 148 * 16 ? (n4 + 255) / 256 : 148 * 16);
+    f32_to_f16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(src, n, scale, static_cast<__half *>(dst));
+    return done();
+}
+
+extern "C" int b200_transpose_f16(const void *src, int rows, int cols, void *dst, void *stream)
+{
+    if (!src || !dst || rows <= 0 || cols <= 0 || (rows + 31) / 32 > 65535) return B200_E_BADARG;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+    transpose_f16_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(static_cast<const __half *>(src), rows, cols,
+                                                                  static_cast<__half *>(dst));
     return done();
 }
 

@@ -13,10 +13,15 @@
  *  - No transposed, repeated or copied activations: kernels index heads and
  *    KV groups in place; residual adds ride on the product's epilogue; saved
  *    activations are the buffers the forward wrote, not copies.
- *  - The frozen weights are fp32 copies of their binary16 values (every product
- *    equals the reference's float(half) * float); with tensor cores on, a
- *    transposed copy serves the backward product so that both passes read
- *    operands contiguous along the contraction.
+ *  - The frozen weights keep their binary16 values. With tensor cores on (the
+ *    default) they are stored as binary16, once as [out, in] and once
+ *    transposed, so that the forward and the backward product both read
+ *    operands contiguous along the contraction; the activation operand of each
+ *    product is a binary16 copy made just before it (gradients scaled by a power
+ *    of two into binary16's range, scaled back in the product's epilogue) and
+ *    accumulation is fp32. With tensor cores off (LLMB200_SFT_TC=0) the weights
+ *    are fp32 copies of the binary16 values and every product runs on the CUDA
+ *    cores in fp32: exactly the reference's float(half) * float.
  *  - Clip + AdamW run on the device over one flat parameter vector.
  */
 #include "internal.h"
@@ -29,8 +34,10 @@
 #include <time.h>
 
 typedef struct {
-    float *w;        /* [rows, cols] */
-    float *wt;       /* [cols, rows] or NULL */
+    float *w;        /* fp32 [rows, cols]          (CUDA-core mode; q/k/v also fp32 wt) */
+    float *wt;       /* fp32 [cols, rows] or NULL */
+    void *wh;        /* binary16 [rows, cols]      (tensor-core mode) */
+    void *wth;       /* binary16 [cols, rows] */
     int rows, cols;
 } SftMat;
 
@@ -68,6 +75,8 @@ struct SFTState {
     /* scratch */
     float *x_final, *ln_final, *att, *act, *logits, *dlogits, *losses;
     float *dx, *d_ln, *d_lnx, *d_act, *d_gu, *d_att, *dqkv, *d_score;
+    void *xh;                   /* binary16 operand copy of the activation / gradient a product reads */
+    float gscale;               /* power of two applied to gradient operands before rounding to binary16 */
     uint32_t *tokens, *targets;
     double *partials;
     float *d_norm;
@@ -108,53 +117,121 @@ static float *dalloc(SFTState *s, size_t n_floats)
 
 /* ---------------------------------------------------------------- weights */
 
-/* rows of `src` ([rows, cols] fp32, host) into dst rows row0.. of a [*, cols] device matrix */
+static void *halloc(SFTState *s, size_t n_halves)
+{
+    void *p = NULL;
+    cudaError_t e = cudaMalloc(&p, (n_halves ? n_halves : 1) * 2);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "[llmb200] sft: allocating %zu halves failed: %s\n", n_halves, cudaGetErrorString(e));
+        if (!s->err) s->err = (int)e;
+        return NULL;
+    }
+    return p;
+}
+
+/* host fp32 -> device binary16 (round to nearest even) through the runtime's staging buffers */
+static int upload_half(void *d_dst, const float *src, size_t n)
+{
+    const size_t chunk = LLMB200_STAGE_BYTES / sizeof(float);
+    for (size_t o = 0; o < n; o += chunk) {
+        const size_t m = (n - o) < chunk ? (n - o) : chunk;
+        const int sb = g_rt.stage_next;
+        g_rt.stage_next ^= 1;
+        CU_TRY(cudaEventSynchronize(g_rt.stage_done[sb]), return -100);
+        memcpy(g_rt.h_stage[sb], src + o, m * sizeof(float));
+        CU_TRY(cudaMemcpyAsync(g_rt.d_stage[sb], g_rt.h_stage[sb], m * sizeof(float), cudaMemcpyHostToDevice, g_rt.stream),
+               return -101);
+        int rc = b200_f32_to_f16(g_rt.d_stage[sb], m, 1.0f, (char *)d_dst + o * 2, g_rt.stream);
+        if (rc) return rc;
+        CU_TRY(cudaEventRecord(g_rt.stage_done[sb], g_rt.stream), return -102);
+    }
+    return 0;
+}
+
+/* rows of `src` ([rows, cols] fp32, host) into rows row0.. of the device matrix, as binary16 values */
 static int mat_put(SFTState *s, SftMat *m, int row0, const float *src, int rows)
 {
     if (!src) return B200_E_BADARG;
-    int rc = llmb200_upload_f32_into(m->w + (size_t)row0 * m->cols, src, (size_t)rows * m->cols);
+    const size_t off = (size_t)row0 * m->cols, n = (size_t)rows * m->cols;
+    if (s->use_tc) return upload_half((char *)m->wh + off * 2, src, n);
+    int rc = llmb200_upload_f32_into(m->w + off, src, n);
     if (rc) return rc;
-    return b200_round_f16(m->w + (size_t)row0 * m->cols, (size_t)rows * m->cols, g_rt.stream);
+    return b200_round_f16(m->w + off, n, g_rt.stream);
 }
 
 static int mat_alloc(SFTState *s, SftMat *m, int rows, int cols)
 {
     m->rows = rows;
     m->cols = cols;
+    if (s->use_tc) {
+        m->wh = halloc(s, (size_t)rows * cols);
+        m->wth = halloc(s, (size_t)rows * cols);
+        return (m->wh && m->wth) ? 0 : -1;
+    }
     m->w = dalloc(s, (size_t)rows * cols);
-    m->wt = s->use_tc ? dalloc(s, (size_t)rows * cols) : NULL;
-    return (m->w && (!s->use_tc || m->wt)) ? 0 : -1;
+    return m->w ? 0 : -1;
 }
 
 /* The fused q/k/v matrix carries XR extra rows (the LoRA A matrices) and always has a transposed copy
  * [D + XR, QKV] whose extra rows hold sc * B (see b200_lora_pack). */
 static int qkv_alloc(SFTState *s, SftMat *m)
 {
+    const size_t n = (size_t)s->QKVX * s->D, nt = (size_t)(s->D + s->XR) * s->QKV;
     m->rows = s->QKVX;
     m->cols = s->D;
-    m->w = dalloc(s, (size_t)s->QKVX * s->D);
-    m->wt = dalloc(s, (size_t)(s->D + s->XR) * s->QKV);
-    if (m->w) cudaMemsetAsync(m->w, 0, (size_t)s->QKVX * s->D * 4, g_rt.stream);
-    if (m->wt) cudaMemsetAsync(m->wt, 0, (size_t)(s->D + s->XR) * s->QKV * 4, g_rt.stream);
+    if (s->use_tc) {
+        m->wh = halloc(s, n);
+        m->wth = halloc(s, nt);
+        if (m->wh) cudaMemsetAsync(m->wh, 0, n * 2, g_rt.stream);
+        if (m->wth) cudaMemsetAsync(m->wth, 0, nt * 2, g_rt.stream);
+        return (m->wh && m->wth) ? 0 : -1;
+    }
+    m->w = dalloc(s, n);
+    m->wt = dalloc(s, nt);
+    if (m->w) cudaMemsetAsync(m->w, 0, n * 4, g_rt.stream);
+    if (m->wt) cudaMemsetAsync(m->wt, 0, nt * 4, g_rt.stream);
     return (m->w && m->wt) ? 0 : -1;
 }
 
-static int mat_finish(SFTState *s, SftMat *m)
+/* the transposed copy of the first `rows` rows (all of them unless the matrix carries extra rows) */
+static int mat_finish_rows(SFTState *s, SftMat *m, int rows)
 {
+    if (s->use_tc) return b200_transpose_f16(m->wh, rows, m->cols, m->wth, g_rt.stream);
     if (!m->wt) return 0;
-    return b200_transpose_f32(m->w, m->rows, m->cols, m->wt, g_rt.stream);
+    return b200_transpose_f32(m->w, rows, m->cols, m->wt, g_rt.stream);
 }
+static int mat_finish(SFTState *s, SftMat *m) { return mat_finish_rows(s, m, m->rows); }
 
 static void mat_free(SftMat *m)
 {
     cudaFree(m->w);
     cudaFree(m->wt);
+    cudaFree(m->wh);
+    cudaFree(m->wth);
     m->w = m->wt = NULL;
+    m->wh = m->wth = NULL;
+}
+
+/* One product on the tensor cores: C[M, N] = alpha * half(A * a_scale)[M, K] * Bh[N, K]^T (+ R). */
+static void gemm_tc(SFTState *s, const float *A, float a_scale, const void *Bh, float *C, long long ldc, const float *R,
+                    int N, int K)
+{
+    S_TRY(s, b200_f32_to_f16(A, (size_t)s->M * K, a_scale, s->xh, g_rt.stream));
+    b200_gemm_args g = {0};
+    g.A = (const float *)s->xh; g.a_row = K; g.a_col = 1;
+    g.B = (const float *)Bh; g.b_row = 1; g.b_col = K;
+    g.C = C; g.ldc = ldc;
+    g.R = R; g.ldr = ldc;
+    g.M = s->M; g.N = N; g.K = K;
+    g.alpha = 1.0f / a_scale;
+    g.d_err = (unsigned *)s->d_norm + 1;
+    S_TRY(s, b200_gemm_f16(&g, g_rt.stream));
 }
 
 /* C[M, W.rows] = A[M, W.cols] * W^T (+ R): the reference's f16_matmul. */
 static void gemm_fwd(SFTState *s, const float *A, const SftMat *W, float *C, const float *R)
 {
+    if (s->use_tc) { gemm_tc(s, A, 1.0f, W->wh, C, W->rows, R, W->rows, W->cols); return; }
     b200_gemm_args g = {0};
     g.A = A; g.a_row = W->cols; g.a_col = 1;
     g.B = W->w; g.b_row = 1; g.b_col = W->cols;
@@ -162,31 +239,19 @@ static void gemm_fwd(SFTState *s, const float *A, const SftMat *W, float *C, con
     g.R = R; g.ldr = W->rows;
     g.M = s->M; g.N = W->rows; g.K = W->cols;
     g.alpha = 1.0f;
-    g.d_err = (unsigned *)s->d_norm + 1;
-    if (s->use_tc) {
-        int rc = b200_gemm_tf32(&g, g_rt.stream);
-        if (rc == 0) return;
-        if (rc != B200_E_UNSUPPORTED) { S_TRY(s, rc); return; }
-    }
     S_TRY(s, b200_gemm_f32(&g, g_rt.stream));
 }
 
-/* C[M, W.cols] = A[M, W.rows] * W: the reference's f16_matmul_nt. */
+/* C[M, W.cols] = A[M, W.rows] * W: the reference's f16_matmul_nt. A is a gradient. */
 static void gemm_bwd(SFTState *s, const float *A, const SftMat *W, float *C)
 {
+    if (s->use_tc) { gemm_tc(s, A, s->gscale, W->wth, C, W->cols, NULL, W->cols, W->rows); return; }
     b200_gemm_args g = {0};
     g.A = A; g.a_row = W->rows; g.a_col = 1;
+    g.B = W->w; g.b_row = W->cols; g.b_col = 1;
     g.C = C; g.ldc = W->cols;
     g.M = s->M; g.N = W->cols; g.K = W->rows;
     g.alpha = 1.0f;
-    g.d_err = (unsigned *)s->d_norm + 1;
-    if (s->use_tc && W->wt) {
-        g.B = W->wt; g.b_row = 1; g.b_col = W->rows;
-        int rc = b200_gemm_tf32(&g, g_rt.stream);
-        if (rc == 0) return;
-        if (rc != B200_E_UNSUPPORTED) { S_TRY(s, rc); return; }
-    }
-    g.B = W->w; g.b_row = W->cols; g.b_col = 1;
     S_TRY(s, b200_gemm_f32(&g, g_rt.stream));
 }
 
@@ -238,8 +303,15 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->eps = 1e-6f;
     s->lora_rank = lora_rank;
     s->lora_scaling = lora_alpha / (float)lora_rank;
+    /* Tensor cores need 16-byte operand rows (dimensions in multiples of 8 halves) and at least 16 x 64
+     * outputs; otherwise, or with LLMB200_SFT_TC=0, every product runs on the CUDA cores in fp32. */
     const char *tc = getenv("LLMB200_SFT_TC");
-    s->use_tc = !(tc && tc[0] == '0');
+    s->use_tc = !(tc && tc[0] == '0') && s->M >= 16 && s->D >= 64 && s->V >= 64 && !(s->D % 8) && !(s->Hq_hd % 8) &&
+                !(s->Hkv_hd % 8) && !(s->IS % 8);
+    /* gradients reach at most 1/M (the loss scale) at the logits: 8 * M rounded up to a power of two maps
+     * them to ~8 in binary16 and leaves four decades below before the subnormals start */
+    s->gscale = 8.0f;
+    while (s->gscale < 8.0f * (float)s->M) s->gscale *= 2.0f;
     s->rope_thetas = calloc(s->NL, sizeof(float));
     s->layers = calloc(s->NL, sizeof(SftLayer));
 
@@ -291,6 +363,13 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->d_act = dalloc(s, (size_t)M * s->IS); s->d_gu = dalloc(s, (size_t)M * 2 * s->IS);
     s->d_att = dalloc(s, (size_t)M * s->Hq_hd); s->dqkv = dalloc(s, (size_t)M * s->QKV);
     s->d_score = dalloc(s, (size_t)s->S * s->Hq * s->N * (s->N > 2 * s->hd ? s->N : 2 * s->hd));
+    if (s->use_tc) {
+        size_t widest = (size_t)s->V;
+        if ((size_t)2 * s->IS > widest) widest = (size_t)2 * s->IS;
+        if ((size_t)s->QKV > widest) widest = (size_t)s->QKV;
+        if ((size_t)s->D > widest) widest = (size_t)s->D;
+        s->xh = halloc(s, (size_t)M * widest);
+    }
     s->tokens = (uint32_t *)dalloc(s, M); s->targets = (uint32_t *)dalloc(s, M);
     s->partials = (double *)dalloc(s, 2 * N_PARTIALS);
     s->d_norm = dalloc(s, 2);                 /* [0] gradient norm, [1] error word of the tensor-core products */
@@ -342,7 +421,7 @@ int llmb200_sft_load_layer(SFTState *s, int L, const LayerWeightRef *r, float ro
     if (!rc) rc = mat_put(s, &l->gu, 0, r->gate_proj.data, s->IS);
     if (!rc) rc = mat_put(s, &l->gu, s->IS, r->up_proj.data, s->IS);
     if (!rc) rc = mat_put(s, &l->down, 0, r->down_proj.data, s->D);
-    if (!rc) rc = b200_transpose_f32(l->qkv.w, s->QKV, s->D, l->qkv.wt, g_rt.stream);   /* rows 0..D-1 of wt */
+    if (!rc) rc = mat_finish_rows(s, &l->qkv, s->QKV);          /* rows 0..D-1 of the transposed copy */
     if (!rc) rc = mat_finish(s, &l->o);
     if (!rc) rc = mat_finish(s, &l->gu);
     if (!rc) rc = mat_finish(s, &l->down);
@@ -461,7 +540,7 @@ void sft_state_free(SFTState *s)
     mat_free(&s->lm_head);
     void *bufs[] = { s->final_g, s->d_emb, s->lora_p, s->lora_g, s->lora_m, s->lora_v, s->x_final, s->ln_final, s->att,
                      s->act, s->logits, s->dlogits, s->losses, s->dx, s->d_ln, s->d_act, s->d_gu, s->d_att, s->dqkv,
-                     s->d_score, s->d_lnx, s->tokens, s->targets, s->partials, s->d_norm, s->x_shared,
+                     s->d_score, s->d_lnx, s->xh, s->tokens, s->targets, s->partials, s->d_norm, s->x_shared,
                      s->losses_shared };
     for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
     cudaFreeHost(s->h_grad); cudaFreeHost(s->h_tok); cudaFreeHost(s->h_loss);
@@ -491,7 +570,12 @@ static void forward_device(SFTState *s)
         S_TRY(s, b200_rms_norm_rows(l->x_in, l->g_in, l->ln1, M, s->D, s->eps, st));
         /* the LoRA matrices ride along with the frozen q/k/v weight: the product below also yields
          * mid_q = ln1 A_q^T and mid_v = ln1 A_v^T in the last columns of qkv_out (:639, :652) */
-        S_TRY(s, b200_lora_pack(l->qkv.w, l->qkv.wt, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR, sc, st));
+        if (s->use_tc)
+            S_TRY(s, b200_lora_pack_f16(l->qkv.wh, l->qkv.wth, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR,
+                                        sc, st));
+        else
+            S_TRY(s, b200_lora_pack(l->qkv.w, l->qkv.wt, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR, sc,
+                                    st));
         gemm_fwd(s, l->ln1, &l->qkv, l->qkv_out, NULL);
         /* q += sc * mid_q B_q^T, v += sc * mid_v B_v^T (:641-643, :654-656) */
         S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, 0, s->Hq_hd, l->mid_q, s->QKVX, pB_q, R, sc, M, st));
@@ -549,16 +633,15 @@ static void backward_device(SFTState *s)
          * sc*B_v as extra rows, so the same product leaves tmp_q = sc dq B_q and tmp_v = sc dv B_v (:948-949,
          * :963-964) in columns D.. of d_lnx. */
         const int DX = s->D + s->XR;
-        {
+        if (s->use_tc) {
+            gemm_tc(s, s->dqkv, s->gscale, l->qkv.wth, s->d_lnx, DX, NULL, DX, QKV);
+        } else {
             b200_gemm_args g = {0};
             g.A = s->dqkv; g.a_row = QKV; g.a_col = 1;
             g.B = l->qkv.wt; g.b_row = 1; g.b_col = QKV;
             g.C = s->d_lnx; g.ldc = DX;
             g.M = M; g.N = DX; g.K = QKV; g.alpha = 1.0f;
-            g.d_err = (unsigned *)s->d_norm + 1;
-            int rc = s->use_tc ? b200_gemm_tf32(&g, st) : B200_E_UNSUPPORTED;
-            if (rc == B200_E_UNSUPPORTED) rc = b200_gemm_f32(&g, st);
-            S_TRY(s, rc);
+            S_TRY(s, b200_gemm_f32(&g, st));
         }
         const float *tmp_q = s->d_lnx + s->D, *tmp_v = tmp_q + R;
         /* dB = sc dq^T mid (:946-947, :961-962); dA = tmp^T ln1 (:950, :965) */
@@ -574,7 +657,12 @@ static void backward_device(SFTState *s)
             gemm_small(s, tmp_v, 1, DX, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
         }
         /* d_ln += tmp_q A_q + tmp_v A_v (:951-953, :966, :970): one product over the 2R packed rows of the weight */
-        gemm_small(s, tmp_q, DX, 1, l->qkv.w + (size_t)QKV * s->D, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, 2 * R, 1.0f);
+        if (s->use_tc) {                       /* the packed rows are binary16 there: take A_q, A_v from the LoRA vector */
+            gemm_small(s, tmp_q, DX, 1, pA_q, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, R, 1.0f);
+            gemm_small(s, tmp_v, DX, 1, pA_v, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, R, 1.0f);
+        } else {
+            gemm_small(s, tmp_q, DX, 1, l->qkv.w + (size_t)QKV * s->D, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, 2 * R, 1.0f);
+        }
         /* input norm + residual + clamp (:974-979) */
         S_TRY(s, b200_rms_norm_bwd_rows(l->x_in, s->d_lnx, DX, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, st));
     }
@@ -793,10 +881,9 @@ float llmb200_sft_last_step_ms(SFTState *s, float *update_ms)
 int llmb200_sft_use_tensor_cores(SFTState *s, int on)
 {
     if (!s) return 0;
-    const int prev = s->use_tc;
-    /* the transposed copies exist only when the state was created with tensor cores on */
-    s->use_tc = on && s->lm_head.wt != NULL;
-    return prev;
+    /* the weights are stored for one mode or the other when the state is created */
+    (void)on;
+    return s->use_tc;
 }
 int llmb200_sft_error(SFTState *s) { return s ? s->err : -1; }
 

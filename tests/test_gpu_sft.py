@@ -88,6 +88,43 @@ def test_gemm_tf32_tensor_cores(pkg, lib, M, N, K):
     assert np.abs(got - want).mean() < 1e-3 * np.abs(want - R).mean() + 1e-6
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (70, 200, 104), (512, 2560, 4096), (512, 6176, 256), (512, 19456, 128),
+                                   (128, 256, 4096), (64, 640, 2560)])
+def test_gemm_f16_tensor_cores(pkg, lib, M, N, K):
+    """binary16 operands (the activation copy scaled by a power of two, as the engine does for gradients),
+    fp32 accumulate: against float64 on the same rounded operands the only error is the accumulation's."""
+    rng = np.random.default_rng(M + N + K + 1)
+    A = (rng.standard_normal((M, K)) * 1e-4).astype(np.float32)          # gradient-sized values
+    B = o.f16_round(rng.standard_normal((N, K)) * 0.02)
+    R = rng.standard_normal((M, N)).astype(np.float32)
+    scale = 4096.0
+    dA32, dB32, dR = dev(A), dev(B), dev(R)
+    dAh = torch.zeros(M, K, dtype=torch.float16, device="cuda")
+    dBh = torch.zeros(N, K, dtype=torch.float16, device="cuda")
+    assert lib.b200_f32_to_f16(dA32.data_ptr(), A.size, scale, dAh.data_ptr(), None) == 0
+    assert lib.b200_f32_to_f16(dB32.data_ptr(), B.size, 1.0, dBh.data_ptr(), None) == 0
+    Ah = host(dAh)
+    assert np.array_equal(Ah, (A * np.float32(scale)).astype(np.float16))          # round to nearest even
+    assert np.array_equal(host(dBh).astype(np.float32), B)                          # binary16 values are kept exactly
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dC = torch.full((M, N), 7.0, dtype=torch.float32, device="cuda")
+    g = pkg.GemmArgs()
+    g.A, g.a_row, g.a_col = dAh.data_ptr(), K, 1
+    g.B, g.b_row, g.b_col = dBh.data_ptr(), 1, K
+    g.C, g.ldc, g.R, g.ldr = dC.data_ptr(), N, dR.data_ptr(), N
+    g.M, g.N, g.K, g.alpha, g.d_err = M, N, K, 1.0 / scale, err.data_ptr()
+    assert lib.b200_gemm_f16(C.byref(g), None) == 0
+    got = host(dC)
+    assert int(host(err)[0]) == 0
+    want = (Ah.astype(np.float64) @ B.astype(np.float64).T) / scale + R
+    bound = (np.abs(Ah.astype(np.float64)) @ np.abs(B.astype(np.float64)).T) / scale
+    assert (np.abs(got - want) <= 1e-5 * bound + 1e-6).all()
+    # transposed copy
+    dT = torch.zeros(K, N, dtype=torch.float16, device="cuda")
+    assert lib.b200_transpose_f16(dBh.data_ptr(), N, K, dT.data_ptr(), None) == 0
+    assert np.array_equal(host(dT), host(dBh).T)
+
+
 def test_gemm_tf32_refuses_what_it_cannot_do(pkg, lib):
     g = pkg.GemmArgs()
     x = torch.zeros(256 * 256, device="cuda")
