@@ -158,6 +158,25 @@ int b200_clip_adamw(float *p, float *g, float *m, float *v, size_t n, const doub
                     float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
                     int apply_update, float *norm_out, void *stream);
 
+/* Variants that also (or only) write a binary16 copy of their result, the
+ * operand the next tensor-core product reads, so that no separate conversion
+ * pass is needed. *_h pointers may be NULL; where noted the fp32 output may be
+ * NULL instead. h_scale multiplies the value before it is rounded (gradients
+ * are moved into binary16's range by a power of two). */
+int b200_rms_norm_rows_h(const float *x, const float *gamma, float *out, void *out_h, int rows, int dim, float eps,
+                         void *stream);
+int b200_rms_norm_bwd_rows_h(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx, int rows,
+                             int dim, float eps, int accumulate, float clamp, void *dx_h, float h_scale, void *stream);
+/* out may be NULL when out_h is given */
+int b200_attn_train_fwd_h(const float *q, const float *k, const float *v, long long v_ld, int n_seq, int seq_len,
+                          int n_q, int n_kv, int hd, float scale, float *probs, float *out, void *out_h, void *stream);
+/* act may be NULL when act_h is given; likewise d_gu / d_gu_h */
+int b200_silu_mul_rows_h(const float *gu, int rows, int inter, float *act, void *act_h, void *stream);
+int b200_silu_mul_bwd_rows_h(const float *d_act, const float *gu, int rows, int inter, float *d_gu, void *d_gu_h,
+                             float h_scale, void *stream);
+int b200_softmax_ce_rows_h(const float *logits, const uint32_t *targets, int rows, int vocab, float grad_scale,
+                           float *losses, float *dlogits, void *dlogits_h, float h_scale, void *stream);
+
 #define B200_E_UNSUPPORTED (-4)
 
 #ifdef __cplusplus

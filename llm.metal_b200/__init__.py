@@ -134,7 +134,9 @@ SYMBOLS_MAIN = {
                                 "b200_transpose_f32", "b200_rms_norm_rows", "b200_rms_norm_bwd_rows",
                                 "b200_qk_norm_rope", "b200_qk_norm_rope_bwd", "b200_attn_train_fwd",
                                 "b200_attn_train_bwd", "b200_silu_mul_rows", "b200_silu_mul_bwd_rows", "b200_lora_add", "b200_lora_pack", "b200_xty_skinny",
-                                "b200_softmax_ce_rows", "b200_sumsq_partials", "b200_clip_adamw"],
+                                "b200_softmax_ce_rows", "b200_sumsq_partials", "b200_clip_adamw",
+                                "b200_rms_norm_rows_h", "b200_rms_norm_bwd_rows_h", "b200_attn_train_fwd_h",
+                                "b200_silu_mul_rows_h", "b200_silu_mul_bwd_rows_h", "b200_softmax_ce_rows_h"],
     "llmb200_sft.h": ["sft_state_create", "sft_state_free", "sft_train_step", "forward_to_logits", "sft_backward",
                       "sft_get_logits", "sft_get_dlogits", "sft_get_x_cpu", "sft_get_losses_cpu", "sft_get_seq_len",
                       "sft_get_vocab_size", "sft_get_d_model", "sft_get_lora_rank", "sft_get_n_layers",
@@ -225,6 +227,12 @@ def lib():
         "b200_softmax_ce_rows": (i, [vp, vp, i, i, fl, vp, vp, vp]),
         "b200_sumsq_partials": (i, [vp, sz, vp, i, vp]),
         "b200_clip_adamw": (i, [vp, vp, vp, vp, sz, vp, i, fl, fl, fl, fl, fl, fl, fl, fl, i, vp, vp]),
+        "b200_rms_norm_rows_h": (i, [vp, vp, vp, vp, i, i, fl, vp]),
+        "b200_rms_norm_bwd_rows_h": (i, [vp, vp, ll, vp, vp, i, i, fl, i, fl, vp, fl, vp]),
+        "b200_attn_train_fwd_h": (i, [vp, vp, vp, ll, i, i, i, i, i, fl, vp, vp, vp, vp]),
+        "b200_silu_mul_rows_h": (i, [vp, i, i, vp, vp, vp]),
+        "b200_silu_mul_bwd_rows_h": (i, [vp, vp, i, i, vp, vp, fl, vp]),
+        "b200_softmax_ce_rows_h": (i, [vp, vp, i, i, fl, vp, vp, vp, fl, vp]),
         # ---- llmb200_sft.h
         "sft_state_create": (vp, [vp, i, i, fl]), "sft_state_free": (None, [vp]),
         "sft_train_step": (fl, [vp, c_u32_p, c_u32_p, fl]),

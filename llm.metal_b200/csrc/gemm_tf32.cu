@@ -390,7 +390,7 @@ void pick_tile(int M, int N, int K, int f16, int *bn_out, int *ksub_out, int *sp
         const long long cost = ((tiles + sms - 1) / sms) * (BM + bn);
         if (best < 0 || cost < best || (cost == best && bn > *bn_out)) { best = cost; *bn_out = bn; }
     }
-    *ksub_out = 1;
+    *ksub_out = *bn_out <= 192 ? 2 : 1;       // two sub-tiles per slot as long as two slots still fit
 }
 
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, EpiArgs e, cudaStream_t st)

@@ -72,7 +72,7 @@ __device__ __forceinline__ float group_sum_f(float v, float *sh)
 
 template <int G>
 __global__ void __launch_bounds__(256)
-rms_norm_rows_kernel(const float *x, const float *gamma, float *out, int rows, int dim, float eps)
+rms_norm_rows_kernel(const float *x, const float *gamma, float *out, __half *out_h, int rows, int dim, float eps)
 {
     __shared__ float sh[8];
     const int row = blockIdx.x * (256 / G) + threadIdx.x / G;
@@ -85,13 +85,17 @@ rms_norm_rows_kernel(const float *x, const float *gamma, float *out, int rows, i
     if (!on) return;
     const float inv = rsqrtf(ss / (float)dim + eps);
     float *o = out + (size_t)row * dim;
-    for (int i = l; i < dim; i += G) o[i] = xr[i] * inv * gamma[i];
+    for (int i = l; i < dim; i += G) {
+        const float v = xr[i] * inv * gamma[i];
+        o[i] = v;
+        if (out_h) out_h[(size_t)row * dim + i] = __float2half_rn(v);
+    }
 }
 
 template <int G>
 __global__ void __launch_bounds__(256)
 rms_norm_bwd_rows_kernel(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx, int rows,
-                         int dim, float eps, int accumulate, float clamp)
+                         int dim, float eps, int accumulate, float clamp, __half *dx_h, float h_scale)
 {
     __shared__ float sh[8];
     const int row = blockIdx.x * (256 / G) + threadIdx.x / G;
@@ -115,6 +119,7 @@ rms_norm_bwd_rows_kernel(const float *x, const float *dy, long long dy_ld, const
         if (accumulate) v += o[i];
         if (clamp > 0.f) v = fminf(fmaxf(v, -clamp), clamp);
         o[i] = v;
+        if (dx_h) dx_h[(size_t)row * dim + i] = __float2half_rn(v * h_scale);
     }
 }
 
@@ -205,7 +210,7 @@ constexpr int ATT_WARPS = 4;
 template <int HD>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_train_fwd_kernel(const float *q, const float *k, const float *v, long long v_ld, int n_seq, int N, int n_q,
-                      int n_kv, float scale, float *probs, float *out)
+                      int n_kv, float scale, float *probs, float *out, __half *out_h)
 {
     extern __shared__ float sh[];
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -255,7 +260,8 @@ attn_train_fwd_kernel(const float *q, const float *k, const float *v, long long 
     for (int d = l; d < HD; d += 32) {
         float acc = 0.f;
         for (int j = 0; j <= i; ++j) acc = fmaf(sc[j], v[(row0 + j) * v_ld + (size_t)kvh * HD + d], acc);
-        o[d] = acc;
+        if (out) o[d] = acc;
+        if (out_h) out_h[((row0 + i) * n_q + h) * HD + d] = __float2half_rn(acc);
     }
 }
 
@@ -430,16 +436,17 @@ __device__ __forceinline__ void tile_wb(const float *Wm, const float *B, int n, 
 template <int HD>
 __global__ void __launch_bounds__(256)
 attn_fwd_tile_kernel(const float *q, const float *k, const float *v, long long v_ld, int N, int n_q, int n_kv,
-                     float scale, float *probs, float *out)
+                     float scale, float *probs, float *out, __half *out_h)
 {
     extern __shared__ __align__(16) float sh[];
-    float *Qt = sh, *Kt = Qt + HD * ATP, *Vs = Kt + HD * ATP, *P = Vs + AT * HD;     // P [AT][ATP]
+    // Two operand regions + the score tile: V takes over Q's region once the scores are done, which keeps
+    // the block at ~87 KB (HD 128) so that two blocks share an SM.
+    float *Qt = sh, *Kt = Qt + HD * ATP, *Vs = Qt, *P = Kt + HD * ATP;               // P [AT][ATP]
     const int h = blockIdx.x % n_q, s = blockIdx.x / n_q, kvh = h / (n_q / n_kv);
     const size_t row0 = (size_t)s * N;
     const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
     load_transposed<HD>(Qt, q + (row0 * n_q + h) * HD, (long long)n_q * HD, N);
     load_transposed<HD>(Kt, k + (row0 * n_kv + kvh) * HD, (long long)n_kv * HD, N);
-    load_rows<HD>(Vs, v + row0 * v_ld + (size_t)kvh * HD, v_ld, N);
     __syncthreads();
     float acc[4][4];
     tile_abt<HD>(Qt, Kt, ty, tx, acc);
@@ -450,7 +457,8 @@ attn_fwd_tile_kernel(const float *q, const float *k, const float *v, long long v
             const int i = 4 * ty + a, j = 4 * tx + b;
             P[i * ATP + j] = (j <= i && i < N) ? acc[a][b] * scale : -1e30f;
         }
-    __syncthreads();
+    __syncthreads();                                          // everybody is done with Q: its region becomes V
+    load_rows<HD>(Vs, v + row0 * v_ld + (size_t)kvh * HD, v_ld, N);
     {   // softmax: four threads per row, 16 columns each
         const int i = threadIdx.x / 4, part = threadIdx.x % 4;
         float *pr = P + i * ATP + 16 * part;
@@ -485,9 +493,12 @@ attn_fwd_tile_kernel(const float *q, const float *k, const float *v, long long v
     for (int a = 0; a < 4; ++a) {
         const int i = 4 * ty + a;
         if (i >= N) continue;
-        float *dst = out + ((row0 + i) * n_q + h) * HD + (HD / 16) * tx;
+        const size_t base = ((row0 + i) * n_q + h) * HD + (HD / 16) * tx;
 #pragma unroll
-        for (int c = 0; c < HD / 16; ++c) dst[c] = o[a][c];
+        for (int c = 0; c < HD / 16; ++c) {
+            if (out) out[base + c] = o[a][c];
+            if (out_h) out_h[base + c] = __float2half_rn(o[a][c]);
+        }
     }
 }
 
@@ -498,17 +509,16 @@ attn_bwd_tile_kernel(const float *d_out, const float *probs, const float *q, con
                      long long v_ld, int N, int n_q, int n_kv, float scale, float *dqkv, long long ld, float *part)
 {
     extern __shared__ __align__(16) float sh[];
-    float *dOt = sh, *Vt = dOt + HD * ATP, *dOs = Vt + HD * ATP, *Ks = dOs + AT * HD, *Qs = Ks + AT * HD;
-    float *P = Qs + AT * HD, *dS = P + AT * ATP;
+    // Two operand regions (each holds a transposed [HD][ATP] or a row-major [AT][HD] tile), reloaded as the
+    // four products go by, + the P and dS tiles: ~104 KB for HD 128, so that two blocks share an SM.
+    float *R1 = sh, *R2 = R1 + HD * ATP, *P = R2 + HD * ATP, *dS = P + AT * ATP;
+    float *dOt = R1, *Vt = R2, *Ks = R1, *Qs = R2, *dOs = R1;
     const int h = blockIdx.x % n_q, s = blockIdx.x / n_q, kvh = h / (n_q / n_kv);
     const size_t row0 = (size_t)s * N;
     const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
     const float *dop = d_out + (row0 * n_q + h) * HD;
     load_transposed<HD>(dOt, dop, (long long)n_q * HD, N);
-    load_rows<HD>(dOs, dop, (long long)n_q * HD, N);
     load_transposed<HD>(Vt, v + row0 * v_ld + (size_t)kvh * HD, v_ld, N);
-    load_rows<HD>(Ks, k + (row0 * n_kv + kvh) * HD, (long long)n_kv * HD, N);
-    load_rows<HD>(Qs, q + (row0 * n_q + h) * HD, (long long)n_q * HD, N);
     const float *gp = probs + ((size_t)s * n_q + h) * N * N;
     for (int e = threadIdx.x; e < AT * AT; e += blockDim.x) {
         const int i = e / AT, j = e % AT;
@@ -524,7 +534,9 @@ attn_bwd_tile_kernel(const float *d_out, const float *probs, const float *q, con
             const int i = 4 * ty + a, j = 4 * tx + b;
             dS[i * ATP + j] = (j <= i && i < N) ? acc[a][b] : 0.f;
         }
-    __syncthreads();
+    __syncthreads();                                          // dO^T and V^T are used up: bring in K and Q
+    load_rows<HD>(Ks, k + (row0 * n_kv + kvh) * HD, (long long)n_kv * HD, N);
+    load_rows<HD>(Qs, q + (row0 * n_q + h) * HD, (long long)n_q * HD, N);
     {   // d_score = p * (d_raw - sum_k p_k d_raw_k) * scale, four threads per row
         const int i = threadIdx.x / 4, part4 = threadIdx.x % 4;
         float *dr = dS + i * ATP + 16 * part4;
@@ -557,6 +569,9 @@ attn_bwd_tile_kernel(const float *d_out, const float *probs, const float *q, con
 #pragma unroll
         for (int c = 0; c < HD / 16; ++c) pk[(size_t)j * 2 * HD + (HD / 16) * tx + c] = o[a][c];
     }
+    __syncthreads();                                          // K is used up: its region takes dO, row-major
+    load_rows<HD>(dOs, dop, (long long)n_q * HD, N);
+    __syncthreads();
     tile_wb<HD, true>(P, dOs, N, ty, tx, o);                  // dV_j = sum_i P[i][j] dO_i
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
@@ -587,23 +602,30 @@ __global__ void attn_bwd_reduce_kernel(const float *part, int n_seq, int N, int 
 }
 
 // ---- SwiGLU ------------------------------------------------------------------------------------
-__global__ void silu_mul_rows_kernel(const float *gu, int inter, float *act, size_t total)
+__global__ void silu_mul_rows_kernel(const float *gu, int inter, float *act, __half *act_h, size_t total)
 {
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
         const size_t m = e / inter, i = e % inter;
         const float g = gu[m * 2 * inter + i], u = gu[m * 2 * inter + inter + i];
-        act[e] = g / (1.0f + expf(-g)) * u;
+        const float v = g / (1.0f + expf(-g)) * u;
+        if (act) act[e] = v;
+        if (act_h) act_h[e] = __float2half_rn(v);
     }
 }
 
-__global__ void silu_mul_bwd_rows_kernel(const float *d_act, const float *gu, int inter, float *d_gu, size_t total)
+__global__ void silu_mul_bwd_rows_kernel(const float *d_act, const float *gu, int inter, float *d_gu, __half *d_gu_h,
+                                         float h_scale, size_t total)
 {
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
         const size_t m = e / inter, i = e % inter;
         const float g = gu[m * 2 * inter + i], u = gu[m * 2 * inter + inter + i], dy = d_act[e];
         const float sig = 1.0f / (1.0f + expf(-g));
-        d_gu[m * 2 * inter + i] = dy * u * (sig * (1.0f + g * (1.0f - sig)));
-        d_gu[m * 2 * inter + inter + i] = dy * (g * sig);
+        const float dg = dy * u * (sig * (1.0f + g * (1.0f - sig))), du = dy * (g * sig);
+        if (d_gu) { d_gu[m * 2 * inter + i] = dg; d_gu[m * 2 * inter + inter + i] = du; }
+        if (d_gu_h) {
+            d_gu_h[m * 2 * inter + i] = __float2half_rn(dg * h_scale);
+            d_gu_h[m * 2 * inter + inter + i] = __float2half_rn(du * h_scale);
+        }
     }
 }
 
@@ -672,21 +694,22 @@ __global__ void lora_pack_kernel(T *w_ext, T *wt_ext, const float *A_q, const fl
 
 // ---- rank-R LoRA gradients: C(p, r) = alpha * sum_m X[m, p] * Y[m, r], X wide, Y narrow (R <= MAXR) ------
 // float_matmul_tn of the reference (shaders/q8_kernels.metal:1070-1094) for dB = sc * dY^T mid and
-// dA = tmp^T ln1 (src/nn/fast_sft.c:946-950, 961-965). A block owns 32 columns p; its eight warps take
-// every eighth row m and are summed in warp order through shared memory, so the result does not depend on
-// scheduling. A thread keeps its R sums in registers; the rows of Y are staged in shared memory 4096/MAXR
-// at a time and read as broadcasts; four X loads are in flight per thread.
+// dA = tmp^T ln1 (src/nn/fast_sft.c:946-950, 961-965). A block owns 16 columns p; its sixteen thread groups
+// take every sixteenth row m and are summed in group order through shared memory, so the result does not
+// depend on scheduling. A thread keeps its R sums in registers; the rows of Y are staged in shared memory
+// 4096/MAXR at a time and read as broadcasts; four X loads are in flight per thread.
 template <int MAXR>
 __global__ void __launch_bounds__(256)
 xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y, int rows, int P, int R, float alpha,
                   float *C, long long c_p, long long c_r)
 {
     constexpr int CH = 4096 / MAXR;                      // rows of Y per shared-memory chunk
+    constexpr int PW = 16, NG = 16;                      // columns per block, row groups per block
+    static_assert(MAXR <= 16, "the cross-group buffer is sized for MAXR <= 16");
     __shared__ float ys[CH * MAXR];
-    __shared__ float red[7 * 32 * (MAXR + 1) > 4096 ? 1 : 7 * 32 * (MAXR + 1)];
-    static_assert(MAXR <= 16, "the cross-warp buffer is sized for MAXR <= 16");
-    const int pl = threadIdx.x & 31, mg = threadIdx.x >> 5;
-    const int p = blockIdx.x * 32 + pl;
+    __shared__ float red[(NG - 1) * PW * (MAXR + 1)];
+    const int pl = threadIdx.x % PW, mg = threadIdx.x / PW;
+    const int p = blockIdx.x * PW + pl;
     const bool on = p < P;
     float acc[MAXR];
 #pragma unroll
@@ -701,18 +724,18 @@ xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y
         __syncthreads();
         if (on) {
             int m = mg;
-            for (; m + 24 < cn; m += 32) {               // four rows of this warp in flight
-                const float x0 = X[(size_t)(c0 + m) * ld_x + p], x1 = X[(size_t)(c0 + m + 8) * ld_x + p];
-                const float x2 = X[(size_t)(c0 + m + 16) * ld_x + p], x3 = X[(size_t)(c0 + m + 24) * ld_x + p];
+            for (; m + 3 * NG < cn; m += 4 * NG) {       // four rows of this group in flight
+                const float x0 = X[(size_t)(c0 + m) * ld_x + p], x1 = X[(size_t)(c0 + m + NG) * ld_x + p];
+                const float x2 = X[(size_t)(c0 + m + 2 * NG) * ld_x + p], x3 = X[(size_t)(c0 + m + 3 * NG) * ld_x + p];
 #pragma unroll
                 for (int r = 0; r < MAXR; ++r) {
                     acc[r] = fmaf(x0, ys[m * MAXR + r], acc[r]);
-                    acc[r] = fmaf(x1, ys[(m + 8) * MAXR + r], acc[r]);
-                    acc[r] = fmaf(x2, ys[(m + 16) * MAXR + r], acc[r]);
-                    acc[r] = fmaf(x3, ys[(m + 24) * MAXR + r], acc[r]);
+                    acc[r] = fmaf(x1, ys[(m + NG) * MAXR + r], acc[r]);
+                    acc[r] = fmaf(x2, ys[(m + 2 * NG) * MAXR + r], acc[r]);
+                    acc[r] = fmaf(x3, ys[(m + 3 * NG) * MAXR + r], acc[r]);
                 }
             }
-            for (; m < cn; m += 8) {
+            for (; m < cn; m += NG) {
                 const float x0 = X[(size_t)(c0 + m) * ld_x + p];
 #pragma unroll
                 for (int r = 0; r < MAXR; ++r) acc[r] = fmaf(x0, ys[m * MAXR + r], acc[r]);
@@ -721,7 +744,7 @@ xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y
     }
     if (mg > 0) {
 #pragma unroll
-        for (int r = 0; r < MAXR; ++r) red[((mg - 1) * 32 + pl) * (MAXR + 1) + r] = acc[r];
+        for (int r = 0; r < MAXR; ++r) red[((mg - 1) * PW + pl) * (MAXR + 1) + r] = acc[r];
     }
     __syncthreads();
     if (mg == 0 && on) {
@@ -730,7 +753,7 @@ xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y
             if (r < R) {
                 float v = acc[r];
 #pragma unroll
-                for (int g = 0; g < 7; ++g) v += red[(g * 32 + pl) * (MAXR + 1) + r];
+                for (int g = 0; g < NG - 1; ++g) v += red[(g * PW + pl) * (MAXR + 1) + r];
                 C[(size_t)p * c_p + (size_t)r * c_r] = alpha * v;
             }
         }
@@ -740,7 +763,7 @@ xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y
 // ---- softmax cross-entropy: one block per row ----------------------------------------------------
 __global__ void __launch_bounds__(1024)
 softmax_ce_rows_kernel(const float *logits, const uint32_t *targets, int vocab, float grad_scale, float *losses,
-                       float *dlogits)
+                       float *dlogits, __half *dlogits_h, float h_scale)
 {
     __shared__ float sh[32];
     const size_t off = (size_t)blockIdx.x * vocab;
@@ -758,7 +781,9 @@ softmax_ce_rows_kernel(const float *logits, const uint32_t *targets, int vocab, 
     float *dr = dlogits + off;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
         const float p = expf(lr[i] - lse);
-        dr[i] = (p - ((uint32_t)i == tgt ? 1.0f : 0.0f)) * grad_scale;
+        const float d = (p - ((uint32_t)i == tgt ? 1.0f : 0.0f)) * grad_scale;
+        dr[i] = d;
+        if (dlogits_h) dlogits_h[off + i] = __float2half_rn(d * h_scale);
     }
 }
 
@@ -907,26 +932,43 @@ extern "C" int b200_embed_rows(const float *emb, const uint32_t *tokens, int row
     return done();
 }
 
+extern "C" int b200_rms_norm_rows_h(const float *x, const float *gamma, float *out, void *out_h, int rows, int dim,
+                                    float eps, void *stream)
+{
+    if (!x || !gamma || !out || rows <= 0 || dim <= 0) return B200_E_BADARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    __half *oh = static_cast<__half *>(out_h);
+    if (dim >= 1024) rms_norm_rows_kernel<256><<<rows, 256, 0, st>>>(x, gamma, out, oh, rows, dim, eps);
+    else rms_norm_rows_kernel<32><<<(rows + 7) / 8, 256, 0, st>>>(x, gamma, out, oh, rows, dim, eps);
+    return done();
+}
+
 extern "C" int b200_rms_norm_rows(const float *x, const float *gamma, float *out, int rows, int dim, float eps,
                                   void *stream)
 {
-    if (!x || !gamma || !out || rows <= 0 || dim <= 0) return B200_E_BADARG;
-    if (dim >= 1024) rms_norm_rows_kernel<256><<<rows, 256, 0, (cudaStream_t)stream>>>(x, gamma, out, rows, dim, eps);
-    else rms_norm_rows_kernel<32><<<(rows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(x, gamma, out, rows, dim, eps);
+    return b200_rms_norm_rows_h(x, gamma, out, nullptr, rows, dim, eps, stream);
+}
+
+extern "C" int b200_rms_norm_bwd_rows_h(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx,
+                                        int rows, int dim, float eps, int accumulate, float clamp, void *dx_h,
+                                        float h_scale, void *stream)
+{
+    if (!x || !dy || !gamma || !dx || rows <= 0 || dim <= 0 || dy_ld < dim) return B200_E_BADARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    __half *dh = static_cast<__half *>(dx_h);
+    if (dim >= 1024)
+        rms_norm_bwd_rows_kernel<256><<<rows, 256, 0, st>>>(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate, clamp, dh,
+                                                            h_scale);
+    else
+        rms_norm_bwd_rows_kernel<32><<<(rows + 7) / 8, 256, 0, st>>>(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate,
+                                                                    clamp, dh, h_scale);
     return done();
 }
 
 extern "C" int b200_rms_norm_bwd_rows(const float *x, const float *dy, long long dy_ld, const float *gamma, float *dx,
                                       int rows, int dim, float eps, int accumulate, float clamp, void *stream)
 {
-    if (!x || !dy || !gamma || !dx || rows <= 0 || dim <= 0 || dy_ld < dim) return B200_E_BADARG;
-    cudaStream_t st = (cudaStream_t)stream;
-    if (dim >= 1024)
-        rms_norm_bwd_rows_kernel<256><<<rows, 256, 0, st>>>(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate, clamp);
-    else
-        rms_norm_bwd_rows_kernel<32><<<(rows + 7) / 8, 256, 0, st>>>(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate,
-                                                                    clamp);
-    return done();
+    return b200_rms_norm_bwd_rows_h(x, dy, dy_ld, gamma, dx, rows, dim, eps, accumulate, clamp, nullptr, 1.0f, stream);
 }
 
 extern "C" int b200_qk_norm_rope(const float *qkv, long long ld, const float *q_gamma, const float *k_gamma,
@@ -970,13 +1012,13 @@ static bool attn_shape_ok(int n_seq, int seq_len, int n_q, int n_kv, int hd)
 
 template <int HD>
 static int attn_fwd_launch(const float *q, const float *k, const float *v, long long v_ld, int n_seq, int N, int n_q,
-                           int n_kv, float scale, float *probs, float *out, cudaStream_t st)
+                           int n_kv, float scale, float *probs, float *out, __half *out_h, cudaStream_t st)
 {
     if constexpr (HD <= 128) if (N <= AT) {                   // short sequences: one block per (sequence, head)
-        const size_t tsm = ((size_t)2 * HD * ATP + (size_t)AT * HD + (size_t)AT * ATP) * sizeof(float);
+        const size_t tsm = ((size_t)2 * HD * ATP + (size_t)AT * ATP) * sizeof(float);
         int rc = opt_in_smem(attn_fwd_tile_kernel<HD>, tsm);
         if (rc) return rc;
-        attn_fwd_tile_kernel<HD><<<n_seq * n_q, 256, tsm, st>>>(q, k, v, v_ld, N, n_q, n_kv, scale, probs, out);
+        attn_fwd_tile_kernel<HD><<<n_seq * n_q, 256, tsm, st>>>(q, k, v, v_ld, N, n_q, n_kv, scale, probs, out, out_h);
         return done();
     }
     const size_t smem = (size_t)ATT_WARPS * (HD + N) * sizeof(float);
@@ -984,20 +1026,29 @@ static int attn_fwd_launch(const float *q, const float *k, const float *v, long 
     if (rc) return rc;
     const long long units = (long long)n_seq * n_q * N;
     attn_train_fwd_kernel<HD><<<(unsigned)((units + ATT_WARPS - 1) / ATT_WARPS), ATT_WARPS * 32, smem, st>>>(
-        q, k, v, v_ld, n_seq, N, n_q, n_kv, scale, probs, out);
+        q, k, v, v_ld, n_seq, N, n_q, n_kv, scale, probs, out, out_h);
     return done();
+}
+
+extern "C" int b200_attn_train_fwd_h(const float *q, const float *k, const float *v, long long v_ld, int n_seq,
+                                     int seq_len, int n_q, int n_kv, int hd, float scale, float *probs, float *out,
+                                     void *out_h, void *stream)
+{
+    if (!q || !k || !v || !probs || (!out && !out_h) || !attn_shape_ok(n_seq, seq_len, n_q, n_kv, hd)) return B200_E_BADARG;
+    if ((v_ld & 3) || ((uintptr_t)v & 15) || ((uintptr_t)k & 15)) return B200_E_BADARG;     // 16-byte row loads
+    cudaStream_t st = (cudaStream_t)stream;
+    __half *oh = static_cast<__half *>(out_h);
+    if (hd == 64) return attn_fwd_launch<64>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, oh, st);
+    if (hd == 128) return attn_fwd_launch<128>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, oh, st);
+    return attn_fwd_launch<256>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, oh, st);
 }
 
 extern "C" int b200_attn_train_fwd(const float *q, const float *k, const float *v, long long v_ld, int n_seq,
                                    int seq_len, int n_q, int n_kv, int hd, float scale, float *probs, float *out,
                                    void *stream)
 {
-    if (!q || !k || !v || !probs || !out || !attn_shape_ok(n_seq, seq_len, n_q, n_kv, hd)) return B200_E_BADARG;
-    if ((v_ld & 3) || ((uintptr_t)v & 15) || ((uintptr_t)k & 15)) return B200_E_BADARG;     // 16-byte row loads
-    cudaStream_t st = (cudaStream_t)stream;
-    if (hd == 64) return attn_fwd_launch<64>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, st);
-    if (hd == 128) return attn_fwd_launch<128>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, st);
-    return attn_fwd_launch<256>(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, probs, out, st);
+    if (!out) return B200_E_BADARG;
+    return b200_attn_train_fwd_h(q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, hd, scale, probs, out, nullptr, stream);
 }
 
 template <int HD>
@@ -1007,7 +1058,7 @@ static int attn_bwd_launch(const float *d_out, const float *probs, const float *
 {
     if constexpr (HD <= 128) if (N <= AT) {
         // d_score is used as the per-head dK/dV scratch [S][n_q][N][2][HD] here
-        const size_t tsm = ((size_t)2 * HD * ATP + (size_t)3 * AT * HD + (size_t)2 * AT * ATP) * sizeof(float);
+        const size_t tsm = ((size_t)2 * HD * ATP + (size_t)2 * AT * ATP) * sizeof(float);
         int rc = opt_in_smem(attn_bwd_tile_kernel<HD>, tsm);
         if (rc) return rc;
         attn_bwd_tile_kernel<HD><<<n_seq * n_q, 256, tsm, st>>>(d_out, probs, q, k, v, v_ld, N, n_q, n_kv, scale, dqkv, ld,
@@ -1045,23 +1096,37 @@ extern "C" int b200_attn_train_bwd(const float *d_out, const float *probs, const
     return attn_bwd_launch<256>(d_out, probs, q, k, v, v_ld, n_seq, seq_len, n_q, n_kv, scale, d_score, dqkv, ld, st);
 }
 
-extern "C" int b200_silu_mul_rows(const float *gu, int rows, int inter, float *act, void *stream)
+extern "C" int b200_silu_mul_rows_h(const float *gu, int rows, int inter, float *act, void *act_h, void *stream)
 {
-    if (!gu || !act || rows <= 0 || inter <= 0) return B200_E_BADARG;
+    if (!gu || (!act && !act_h) || rows <= 0 || inter <= 0) return B200_E_BADARG;
     const size_t total = (size_t)rows * inter;
     const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    silu_mul_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gu, inter, act, total);
+    silu_mul_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gu, inter, act, static_cast<__half *>(act_h), total);
+    return done();
+}
+
+extern "C" int b200_silu_mul_rows(const float *gu, int rows, int inter, float *act, void *stream)
+{
+    if (!act) return B200_E_BADARG;
+    return b200_silu_mul_rows_h(gu, rows, inter, act, nullptr, stream);
+}
+
+extern "C" int b200_silu_mul_bwd_rows_h(const float *d_act, const float *gu, int rows, int inter, float *d_gu, void *d_gu_h,
+                                        float h_scale, void *stream)
+{
+    if (!d_act || !gu || (!d_gu && !d_gu_h) || rows <= 0 || inter <= 0) return B200_E_BADARG;
+    const size_t total = (size_t)rows * inter;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    silu_mul_bwd_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_act, gu, inter, d_gu, static_cast<__half *>(d_gu_h),
+                                                                    h_scale, total);
     return done();
 }
 
 extern "C" int b200_silu_mul_bwd_rows(const float *d_act, const float *gu, int rows, int inter, float *d_gu,
                                       void *stream)
 {
-    if (!d_act || !gu || !d_gu || rows <= 0 || inter <= 0) return B200_E_BADARG;
-    const size_t total = (size_t)rows * inter;
-    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    silu_mul_bwd_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_act, gu, inter, d_gu, total);
-    return done();
+    if (!d_gu) return B200_E_BADARG;
+    return b200_silu_mul_bwd_rows_h(d_act, gu, rows, inter, d_gu, nullptr, 1.0f, stream);
 }
 
 extern "C" int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, long long mid_ld,
@@ -1126,17 +1191,25 @@ extern "C" int b200_xty_skinny(const float *X, long long ld_x, const float *Y, l
 {
     if (!X || !Y || !C || rows <= 0 || P <= 0 || R <= 0 || ld_x < P || ld_y < R) return B200_E_BADARG;
     if (R > 16) return B200_E_UNSUPPORTED;               // wider ranks go through b200_gemm_f32
-    xty_skinny_kernel<16><<<(unsigned)((P + 31) / 32), 256, 0, (cudaStream_t)stream>>>(X, ld_x, Y, ld_y, rows, P, R, alpha,
+    xty_skinny_kernel<16><<<(unsigned)((P + 15) / 16), 256, 0, (cudaStream_t)stream>>>(X, ld_x, Y, ld_y, rows, P, R, alpha,
                                                                                         C, c_p, c_r);
+    return done();
+}
+
+extern "C" int b200_softmax_ce_rows_h(const float *logits, const uint32_t *targets, int rows, int vocab,
+                                      float grad_scale, float *losses, float *dlogits, void *dlogits_h, float h_scale,
+                                      void *stream)
+{
+    if (!logits || !targets || !losses || !dlogits || rows <= 0 || vocab <= 0) return B200_E_BADARG;
+    softmax_ce_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, targets, vocab, grad_scale, losses, dlogits,
+                                                                   static_cast<__half *>(dlogits_h), h_scale);
     return done();
 }
 
 extern "C" int b200_softmax_ce_rows(const float *logits, const uint32_t *targets, int rows, int vocab,
                                     float grad_scale, float *losses, float *dlogits, void *stream)
 {
-    if (!logits || !targets || !losses || !dlogits || rows <= 0 || vocab <= 0) return B200_E_BADARG;
-    softmax_ce_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, targets, vocab, grad_scale, losses, dlogits);
-    return done();
+    return b200_softmax_ce_rows_h(logits, targets, rows, vocab, grad_scale, losses, dlogits, nullptr, 1.0f, stream);
 }
 
 extern "C" int b200_sumsq_partials(const float *g, size_t n, double *partials, int n_partials, void *stream)

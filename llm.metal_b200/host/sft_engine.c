@@ -77,6 +77,7 @@ struct SFTState {
     float *dx, *d_ln, *d_lnx, *d_act, *d_gu, *d_att, *dqkv, *d_score;
     void *xh;                   /* binary16 operand copy of the activation / gradient a product reads */
     float gscale;               /* power of two applied to gradient operands before rounding to binary16 */
+    int xh_has_dlogits;         /* the loss kernel has left half(dlogits * gscale) in xh */
     uint32_t *tokens, *targets;
     double *partials;
     float *d_norm;
@@ -216,7 +217,8 @@ static void mat_free(SftMat *m)
 static void gemm_tc(SFTState *s, const float *A, float a_scale, const void *Bh, float *C, long long ldc, const float *R,
                     int N, int K)
 {
-    S_TRY(s, b200_f32_to_f16(A, (size_t)s->M * K, a_scale, s->xh, g_rt.stream));
+    /* A == NULL: the producing kernel has already left the binary16 operand (times a_scale) in xh */
+    if (A) S_TRY(s, b200_f32_to_f16(A, (size_t)s->M * K, a_scale, s->xh, g_rt.stream));
     b200_gemm_args g = {0};
     g.A = (const float *)s->xh; g.a_row = K; g.a_col = 1;
     g.B = (const float *)Bh; g.b_row = 1; g.b_col = K;
@@ -563,11 +565,12 @@ static void forward_device(SFTState *s)
     cudaStream_t st = g_rt.stream;
     const int M = s->M, R = s->lora_rank;
     const float sc = s->lora_scaling, attn_scale = 1.0f / sqrtf((float)s->hd);
+    s->xh_has_dlogits = 0;
     for (int L = 0; L < s->NL; ++L) {
         SftLayer *l = &s->layers[L];
         float *pA_q = s->lora_p + l->lora_off + s->sub_off[0], *pB_q = s->lora_p + l->lora_off + s->sub_off[1];
         float *pA_v = s->lora_p + l->lora_off + s->sub_off[2], *pB_v = s->lora_p + l->lora_off + s->sub_off[3];
-        S_TRY(s, b200_rms_norm_rows(l->x_in, l->g_in, l->ln1, M, s->D, s->eps, st));
+        S_TRY(s, b200_rms_norm_rows_h(l->x_in, l->g_in, l->ln1, s->xh, M, s->D, s->eps, st));
         /* the LoRA matrices ride along with the frozen q/k/v weight: the product below also yields
          * mid_q = ln1 A_q^T and mid_v = ln1 A_v^T in the last columns of qkv_out (:639, :652) */
         if (s->use_tc)
@@ -576,29 +579,33 @@ static void forward_device(SFTState *s)
         else
             S_TRY(s, b200_lora_pack(l->qkv.w, l->qkv.wt, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR, sc,
                                     st));
-        gemm_fwd(s, l->ln1, &l->qkv, l->qkv_out, NULL);
+        gemm_fwd(s, s->use_tc ? NULL : l->ln1, &l->qkv, l->qkv_out, NULL);
         /* q += sc * mid_q B_q^T, v += sc * mid_v B_v^T (:641-643, :654-656) */
         S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, 0, s->Hq_hd, l->mid_q, s->QKVX, pB_q, R, sc, M, st));
         S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, s->Hq_hd + s->Hkv_hd, s->Hkv_hd, l->mid_v, s->QKVX, pB_v, R, sc, M, st));
         S_TRY(s, b200_qk_norm_rope(l->qkv_out, s->QKVX, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv, s->hd,
                                    s->eps, l->q_f, l->k_f, st));
-        S_TRY(s, b200_attn_train_fwd(l->q_f, l->k_f, l->qkv_out + s->Hq_hd + s->Hkv_hd, s->QKVX, s->S, s->N, s->Hq,
-                                     s->Hkv, s->hd, attn_scale, l->probs, s->att, st));
-        gemm_fwd(s, s->att, &l->o, l->x_mid, l->x_in);                       /* + residual (:686) */
-        S_TRY(s, b200_rms_norm_rows(l->x_mid, l->g_post, l->ln2, M, s->D, s->eps, st));
-        gemm_fwd(s, l->ln2, &l->gu, l->gu_out, NULL);
-        S_TRY(s, b200_silu_mul_rows(l->gu_out, M, s->IS, s->act, st));
-        gemm_fwd(s, s->act, &l->down, layer_out(s, L), l->x_mid);            /* + residual (:738) */
+        /* with tensor cores on, the operand of the next product is written as binary16 straight into xh and
+         * the fp32 copy of a tensor nothing else reads (attention output, activation) is not written at all */
+        S_TRY(s, b200_attn_train_fwd_h(l->q_f, l->k_f, l->qkv_out + s->Hq_hd + s->Hkv_hd, s->QKVX, s->S, s->N, s->Hq,
+                                       s->Hkv, s->hd, attn_scale, l->probs, s->use_tc ? NULL : s->att, s->xh, st));
+        gemm_fwd(s, s->use_tc ? NULL : s->att, &l->o, l->x_mid, l->x_in);    /* + residual (:686) */
+        S_TRY(s, b200_rms_norm_rows_h(l->x_mid, l->g_post, l->ln2, s->xh, M, s->D, s->eps, st));
+        gemm_fwd(s, s->use_tc ? NULL : l->ln2, &l->gu, l->gu_out, NULL);
+        S_TRY(s, b200_silu_mul_rows_h(l->gu_out, M, s->IS, s->use_tc ? NULL : s->act, s->xh, st));
+        gemm_fwd(s, s->use_tc ? NULL : s->act, &l->down, layer_out(s, L), l->x_mid);   /* + residual (:738) */
     }
-    S_TRY(s, b200_rms_norm_rows(s->x_final, s->final_g, s->ln_final, M, s->D, s->eps, st));
-    gemm_fwd(s, s->ln_final, &s->lm_head, s->logits, NULL);
+    S_TRY(s, b200_rms_norm_rows_h(s->x_final, s->final_g, s->ln_final, s->xh, M, s->D, s->eps, st));
+    gemm_fwd(s, s->use_tc ? NULL : s->ln_final, &s->lm_head, s->logits, NULL);
 }
 
 static void loss_device(SFTState *s)
 {
     /* 1/N per sequence (:759), and the mean over the S sequences of a step */
     const float gs = 1.0f / ((float)s->N * (float)s->S);
-    S_TRY(s, b200_softmax_ce_rows(s->logits, s->targets, s->M, s->V, gs, s->losses, s->dlogits, g_rt.stream));
+    S_TRY(s, b200_softmax_ce_rows_h(s->logits, s->targets, s->M, s->V, gs, s->losses, s->dlogits, s->xh, s->gscale,
+                                    g_rt.stream));
+    s->xh_has_dlogits = s->use_tc;
 }
 
 /* ---------------------------------------------------------------- backward */
@@ -608,8 +615,12 @@ static void backward_device(SFTState *s)
     cudaStream_t st = g_rt.stream;
     const int M = s->M, R = s->lora_rank, QKV = s->QKV;
     const float sc = s->lora_scaling, attn_scale = 1.0f / sqrtf((float)s->hd);
-    gemm_bwd(s, s->dlogits, &s->lm_head, s->d_ln);                                           /* :777 */
-    S_TRY(s, b200_rms_norm_bwd_rows(s->x_final, s->d_ln, s->D, s->final_g, s->dx, M, s->D, s->eps, 0, 0.f, st));
+    /* the loss kernel leaves the binary16 copy of dlogits in xh; a caller that wrote dlogits itself
+     * (sft_get_dlogits + sft_backward) gets it converted here */
+    gemm_bwd(s, s->xh_has_dlogits ? NULL : s->dlogits, &s->lm_head, s->d_ln);                /* :777 */
+    s->xh_has_dlogits = 0;
+    const float hs = s->gscale;
+    S_TRY(s, b200_rms_norm_bwd_rows_h(s->x_final, s->d_ln, s->D, s->final_g, s->dx, M, s->D, s->eps, 0, 0.f, s->xh, hs, st));
     for (int L = s->NL - 1; L >= 0; --L) {
         SftLayer *l = &s->layers[L];
         float *pA_q = s->lora_p + l->lora_off + s->sub_off[0], *pB_q = s->lora_p + l->lora_off + s->sub_off[1];
@@ -617,12 +628,12 @@ static void backward_device(SFTState *s)
         float *gA_q = s->lora_g + l->lora_off + s->sub_off[0], *gB_q = s->lora_g + l->lora_off + s->sub_off[1];
         float *gA_v = s->lora_g + l->lora_off + s->sub_off[2], *gB_v = s->lora_g + l->lora_off + s->sub_off[3];
         /* FFN (:841-872) */
-        gemm_bwd(s, s->dx, &l->down, s->d_act);
-        S_TRY(s, b200_silu_mul_bwd_rows(s->d_act, l->gu_out, M, s->IS, s->d_gu, st));
-        gemm_bwd(s, s->d_gu, &l->gu, s->d_ln);
-        S_TRY(s, b200_rms_norm_bwd_rows(l->x_mid, s->d_ln, s->D, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, st));
+        gemm_bwd(s, s->use_tc ? NULL : s->dx, &l->down, s->d_act);           /* dx is in xh already */
+        S_TRY(s, b200_silu_mul_bwd_rows_h(s->d_act, l->gu_out, M, s->IS, s->use_tc ? NULL : s->d_gu, s->xh, hs, st));
+        gemm_bwd(s, s->use_tc ? NULL : s->d_gu, &l->gu, s->d_ln);
+        S_TRY(s, b200_rms_norm_bwd_rows_h(l->x_mid, s->d_ln, s->D, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, s->xh, hs, st));
         /* attention (:889-918) */
-        gemm_bwd(s, s->dx, &l->o, s->d_att);
+        gemm_bwd(s, s->use_tc ? NULL : s->dx, &l->o, s->d_att);
         const float *v = l->qkv_out + s->Hq_hd + s->Hkv_hd;
         S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd,
                                      attn_scale, s->d_score, s->dqkv, QKV, st));
@@ -664,7 +675,7 @@ static void backward_device(SFTState *s)
             gemm_small(s, tmp_q, DX, 1, l->qkv.w + (size_t)QKV * s->D, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, 2 * R, 1.0f);
         }
         /* input norm + residual + clamp (:974-979) */
-        S_TRY(s, b200_rms_norm_bwd_rows(l->x_in, s->d_lnx, DX, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, st));
+        S_TRY(s, b200_rms_norm_bwd_rows_h(l->x_in, s->d_lnx, DX, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, s->xh, hs, st));
     }
 }
 
