@@ -377,7 +377,12 @@ void pick_tile(int M, int N, int K, int f16, int *bn_out, int *ksub_out, int *sp
     *splits_out = 1;
     if ((long long)mt * ((N + 127) / 128) <= sms) {
         const long long tiles256 = (long long)mt * ((N + 255) / 256);
-        if (nkb >= 1024 && tiles256 * 3 <= sms && tiles256 <= MAX_SPLIT_TILES) {
+        static int split_nkb = -1;
+        if (split_nkb < 0) {
+            const char *t = getenv("LLMB200_GEMM_SPLIT_NKB");
+            split_nkb = t ? atoi(t) : 1024;
+        }
+        if (nkb >= split_nkb && tiles256 * 3 <= sms && tiles256 <= MAX_SPLIT_TILES) {
             *bn_out = 256; *ksub_out = 1; *splits_out = 3;
         } else {
             *bn_out = 128; *ksub_out = 2;
