@@ -19,30 +19,6 @@ extern unsigned long long g_b200_launches;
 
 namespace {
 
-__device__ __forceinline__ float block_sum_f(float v, float *sh)
-{
-    v = warp_sum(v);
-    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
-    __syncthreads();
-    if (l == 0) sh[w] = v;
-    __syncthreads();
-    float t = 0.f;
-    for (int i = 0; i < nw; ++i) t += sh[i];      // fixed order
-    return t;
-}
-
-__device__ __forceinline__ float block_max_f(float v, float *sh)
-{
-    v = warp_max(v);
-    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
-    __syncthreads();
-    if (l == 0) sh[w] = v;
-    __syncthreads();
-    float t = sh[0];
-    for (int i = 1; i < nw; ++i) t = fmaxf(t, sh[i]);
-    return t;
-}
-
 // ---- embedding -----------------------------------------------------------------------------
 __global__ void embed_rows_kernel(const float *emb, const uint32_t *tokens, int dim, int vocab, float scale, float *x)
 {
@@ -761,29 +737,78 @@ xty_skinny_kernel(const float *X, long long ld_x, const float *Y, long long ld_y
 }
 
 // ---- softmax cross-entropy: one block per row ----------------------------------------------------
+// Two passes over the row instead of the reference's three: the first keeps a running (max, sum of
+// exponentials) per thread (merged across the block in a fixed order), the second writes the gradient.
+// Rows are read four values at a time when the vocabulary allows it.
+__device__ __forceinline__ void lse_add(float &m, float &s, float v)
+{
+    if (v > m) { s = s * expf(m - v) + 1.0f; m = v; }
+    else s += expf(v - m);
+}
+
 __global__ void __launch_bounds__(1024)
 softmax_ce_rows_kernel(const float *logits, const uint32_t *targets, int vocab, float grad_scale, float *losses,
                        float *dlogits, __half *dlogits_h, float h_scale)
 {
-    __shared__ float sh[32];
+    __shared__ float sh_m[32], sh_s[32];
     const size_t off = (size_t)blockIdx.x * vocab;
     const float *lr = logits + off;
     uint32_t tgt = targets[blockIdx.x];
     if (tgt >= (uint32_t)vocab) tgt = 0;
-    float mx = -1e30f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, lr[i]);
-    mx = block_max_f(mx, sh);
-    float sum = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += expf(lr[i] - mx);
-    sum = block_sum_f(sum, sh);
-    const float lse = logf(sum) + mx;
+    const bool vec = (vocab & 3) == 0 && ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(dlogits_h) & 7) == 0;
+    float m = -1e30f, sum = 0.f;
+    if (vec) {
+        const float4 *lr4 = reinterpret_cast<const float4 *>(lr);
+        for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+            const float4 v = lr4[i];
+            lse_add(m, sum, v.x); lse_add(m, sum, v.y); lse_add(m, sum, v.z); lse_add(m, sum, v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) lse_add(m, sum, lr[i]);
+    }
+    // merge (max, sum) pairs: lanes of a warp by shuffles, warps through shared memory in warp order
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m, o), so = __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mn = fmaxf(m, mo);
+        sum = sum * expf(m - mn) + so * expf(mo - mn);
+        m = mn;
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) { sh_m[w] = m; sh_s[w] = sum; }
+    __syncthreads();
+    float M = sh_m[0];
+    for (int i = 1; i < nw; ++i) M = fmaxf(M, sh_m[i]);
+    float S = 0.f;
+    for (int i = 0; i < nw; ++i) S += sh_s[i] * expf(sh_m[i] - M);
+    const float lse = logf(S) + M;
     if (threadIdx.x == 0) losses[blockIdx.x] = lse - lr[tgt];
     float *dr = dlogits + off;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float p = expf(lr[i] - lse);
-        const float d = (p - ((uint32_t)i == tgt ? 1.0f : 0.0f)) * grad_scale;
-        dr[i] = d;
-        if (dlogits_h) dlogits_h[off + i] = __float2half_rn(d * h_scale);
+    if (vec) {
+        const float4 *lr4 = reinterpret_cast<const float4 *>(lr);
+        for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+            const float4 v = lr4[i];
+            float d[4] = {expf(v.x - lse), expf(v.y - lse), expf(v.z - lse), expf(v.w - lse)};
+            if ((uint32_t)i == tgt / 4) d[tgt & 3] -= 1.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) d[c] *= grad_scale;
+            reinterpret_cast<float4 *>(dr)[i] = make_float4(d[0], d[1], d[2], d[3]);
+            if (dlogits_h) {
+                __half2 a = __floats2half2_rn(d[0] * h_scale, d[1] * h_scale), b = __floats2half2_rn(d[2] * h_scale, d[3] * h_scale);
+                uint2 o;
+                o.x = *reinterpret_cast<unsigned *>(&a);
+                o.y = *reinterpret_cast<unsigned *>(&b);
+                reinterpret_cast<uint2 *>(dlogits_h + off)[i] = o;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float p = expf(lr[i] - lse);
+            const float d = (p - ((uint32_t)i == tgt ? 1.0f : 0.0f)) * grad_scale;
+            dr[i] = d;
+            if (dlogits_h) dlogits_h[off + i] = __float2half_rn(d * h_scale);
+        }
     }
 }
 

@@ -258,16 +258,23 @@ def test_silu_lora_add_softmax_ce(lib):
         want[:, col0:col0 + n_cols] += 2.0 * (mid[:, :R] @ B.T)
         assert sc.rel_err(host(dyy), want) < 1e-5
 
-    V = 5000
-    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
-    tg = rng.integers(0, V, rows).astype(np.uint32)
-    dl, dt = dev(logits), dev(tg.view(np.int32))
-    losses, dlog = torch.zeros(rows, device="cuda"), torch.zeros(rows, V, device="cuda")
-    assert lib.b200_softmax_ce_rows(dl.data_ptr(), dt.data_ptr(), rows, V, 0.25, losses.data_ptr(), dlog.data_ptr(),
-                                    None) == 0
-    wl, wd = o.softmax_ce(logits.astype(np.float64), tg.astype(np.int64))
-    assert np.abs(host(losses) - wl).max() < 1e-5
-    assert np.abs(host(dlog) - 0.25 * wd).max() < 1e-6
+    for V in (5000, 5003):                      # four-at-a-time and scalar paths
+        logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+        tg = rng.integers(0, V, rows).astype(np.uint32)
+        dl, dt = dev(logits), dev(tg.view(np.int32))
+        losses, dlog = torch.zeros(rows, device="cuda"), torch.zeros(rows, V, device="cuda")
+        dlog_h = torch.zeros(rows, V, dtype=torch.float16, device="cuda")
+        assert lib.b200_softmax_ce_rows_h(dl.data_ptr(), dt.data_ptr(), rows, V, 0.25, losses.data_ptr(), dlog.data_ptr(),
+                                          dlog_h.data_ptr(), 64.0, None) == 0
+        wl, wd = o.softmax_ce(logits.astype(np.float64), tg.astype(np.int64))
+        assert np.abs(host(losses) - wl).max() < 1e-5
+        got = host(dlog)
+        assert np.abs(got - 0.25 * wd).max() < 1e-6
+        assert np.array_equal(host(dlog_h), (got * np.float32(64.0)).astype(np.float16))
+        dlog2 = torch.zeros(rows, V, device="cuda")
+        assert lib.b200_softmax_ce_rows(dl.data_ptr(), dt.data_ptr(), rows, V, 0.25, losses.data_ptr(), dlog2.data_ptr(),
+                                        None) == 0
+        assert np.array_equal(host(dlog2), got)
 
 
 @pytest.mark.parametrize("rows,P,R", [(512, 4096, 16), (37, 130, 8), (300, 2560, 16), (64, 2560, 3)])
