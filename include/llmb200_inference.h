@@ -66,6 +66,13 @@ void inference_state_load_eos(InferenceState *state, const char *model_path);
 int qwen3_generate_fast(llmb200_qwen3_model *model, const uint32_t *prompt_tokens, int prompt_len,
                         uint32_t *output_tokens, int max_gen_len, int max_seq_len, int use_fp16);
 
+/* Attaches the LoRA matrices of an SFT state (Q and V projections, read in
+ * place on the device) to the decode step: q += s B_q (A_q ln), v += s B_v (A_v ln)
+ * per layer. One GPU only. Replaces inference_state_set_lora
+ * (src/nn/fast_inference.c:496-520; declared in fast_inference.h:56-58). */
+struct SFTState;
+void inference_state_set_lora(InferenceState *state, struct SFTState *sft);
+
 /* ========================= Part 2: additions ============================== */
 
 /* Tensor parallelism. One process per GPU; rank r of `world` holds the r-th

@@ -124,6 +124,9 @@ typedef struct b200_matvec_args {
     /* launch shape: 0 = choose (a multiple of the SM count) */
     int grid;
     int use_pdl;                   /* programmatic dependent launch: prefetch weights under the previous kernel's tail */
+    /* optional: block 0 also stores the assembled (summed, normalised) input vector here, cols floats --
+     * what a LoRA side path multiplies by A (src/nn/fast_inference.c:406-421 reads mb_ln_out) */
+    float *d_in_copy;
 } b200_matvec_args;
 
 int b200_matvec(const b200_matvec_args *a, void *stream);
@@ -241,6 +244,13 @@ typedef struct b200_token_args {
 } b200_token_args;
 
 int b200_decode_token(const b200_token_args *a, void *stream);
+
+/* LoRA side path of one decode token: qkv[0..q_rows) += scaling * B_q (A_q x) and
+ * qkv[q_rows + kv_rows ..) += scaling * B_v (A_v x), with x [d_model] the normalised
+ * layer input (b200_matvec_args.d_in_copy), A [rank, d_model], B [rows, rank],
+ * fp32. Replaces the six per-layer dispatches of src/nn/fast_inference.c:406-421. */
+int b200_lora_decode(const float *x, const float *A_q, const float *B_q, const float *A_v, const float *B_v,
+                     float *qkv, int d_model, int q_rows, int kv_rows, int rank, float scaling, void *stream);
 
 /* Number of kernel launches issued through this ABI since the last reset
  * (what bench.py reports as gpu_launches). */

@@ -54,6 +54,7 @@ class MatvecArgs(C.Structure):
         ("d_epoch", C.c_void_p), ("epoch_mul", C.c_int), ("epoch_add", C.c_int),
         ("d_err", C.c_void_p),
         ("grid", C.c_int), ("use_pdl", C.c_int),
+        ("d_in_copy", C.c_void_p),
     ]
 
 
@@ -118,12 +119,12 @@ SYMBOLS_MAIN = {
                        "metal_buf_free", "metal_buf_ptr", "wmat_create_q8", "wmat_create_f16", "wmat_free", "wmat_convert",
                        "norm_upload", "layers_convert_upload", "layers_free"],
     "llmb200_kernels.h": ["b200_packed_row_stride", "b200_q8_pack", "b200_f16_pack", "b200_q8_unpack_blocks", "b200_matvec",
-                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_op_plan_matvec", "b200_decode_token",
+                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_op_plan_matvec", "b200_decode_token", "b200_lora_decode",
                           "b200_launch_count"],
     "llmb200_inference.h": ["inference_state_create", "inference_state_create_gemma3", "inference_state_free",
                             "inference_generate", "inference_state_model_type", "inference_state_vocab_size",
                             "inference_state_reset", "inference_forward_token", "inference_state_load_eos",
-                            "qwen3_generate_fast", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
+                            "qwen3_generate_fast", "inference_state_set_lora", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
                             "llmb200_state_begin", "llmb200_state_load_layer", "llmb200_state_finish",
                             "llmb200_state_set_eos", "llmb200_last_decode_ms", "llmb200_last_prefill_ms",
                             "llmb200_state_error", "llmb200_state_run_device_steps", "llmb200_state_profile_token",
@@ -185,6 +186,7 @@ def lib():
         "b200_attn_decode_static": (i, [C.POINTER(AttnArgs), vp]),
         "b200_tp_argmax_finalize": (i, [vp, vp, i, vp, vp, i, i, vp, vp, vp, vp, vp, i, vp]),
         "b200_op_plan_matvec": (i, [vp, vp]), "b200_decode_token": (i, [vp, vp]),
+        "b200_lora_decode": (i, [vp, vp, vp, vp, vp, vp, i, i, i, i, fl, vp]),
         "b200_launch_count": (C.c_ulonglong, [i]),
         "inference_state_create": (vp, [vp, i, i]), "inference_state_create_gemma3": (vp, [vp, i, i]),
         "inference_state_free": (None, [vp]),
@@ -193,6 +195,7 @@ def lib():
         "inference_state_reset": (None, [vp]), "inference_forward_token": (c_float_p, [vp, i]),
         "inference_state_load_eos": (None, [vp, C.c_char_p]),
         "qwen3_generate_fast": (i, [vp, c_u32_p, i, c_u32_p, i, i, i]),
+        "inference_state_set_lora": (None, [vp, vp]),
         "llmb200_set_tp": (i, [i, i]), "llmb200_state_comm_handle": (i, [vp, vp]),
         "llmb200_state_connect": (i, [vp, vp, i]),
         "llmb200_state_begin": (vp, [C.POINTER(Config)]),

@@ -226,6 +226,14 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
             for (int e = 0; e < E; ++e) x[s][e] = gm[s][e] * x[s][e] * inv;
     }
     }
+    if (p.d_in_copy && blockIdx.x == 0 && g == 0) {
+#pragma unroll
+        for (int s = 0; s < SPT; ++s)
+#pragma unroll
+            for (int e = 0; e < E; e += 4)
+                if (on[s])
+                    *reinterpret_cast<float4 *>(p.d_in_copy + col[s] + e) = make_float4(x[s][e], x[s][e + 1], x[s][e + 2], x[s][e + 3]);
+    }
     if (geo.share_x) {
         if (g == 0) {
 #pragma unroll

@@ -29,6 +29,7 @@
  */
 #include "internal.h"
 #include "../../include/llmb200_inference.h"
+#include "../../include/llmb200_sft.h"
 
 #include <math.h>
 #include <stdlib.h>
@@ -85,6 +86,11 @@ struct InferenceState {
     cudaGraphExec_t g_full, g_nolm;
     int kernels_full, kernels_nolm;   /* kernel nodes per graph */
     int use_pdl;
+    /* LoRA adapter attached with inference_state_set_lora: device pointers into the SFT state's vectors */
+    struct { const float *A_q, *B_q, *A_v, *B_v; } *lora;
+    int lora_rank;
+    float lora_scaling;
+    float *xnorm;            /* [D]: the normalised layer input, kept by the q/k/v matvec for the LoRA kernel */
     int cur_len;
     double last_decode_ms, last_prefill_ms;
     int last_n_decoded;
@@ -394,8 +400,13 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
         a.d_resid_out = s->resid[1];
         a.d_norm_gamma = ly->g_input;
         a.out_mode = B200_OUT_STORE; a.d_out[0] = s->qkv; a.n_out = 1;
+        if (s->lora) a.d_in_copy = s->xnorm;
         prof_mark(s, K_QKV);
         if (want(s, K_QKV, &a)) K_TRY(b200_matvec(&a, st), return -1);
+        /* q += s B_q (A_q ln), v += s B_v (A_v ln)  (src/nn/fast_inference.c:406-421) */
+        if (s->lora && (s->only_kind < 0 || s->only_kind == K_QKV))
+            K_TRY(b200_lora_decode(s->xnorm, s->lora[l].A_q, s->lora[l].B_q, s->lora[l].A_v, s->lora[l].B_v, s->qkv, D,
+                                   s->Hq_l * s->hd, s->Hkv_l * s->hd, s->lora_rank, s->lora_scaling, st), return -1);
         prof_mark(s, -1);
         /* --- attention --- */
         b200_attn_args at;
@@ -611,7 +622,7 @@ static int ensure_graphs(InferenceState *s)
      * pay a device-wide barrier plus an input broadcast each -- so the graph of per-step kernels is the default. */
     s->fused = 0;
     const char *tk = getenv("LLMB200_TOKEN_KERNEL");
-    if (tk && tk[0] == '1') {
+    if (tk && tk[0] == '1' && !s->lora) {          /* the whole-token kernel has no LoRA side path */
         int pr = build_plan(s);
         if (pr < 0) return -1;
         if (pr == 0) {
@@ -742,6 +753,38 @@ InferenceState *inference_state_create_gemma3(llmb200_gemma3_model *m, int max_s
     return s;
 }
 
+/* Attaches the SFT state's LoRA matrices (Q and V projections) to the decode step; the adapter is read in
+ * place, so later training steps are seen by later tokens. Replaces inference_state_set_lora
+ * (src/nn/fast_inference.c:496-520). One GPU only: with tensor parallelism the call is refused. */
+void inference_state_set_lora(InferenceState *s, SFTState *sft)
+{
+    if (!s || !sft) return;
+    const int R = sft_get_lora_rank(sft);
+    if (R == 0) return;
+    if (s->tp_size != 1) {
+        fprintf(stderr, "[FastGen] inference_state_set_lora: not available with tensor parallelism\n");
+        return;
+    }
+    if (R > 64 || sft_get_n_layers(sft) != s->L || sft_get_d_model(sft) != s->D) {
+        fprintf(stderr, "[FastGen] inference_state_set_lora: adapter does not match the model (layers %d/%d, d_model %d/%d, rank %d)\n",
+                sft_get_n_layers(sft), s->L, sft_get_d_model(sft), s->D, R);
+        return;
+    }
+    if (!s->lora) s->lora = calloc(s->L, sizeof(*s->lora));
+    if (!s->xnorm) CU_TRY(cudaMalloc((void **)&s->xnorm, (size_t)s->D * sizeof(float)), return);
+    if (!s->lora) return;
+    for (int l = 0; l < s->L; ++l) {
+        MetalBuf *b[4];
+        for (int k = 0; k < 4; ++k) b[k] = sft_get_lora_weight_buf(sft, l, k);
+        if (!b[0] || !b[1] || !b[2] || !b[3]) { free(s->lora); s->lora = NULL; return; }
+        s->lora[l].A_q = b[0]->dev; s->lora[l].B_q = b[1]->dev; s->lora[l].A_v = b[2]->dev; s->lora[l].B_v = b[3]->dev;
+    }
+    s->lora_rank = R;
+    s->lora_scaling = sft_get_lora_scaling(sft);
+    if (g_rt.refs > 0) cudaStreamSynchronize(g_rt.stream);
+    free_graphs(s);                      /* the per-token graph gains one kernel per layer */
+}
+
 void inference_state_free(InferenceState *s)
 {
     if (!s) return;
@@ -760,6 +803,8 @@ void inference_state_free(InferenceState *s)
     cudaFree(s->lm.w); cudaFree(s->g_final); cudaFree(s->emb);
     cudaFree(s->resid[0]); cudaFree(s->resid[1]); cudaFree(s->qkv); cudaFree(s->attn_out); cudaFree(s->act);
     cudaFree(s->d_ops); cudaFree(s->d_gbar);
+    cudaFree(s->xnorm);
+    free(s->lora);
     cudaFree(s->attn_scratch); cudaFree(s->am_scratch); cudaFree(s->attn_tickets); cudaFree(s->mv_ticket);
     cudaFree(s->d_pos);
     for (int p = 0; p < s->tp_size; ++p)
