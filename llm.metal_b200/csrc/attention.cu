@@ -24,7 +24,7 @@ extern unsigned long long g_b200_launches;
 
 namespace {
 
-constexpr int ATT_THREADS = 256;
+constexpr int ATT_THREADS = 512;
 
 __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
 {
