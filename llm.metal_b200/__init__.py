@@ -112,7 +112,7 @@ class SynthSpec(C.Structure):
                 ("weight_std", C.c_float), ("gamma_jitter", C.c_float)]
 
 
-# Every symbol include/*.h declares, by header. tests/test_abi_symbols.py checks the lists against the
+# Every symbol include/*.h declares, by header. tests/test_cpu_oracle_and_abi.py checks the lists against the
 # headers and against the built libraries.
 SYMBOLS_MAIN = {
     "llmb200_wmat.h": ["fast_metal_init", "fast_metal_shutdown", "metal_flush", "metal_buf_create", "metal_buf_from_data",
@@ -290,7 +290,7 @@ def synth():
     return S
 
 
-# ---- the architectures BASELINE.json names --------------------------------------------------------
+# ---- the architectures the benchmarks and tests use ------------------------------------------------
 
 def spec(name, seed=1234, gamma_jitter=0.0, **over):
     """SynthSpec of a named architecture. All matrices N(0, 0.02)."""

@@ -1,21 +1,24 @@
 // Tensor-core GEMM for the frozen projections of the LoRA-SFT step (sm_100a only).
 //
-//   C[M,N] = alpha * A[M,K] * B[N,K]^T (+ R),  A, B, C, R fp32 row-major, A and B contiguous along k.
+//   C[M,N] = alpha * A[M,K] * B[N,K]^T (+ R),  C, R fp32 row-major; A and B contiguous along k, either
+//   binary16 (b200_gemm_f16: tcgen05.mma kind::f16) or fp32 read as TF32 (b200_gemm_tf32: kind::tf32).
 //
 // Replaces the reference's scalar tiled products f16_matmul / f16_matmul_nt
 // (shaders/q8_kernels.metal:383-435) for the seven projections and the LM head,
 // forward and backward (the backward product reads a transposed weight copy so
-// that it has the same operand layout). Operands are fp32 in memory; the tensor
-// core reads them as TF32 (10-bit mantissa): weights holding binary16 values
-// are exact, activations are rounded once per product, accumulation is fp32.
+// that it has the same operand layout). The weights hold binary16 values and are
+// exact in either operand format; the activation operand is rounded once per
+// product (11 significant bits either way); accumulation is fp32 in tensor memory.
 //
 // Structure per CTA (one 128 x bn output tile, bn chosen per launch; 192 threads):
-//   warp 0      producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle) of a 128 x 32 A tile and a
-//               BN x 32 B tile per stage into a ring guarded by full/empty mbarriers
-//   warp 1      allocates BN columns of tensor memory; one lane issues tcgen05.mma
-//               (kind::tf32, M=128, N=BN, K=8; four per stage) and tcgen05.commit to
-//               release ring slots and, at the end, to publish the accumulator
-//   warps 2-5   epilogue: tcgen05.ld of the accumulator (lane = row), alpha / residual, stores
+//   warp 0      producer: TMA (cp.async.bulk.tensor.2d, 128B swizzle) of a 128-row A tile and a bn-row
+//               B tile, 128 bytes of k wide, one to three of each per slot of a ring guarded by
+//               full/empty mbarriers
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M=128, N=bn, 32 bytes of k per
+//               instruction, four per sub-tile) and tcgen05.commit to release ring slots and, at the end,
+//               to publish the accumulator
+//   warps 2-5   epilogue: tcgen05.ld of the accumulator (lane = row), alpha / residual, stores; with
+//               split-k the CTAs of a tile add into C one after the other in split order
 // Every wait is bounded; on a timeout the CTA raises *d_err, lets copies in
 // flight land, frees its tensor memory and returns.
 #include "stream_core.cuh"

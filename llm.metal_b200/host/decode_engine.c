@@ -211,6 +211,8 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
     /* sequence splits: enough blocks to cover the GPU, at least 64 keys each at full length */
     s->n_split = 148 / s->Hkv_l;
     if (s->n_split > 32) s->n_split = 32;
+    const char *sp = getenv("LLMB200_ATT_SPLITS");                /* experiments */
+    if (sp && atoi(sp) > 0 && atoi(sp) <= 64) s->n_split = atoi(sp);
     if (s->n_split > (max_seq + 63) / 64) s->n_split = (max_seq + 63) / 64;
     if (s->n_split < 1) s->n_split = 1;
 
