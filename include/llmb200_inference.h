@@ -66,6 +66,16 @@ void inference_state_load_eos(InferenceState *state, const char *model_path);
 int qwen3_generate_fast(llmb200_qwen3_model *model, const uint32_t *prompt_tokens, int prompt_len,
                         uint32_t *output_tokens, int max_gen_len, int max_seq_len, int use_fp16);
 
+/* Batched F16 generation: batch_size (1..32) sequences start from the same
+ * prompt and advance one position per step, sharing one read of the weights.
+ * output_tokens is [batch_size][max_gen_len]; returns the number of tokens
+ * generated per sequence (0 on failure). Stops when every sequence has
+ * produced an EOS id (151645 / 151643) or the cache is full.
+ * Replaces qwen3_generate_fast_batch (src/nn/fast_inference.c:895-985;
+ * fast_inference.h:66-72), whose extra stop on token id 0 is not copied. */
+int qwen3_generate_fast_batch(llmb200_qwen3_model *model, const uint32_t *prompt_tokens, int prompt_len,
+                              uint32_t *output_tokens, int max_gen_len, int max_seq_len, int batch_size);
+
 /* Attaches the LoRA matrices of an SFT state (Q and V projections, read in
  * place on the device) to the decode step: q += s B_q (A_q ln), v += s B_v (A_v ln)
  * per layer. One GPU only. Replaces inference_state_set_lora
@@ -138,6 +148,24 @@ int llmb200_state_graph_kernels(InferenceState *state, int with_lm_head);
  * (interleaved rows g0,u0,g1,u1,...), 3 down, 4 LM head (layer ignored).
  * Returns the byte count, or 0 on error; buf may be NULL to query the size. */
 size_t llmb200_state_export_weight(InferenceState *state, int layer, int which, void *buf, size_t cap);
+
+/* Batched decode state, built layer by layer (cfg->use_fp16 is ignored: weights
+ * are binary16; cfg->max_seq_len is clamped to 4096). Sequences may have
+ * different prompts of one common length: prompts is [batch][prompt_len],
+ * output_tokens [batch][max_gen_len]. */
+typedef struct llmb200_batch_state llmb200_batch_state;
+llmb200_batch_state *llmb200_batch_begin(const llmb200_config *cfg, int batch_size, int max_gen_len);
+int llmb200_batch_load_layer(llmb200_batch_state *state, int layer, const LayerWeightRef *refs, float rope_theta);
+int llmb200_batch_finish(llmb200_batch_state *state, const float *lm_head, const float *final_norm_gamma,
+                         const float *token_emb);
+void llmb200_batch_set_eos(llmb200_batch_state *state, const int *eos, int n);
+int llmb200_batch_generate(llmb200_batch_state *state, const uint32_t *prompts, int prompt_len,
+                           uint32_t *output_tokens, int max_gen_len);
+/* Wall time of the decode loop of the last llmb200_batch_generate and its step count. */
+double llmb200_batch_last_decode_ms(llmb200_batch_state *state, int *n_steps);
+/* The logits [batch][vocab] of the last step, copied to dst (cap floats); NULL if it does not fit. */
+const float *llmb200_batch_logits(llmb200_batch_state *state, float *dst, size_t cap);
+void llmb200_batch_free(llmb200_batch_state *state);
 
 #ifdef __cplusplus
 }

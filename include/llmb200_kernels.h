@@ -154,6 +154,12 @@ typedef struct b200_attn_args {
     int n_q, n_kv, hd, max_seq, n_split;
     float eps;
     int use_pdl;
+    /* Batched form (several sequences at the same position, one launch): n_items > 1 adds a grid
+     * dimension; item i reads d_qkv + i*qkv_item_stride, its own caches at + i*cache_item_stride halves,
+     * writes d_out + i*out_item_stride and uses scratch / tickets slice i (b200_attn_scratch_floats and
+     * n_kv words per item). 0 or 1 = one sequence. */
+    int n_items;
+    long long qkv_item_stride, cache_item_stride, out_item_stride;
 } b200_attn_args;
 
 size_t b200_attn_scratch_floats(int n_q, int hd, int n_split);
@@ -251,6 +257,14 @@ int b200_decode_token(const b200_token_args *a, void *stream);
  * fp32. Replaces the six per-layer dispatches of src/nn/fast_inference.c:406-421. */
 int b200_lora_decode(const float *x, const float *A_q, const float *B_q, const float *A_v, const float *B_v,
                      float *qkv, int d_model, int q_rows, int kv_rows, int rank, float scaling, void *stream);
+
+/* Batched decode: arg-max of each of n_rows logit rows (lowest index on ties,
+ * src/nn/fast_inference.c:469-476) written to next_tokens[row] and, when ctl[2]
+ * is set, to history[ctl[1]*n_rows + row]; the last row to finish then advances
+ * the position ctl[0] (and the step count ctl[1] when recording). done_count is
+ * a zeroed scratch word. */
+int b200_argmax_rows(const float *logits, int n_rows, int vocab, unsigned *next_tokens, unsigned *history,
+                     int max_steps, int *ctl, unsigned *done_count, void *stream);
 
 /* Number of kernel launches issued through this ABI since the last reset
  * (what bench.py reports as gpu_launches). */

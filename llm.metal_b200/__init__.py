@@ -67,6 +67,8 @@ class AttnArgs(C.Structure):
         ("d_pos", C.c_void_p),
         ("n_q", C.c_int), ("n_kv", C.c_int), ("hd", C.c_int), ("max_seq", C.c_int), ("n_split", C.c_int),
         ("eps", C.c_float), ("use_pdl", C.c_int),
+        ("n_items", C.c_int), ("qkv_item_stride", C.c_longlong), ("cache_item_stride", C.c_longlong),
+        ("out_item_stride", C.c_longlong),
     ]
 
 
@@ -112,25 +114,27 @@ class SynthSpec(C.Structure):
                 ("weight_std", C.c_float), ("gamma_jitter", C.c_float)]
 
 
-# Every symbol include/*.h declares, by header. tests/test_cpu_oracle_and_abi.py checks the lists against the
+# Every symbol include/*.h declares, by header. the ABI test under tests/ checks the lists against the
 # headers and against the built libraries.
 SYMBOLS_MAIN = {
     "llmb200_wmat.h": ["fast_metal_init", "fast_metal_shutdown", "metal_flush", "metal_buf_create", "metal_buf_from_data",
                        "metal_buf_free", "metal_buf_ptr", "wmat_create_q8", "wmat_create_f16", "wmat_free", "wmat_convert",
                        "norm_upload", "layers_convert_upload", "layers_free"],
     "llmb200_kernels.h": ["b200_packed_row_stride", "b200_q8_pack", "b200_f16_pack", "b200_q8_unpack_blocks", "b200_matvec",
-                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_op_plan_matvec", "b200_decode_token", "b200_lora_decode",
+                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_op_plan_matvec", "b200_decode_token", "b200_lora_decode", "b200_argmax_rows",
                           "b200_launch_count"],
     "llmb200_inference.h": ["inference_state_create", "inference_state_create_gemma3", "inference_state_free",
                             "inference_generate", "inference_state_model_type", "inference_state_vocab_size",
                             "inference_state_reset", "inference_forward_token", "inference_state_load_eos",
-                            "qwen3_generate_fast", "inference_state_set_lora", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
+                            "qwen3_generate_fast", "qwen3_generate_fast_batch", "inference_state_set_lora", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
                             "llmb200_state_begin", "llmb200_state_load_layer", "llmb200_state_finish",
                             "llmb200_state_set_eos", "llmb200_last_decode_ms", "llmb200_last_prefill_ms",
                             "llmb200_state_error", "llmb200_state_run_device_steps", "llmb200_state_profile_token",
                             "llmb200_state_time_kind", "llmb200_state_step_trace",
                             "llmb200_state_weight_bytes", "llmb200_state_position", "llmb200_state_graph_kernels",
-                            "llmb200_state_export_weight"],
+                            "llmb200_state_export_weight", "llmb200_batch_begin", "llmb200_batch_load_layer",
+                            "llmb200_batch_finish", "llmb200_batch_set_eos", "llmb200_batch_generate",
+                            "llmb200_batch_last_decode_ms", "llmb200_batch_logits", "llmb200_batch_free"],
     "llmb200_train_kernels.h": ["b200_gemm_f32", "b200_gemm_tf32", "b200_gemm_f16", "b200_f32_to_f16", "b200_transpose_f16", "b200_lora_pack_f16", "b200_embed_rows", "b200_round_f16",
                                 "b200_transpose_f32", "b200_rms_norm_rows", "b200_rms_norm_bwd_rows",
                                 "b200_qk_norm_rope", "b200_qk_norm_rope_bwd", "b200_attn_train_fwd",
@@ -187,6 +191,7 @@ def lib():
         "b200_tp_argmax_finalize": (i, [vp, vp, i, vp, vp, i, i, vp, vp, vp, vp, vp, i, vp]),
         "b200_op_plan_matvec": (i, [vp, vp]), "b200_decode_token": (i, [vp, vp]),
         "b200_lora_decode": (i, [vp, vp, vp, vp, vp, vp, i, i, i, i, fl, vp]),
+        "b200_argmax_rows": (i, [vp, i, i, vp, vp, i, vp, vp, vp]),
         "b200_launch_count": (C.c_ulonglong, [i]),
         "inference_state_create": (vp, [vp, i, i]), "inference_state_create_gemma3": (vp, [vp, i, i]),
         "inference_state_free": (None, [vp]),
@@ -196,6 +201,15 @@ def lib():
         "inference_state_load_eos": (None, [vp, C.c_char_p]),
         "qwen3_generate_fast": (i, [vp, c_u32_p, i, c_u32_p, i, i, i]),
         "inference_state_set_lora": (None, [vp, vp]),
+        "qwen3_generate_fast_batch": (i, [vp, c_u32_p, i, c_u32_p, i, i, i]),
+        "llmb200_batch_begin": (vp, [C.POINTER(Config), i, i]),
+        "llmb200_batch_load_layer": (i, [vp, i, C.POINTER(LayerWeightRef), C.c_float]),
+        "llmb200_batch_finish": (i, [vp, c_float_p, c_float_p, c_float_p]),
+        "llmb200_batch_set_eos": (None, [vp, c_int_p, i]),
+        "llmb200_batch_generate": (i, [vp, c_u32_p, i, c_u32_p, i]),
+        "llmb200_batch_last_decode_ms": (C.c_double, [vp, c_int_p]),
+        "llmb200_batch_logits": (c_float_p, [vp, c_float_p, sz]),
+        "llmb200_batch_free": (None, [vp]),
         "llmb200_set_tp": (i, [i, i]), "llmb200_state_comm_handle": (i, [vp, vp]),
         "llmb200_state_connect": (i, [vp, vp, i]),
         "llmb200_state_begin": (vp, [C.POINTER(Config)]),

@@ -21,8 +21,8 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libllmb200.so")
 LIB_SYNTH = os.path.join(HERE, "libllmb200_synth.so")
 
-CU_SOURCES = ["pack.cu", "matvec.cu", "attention.cu", "decode_token.cu", "lora_decode.cu", "gemm_f32.cu", "gemm_tf32.cu", "train_kernels.cu"]
-C_SOURCES = ["weights.c", "decode_engine.c", "sft_engine.c"]
+CU_SOURCES = ["pack.cu", "matvec.cu", "attention.cu", "decode_token.cu", "lora_decode.cu", "batch_kernels.cu", "gemm_f32.cu", "gemm_tf32.cu", "train_kernels.cu"]
+C_SOURCES = ["weights.c", "decode_engine.c", "sft_engine.c", "batch_engine.c"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -44,8 +44,19 @@ __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
 // head are merged (shuffles inside a warp, shared memory across warps).
 template <int HD, int G>
 __global__ void __launch_bounds__(ATT_THREADS)
-attn_decode_kernel(const __grid_constant__ b200_attn_args p, const int chunk_cap)
+attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_cap)
 {
+    // batched form: blockIdx.z selects the sequence; its buffers are slices of the shared ones
+    b200_attn_args p = pa;
+    if (pa.n_items > 1) {
+        const long long it = blockIdx.z;
+        p.d_qkv = pa.d_qkv + it * pa.qkv_item_stride;
+        p.d_k_cache = static_cast<__half *>(pa.d_k_cache) + it * pa.cache_item_stride;
+        p.d_v_cache = static_cast<__half *>(pa.d_v_cache) + it * pa.cache_item_stride;
+        p.d_out = pa.d_out + it * pa.out_item_stride;
+        p.d_scratch = pa.d_scratch + it * (long long)pa.n_q * pa.n_split * (HD + 2);
+        p.d_tickets = pa.d_tickets + it * pa.n_kv;
+    }
     constexpr int DPT = HD / 8;                 // head-dim values per thread
     constexpr int NV = DPT / 8;                 // 16-byte loads per K (and per V) row per thread
     constexpr int TPH = ATT_THREADS / G;        // threads per head group
@@ -281,7 +292,7 @@ int launch_attn(const b200_attn_args &a, cudaStream_t st)
         if (e != cudaSuccess) return (int)e;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.n_split, a.n_kv);
+    cfg.gridDim = dim3(a.n_split, a.n_kv, a.n_items > 1 ? a.n_items : 1);
     cfg.blockDim = dim3(ATT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;

@@ -444,7 +444,7 @@ static int gemm_tc(const b200_gemm_args *a, int f16, void *stream)
     const int gran = f16 ? 7 : 3;                                  // 16-byte granularity of rows and of k
     if ((a->K & gran) || (lda & gran) || (ldb & gran) || lda < a->K || ldb < a->K) return B200_E_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15)) return B200_E_UNSUPPORTED;
-    if (a->N < 64 || a->M < 16) return B200_E_UNSUPPORTED;        // the CUDA-core kernel is the better fit
+    if (a->N < 64) return B200_E_UNSUPPORTED;                     // the CUDA-core kernel is the better fit
     if ((a->N + 63) / 64 > 65535) return B200_E_UNSUPPORTED;
 
     CUtensorMap ma, mb;

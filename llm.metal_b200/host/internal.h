@@ -69,6 +69,8 @@ int llmb200_upload_packed(int wtype, const float *src, long long ld, int rows, i
 float *llmb200_upload_f32(const float *src, size_t n);
 /* Plain fp32 host -> existing device memory through the staging buffers. */
 int llmb200_upload_f32_into(float *d_dst, const float *src, size_t n);
+/* Host fp32 -> existing device memory as binary16 (round to nearest even), through the staging buffers. */
+int llmb200_upload_f16_into(void *d_dst, const float *src, size_t n);
 /* A MetalBuf handle over device memory the caller keeps owning. metal_buf_ptr
  * on it returns a host copy refreshed by every call. */
 MetalBuf *llmb200_buf_wrap(void *dev, size_t size);

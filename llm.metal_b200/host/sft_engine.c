@@ -130,31 +130,12 @@ static void *halloc(SFTState *s, size_t n_halves)
     return p;
 }
 
-/* host fp32 -> device binary16 (round to nearest even) through the runtime's staging buffers */
-static int upload_half(void *d_dst, const float *src, size_t n)
-{
-    const size_t chunk = LLMB200_STAGE_BYTES / sizeof(float);
-    for (size_t o = 0; o < n; o += chunk) {
-        const size_t m = (n - o) < chunk ? (n - o) : chunk;
-        const int sb = g_rt.stage_next;
-        g_rt.stage_next ^= 1;
-        CU_TRY(cudaEventSynchronize(g_rt.stage_done[sb]), return -100);
-        memcpy(g_rt.h_stage[sb], src + o, m * sizeof(float));
-        CU_TRY(cudaMemcpyAsync(g_rt.d_stage[sb], g_rt.h_stage[sb], m * sizeof(float), cudaMemcpyHostToDevice, g_rt.stream),
-               return -101);
-        int rc = b200_f32_to_f16(g_rt.d_stage[sb], m, 1.0f, (char *)d_dst + o * 2, g_rt.stream);
-        if (rc) return rc;
-        CU_TRY(cudaEventRecord(g_rt.stage_done[sb], g_rt.stream), return -102);
-    }
-    return 0;
-}
-
 /* rows of `src` ([rows, cols] fp32, host) into rows row0.. of the device matrix, as binary16 values */
 static int mat_put(SFTState *s, SftMat *m, int row0, const float *src, int rows)
 {
     if (!src) return B200_E_BADARG;
     const size_t off = (size_t)row0 * m->cols, n = (size_t)rows * m->cols;
-    if (s->use_tc) return upload_half((char *)m->wh + off * 2, src, n);
+    if (s->use_tc) return llmb200_upload_f16_into((char *)m->wh + off * 2, src, n);
     int rc = llmb200_upload_f32_into(m->w + off, src, n);
     if (rc) return rc;
     return b200_round_f16(m->w + off, n, g_rt.stream);

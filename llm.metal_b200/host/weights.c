@@ -10,6 +10,7 @@
  * There is no CPU path: without a usable CUDA device every entry point fails.
  */
 #include "internal.h"
+#include "../../include/llmb200_train_kernels.h"
 
 #include <stdlib.h>
 #include <string.h>
@@ -197,6 +198,25 @@ float *llmb200_upload_f32(const float *src, size_t n)
     CU_TRY(cudaMalloc((void **)&d, (n ? n : 1) * sizeof(float)), return NULL);
     if (llmb200_upload_f32_into(d, src, n) != 0) { cudaFree(d); return NULL; }
     return d;
+}
+
+/* host fp32 -> device binary16 (round to nearest even) through the runtime's staging buffers */
+int llmb200_upload_f16_into(void *d_dst, const float *src, size_t n)
+{
+    const size_t chunk = LLMB200_STAGE_BYTES / sizeof(float);
+    for (size_t o = 0; o < n; o += chunk) {
+        const size_t m = (n - o) < chunk ? (n - o) : chunk;
+        const int sb = g_rt.stage_next;
+        g_rt.stage_next ^= 1;
+        CU_TRY(cudaEventSynchronize(g_rt.stage_done[sb]), return -100);
+        memcpy(g_rt.h_stage[sb], src + o, m * sizeof(float));
+        CU_TRY(cudaMemcpyAsync(g_rt.d_stage[sb], g_rt.h_stage[sb], m * sizeof(float), cudaMemcpyHostToDevice, g_rt.stream),
+               return -101);
+        int rc = b200_f32_to_f16(g_rt.d_stage[sb], m, 1.0f, (char *)d_dst + o * 2, g_rt.stream);
+        if (rc) return rc;
+        CU_TRY(cudaEventRecord(g_rt.stage_done[sb], g_rt.stream), return -102);
+    }
+    return 0;
 }
 
 MetalBuf *llmb200_buf_wrap(void *dev, size_t size)
