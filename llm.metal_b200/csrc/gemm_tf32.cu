@@ -427,7 +427,9 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, EpiArgs e, cudaStream_t
         if (rc != cudaSuccess) return (int)rc;
         attr_set = smem;
     }
-    if (cudaGetSymbolAddress((void **)&e.flags, g_split_flags) != cudaSuccess) return B200_E_UNSUPPORTED;
+    static unsigned *flags_addr = nullptr;       // looked up once (the first launch must not be inside a stream capture)
+    if (!flags_addr && cudaGetSymbolAddress((void **)&flags_addr, g_split_flags) != cudaSuccess) return B200_E_UNSUPPORTED;
+    e.flags = flags_addr;
     dim3 grid((e.M + BM - 1) / BM, (e.N + e.bn - 1) / e.bn, e.splits);
     gemm_tf32_kernel<<<grid, GEMM_THREADS, smem, st>>>(ma, mb, e);
     ++g_b200_launches;

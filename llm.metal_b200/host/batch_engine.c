@@ -244,6 +244,14 @@ static void enqueue_step(BState *s)
 static int ensure_graph(BState *s)
 {
     if (s->graph) return 0;
+    /* One eager pass first: kernels set their attributes and look up their symbols on first use, which must
+     * not happen inside a capture. Its side effects (position, tokens, cache row 0) are reset by the caller. */
+    cudaMemsetAsync(s->d_tok, 0, (size_t)s->B * 4, g_rt.stream);
+    enqueue_step(s);
+    if (s->err || cudaStreamSynchronize(g_rt.stream) != cudaSuccess) {
+        fprintf(stderr, "[BatchGen] the first decode step failed\n");
+        return -1;
+    }
     cudaGraph_t g = NULL;
     CU_TRY(cudaStreamBeginCapture(g_rt.stream, cudaStreamCaptureModeThreadLocal), return -1);
     enqueue_step(s);
