@@ -89,7 +89,9 @@ def test_gemm_tf32_tensor_cores(pkg, lib, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (70, 200, 104), (512, 2560, 4096), (512, 6176, 256), (512, 19456, 128),
-                                   (128, 256, 4096), (64, 640, 2560)])
+                                   (128, 256, 4096), (64, 640, 2560),
+                                   # few rows (batched decode: one row per sequence)
+                                   (5, 768, 512), (32, 2560, 9728), (32, 19456, 256), (17, 300, 1000)])
 def test_gemm_f16_tensor_cores(pkg, lib, M, N, K):
     """binary16 operands (the activation copy scaled by a power of two, as the engine does for gradients),
     fp32 accumulate: against float64 on the same rounded operands the only error is the accumulation's."""
