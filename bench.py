@@ -380,15 +380,15 @@ def batch_main(args, rank, local_rank, world):
 
     for _ in range(args.warmup):
         one()
-    L.b200_launch_count(1)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     runs = [one() for _ in range(args.steps)]
     clocks = sampler.stop() if rank == 0 else None
-    launches = int(L.b200_launch_count(0))
     ms = sum(m for m, _ in runs)
     steps = sum(n for _, n in runs)
+    # every step (prompt positions included) replays one graph of this many kernels
+    launches = int(L.llmb200_batch_graph_kernels(st)) * args.steps * (P + G - 1)
     value = steps * B * world / (ms / 1e3)
     per_layer = ((sp.n_q_heads + 2 * sp.n_kv_heads) * hd * D + D * sp.n_q_heads * hd + 3 * IS * D) * 2
     step_bytes = sp.n_layers * per_layer + V * D * 2 + B * sp.n_layers * 2 * sp.n_kv_heads * hd * 2 * (P + G // 2)

@@ -163,6 +163,8 @@ int llmb200_batch_generate(llmb200_batch_state *state, const uint32_t *prompts, 
                            uint32_t *output_tokens, int max_gen_len);
 /* Wall time of the decode loop of the last llmb200_batch_generate and its step count. */
 double llmb200_batch_last_decode_ms(llmb200_batch_state *state, int *n_steps);
+/* Kernel nodes in the per-step CUDA graph (0 before the first generate). */
+int llmb200_batch_graph_kernels(llmb200_batch_state *state);
 /* The logits [batch][vocab] of the last step, copied to dst (cap floats); NULL if it does not fit. */
 const float *llmb200_batch_logits(llmb200_batch_state *state, float *dst, size_t cap);
 void llmb200_batch_free(llmb200_batch_state *state);

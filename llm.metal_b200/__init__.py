@@ -134,7 +134,7 @@ SYMBOLS_MAIN = {
                             "llmb200_state_weight_bytes", "llmb200_state_position", "llmb200_state_graph_kernels",
                             "llmb200_state_export_weight", "llmb200_batch_begin", "llmb200_batch_load_layer",
                             "llmb200_batch_finish", "llmb200_batch_set_eos", "llmb200_batch_generate",
-                            "llmb200_batch_last_decode_ms", "llmb200_batch_logits", "llmb200_batch_free"],
+                            "llmb200_batch_last_decode_ms", "llmb200_batch_graph_kernels", "llmb200_batch_logits", "llmb200_batch_free"],
     "llmb200_train_kernels.h": ["b200_gemm_f32", "b200_gemm_tf32", "b200_gemm_f16", "b200_f32_to_f16", "b200_transpose_f16", "b200_lora_pack_f16", "b200_embed_rows", "b200_round_f16",
                                 "b200_transpose_f32", "b200_rms_norm_rows", "b200_rms_norm_bwd_rows",
                                 "b200_qk_norm_rope", "b200_qk_norm_rope_bwd", "b200_attn_train_fwd",
@@ -208,6 +208,7 @@ def lib():
         "llmb200_batch_set_eos": (None, [vp, c_int_p, i]),
         "llmb200_batch_generate": (i, [vp, c_u32_p, i, c_u32_p, i]),
         "llmb200_batch_last_decode_ms": (C.c_double, [vp, c_int_p]),
+        "llmb200_batch_graph_kernels": (i, [vp]),
         "llmb200_batch_logits": (c_float_p, [vp, c_float_p, sz]),
         "llmb200_batch_free": (None, [vp]),
         "llmb200_set_tp": (i, [i, i]), "llmb200_state_comm_handle": (i, [vp, vp]),

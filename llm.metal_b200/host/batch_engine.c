@@ -44,6 +44,7 @@ struct llmb200_batch_state {
     int finished, err;
     double last_decode_ms;
     int last_steps;
+    int kernels_per_step;
 };
 typedef struct llmb200_batch_state BState;
 
@@ -254,7 +255,9 @@ static int ensure_graph(BState *s)
     }
     cudaGraph_t g = NULL;
     CU_TRY(cudaStreamBeginCapture(g_rt.stream, cudaStreamCaptureModeThreadLocal), return -1);
+    const unsigned long long before = b200_launch_count(0);
     enqueue_step(s);
+    s->kernels_per_step = (int)(b200_launch_count(0) - before);
     cudaError_t e = cudaStreamEndCapture(g_rt.stream, &g);
     if (s->err || e != cudaSuccess || !g) {
         if (g) cudaGraphDestroy(g);
@@ -353,6 +356,8 @@ double llmb200_batch_last_decode_ms(BState *s, int *n_steps)
     if (n_steps) *n_steps = s->last_steps;
     return s->last_decode_ms;
 }
+
+int llmb200_batch_graph_kernels(BState *s) { return s ? s->kernels_per_step : 0; }
 
 const float *llmb200_batch_logits(BState *s, float *dst, size_t cap)
 {
