@@ -43,6 +43,9 @@ WORKLOADS = {
     # name: (architecture, use_fp16, prompt, generate, max_seq)
     "qwen3-4b-q8": ("qwen3-4b", 0, 512, 512, 4096),
     "tiny-qwen3-q8": ("tiny-qwen3", 0, 16, 32, 64),
+    # Gemma3-1B, binary16 weights (src/nn/gemma3.c:11-25): 4-norm blocks, GeGLU, per-layer rope base, tied LM head
+    "gemma3-1b-f16": ("gemma3-1b", 1, 128, 256, 512),
+    "tiny-gemma3-f16": ("tiny-gemma3", 1, 16, 32, 96),
 }
 HBM_FALLBACK_GBS = 6650.0
 
@@ -149,12 +152,14 @@ def build_state_streaming(pkg, L, S, sp, max_seq, use_fp16, threads):
     return st
 
 
-def algorithmic_bytes_per_token(sp, n_attend, world=1):
-    """Bytes one decode token has to move per GPU: Q8_0 weights + gammas + F16 K/V rows + one embedding row."""
+def algorithmic_bytes_per_token(sp, n_attend, world=1, use_fp16=0, gemma=False):
+    """Bytes one decode token has to move per GPU: weights (Q8_0 34 bytes per 32, or binary16) + gammas +
+    F16 K/V rows + one embedding row."""
     D, hd, IS, V, Lr = sp.d_model, sp.head_dim, sp.intermediate_size, sp.vocab_size, sp.n_layers
-    per_layer = ((sp.n_q_heads + 2 * sp.n_kv_heads) * hd * D + D * sp.n_q_heads * hd + 3 * IS * D) * 34 // 32
-    weights = (Lr * per_layer + V * D * 34 // 32) // world
-    gammas = (Lr * (2 * D + 2 * hd) + D) * 4
+    num, den = (2, 1) if use_fp16 else (34, 32)
+    per_layer = ((sp.n_q_heads + 2 * sp.n_kv_heads) * hd * D + D * sp.n_q_heads * hd + 3 * IS * D) * num // den
+    weights = (Lr * per_layer + V * D * num // den) // world
+    gammas = (Lr * ((4 if gemma else 2) * D + 2 * hd) + D) * 4
     kv = Lr * 2 * (sp.n_kv_heads // world) * hd * 2 * n_attend
     return weights + gammas + kv + D * 4
 
@@ -603,13 +608,21 @@ def main():
     if args.layers:
         sp.n_layers = args.layers
     threads = max(1, min(32, (os.cpu_count() or 8) // max(world, 1)))
-    config = {"workload": f"{arch}{'' if not args.layers else f' cut to {args.layers} layers'} Q8_0 batch-1 greedy decode, "
+    gemma = arch.endswith("gemma3") or arch.startswith("gemma3")
+    wname = "F16" if use_fp16 else "Q8_0"
+    if gemma and world > 1:
+        raise SystemExit("the Gemma3 workloads have one KV head: replicas only, run them at --gpus 1")
+    config = {"workload": f"{arch}{'' if not args.layers else f' cut to {args.layers} layers'} {wname} batch-1 greedy decode, "
                           f"prompt {P}, generate {G}, F16 KV cache {max_seq}",
               "prompt_len": P, "gen_len": G, "kv_cache": "f16", "parallelism": f"tp{world}",
               "l2": "inputs larger than L2 (weights streamed per token >> 126 MB); no flush needed"}
 
     if args.impl == "reference":
         if rank != 0:
+            return 0
+        if gemma:
+            emit(json.dumps({"impl": "reference", "unavailable": "the reference has no CPU Gemma3 forward (src/nn/gemma3.c "
+                             "holds create/load only); the checker for this workload is a restatement"}))
             return 0
         cb = cpu_reference_sample(pkg, S, sp, threads)
         line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
@@ -630,7 +643,15 @@ def main():
     if L.llmb200_set_tp(rank, world) != 0:
         raise RuntimeError("llmb200_set_tp failed")
     t0 = time.time()
-    st = build_state_streaming(pkg, L, S, sp, max_seq, use_fp16, threads)
+    if gemma:
+        model = S.llmb200_synth_gemma3(C.byref(sp), threads)
+        st = L.inference_state_create_gemma3(model, max_seq, use_fp16)
+        L.metal_flush()                          # uploads read the host weights until the stream has drained
+        S.llmb200_synth_free_gemma3(model)       # the state holds its own device copies, embedding table included
+        if not st:
+            raise RuntimeError("inference_state_create_gemma3 failed")
+    else:
+        st = build_state_streaming(pkg, L, S, sp, max_seq, use_fp16, threads)
     if world > 1:
         h = (C.c_ubyte * pkg.LLMB200_HANDLE_BYTES)()
         if L.llmb200_state_comm_handle(st, h) != 0:
@@ -711,10 +732,11 @@ def main():
     peak, peak_kind = measured_peaks()
     D, IS = sp.d_model, sp.intermediate_size
     gu_rows, gu_cols = 2 * IS // world, D
-    gu_bytes = gu_rows * gu_cols * 34 // 32 + 4 * gu_cols + 4 * (gu_rows // 2)
+    gu_bytes = gu_rows * gu_cols * (2 if use_fp16 else 34 / 32) + 4 * gu_cols + 4 * (gu_rows // 2)
+    gu_bytes = int(gu_bytes)
     gu_s = 1e-6 * prof["gateup_matvec"]["us_per_launch"]
     achieved = gu_bytes / gu_s / 1e9
-    roofline = {"bound": "hbm", "kernel": "matvec_kernel<Q8> gate/up (rows %d x cols %d)" % (gu_rows, gu_cols),
+    roofline = {"bound": "hbm", "kernel": "matvec_kernel<%s> gate/up (rows %d x cols %d)" % (wname, gu_rows, gu_cols),
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch from the ncu --set full capture
                 # (profiles/matvec_gateup_qwen3-4b_4layers_full.md): 53.01 MB at N=1; the rows, and with them the
@@ -726,12 +748,13 @@ def main():
     value = n_tok / (sum(step_ms) / 1e3)
     e2e_ms = sum(m for m, _ in e2e)
     e2e_tok = sum(n for _, n in e2e)
-    mean_bytes = float(np.mean([algorithmic_bytes_per_token(sp, n, world) for n in range(P + 1, P + G)]))
+    mean_bytes = float(np.mean([algorithmic_bytes_per_token(sp, n, world, use_fp16, gemma) for n in range(P + 1, P + G)]))
     per_token_kernels = L.llmb200_state_graph_kernels(st, 1)
     line = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sum(step_ms) / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32 accumulate over int8 (Q8_0) weights", "data": "synthetic", "config": config,
+        "vs_baseline": None, "dtype": "f32 accumulate over %s weights" % ("binary16" if use_fp16 else "int8 (Q8_0)"),
+        "data": "synthetic", "config": config,
         "e2e": {"value": e2e_tok / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": int(P * 4 + 8),
                 "d2h_bytes_per_step": int(G * 4)},
         "gpu_launches": int(args.steps * (G - 1) * per_token_kernels),
@@ -741,7 +764,7 @@ def main():
         "kernels": prof, "clocks": clocks, "ms_per_token": sum(step_ms) / n_tok, "build_seconds": build_s,
         "first_tokens": first_tokens,
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not gemma:
         if rank == 0:
             line["cpu_baseline"] = cpu_reference_sample(pkg, S, sp, threads)
     L.inference_state_free(st)

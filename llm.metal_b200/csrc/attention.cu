@@ -36,8 +36,9 @@ __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
     }
 }
 
-// Thread layout: the block's 256 threads are split into G head groups; a head group is KL key lanes of
-// 8 threads; the 8 threads of a key lane split the head dimension (DPT = HD/8 values each). A key lane
+// Thread layout: the block's threads are split into G head groups; a head group is KL key lanes of
+// 8 threads (16 for head dimensions above 128); the threads of a key lane split the head dimension
+// (DPT = 16 values each at head dimension 128 and 256). A key lane
 // walks keys kl, kl+KL, ... of the block's slice with its own online softmax (running max, sum and
 // output), so nothing is exchanged between threads while keys stream in; K and V rows are prefetched
 // two keys ahead, the first ones before the query is even normalised. At the end the key lanes of a
@@ -57,10 +58,11 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
         p.d_scratch = pa.d_scratch + it * (long long)pa.n_q * pa.n_split * (HD + 2);
         p.d_tickets = pa.d_tickets + it * pa.n_kv;
     }
-    constexpr int DPT = HD / 8;                 // head-dim values per thread
+    constexpr int DLN = HD > 128 ? 16 : 8;      // threads that share one key (a key lane)
+    constexpr int DPT = HD / DLN;               // head-dim values per thread (at most 16: no register spills)
     constexpr int NV = DPT / 8;                 // 16-byte loads per K (and per V) row per thread
     constexpr int TPH = ATT_THREADS / G;        // threads per head group
-    constexpr int KL = TPH / 8;                 // key lanes per head
+    constexpr int KL = TPH / DLN;               // key lanes per head
     constexpr int WPH = TPH / 32;               // warps per head
     constexpr int HALF = HD / 2;
     constexpr int PF = 2;                       // keys in flight per key lane
@@ -74,7 +76,7 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = ATT_THREADS / 32;
     const int split = blockIdx.x, kvh = blockIdx.y;
-    const int g = tid / TPH, r = tid - g * TPH, kl = r >> 3, dl = r & 7;
+    const int g = tid / TPH, r = tid - g * TPH, kl = r / DLN, dl = r % DLN;
 
     pdl_launch_dependents();
     pdl_wait();
@@ -179,6 +181,7 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (DLN == 16) s += __shfl_xor_sync(0xffffffffu, s, 8);
         s *= scale;
         if (valid) {
             const float mn = fmaxf(m, s);
@@ -198,7 +201,7 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
 
     // ---- merge the key lanes of a head: inside the warp, then across the head's warps ----
 #pragma unroll
-    for (int o = 8; o < 32; o <<= 1) {
+    for (int o = DLN; o < 32; o <<= 1) {
         const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
         const float mn = fmaxf(m, mo);
         const float ca = (m == -INFINITY) ? 0.0f : expf(m - mn), cb = (mo == -INFINITY) ? 0.0f : expf(mo - mn);
@@ -208,7 +211,7 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
         m = mn;
     }
     const int wh = r >> 5;                      // warp index inside the head group
-    if ((r & 31) < 8) {                         // key lane 0 of each warp holds the warp's state
+    if ((r & 31) < DLN) {                       // key lane 0 of each warp holds the warp's state
         float *dst = mrg + ((size_t)g * WPH + wh) * (HD + 2);
 #pragma unroll
         for (int e = 0; e < DPT; ++e) dst[dl * DPT + e] = acc[e];
