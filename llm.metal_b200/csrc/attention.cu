@@ -79,6 +79,16 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
     const int g = tid / TPH, r = tid - g * TPH, kl = r / DLN, dl = r % DLN;
 
     pdl_launch_dependents();
+    // Norm weights and rotation frequencies are constants: fetch them before waiting for the kernel
+    // that produces q/k/v, so that their round trip is not part of the dependent chain.
+    float gq_a[HALF / 32], gq_b[HALF / 32], gk_a[HALF / 32], gk_b[HALF / 32], fr[HALF / 32];
+#pragma unroll
+    for (int j = 0; j < HALF / 32; ++j) {
+        const int d = lane + 32 * j;
+        gq_a[j] = p.d_q_gamma ? p.d_q_gamma[d] : 1.0f; gq_b[j] = p.d_q_gamma ? p.d_q_gamma[d + HALF] : 1.0f;
+        gk_a[j] = p.d_k_gamma ? p.d_k_gamma[d] : 1.0f; gk_b[j] = p.d_k_gamma ? p.d_k_gamma[d + HALF] : 1.0f;
+        fr[j] = p.d_inv_freq[d];
+    }
     pdl_wait();
 
     const int pos = *p.d_pos;
@@ -122,15 +132,14 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
             const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
 #pragma unroll
             for (int j = 0; j < HALF / 32; ++j) {
-                const int d = lane + 32 * j;
-                a[j] = gamma[d] * a[j] * inv; b[j] = gamma[d + HALF] * b[j] * inv;
+                a[j] = (is_k ? gk_a[j] : gq_a[j]) * a[j] * inv; b[j] = (is_k ? gk_b[j] : gq_b[j]) * b[j] * inv;
             }
         }
 #pragma unroll
         for (int j = 0; j < HALF / 32; ++j) {
             const int d = lane + 32 * j;
             float sn, cs;
-            sincosf((float)pos * p.d_inv_freq[d], &sn, &cs);
+            sincosf((float)pos * fr[j], &sn, &cs);
             const float r0 = a[j] * cs - b[j] * sn;
             const float r1 = a[j] * sn + b[j] * cs;
             if (is_k) {
@@ -239,43 +248,50 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
     }
 
     // ---- the last block of this KV head merges the splits ----
-    __threadfence();
+    // The barrier orders every thread's partials before thread 0; its fence (cumulative) then makes
+    // them visible device-wide before the ticket is taken.
     __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(p.d_tickets + kvh, 1u) == (unsigned)p.n_split - 1u);
+    if (tid == 0) {
+        __threadfence();
+        s_last = (atomicAdd(p.d_tickets + kvh, 1u) == (unsigned)p.n_split - 1u);
+        __threadfence();
+    }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
-    // Two short passes instead of one long dependent loop per output: first all (max, sum) pairs are
-    // fetched at once and turned into one weight per (head, split) in shared memory, then every output
-    // is a weighted sum whose loads do not depend on anything and can all be in flight together.
-    float *m_sm = mrg, *w_sm = mrg + G * p.n_split;
-    for (int i = tid; i < G * p.n_split; i += ATT_THREADS) {
-        const int gg = i / p.n_split, s = i - gg * p.n_split;
-        const float *rec = p.d_scratch + ((size_t)(kvh * G + gg) * p.n_split + s) * (HD + 2) + HD;
-        m_sm[i] = __ldcg(rec);
-        w_sm[i] = __ldcg(rec + 1);
+    // Every output element folds the splits with its own running (max, sum, value): the three loads of
+    // a split depend on nothing, so the unrolled loop keeps a batch of them in flight and the whole merge
+    // costs two round trips to L2 instead of one pass for the weights and another for the values.
+    constexpr int NO = (G * HD + ATT_THREADS - 1) / ATT_THREADS;    // outputs per thread, folded side by side
+    constexpr int UN = NO > 1 ? 6 : 9;
+    const float *base[NO];
+    int od[NO];
+    float M[NO], L[NO], O[NO];
+#pragma unroll
+    for (int k = 0; k < NO; ++k) {
+        const int o = min(tid + k * ATT_THREADS, G * HD - 1);      // surplus threads repeat the last output
+        const int gg = o / HD;
+        od[k] = o % HD;
+        base[k] = p.d_scratch + (size_t)(kvh * G + gg) * p.n_split * (HD + 2);
+        M[k] = -INFINITY; L[k] = 0.0f; O[k] = 0.0f;
     }
-    __syncthreads();
-    if (tid < G) {
-        float M = -INFINITY, L = 0.0f;
-        for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, m_sm[tid * p.n_split + s]);
-        for (int s = 0; s < p.n_split; ++s) {
-            const float ls = w_sm[tid * p.n_split + s];
-            const float w = ls > 0.0f ? expf(m_sm[tid * p.n_split + s] - M) : 0.0f;
-            L = fmaf(ls, w, L);
-            w_sm[tid * p.n_split + s] = w;
+#pragma unroll UN
+    for (int s = 0; s < p.n_split; ++s) {
+#pragma unroll
+        for (int k = 0; k < NO; ++k) {
+            const float *rec = base[k] + (size_t)s * (HD + 2);
+            const float ms = __ldcg(rec + HD), ls = __ldcg(rec + HD + 1), as = __ldcg(rec + od[k]);
+            const float Mn = fmaxf(M[k], ms);
+            const float c0 = (M[k] == -INFINITY) ? 0.0f : expf(M[k] - Mn);
+            const float c1 = ls > 0.0f ? expf(ms - Mn) : 0.0f;
+            L[k] = fmaf(L[k], c0, ls * c1);
+            O[k] = fmaf(O[k], c0, as * c1);
+            M[k] = Mn;
         }
-        const float inv = 1.0f / L;
-        for (int s = 0; s < p.n_split; ++s) w_sm[tid * p.n_split + s] *= inv;
     }
-    __syncthreads();
-    for (int o = tid; o < G * HD; o += ATT_THREADS) {
-        const int gg = o / HD, d = o % HD;
-        const float *base = p.d_scratch + (size_t)(kvh * G + gg) * p.n_split * (HD + 2) + d;
-        float acc2 = 0.0f;
-#pragma unroll 8
-        for (int s = 0; s < p.n_split; ++s) acc2 = fmaf(__ldcg(base + (size_t)s * (HD + 2)), w_sm[gg * p.n_split + s], acc2);
-        p.d_out[(size_t)(kvh * G + gg) * HD + d] = acc2;
+#pragma unroll
+    for (int k = 0; k < NO; ++k) {
+        const int o = tid + k * ATT_THREADS;
+        if (o < G * HD) p.d_out[(size_t)(kvh * G) * HD + o] = O[k] / L[k];
     }
     if (tid == 0) p.d_tickets[kvh] = 0u;
 }

@@ -111,6 +111,20 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
 #pragma unroll
     for (int s = 0; s < SPT; ++s) { col[s] = (s * T + t) * E; on[s] = col[s] < p.cols; }
 
+    // The norm weights are constants: their round trip is taken before the wait for the previous
+    // kernel, not after it.
+    float gm[SPT][E];
+    const bool pre_gamma = p.d_norm_gamma && (!geo.share_x || g == 0);
+    if (pre_gamma) {
+#pragma unroll
+        for (int s = 0; s < SPT; ++s)
+#pragma unroll
+            for (int e = 0; e < E; e += 4) {
+                float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(p.d_norm_gamma + col[s] + e) : make_float4(0, 0, 0, 0);
+                gm[s][e] = v4.x; gm[s][e + 1] = v4.y; gm[s][e + 2] = v4.z; gm[s][e + 3] = v4.w;
+            }
+    }
+
     pdl_wait();
 
     // Tensor parallel: every rank's partial vector must have landed in `slots`
@@ -204,15 +218,6 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
         }
     }
     if (p.d_norm_gamma) {
-        // gamma is fetched before the reduction so that its latency hides behind the barriers
-        float gm[SPT][E];
-#pragma unroll
-        for (int s = 0; s < SPT; ++s)
-#pragma unroll
-            for (int e = 0; e < E; e += 4) {
-                float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(p.d_norm_gamma + col[s] + e) : make_float4(0, 0, 0, 0);
-                gm[s][e] = v4.x; gm[s][e + 1] = v4.y; gm[s][e + 2] = v4.z; gm[s][e + 3] = v4.w;
-            }
         float ss = 0.0f;
 #pragma unroll
         for (int s = 0; s < SPT; ++s)
