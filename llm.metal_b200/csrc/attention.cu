@@ -91,6 +91,23 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
     }
     pdl_wait();
 
+    // The new q/k/v rows do not depend on the position: their loads go out before the position is read,
+    // so that the two round trips overlap. Warp vi < G takes query head vi, warp G the new key and value.
+    static_assert(ATT_THREADS / 32 > G, "one warp per new row");
+    const bool row_k = (warp == G);
+    float ra[HALF / 32], rb[HALF / 32], rv[HD / 32];
+    if (warp <= G) {
+        const float *src = row_k ? p.d_qkv + (size_t)p.n_q * HD + (size_t)kvh * HD
+                                 : p.d_qkv + (size_t)(kvh * G + warp) * HD;
+#pragma unroll
+        for (int j = 0; j < HALF / 32; ++j) { ra[j] = src[lane + 32 * j]; rb[j] = src[lane + 32 * j + HALF]; }
+        if (row_k) {
+            const float *vsrc = p.d_qkv + (size_t)(p.n_q + p.n_kv) * HD + (size_t)kvh * HD;
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) rv[j] = vsrc[lane + 32 * j];
+        }
+    }
+
     const int pos = *p.d_pos;
     const int n = pos + 1;
     const int chunk = (n + p.n_split - 1) / p.n_split;
@@ -114,25 +131,18 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
     fetch(kq1, vq1, j0 + kl + KL);
 
     // ---- normalise + rotate the G query heads and the new key; fetch the new value ----
-    for (int vi = warp; vi <= G; vi += nw) {
-        const bool is_k = (vi == G);
-        const float *src = is_k ? p.d_qkv + (size_t)p.n_q * HD + (size_t)kvh * HD
-                                : p.d_qkv + (size_t)(kvh * G + vi) * HD;
-        const float *gamma = is_k ? p.d_k_gamma : p.d_q_gamma;
-        float a[HALF / 32], b[HALF / 32];
+    if (warp <= G) {
+        const int vi = warp;
+        const bool is_k = row_k;
         float ss = 0.0f;
 #pragma unroll
-        for (int j = 0; j < HALF / 32; ++j) {
-            const int d = lane + 32 * j;
-            a[j] = src[d]; b[j] = src[d + HALF];
-            ss = fmaf(a[j], a[j], ss); ss = fmaf(b[j], b[j], ss);
-        }
+        for (int j = 0; j < HALF / 32; ++j) { ss = fmaf(ra[j], ra[j], ss); ss = fmaf(rb[j], rb[j], ss); }
         ss = warp_sum(ss);
-        if (gamma) {
+        if (is_k ? p.d_k_gamma != nullptr : p.d_q_gamma != nullptr) {
             const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
 #pragma unroll
             for (int j = 0; j < HALF / 32; ++j) {
-                a[j] = (is_k ? gk_a[j] : gq_a[j]) * a[j] * inv; b[j] = (is_k ? gk_b[j] : gq_b[j]) * b[j] * inv;
+                ra[j] = (is_k ? gk_a[j] : gq_a[j]) * ra[j] * inv; rb[j] = (is_k ? gk_b[j] : gq_b[j]) * rb[j] * inv;
             }
         }
 #pragma unroll
@@ -140,8 +150,8 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
             const int d = lane + 32 * j;
             float sn, cs;
             sincosf((float)pos * fr[j], &sn, &cs);
-            const float r0 = a[j] * cs - b[j] * sn;
-            const float r1 = a[j] * sn + b[j] * cs;
+            const float r0 = ra[j] * cs - rb[j] * sn;
+            const float r1 = ra[j] * sn + rb[j] * cs;
             if (is_k) {
                 const __half h0 = __float2half_rn(r0), h1 = __float2half_rn(r1);
                 k_new[d] = __half2float(h0); k_new[d + HALF] = __half2float(h1);
@@ -151,9 +161,10 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
             }
         }
         if (is_k) {
-            const float *vsrc = p.d_qkv + (size_t)(p.n_q + p.n_kv) * HD + (size_t)kvh * HD;
-            for (int d = lane; d < HD; d += 32) {
-                const __half h = __float2half_rn(vsrc[d]);
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) {
+                const int d = lane + 32 * j;
+                const __half h = __float2half_rn(rv[j]);
                 v_new[d] = __half2float(h);
                 if (split == 0) vc[(size_t)pos * HD + d] = h;
             }
@@ -262,7 +273,7 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
     // a split depend on nothing, so the unrolled loop keeps a batch of them in flight and the whole merge
     // costs two round trips to L2 instead of one pass for the weights and another for the values.
     constexpr int NO = (G * HD + ATT_THREADS - 1) / ATT_THREADS;    // outputs per thread, folded side by side
-    constexpr int UN = NO > 1 ? 6 : 9;
+    constexpr int UN = NO > 1 ? 9 : 18;
     const float *base[NO];
     int od[NO];
     float M[NO], L[NO], O[NO];
