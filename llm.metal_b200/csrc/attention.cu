@@ -285,18 +285,51 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
         base[k] = p.d_scratch + (size_t)(kvh * G + gg) * p.n_split * (HD + 2);
         M[k] = -INFINITY; L[k] = 0.0f; O[k] = 0.0f;
     }
-#pragma unroll UN
-    for (int s = 0; s < p.n_split; ++s) {
+    // Batches of UN splits, all loads of a batch issued before the first use; a short last batch repeats
+    // the final split's addresses (valid memory) and drops the values.
+    if (p.n_split == UN) {
+        // the usual split count (one split per SM at 8 KV heads): no clamping, no predicates
 #pragma unroll
-        for (int k = 0; k < NO; ++k) {
-            const float *rec = base[k] + (size_t)s * (HD + 2);
-            const float ms = __ldcg(rec + HD), ls = __ldcg(rec + HD + 1), as = __ldcg(rec + od[k]);
-            const float Mn = fmaxf(M[k], ms);
-            const float c0 = (M[k] == -INFINITY) ? 0.0f : expf(M[k] - Mn);
-            const float c1 = ls > 0.0f ? expf(ms - Mn) : 0.0f;
-            L[k] = fmaf(L[k], c0, ls * c1);
-            O[k] = fmaf(O[k], c0, as * c1);
-            M[k] = Mn;
+        for (int s = 0; s < UN; ++s) {
+#pragma unroll
+            for (int k = 0; k < NO; ++k) {
+                const float *rec = base[k] + (size_t)s * (HD + 2);
+                const float ms = __ldcg(rec + HD), ls = __ldcg(rec + HD + 1), as = __ldcg(rec + od[k]);
+                const float Mn = fmaxf(M[k], ms);
+                const float c0 = (M[k] == -INFINITY) ? 0.0f : expf(M[k] - Mn);
+                const float c1 = ls > 0.0f ? expf(ms - Mn) : 0.0f;
+                L[k] = fmaf(L[k], c0, ls * c1);
+                O[k] = fmaf(O[k], c0, as * c1);
+                M[k] = Mn;
+            }
+        }
+    } else
+    for (int s0 = 0; s0 < p.n_split; s0 += UN) {
+        float2 ml[UN][NO];
+        float av[UN][NO];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int sc = min(s0 + u, p.n_split - 1);
+#pragma unroll
+            for (int k = 0; k < NO; ++k) {
+                const float *rec = base[k] + (size_t)sc * (HD + 2);
+                ml[u][k] = __ldcg(reinterpret_cast<const float2 *>(rec + HD));
+                av[u][k] = __ldcg(rec + od[k]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const bool valid = s0 + u < p.n_split;
+#pragma unroll
+            for (int k = 0; k < NO; ++k) {
+                const float ms = ml[u][k].x, ls = valid ? ml[u][k].y : 0.0f;
+                const float Mn = ls > 0.0f ? fmaxf(M[k], ms) : M[k];
+                const float c0 = (M[k] == -INFINITY) ? 0.0f : expf(M[k] - Mn);
+                const float c1 = ls > 0.0f ? expf(ms - Mn) : 0.0f;
+                L[k] = fmaf(L[k], c0, ls * c1);
+                O[k] = fmaf(O[k], c0, av[u][k] * c1);
+                M[k] = Mn;
+            }
         }
     }
 #pragma unroll
@@ -352,6 +385,7 @@ extern "C" int b200_attn_decode(const b200_attn_args *ap, void *stream)
     if (a.n_q <= 0 || a.n_kv <= 0 || a.n_q % a.n_kv || a.max_seq <= 0 || a.n_split <= 0 || a.n_split > 1024)
         return B200_E_BADARG;
     if (((uintptr_t)a.d_k_cache % 16) || ((uintptr_t)a.d_v_cache % 16)) return B200_E_BADARG;
+    if ((uintptr_t)a.d_scratch % 8) return B200_E_BADARG;       // (max, sum) pairs are read as one 8-byte load
     const int G = a.n_q / a.n_kv;
     cudaStream_t st = (cudaStream_t)stream;
 #define B200_ATT(HD_, G_) if (a.hd == HD_ && G == G_) return launch_attn<HD_, G_>(a, st)
