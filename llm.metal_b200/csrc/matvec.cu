@@ -332,9 +332,11 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
 
     // ---------------- last-block bookkeeping ----------------
     if (p.d_argmax_scratch && wg == 0 && lane < RB) { am_v[g * RB + lane] = best_v; am_i[g * RB + lane] = best_i; }
-    __threadfence_system();
+    // The barrier orders every thread's stores (peers' slots included) before thread 0; its system-wide
+    // fence is cumulative, so one fence per block publishes them all before the ticket is taken.
     named_barrier(1, nC);
     if (tid == 0) {
+        __threadfence_system();
         if (p.d_argmax_scratch) {
             float bv = am_v[0]; int bi = am_i[0];
             for (int k = 1; k < NG * RB; ++k) if (better(am_v[k], am_i[k], bv, bi)) { bv = am_v[k]; bi = am_i[k]; }

@@ -210,7 +210,7 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
 
     /* sequence splits: enough blocks to cover the GPU, at least 64 keys each at full length */
     s->n_split = 148 / s->Hkv_l;
-    if (s->n_split > 32) s->n_split = 32;
+    if (s->n_split > 18) s->n_split = 18;                       /* the merge folds up to 18 splits from one batch of loads */
     const char *sp = getenv("LLMB200_ATT_SPLITS");                /* experiments */
     if (sp && atoi(sp) > 0 && atoi(sp) <= 64) s->n_split = atoi(sp);
     if (s->n_split > (max_seq + 63) / 64) s->n_split = (max_seq + 63) / 64;
