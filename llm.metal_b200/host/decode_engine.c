@@ -210,10 +210,13 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
 
     /* sequence splits: enough blocks to cover the GPU, at least 64 keys each at full length */
     s->n_split = 148 / s->Hkv_l;
-    if (s->n_split > 18) s->n_split = 18;                       /* the merge folds up to 18 splits from one batch of loads */
+    {   /* the merge folds one batch of splits without predicates: 18, or 9 where a thread owns two outputs */
+        const int batch = (s->Hq_l / s->Hkv_l) * s->hd > 512 ? 9 : 18;
+        if (s->n_split > batch) s->n_split = batch;
+    }
     const char *sp = getenv("LLMB200_ATT_SPLITS");                /* experiments */
     if (sp && atoi(sp) > 0 && atoi(sp) <= 64) s->n_split = atoi(sp);
-    if (s->n_split > (max_seq + 63) / 64) s->n_split = (max_seq + 63) / 64;
+    if (s->n_split > (max_seq + 31) / 32) s->n_split = (max_seq + 31) / 32;    /* at least 32 cache rows per split */
     if (s->n_split < 1) s->n_split = 1;
 
     s->resid[0] = dev_zero((size_t)s->D * 4);
