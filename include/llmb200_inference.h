@@ -134,9 +134,11 @@ int llmb200_state_profile_token(InferenceState *state, float *ms, int *launches)
  * different layer's weights, so nothing is served from L2. Returns the elapsed milliseconds for
  * *launches launches (negative on error). The token state is left untouched. */
 float llmb200_state_time_kind(InferenceState *state, int kind, int reps, int *launches);
-/* Step trace of the last whole-token launch (only when LLMB200_TRACE=1 was set at create time): start
- * end, input-ready and first-weights-ready nanosecond stamps of each step on block 0, 4 words per step. Returns steps copied. */
-int llmb200_state_step_trace(InferenceState *state, unsigned long long *out, int cap_steps);
+/* Stage trace of the last whole-token launch (only when LLMB200_TRACE=1 was set at create time): for
+ * every block and stage 16 words (b200_token_args.d_trace), laid out
+ * [block][stage][16], stages = 6 per layer (q/k/v, attention, o, gate/up, down, one unused) + the LM head.
+ * Copies at most cap_words words; returns the number of blocks, 0 when there is no trace. */
+int llmb200_state_step_trace(InferenceState *state, unsigned long long *out, size_t cap_words);
 /* Bytes of weights one token streams on this rank (all matrices + LM head). */
 unsigned long long llmb200_state_weight_bytes(InferenceState *state);
 int llmb200_state_position(InferenceState *state);

@@ -191,63 +191,112 @@ int b200_tp_argmax_finalize(const float *d_vals, const int *d_idx, int n_ranks,
  * Whole-token kernel: every matvec and attention step of one token in ONE
  * persistent launch (one block per SM, cooperative). Replaces the reference's
  * single command buffer with its barrier after every dispatch
- * (src/nn/fast_metal.m:223-247; op sequence src/nn/fast_inference.c:394-466):
- * here the steps are separated by device-wide barriers inside the kernel,
- * while a producer warp keeps streaming the weights of the coming steps into
- * the shared-memory ring, so HBM stays busy across step boundaries.
+ * (src/nn/fast_metal.m:223-247; op sequence src/nn/fast_inference.c:394-466).
  *
- * The caller describes the token as an array of b200_op in device memory
- * (same field meaning as b200_matvec_args / b200_attn_args); geometry fields
- * are filled by b200_op_plan_matvec. All matrices of a plan share one wtype.
+ * Structure: per layer five stages (q/k/v matvec, attention, o matvec, gate/up
+ * matvec, down matvec), then the LM head. A producer warp per block streams
+ * the block's share of every stage's weights, in stage order, through one
+ * shared-memory ring with bulk copies; it depends on no activation, so it runs
+ * ahead across stage boundaries and HBM stays busy while the consumers hand a
+ * stage's result over. Hand-over is through "flagged" vectors in global
+ * memory: every fp32 value travels as an 8-byte word {value, flag} written
+ * with one store, flag = epoch * (n_layers + 1) + layer + 1; a reader polls
+ * the word until the flag matches, so data and readiness arrive in the same
+ * round trip to L2 and no device-wide barrier exists. The residual stream is
+ * kept by every block in its own shared memory and updated from the flagged
+ * o / down outputs ("slots", one per tensor-parallel rank, summed in rank
+ * order). Every wait is bounded (spin_limit); a wait that runs out raises
+ * *d_err and the block's abort flag, after which all later waits fall through.
+ *
+ * b200_flagged is the 8-byte word: low half the fp32 bits, high half the flag.
  * ---------------------------------------------------------------------- */
-enum { B200_OP_MATVEC = 0, B200_OP_ATTN = 1 };
+typedef unsigned long long b200_flagged;
+#define B200_CNT_STRIDE 32
+enum { B200_CNT_QKV = 0, B200_CNT_ATTN = 1, B200_CNT_ACT = 2, B200_CNT_SLOTS_O = 3, B200_CNT_SLOTS_DN = 4, B200_CNT_PART = 8 };
 
-typedef struct b200_op {
-    int type;
-    /* matvec: weights + geometry */
-    const void *d_w; long long row_stride; int rows, cols;
-    int rb, T, NG, spt;
-    /* matvec: input assembly */
-    int in_mode;
-    const float *d_in_vec; const float *d_resid_in; float *d_resid_out;
-    const float *d_slots; int n_slots; long long slot_stride;
-    const float *d_slot_norm_gamma; const float *d_norm_gamma;
-    /* matvec: output */
-    int out_mode, act;
-    float *d_out[B200_MAX_PEERS]; int n_out; long long out_offset;
-    int argmax;                                   /* 1: this step picks the next token id (LM head) */
-    /* tensor-parallel hand-shake around this step */
-    const unsigned *d_wait_flags; int n_wait, wait_add;
-    unsigned *d_signal_flags[B200_MAX_PEERS]; int n_signal, signal_index, signal_add;
-    /* attention */
-    const float *d_qkv; const float *d_q_gamma; const float *d_k_gamma; const float *d_inv_freq;
-    void *d_k_cache; void *d_v_cache; float *d_attn_out;
-} b200_op;
+/* Pointers of one layer (device table, n_layers entries). Gammas may be NULL where the
+ * architecture has none (pre_ff / post_ff outside Gemma3, q/k norm when absent). */
+typedef struct b200_token_layer {
+    const void *w_qkv, *w_o, *w_gateup, *w_down;     /* packed rows, see the layout note above */
+    const float *g_input, *g_post_attn, *g_pre_ff, *g_post_ff, *g_qn, *g_kn;
+    const float *inv_freq;                           /* [hd/2] */
+    void *k_cache, *v_cache;                         /* binary16 [n_kv][max_seq][hd] */
+} b200_token_layer;
 
-/* Fills rb, T, NG, spt of a matvec step from rows/cols/row_stride/out_mode. Returns 0, or
- * B200_E_TOOLARGE when a row does not fit the kernel's thread/ring budget. */
-int b200_op_plan_matvec(b200_op *op, int wtype);
+/* Geometry of one matvec stage. rows/cols/row_stride/glu are the caller's; the rest is filled by
+ * b200_token_plan. */
+typedef struct b200_stage_geom {
+    int rows, cols; long long row_stride;
+    int glu;                      /* rows are (gate, up) pairs */
+    int T, NG, spt;               /* threads per consumer group, groups, 16-byte column slices per thread */
+    int rg, rb;                   /* rows per group in a chunk; rows per chunk (one ring slot) = NG * rg */
+    int pw;                       /* rows per emission window, a multiple of rb */
+    int cta_base, cta_rem;        /* row units per block: base, +1 for the first rem blocks */
+    int direct_in;                /* reserved, 0 */
+} b200_stage_geom;
+
+enum { B200_ST_QKV = 0, B200_ST_O = 1, B200_ST_GATEUP = 2, B200_ST_DOWN = 3, B200_ST_LM = 4, B200_ST_KINDS = 5 };
 
 typedef struct b200_token_args {
-    const b200_op *d_ops; int n_ops; int wtype;
-    int wide;                                     /* 1 when any step was planned with spt == 2 */
-    /* model constants */
+    const b200_token_layer *d_layers; int n_layers;
+    int wtype;                                    /* B200_WT_Q8 or B200_WT_F16, all matrices */
+    int gemma;                                    /* 1: four-norm block and tanh-GELU (src/nn/fast_inference.c:436-462) */
+    b200_stage_geom g[B200_ST_KINDS];
+    const void *w_lm; const float *g_final;
+    int with_lm;                                  /* 0: stop after the last layer (prompt positions) */
     const float *d_emb; int emb_rows; float emb_scale, eps;
-    int n_q, n_kv, hd, max_seq, n_split;
+    int d_model, n_q, n_kv, hd, max_seq, n_split;
     /* device control words */
-    int *d_pos; int *d_tokens; const int *d_prompt_len; unsigned *d_epoch; int epoch_mul; int *d_err;
-    /* scratch */
-    float *d_attn_scratch; unsigned *d_attn_tickets; float *d_argmax_scratch;
-    unsigned *d_grid_barrier;                     /* 2 zero-initialised words */
-    /* what the last block does when the steps are done */
-    int pick_token;                               /* tokens[pos+1] = argmax unless pos+1 < *prompt_len */
-    float *d_argmax_val[B200_MAX_PEERS]; int *d_argmax_idx[B200_MAX_PEERS]; int n_ranks, rank;
-    const float *d_rank_vals; const int *d_rank_idx;   /* [n_ranks] pairs pushed by the ranks (TP) */
-    const unsigned *d_argmax_wait_flags; unsigned *d_argmax_signal_flags[B200_MAX_PEERS]; int argmax_add;
-    /* optional trace, 4 words per step written by block 0: nanosecond timer when step i starts [4i], is
-     * done [4i+1], has its input vector [4i+2], gets its first weights [4i+3]; 4*n_ops words, or NULL */
-    unsigned long long *d_step_ns;
+    int *d_pos; int *d_tokens; const int *d_prompt_len; unsigned *d_epoch; int *d_err;
+    /* flagged vectors local to this GPU */
+    b200_flagged *d_qkv;                          /* [(n_q + 2 n_kv) * hd] */
+    b200_flagged *d_attn_part;                    /* [n_q][n_split][hd + 2] */
+    b200_flagged *d_attn_out;                     /* [n_q * hd] */
+    b200_flagged *d_act;                          /* [g[GATEUP].rows / 2] */
+    b200_flagged *d_am;                           /* [2 * blocks]: (best value, row) of each block */
+    /* flagged vectors written by every rank: [n_ranks][d_model] each */
+    const b200_flagged *d_slots_o, *d_slots_dn;
+    b200_flagged *d_peer_slots_o[B200_MAX_PEERS]; /* slot `rank` inside rank p's d_slots_o, p < n_ranks */
+    b200_flagged *d_peer_slots_dn[B200_MAX_PEERS];
+    const b200_flagged *d_am_rank;                /* [2 * n_ranks] */
+    b200_flagged *d_peer_am[B200_MAX_PEERS];      /* entry `rank` inside rank p's d_am_rank */
+    int n_ranks, rank;
+    /* Arrival counters (hints that spare L2 the polling of 640 threads per block: one thread waits for
+     * the count, then everybody reads the flagged words once; the flags stay the proof of validity).
+     * Each producer adds the number of words it stored; a reader expects (epoch * n_layers + layer + 1)
+     * * words-per-layer. d_counters: B200_CNT_STRIDE words apart: [0] q/k/v rows, [1] attention output,
+     * [2] activations, [3] o slots, [4] down slots (all ranks add to these two), [8 + h] partial
+     * records of KV head h. Zero-initialised by the caller, never reset. */
+    unsigned *d_counters;
+    unsigned *d_peer_counters[B200_MAX_PEERS];    /* rank p's d_counters, p < n_ranks */
+    float *d_logits; long long logits_offset;     /* logits[logits_offset + r] = row r of this rank's LM-head shard */
+    int spin_limit;                               /* iterations of a polling loop before it gives up; 0 = default */
+    /* optional trace: 16 words per block and stage, [block][stage][16], 6 stages
+     * per layer (q/k/v, attention, o, gate/up, down, one unused) + the LM head: [0] stage entered,
+     * [1] input vector complete, [2] first weights in shared memory, [3] thread 0 done with its rows,
+     * [4] results stored, [5] producer issued the stage's first copy, [6] its last copy, [7] all warps
+     * of the block done with their rows; [8..13] thread 0's first two chunks (data there, rows summed,
+     * partials stored), [14] chunks walked, [15] chunks owned. NULL = no trace (a separate kernel instantiation without the
+     * timer reads). */
+    unsigned long long *d_trace;
+    /* filled by b200_token_plan */
+    int n_blocks, smem_bytes, scratch_floats;
+    int att_keys;                                 /* cache rows the attention stage holds in shared memory at a time */
+    /* Bytes of the following stage's weights that a block asks L2 for when it starts streaming a stage
+     * (0 = default, negative = none). */
+    int l2_ahead_bytes;
 } b200_token_args;
+
+/* Fills the geometry (g[k].T ... direct_in), n_split limits and the launch shape for `n_blocks` blocks
+ * (0 = one per SM of the current device). Returns 0, B200_E_BADARG for shapes the kernel does not
+ * cover, B200_E_TOOLARGE when a row or the shared-memory budget is exceeded. Host-only arithmetic
+ * when n_blocks > 0: callable without a GPU. */
+int b200_token_plan(b200_token_args *a, int n_blocks);
+
+/* Host-side replay of the row partition the kernel uses (no GPU needed; for tests): writes up to `cap`
+ * triples {first_row, n_rows, window} of block `block`, stage kind `kind`, in the order the producer
+ * issues them; returns the number of chunks. */
+int b200_token_chunks(const b200_token_args *a, int kind, int block, int *out, int cap);
 
 int b200_decode_token(const b200_token_args *a, void *stream);
 

@@ -72,6 +72,44 @@ class AttnArgs(C.Structure):
     ]
 
 
+class StageGeom(C.Structure):
+    """b200_stage_geom (include/llmb200_kernels.h)."""
+    _fields_ = [("rows", C.c_int), ("cols", C.c_int), ("row_stride", C.c_longlong), ("glu", C.c_int),
+                ("T", C.c_int), ("NG", C.c_int), ("spt", C.c_int), ("rg", C.c_int), ("rb", C.c_int), ("pw", C.c_int),
+                ("cta_base", C.c_int), ("cta_rem", C.c_int), ("direct_in", C.c_int)]
+
+
+class TokenLayer(C.Structure):
+    """b200_token_layer (include/llmb200_kernels.h)."""
+    _fields_ = [(n, C.c_void_p) for n in ("w_qkv", "w_o", "w_gateup", "w_down", "g_input", "g_post_attn", "g_pre_ff",
+                                          "g_post_ff", "g_qn", "g_kn", "inv_freq", "k_cache", "v_cache")]
+
+
+B200_ST_QKV, B200_ST_O, B200_ST_GATEUP, B200_ST_DOWN, B200_ST_LM, B200_ST_KINDS = 0, 1, 2, 3, 4, 5
+
+
+class TokenArgs(C.Structure):
+    """b200_token_args (include/llmb200_kernels.h)."""
+    _fields_ = [
+        ("d_layers", C.c_void_p), ("n_layers", C.c_int), ("wtype", C.c_int), ("gemma", C.c_int),
+        ("g", StageGeom * B200_ST_KINDS),
+        ("w_lm", C.c_void_p), ("g_final", C.c_void_p), ("with_lm", C.c_int),
+        ("d_emb", C.c_void_p), ("emb_rows", C.c_int), ("emb_scale", C.c_float), ("eps", C.c_float),
+        ("d_model", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("hd", C.c_int), ("max_seq", C.c_int), ("n_split", C.c_int),
+        ("d_pos", C.c_void_p), ("d_tokens", C.c_void_p), ("d_prompt_len", C.c_void_p), ("d_epoch", C.c_void_p), ("d_err", C.c_void_p),
+        ("d_qkv", C.c_void_p), ("d_attn_part", C.c_void_p), ("d_attn_out", C.c_void_p), ("d_act", C.c_void_p), ("d_am", C.c_void_p),
+        ("d_slots_o", C.c_void_p), ("d_slots_dn", C.c_void_p),
+        ("d_peer_slots_o", C.c_void_p * B200_MAX_PEERS), ("d_peer_slots_dn", C.c_void_p * B200_MAX_PEERS),
+        ("d_am_rank", C.c_void_p), ("d_peer_am", C.c_void_p * B200_MAX_PEERS),
+        ("n_ranks", C.c_int), ("rank", C.c_int),
+        ("d_counters", C.c_void_p), ("d_peer_counters", C.c_void_p * B200_MAX_PEERS),
+        ("d_logits", C.c_void_p), ("logits_offset", C.c_longlong),
+        ("spin_limit", C.c_int),
+        ("d_trace", C.c_void_p),
+        ("n_blocks", C.c_int), ("smem_bytes", C.c_int), ("scratch_floats", C.c_int), ("att_keys", C.c_int), ("l2_ahead_bytes", C.c_int),
+    ]
+
+
 class Config(C.Structure):
     """llmb200_config (include/llmb200_inference.h)."""
     _fields_ = [("model_type", C.c_int), ("d_model", C.c_int), ("n_q_heads", C.c_int), ("n_kv_heads", C.c_int),
@@ -121,7 +159,7 @@ SYMBOLS_MAIN = {
                        "metal_buf_free", "metal_buf_ptr", "wmat_create_q8", "wmat_create_f16", "wmat_free", "wmat_convert",
                        "norm_upload", "layers_convert_upload", "layers_free"],
     "llmb200_kernels.h": ["b200_packed_row_stride", "b200_q8_pack", "b200_f16_pack", "b200_q8_unpack_blocks", "b200_matvec",
-                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_op_plan_matvec", "b200_decode_token", "b200_lora_decode", "b200_argmax_rows",
+                          "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_token_plan", "b200_token_chunks", "b200_decode_token", "b200_lora_decode", "b200_argmax_rows",
                           "b200_launch_count"],
     "llmb200_inference.h": ["inference_state_create", "inference_state_create_gemma3", "inference_state_free",
                             "inference_generate", "inference_state_model_type", "inference_state_vocab_size",
@@ -189,7 +227,8 @@ def lib():
         "b200_attn_scratch_floats": (sz, [i, i, i]), "b200_attn_decode": (i, [C.POINTER(AttnArgs), vp]),
         "b200_attn_decode_static": (i, [C.POINTER(AttnArgs), vp]),
         "b200_tp_argmax_finalize": (i, [vp, vp, i, vp, vp, i, i, vp, vp, vp, vp, vp, i, vp]),
-        "b200_op_plan_matvec": (i, [vp, vp]), "b200_decode_token": (i, [vp, vp]),
+        "b200_token_plan": (i, [C.POINTER(TokenArgs), i]), "b200_token_chunks": (i, [C.POINTER(TokenArgs), i, i, c_int_p, i]),
+        "b200_decode_token": (i, [C.POINTER(TokenArgs), vp]),
         "b200_lora_decode": (i, [vp, vp, vp, vp, vp, vp, i, i, i, i, fl, vp]),
         "b200_argmax_rows": (i, [vp, i, i, vp, vp, i, vp, vp, vp]),
         "b200_launch_count": (C.c_ulonglong, [i]),
@@ -221,7 +260,7 @@ def lib():
         "llmb200_state_error": (i, [vp]), "llmb200_state_run_device_steps": (C.c_float, [vp, i]),
         "llmb200_state_profile_token": (i, [vp, c_float_p, c_int_p]),
         "llmb200_state_time_kind": (C.c_float, [vp, i, i, c_int_p]),
-        "llmb200_state_step_trace": (i, [vp, C.POINTER(C.c_ulonglong), i]),
+        "llmb200_state_step_trace": (i, [vp, C.POINTER(C.c_ulonglong), sz]),
         "llmb200_state_weight_bytes": (C.c_ulonglong, [vp]), "llmb200_state_position": (i, [vp]),
         "llmb200_state_graph_kernels": (i, [vp, i]),
         "llmb200_state_export_weight": (sz, [vp, i, i, vp, sz]),

@@ -1,19 +1,38 @@
-// Whole-token decode kernel (sm_100a): every matvec and attention step of one
+// Whole-token decode kernel (sm_100a): every matvec and attention stage of one
 // token in one persistent, cooperative launch of one block per SM.
 //
-// Why: a batch-1 token is ~180 dependent steps of a few microseconds of HBM
-// time each. As separate kernels each step pays launch, pipeline fill and
-// drain; here the steps are separated by device-wide barriers only, and the
-// producer warp of every block runs ahead of the consumers through the whole
-// step list, so the next steps' weights are already in shared memory when a
-// barrier opens. Weights stream through a ring of 8 slots filled by bulk
-// asynchronous copies (TMA) and released through mbarriers; the arithmetic of
-// a stage is the one of matvec.cu (stream_core.cuh), the attention step is the
-// split-sequence scheme of attention.cu.
+// Why: a batch-1 token is ~180 dependent stages of a few microseconds of HBM
+// time each. As separate kernels each stage pays launch, pipeline fill and
+// drain, and the weight stream stops at every boundary. Here
 //
-// Every wait (mbarrier, device-wide barrier, peer flag) is bounded: when one
-// runs out the block raises the error word and a shared abort flag, after
-// which all loops fall through and the kernel ends.
+//  * a producer warp per block streams the block's rows of EVERY stage, in
+//    stage order, through one shared-memory ring (cp.async.bulk + mbarriers).
+//    Weights depend on no activation, so the producer runs ahead across stage
+//    boundaries: while the consumers hand a stage's result over, the ring is
+//    already filling with the next stage's rows and HBM never idles;
+//  * results travel between blocks as "flagged" vectors: each fp32 value is
+//    stored together with a flag in one 8-byte word, flag = epoch * (L + 1) +
+//    layer + 1. A reader polls the word itself, so data and readiness arrive
+//    in the same round trip to L2 -- there is no device-wide barrier and no
+//    separate "wait, then load" step;
+//  * every block keeps the residual stream in its own shared memory and adds
+//    the flagged o / down outputs to it (summed in rank order when tensor
+//    parallel), so RMSNorm needs no extra exchange;
+//  * consumer warps run free of each other inside a stage: each leaves its
+//    partial row sums in shared memory and one block-wide barrier per window
+//    of rows precedes the fixed-order final sums and the epilogue.
+//
+// The arithmetic of a row is that of matvec.cu (stream_core.cuh): the
+// reference's q8_matvec / f16_matvec (shaders/q8_kernels.metal:10-42, 97-127)
+// with rms_norm (:133-157), residual_add (:369-375), silu_mul / gelu_mul
+// (:337-363) folded into input assembly and epilogue; the attention stage is
+// per_head_rms_norm, rope, kv_cache_store and attention (:165-331) split over
+// the sequence as in attention.cu.
+//
+// Every wait (mbarrier, flagged word) is bounded: when one runs out the block
+// raises the error word and its abort flag, after which all later waits return
+// at once and the kernel ends; the producer waits (bounded) for its copies in
+// flight before it leaves.
 #include "stream_core.cuh"
 #include "../../include/llmb200_kernels.h"
 
@@ -23,66 +42,106 @@ extern unsigned long long g_b200_launches;
 
 namespace {
 
-constexpr int TK_CONSUMERS = 640;
-constexpr int TK_THREADS = TK_CONSUMERS + 32;
-constexpr int TK_SLOTS = 8;
-constexpr int TK_SLOT_BYTES = 22016;                 // 172 * 128; >= rb * row_stride of every step
-constexpr int TK_ATT_BYTES = 43008;                  // attention scratch; the shared input vector aliases it
-constexpr int TK_XS_FLOATS = 4096;                   // largest input vector handed over through shared memory
-constexpr int TK_MAX_WARPS = TK_CONSUMERS / 32;
-constexpr int ATT_T = 256;                           // consumer threads that work on an attention item
+constexpr int TK_NC = 640;                           // consumer threads
+constexpr int TK_THREADS = TK_NC + 32;               // + the producer warp
+constexpr int TK_NWARP = TK_NC / 32;
+constexpr int TK_SLOTS = 7;                          // 7 x 21.25 KB in flight per SM; the rest of shared memory holds activations
+constexpr int TK_SLOT_BYTES = 21760;                 // 170 * 128
+constexpr int TK_PART = 1024;                        // floats per partial-sum buffer (two buffers)
+constexpr int ATT_T = 512;                           // consumer threads that work on an attention item
+constexpr int TK_SPIN_DEFAULT = 1 << 20;
+constexpr int TK_TRACE_WORDS = 16;
+
+
+// ---------------------------------------------------------------------------
+// Row partition, shared by the producer, the consumers and the host-side replay.
+// A stage's rows (in units of `ralign` rows: 2 for gate/up pairs) go to the blocks in contiguous,
+// nearly equal ranges; a block's range is cut into windows of at most `pw` rows (pw a multiple of rb);
+// a window is cut into chunks of rb = NG * rg consecutive rows (the last one may be short). A chunk
+// is one bulk copy into one ring slot; inside a chunk consumer group g owns rows g*rg .. g*rg + rg-1,
+// so every warp of the block works on every chunk.
+// ---------------------------------------------------------------------------
+struct RowRange { int r0, r1; };
+
+__host__ __device__ inline RowRange block_rows(const b200_stage_geom &g, int block)
+{
+    const int ralign = g.glu ? 2 : 1;
+    RowRange r;
+    r.r0 = (block * g.cta_base + (block < g.cta_rem ? block : g.cta_rem)) * ralign;
+    r.r1 = r.r0 + (g.cta_base + (block < g.cta_rem ? 1 : 0)) * ralign;
+    return r;
+}
+
+// ---------------------------------------------------------------------------
+// Shared-memory layout (byte offsets from the 128-aligned base).
+// ---------------------------------------------------------------------------
+struct Layout {
+    int ring, bars, part, red, flags, layers, resid, scratch, total;
+};
+
+__host__ __device__ inline Layout make_layout(int n_layers, int d_model, int scratch_floats)
+{
+    Layout l;
+    int o = 0;
+    l.ring = o;    o += TK_SLOTS * TK_SLOT_BYTES;
+    l.bars = o;    o += (2 * TK_SLOTS + 2) * 8;      // full[], empty[], the attention stage's K/V barrier
+    l.part = o;    o += 2 * TK_PART * 4;
+    l.red = o;     o += 2 * 32 * 4 + 2 * 32 * 4;      // two sum buffers, one (value, index) buffer
+    l.flags = o;   o += 64;
+    l.layers = o;  o += ((n_layers * (int)sizeof(b200_token_layer) + 15) / 16) * 16;
+    l.resid = o;   o += ((d_model * 4 + 15) / 16) * 16;
+    l.scratch = o; o += ((scratch_floats * 4 + 15) / 16) * 16;
+    l.total = o;
+    return l;
+}
+
+// Scratch floats the attention stage needs besides its K/V staging area: rotated queries, new key and
+// value, the per-warp merge buffer and the new q/k/v rows as produced. The staging area (att_keys rows
+// of K and of V in binary16 = att_keys * hd floats) follows; the split-merge records reuse it.
+__host__ __device__ inline int attention_fixed_floats(int G, int hd)
+{
+    const int wph = (ATT_T / G) / 32;
+    return G * hd + 2 * hd + G * wph * (hd + 2) + (G + 2) * hd;
+}
+
+// ---------------------------------------------------------------------------
+// Device side. Two rules shape it:
+//  * no local memory. With ~220 KB of shared memory per block the L1 that backs the stack is a few
+//    KB, so every stack access is a round trip to L2 (about a microsecond while the weights stream).
+//    Hence: no structures or arrays passed by reference to out-of-line functions, no dynamically
+//    indexed register arrays, no spills; block-wide constants are recomputed from the kernel
+//    parameters (constant bank) and the shared-memory base; running counters travel by value.
+//  * one layer's code stays resident in the instruction cache (every stage runs its code once per
+//    layer, so nothing amortises a miss): loops outside the row loop are kept rolled.
+// ---------------------------------------------------------------------------
+extern __shared__ __align__(128) unsigned char tk_smem[];
 
 struct Smem {
     unsigned char *ring;
-    uint64_t *full, *empty;
-    float *wpart;        // [TK_SLOTS][TK_MAX_WARPS][8] partial row sums of the stage in each slot
-    int *cnt;            // [TK_SLOTS] warps that have delivered their partials
-    float *red;          // [8][32]
-    float *am_v; int *am_i;   // [TK_MAX_WARPS * 8] each
-    int *flags;          // [0] abort, [1] last-block
-    float *att;          // TK_ATT_BYTES, also xs
+    uint64_t *full, *empty, *att_bar;
+    float *part, *red, *resid, *scratch;
+    volatile int *flags;                             // [0] abort, [1] always 0
+    const b200_token_layer *layers;
 };
 
-__device__ __forceinline__ Smem carve(unsigned char *base)
+__device__ __forceinline__ Smem smem_of(const b200_token_args &p)
 {
-    Smem s;
-    s.ring = base;
-    unsigned char *p = base + (size_t)TK_SLOTS * TK_SLOT_BYTES;
-    s.full = reinterpret_cast<uint64_t *>(p); p += TK_SLOTS * 8;
-    s.empty = reinterpret_cast<uint64_t *>(p); p += TK_SLOTS * 8;
-    s.wpart = reinterpret_cast<float *>(p); p += TK_SLOTS * TK_MAX_WARPS * 8 * 4;
-    s.cnt = reinterpret_cast<int *>(p); p += TK_SLOTS * 4 + 32;
-    s.red = reinterpret_cast<float *>(p); p += 8 * 32 * 4;
-    s.am_v = reinterpret_cast<float *>(p); p += TK_MAX_WARPS * 8 * 4;
-    s.am_i = reinterpret_cast<int *>(p); p += TK_MAX_WARPS * 8 * 4;
-    s.flags = reinterpret_cast<int *>(p); p += 64;
-    s.att = reinterpret_cast<float *>(p);
-    return s;
+    const Layout lo = make_layout(p.n_layers, p.d_model, p.scratch_floats);
+    Smem m;
+    m.ring = tk_smem + lo.ring;
+    m.full = reinterpret_cast<uint64_t *>(tk_smem + lo.bars);
+    m.empty = m.full + TK_SLOTS;
+    m.att_bar = m.full + 2 * TK_SLOTS;
+    m.part = reinterpret_cast<float *>(tk_smem + lo.part);
+    m.red = reinterpret_cast<float *>(tk_smem + lo.red);
+    m.resid = reinterpret_cast<float *>(tk_smem + lo.resid);
+    m.scratch = reinterpret_cast<float *>(tk_smem + lo.scratch);
+    m.flags = reinterpret_cast<volatile int *>(tk_smem + lo.flags);
+    m.layers = reinterpret_cast<const b200_token_layer *>(tk_smem + lo.layers);
+    return m;
 }
-constexpr size_t TK_SMEM_BYTES = (size_t)TK_SLOTS * TK_SLOT_BYTES + TK_SLOTS * 16 + TK_SLOTS * TK_MAX_WARPS * 8 * 4 + (TK_SLOTS * 4 + 32) +
-                                 8 * 32 * 4 + TK_MAX_WARPS * 8 * 8 + 64 + TK_ATT_BYTES;
-static_assert(TK_SMEM_BYTES <= 232448, "more shared memory than an sm_100 block can have");
 
-// Rows of a step owned by this block, and by each of its consumer groups.
-struct RowSplit { int r0, r1; };
-__device__ __forceinline__ RowSplit block_rows(const b200_op &op)
-{
-    const int ralign = op.out_mode == B200_OUT_GLU ? 2 : 1;
-    const long long units = op.rows / ralign;
-    RowSplit r;
-    r.r0 = (int)(units * blockIdx.x / gridDim.x) * ralign;
-    r.r1 = (int)(units * (blockIdx.x + 1) / gridDim.x) * ralign;
-    return r;
-}
-__device__ __forceinline__ RowSplit group_rows(const b200_op &op, const RowSplit &b, int g)
-{
-    const int ralign = op.out_mode == B200_OUT_GLU ? 2 : 1;
-    const int units = (b.r1 - b.r0) / ralign;
-    RowSplit r;
-    r.r0 = b.r0 + (int)((long long)units * g / op.NG) * ralign;
-    r.r1 = b.r0 + (int)((long long)units * (g + 1) / op.NG) * ralign;
-    return r;
-}
+__device__ __forceinline__ int spin_of(const b200_token_args &p) { return p.spin_limit > 0 ? p.spin_limit : TK_SPIN_DEFAULT; }
 
 __device__ __forceinline__ unsigned long long global_ns()
 {
@@ -91,271 +150,498 @@ __device__ __forceinline__ unsigned long long global_ns()
     return t;
 }
 
-// mbarrier wait that also ends as soon as the block's abort flag is up, so that after one failed wait
-// every later wait returns at once and the block still walks through all its barriers.
-__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *b, unsigned parity, volatile int *abort_flag)
+__device__ __forceinline__ void raise(volatile int *flags, int *d_err, int code)
 {
-    for (int it = 0; it < (1 << 22); ++it) {
+    flags[0] = 1;
+    if (d_err) *d_err = code;
+}
+
+// mbarrier wait that ends as soon as the block's abort flag is up.
+__device__ __forceinline__ bool mbar_wait_abort(uint64_t *b, unsigned parity, volatile int *abort_flag, int limit)
+{
+#pragma unroll 1
+    for (int it = 0; it < limit; ++it) {
         if (mbar_try_wait(b, parity)) return true;
         if ((it & 63) == 63 && *abort_flag) return false;
     }
     return false;
 }
 
-// Device-wide barrier over the consumer threads of all blocks. `target` is the total number of
-// arrivals expected so far. Returns false when the wait ran out.
-__device__ __forceinline__ bool grid_barrier(unsigned *counter, unsigned target, int tid, volatile int *abort_flag)
+__device__ __forceinline__ void fl_store(b200_flagged *p, float v, unsigned flag)
 {
-    named_barrier(1, TK_CONSUMERS);
-    if (tid == 0) {
-        __threadfence();
-        atomicAdd(counter, 1u);                         // always arrive, so that the other blocks are not held up
-        bool ok = *abort_flag != 0;
-        for (int it = 0; it < B200_SPIN_LIMIT / 2 && !ok; ++it) {
-            unsigned v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-            if ((int)(v - target) >= 0) ok = true;
-        }
-        if (!ok) *abort_flag = 1;
-        abort_flag[3] = *abort_flag;                    // the block's decision, read by everyone after the barrier
-        __threadfence();
+    const unsigned long long w = ((unsigned long long)flag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+
+// Arrival counters: a producer adds the number of words it has stored, one thread of a reading block
+// waits for the expected total. The counter is only a hint that keeps hundreds of threads from
+// polling L2 while nothing is there yet -- validity is proved by the flags of the words themselves, so
+// no fence orders the stores before the count and a wait that runs out simply falls through to the
+// flagged polls (whose limit raises the error).
+__device__ __forceinline__ void cnt_add(unsigned *cnt, unsigned n)
+{
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cnt_wait(const unsigned *cnt, unsigned target, volatile int *flags, int spin)
+{
+#pragma unroll 1
+    for (int it = 0; it < spin; ++it) {
+        unsigned v;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        if ((int)(v - target) >= 0) return;
+        if ((it & 31) == 31 && flags[0]) return;
+        __nanosleep(20);
     }
-    named_barrier(1, TK_CONSUMERS);
-    return !abort_flag[3];
+}
+
+// Reads N pairs of flagged words, pair k STEP words after pair k-1; only the first `count` pairs exist
+// (the others read as zero). All loads of a round are issued before the first flag is looked at, so a
+// ready vector costs one round trip to L2 however many words a thread needs; a round with a stale
+// flag is repeated as a whole. On a timeout the abort flag goes up and the values read as zero.
+template <int N, int STEP>
+__device__ __forceinline__ void fl_poll(const b200_flagged *base, int count, unsigned flag, float (&a)[N], float (&b)[N],
+                                        volatile int *flags, int *d_err, int spin)
+{
+#pragma unroll 1
+    for (int it = 0;; ++it) {
+        unsigned long long v0[N], v1[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            v0[k] = 0ull; v1[k] = 0ull;
+            if (k < count)
+                asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(base + (size_t)k * STEP) : "memory");
+        }
+        bool ok = true;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            ok = ok && (k >= count || ((unsigned)(v0[k] >> 32) == flag && (unsigned)(v1[k] >> 32) == flag));
+            a[k] = __uint_as_float((unsigned)v0[k]);
+            b[k] = __uint_as_float((unsigned)v1[k]);
+        }
+        if (ok) return;
+        if (it >= spin || ((it & 31) == 0 && flags[0])) break;       // an aborted block no longer waits
+        if (it > 4) __nanosleep(40);
+    }
+    raise(flags, d_err, 5);
+#pragma unroll
+    for (int k = 0; k < N; ++k) { a[k] = 0.0f; b[k] = 0.0f; }
+}
+
+// Sum over the consumer threads; every thread gets it. One block-wide barrier. `buf` (0 or 1) picks
+// the exchange buffer: two calls on the same buffer must have another consumer barrier between them.
+__device__ __forceinline__ float cons_sum(float v, float *red, int buf, int tid)
+{
+    v = warp_sum(v);
+    float *r = red + buf * 32;
+    if ((tid & 31) == 0) r[tid >> 5] = v;
+    named_barrier(1, TK_NC);
+    // 20 partials, fetched with five 16-byte loads and added in warp order
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < TK_NWARP; w += 4) {
+        const float4 v4 = *reinterpret_cast<const float4 *>(r + w);
+        tot += v4.x; tot += v4.y; tot += v4.z; tot += v4.w;
+    }
+    return tot;
+}
+static_assert(TK_NWARP % 4 == 0, "cons_sum reads the warp partials four at a time");
+
+// Sum of the nwg warp partials of one row, in warp order; the loads go out four at a time.
+__device__ __forceinline__ float row_sum(const float *pr, int nwg)
+{
+    float y = 0.0f;
+#pragma unroll 1
+    for (int w = 0; w < nwg; w += 4) {
+        const float a = pr[w], b = w + 1 < nwg ? pr[w + 1] : 0.0f, c = w + 2 < nwg ? pr[w + 2] : 0.0f, d = w + 3 < nwg ? pr[w + 3] : 0.0f;
+        y += a; y += b; y += c; y += d;
+    }
+    return y;
 }
 
 // ---------------------------------------------------------------------------
-// One matvec step, consumer side.
+// A matvec stage, consumer side, in three out-of-line pieces that exchange nothing but scalars and
+// shared memory: (1) the input vector: stage_residual (residual update + RMS statistics; the norm
+// weights are parked in shared memory) or stage_vector (a flagged vector fetched once per block);
+// (2) stage_rows: this thread's slices of x from shared memory into registers, then the block's rows
+// of one window from the ring, warp partials into shared memory; (3) stage_emit: final sums and the
+// epilogue of the window. kind selects what is read and written (l is the layer, n_layers for the
+// LM head).
 // ---------------------------------------------------------------------------
-template <int WT, int SPT, int RB>
-__device__ __forceinline__ void matvec_step(const b200_op &op, const b200_token_args &p, const Smem &sm, int tid, int pos,
-                                            unsigned &fill_parity, float &best_v, int &best_i, unsigned long long *trace)
+
+// Residual update of the q/k/v, gate/up and LM-head stages:
+//   residual <- embedding row (first stage of a token) | residual + sum over ranks of the slots
+// (the sum is RMS-normalised first where the architecture has post norms), and the RMS statistics of
+// the new residual. Leaves the stage's norm weights in scratch[D .. 2D). Returns 1/sqrt(mean(r^2)+eps).
+__device__ __forceinline__ float stage_residual(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long *trace)
+{
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const int tid = threadIdx.x, D = p.d_model, L = p.n_layers;
+    const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+    const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
+    const unsigned words_slots = (unsigned)(D * p.n_ranks);
+    const b200_token_layer *ly = sm.layers + (l < L ? l : L - 1);
+    const float *norm_gamma, *slot_gamma;
+    const b200_flagged *slots;
+    const unsigned *in_cnt;
+    unsigned slots_flag, target;
+    if (kind == B200_ST_GATEUP) {
+        norm_gamma = p.gemma ? ly->g_pre_ff : ly->g_post_attn;
+        slot_gamma = p.gemma ? ly->g_post_attn : nullptr;
+        slots = p.d_slots_o; slots_flag = flag;
+        in_cnt = p.d_counters + B200_CNT_SLOTS_O * B200_CNT_STRIDE; target = cnt_mul * words_slots;
+    } else {
+        // q/k/v of layer l, or the LM head (l == L): the down slots of the layer before
+        norm_gamma = kind == B200_ST_LM ? p.g_final : ly->g_input;
+        slot_gamma = (p.gemma && l > 0) ? sm.layers[l - 1].g_post_ff : nullptr;
+        slots = p.d_slots_dn; slots_flag = flag - 1u;
+        in_cnt = p.d_counters + B200_CNT_SLOTS_DN * B200_CNT_STRIDE; target = (cnt_mul - 1u) * words_slots;
+    }
+    float *gam = sm.scratch + D;
+    float ss = 0.0f;
+    if (kind == B200_ST_QKV && l == 0) {
+        long long tok = p.d_tokens[*p.d_pos];
+        if (tok < 0 || tok >= p.emb_rows) tok = 0;   // never index outside the table
+        const float *er = p.d_emb + tok * (long long)D;
+#pragma unroll 1
+        for (int i = tid * 4; i < D; i += TK_NC * 4) {
+            float4 v = *reinterpret_cast<const float4 *>(er + i);
+            const float4 g4 = *reinterpret_cast<const float4 *>(norm_gamma + i);
+            v.x *= p.emb_scale; v.y *= p.emb_scale; v.z *= p.emb_scale; v.w *= p.emb_scale;
+            *reinterpret_cast<float4 *>(sm.resid + i) = v;
+            *reinterpret_cast<float4 *>(gam + i) = g4;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        // Up to 4 pairs per thread and round, all in flight together; the norm weights of the first round's
+        // elements are requested before the wait, so that their round trip hides behind it. Every thread
+        // reaches the barrier, whether or not it owns elements.
+        constexpr int NB = 4;
+        float sq = 0.0f;
+        float2 gq[NB];
+        {
+            const int cnt0 = tid * 2 < D ? (D - tid * 2 + TK_NC * 2 - 1) / (TK_NC * 2) : 0;
+#pragma unroll
+            for (int u = 0; u < NB; ++u) gq[u] = u < cnt0 ? *reinterpret_cast<const float2 *>(norm_gamma + tid * 2 + u * TK_NC * 2) : make_float2(0, 0);
+        }
+        if (tid == 0) { cnt_wait(in_cnt, target, sm.flags, spin); if (trace) trace[8] = global_ns(); }
+        named_barrier(1, TK_NC);
+        if (trace && tid == 0) trace[9] = global_ns();
+#pragma unroll 1
+        for (int i0 = tid * 2; i0 < D; i0 += TK_NC * 2 * NB) {
+            const int cnt = (D - i0 + TK_NC * 2 - 1) / (TK_NC * 2);
+            if (i0 != tid * 2) {
+#pragma unroll
+                for (int u = 0; u < NB; ++u) gq[u] = u < cnt ? *reinterpret_cast<const float2 *>(norm_gamma + i0 + u * TK_NC * 2) : make_float2(0, 0);
+            }
+            float s0[NB], s1[NB];
+#pragma unroll
+            for (int u = 0; u < NB; ++u) { s0[u] = 0.0f; s1[u] = 0.0f; }
+#pragma unroll 1
+            for (int k = 0; k < p.n_ranks; ++k) {
+                float a[NB], b[NB];
+                fl_poll<NB, TK_NC * 2>(slots + (size_t)k * D + i0, cnt, slots_flag, a, b, sm.flags, p.d_err, spin);
+#pragma unroll
+                for (int u = 0; u < NB; ++u) { s0[u] += a[u]; s1[u] += b[u]; }
+            }
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int i = i0 + u * TK_NC * 2;
+                if (u < cnt) {
+                    *reinterpret_cast<float2 *>(gam + i) = gq[u];
+                    if (slot_gamma) {
+                        sm.scratch[i] = s0[u]; sm.scratch[i + 1] = s1[u];
+                        sq = fmaf(s0[u], s0[u], sq); sq = fmaf(s1[u], s1[u], sq);
+                    } else {
+                        const float r0 = sm.resid[i] + s0[u], r1 = sm.resid[i + 1] + s1[u];
+                        sm.resid[i] = r0; sm.resid[i + 1] = r1;
+                        ss = fmaf(r0, r0, ss); ss = fmaf(r1, r1, ss);
+                    }
+                }
+            }
+        }
+        if (trace && tid == 0) trace[10] = global_ns();
+        if (slot_gamma) {
+            // the sum of the slots is normalised before it joins the residual (Gemma3's post norms)
+            const float inv_s = 1.0f / sqrtf(cons_sum(sq, sm.red, 0, tid) / (float)D + p.eps);
+#pragma unroll 1
+            for (int i = tid * 2; i < D; i += TK_NC * 2) {
+                const float r0 = sm.resid[i] + slot_gamma[i] * sm.scratch[i] * inv_s;
+                const float r1 = sm.resid[i + 1] + slot_gamma[i + 1] * sm.scratch[i + 1] * inv_s;
+                sm.resid[i] = r0; sm.resid[i + 1] = r1;
+                ss = fmaf(r0, r0, ss); ss = fmaf(r1, r1, ss);
+            }
+        }
+    }
+    const float tot = cons_sum(ss, sm.red, 1, tid);
+    if (trace && tid == 0) trace[11] = global_ns();
+    return 1.0f / sqrtf(tot / (float)D + p.eps);
+}
+
+// Input vector of the o and down stages: the flagged vector, fetched once per block with coalesced
+// loads into scratch[0 .. cols).
+__device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long *trace)
+{
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const int tid = threadIdx.x, L = p.n_layers, cols = p.g[kind].cols;
+    const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+    const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
+    const b200_flagged *in_vec = kind == B200_ST_O ? p.d_attn_out : p.d_act;
+    const unsigned *in_cnt = p.d_counters + (kind == B200_ST_O ? B200_CNT_ATTN : B200_CNT_ACT) * B200_CNT_STRIDE;
+    if (tid == 0) { cnt_wait(in_cnt, cnt_mul * (unsigned)cols, sm.flags, spin); if (trace) trace[8] = global_ns(); }
+    named_barrier(1, TK_NC);
+    if (trace && tid == 0) trace[9] = global_ns();
+    constexpr int NB = 4;
+#pragma unroll 1
+    for (int i0 = tid * 2; i0 < cols; i0 += TK_NC * 2 * NB) {
+        float a[NB], b[NB];
+        fl_poll<NB, TK_NC * 2>(in_vec + i0, (cols - i0 + TK_NC * 2 - 1) / (TK_NC * 2), flag, a, b, sm.flags, p.d_err, spin);
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+            const int i = i0 + u * TK_NC * 2;
+            if (i < cols) *reinterpret_cast<float2 *>(sm.scratch + i) = make_float2(a[u], b[u]);
+        }
+    }
+    if (trace && tid == 0) trace[10] = global_ns();
+    named_barrier(1, TK_NC);
+    if (trace && tid == 0) trace[11] = global_ns();
+}
+
+// Rows [w0, w1) of the block: every warp works on every chunk. A thread owns SPT 16-byte column
+// slices (its slices of x stay in registers) and, in each chunk, the RG rows of its group; eight row
+// partials are collected in registers (8 / RG chunks) and then folded across the warp's lanes by one
+// transposing shuffle reduction; the warp partial of each row goes to part[]. `state` is the running
+// chunk number; returned advanced.
+template <int WT, int SPT, int RG, bool TRACE>
+__device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kind, float inv, int w0, int w1, unsigned state, unsigned win,
+                                            unsigned long long *trace)
 {
     constexpr int E = (WT == B200_WT_Q8) ? 16 : 8;
-    const int T = op.T, NG = op.NG, spg = TK_SLOTS / NG;
-    const int g = tid / T, t = tid - g * T, lane = t & 31, wg = t >> 5, nwg = T >> 5;
-    const bool active = g < NG;                        // threads beyond NG*T sit this step out
-    const RowSplit br = block_rows(op);
+    constexpr int NACC = 8 / RG;                     // chunks per reduction
+    const b200_stage_geom &G = p.g[kind];
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const int tid = threadIdx.x, T = G.T, NG = G.NG, RB = G.rb;
+    const int g = tid / T, t = tid - g * T, lane = tid & 31, wg = t >> 5, nwgp = (T >> 5) | 1;
+    const bool active = g < NG;
 
-    if (active) {
-        int col[SPT];
-        bool on[SPT];
-#pragma unroll
-        for (int s = 0; s < SPT; ++s) { col[s] = (s * T + t) * E; on[s] = col[s] < op.cols; }
-        float *gred = sm.red + g * 32;
-        float *xs = sm.att;
-        const bool share_x = NG > 1 && (op.in_mode != B200_IN_VEC || op.d_norm_gamma) && SPT * T * E <= TK_XS_FLOATS;
-
-        // ---------------- input assembly ----------------
-        float x[SPT][E];
-        if (!share_x || g == 0) {
-            if (op.in_mode == B200_IN_VEC) {
-#pragma unroll
-                for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                    for (int e = 0; e < E; e += 4) {
-                        // produced earlier in this same kernel by other SMs: read from L2
-                        float4 v4 = on[s] ? __ldcg(reinterpret_cast<const float4 *>(op.d_in_vec + col[s] + e)) : make_float4(0, 0, 0, 0);
-                        x[s][e] = v4.x; x[s][e + 1] = v4.y; x[s][e + 2] = v4.z; x[s][e + 3] = v4.w;
-                    }
-            } else {
-                if (op.in_mode == B200_IN_EMBED) {
-                    long long tok = p.d_tokens[pos];
-                    if (tok < 0 || tok >= p.emb_rows) tok = 0;
-                    const float *er = p.d_emb + tok * (long long)op.cols;
-#pragma unroll
-                    for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                        for (int e = 0; e < E; e += 4) {
-                            float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(er + col[s] + e) : make_float4(0, 0, 0, 0);
-                            x[s][e] = v4.x * p.emb_scale; x[s][e + 1] = v4.y * p.emb_scale;
-                            x[s][e + 2] = v4.z * p.emb_scale; x[s][e + 3] = v4.w * p.emb_scale;
-                        }
-                } else {
-                    float sacc[SPT][E];
-#pragma unroll
-                    for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                        for (int e = 0; e < E; ++e) sacc[s][e] = 0.0f;
-                    for (int k = 0; k < op.n_slots; ++k) {
-                        const float *sl = op.d_slots + (long long)k * op.slot_stride;
-#pragma unroll
-                        for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                            for (int e = 0; e < E; e += 4)
-                                if (on[s]) {
-                                    float4 v4 = __ldcg(reinterpret_cast<const float4 *>(sl + col[s] + e));
-                                    sacc[s][e] += v4.x; sacc[s][e + 1] += v4.y; sacc[s][e + 2] += v4.z; sacc[s][e + 3] += v4.w;
-                                }
-                    }
-                    if (op.d_slot_norm_gamma) {
-                        float ss = 0.0f;
-#pragma unroll
-                        for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                            for (int e = 0; e < E; ++e) ss = fmaf(sacc[s][e], sacc[s][e], ss);
-                        ss = group_sum(ss, gred, 2 + g, T, t);
-                        const float inv = 1.0f / sqrtf(ss / (float)op.cols + p.eps);
-#pragma unroll
-                        for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                            for (int e = 0; e < E; ++e)
-                                if (on[s]) sacc[s][e] = op.d_slot_norm_gamma[col[s] + e] * sacc[s][e] * inv;
-                    }
-#pragma unroll
-                    for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                        for (int e = 0; e < E; e += 4) {
-                            float4 v4 = on[s] ? __ldcg(reinterpret_cast<const float4 *>(op.d_resid_in + col[s] + e)) : make_float4(0, 0, 0, 0);
-                            x[s][e] = v4.x + sacc[s][e]; x[s][e + 1] = v4.y + sacc[s][e + 1];
-                            x[s][e + 2] = v4.z + sacc[s][e + 2]; x[s][e + 3] = v4.w + sacc[s][e + 3];
-                        }
-                }
-                if (blockIdx.x == 0 && g == 0 && op.d_resid_out) {
-#pragma unroll
-                    for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                        for (int e = 0; e < E; e += 4)
-                            if (on[s])
-                                *reinterpret_cast<float4 *>(op.d_resid_out + col[s] + e) =
-                                    make_float4(x[s][e], x[s][e + 1], x[s][e + 2], x[s][e + 3]);
-                }
-            }
-            if (op.d_norm_gamma) {
-                float gm[SPT][E];
-#pragma unroll
-                for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                    for (int e = 0; e < E; e += 4) {
-                        float4 v4 = on[s] ? *reinterpret_cast<const float4 *>(op.d_norm_gamma + col[s] + e) : make_float4(0, 0, 0, 0);
-                        gm[s][e] = v4.x; gm[s][e + 1] = v4.y; gm[s][e + 2] = v4.z; gm[s][e + 3] = v4.w;
-                    }
-                float ss = 0.0f;
-#pragma unroll
-                for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                    for (int e = 0; e < E; ++e) ss = fmaf(x[s][e], x[s][e], ss);
-                ss = group_sum(ss, gred, 2 + g, T, t);
-                const float inv = 1.0f / sqrtf(ss / (float)op.cols + p.eps);
-#pragma unroll
-                for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                    for (int e = 0; e < E; ++e) x[s][e] = gm[s][e] * x[s][e] * inv;
-            }
-        }
-        if (share_x) {
-            if (g == 0) {
-#pragma unroll
-                for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                    for (int e = 0; e < E; e += 4)
-                        *reinterpret_cast<float4 *>(xs + (size_t)(s * T + t) * E + e) = make_float4(x[s][e], x[s][e + 1], x[s][e + 2], x[s][e + 3]);
-            }
-            named_barrier(10, NG * T);
-            if (g != 0) {
-#pragma unroll
-                for (int s = 0; s < SPT; ++s)
-#pragma unroll
-                    for (int e = 0; e < E; e += 4) {
-                        const float4 v4 = *reinterpret_cast<const float4 *>(xs + (size_t)(s * T + t) * E + e);
-                        x[s][e] = v4.x; x[s][e + 1] = v4.y; x[s][e + 2] = v4.z; x[s][e + 3] = v4.w;
-                    }
-            }
-        }
-
-        if (trace && tid == 0) trace[2] = global_ns();
-        // ---------------- this group's stages ----------------
-        uint32_t qoff[SPT], soff[SPT];
+    // ---------------- this thread's slices of the input vector -> registers ----------------
+    float x[SPT][E];
+    uint32_t qoff[SPT], soff[SPT];
+    {
+        const bool normed = kind != B200_ST_O && kind != B200_ST_DOWN;
+        const float *xv = normed ? sm.resid : sm.scratch;
+        const float *gam = sm.scratch + p.d_model;
 #pragma unroll
         for (int s = 0; s < SPT; ++s) {
-            const int c = on[s] ? col[s] : 0;
-            qoff[s] = (uint32_t)(WT == B200_WT_Q8 ? c : 2 * c);
-            soff[s] = (uint32_t)op.cols + (uint32_t)(c >> 5) * 2u;
-        }
-        const uint32_t ring_s = smem_u32(sm.ring), stride = (uint32_t)op.row_stride;
-        const RowSplit gr = group_rows(op, br, g);
-        const int nst = (gr.r1 - gr.r0 + RB - 1) / RB;
-        for (int k = 0; k < nst; ++k) {
-            const int slot = g * spg + (k % spg);
-            const unsigned par = ((fill_parity >> slot) + (unsigned)(k / spg)) & 1u;
-            if (!mbar_wait_or_abort(&sm.full[slot], par, sm.flags)) { sm.flags[0] = 1; if (p.d_err) *p.d_err = 3; }
-            if (trace && tid == 0 && k == 0) trace[3] = global_ns();
-            const uint32_t sb = ring_s + (uint32_t)slot * TK_SLOT_BYTES;
-            const int row0 = gr.r0 + k * RB;
-            const int nr = min(RB, gr.r1 - row0);
-            // rows are fetched from the slot four at a time: enough loads in flight, few live registers
-            constexpr int CH = RB < 4 ? RB : 4;
-            float v[RB];
+            const int col = (s * T + t) * E;
+            const bool on = active && col < G.cols;
 #pragma unroll
-            for (int jb = 0; jb < RB; jb += CH) {
-                uint4 wq[CH][SPT];
-                uint32_t ws[CH][SPT];
-#pragma unroll
-                for (int j = 0; j < CH; ++j)
-#pragma unroll
-                    for (int s = 0; s < SPT; ++s) {
-                        wq[j][s] = lds_128(sb + (uint32_t)(jb + j) * stride + qoff[s]);
-                        if (WT == B200_WT_Q8) ws[j][s] = lds_u16(sb + (uint32_t)(jb + j) * stride + soff[s]);
+            for (int e = 0; e < E; e += 4) {
+                float4 v4 = make_float4(0, 0, 0, 0);
+                if (on) {
+                    v4 = *reinterpret_cast<const float4 *>(xv + col + e);
+                    if (normed) {
+                        const float4 g4 = *reinterpret_cast<const float4 *>(gam + col + e);
+                        v4.x = g4.x * v4.x * inv; v4.y = g4.y * v4.y * inv; v4.z = g4.z * v4.z * inv; v4.w = g4.w * v4.w * inv;
                     }
-#pragma unroll
-                for (int j = 0; j < CH; ++j) {
-                    float acc = 0.0f;
-#pragma unroll
-                    for (int s = 0; s < SPT; ++s) {
-                        float d;
-                        if (WT == B200_WT_Q8) d = __half2float(__ushort_as_half((unsigned short)ws[j][s])) * dot16_q8(wq[j][s], x[s]);
-                        else d = dot8_f16(wq[j][s], x[s]);
-                        acc += d;
-                    }
-                    v[jb + j] = acc;
                 }
+                x[s][e] = v4.x; x[s][e + 1] = v4.y; x[s][e + 2] = v4.z; x[s][e + 3] = v4.w;
             }
-            // Warps run free of each other: each leaves its partial sums of the stage's rows in shared memory
-            // and counts itself in; the warp that arrives last (no waiting involved) adds the partials in warp
-            // order, emits the rows and hands the slot back to the producer.
-            const float tot = reduce_rows<RB>(v, lane);
-            float *wp = sm.wpart + (size_t)slot * TK_MAX_WARPS * 8;
-            if (lane < RB) wp[wg * 8 + lane] = tot;
-            __threadfence_block();
-            int last = 0;
-            if (lane == 0) last = (atomicAdd(&sm.cnt[slot], 1) == nwg - 1);
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence_block();
-                float y = 0.0f;
-                if (lane < RB)
-                    for (int w = 0; w < nwg; ++w) y += wp[w * 8 + lane];
+            // Byte offsets of the slice inside a row. Threads past the end of the row read slice 0 (valid
+            // memory) against a zero input slice.
+            const int cc = on ? col : 0;
+            qoff[s] = (uint32_t)(WT == B200_WT_Q8 ? cc : 2 * cc);
+            soff[s] = (uint32_t)G.cols + (uint32_t)(cc >> 5) * 2u;   // Q8: scales follow the quants of a row
+        }
+    }
+    if (TRACE && trace && tid == 0) trace[1] = global_ns();
+
+    const uint32_t ring_s = smem_u32(sm.ring), stride = (uint32_t)G.row_stride;
+    const uint32_t grow = (uint32_t)(g * RG) * stride;           // this group's first row inside a chunk
+    float *part = sm.part + (win & 1u) * TK_PART;
+    const int nrows = w1 - w0, nchunks = (nrows + RB - 1) / RB;
+    unsigned seq = state;
+    bool first = true;
+#pragma unroll 1
+    for (int cbase = 0; cbase < nchunks; cbase += NACC) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+#pragma unroll
+        for (int u = 0; u < NACC; ++u) {
+            if (cbase + u < nchunks) {
+                const unsigned slot = seq % TK_SLOTS, par = (seq / TK_SLOTS) & 1u;
+                ++seq;
+                if (!mbar_wait_abort(&sm.full[slot], par, sm.flags, spin) && !sm.flags[0]) raise(sm.flags, p.d_err, 3);
+                if (TRACE && trace && tid == 0 && first) { trace[2] = global_ns(); first = false; }
+                if (active) {
+                    // rows past the end of a short chunk hold bytes of an earlier chunk: computed, never stored
+                    const uint32_t sb = ring_s + slot * TK_SLOT_BYTES + grow;
+                    uint4 wq[RG][SPT];
+                    uint32_t ws[RG][SPT];
+#pragma unroll
+                    for (int j = 0; j < RG; ++j)
+#pragma unroll
+                        for (int s = 0; s < SPT; ++s) {
+                            wq[j][s] = lds_128(sb + (uint32_t)j * stride + qoff[s]);
+                            if (WT == B200_WT_Q8) ws[j][s] = lds_u16(sb + (uint32_t)j * stride + soff[s]);
+                        }
+#pragma unroll
+                    for (int j = 0; j < RG; ++j) {
+                        float acc = 0.0f;
+#pragma unroll
+                        for (int s = 0; s < SPT; ++s) {
+                            float d;
+                            if (WT == B200_WT_Q8) d = __half2float(__ushort_as_half((unsigned short)ws[j][s])) * dot16_q8(wq[j][s], x[s]);
+                            else d = dot8_f16(wq[j][s], x[s]);
+                            acc += d;
+                        }
+                        v[u * RG + j] = acc;
+                    }
+                }
                 __syncwarp();
-                if (lane == 0) { sm.cnt[slot] = 0; mbar_arrive(&sm.empty[slot]); }
-                const int row = row0 + lane;
-                if (op.out_mode == B200_OUT_GLU) {
-                    const float u = __shfl_down_sync(0xffffffffu, y, 1);
-                    if (lane < nr && !(lane & 1)) {
-                        const float a = op.act == 0 ? act_silu(y) : act_gelu_tanh(y);
-                        op.d_out[0][op.out_offset + (row >> 1)] = a * u;
-                    }
-                } else if (lane < nr) {
-                    for (int q = 0; q < op.n_out; ++q) op.d_out[q][op.out_offset + row] = y;
-                    if (op.argmax && better(y, row, best_v, best_i)) { best_v = y; best_i = row; }
-                }
+                if (lane == 0) mbar_arrive(&sm.empty[slot]);      // this warp no longer reads the slot
+            }
+        }
+        if (active) {
+            // lane i < 8 ends up with the warp's total of partial i: chunk cbase + i / RG, row g*RG + i % RG of it
+            const float tot = reduce_rows<8>(v, lane);
+            const int c = cbase + lane / RG, rin = g * RG + lane % RG;
+            const int lrow = c * RB + rin;
+            if (lane < 8 && c < nchunks && rin < RB && lrow < nrows) part[lrow * nwgp + wg] = tot;
+        }
+    }
+    if (TRACE && trace && tid == 0) trace[3] = global_ns();
+    return seq;
+}
+
+// Final sums and epilogue of rows [w0, w1): thread i adds the warp partials of row i in warp order.
+// best (value bits | row << 32) carries the LM head's running arg-max of this thread.
+template <bool TRACE>
+__device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &p, int kind, int l, unsigned ep, int w0, int w1, unsigned win,
+                                                      unsigned long long best, unsigned long long *trace)
+{
+    const b200_stage_geom &G = p.g[kind];
+    const Smem sm = smem_of(p);
+    const int tid = threadIdx.x, lane = tid & 31, L = p.n_layers;
+    const int nwg = G.T >> 5, nwgp = nwg | 1;
+    const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+    unsigned *const cn = p.d_counters;
+    const float *part = sm.part + (win & 1u) * TK_PART;
+    named_barrier(1, TK_NC);
+    if (TRACE && trace && tid == 0) trace[7] = global_ns();
+    const int n = w1 - w0;
+    unsigned stored = 0;
+    if (kind == B200_ST_GATEUP) {
+#pragma unroll 1
+        for (int i = tid; i < n / 2; i += TK_NC) {
+            const float gte = row_sum(part + (2 * i) * nwgp, nwg), up = row_sum(part + (2 * i + 1) * nwgp, nwg);
+            const float a = p.gemma ? act_gelu_tanh(gte) : act_silu(gte);
+            fl_store(p.d_act + (w0 >> 1) + i, a * up, flag);
+            ++stored;
+        }
+        stored = (unsigned)__reduce_add_sync(0xffffffffu, stored);
+        if (lane == 0 && stored) cnt_add(cn + B200_CNT_ACT * B200_CNT_STRIDE, stored);
+        return best;
+    }
+    float best_v = __uint_as_float((unsigned)best);
+    int best_i = (int)(best >> 32);
+#pragma unroll 1
+    for (int i = tid; i < n; i += TK_NC) {
+        const float y = row_sum(part + i * nwgp, nwg);
+        const int row = w0 + i;
+        if (kind == B200_ST_QKV) fl_store(p.d_qkv + row, y, flag);
+        else if (kind == B200_ST_LM) {
+            p.d_logits[p.logits_offset + row] = y;
+            if (better(y, row, best_v, best_i)) { best_v = y; best_i = row; }
+        } else {
+            // partial sums into slot `rank` of every rank
+#pragma unroll 1
+            for (int q = 0; q < p.n_ranks; ++q) fl_store((kind == B200_ST_O ? p.d_peer_slots_o[q] : p.d_peer_slots_dn[q]) + row, y, flag);
+        }
+        ++stored;
+    }
+    if (kind != B200_ST_LM) {
+        // one add per warp and receiver: the words this warp has stored
+        stored = (unsigned)__reduce_add_sync(0xffffffffu, stored);
+        if (lane == 0 && stored) {
+            if (kind == B200_ST_QKV) cnt_add(cn + B200_CNT_QKV * B200_CNT_STRIDE, stored);
+            else {
+#pragma unroll 1
+                for (int q = 0; q < p.n_ranks; ++q)
+                    cnt_add(p.d_peer_counters[q] + (kind == B200_ST_O ? B200_CNT_SLOTS_O : B200_CNT_SLOTS_DN) * B200_CNT_STRIDE, stored);
             }
         }
     }
-    // every consumer thread advances the fill parities of all slots by this step's stage counts
-    for (int gg = 0; gg < NG; ++gg) {
-        const RowSplit gr = group_rows(op, br, gg);
-        const int nst = (gr.r1 - gr.r0 + RB - 1) / RB;
-        for (int j = 0; j < spg; ++j) {
-            const int fills = nst > j ? (nst - j + spg - 1) / spg : 0;
-            fill_parity ^= (unsigned)(fills & 1) << (gg * spg + j);
+    return ((unsigned long long)(unsigned)best_i << 32) | (unsigned long long)__float_as_uint(best_v);
+}
+
+// One matvec stage. `state`: running chunk number (low word) and window number (high word).
+template <int WT, bool TRACE>
+__device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long state,
+                                                      unsigned long long *trace)
+{
+    const b200_stage_geom &G = p.g[kind];
+    const int tid = threadIdx.x;
+    if (TRACE && trace && tid == 0) trace[0] = global_ns();
+    float inv = 0.0f;
+    if (kind == B200_ST_O || kind == B200_ST_DOWN) stage_vector(p, kind, l, ep, TRACE ? trace : nullptr);
+    else inv = stage_residual(p, kind, l, ep, TRACE ? trace : nullptr);
+    if (kind == B200_ST_LM && !p.with_lm) return state;          // only the residual update that ends a prompt position
+    unsigned seq = (unsigned)state, win = (unsigned)(state >> 32);
+    unsigned long long best = ((unsigned long long)0x7fffffffu << 32) | (unsigned long long)__float_as_uint(-INFINITY);
+    const RowRange br = block_rows(G, blockIdx.x);
+#pragma unroll 1
+    for (int w0 = br.r0; w0 < br.r1; w0 += G.pw) {
+        const int w1 = w0 + G.pw < br.r1 ? w0 + G.pw : br.r1;
+        if (G.spt == 1) {
+            if (G.rg == 2) seq = stage_rows<WT, 1, 2, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else if (G.rg == 4) seq = stage_rows<WT, 1, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else if (G.rg == 8) seq = stage_rows<WT, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else seq = stage_rows<WT, 1, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+        } else {
+            if (G.rg == 2) seq = stage_rows<WT, 2, 2, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else seq = stage_rows<WT, 2, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+        }
+        best = stage_emit<TRACE>(p, kind, l, ep, w0, w1, win, best, trace);
+        ++win;
+    }
+    if (TRACE && trace && tid == 0) trace[4] = global_ns();
+    if (kind == B200_ST_LM) {
+        // best row of the block -> flagged pair (folded over the blocks by block 0)
+        const Smem sm = smem_of(p);
+        const int lane = tid & 31, warp = tid >> 5, L = p.n_layers;
+        const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+        float best_v = __uint_as_float((unsigned)best);
+        int best_i = (int)(best >> 32);
+#pragma unroll 1
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (better(ov, oi, best_v, best_i)) { best_v = ov; best_i = oi; }
+        }
+        float *am_v = sm.red + 64;
+        int *am_i = reinterpret_cast<int *>(sm.red + 96);
+        if (lane == 0) { am_v[warp] = best_v; am_i[warp] = best_i; }
+        named_barrier(1, TK_NC);
+        if (tid == 0) {
+#pragma unroll 1
+            for (int ww = 1; ww < TK_NWARP; ++ww) if (better(am_v[ww], am_i[ww], best_v, best_i)) { best_v = am_v[ww]; best_i = am_i[ww]; }
+            if (p.n_ranks > 1) __threadfence_system();   // this block's logits are visible before its pair is
+            fl_store(p.d_am + 2 * blockIdx.x, best_v, flag);
+            fl_store(p.d_am + 2 * blockIdx.x + 1, __int_as_float(best_i), flag);
         }
     }
+    return ((unsigned long long)win << 32) | seq;
 }
 
 // ---------------------------------------------------------------------------
-// One attention step: items (kv head, sequence split) are dealt to the blocks;
-// the first ATT_T consumer threads of a block work on an item. Scheme and math
-// as in attention.cu; the last block to finish a KV head merges its splits.
+// Attention stage: item (kv head, sequence split) = block index. The block rebuilds the normalised,
+// rotated query heads of its KV head and the new key/value row, stores the row to the cache (split 0),
+// attends over its slice with one online softmax per key lane and leaves (max, sum, output) as a
+// flagged record; block (kv head, split g) then merges all splits of query head g of that KV head.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
 {
@@ -367,446 +653,597 @@ __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
     }
 }
 
-template <int HD, int G>
-__device__ __forceinline__ void attention_step(const b200_op &op, const b200_token_args &p, const Smem &sm, int tid, int pos)
+template <int HD, bool TRACE>
+__device__ __forceinline__ void attention_stage(const b200_token_args &p, int l, unsigned ep, unsigned long long *trace)
 {
-    constexpr int TPK = HD / 8;                 // threads per key row in the PV pass
-    constexpr int KPW = 32 / TPK;               // key rows a warp handles side by side
+    constexpr int DPT = 8;                           // head-dim values per thread
+    constexpr int DLN = HD / DPT;                    // threads that share one key (a key lane): 8, 16 or 32
     constexpr int HALF = HD / 2;
-    constexpr int NW = ATT_T / 32;
-    if (tid >= ATT_T) return;
-    const int chunk_cap = (p.max_seq + p.n_split - 1) / p.n_split;
-    float *q_s = sm.att;                        // [G][HD]
-    float *k_new = q_s + G * HD;                // [HD]
-    float *v_new = k_new + HD;                  // [HD]
-    float *ml = v_new + HD;                     // [2*G]
-    float *scores = ml + 16;                    // [G][chunk_cap]
-    float *ored = scores + (size_t)G * chunk_cap;  // [NW][G][HD]
-    const int lane = tid & 31, warp = tid >> 5;
-    const int n = pos + 1;
-    const int chunk = (n + p.n_split - 1) / p.n_split;
-    const int n_items = p.n_kv * p.n_split;
-
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const b200_token_layer &ly = sm.layers[l];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.n_q / p.n_kv, L = p.n_layers;
+    const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+    const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
+    const int item = blockIdx.x;
+    if (TRACE && trace && tid == 0) trace[0] = global_ns();
+    if (item < p.n_kv * p.n_split && tid < ATT_T) {
         const int kvh = item / p.n_split, split = item - kvh * p.n_split;
+        const int TPH = ATT_T / G, WPH = TPH / 32, KL = TPH / DLN;
+        const int g = tid / TPH, r = tid - g * TPH, kl = r / DLN, dl = r - kl * DLN;
+        const int pos = *p.d_pos, n = pos + 1;
+        const int chunk = (n + p.n_split - 1) / p.n_split;
         const int j0 = min(split * chunk, n), j1 = min(j0 + chunk, n);
-        const int len = j1 - j0;
-        __half *kc = static_cast<__half *>(op.d_k_cache) + (size_t)kvh * p.max_seq * HD;
-        __half *vc = static_cast<__half *>(op.d_v_cache) + (size_t)kvh * p.max_seq * HD;
+        const int KCH = p.att_keys;                  // cache rows staged in shared memory at a time
+        const int nsub = (chunk + KCH - 1) / KCH;    // the same for every block and layer of this token
 
-        for (int vi = warp; vi <= G; vi += NW) {
-            const bool is_k = (vi == G);
-            const float *src = is_k ? op.d_qkv + (size_t)p.n_q * HD + (size_t)kvh * HD : op.d_qkv + (size_t)(kvh * G + vi) * HD;
-            const float *gamma = is_k ? op.d_k_gamma : op.d_q_gamma;
-            float a[HALF / 32], b[HALF / 32];
+        float *q_s = sm.scratch;                     // [G][HD]
+        float *k_new = q_s + G * HD;                 // [HD]
+        float *v_new = k_new + HD;                   // [HD]
+        float *mrg = v_new + HD;                     // [G][WPH][HD + 2]
+        float *raw = mrg + G * WPH * (HD + 2);       // [(G + 2) * HD] new q heads, k row, v row as produced
+        __half *ks = reinterpret_cast<__half *>(raw + (G + 2) * HD);   // [KCH][HD] staged keys
+        __half *vs = ks + (size_t)KCH * HD;                            // [KCH][HD] staged values
+        float *stg = reinterpret_cast<float *>(ks);  // [n_split][HD + 2]: the staging area again, once the keys are done
+
+        const __half *kc = static_cast<const __half *>(ly.k_cache) + (size_t)kvh * p.max_seq * HD;
+        const __half *vc = static_cast<const __half *>(ly.v_cache) + (size_t)kvh * p.max_seq * HD;
+
+        // The block's slice of the cache is two contiguous byte ranges: one bulk copy each into shared
+        // memory, started before the wait for q/k/v so that its latency hides behind that wait. The row
+        // of the new position (not in the cache yet) is copied like the others and never read.
+        auto stage_rows = [&](int c0, int c1) {
+            const unsigned bytes = c1 > c0 ? (unsigned)(c1 - c0) * HD * 2u : 0u;
+            mbar_expect_tx(sm.att_bar, 2u * bytes);
+            if (bytes) {
+                bulk_load(ks, kc + (size_t)c0 * HD, bytes, sm.att_bar);
+                bulk_load(vs, vc + (size_t)c0 * HD, bytes, sm.att_bar);
+            }
+        };
+        if (tid == 0) stage_rows(j0, min(j0 + KCH, j1));
+
+        // ---- the new rows of this KV head ----
+        if (tid == 0) cnt_wait(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, spin);
+        named_barrier(2, ATT_T);
+        {
+            // q heads of this KV head are contiguous; its k row and v row follow at their own offsets
+            const int nq = G * HD;
+#pragma unroll 1
+            for (int i = tid * 2; i < (G + 2) * HD; i += ATT_T * 2) {
+                const int src = i < nq ? kvh * nq + i
+                              : i < nq + HD ? p.n_q * HD + kvh * HD + (i - nq)
+                                            : (p.n_q + p.n_kv) * HD + kvh * HD + (i - nq - HD);
+                float a[1], b[1];
+                fl_poll<1, 2>(p.d_qkv + src, 1, flag, a, b, sm.flags, p.d_err, spin);
+                *reinterpret_cast<float2 *>(raw + i) = make_float2(a[0], b[0]);
+            }
+        }
+        named_barrier(2, ATT_T);
+        if (TRACE && trace && tid == 0) trace[1] = global_ns();
+
+        // ---- normalise + rotate: warp vi < G takes query head vi, warp G the new key and value ----
+        if (warp <= G) {
+            const bool is_k = (warp == G);
+            const float *src = raw + warp * HD;
+            const float *gamma = is_k ? ly.g_kn : ly.g_qn;
             float ss = 0.0f;
-#pragma unroll
-            for (int j = 0; j < HALF / 32; ++j) {
-                const int d = lane + 32 * j;
-                a[j] = __ldcg(src + d); b[j] = __ldcg(src + d + HALF);
-                ss = fmaf(a[j], a[j], ss); ss = fmaf(b[j], b[j], ss);
-            }
+#pragma unroll 1
+            for (int d = lane; d < HD; d += 32) ss = fmaf(src[d], src[d], ss);
             ss = warp_sum(ss);
-            if (gamma) {
-                const float inv = 1.0f / sqrtf(ss / (float)HD + p.eps);
-#pragma unroll
-                for (int j = 0; j < HALF / 32; ++j) {
-                    const int d = lane + 32 * j;
-                    a[j] = gamma[d] * a[j] * inv; b[j] = gamma[d + HALF] * b[j] * inv;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < HALF / 32; ++j) {
-                const int d = lane + 32 * j;
+            const float inv = gamma ? 1.0f / sqrtf(ss / (float)HD + p.eps) : 1.0f;
+            __half *kdst = const_cast<__half *>(kc) + (size_t)pos * HD, *vdst = const_cast<__half *>(vc) + (size_t)pos * HD;
+#pragma unroll 1
+            for (int d = lane; d < HALF; d += 32) {
+                float ra = src[d], rb = src[d + HALF];
+                if (gamma) { ra = gamma[d] * ra * inv; rb = gamma[d + HALF] * rb * inv; }
                 float sn, cs;
-                sincosf((float)pos * op.d_inv_freq[d], &sn, &cs);
-                const float r0 = a[j] * cs - b[j] * sn, r1 = a[j] * sn + b[j] * cs;
+                sincosf((float)pos * ly.inv_freq[d], &sn, &cs);
+                const float r0 = ra * cs - rb * sn;
+                const float r1 = ra * sn + rb * cs;
                 if (is_k) {
                     const __half h0 = __float2half_rn(r0), h1 = __float2half_rn(r1);
                     k_new[d] = __half2float(h0); k_new[d + HALF] = __half2float(h1);
-                    if (split == 0) { kc[(size_t)pos * HD + d] = h0; kc[(size_t)pos * HD + d + HALF] = h1; }
+                    if (split == 0) { kdst[d] = h0; kdst[d + HALF] = h1; }
                 } else {
-                    q_s[vi * HD + d] = r0; q_s[vi * HD + d + HALF] = r1;
+                    q_s[warp * HD + d] = r0; q_s[warp * HD + d + HALF] = r1;
                 }
             }
             if (is_k) {
-                const float *vsrc = op.d_qkv + (size_t)(p.n_q + p.n_kv) * HD + (size_t)kvh * HD;
+                const float *vsrc = raw + (G + 1) * HD;
+#pragma unroll 1
                 for (int d = lane; d < HD; d += 32) {
-                    const __half h = __float2half_rn(__ldcg(vsrc + d));
+                    const __half h = __float2half_rn(vsrc[d]);
                     v_new[d] = __half2float(h);
-                    if (split == 0) vc[(size_t)pos * HD + d] = h;
+                    if (split == 0) vdst[d] = h;
                 }
             }
         }
-        named_barrier(11, ATT_T);
+        named_barrier(2, ATT_T);
 
+        // ---- the keys of this lane, from shared memory: online softmax in registers ----
+        float q[DPT], acc[DPT];
+#pragma unroll
+        for (int e = 0; e < DPT; ++e) { q[e] = q_s[g * HD + dl * DPT + e]; acc[e] = 0.0f; }
         const float scale = 1.0f / sqrtf((float)HD);
-        for (int j = j0 + tid; j < j1; j += ATT_T) {
-            float acc[G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[g] = 0.0f;
-            if (j == pos) {
-                for (int d = 0; d < HD; ++d) {
-                    const float kv = k_new[d];
-#pragma unroll
-                    for (int g = 0; g < G; ++g) acc[g] = fmaf(q_s[g * HD + d], kv, acc[g]);
-                }
-            } else {
-                const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * HD);
-#pragma unroll 4
-                for (int c = 0; c < HD / 8; ++c) {
-                    float kf[8];
-                    halves8_to_float(__ldcg(kr + c), kf);
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const float4 qa = *reinterpret_cast<const float4 *>(q_s + g * HD + 8 * c);
-                        const float4 qb = *reinterpret_cast<const float4 *>(q_s + g * HD + 8 * c + 4);
-                        float t = acc[g];
-                        t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t); t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
-                        t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t); t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
-                        acc[g] = t;
-                    }
-                }
+        float m = -INFINITY, lsum = 0.0f;
+#pragma unroll 1
+        for (int sub = 0; sub < nsub; ++sub) {
+            const int c0 = min(j0 + sub * KCH, j1), c1 = min(c0 + KCH, j1);
+            if (sub > 0) {
+                named_barrier(2, ATT_T);             // everybody is done with the rows staged before
+                if (tid == 0) stage_rows(c0, c1);
             }
+            if (!mbar_wait_abort(sm.att_bar, (unsigned)(l * nsub + sub) & 1u, sm.flags, spin) && !sm.flags[0]) raise(sm.flags, p.d_err, 6);
+            // same trip count for every key lane of the block, so that the warp-wide shuffles stay convergent
+            const int rounds = (c1 - c0 + KL - 1) / KL;
+#pragma unroll 1
+            for (int it = 0, j = c0 + kl; it < rounds; ++it, j += KL) {
+                const bool valid = j < c1;           // every lane of the warp runs the shuffles; only valid keys count
+                float kf[DPT], vf[DPT];
+                if (!valid) {
 #pragma unroll
-            for (int g = 0; g < G; ++g) scores[(size_t)g * chunk_cap + (j - j0)] = acc[g] * scale;
-        }
-        named_barrier(11, ATT_T);
-
-        for (int g = warp; g < G; g += NW) {
-            float *sc = scores + (size_t)g * chunk_cap;
-            float m = -INFINITY;
-            for (int i = lane; i < len; i += 32) m = fmaxf(m, sc[i]);
-            m = warp_max(m);
-            float l = 0.0f;
-            for (int i = lane; i < len; i += 32) { const float e = expf(sc[i] - m); sc[i] = e; l += e; }
-            l = warp_sum(l);
-            if (lane == 0) { ml[2 * g] = m; ml[2 * g + 1] = l; }
-        }
-        named_barrier(11, ATT_T);
-
-        {
-            const int kl = lane / TPK, dl = lane % TPK;
-            float acc[G][8];
+                    for (int e = 0; e < DPT; ++e) { kf[e] = 0.0f; vf[e] = 0.0f; }
+                } else if (j == pos) {
 #pragma unroll
-            for (int g = 0; g < G; ++g)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[g][e] = 0.0f;
-            for (int j = j0 + warp * KPW + kl; j < j1; j += NW * KPW) {
-                float vf[8];
-                if (j == pos) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) vf[e] = v_new[8 * dl + e];
+                    for (int e = 0; e < DPT; ++e) { kf[e] = k_new[dl * DPT + e]; vf[e] = v_new[dl * DPT + e]; }
                 } else {
-                    halves8_to_float(__ldcg(reinterpret_cast<const uint4 *>(vc + (size_t)j * HD) + dl), vf);
+                    halves8_to_float(*reinterpret_cast<const uint4 *>(ks + (size_t)(j - c0) * HD + dl * DPT), kf);
+                    halves8_to_float(*reinterpret_cast<const uint4 *>(vs + (size_t)(j - c0) * HD + dl * DPT), vf);
                 }
+                float s = 0.0f;
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float pj = scores[(size_t)g * chunk_cap + (j - j0)];
+                for (int e = 0; e < DPT; ++e) s = fmaf(q[e], kf[e], s);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
+                for (int o = 1; o < DLN; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                s *= scale;
+                if (valid) {
+                    const float mn = fmaxf(m, s);
+                    const float corr = expf(m - mn), pj = expf(s - mn);
+                    lsum = fmaf(lsum, corr, pj);
+#pragma unroll
+                    for (int e = 0; e < DPT; ++e) acc[e] = fmaf(acc[e], corr, pj * vf[e]);
+                    m = mn;
                 }
-            }
-#pragma unroll
-            for (int o = TPK; o < 32; o <<= 1)
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
-            if (lane < TPK) {
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) ored[((size_t)warp * G + g) * HD + 8 * dl + e] = acc[g][e];
             }
         }
-        named_barrier(11, ATT_T);
-        for (int o = tid; o < G * HD; o += ATT_T) {
-            const int g = o / HD, d = o % HD;
+
+        // ---- merge the key lanes of a head: inside the warp, then across the head's warps ----
+#pragma unroll 1
+        for (int o = DLN; o < 32; o <<= 1) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, lsum, o);
+            const float mn = fmaxf(m, mo);
+            const float ca = (m == -INFINITY) ? 0.0f : expf(m - mn), cb = (mo == -INFINITY) ? 0.0f : expf(mo - mn);
+            lsum = lsum * ca + lo * cb;
+#pragma unroll
+            for (int e = 0; e < DPT; ++e) acc[e] = acc[e] * ca + __shfl_xor_sync(0xffffffffu, acc[e], o) * cb;
+            m = mn;
+        }
+        const int wh = r >> 5;                       // warp index inside the head group
+        if ((r & 31) < DLN) {                        // key lane 0 of each warp holds the warp's state
+            float *dst = mrg + ((size_t)g * WPH + wh) * (HD + 2);
+#pragma unroll
+            for (int e = 0; e < DPT; ++e) dst[dl * DPT + e] = acc[e];
+            if (dl == 0) { dst[HD] = m; dst[HD + 1] = lsum; }
+        }
+        named_barrier(2, ATT_T);
+        // record of (head, split): unnormalised output [HD], running max, sum
+        unsigned nst = 0;
+#pragma unroll 1
+        for (int o = tid; o < G * (HD + 2); o += ATT_T) {
+            const int gg = o / (HD + 2), d = o - gg * (HD + 2);
+            const float *src = mrg + (size_t)gg * WPH * (HD + 2);
+            float M = -INFINITY;
+#pragma unroll 1
+            for (int w = 0; w < WPH; ++w) M = fmaxf(M, src[w * (HD + 2) + HD]);
             float v = 0.0f;
+            if (d == HD) v = M;
+            else {
+#pragma unroll 1
+                for (int w = 0; w < WPH; ++w) {
+                    const float mw = src[w * (HD + 2) + HD];
+                    const float cf = (mw == -INFINITY) ? 0.0f : expf(mw - M);
+                    v = fmaf(src[w * (HD + 2) + d], cf, v);
+                }
+            }
+            fl_store(p.d_attn_part + ((size_t)(kvh * G + gg) * p.n_split + split) * (HD + 2) + d, v, flag);
+            ++nst;
+        }
+        nst = (unsigned)__reduce_add_sync(0xffffffffu, nst);
+        if (lane == 0 && nst) cnt_add(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, nst);
+        if (TRACE && trace && tid == 0) trace[3] = global_ns();
+
+        // ---- this block merges the splits of query heads split, split + n_split, ... of its KV head ----
+#pragma unroll 1
+        for (int gm = split; gm < G; gm += p.n_split) {
+            const int head = kvh * G + gm;
+            const b200_flagged *rec = p.d_attn_part + (size_t)head * p.n_split * (HD + 2);
+            if (tid == 0)
+                cnt_wait(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, cnt_mul * (unsigned)(p.n_split * G * (HD + 2)), sm.flags, spin);
+            named_barrier(2, ATT_T);                 // also: the staging area is free (keys done, previous head merged)
+            {
+                constexpr int NB = 4;
+                const int tot = p.n_split * (HD + 2);
+#pragma unroll 1
+                for (int i0 = tid * 2; i0 < tot; i0 += ATT_T * 2 * NB) {
+                    float a[NB], b[NB];
+                    fl_poll<NB, ATT_T * 2>(rec + i0, (tot - i0 + ATT_T * 2 - 1) / (ATT_T * 2), flag, a, b, sm.flags, p.d_err, spin);
 #pragma unroll
-            for (int k = 0; k < NW; ++k) v += ored[((size_t)k * G + g) * HD + d];
-            p.d_attn_scratch[((size_t)(kvh * G + g) * p.n_split + split) * (HD + 2) + d] = v;
-        }
-        if (tid < 2 * G) {
-            const int g = tid >> 1;
-            p.d_attn_scratch[((size_t)(kvh * G + g) * p.n_split + split) * (HD + 2) + HD + (tid & 1)] = ml[tid];
-        }
-        __threadfence();
-        named_barrier(11, ATT_T);
-        if (tid == 0) sm.flags[1] = (atomicAdd(p.d_attn_tickets + kvh, 1u) == (unsigned)p.n_split - 1u);
-        named_barrier(11, ATT_T);
-        if (sm.flags[1]) {
-            __threadfence();
-            for (int o = tid; o < G * HD; o += ATT_T) {
-                const int g = o / HD, d = o % HD;
-                const float *base = p.d_attn_scratch + (size_t)(kvh * G + g) * p.n_split * (HD + 2);
-                float M = -INFINITY;
-                for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, __ldcg(base + (size_t)s * (HD + 2) + HD));
-                float Lsum = 0.0f, acc = 0.0f;
-                for (int s = 0; s < p.n_split; ++s) {
-                    const float m = __ldcg(base + (size_t)s * (HD + 2) + HD);
-                    const float l = __ldcg(base + (size_t)s * (HD + 2) + HD + 1);
-                    if (l > 0.0f) {
-                        const float w = expf(m - M);
-                        Lsum = fmaf(l, w, Lsum);
-                        acc = fmaf(__ldcg(base + (size_t)s * (HD + 2) + d), w, acc);
+                    for (int u = 0; u < NB; ++u) {
+                        const int i = i0 + u * ATT_T * 2;
+                        if (i < tot) *reinterpret_cast<float2 *>(stg + i) = make_float2(a[u], b[u]);
                     }
                 }
-                op.d_attn_out[(size_t)(kvh * G + g) * HD + d] = acc / Lsum;
             }
-            if (tid == 0) p.d_attn_tickets[kvh] = 0u;
-            __threadfence();
+            named_barrier(2, ATT_T);
+            unsigned nout = 0;
+#pragma unroll 1
+            for (int d = tid; d < HD; d += ATT_T) {
+                float M = -INFINITY;
+#pragma unroll 1
+                for (int s = 0; s < p.n_split; ++s)
+                    if (stg[s * (HD + 2) + HD + 1] > 0.0f) M = fmaxf(M, stg[s * (HD + 2) + HD]);
+                float Lsum = 0.0f, O = 0.0f;
+#pragma unroll 1
+                for (int s = 0; s < p.n_split; ++s) {
+                    const float ls = stg[s * (HD + 2) + HD + 1];
+                    const float wgt = ls > 0.0f ? expf(stg[s * (HD + 2) + HD] - M) : 0.0f;
+                    Lsum = fmaf(ls, wgt, Lsum);
+                    O = fmaf(stg[s * (HD + 2) + d], wgt, O);
+                }
+                fl_store(p.d_attn_out + (size_t)head * HD + d, O / Lsum, flag);
+                ++nout;
+            }
+            nout = (unsigned)__reduce_add_sync(0xffffffffu, nout);
+            if (lane == 0 && nout) cnt_add(p.d_counters + B200_CNT_ATTN * B200_CNT_STRIDE, nout);
         }
-        named_barrier(11, ATT_T);               // smem is reused by the next item
+    }
+    // the o stage reuses the scratch area: nobody goes on before the attention threads are done with it
+    named_barrier(1, TK_NC);
+    if (TRACE && trace && tid == 0) trace[4] = global_ns();
+}
+
+// ---------------------------------------------------------------------------
+// Producer: one thread issues every bulk copy of the block, stage after stage. Returns the advanced
+// chunk number; bit 31 set = gave up.
+// ---------------------------------------------------------------------------
+// Asks L2 for this block's rows of a stage that the ring will only reach later: while the consumers
+// hand results over (and the ring is full) HBM keeps working, and the ring later fills at L2 speed.
+__device__ __forceinline__ void prefetch_share(const b200_token_args &p, int kind, const void *d_w)
+{
+    const b200_stage_geom &G = p.g[kind];
+    const RowRange br = block_rows(G, blockIdx.x);
+    const unsigned char *a = static_cast<const unsigned char *>(d_w) + (size_t)br.r0 * G.row_stride;
+    long long left = (long long)(br.r1 - br.r0) * G.row_stride;
+    if (left > (long long)p.l2_ahead_bytes) left = p.l2_ahead_bytes;
+#pragma unroll 1
+    for (; left > 0; left -= 16384, a += 16384) {
+        const unsigned n = left < 16384 ? (unsigned)left : 16384u;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a), "r"(n) : "memory");
     }
 }
 
-// WIDE: the plan contains rows so long that a thread owns two slices (more registers); kept out of the
-// common instantiation so that it does not cost the narrow steps their registers.
-template <int WT, bool WIDE>
+__device__ __noinline__ unsigned produce_stage(const b200_token_args &p, int kind, const void *d_w, unsigned seq, unsigned long long *trace)
+{
+    const b200_stage_geom &G = p.g[kind];
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const int rb = G.rb;
+    const RowRange br = block_rows(G, blockIdx.x);
+    const unsigned char *wbase = static_cast<const unsigned char *>(d_w);
+    const unsigned stride = (unsigned)G.row_stride;
+    const uint32_t ring_s = smem_u32(sm.ring), full_s = smem_u32(sm.full);
+    bool first = true;
+#pragma unroll 1
+    for (int w0 = br.r0; w0 < br.r1; w0 += G.pw) {
+        const int w1 = w0 + G.pw < br.r1 ? w0 + G.pw : br.r1;
+#pragma unroll 1
+        for (int row0 = w0; row0 < w1; row0 += rb) {
+            const unsigned slot = seq % TK_SLOTS;
+            if (seq >= TK_SLOTS && !mbar_wait_abort(&sm.empty[slot], (seq / TK_SLOTS - 1u) & 1u, sm.flags, spin)) {
+                if (!sm.flags[0]) raise(sm.flags, p.d_err, 2);
+                return seq | 0x80000000u;
+            }
+            const unsigned bytes = (unsigned)(w1 - row0 < rb ? w1 - row0 : rb) * stride;
+            const uint32_t bar = full_s + slot * 8u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(ring_s + slot * (unsigned)TK_SLOT_BYTES), "l"(wbase + (size_t)row0 * stride), "r"(bytes), "r"(bar) : "memory");
+            if (trace) { const unsigned long long t = global_ns(); if (first) { trace[5] = t; first = false; } trace[6] = t; }
+            ++seq;
+        }
+    }
+    return sm.flags[0] ? (seq | 0x80000000u) : seq;
+}
+
+template <int WT, bool TRACE>
 __global__ void __launch_bounds__(TK_THREADS, 1)
 decode_token_kernel(const __grid_constant__ b200_token_args p)
 {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ b200_op s_op;
-    const Smem sm = carve(smem_raw);
+    const Smem sm = smem_of(p);
     const int tid = threadIdx.x;
+    const int spin = spin_of(p);
+    const int L = p.n_layers;
 
     if (tid == 0) {
-        for (int i = 0; i < TK_SLOTS; ++i) { mbar_init(&sm.full[i], 1); mbar_init(&sm.empty[i], 1); }
-        sm.flags[0] = 0; sm.flags[1] = 0; sm.flags[2] = 0; sm.flags[3] = 0;
-        for (int i = 0; i < TK_SLOTS; ++i) sm.cnt[i] = 0;
+        for (int i = 0; i < TK_SLOTS; ++i) { mbar_init(&sm.full[i], 1); mbar_init(&sm.empty[i], TK_NWARP); }
+        mbar_init(sm.att_bar, 1);
+        sm.flags[0] = 0; sm.flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    {   // the layer table, once per token: every later pointer read is a shared-memory load
+        const int words = L * (int)(sizeof(b200_token_layer) / 8);
+        const unsigned long long *src = reinterpret_cast<const unsigned long long *>(p.d_layers);
+        unsigned long long *dst = reinterpret_cast<unsigned long long *>(const_cast<b200_token_layer *>(sm.layers));
+        for (int i = tid; i < words; i += TK_THREADS) dst[i] = src[i];
+    }
     __syncthreads();
+    unsigned long long *tr = (TRACE && p.d_trace) ? p.d_trace + (size_t)blockIdx.x * (6 * L + 1) * TK_TRACE_WORDS : nullptr;
 
-    // ---------------- producer warp: runs ahead through the whole step list ----------------
-    if (tid >= TK_CONSUMERS) {
-        if (tid == TK_CONSUMERS) {
-            int fills[TK_SLOTS];
-            for (int i = 0; i < TK_SLOTS; ++i) fills[i] = 0;
-            bool dead = false;
-            for (int oi = 0; oi < p.n_ops && !dead; ++oi) {
-                const b200_op &op = p.d_ops[oi];
-                if (op.type != B200_OP_MATVEC) continue;
-                const int rb = op.rb, NG = op.NG, spg = TK_SLOTS / NG;
-                const RowSplit br = block_rows(op);
-                // per-group row ranges once per step: the issue loop below must stay a handful of instructions per copy
-                int g0[TK_SLOTS], g1[TK_SLOTS], maxk = 0;
-                for (int g = 0; g < NG; ++g) {
-                    const RowSplit gr = group_rows(op, br, g);
-                    g0[g] = gr.r0; g1[g] = gr.r1;
-                    maxk = max(maxk, (gr.r1 - gr.r0 + rb - 1) / rb);
-                }
-                const unsigned char *wbase = static_cast<const unsigned char *>(op.d_w);
-                const unsigned stride = (unsigned)op.row_stride;
-                for (int k = 0; k < maxk && !dead; ++k) {
-                    for (int g = 0; g < NG; ++g) {
-                        const int row0 = g0[g] + k * rb;
-                        if (row0 >= g1[g]) continue;
-                        const int slot = g * spg + (k % spg);
-                        if (fills[slot] > 0 && !mbar_wait_or_abort(&sm.empty[slot], (unsigned)(fills[slot] - 1) & 1u, sm.flags)) {
-                            sm.flags[0] = 1; if (p.d_err) *p.d_err = 2; dead = true; break;
+    // ---------------- producer warp ----------------
+    if (tid >= TK_NC) {
+        if (tid == TK_NC) {
+            unsigned seq = 0;
+#pragma unroll 1
+            for (int l = 0; l < L && !(seq >> 31); ++l) {
+#pragma unroll 1
+                for (int kind = 0; kind < 4 && !(seq >> 31); ++kind) {
+                    const b200_token_layer &ly = sm.layers[l];
+                    const void *w = kind == B200_ST_QKV ? ly.w_qkv : kind == B200_ST_O ? ly.w_o : kind == B200_ST_GATEUP ? ly.w_gateup : ly.w_down;
+                    if (p.l2_ahead_bytes > 0) {
+                        // the stage after this one
+                        const int nk = kind == 3 ? (l + 1 < L ? B200_ST_QKV : (p.with_lm ? B200_ST_LM : -1)) : kind + 1;
+                        if (nk >= 0) {
+                            const b200_token_layer &nl = sm.layers[kind == 3 && l + 1 < L ? l + 1 : l];
+                            const void *nw = nk == B200_ST_QKV ? nl.w_qkv : nk == B200_ST_O ? nl.w_o : nk == B200_ST_GATEUP ? nl.w_gateup
+                                           : nk == B200_ST_DOWN ? nl.w_down : p.w_lm;
+                            prefetch_share(p, nk, nw);
                         }
-                        if (*(volatile int *)sm.flags) { dead = true; break; }
-                        const unsigned bytes = (unsigned)min(rb, g1[g] - row0) * stride;
-                        mbar_expect_tx(&sm.full[slot], bytes);
-                        bulk_load(sm.ring + (size_t)slot * TK_SLOT_BYTES, wbase + (size_t)row0 * stride, bytes, &sm.full[slot]);
-                        ++fills[slot];
                     }
+                    seq = produce_stage(p, kind, w, seq, tr ? tr + (size_t)(6 * l + (kind == 0 ? 0 : kind + 1)) * TK_TRACE_WORDS : nullptr);
                 }
+            }
+            if (!(seq >> 31) && p.with_lm) seq = produce_stage(p, B200_ST_LM, p.w_lm, seq, tr ? tr + (size_t)(6 * L) * TK_TRACE_WORDS : nullptr);
+            seq &= 0x7fffffffu;
+            // copies still in flight must land before the block may leave: wait for the last fill of every slot
+            const unsigned nfill = seq < TK_SLOTS ? seq : TK_SLOTS;
+#pragma unroll 1
+            for (unsigned i = 0; i < nfill; ++i) {
+                const unsigned s = seq - 1u - i;
+                mbar_wait_abort(&sm.full[s % TK_SLOTS], (s / TK_SLOTS) & 1u, sm.flags + 1, spin);   // flags[1] stays 0: a plain bounded wait
             }
         }
         return;
     }
 
     // ---------------- consumers ----------------
+    // One loop over the stages with a single (inlined) call site per stage type: no function calls,
+    // hence nothing saved to and restored from the stack between stages.
     const int pos = *p.d_pos;
     const unsigned ep = *p.d_epoch;
-    unsigned fill_parity = 0, arrivals = 0;
-    float best_v = -INFINITY;
-    int best_i = 0x7fffffff;
-    volatile int *abort_flag = sm.flags;
-
-    for (int oi = 0; oi <= p.n_ops; ++oi) {
-        if (oi > 0) {
-            // everything the previous step wrote must be visible device-wide (and to the peers) before anyone goes on
-            arrivals += gridDim.x;
-            if (!grid_barrier(p.d_grid_barrier, arrivals, tid, abort_flag)) { if (tid == 0 && p.d_err) *p.d_err = 4; break; }
-            if (s_op.n_signal > 0 && blockIdx.x == 0 && tid == 0) {
-                __threadfence_system();
-                const unsigned val = ep * (unsigned)p.epoch_mul + (unsigned)s_op.signal_add;
-                for (int q = 0; q < s_op.n_signal; ++q) st_release_sys(s_op.d_signal_flags[q] + s_op.signal_index, val);
-            }
-            named_barrier(1, TK_CONSUMERS);                 // s_op is about to be overwritten
-        }
-        if (oi == p.n_ops) break;
-        if (tid == 0) sm.flags[2] = sm.flags[0];            // one thread decides for the block whether to go on
-        if (tid < (int)(sizeof(b200_op) / 4))
-            reinterpret_cast<uint32_t *>(&s_op)[tid] = reinterpret_cast<const uint32_t *>(p.d_ops + oi)[tid];
-        named_barrier(1, TK_CONSUMERS);
-        if (s_op.n_wait > 0) {
-            if (tid < s_op.n_wait) {
-                const unsigned want = ep * (unsigned)p.epoch_mul + (unsigned)s_op.wait_add;
-                if (!wait_flag_ge(s_op.d_wait_flags + tid, want)) { *abort_flag = 1; if (p.d_err) *p.d_err = 1; }
-            }
-            named_barrier(1, TK_CONSUMERS);
-        }
-        if (sm.flags[2]) break;
-        unsigned long long *trace = (p.d_step_ns && blockIdx.x == 0) ? p.d_step_ns + 4 * oi : nullptr;
-        if (trace && tid == 0) trace[0] = global_ns();
-        if (s_op.type == B200_OP_MATVEC) {
-#define TK_MV(SPT_, RB_) matvec_step<WT, SPT_, RB_>(s_op, p, sm, tid, pos, fill_parity, best_v, best_i, trace)
-            if (s_op.spt == 1) {
-                switch (s_op.rb) {
-                case 8: TK_MV(1, 8); break;
-                case 4: TK_MV(1, 4); break;
-                case 2: TK_MV(1, 2); break;
-                default: TK_MV(1, 1); break;
-                }
-            } else if (WIDE) {
-                if (s_op.rb == 2) TK_MV(2, 2); else TK_MV(2, 1);
-            }
-#undef TK_MV
-            if (s_op.n_out > 1 || s_op.n_signal > 0) __threadfence_system(); else __threadfence();
-        } else {
-            if (p.hd == 128) attention_step<128, 4>(s_op, p, sm, tid, pos);
-            else if (p.hd == 64) attention_step<64, 4>(s_op, p, sm, tid, pos);
-            else attention_step<256, 4>(s_op, p, sm, tid, pos);
-            __threadfence();
-        }
-        if (trace && tid == 0) trace[1] = global_ns();
-        if (oi == p.n_ops - 1 && p.pick_token) {
-            // this block's best row of the last step -> scratch, before the closing barrier
-            const int T = s_op.T, g = tid / T, t = tid - g * T;
-            if ((tid & 31) < 8) {
-                const bool act = g < s_op.NG;
-                sm.am_v[(tid >> 5) * 8 + (tid & 31)] = act ? best_v : -INFINITY;
-                sm.am_i[(tid >> 5) * 8 + (tid & 31)] = act ? best_i : 0x7fffffff;
-            }
-            named_barrier(1, TK_CONSUMERS);
-            if (tid == 0) {
-                float bv = -INFINITY; int bi = 0x7fffffff;
-                for (int k = 0; k < TK_MAX_WARPS * 8; ++k) if (better(sm.am_v[k], sm.am_i[k], bv, bi)) { bv = sm.am_v[k]; bi = sm.am_i[k]; }
-                p.d_argmax_scratch[2 * blockIdx.x] = bv;
-                reinterpret_cast<int *>(p.d_argmax_scratch)[2 * blockIdx.x + 1] = bi;
-                __threadfence();
+    unsigned long long state = 0;                    // chunk number | window number << 32
+    const bool tail = p.with_lm || p.n_ranks > 1;    // the LM head, or the residual update that ends a prompt position
+#pragma unroll 1
+    for (int l = 0; l <= L; ++l) {
+        if (l == L && !tail) break;
+#pragma unroll 1
+        for (int k = 0; k < 5; ++k) {
+            if (l == L && k > 0) break;
+            unsigned long long *t = tr ? tr + (size_t)(6 * l + k) * TK_TRACE_WORDS : nullptr;
+            if (k == 1) {
+                if (p.hd == 128) attention_stage<128, TRACE>(p, l, ep, t);
+                else if (p.hd == 64) attention_stage<64, TRACE>(p, l, ep, t);
+                else attention_stage<256, TRACE>(p, l, ep, t);
+            } else {
+                const int kind = l == L ? B200_ST_LM : k == 0 ? B200_ST_QKV : k - 1;     // 2, 3, 4 -> o, gate/up, down
+                state = run_matvec<WT, TRACE>(p, kind, l, ep, state, t);
             }
         }
     }
 
-    // ---------------- closing work of block 0, warp 0 ----------------
-    if (blockIdx.x == 0 && tid < 32 && !sm.flags[2]) {
-        const int lane = tid;
-        int tok = 0;
-        if (p.pick_token) {
+    const unsigned flag_lm = ep * (unsigned)(L + 1) + (unsigned)L + 1u;
+    if (p.with_lm) {
+        // --- block 0 folds the best rows of all blocks (and all ranks) ---
+        if (blockIdx.x == 0 && tid < 32) {
+            const int lane = tid;
             float bv = -INFINITY; int bi = 0x7fffffff;
-            for (int b = lane; b < (int)gridDim.x; b += 32) {
-                const float v = __ldcg(p.d_argmax_scratch + 2 * b);
-                const int i = __ldcg(reinterpret_cast<const int *>(p.d_argmax_scratch) + 2 * b + 1);
-                if (better(v, i, bv, bi)) { bv = v; bi = i; }
-            }
+#pragma unroll 1
+            for (int b0 = lane; b0 < (int)gridDim.x; b0 += 32 * 4) {
+                float v[4], fi[4];
+                const int cnt = ((int)gridDim.x - b0 + 31) / 32;
+                fl_poll<4, 64>(p.d_am + 2 * b0, cnt, flag_lm, v, fi, sm.flags, p.d_err, spin);
 #pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < cnt && better(v[u], __float_as_int(fi[u]), bv, bi)) { bv = v[u]; bi = __float_as_int(fi[u]); }
+            }
+#pragma unroll 1
             for (int o = 16; o > 0; o >>= 1) {
                 const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi2 = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (better(ov, oi2, bv, bi)) { bv = ov; bi = oi2; }
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
             }
-            if (bi == 0x7fffffff) bi = 0;               // nothing compared greater (all NaN): index 0, as the reference's loop
-            bi += (int)s_op.out_offset;
+            if (bi == 0x7fffffff) bi = 0;            // nothing compared greater (all NaN): index 0, as the reference's loop
+            bi += (int)p.logits_offset;              // global row of a sharded LM head
             if (p.n_ranks > 1) {
-                // push (value, row) to every rank, raise the flag, then take the best of all ranks
-                if (lane < p.n_ranks) { p.d_argmax_val[lane][0] = bv; p.d_argmax_idx[lane][0] = bi; }
+                // (value, row) to every rank, then the best of all ranks, lowest row on ties
                 __threadfence_system();
-                __syncwarp();
-                const unsigned val = ep * (unsigned)p.epoch_mul + (unsigned)p.argmax_add;
-                if (lane < p.n_ranks) st_release_sys(p.d_argmax_signal_flags[lane] + p.rank, val);
-                bool ok = true;
-                if (lane < p.n_ranks) ok = wait_flag_ge(p.d_argmax_wait_flags + lane, val);
-                if (!ok && p.d_err) *p.d_err = 1;
-                __syncwarp();
-                float gv = -INFINITY; int gi = 0x7fffffff;
-                for (int r = 0; r < p.n_ranks; ++r) {
-                    const float v = __ldcv(p.d_rank_vals + r);
-                    const int i = __ldcv(p.d_rank_idx + r);
-                    if (better(v, i, gv, gi)) { gv = v; gi = i; }
+                if (lane < p.n_ranks) {
+                    fl_store(p.d_peer_am[lane], bv, flag_lm);
+                    fl_store(p.d_peer_am[lane] + 1, __int_as_float(bi), flag_lm);
                 }
-                if (gi == 0x7fffffff) gi = 0;
-                bi = gi;
+                float gv[1], gf[1];
+                fl_poll<1, 2>(p.d_am_rank + 2 * (lane < p.n_ranks ? lane : 0), lane < p.n_ranks ? 1 : 0, flag_lm, gv, gf, sm.flags, p.d_err, spin);
+                float xv = lane < p.n_ranks ? gv[0] : -INFINITY;
+                int xi = lane < p.n_ranks ? __float_as_int(gf[0]) : 0x7fffffff;
+#pragma unroll 1
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, xv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, xi, o);
+                    if (better(ov, oi, xv, xi)) { xv = ov; xi = oi; }
+                }
+                if (xi == 0x7fffffff) xi = 0;
+                bi = xi;
+                __threadfence_system();
             }
-            tok = bi;
-        }
-        if (lane == 0) {
-            if (p.pick_token && pos + 1 >= *p.d_prompt_len) p.d_tokens[pos + 1] = tok;
-            *p.d_pos = pos + 1;
-            *p.d_epoch = ep + 1u;
+            if (lane == 0 && pos + 1 >= *p.d_prompt_len) p.d_tokens[pos + 1] = bi;
         }
     }
-    // the last block to get here re-arms the barrier counters for the next launch
-    if (tid == 0) {
-        __threadfence();
-        if (atomicAdd(p.d_grid_barrier + 1, 1u) == gridDim.x - 1) {
-            p.d_grid_barrier[0] = 0u;
-            p.d_grid_barrier[1] = 0u;
-            __threadfence();
-        }
+    if (blockIdx.x == 0 && tid == 0) {
+        *p.d_pos = pos + 1;
+        *p.d_epoch = ep + 1u;
     }
 }
 
 int g_tk_sm_count = 0;
 
+int tk_sm_count()
+{
+    if (!g_tk_sm_count) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            return 0;
+        g_tk_sm_count = n;
+    }
+    return g_tk_sm_count;
+}
+
+int plan_stage(b200_stage_geom &g, int wtype, int n_blocks, int xin_floats)
+{
+    if (g.rows <= 0 || g.cols <= 0 || g.row_stride <= 0 || (g.row_stride % 16)) return B200_E_BADARG;
+    if (wtype == B200_WT_Q8 ? (g.cols % 32) : (g.cols % 8)) return B200_E_BADARG;
+    if (g.row_stride < (long long)b200_packed_row_stride(wtype, g.cols)) return B200_E_BADARG;
+    const int ralign = g.glu ? 2 : 1;
+    if (g.rows % ralign) return B200_E_BADARG;
+    const int E = wtype == B200_WT_Q8 ? 16 : 8;
+    const int nsl = (g.cols + E - 1) / E;
+    // Up to two slices per thread; a group is at most 320 threads so that wide rows still leave two groups.
+    g.spt = nsl <= 320 ? 1 : 2;
+    g.T = (((nsl + g.spt - 1) / g.spt) + 31) / 32 * 32;
+    if (g.T > TK_NC) return B200_E_TOOLARGE;
+    g.NG = TK_NC / g.T;
+    if (g.NG > TK_NWARP) g.NG = TK_NWARP;
+    // a chunk (one ring slot) holds rg rows for each group: as many as fit, a power of two up to 8
+    // (2 with two slices per thread: the row partials of a chunk live in registers)
+    const int fit = (int)(TK_SLOT_BYTES / g.row_stride);          // rows per slot
+    if (fit < ralign) return B200_E_TOOLARGE;
+    while (g.NG > 1 && g.NG * ralign > fit) --g.NG;               // a slot must hold at least one row (pair) per group
+    int rg = g.spt == 1 ? 8 : 2;
+    while (rg > ralign && rg * g.NG > fit) rg >>= 1;
+    if (rg * g.NG > fit || rg < ralign) return B200_E_TOOLARGE;
+    g.rg = rg;
+    g.rb = rg * g.NG;
+    const int nwgp = (g.T / 32) | 1;
+    int pw = TK_PART / nwgp;                           // rows whose warp partials fit one buffer
+    pw -= pw % g.rb;                                   // whole chunks in a full window
+    if (pw < g.rb) return B200_E_TOOLARGE;
+    g.pw = pw;
+    const int units = g.rows / ralign;
+    g.cta_base = units / n_blocks;
+    g.cta_rem = units % n_blocks;
+    if (g.cols > xin_floats) return B200_E_TOOLARGE;   // the input vector is held in shared memory once per block
+    g.direct_in = 0;
+    return 0;
+}
+
 } // namespace
 
-extern "C" int b200_op_plan_matvec(b200_op *op, int wtype)
+extern "C" int b200_token_plan(b200_token_args *a, int n_blocks)
 {
-    if (!op || op->rows <= 0 || op->cols <= 0 || op->row_stride <= 0) return B200_E_BADARG;
-    const int E = wtype == B200_WT_Q8 ? 16 : 8;
-    const int nsl = (op->cols + E - 1) / E;
-    int spt = nsl <= TK_CONSUMERS ? 1 : 2;
-    int T = (((nsl + spt - 1) / spt) + 31) / 32 * 32;
-    if (T > TK_CONSUMERS) return B200_E_TOOLARGE;
-    int ng = TK_CONSUMERS / T;                               // power of two <= 8: slots are split evenly between groups
-    int p2 = 1;
-    while (p2 * 2 <= ng && p2 * 2 <= TK_SLOTS) p2 *= 2;
-    const int ralign = op->out_mode == B200_OUT_GLU ? 2 : 1;
-    int rb = spt == 1 ? 8 : 2;
-    while (rb > 1 && (long long)rb * op->row_stride > TK_SLOT_BYTES) rb >>= 1;
-    if ((long long)rb * op->row_stride > TK_SLOT_BYTES || rb < ralign) return B200_E_TOOLARGE;
-    op->spt = spt; op->T = T; op->NG = p2; op->rb = rb;
+    if (!a || a->n_layers <= 0 || a->d_model <= 0 || (a->d_model % 4)) return B200_E_BADARG;
+    if (a->wtype != B200_WT_Q8 && a->wtype != B200_WT_F16) return B200_E_BADARG;
+    if (a->n_kv <= 0 || a->n_q <= 0 || a->n_q % a->n_kv || (a->hd != 64 && a->hd != 128 && a->hd != 256)) return B200_E_BADARG;
+    const int G = a->n_q / a->n_kv;
+    if (G != 1 && G != 2 && G != 4 && G != 8) return B200_E_BADARG;
+    if (a->n_ranks < 1 || a->n_ranks > B200_MAX_PEERS || a->rank < 0 || a->rank >= a->n_ranks) return B200_E_BADARG;
+    if (n_blocks <= 0) n_blocks = tk_sm_count();
+    if (n_blocks <= 0) return B200_E_STATE;
+    // sequence splits: items (kv head, split) must fit the blocks; at least 32 cache rows per split at full
+    // length; by default few enough that the block merging a head reads little (18, or 9 for wide heads)
+    int ns = a->n_split > 0 ? a->n_split : (a->hd > 128 ? 9 : 18);
+    if (ns > n_blocks / a->n_kv) ns = n_blocks / a->n_kv;
+    if (ns > (a->max_seq + 31) / 32) ns = (a->max_seq + 31) / 32;
+    if (ns > 32) ns = 32;
+    if (ns < 1) return B200_E_TOOLARGE;                // more KV heads than blocks
+    a->n_split = ns;
+    // Shared memory beyond the ring and the fixed areas is one scratch area: the block-wide input vector
+    // of the o and down stages, the slot sums of a normalised residual update, and the attention stage's
+    // buffers with as many staged cache rows as fit.
+    const Layout fixed = make_layout(a->n_layers, a->d_model, 0);
+    int scratch = (232448 - 128 - fixed.total) / 4;
+    scratch -= scratch % 4;
+    const int att_fixed = attention_fixed_floats(G, a->hd);
+    const int chunk_cap = (a->max_seq + ns - 1) / ns;
+    int keys = scratch > att_fixed ? (scratch - att_fixed) / a->hd : 0;
+    if (keys > chunk_cap) keys = chunk_cap;
+    if (keys * a->hd < ns * (a->hd + 2) || keys < 1 || scratch < 2 * a->d_model) return B200_E_TOOLARGE;
+    a->att_keys = keys;
+    int need = att_fixed + keys * a->hd;               // what is actually used: the rest is left to L1
+    if (need < 2 * a->d_model) need = 2 * a->d_model;  // slot sums and the stage's norm weights
+    for (int k = 0; k < B200_ST_KINDS; ++k) {
+        int rc = plan_stage(a->g[k], a->wtype, n_blocks, scratch);
+        if (rc) return rc;
+        if ((k == B200_ST_O || k == B200_ST_DOWN) && !a->g[k].direct_in && a->g[k].cols > need) need = a->g[k].cols;
+    }
+    scratch = (need + 3) / 4 * 4;
+    if (a->l2_ahead_bytes == 0) a->l2_ahead_bytes = 512 << 10;   // default: up to 512 KB of the next stage per block
+    if (a->l2_ahead_bytes < 0) a->l2_ahead_bytes = 0;
+    if (a->g[B200_ST_QKV].cols != a->d_model || a->g[B200_ST_GATEUP].cols != a->d_model || !a->g[B200_ST_GATEUP].glu ||
+        a->g[B200_ST_QKV].rows != (a->n_q + 2 * a->n_kv) * a->hd || a->g[B200_ST_O].cols != a->n_q * a->hd ||
+        a->g[B200_ST_O].rows != a->d_model || a->g[B200_ST_DOWN].rows != a->d_model ||
+        a->g[B200_ST_DOWN].cols != a->g[B200_ST_GATEUP].rows / 2 || a->g[B200_ST_QKV].glu || a->g[B200_ST_O].glu ||
+        a->g[B200_ST_DOWN].glu || a->g[B200_ST_LM].cols != a->d_model || a->g[B200_ST_LM].glu)
+        return B200_E_BADARG;
+    a->scratch_floats = scratch;
+    a->n_blocks = n_blocks;
+    const Layout lo = make_layout(a->n_layers, a->d_model, scratch);
+    a->smem_bytes = lo.total;
+    if (a->smem_bytes > 232448) return B200_E_TOOLARGE;
     return 0;
+}
+
+extern "C" int b200_token_chunks(const b200_token_args *a, int kind, int block, int *out, int cap)
+{
+    if (!a || kind < 0 || kind >= B200_ST_KINDS || block < 0 || block >= a->n_blocks) return B200_E_BADARG;
+    const b200_stage_geom &G = a->g[kind];
+    const RowRange br = block_rows(G, block);
+    int n = 0;
+    for (int w0 = br.r0; w0 < br.r1; w0 += G.pw) {
+        const int w1 = w0 + G.pw < br.r1 ? w0 + G.pw : br.r1;
+        for (int row0 = w0; row0 < w1; row0 += G.rb) {
+            if (out && n < cap) { out[3 * n] = row0; out[3 * n + 1] = min(G.rb, w1 - row0); out[3 * n + 2] = (w0 - br.r0) / G.pw; }
+            ++n;
+        }
+    }
+    return n;
 }
 
 extern "C" int b200_decode_token(const b200_token_args *ap, void *stream)
 {
-    if (!ap || !ap->d_ops || ap->n_ops <= 0 || !ap->d_pos || !ap->d_tokens || !ap->d_prompt_len || !ap->d_epoch ||
-        !ap->d_grid_barrier || !ap->d_emb || !ap->d_attn_scratch || !ap->d_attn_tickets || !ap->d_argmax_scratch)
+    if (!ap || !ap->d_layers || !ap->d_pos || !ap->d_tokens || !ap->d_prompt_len || !ap->d_epoch || !ap->d_err || !ap->d_emb ||
+        !ap->d_qkv || !ap->d_attn_part || !ap->d_attn_out || !ap->d_act || !ap->d_slots_o || !ap->d_slots_dn || !ap->d_counters)
         return B200_E_BADARG;
-    if (ap->wtype != B200_WT_Q8 && ap->wtype != B200_WT_F16) return B200_E_BADARG;
-    if (ap->n_kv <= 0 || ap->n_q != 4 * ap->n_kv || (ap->hd != 64 && ap->hd != 128 && ap->hd != 256) || ap->n_split <= 0 ||
-        ap->n_ranks < 1 || ap->n_ranks > B200_MAX_PEERS)
-        return B200_E_BADARG;
-    const int chunk_cap = (ap->max_seq + ap->n_split - 1) / ap->n_split;
-    const size_t att = ((size_t)4 * ap->hd + 2 * ap->hd + 16 + (size_t)4 * chunk_cap + (size_t)(ATT_T / 32) * 4 * ap->hd) * sizeof(float);
-    if (att > TK_ATT_BYTES) return B200_E_TOOLARGE;
-    if (!g_tk_sm_count) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        g_tk_sm_count = n;
-    }
-    void (*kern)(const b200_token_args) =
-        ap->wtype == B200_WT_Q8 ? (ap->wide ? decode_token_kernel<B200_WT_Q8, true> : decode_token_kernel<B200_WT_Q8, false>)
-                                : (ap->wide ? decode_token_kernel<B200_WT_F16, true> : decode_token_kernel<B200_WT_F16, false>);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TK_SMEM_BYTES);
+    if (ap->n_blocks <= 0 || ap->smem_bytes <= 0 || ap->scratch_floats <= 0) return B200_E_STATE;   // b200_token_plan first
+    if (ap->with_lm && (!ap->w_lm || !ap->g_final || !ap->d_logits || !ap->d_am || ap->g[B200_ST_LM].rows <= 0)) return B200_E_BADARG;
+    if (ap->n_ranks > 1 && ap->with_lm && !ap->d_am_rank) return B200_E_BADARG;
+    for (int q = 0; q < ap->n_ranks; ++q)
+        if (!ap->d_peer_slots_o[q] || !ap->d_peer_slots_dn[q] || !ap->d_peer_counters[q] || (ap->n_ranks > 1 && ap->with_lm && !ap->d_peer_am[q])) return B200_E_BADARG;
+    if (ap->n_kv * ap->n_split > ap->n_blocks || B200_CNT_PART + ap->n_kv > 72) return B200_E_BADARG;
+    const int sms = tk_sm_count();
+    if (sms <= 0) return B200_E_STATE;
+    if (ap->n_blocks > sms) return B200_E_TOOLARGE;    // all blocks must be resident at once
+    void (*kern)(const b200_token_args);
+    if (ap->wtype == B200_WT_Q8) kern = ap->d_trace ? decode_token_kernel<B200_WT_Q8, true> : decode_token_kernel<B200_WT_Q8, false>;
+    else kern = ap->d_trace ? decode_token_kernel<B200_WT_F16, true> : decode_token_kernel<B200_WT_F16, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ap->smem_bytes);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(g_tk_sm_count);
+    cfg.gridDim = dim3(ap->n_blocks);
     cfg.blockDim = dim3(TK_THREADS);
-    cfg.dynamicSmemBytes = TK_SMEM_BYTES;
+    cfg.dynamicSmemBytes = ap->smem_bytes;
     cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;          // all blocks resident at once: the in-kernel barriers need it
+    attr[0].id = cudaLaunchAttributeCooperative;          // all blocks resident at once: they wait on one another
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;

@@ -98,9 +98,13 @@ struct InferenceState {
     /* instrumentation */
     cudaEvent_t *prof_ev;
     int prof_n, prof_cap, prof_on;
-    /* whole-token kernel: step list on the device, barrier words, launch arguments */
-    b200_op *d_ops; unsigned *d_gbar; int n_ops, fused, plan_wide;
-    unsigned long long *d_step_ns;   /* step trace of the whole-token kernel (LLMB200_TRACE=1) */
+    /* whole-token kernel: layer table on the device, flagged hand-over vectors, launch arguments */
+    b200_token_layer *d_tk_layers;
+    b200_flagged *fl_qkv, *fl_part, *fl_attn, *fl_act, *fl_am;
+    size_t off_fl_slots_o, off_fl_slots_dn, off_fl_am, off_counters;
+    b200_token_args tk;              /* planned arguments; with_lm is set per launch */
+    int fused, tk_planned, n_sm;
+    unsigned long long *d_step_ns;   /* stage trace of the whole-token kernel (LLMB200_TRACE=1) */
     int only_kind;           /* >= 0: enqueue_token launches only this kind of kernel (timing loops) */
     int *prof_kind;
 };
@@ -208,8 +212,12 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
     if (alloc_mat(&s->lm, s->wtype, s->V_l, s->D)) goto fail;
     s->weight_bytes += (unsigned long long)s->lm.stride * s->lm.rows;
 
-    /* sequence splits: enough blocks to cover the GPU, at least 64 keys each at full length */
-    s->n_split = 148 / s->Hkv_l;
+    if (cudaDeviceGetAttribute(&s->n_sm, cudaDevAttrMultiProcessorCount, g_rt.device) != cudaSuccess || s->n_sm <= 0) {
+        fprintf(stderr, "[FastGen] cannot read the multiprocessor count\n");
+        goto fail;
+    }
+    /* sequence splits: enough blocks to cover the GPU, at least 32 cache rows each at full length */
+    s->n_split = s->n_sm / s->Hkv_l;
     {   /* the merge folds one batch of splits without predicates: 18, or 9 where a thread owns two outputs */
         const int batch = (s->Hq_l / s->Hkv_l) * s->hd > 512 ? 9 : 18;
         if (s->n_split > batch) s->n_split = batch;
@@ -225,7 +233,7 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
     s->attn_out = dev_zero((size_t)s->Hq_l * s->hd * 4);
     s->act = dev_zero((size_t)s->IS_l * 4);
     s->attn_scratch = dev_zero(b200_attn_scratch_floats(s->Hq_l, s->hd, s->n_split) * 4);
-    s->am_scratch = dev_zero((size_t)2 * 148 * 32 * 4);
+    s->am_scratch = dev_zero((size_t)2 * s->n_sm * 32 * 4);
     s->attn_tickets = (unsigned *)dev_zero((size_t)s->Hkv_l * 4);
     s->mv_ticket = (unsigned *)dev_zero(4);
     int *ctl = (int *)dev_zero((size_t)(8 + max_seq + 2) * 4);
@@ -243,6 +251,11 @@ InferenceState *llmb200_state_begin(const llmb200_config *c)
     s->off_am_val = off;   off += 128;
     s->off_am_idx = off;   off += 128;
     s->off_logits = off;   off += align_up((size_t)s->V * 4, 256);
+    /* flagged vectors of the whole-token kernel: [k][D] per exchange, (value, row) pair per rank */
+    s->off_fl_slots_o = off;  off += align_up((size_t)B200_MAX_PEERS * s->D * 8, 256);
+    s->off_fl_slots_dn = off; off += align_up((size_t)B200_MAX_PEERS * s->D * 8, 256);
+    s->off_fl_am = off;       off += 256;
+    s->off_counters = off;    off += (size_t)72 * B200_CNT_STRIDE * 4;   /* arrival counters, one 128-byte line each */
     s->comm_bytes = off;
     s->comm = (char *)dev_zero(off);
     if (!s->comm) goto fail;
@@ -503,95 +516,98 @@ static int enqueue_token(InferenceState *s, int with_lm, int pdl)
 
 /* ------------------------------------------------------------ whole-token kernel */
 
-/* Builds the step list of one token (the same sequence enqueue_token launches kernel by kernel) and
- * copies it to the device. Returns 0 when the whole-token kernel can run this model, 1 when it cannot
- * (head grouping, row length or attention scratch outside its limits), -1 on a CUDA error. */
+/* Plans the whole-token kernel for this model: geometry of the five matvec stages, the layer table and
+ * the flagged hand-over vectors. Returns 0 when the kernel can run this model, 1 when it cannot (shape
+ * or shared-memory budget outside its limits), -1 on a CUDA error. */
 static int build_plan(InferenceState *s)
 {
-    const int k = s->tp_size, me = s->tp_rank, D = s->D, L = s->L, gemma = s->mt == MODEL_GEMMA3;
-    if (s->Hq_l != 4 * s->Hkv_l) return 1;
-    const int n = 5 * L + 1;
-    b200_op *ops = calloc((size_t)n, sizeof(b200_op));
-    if (!ops) return -1;
-    float *slots_o = (float *)(s->comm + s->off_slots_o), *slots_dn = (float *)(s->comm + s->off_slots_dn);
-    int rc = 0, wide = 0, i = 0;
-#define MV(dst, m) do { (dst)->type = B200_OP_MATVEC; (dst)->d_w = (m)->w; (dst)->row_stride = (m)->stride; (dst)->rows = (m)->rows; (dst)->cols = (m)->cols; } while (0)
-    for (int l = 0; l < L; ++l) {
-        Layer *ly = &s->layers[l];
-        b200_op *o = &ops[i++];                                  /* qkv */
-        MV(o, &ly->qkv);
-        if (l == 0) { o->in_mode = B200_IN_EMBED; o->wait_add = -1; }
-        else {
-            o->in_mode = B200_IN_RESID; o->d_resid_in = s->resid[0]; o->d_slots = slots_dn; o->n_slots = k; o->slot_stride = D;
-            o->d_slot_norm_gamma = gemma ? s->layers[l - 1].g_post_ff : NULL; o->wait_add = l;
-        }
-        if (k > 1) { o->d_wait_flags = flags_of(s, me, 1); o->n_wait = k; }
-        o->d_resid_out = s->resid[1]; o->d_norm_gamma = ly->g_input;
-        o->out_mode = B200_OUT_STORE; o->d_out[0] = s->qkv; o->n_out = 1;
-        o = &ops[i++];                                           /* attention */
-        o->type = B200_OP_ATTN;
-        o->d_qkv = s->qkv; o->d_q_gamma = ly->g_qn; o->d_k_gamma = ly->g_kn; o->d_inv_freq = ly->inv_freq;
-        o->d_k_cache = ly->k_cache; o->d_v_cache = ly->v_cache; o->d_attn_out = s->attn_out;
-        o = &ops[i++];                                           /* o */
-        MV(o, &ly->o);
-        o->in_mode = B200_IN_VEC; o->d_in_vec = s->attn_out; o->out_mode = B200_OUT_STORE; o->n_out = k;
-        for (int p = 0; p < k; ++p) o->d_out[p] = (float *)(s->peer[p] + s->off_slots_o) + (size_t)me * D;
-        if (k > 1) { o->n_signal = k; o->signal_index = me; o->signal_add = l + 1; for (int p = 0; p < k; ++p) o->d_signal_flags[p] = flags_of(s, p, 0); }
-        o = &ops[i++];                                           /* gate/up */
-        MV(o, &ly->gateup);
-        o->in_mode = B200_IN_RESID; o->d_resid_in = s->resid[1]; o->d_resid_out = s->resid[0];
-        o->d_slots = slots_o; o->n_slots = k; o->slot_stride = D;
-        o->d_slot_norm_gamma = gemma ? ly->g_post_attn : NULL; o->d_norm_gamma = gemma ? ly->g_pre_ff : ly->g_post_attn;
-        if (k > 1) { o->d_wait_flags = flags_of(s, me, 0); o->n_wait = k; o->wait_add = l + 1; }
-        o->out_mode = B200_OUT_GLU; o->act = gemma ? 1 : 0; o->d_out[0] = s->act; o->n_out = 1;
-        o = &ops[i++];                                           /* down */
-        MV(o, &ly->down);
-        o->in_mode = B200_IN_VEC; o->d_in_vec = s->act; o->out_mode = B200_OUT_STORE; o->n_out = k;
-        for (int p = 0; p < k; ++p) o->d_out[p] = (float *)(s->peer[p] + s->off_slots_dn) + (size_t)me * D;
-        if (k > 1) { o->n_signal = k; o->signal_index = me; o->signal_add = l + 1; for (int p = 0; p < k; ++p) o->d_signal_flags[p] = flags_of(s, p, 1); }
+    if (s->tk_planned) return 0;
+    const int k = s->tp_size, me = s->tp_rank, D = s->D, L = s->L;
+    b200_token_args *a = &s->tk;
+    memset(a, 0, sizeof(*a));
+    a->n_layers = L; a->wtype = s->wtype; a->gemma = s->mt == MODEL_GEMMA3;
+    const Layer *l0 = &s->layers[0];
+    const PackedMat *m[B200_ST_KINDS] = {&l0->qkv, &l0->o, &l0->gateup, &l0->down, &s->lm};
+    for (int i = 0; i < B200_ST_KINDS; ++i) {
+        a->g[i].rows = m[i]->rows; a->g[i].cols = m[i]->cols; a->g[i].row_stride = m[i]->stride;
+        a->g[i].glu = i == B200_ST_GATEUP;
     }
-    b200_op *o = &ops[i++];                                      /* final norm + LM head */
-    MV(o, &s->lm);
-    o->in_mode = B200_IN_RESID; o->d_resid_in = s->resid[0]; o->d_slots = slots_dn; o->n_slots = k; o->slot_stride = D;
-    o->d_slot_norm_gamma = gemma ? s->layers[L - 1].g_post_ff : NULL; o->d_norm_gamma = s->g_final;
-    if (k > 1) { o->d_wait_flags = flags_of(s, me, 1); o->n_wait = k; o->wait_add = L; }
-    o->out_mode = B200_OUT_STORE; o->n_out = k; o->out_offset = (long long)me * s->V_l; o->argmax = 1;
-    for (int p = 0; p < k; ++p) o->d_out[p] = (float *)(s->peer[p] + s->off_logits);
-#undef MV
-    for (int j = 0; j < n && rc == 0; ++j)
-        if (ops[j].type == B200_OP_MATVEC) { rc = b200_op_plan_matvec(&ops[j], s->wtype); if (ops[j].spt == 2) wide = 1; }
-    if (rc != 0) { free(ops); return 1; }
-    if (!s->d_ops) CU_TRY(cudaMalloc((void **)&s->d_ops, (size_t)n * sizeof(b200_op)), { free(ops); return -1; });
-    if (!s->d_gbar) { s->d_gbar = (unsigned *)dev_zero(8); if (!s->d_gbar) { free(ops); return -1; } }
-    CU_TRY(cudaMemcpy(s->d_ops, ops, (size_t)n * sizeof(b200_op), cudaMemcpyHostToDevice), { free(ops); return -1; });
-    free(ops);
-    s->n_ops = n; s->plan_wide = wide;
-    if (getenv("LLMB200_TRACE") && !s->d_step_ns) s->d_step_ns = (unsigned long long *)dev_zero((size_t)4 * n * 8);
+    a->w_lm = s->lm.w; a->g_final = s->g_final;
+    a->d_emb = s->emb; a->emb_rows = s->V; a->emb_scale = s->emb_scale;
+    a->eps = 1e-6f;                               /* hard-wired in the reference: src/nn/fast_inference.c:383 */
+    a->d_model = D; a->n_q = s->Hq_l; a->n_kv = s->Hkv_l; a->hd = s->hd; a->max_seq = s->max_seq;
+    a->n_split = 0;
+    {   /* few enough splits that a merging block reads little: 18 at head_dim <= 128, 9 above */
+        int cap = s->hd > 128 ? 9 : 18;
+        const char *sp = getenv("LLMB200_ATT_SPLITS");
+        if (sp && atoi(sp) > 0 && atoi(sp) <= 32) cap = atoi(sp);
+        a->n_split = s->n_sm / s->Hkv_l < cap ? s->n_sm / s->Hkv_l : cap;
+    }
+    a->n_ranks = k; a->rank = me;
+    {
+        const char *la = getenv("LLMB200_L2_AHEAD_KB");         /* experiments: 0 = no L2 prefetch */
+        if (la) a->l2_ahead_bytes = atoi(la) > 0 ? atoi(la) * 1024 : -1;
+    }
+    int rc = b200_token_plan(a, s->n_sm);
+    if (rc != 0) return 1;
+
+    b200_token_layer *tl = calloc((size_t)L, sizeof(*tl));
+    if (!tl) return -1;
+    for (int l = 0; l < L; ++l) {
+        const Layer *ly = &s->layers[l];
+        tl[l].w_qkv = ly->qkv.w; tl[l].w_o = ly->o.w; tl[l].w_gateup = ly->gateup.w; tl[l].w_down = ly->down.w;
+        tl[l].g_input = ly->g_input; tl[l].g_post_attn = ly->g_post_attn; tl[l].g_pre_ff = ly->g_pre_ff;
+        tl[l].g_post_ff = ly->g_post_ff; tl[l].g_qn = ly->g_qn; tl[l].g_kn = ly->g_kn; tl[l].inv_freq = ly->inv_freq;
+        tl[l].k_cache = ly->k_cache; tl[l].v_cache = ly->v_cache;
+    }
+    if (!s->d_tk_layers) CU_TRY(cudaMalloc((void **)&s->d_tk_layers, (size_t)L * sizeof(*tl)), { free(tl); return -1; });
+    CU_TRY(cudaMemcpy(s->d_tk_layers, tl, (size_t)L * sizeof(*tl), cudaMemcpyHostToDevice), { free(tl); return -1; });
+    free(tl);
+    const int qkv_rows = (s->Hq_l + 2 * s->Hkv_l) * s->hd;
+    if (!s->fl_qkv) s->fl_qkv = (b200_flagged *)dev_zero((size_t)qkv_rows * 8);
+    if (!s->fl_part) s->fl_part = (b200_flagged *)dev_zero((size_t)s->Hq_l * a->n_split * (s->hd + 2) * 8);
+    if (!s->fl_attn) s->fl_attn = (b200_flagged *)dev_zero((size_t)s->Hq_l * s->hd * 8);
+    if (!s->fl_act) s->fl_act = (b200_flagged *)dev_zero((size_t)s->IS_l * 8);
+    if (!s->fl_am) s->fl_am = (b200_flagged *)dev_zero((size_t)2 * s->n_sm * 8);
+    if (!s->fl_qkv || !s->fl_part || !s->fl_attn || !s->fl_act || !s->fl_am) return -1;
+    if (getenv("LLMB200_TRACE") && !s->d_step_ns)
+        s->d_step_ns = (unsigned long long *)dev_zero((size_t)s->n_sm * (6 * L + 1) * 16 * 8);
+    CU_TRY(cudaStreamSynchronize(g_rt.stream), return -1);
+
+    a->d_layers = s->d_tk_layers;
+    a->d_pos = s->d_pos; a->d_tokens = s->d_tokens; a->d_prompt_len = s->d_prompt_len; a->d_epoch = s->d_epoch; a->d_err = s->d_err;
+    a->d_qkv = s->fl_qkv; a->d_attn_part = s->fl_part; a->d_attn_out = s->fl_attn; a->d_act = s->fl_act; a->d_am = s->fl_am;
+    a->d_logits = (float *)(s->comm + s->off_logits); a->logits_offset = (long long)me * s->V_l;
+    a->d_trace = s->d_step_ns;
+    {
+        const char *sl = getenv("LLMB200_SPIN_LIMIT");
+        a->spin_limit = sl && atoi(sl) > 0 ? atoi(sl) : 0;
+    }
+    s->tk_planned = 1;
     return 0;
+}
+
+/* Pointers into the peers' exchange regions: valid only once the peers are connected. */
+static void bind_peers(InferenceState *s)
+{
+    const int k = s->tp_size, me = s->tp_rank, D = s->D;
+    b200_token_args *a = &s->tk;
+    a->d_slots_o = (const b200_flagged *)(s->comm + s->off_fl_slots_o);
+    a->d_slots_dn = (const b200_flagged *)(s->comm + s->off_fl_slots_dn);
+    a->d_am_rank = (const b200_flagged *)(s->comm + s->off_fl_am);
+    a->d_counters = (unsigned *)(s->comm + s->off_counters);
+    for (int p = 0; p < k; ++p) {
+        a->d_peer_slots_o[p] = (b200_flagged *)(s->peer[p] + s->off_fl_slots_o) + (size_t)me * D;
+        a->d_peer_slots_dn[p] = (b200_flagged *)(s->peer[p] + s->off_fl_slots_dn) + (size_t)me * D;
+        a->d_peer_am[p] = (b200_flagged *)(s->peer[p] + s->off_fl_am) + 2 * me;
+        a->d_peer_counters[p] = (unsigned *)(s->peer[p] + s->off_counters);
+    }
 }
 
 static int enqueue_token_fused(InferenceState *s, int with_lm)
 {
-    const int k = s->tp_size, me = s->tp_rank;
-    b200_token_args a;
-    memset(&a, 0, sizeof(a));
-    a.d_ops = s->d_ops; a.n_ops = with_lm ? s->n_ops : s->n_ops - 1; a.wtype = s->wtype; a.wide = s->plan_wide;
-    a.d_emb = s->emb; a.emb_rows = s->V; a.emb_scale = s->emb_scale; a.eps = 1e-6f;
-    a.n_q = s->Hq_l; a.n_kv = s->Hkv_l; a.hd = s->hd; a.max_seq = s->max_seq; a.n_split = s->n_split;
-    a.d_pos = s->d_pos; a.d_tokens = s->d_tokens; a.d_prompt_len = s->d_prompt_len; a.d_epoch = s->d_epoch;
-    a.epoch_mul = s->L + 1; a.d_err = s->d_err;
-    a.d_attn_scratch = s->attn_scratch; a.d_attn_tickets = s->attn_tickets; a.d_argmax_scratch = s->am_scratch;
-    a.d_grid_barrier = s->d_gbar;
-    a.d_step_ns = s->d_step_ns;
-    a.pick_token = with_lm; a.n_ranks = k; a.rank = me; a.argmax_add = s->L;
-    for (int p = 0; p < k; ++p) {
-        a.d_argmax_val[p] = (float *)(s->peer[p] + s->off_am_val) + me;
-        a.d_argmax_idx[p] = (int *)(s->peer[p] + s->off_am_idx) + me;
-        a.d_argmax_signal_flags[p] = flags_of(s, p, 2);
-    }
-    a.d_rank_vals = (const float *)(s->comm + s->off_am_val);
-    a.d_rank_idx = (const int *)(s->comm + s->off_am_idx);
-    a.d_argmax_wait_flags = flags_of(s, me, 2);
+    b200_token_args a = s->tk;
+    a.with_lm = with_lm;
     K_TRY(b200_decode_token(&a, g_rt.stream), return -1);
     return 0;
 }
@@ -622,18 +638,19 @@ static int ensure_graphs(InferenceState *s)
     if (!s->finished) { fprintf(stderr, "[FastGen] state is not fully loaded\n"); return -1; }
     if (!s->connected) { fprintf(stderr, "[FastGen] tensor-parallel peers are not connected (llmb200_state_connect)\n"); return -1; }
     free_graphs(s);
-    /* LLMB200_TOKEN_KERNEL=1 selects the whole-token persistent kernel (one launch per token, device-wide
-     * barriers between steps). It is measured slower than the kernel-per-step graph at present -- its steps
-     * pay a device-wide barrier plus an input broadcast each -- so the graph of per-step kernels is the default. */
+    /* The whole-token persistent kernel (one launch per token) is the default; LLMB200_TOKEN_KERNEL=0
+     * selects one kernel per stage, which is also what runs when the model is outside the persistent
+     * kernel's limits or a LoRA adapter is attached (it has no LoRA side path). */
     s->fused = 0;
     const char *tk = getenv("LLMB200_TOKEN_KERNEL");
-    if (tk && tk[0] == '1' && !s->lora) {          /* the whole-token kernel has no LoRA side path */
+    if (!(tk && tk[0] == '0') && !s->lora) {
         int pr = build_plan(s);
         if (pr < 0) return -1;
         if (pr == 0) {
+            bind_peers(s);
             s->fused = 1;
             if (capture(s, 1, 0, &s->g_full) == 0 && capture(s, 0, 0, &s->g_nolm) == 0) return 0;
-            fprintf(stderr, "[FastGen] whole-token kernel could not be captured; using one kernel per step\n");
+            fprintf(stderr, "[FastGen] whole-token kernel could not be captured; using one kernel per stage\n");
             free_graphs(s);
             s->fused = 0;
         }
@@ -807,7 +824,8 @@ void inference_state_free(InferenceState *s)
     }
     cudaFree(s->lm.w); cudaFree(s->g_final); cudaFree(s->emb);
     cudaFree(s->resid[0]); cudaFree(s->resid[1]); cudaFree(s->qkv); cudaFree(s->attn_out); cudaFree(s->act);
-    cudaFree(s->d_ops); cudaFree(s->d_gbar);
+    cudaFree(s->d_tk_layers); cudaFree(s->fl_qkv); cudaFree(s->fl_part); cudaFree(s->fl_attn); cudaFree(s->fl_act);
+    cudaFree(s->fl_am); cudaFree(s->d_step_ns);
     cudaFree(s->xnorm);
     free(s->lora);
     cudaFree(s->attn_scratch); cudaFree(s->am_scratch); cudaFree(s->attn_tickets); cudaFree(s->mv_ticket);
@@ -838,15 +856,16 @@ int llmb200_state_graph_kernels(InferenceState *s, int with_lm_head)
     if (!s || ensure_graphs(s) != 0) return -1;
     return with_lm_head ? s->kernels_full : s->kernels_nolm;
 }
-/* Step trace of the last whole-token launch (needs LLMB200_TRACE=1 at create time): 2*n words of the
- * nanosecond timer, start and end of each step on block 0. Returns the number of steps copied. */
-int llmb200_state_step_trace(InferenceState *s, unsigned long long *out, int cap_steps)
+/* Stage trace of the last whole-token launch (needs LLMB200_TRACE=1 at create time), [block][stage][8]
+ * words of the nanosecond timer (b200_token_args.d_trace). Returns the number of blocks. */
+int llmb200_state_step_trace(InferenceState *s, unsigned long long *out, size_t cap_words)
 {
     if (!s || !s->d_step_ns || !out) return 0;
-    int n = s->n_ops < cap_steps ? s->n_ops : cap_steps;
+    size_t n = (size_t)s->n_sm * (6 * s->L + 1) * 16;
+    if (n > cap_words) n = cap_words;
     if (cudaStreamSynchronize(g_rt.stream) != cudaSuccess) return 0;
-    if (cudaMemcpy(out, s->d_step_ns, (size_t)4 * n * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
-    return n;
+    if (cudaMemcpy(out, s->d_step_ns, n * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    return s->n_sm;
 }
 unsigned long long llmb200_state_weight_bytes(InferenceState *s) { return s ? s->weight_bytes : 0; }
 double llmb200_last_decode_ms(InferenceState *s, int *n) { if (n) *n = s->last_n_decoded; return s->last_decode_ms; }
@@ -892,8 +911,16 @@ const float *inference_forward_token(InferenceState *s, int token)
     /* prompt_len beyond pos+1 keeps the graph from overwriting caller-supplied ids */
     if (set_control(s, s->cur_len, s->max_seq + 2, &t, s->cur_len, 1) != 0) return NULL;
     CU_TRY(cudaGraphLaunch(s->g_full, g_rt.stream), return NULL);
-    CU_TRY(cudaMemcpyAsync(s->h_logits, s->comm + s->off_logits, (size_t)s->V * 4, cudaMemcpyDeviceToHost, g_rt.stream),
-           return NULL);
+    if (s->fused && s->tp_size > 1) {
+        /* the whole-token kernel leaves every rank's logits shard on that rank: fetch each from its owner
+         * (the pick exchange at the end of the kernel has ordered the peers' stores before this point) */
+        for (int p = 0; p < s->tp_size; ++p)
+            CU_TRY(cudaMemcpyAsync(s->h_logits + (size_t)p * s->V_l, s->peer[p] + s->off_logits + (size_t)p * s->V_l * 4,
+                                   (size_t)s->V_l * 4, cudaMemcpyDeviceToHost, g_rt.stream), return NULL);
+    } else {
+        CU_TRY(cudaMemcpyAsync(s->h_logits, s->comm + s->off_logits, (size_t)s->V * 4, cudaMemcpyDeviceToHost, g_rt.stream),
+               return NULL);
+    }
     CU_TRY(cudaStreamSynchronize(g_rt.stream), return NULL);
     s->cur_len++;
     return s->h_logits;
