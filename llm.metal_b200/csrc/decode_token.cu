@@ -53,6 +53,7 @@ constexpr int TK_SPIN_DEFAULT = 1 << 20;
 constexpr int TK_TRACE_WORDS = 16;
 
 
+
 // ---------------------------------------------------------------------------
 // Row partition, shared by the producer, the consumers and the host-side replay.
 // A stage's rows (in units of `ralign` rows: 2 for gate/up pairs) go to the blocks in contiguous,
@@ -167,10 +168,14 @@ __device__ __forceinline__ bool mbar_wait_abort(uint64_t *b, unsigned parity, vo
     return false;
 }
 
+// Flag-carrying words, arrival counters: relaxed accesses at device scope, or at system scope (MULTI)
+// when other GPUs write into this one's vectors and counters.
+template <bool MULTI>
 __device__ __forceinline__ void fl_store(b200_flagged *p, float v, unsigned flag)
 {
     const unsigned long long w = ((unsigned long long)flag << 32) | (unsigned long long)__float_as_uint(v);
-    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+    if (MULTI) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+    else asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 
 // Arrival counters: a producer adds the number of words it has stored, one thread of a reading block
@@ -178,16 +183,20 @@ __device__ __forceinline__ void fl_store(b200_flagged *p, float v, unsigned flag
 // polling L2 while nothing is there yet -- validity is proved by the flags of the words themselves, so
 // no fence orders the stores before the count and a wait that runs out simply falls through to the
 // flagged polls (whose limit raises the error).
+template <bool MULTI>
 __device__ __forceinline__ void cnt_add(unsigned *cnt, unsigned n)
 {
-    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(n) : "memory");
+    if (MULTI) asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(n) : "memory");
+    else asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(cnt), "r"(n) : "memory");
 }
+template <bool MULTI>
 __device__ __forceinline__ void cnt_wait(const unsigned *cnt, unsigned target, volatile int *flags, int spin)
 {
 #pragma unroll 1
     for (int it = 0; it < spin; ++it) {
         unsigned v;
-        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        if (MULTI) asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        else asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
         if ((int)(v - target) >= 0) return;
         if ((it & 31) == 31 && flags[0]) return;
         __nanosleep(20);
@@ -198,7 +207,7 @@ __device__ __forceinline__ void cnt_wait(const unsigned *cnt, unsigned target, v
 // (the others read as zero). All loads of a round are issued before the first flag is looked at, so a
 // ready vector costs one round trip to L2 however many words a thread needs; a round with a stale
 // flag is repeated as a whole. On a timeout the abort flag goes up and the values read as zero.
-template <int N, int STEP>
+template <int N, int STEP, bool MULTI>
 __device__ __forceinline__ void fl_poll(const b200_flagged *base, int count, unsigned flag, float (&a)[N], float (&b)[N],
                                         volatile int *flags, int *d_err, int spin)
 {
@@ -208,8 +217,10 @@ __device__ __forceinline__ void fl_poll(const b200_flagged *base, int count, uns
 #pragma unroll
         for (int k = 0; k < N; ++k) {
             v0[k] = 0ull; v1[k] = 0ull;
-            if (k < count)
-                asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(base + (size_t)k * STEP) : "memory");
+            if (k < count) {
+                if (MULTI) asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(base + (size_t)k * STEP) : "memory");
+                else asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(base + (size_t)k * STEP) : "memory");
+            }
         }
         bool ok = true;
 #pragma unroll
@@ -272,6 +283,7 @@ __device__ __forceinline__ float row_sum(const float *pr, int nwg)
 //   residual <- embedding row (first stage of a token) | residual + sum over ranks of the slots
 // (the sum is RMS-normalised first where the architecture has post norms), and the RMS statistics of
 // the new residual. Leaves the stage's norm weights in scratch[D .. 2D). Returns 1/sqrt(mean(r^2)+eps).
+template <bool MULTI>
 __device__ __forceinline__ float stage_residual(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long *trace)
 {
     const Smem sm = smem_of(p);
@@ -324,7 +336,7 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
 #pragma unroll
             for (int u = 0; u < NB; ++u) gq[u] = u < cnt0 ? *reinterpret_cast<const float2 *>(norm_gamma + tid * 2 + u * TK_NC * 2) : make_float2(0, 0);
         }
-        if (tid == 0) { cnt_wait(in_cnt, target, sm.flags, spin); if (trace) trace[8] = global_ns(); }
+        if (tid == 0) { cnt_wait<MULTI>(in_cnt, target, sm.flags, spin); if (trace) trace[8] = global_ns(); }
         named_barrier(1, TK_NC);
         if (trace && tid == 0) trace[9] = global_ns();
 #pragma unroll 1
@@ -340,7 +352,7 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
 #pragma unroll 1
             for (int k = 0; k < p.n_ranks; ++k) {
                 float a[NB], b[NB];
-                fl_poll<NB, TK_NC * 2>(slots + (size_t)k * D + i0, cnt, slots_flag, a, b, sm.flags, p.d_err, spin);
+                fl_poll<NB, TK_NC * 2, MULTI>(slots + (size_t)k * D + i0, cnt, slots_flag, a, b, sm.flags, p.d_err, spin);
 #pragma unroll
                 for (int u = 0; u < NB; ++u) { s0[u] += a[u]; s1[u] += b[u]; }
             }
@@ -380,6 +392,7 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
 
 // Input vector of the o and down stages: the flagged vector, fetched once per block with coalesced
 // loads into scratch[0 .. cols).
+template <bool MULTI>
 __device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long *trace)
 {
     const Smem sm = smem_of(p);
@@ -389,14 +402,14 @@ __device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind,
     const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
     const b200_flagged *in_vec = kind == B200_ST_O ? p.d_attn_out : p.d_act;
     const unsigned *in_cnt = p.d_counters + (kind == B200_ST_O ? B200_CNT_ATTN : B200_CNT_ACT) * B200_CNT_STRIDE;
-    if (tid == 0) { cnt_wait(in_cnt, cnt_mul * (unsigned)cols, sm.flags, spin); if (trace) trace[8] = global_ns(); }
+    if (tid == 0) { cnt_wait<false>(in_cnt, cnt_mul * (unsigned)cols, sm.flags, spin); if (trace) trace[8] = global_ns(); }
     named_barrier(1, TK_NC);
     if (trace && tid == 0) trace[9] = global_ns();
     constexpr int NB = 4;
 #pragma unroll 1
     for (int i0 = tid * 2; i0 < cols; i0 += TK_NC * 2 * NB) {
         float a[NB], b[NB];
-        fl_poll<NB, TK_NC * 2>(in_vec + i0, (cols - i0 + TK_NC * 2 - 1) / (TK_NC * 2), flag, a, b, sm.flags, p.d_err, spin);
+        fl_poll<NB, TK_NC * 2, false>(in_vec + i0, (cols - i0 + TK_NC * 2 - 1) / (TK_NC * 2), flag, a, b, sm.flags, p.d_err, spin);
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
             const int i = i0 + u * TK_NC * 2;
@@ -413,20 +426,21 @@ __device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind,
 // partials are collected in registers (8 / RG chunks) and then folded across the warp's lanes by one
 // transposing shuffle reduction; the warp partial of each row goes to part[]. `state` is the running
 // chunk number; returned advanced.
-template <int WT, int SPT, int RG, bool TRACE>
+template <int WT, int SPT, int RG, int NACC, bool TRACE>
 __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kind, float inv, int w0, int w1, unsigned state, unsigned win,
                                             unsigned long long *trace)
 {
     constexpr int E = (WT == B200_WT_Q8) ? 16 : 8;
-    constexpr int NACC = 8 / RG;                     // chunks per reduction
     const b200_stage_geom &G = p.g[kind];
     const Smem sm = smem_of(p);
     const int spin = spin_of(p);
+    if (TRACE && trace && threadIdx.x == 0) trace[13] = global_ns();
     const int tid = threadIdx.x, T = G.T, NG = G.NG, RB = G.rb;
     const int g = tid / T, t = tid - g * T, lane = tid & 31, wg = t >> 5, nwgp = (T >> 5) | 1;
     const bool active = g < NG;
 
     // ---------------- this thread's slices of the input vector -> registers ----------------
+    if (TRACE && trace && tid == 0) trace[14] = (unsigned long long)g + global_ns();
     float x[SPT][E];
     uint32_t qoff[SPT], soff[SPT];
     {
@@ -461,17 +475,20 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
     const uint32_t ring_s = smem_u32(sm.ring), stride = (uint32_t)G.row_stride;
     const uint32_t grow = (uint32_t)(g * RG) * stride;           // this group's first row inside a chunk
     float *part = sm.part + (win & 1u) * TK_PART;
-    const int nrows = w1 - w0, nchunks = (nrows + RB - 1) / RB;
+    const int nrows = w1 - w0;
     unsigned seq = state;
     bool first = true;
+    // NV = RG * NACC row partials (NACC chunks) are folded across the lanes per pass: measured on Qwen3-4B,
+    // eight per pass (fewer shuffles per weight) beat one chunk per pass (smaller loop body) by 3 %.
+    constexpr int NV = RG * NACC;
 #pragma unroll 1
-    for (int cbase = 0; cbase < nchunks; cbase += NACC) {
-        float v[8];
+    for (int r0 = 0; r0 < nrows; r0 += RB * NACC) {
+        float v[NV];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+        for (int i = 0; i < NV; ++i) v[i] = 0.0f;
 #pragma unroll
         for (int u = 0; u < NACC; ++u) {
-            if (cbase + u < nchunks) {
+            if (r0 + u * RB < nrows) {
                 const unsigned slot = seq % TK_SLOTS, par = (seq / TK_SLOTS) & 1u;
                 ++seq;
                 if (!mbar_wait_abort(&sm.full[slot], par, sm.flags, spin) && !sm.flags[0]) raise(sm.flags, p.d_err, 3);
@@ -506,11 +523,11 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
             }
         }
         if (active) {
-            // lane i < 8 ends up with the warp's total of partial i: chunk cbase + i / RG, row g*RG + i % RG of it
-            const float tot = reduce_rows<8>(v, lane);
-            const int c = cbase + lane / RG, rin = g * RG + lane % RG;
-            const int lrow = c * RB + rin;
-            if (lane < 8 && c < nchunks && rin < RB && lrow < nrows) part[lrow * nwgp + wg] = tot;
+            // lane i < NV ends up with the warp's total of partial i: chunk i / RG of this pass, row g*RG + i % RG of it
+            const float tot = reduce_rows<NV>(v, lane);
+            const int rin = g * RG + lane % RG;
+            const int lrow = r0 + (lane / RG) * RB + rin;
+            if (lane < NV && lrow < nrows && rin < RB) part[lrow * nwgp + wg] = tot;
         }
     }
     if (TRACE && trace && tid == 0) trace[3] = global_ns();
@@ -519,7 +536,7 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
 
 // Final sums and epilogue of rows [w0, w1): thread i adds the warp partials of row i in warp order.
 // best (value bits | row << 32) carries the LM head's running arg-max of this thread.
-template <bool TRACE>
+template <bool TRACE, bool MULTI>
 __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &p, int kind, int l, unsigned ep, int w0, int w1, unsigned win,
                                                       unsigned long long best, unsigned long long *trace)
 {
@@ -539,11 +556,11 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
         for (int i = tid; i < n / 2; i += TK_NC) {
             const float gte = row_sum(part + (2 * i) * nwgp, nwg), up = row_sum(part + (2 * i + 1) * nwgp, nwg);
             const float a = p.gemma ? act_gelu_tanh(gte) : act_silu(gte);
-            fl_store(p.d_act + (w0 >> 1) + i, a * up, flag);
+            fl_store<false>(p.d_act + (w0 >> 1) + i, a * up, flag);
             ++stored;
         }
         stored = (unsigned)__reduce_add_sync(0xffffffffu, stored);
-        if (lane == 0 && stored) cnt_add(cn + B200_CNT_ACT * B200_CNT_STRIDE, stored);
+        if (lane == 0 && stored) cnt_add<false>(cn + B200_CNT_ACT * B200_CNT_STRIDE, stored);
         return best;
     }
     float best_v = __uint_as_float((unsigned)best);
@@ -552,14 +569,14 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
     for (int i = tid; i < n; i += TK_NC) {
         const float y = row_sum(part + i * nwgp, nwg);
         const int row = w0 + i;
-        if (kind == B200_ST_QKV) fl_store(p.d_qkv + row, y, flag);
+        if (kind == B200_ST_QKV) fl_store<false>(p.d_qkv + row, y, flag);
         else if (kind == B200_ST_LM) {
             p.d_logits[p.logits_offset + row] = y;
             if (better(y, row, best_v, best_i)) { best_v = y; best_i = row; }
         } else {
             // partial sums into slot `rank` of every rank
 #pragma unroll 1
-            for (int q = 0; q < p.n_ranks; ++q) fl_store((kind == B200_ST_O ? p.d_peer_slots_o[q] : p.d_peer_slots_dn[q]) + row, y, flag);
+            for (int q = 0; q < p.n_ranks; ++q) fl_store<MULTI>((kind == B200_ST_O ? p.d_peer_slots_o[q] : p.d_peer_slots_dn[q]) + row, y, flag);
         }
         ++stored;
     }
@@ -567,11 +584,11 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
         // one add per warp and receiver: the words this warp has stored
         stored = (unsigned)__reduce_add_sync(0xffffffffu, stored);
         if (lane == 0 && stored) {
-            if (kind == B200_ST_QKV) cnt_add(cn + B200_CNT_QKV * B200_CNT_STRIDE, stored);
+            if (kind == B200_ST_QKV) cnt_add<false>(cn + B200_CNT_QKV * B200_CNT_STRIDE, stored);
             else {
 #pragma unroll 1
                 for (int q = 0; q < p.n_ranks; ++q)
-                    cnt_add(p.d_peer_counters[q] + (kind == B200_ST_O ? B200_CNT_SLOTS_O : B200_CNT_SLOTS_DN) * B200_CNT_STRIDE, stored);
+                    cnt_add<MULTI>(p.d_peer_counters[q] + (kind == B200_ST_O ? B200_CNT_SLOTS_O : B200_CNT_SLOTS_DN) * B200_CNT_STRIDE, stored);
             }
         }
     }
@@ -579,7 +596,7 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
 }
 
 // One matvec stage. `state`: running chunk number (low word) and window number (high word).
-template <int WT, bool TRACE>
+template <int WT, bool TRACE, bool MULTI>
 __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long state,
                                                       unsigned long long *trace)
 {
@@ -587,8 +604,9 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
     const int tid = threadIdx.x;
     if (TRACE && trace && tid == 0) trace[0] = global_ns();
     float inv = 0.0f;
-    if (kind == B200_ST_O || kind == B200_ST_DOWN) stage_vector(p, kind, l, ep, TRACE ? trace : nullptr);
-    else inv = stage_residual(p, kind, l, ep, TRACE ? trace : nullptr);
+    if (kind == B200_ST_O || kind == B200_ST_DOWN) stage_vector<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
+    else inv = stage_residual<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
+    if (TRACE && trace && tid == 0) trace[12] = global_ns();
     if (kind == B200_ST_LM && !p.with_lm) return state;          // only the residual update that ends a prompt position
     unsigned seq = (unsigned)state, win = (unsigned)(state >> 32);
     unsigned long long best = ((unsigned long long)0x7fffffffu << 32) | (unsigned long long)__float_as_uint(-INFINITY);
@@ -597,15 +615,15 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
     for (int w0 = br.r0; w0 < br.r1; w0 += G.pw) {
         const int w1 = w0 + G.pw < br.r1 ? w0 + G.pw : br.r1;
         if (G.spt == 1) {
-            if (G.rg == 2) seq = stage_rows<WT, 1, 2, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
-            else if (G.rg == 4) seq = stage_rows<WT, 1, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
-            else if (G.rg == 8) seq = stage_rows<WT, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
-            else seq = stage_rows<WT, 1, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            if (G.rg == 2) seq = stage_rows<WT, 1, 2, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else if (G.rg == 4) seq = stage_rows<WT, 1, 4, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else if (G.rg == 8) seq = stage_rows<WT, 1, 8, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else seq = stage_rows<WT, 1, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
         } else {
-            if (G.rg == 2) seq = stage_rows<WT, 2, 2, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
-            else seq = stage_rows<WT, 2, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            if (G.rg == 2) seq = stage_rows<WT, 2, 2, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else seq = stage_rows<WT, 2, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
         }
-        best = stage_emit<TRACE>(p, kind, l, ep, w0, w1, win, best, trace);
+        best = stage_emit<TRACE, MULTI>(p, kind, l, ep, w0, w1, win, best, trace);
         ++win;
     }
     if (TRACE && trace && tid == 0) trace[4] = global_ns();
@@ -630,8 +648,8 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
 #pragma unroll 1
             for (int ww = 1; ww < TK_NWARP; ++ww) if (better(am_v[ww], am_i[ww], best_v, best_i)) { best_v = am_v[ww]; best_i = am_i[ww]; }
             if (p.n_ranks > 1) __threadfence_system();   // this block's logits are visible before its pair is
-            fl_store(p.d_am + 2 * blockIdx.x, best_v, flag);
-            fl_store(p.d_am + 2 * blockIdx.x + 1, __int_as_float(best_i), flag);
+            fl_store<false>(p.d_am + 2 * blockIdx.x, best_v, flag);
+            fl_store<false>(p.d_am + 2 * blockIdx.x + 1, __int_as_float(best_i), flag);
         }
     }
     return ((unsigned long long)win << 32) | seq;
@@ -653,7 +671,7 @@ __device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
     }
 }
 
-template <int HD, bool TRACE>
+template <int HD, bool TRACE, bool MULTI>
 __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l, unsigned ep, unsigned long long *trace)
 {
     constexpr int DPT = 8;                           // head-dim values per thread
@@ -704,7 +722,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         if (tid == 0) stage_rows(j0, min(j0 + KCH, j1));
 
         // ---- the new rows of this KV head ----
-        if (tid == 0) cnt_wait(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, spin);
+        if (tid == 0) cnt_wait<false>(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, spin);
         named_barrier(2, ATT_T);
         {
             // q heads of this KV head are contiguous; its k row and v row follow at their own offsets
@@ -715,7 +733,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                               : i < nq + HD ? p.n_q * HD + kvh * HD + (i - nq)
                                             : (p.n_q + p.n_kv) * HD + kvh * HD + (i - nq - HD);
                 float a[1], b[1];
-                fl_poll<1, 2>(p.d_qkv + src, 1, flag, a, b, sm.flags, p.d_err, spin);
+                fl_poll<1, 2, false>(p.d_qkv + src, 1, flag, a, b, sm.flags, p.d_err, spin);
                 *reinterpret_cast<float2 *>(raw + i) = make_float2(a[0], b[0]);
             }
         }
@@ -846,11 +864,11 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                     v = fmaf(src[w * (HD + 2) + d], cf, v);
                 }
             }
-            fl_store(p.d_attn_part + ((size_t)(kvh * G + gg) * p.n_split + split) * (HD + 2) + d, v, flag);
+            fl_store<false>(p.d_attn_part + ((size_t)(kvh * G + gg) * p.n_split + split) * (HD + 2) + d, v, flag);
             ++nst;
         }
         nst = (unsigned)__reduce_add_sync(0xffffffffu, nst);
-        if (lane == 0 && nst) cnt_add(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, nst);
+        if (lane == 0 && nst) cnt_add<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, nst);
         if (TRACE && trace && tid == 0) trace[3] = global_ns();
 
         // ---- this block merges the splits of query heads split, split + n_split, ... of its KV head ----
@@ -859,7 +877,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             const int head = kvh * G + gm;
             const b200_flagged *rec = p.d_attn_part + (size_t)head * p.n_split * (HD + 2);
             if (tid == 0)
-                cnt_wait(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, cnt_mul * (unsigned)(p.n_split * G * (HD + 2)), sm.flags, spin);
+                cnt_wait<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, cnt_mul * (unsigned)(p.n_split * G * (HD + 2)), sm.flags, spin);
             named_barrier(2, ATT_T);                 // also: the staging area is free (keys done, previous head merged)
             {
                 constexpr int NB = 4;
@@ -867,7 +885,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
 #pragma unroll 1
                 for (int i0 = tid * 2; i0 < tot; i0 += ATT_T * 2 * NB) {
                     float a[NB], b[NB];
-                    fl_poll<NB, ATT_T * 2>(rec + i0, (tot - i0 + ATT_T * 2 - 1) / (ATT_T * 2), flag, a, b, sm.flags, p.d_err, spin);
+                    fl_poll<NB, ATT_T * 2, false>(rec + i0, (tot - i0 + ATT_T * 2 - 1) / (ATT_T * 2), flag, a, b, sm.flags, p.d_err, spin);
 #pragma unroll
                     for (int u = 0; u < NB; ++u) {
                         const int i = i0 + u * ATT_T * 2;
@@ -891,11 +909,11 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                     Lsum = fmaf(ls, wgt, Lsum);
                     O = fmaf(stg[s * (HD + 2) + d], wgt, O);
                 }
-                fl_store(p.d_attn_out + (size_t)head * HD + d, O / Lsum, flag);
+                fl_store<false>(p.d_attn_out + (size_t)head * HD + d, O / Lsum, flag);
                 ++nout;
             }
             nout = (unsigned)__reduce_add_sync(0xffffffffu, nout);
-            if (lane == 0 && nout) cnt_add(p.d_counters + B200_CNT_ATTN * B200_CNT_STRIDE, nout);
+            if (lane == 0 && nout) cnt_add<false>(p.d_counters + B200_CNT_ATTN * B200_CNT_STRIDE, nout);
         }
     }
     // the o stage reuses the scratch area: nobody goes on before the attention threads are done with it
@@ -956,7 +974,7 @@ __device__ __noinline__ unsigned produce_stage(const b200_token_args &p, int kin
     return sm.flags[0] ? (seq | 0x80000000u) : seq;
 }
 
-template <int WT, bool TRACE>
+template <int WT, bool TRACE, bool MULTI>
 __global__ void __launch_bounds__(TK_THREADS, 1)
 decode_token_kernel(const __grid_constant__ b200_token_args p)
 {
@@ -1032,12 +1050,12 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
             if (l == L && k > 0) break;
             unsigned long long *t = tr ? tr + (size_t)(6 * l + k) * TK_TRACE_WORDS : nullptr;
             if (k == 1) {
-                if (p.hd == 128) attention_stage<128, TRACE>(p, l, ep, t);
-                else if (p.hd == 64) attention_stage<64, TRACE>(p, l, ep, t);
-                else attention_stage<256, TRACE>(p, l, ep, t);
+                if (p.hd == 128) attention_stage<128, TRACE, MULTI>(p, l, ep, t);
+                else if (p.hd == 64) attention_stage<64, TRACE, MULTI>(p, l, ep, t);
+                else attention_stage<256, TRACE, MULTI>(p, l, ep, t);
             } else {
                 const int kind = l == L ? B200_ST_LM : k == 0 ? B200_ST_QKV : k - 1;     // 2, 3, 4 -> o, gate/up, down
-                state = run_matvec<WT, TRACE>(p, kind, l, ep, state, t);
+                state = run_matvec<WT, TRACE, MULTI>(p, kind, l, ep, state, t);
             }
         }
     }
@@ -1052,7 +1070,7 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
             for (int b0 = lane; b0 < (int)gridDim.x; b0 += 32 * 4) {
                 float v[4], fi[4];
                 const int cnt = ((int)gridDim.x - b0 + 31) / 32;
-                fl_poll<4, 64>(p.d_am + 2 * b0, cnt, flag_lm, v, fi, sm.flags, p.d_err, spin);
+                fl_poll<4, 64, false>(p.d_am + 2 * b0, cnt, flag_lm, v, fi, sm.flags, p.d_err, spin);
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
                     if (u < cnt && better(v[u], __float_as_int(fi[u]), bv, bi)) { bv = v[u]; bi = __float_as_int(fi[u]); }
@@ -1069,11 +1087,11 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
                 // (value, row) to every rank, then the best of all ranks, lowest row on ties
                 __threadfence_system();
                 if (lane < p.n_ranks) {
-                    fl_store(p.d_peer_am[lane], bv, flag_lm);
-                    fl_store(p.d_peer_am[lane] + 1, __int_as_float(bi), flag_lm);
+                    fl_store<true>(p.d_peer_am[lane], bv, flag_lm);
+                    fl_store<true>(p.d_peer_am[lane] + 1, __int_as_float(bi), flag_lm);
                 }
                 float gv[1], gf[1];
-                fl_poll<1, 2>(p.d_am_rank + 2 * (lane < p.n_ranks ? lane : 0), lane < p.n_ranks ? 1 : 0, flag_lm, gv, gf, sm.flags, p.d_err, spin);
+                fl_poll<1, 2, true>(p.d_am_rank + 2 * (lane < p.n_ranks ? lane : 0), lane < p.n_ranks ? 1 : 0, flag_lm, gv, gf, sm.flags, p.d_err, spin);
                 float xv = lane < p.n_ranks ? gv[0] : -INFINITY;
                 int xi = lane < p.n_ranks ? __float_as_int(gf[0]) : 0x7fffffff;
 #pragma unroll 1
@@ -1186,8 +1204,7 @@ extern "C" int b200_token_plan(b200_token_args *a, int n_blocks)
         if ((k == B200_ST_O || k == B200_ST_DOWN) && !a->g[k].direct_in && a->g[k].cols > need) need = a->g[k].cols;
     }
     scratch = (need + 3) / 4 * 4;
-    if (a->l2_ahead_bytes == 0) a->l2_ahead_bytes = 512 << 10;   // default: up to 512 KB of the next stage per block
-    if (a->l2_ahead_bytes < 0) a->l2_ahead_bytes = 0;
+    if (a->l2_ahead_bytes < 0) a->l2_ahead_bytes = 0;     // default 0: measured slower than leaving the order of HBM requests to the ring
     if (a->g[B200_ST_QKV].cols != a->d_model || a->g[B200_ST_GATEUP].cols != a->d_model || !a->g[B200_ST_GATEUP].glu ||
         a->g[B200_ST_QKV].rows != (a->n_q + 2 * a->n_kv) * a->hd || a->g[B200_ST_O].cols != a->n_q * a->hd ||
         a->g[B200_ST_O].rows != a->d_model || a->g[B200_ST_DOWN].rows != a->d_model ||
@@ -1233,8 +1250,11 @@ extern "C" int b200_decode_token(const b200_token_args *ap, void *stream)
     if (sms <= 0) return B200_E_STATE;
     if (ap->n_blocks > sms) return B200_E_TOOLARGE;    // all blocks must be resident at once
     void (*kern)(const b200_token_args);
-    if (ap->wtype == B200_WT_Q8) kern = ap->d_trace ? decode_token_kernel<B200_WT_Q8, true> : decode_token_kernel<B200_WT_Q8, false>;
-    else kern = ap->d_trace ? decode_token_kernel<B200_WT_F16, true> : decode_token_kernel<B200_WT_F16, false>;
+    const bool multi = ap->n_ranks > 1, trace = ap->d_trace != nullptr;
+#define TK_PICK(WT_) (multi ? (trace ? decode_token_kernel<WT_, true, true> : decode_token_kernel<WT_, false, true>) \
+                            : (trace ? decode_token_kernel<WT_, true, false> : decode_token_kernel<WT_, false, false>))
+    kern = ap->wtype == B200_WT_Q8 ? TK_PICK(B200_WT_Q8) : TK_PICK(B200_WT_F16);
+#undef TK_PICK
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ap->smem_bytes);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};

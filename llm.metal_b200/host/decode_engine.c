@@ -545,8 +545,8 @@ static int build_plan(InferenceState *s)
     }
     a->n_ranks = k; a->rank = me;
     {
-        const char *la = getenv("LLMB200_L2_AHEAD_KB");         /* experiments: 0 = no L2 prefetch */
-        if (la) a->l2_ahead_bytes = atoi(la) > 0 ? atoi(la) * 1024 : -1;
+        const char *la = getenv("LLMB200_L2_AHEAD_KB");         /* experiments: L2 prefetch of the following stage */
+        if (la && atoi(la) > 0) a->l2_ahead_bytes = atoi(la) * 1024;
     }
     int rc = b200_token_plan(a, s->n_sm);
     if (rc != 0) return 1;
