@@ -70,9 +70,9 @@ int qwen3_generate_fast(llmb200_qwen3_model *model, const uint32_t *prompt_token
  * prompt and advance one position per step, sharing one read of the weights.
  * output_tokens is [batch_size][max_gen_len]; returns the number of tokens
  * generated per sequence (0 on failure). Stops when every sequence has
- * produced an EOS id (151645 / 151643) or the cache is full.
- * Replaces qwen3_generate_fast_batch (src/nn/fast_inference.c:895-985;
- * fast_inference.h:66-72), whose extra stop on token id 0 is not copied. */
+ * produced an EOS id (151645, 151643 or 0, the reference's list) or the cache
+ * is full. Replaces qwen3_generate_fast_batch
+ * (src/nn/fast_inference.c:895-985; fast_inference.h:66-72). */
 int qwen3_generate_fast_batch(llmb200_qwen3_model *model, const uint32_t *prompt_tokens, int prompt_len,
                               uint32_t *output_tokens, int max_gen_len, int max_seq_len, int batch_size);
 
@@ -119,6 +119,12 @@ double llmb200_last_decode_ms(InferenceState *state, int *n_decoded);
 double llmb200_last_prefill_ms(InferenceState *state);
 /* Non-zero once a bounded device-side wait ran out or a launch failed. */
 int llmb200_state_error(InferenceState *state);
+/* Fault injection on the host, for tests of the bounded waits: "connects" a tensor-parallel state
+ * (world > 1) to itself instead of to its peers, i.e. to ranks that never arrive. The next token then
+ * waits for partial sums nobody writes; every such wait gives up after its iteration limit
+ * (LLMB200_SPIN_LIMIT at create time), the launch completes, llmb200_state_error turns non-zero and
+ * the state is dead. Nothing on the GPU faults or hangs. */
+int llmb200_state_connect_loopback(InferenceState *state);
 /* Device-resident timing: starting from the current position, replay the
  * per-token graph n_steps times back to back with every input already in
  * device memory, timed by CUDA events on the launching stream. Returns the

@@ -127,6 +127,9 @@ typedef struct b200_matvec_args {
     /* optional: block 0 also stores the assembled (summed, normalised) input vector here, cols floats --
      * what a LoRA side path multiplies by A (src/nn/fast_inference.c:406-421 reads mb_ln_out) */
     float *d_in_copy;
+    /* iterations of the bounded wait on d_wait_flags before the kernel gives up and sets *d_err = 1
+     * (0 = default, about a second) */
+    int spin_limit;
 } b200_matvec_args;
 
 int b200_matvec(const b200_matvec_args *a, void *stream);
@@ -144,7 +147,8 @@ int b200_matvec(const b200_matvec_args *a, void *stream);
  *   out        fp32 [n_q*hd]
  *   scratch    fp32, b200_attn_scratch_floats(n_q, hd, n_split) floats
  *   tickets    n_kv zero-initialised words
- * Keys 0..*pos are attended (no window), scores scaled by 1/sqrt(hd).
+ * Keys 0..*pos are attended (no window), scores scaled by 1/sqrt(hd). A position outside
+ * [0, max_seq) is ignored: nothing is written or read, the output keeps its contents.
  * ---------------------------------------------------------------------- */
 typedef struct b200_attn_args {
     const float *d_qkv; const float *d_q_gamma; const float *d_k_gamma; const float *d_inv_freq;
@@ -170,8 +174,8 @@ int    b200_attn_decode(const b200_attn_args *a, void *stream);
  * device-wide synchronisation a cudaMalloc can cause. a->d_scratch and a->d_tickets are ignored; the
  * partial results go to arrays built into the library (held by every GPU that loads it until the
  * process exits). Limits: n_q * n_split * (hd + 2) <= B200_ATTN_STATIC_SCRATCH_FLOATS and
- * n_kv <= B200_ATTN_STATIC_MAX_KV_HEADS; larger requests are refused with B200_E_TOOLARGE and a
- * message on stderr. Calls no cudaMalloc/cudaFree. The first call on a device looks up the arrays'
+ * n_kv <= B200_ATTN_STATIC_MAX_KV_HEADS, one sequence per call (n_items <= 1: the batched form indexes
+ * scratch and tickets by item); anything larger is refused with B200_E_TOOLARGE and a message on stderr. Calls no cudaMalloc/cudaFree. The first call on a device looks up the arrays'
  * device addresses and should therefore come before any stream capture. All calls share the arrays:
  * two calls whose kernels may overlap on the GPU (different streams) race with each other. */
 #define B200_ATTN_STATIC_SCRATCH_FLOATS (1 << 18)      /* 1 MiB */

@@ -54,7 +54,7 @@ class MatvecArgs(C.Structure):
         ("d_epoch", C.c_void_p), ("epoch_mul", C.c_int), ("epoch_add", C.c_int),
         ("d_err", C.c_void_p),
         ("grid", C.c_int), ("use_pdl", C.c_int),
-        ("d_in_copy", C.c_void_p),
+        ("d_in_copy", C.c_void_p), ("spin_limit", C.c_int),
     ]
 
 
@@ -167,7 +167,7 @@ SYMBOLS_MAIN = {
                             "qwen3_generate_fast", "qwen3_generate_fast_batch", "inference_state_set_lora", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
                             "llmb200_state_begin", "llmb200_state_load_layer", "llmb200_state_finish",
                             "llmb200_state_set_eos", "llmb200_last_decode_ms", "llmb200_last_prefill_ms",
-                            "llmb200_state_error", "llmb200_state_run_device_steps", "llmb200_state_profile_token",
+                            "llmb200_state_error", "llmb200_state_connect_loopback", "llmb200_state_run_device_steps", "llmb200_state_profile_token",
                             "llmb200_state_time_kind", "llmb200_state_step_trace",
                             "llmb200_state_weight_bytes", "llmb200_state_position", "llmb200_state_graph_kernels",
                             "llmb200_state_export_weight", "llmb200_batch_begin", "llmb200_batch_load_layer",
@@ -257,7 +257,7 @@ def lib():
         "llmb200_state_finish": (i, [vp, c_float_p, c_float_p, c_float_p]),
         "llmb200_state_set_eos": (None, [vp, c_int_p, i]),
         "llmb200_last_decode_ms": (C.c_double, [vp, c_int_p]), "llmb200_last_prefill_ms": (C.c_double, [vp]),
-        "llmb200_state_error": (i, [vp]), "llmb200_state_run_device_steps": (C.c_float, [vp, i]),
+        "llmb200_state_error": (i, [vp]), "llmb200_state_connect_loopback": (i, [vp]), "llmb200_state_run_device_steps": (C.c_float, [vp, i]),
         "llmb200_state_profile_token": (i, [vp, c_float_p, c_int_p]),
         "llmb200_state_time_kind": (C.c_float, [vp, i, i, c_int_p]),
         "llmb200_state_step_trace": (i, [vp, C.POINTER(C.c_ulonglong), sz]),

@@ -109,6 +109,9 @@ attn_decode_kernel(const __grid_constant__ b200_attn_args pa, const int chunk_ca
     }
 
     const int pos = *p.d_pos;
+    // A position outside the cache writes and reads nothing: the block leaves (all its threads take the
+    // same branch) and the output keeps its previous contents. The engine checks positions on the host.
+    if (pos < 0 || pos >= p.max_seq) return;
     const int n = pos + 1;
     const int chunk = (n + p.n_split - 1) / p.n_split;
     const int j0 = min(split * chunk, n), j1 = min(j0 + chunk, n);
@@ -479,6 +482,12 @@ extern "C" int b200_attn_decode_static(const b200_attn_args *ap, void *stream)
     if (!ap) return B200_E_BADARG;
     const size_t need = b200_attn_scratch_floats(ap->n_q, ap->hd, ap->n_split);
     if (need == 0 || ap->n_kv <= 0) return B200_E_BADARG;
+    if (ap->n_items > 1) {
+        // the batched form indexes scratch and tickets by item: the built-in arrays hold one item
+        fprintf(stderr, "[llmb200] b200_attn_decode_static: one sequence per call (n_items = %d); use b200_attn_decode with "
+                        "caller-provided scratch for the batched form\n", ap->n_items);
+        return B200_E_TOOLARGE;
+    }
     if (need > (size_t)B200_ATTN_STATIC_SCRATCH_FLOATS || ap->n_kv > B200_ATTN_STATIC_MAX_KV_HEADS) {
         fprintf(stderr, "[llmb200] b200_attn_decode_static: n_q*n_split*(hd+2) = %zu floats / %d KV heads exceed the built-in "
                         "scratch (%d floats, %d KV heads); use b200_attn_decode with caller-provided scratch\n",

@@ -65,8 +65,8 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 
 // Bounded wait for a flag another GPU writes. Returns false when it gave up.
 #define B200_SPIN_LIMIT 4000000
-__device__ __forceinline__ bool wait_flag_ge(const unsigned *flag, unsigned want) {
-    for (int it = 0; it < B200_SPIN_LIMIT; ++it) {
+__device__ __forceinline__ bool wait_flag_ge(const unsigned *flag, unsigned want, int limit = B200_SPIN_LIMIT) {
+    for (int it = 0; it < limit; ++it) {
         // signed distance so that a wrapped counter still compares correctly
         if ((int)(ld_acquire_sys(flag) - want) >= 0) return true;
         __nanosleep(20);

@@ -11,10 +11,10 @@
 // rows of a stage with one transposing shuffle reduction per warp plus a
 // fixed-order sum over the group's warps (reproducible run to run).
 //
-// The block is sized (<= ~100 KB shared memory, <= 32K registers) so that a
-// block of the NEXT kernel in the stream fits beside it: launched with
-// programmatic dependent launch, that block fills its own ring with weights
-// while this kernel is still running and only then waits for its input.
+// Launched with programmatic dependent launch, a block of the NEXT kernel in
+// the stream starts as soon as an SM has room for it (with the default 192 KB
+// ring that is when a block of this kernel has left), fills its own ring with
+// weights and only then waits for its input.
 //
 // The math is the reference's q8_matvec / f16_matvec
 // (shaders/q8_kernels.metal:10-42, 97-127): fp32 activations, integer quants
@@ -44,7 +44,6 @@ struct Geometry {
     int nstage;         // ring slots
     unsigned slot_bytes;  // bytes per slot (RB rows, rounded up to 128)
     int share_x;        // 1: group 0 assembles the input vector and hands it to the other groups through shared memory
-    int dbg;            // diagnostics: 1 = no arithmetic, 2 = no waiting for data after the first ring fill
 };
 
 // blockDim.x = NG*T consumers + 32 producer threads.
@@ -88,7 +87,6 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
             const unsigned char *wbase = static_cast<const unsigned char *>(p.d_w);
             for (int i = 0; i < nst; ++i) {
                 const int slot = i % nstage;
-                if ((geo.dbg & 2) && i >= nstage) break;
                 if (i >= nstage && !mbar_wait(&empty[slot], ((i / nstage) - 1) & 1)) {
                     if (p.d_err) *p.d_err = 2;
                     break;
@@ -133,7 +131,7 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
     if (p.n_wait > 0) {
         if (tid < p.n_wait) {
             const unsigned want = (*p.d_epoch) * (unsigned)p.epoch_mul + (unsigned)p.epoch_add;
-            if (!wait_flag_ge(p.d_wait_flags + tid, want)) *p.d_err = 1;
+            if (!wait_flag_ge(p.d_wait_flags + tid, want, p.spin_limit > 0 ? p.spin_limit : B200_SPIN_LIMIT)) *p.d_err = 1;
         }
         named_barrier(1, nC);
     }
@@ -274,9 +272,7 @@ matvec_kernel(const __grid_constant__ b200_matvec_args p, const Geometry geo)
     const uint32_t ring_s = smem_u32(ring), stride = (uint32_t)p.row_stride;
     for (int i = g, it = 0; i < nst; i += NG, ++it) {
         const int slot = i % nstage;
-        if (!((geo.dbg & 2) && i >= nstage))
         if (!mbar_wait(&full[slot], (i / nstage) & 1) && p.d_err) *p.d_err = 3;
-        if (geo.dbg & 1) { mbar_arrive(&empty[slot]); continue; }
         const uint32_t sb = ring_s + (uint32_t)slot * geo.slot_bytes;
         const int row0 = r0 + i * RB;
         const int nr = min(RB, r1 - row0);
@@ -396,10 +392,19 @@ int sm_count()
     return g_sm_count;
 }
 
-int env_int(const char *name, int dflt)
+// Tuning knobs from the environment, read once per process: consumer threads per block and the ring
+// budget in KB (defaults measured on Qwen3-4B shapes).
+struct Knobs { int group_threads, ring_kb; };
+const Knobs &knobs()
 {
-    const char *e = getenv(name);
-    return e && *e ? atoi(e) : dflt;
+    static const Knobs k = [] {
+        auto env_int = [](const char *name, int dflt) { const char *e = getenv(name); return e && *e ? atoi(e) : dflt; };
+        Knobs v;
+        v.group_threads = env_int("LLMB200_MV_GROUP_THREADS", 640);
+        v.ring_kb = env_int("LLMB200_MV_RING_KB", 192);
+        return v;
+    }();
+    return k;
 }
 
 template <int WT, int SPT, int RB, int MAXT>
@@ -492,14 +497,13 @@ extern "C" int b200_matvec(const b200_matvec_args *ap, void *stream)
     while (rb > 1 && (long long)rb * a.row_stride > 24576) rb >>= 1;
     if (rb < ralign) rb = ralign;
     geo.slot_bytes = (unsigned)(((long long)rb * a.row_stride + 127) / 128 * 128);
-    geo.dbg = env_int("LLMB200_MV_DBG", 0);
-    geo.NG = env_int("LLMB200_MV_GROUP_THREADS", 640) / geo.T;
+    geo.NG = knobs().group_threads / geo.T;
     if (geo.NG > 8) geo.NG = 8;
     if (geo.NG < 1) geo.NG = 1;
     // Ring slots: a multiple of the group count, so that a slot is always consumed by the same group.
     // A group works through its stages in order, hence never waits on a slot whose previous phase is
     // still open -- mbarrier parity waits cannot tell phase k from phase k-2.
-    const int ring_budget = env_int("LLMB200_MV_RING_KB", 192) * 1024;
+    const int ring_budget = knobs().ring_kb * 1024;
     while (geo.NG > 1 && (long long)geo.NG * geo.slot_bytes > ring_budget) --geo.NG;
     int per_group = ring_budget / (int)(geo.NG * geo.slot_bytes);
     if (per_group < 1) per_group = 1;
@@ -508,11 +512,7 @@ extern "C" int b200_matvec(const b200_matvec_args *ap, void *stream)
     geo.share_x = geo.NG > 1 && (a.in_mode != B200_IN_VEC || a.d_norm_gamma) && (size_t)spt * geo.T * E * 4 <= 16384;
 
     int grid = a.grid;
-    if (grid <= 0) {
-        // one block per SM, leaving room for the next kernel's block; two for long streams
-        const long long bytes = (long long)a.rows * a.row_stride;
-        grid = sm_count() * (bytes / sm_count() > (long long)env_int("LLMB200_MV_TWO_BLOCK_KB", 1 << 20) * 1024 ? 2 : 1);
-    }
+    if (grid <= 0) grid = sm_count();                // one block per SM
     if (grid > units) grid = units;
     cudaStream_t st = (cudaStream_t)stream;
     if (a.wtype == B200_WT_Q8)

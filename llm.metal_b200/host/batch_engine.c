@@ -108,11 +108,15 @@ BState *llmb200_batch_begin(const llmb200_config *c, int batch_size, int max_gen
     s->max_seq = c->max_seq_len > 4096 ? 4096 : c->max_seq_len;          /* as the reference clamps (:720) */
     if (s->max_seq < 1) s->max_seq = 1;
     s->QKV = (s->Hq + 2 * s->Hkv) * s->hd;
-    s->n_split = 148 / (s->Hkv * s->B);
+    {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g_rt.device) != cudaSuccess || sms <= 0) sms = 1;
+        s->n_split = sms / (s->Hkv * s->B);
+    }
     if (s->n_split < 1) s->n_split = 1;
     if (s->n_split > (s->max_seq + 63) / 64) s->n_split = (s->max_seq + 63) / 64;
     s->hist_cap = max_gen_len;
-    s->eos[0] = 151645; s->eos[1] = 151643; s->n_eos = 2;                 /* the reference's list (:944-946) minus id 0 */
+    s->eos[0] = 151645; s->eos[1] = 151643; s->eos[2] = 0; s->n_eos = 3;  /* the reference's list, id 0 included (:944-946) */
     s->layers = calloc(s->L, sizeof(BLayer));
     const size_t B = s->B, D = s->D, Hq_hd = (size_t)s->Hq * s->hd, Hkv_hd = (size_t)s->Hkv * s->hd;
     for (int l = 0; l < s->L && !s->err; ++l) {
@@ -291,7 +295,10 @@ int llmb200_batch_generate(BState *s, const uint32_t *prompts, int prompt_len, u
 {
     if (!s || !s->finished || !prompts || !output_tokens || prompt_len < 1 || max_gen_len < 1) return 0;
     if (max_gen_len > s->hist_cap) max_gen_len = s->hist_cap;
-    if (prompt_len > s->max_seq) prompt_len = s->max_seq;
+    if (prompt_len > s->max_seq) {               /* as inference_generate: refused, not truncated (the row stride is prompt_len) */
+        fprintf(stderr, "[BatchGen] prompt of %d tokens exceeds the KV cache (%d)\n", prompt_len, s->max_seq);
+        return 0;
+    }
     if (ensure_graph(s) != 0) return 0;
     const int B = s->B;
     cudaStream_t st = g_rt.stream;

@@ -75,7 +75,7 @@ struct InferenceState {
     char *comm;
     size_t comm_bytes, off_slots_o, off_slots_dn, off_flags, off_am_val, off_am_idx, off_logits;
     char *peer[B200_MAX_PEERS];
-    int connected;
+    int connected, loopback;
 
     /* host side */
     float *h_logits;
@@ -831,7 +831,7 @@ void inference_state_free(InferenceState *s)
     cudaFree(s->attn_scratch); cudaFree(s->am_scratch); cudaFree(s->attn_tickets); cudaFree(s->mv_ticket);
     cudaFree(s->d_pos);
     for (int p = 0; p < s->tp_size; ++p)
-        if (p != s->tp_rank && s->peer[p]) cudaIpcCloseMemHandle(s->peer[p]);
+        if (p != s->tp_rank && s->peer[p] && !s->loopback) cudaIpcCloseMemHandle(s->peer[p]);
     cudaFree(s->comm);
     if (s->h_logits) cudaFreeHost(s->h_logits);
     if (s->h_tok) cudaFreeHost(s->h_tok);
@@ -886,6 +886,16 @@ int llmb200_state_error(InferenceState *s)
     int err = 0;
     if (cudaMemcpy(&err, s->d_err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 1;
     return err;
+}
+
+int llmb200_state_connect_loopback(InferenceState *s)
+{
+    if (!s || s->tp_size < 2) return B200_E_BADARG;
+    for (int p = 0; p < s->tp_size; ++p) s->peer[p] = s->comm;   /* nothing is opened: inference_state_free closes nothing it did not open */
+    s->connected = 1;
+    s->loopback = 1;
+    free_graphs(s);
+    return 0;
 }
 
 /* Writes pos / prompt_len (and, when n_tok > 0, token ids starting at tok_at) into the control block. */
@@ -1011,42 +1021,63 @@ int qwen3_generate_fast(llmb200_qwen3_model *model, const uint32_t *prompt, int 
     return n;
 }
 
-/* eos_token_id from config.json: an int or an array of ints. */
+/* Reads the whole file into a NUL-terminated heap buffer (NULL when it cannot be read). */
+static char *slurp(const char *path)
+{
+    FILE *fp = fopen(path, "rb");
+    if (!fp) return NULL;
+    char *text = NULL;
+    long len = -1;
+    if (fseek(fp, 0, SEEK_END) == 0) len = ftell(fp);
+    if (len >= 0 && len < (16L << 20) && fseek(fp, 0, SEEK_SET) == 0 && (text = malloc((size_t)len + 1)) != NULL) {
+        const size_t got = fread(text, 1, (size_t)len, fp);
+        text[got] = 0;
+    }
+    fclose(fp);
+    return text;
+}
+
+/* The "eos_token_id" member of the config.json that belongs to model_path (the file inside it when it
+ * is a directory, else the one beside it): a JSON integer or an array of integers. Stores up to
+ * max_eos ids and returns how many; 0 when the file or the member is missing or holds no integer. */
 static int parse_eos(const char *model_path, int *eos, int max_eos)
 {
-    char path[700];
+    const size_t plen = strlen(model_path);
+    char *cfg = malloc(plen + 16);
+    if (!cfg) return 0;
     struct stat st;
-    if (stat(model_path, &st) == 0 && S_ISDIR(st.st_mode)) snprintf(path, sizeof(path), "%s/config.json", model_path);
-    else {
-        const char *sl = strrchr(model_path, '/');
-        if (sl) snprintf(path, sizeof(path), "%.*s/config.json", (int)(sl - model_path), model_path);
-        else snprintf(path, sizeof(path), "config.json");
+    size_t dir = plen;                                  /* length of the directory part, without the slash */
+    if (!(stat(model_path, &st) == 0 && S_ISDIR(st.st_mode))) {
+        while (dir > 0 && model_path[dir - 1] != '/') --dir;
+        if (dir > 0) --dir;                             /* "a/b.safetensors" -> "a"; no slash at all -> "" (current directory) */
     }
-    FILE *fp = fopen(path, "r");
-    if (!fp) return 0;
-    char buf[4096];
-    size_t n = fread(buf, 1, sizeof(buf) - 1, fp);
-    buf[n] = 0;
-    fclose(fp);
-    const char *p = strstr(buf, "\"eos_token_id\"");
-    if (!p) return 0;
-    p += 14;
-    while (*p == ' ' || *p == ':' || *p == '\t') p++;
-    int cnt = 0;
-    if (*p == '[') {
-        p++;
-        while (*p && *p != ']' && cnt < max_eos) {
-            while (*p == ' ' || *p == ',' || *p == '\n') p++;
-            if (*p == ']') break;
-            char *end;
-            eos[cnt++] = (int)strtol(p, &end, 10);
-            if (end == p) break;
-            p = end;
+    memcpy(cfg, model_path, dir);
+    strcpy(cfg + dir, dir > 0 || model_path[0] == '/' ? "/config.json" : "config.json");
+    char *text = slurp(cfg);
+    free(cfg);
+    if (!text) return 0;
+    int n = 0;
+    const char *key = strstr(text, "\"eos_token_id\"");
+    if (key) {
+        const char *c = key + strlen("\"eos_token_id\"");
+        while (*c && *c != ':') ++c;                    /* the member's value follows the colon */
+        if (*c == ':') ++c;
+        while (*c == ' ' || *c == '\t' || *c == '\r' || *c == '\n') ++c;
+        const int is_array = *c == '[';
+        if (is_array) ++c;
+        /* integers separated by commas and white space, until the array closes (or one integer) */
+        while (n < max_eos) {
+            while (*c == ' ' || *c == '\t' || *c == '\r' || *c == '\n' || (is_array && *c == ',')) ++c;
+            char *after = NULL;
+            const long v = strtol(c, &after, 10);
+            if (after == c) break;                      /* ']' , end of text or anything that is not a number */
+            eos[n++] = (int)v;
+            c = after;
+            if (!is_array) break;
         }
-    } else {
-        eos[cnt++] = (int)strtol(p, NULL, 10);
     }
-    return cnt;
+    free(text);
+    return n;
 }
 
 void inference_state_load_eos(InferenceState *s, const char *model_path)

@@ -698,6 +698,7 @@ static float mean_loss_host(SFTState *s)
 float llmb200_sft_forward_backward(SFTState *s, const uint32_t *inputs, const uint32_t *targets)
 {
     if (!s || !s->finished || !inputs || !targets) return NAN;
+    if (s->err) return NAN;      /* after a failed pass (e.g. an aborted split product leaves its turn counters set) the state is dead */
     cudaStream_t st = g_rt.stream;
     memcpy(s->h_tok, inputs, (size_t)s->M * 4);
     memcpy(s->h_tok + s->M, targets, (size_t)s->M * 4);
@@ -724,6 +725,12 @@ void llmb200_sft_apply_update(SFTState *s, float lr)
 float llmb200_sft_train_batch(SFTState *s, const uint32_t *inputs, const uint32_t *targets, float lr)
 {
     const float loss = llmb200_sft_forward_backward(s, inputs, targets);
+    /* A failed pass (a device wait gave up, a launch failed) or a loss that is not finite leaves partial
+     * gradients: the parameters, the Adam moments and the step count stay as they were. */
+    if (!s || s->err || !isfinite(loss)) {
+        if (s) fprintf(stderr, "[llmb200] sft: step skipped (error %d, loss %g); LoRA parameters unchanged\n", s->err, loss);
+        return loss;
+    }
     llmb200_sft_apply_update(s, lr);
     return loss;
 }

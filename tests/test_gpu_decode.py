@@ -228,7 +228,8 @@ def test_wmat_api_roundtrip(lib, pkg, synth):
 
 
 def test_whole_token_kernel_gives_the_same_tokens(lib, pkg, synth, monkeypatch):
-    """The opt-in persistent whole-token kernel (LLMB200_TOKEN_KERNEL=1) must reproduce the per-step graph exactly."""
+    """The persistent whole-token kernel (the default) and the graph of one kernel per stage (LLMB200_TOKEN_KERNEL=0)
+    must produce the same tokens."""
     sp = pkg.spec("tiny-qwen3", gamma_jitter=0.1)
     model = synth.llmb200_synth_qwen3(C.byref(sp), 8)
     prompt = make_prompt(synth, 16, sp.vocab_size)
@@ -245,3 +246,147 @@ def test_whole_token_kernel_gives_the_same_tokens(lib, pkg, synth, monkeypatch):
     finally:
         synth.llmb200_synth_free_qwen3(model)
     assert outs[0] == outs[1]
+
+
+# ---------------------------------------------------------------------------------------------------
+# Wide cuts: two layers of the benchmarked architectures at full width, against vectors the reference's
+# own C code produced (tests/golden/wide_golden.npz, made by tests/golden/make_wide_golden.py). These are
+# the kernel configurations the benchmarks run: rows of 2560 / 4096 / 9728 (Q8_0) and 1152 / 1024 / 6912
+# (F16) columns, head_dim 128 and 256, the 151936- and 262144-row LM heads with the arg-max over all blocks.
+# ---------------------------------------------------------------------------------------------------
+import os  # noqa: E402
+
+WIDE = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "wide_golden.npz"))
+
+
+def check_wide(lib, pkg, state, tag, vocab):
+    prompt, ref_tok = WIDE[f"{tag}_prompt"], WIDE[f"{tag}_tokens"]
+    absmax, gap, sample, stride = WIDE[f"{tag}_logit_absmax"], WIDE[f"{tag}_top2_gap"], WIDE[f"{tag}_logit_sample"], int(WIDE["stride"])
+    P, G = len(prompt), len(ref_tok)
+    lib.llmb200_state_set_eos(state, None, 0)
+    got = gpu_generate(lib, pkg, state, prompt, G)
+    # logits along the reference's token path
+    seq = np.concatenate([prompt, ref_tok[:-1]])
+    lg = gpu_logits_trace(lib, state, seq, vocab)[P - 1:]
+    rel = np.abs(lg[:, ::stride] - sample).max(axis=1) / absmax
+    assert rel.max() <= 1e-2, f"logit error {rel.max():.3e}"
+    assert np.abs(np.abs(lg).max(axis=1) - absmax).max() <= 1e-2 * absmax.max()
+    if list(got) != list(ref_tok):
+        k = next(i for i in range(G) if got[i] != ref_tok[i])
+        pytest.fail(f"greedy token {k} differs: gpu {got[k]} vs reference {ref_tok[k]}; reference top-2 gap {gap[k]:.3e}, "
+                    f"sampled logit error at that step {rel[k] * absmax[k]:.3e}")
+
+
+@pytest.mark.parametrize("token_kernel", ["1", "0"])
+def test_wide_cut_qwen3_matches_reference_golden(lib, pkg, synth, monkeypatch, token_kernel):
+    monkeypatch.setenv("LLMB200_TOKEN_KERNEL", token_kernel)
+    sp = pkg.spec("qwen3-4b", gamma_jitter=0.1, n_layers=int(WIDE["layers"]))
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 8)
+    state = lib.inference_state_create(model, int(WIDE["max_seq"]), 0)
+    lib.metal_flush()
+    synth.llmb200_synth_free_qwen3(model)              # the state keeps its own device copies
+    assert state
+    try:
+        assert lib.llmb200_state_graph_kernels(state, 1) == (1 if token_kernel == "1" else 5 * sp.n_layers + 1)
+        check_wide(lib, pkg, state, "qwen3", sp.vocab_size)
+    finally:
+        lib.inference_state_free(state)
+
+
+@pytest.mark.parametrize("token_kernel", ["1", "0"])
+def test_wide_cut_gemma3_matches_reference_golden(lib, pkg, synth, monkeypatch, token_kernel):
+    monkeypatch.setenv("LLMB200_TOKEN_KERNEL", token_kernel)
+    sp = pkg.spec("gemma3-1b", gamma_jitter=0.1, n_layers=int(WIDE["layers"]))
+    model = synth.llmb200_synth_gemma3(C.byref(sp), 8)
+    state = lib.inference_state_create_gemma3(model, int(WIDE["max_seq"]), 1)
+    lib.metal_flush()
+    synth.llmb200_synth_free_gemma3(model)
+    assert state
+    try:
+        check_wide(lib, pkg, state, "gemma3", sp.vocab_size)
+    finally:
+        lib.inference_state_free(state)
+
+
+def test_a_rank_that_never_arrives_runs_into_the_bounded_waits(lib, pkg, synth, monkeypatch):
+    """Failure detection without a GPU fault: a two-rank state connected to itself waits for partial sums nobody
+    writes. Every wait must give up after its iteration limit, the launch must complete and the error word must be
+    set; the process and the device stay usable (the next test creates a fresh state)."""
+    monkeypatch.setenv("LLMB200_SPIN_LIMIT", "2000")
+    sp = pkg.spec("tiny-qwen3")
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 4)
+    assert lib.llmb200_set_tp(0, 2) == 0
+    try:
+        state = lib.inference_state_create(model, 32, 0)
+    finally:
+        assert lib.llmb200_set_tp(0, 1) == 0
+    assert state
+    try:
+        assert lib.llmb200_state_connect_loopback(state) == 0
+        assert lib.llmb200_state_error(state) == 0
+        p = lib.inference_forward_token(state, 5)          # completes: nothing hangs
+        assert p
+        assert lib.llmb200_state_error(state) != 0
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model)
+    # a healthy state afterwards: the device context is intact
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 4)
+    state = lib.inference_state_create(model, 32, 0)
+    assert state
+    try:
+        assert lib.inference_forward_token(state, 5) and lib.llmb200_state_error(state) == 0
+    finally:
+        lib.inference_state_free(state)
+        synth.llmb200_synth_free_qwen3(model)
+
+
+def test_layer_containers_roundtrip(lib, pkg, synth):
+    """layers_convert_upload / norm_upload / layers_free (src/nn/wmat.c:87-156): seven matrices and the norm weights of
+    every layer, converted and uploaded in bulk; the device bytes are the reference quantiser's."""
+    D, hd, Hq, Hkv, IS, n_layers = 256, 64, 4, 2, 512, 2
+    shapes = dict(q_proj=(Hq * hd, D), k_proj=(Hkv * hd, D), v_proj=(Hkv * hd, D), o_proj=(D, Hq * hd),
+                  gate_proj=(IS, D), up_proj=(IS, D), down_proj=(D, IS))
+    refs = (pkg.LayerWeightRef * n_layers)()
+    keep = []
+    fp = pkg.c_float_p
+    for l in range(n_layers):
+        for i, (name, (r, c)) in enumerate(shapes.items()):
+            w = np.empty((r, c), dtype=np.float32)
+            synth.llmb200_synth_normal(w.ctypes.data, w.size, 5, 100 * l + i, 0.0, 0.02, 1)
+            keep.append((l, name, w))
+            setattr(refs[l], name, pkg.WeightRef(w.ctypes.data_as(fp), r, c))
+        g = (1.0 + 0.1 * np.arange(D, dtype=np.float32) / D).astype(np.float32)
+        gq = np.linspace(0.5, 1.5, hd).astype(np.float32)
+        keep += [(l, "g", g), (l, "gq", gq)]
+        refs[l].input_norm_g, refs[l].post_attn_norm_g = g.ctypes.data_as(fp), g.ctypes.data_as(fp)
+        refs[l].q_norm_g, refs[l].k_norm_g = gq.ctypes.data_as(fp), gq.ctypes.data_as(fp)
+        refs[l].d_model, refs[l].head_dim = D, hd
+
+    class LayerW(C.Structure):                       # LayerW of include/llmb200_wmat.h
+        _fields_ = [(n, C.POINTER(pkg.WMat)) for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")] + \
+                   [(n, C.c_void_p) for n in ("input_norm_g", "post_attn_norm_g", "pre_ff_norm_g", "post_ff_norm_g", "q_norm_g", "k_norm_g")]
+
+    for use_fp16 in (0, 1):
+        lw = lib.layers_convert_upload(refs, n_layers, use_fp16)
+        assert lw
+        arr = C.cast(lw, C.POINTER(LayerW))
+        for l, name, w in keep:
+            if name in shapes:
+                m = getattr(arr[l], name).contents
+                assert (m.rows, m.cols) == w.shape and m.nb == (0 if use_fp16 else w.shape[1] // 32)
+                p = lib.metal_buf_ptr(m.mbuf)
+                if use_fp16:
+                    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint16)), shape=w.shape).copy()
+                    assert np.array_equal(got, O.f16_bits(w))
+                else:
+                    got = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(w.size // 32 * 34,)).copy()
+                    assert np.array_equal(got, O.q8_quantize(w))
+        g0 = np.ctypeslib.as_array(C.cast(lib.metal_buf_ptr(arr[0].input_norm_g), fp), shape=(D,)).copy()
+        assert np.array_equal(g0, keep[7][2])
+        assert not arr[0].pre_ff_norm_g and not arr[0].post_ff_norm_g        # absent norms stay NULL
+        lib.layers_free(lw, n_layers)
+    nb = lib.norm_upload(keep[7][2].ctypes.data_as(fp), D)
+    assert nb
+    assert np.array_equal(np.ctypeslib.as_array(C.cast(lib.metal_buf_ptr(nb), fp), shape=(D,)), keep[7][2])
+    lib.metal_buf_free(nb)

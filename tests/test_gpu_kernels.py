@@ -207,6 +207,51 @@ def test_matvec_fused_norm_glu_and_argmax(lib, pkg, synth):
         assert float(d_val.item()) == float(y.max())
 
 
+@pytest.mark.parametrize("rows,cols,wtype", [(151936, 2560, 0), (262144, 1152, 1)])
+def test_lm_head_shapes_with_argmax_across_all_blocks(lib, pkg, synth, rows, cols, wtype):
+    """The two LM heads of the benchmarked architectures: the longest streams (413 MB Q8_0, 604 MB F16), ~1000+ rows per
+    block, the device arg-max folded over every block."""
+    w = weights(synth, rows, cols, 31)
+    x = weights(synth, 1, cols, 91, std=1.0)[0]
+    d_w, stride = pack(lib, pkg, w, wtype)
+    d_scr = torch.zeros(2 * 1024 * 32, dtype=torch.float32, device="cuda")
+    d_val = torch.zeros(1, dtype=torch.float32, device="cuda")
+    d_idx = torch.zeros(1, dtype=torch.int32, device="cuda")
+    d_ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kw = dict(d_argmax_scratch=d_scr.data_ptr(), n_argmax_out=1, d_ticket=d_ticket.data_ptr())
+    a_val, a_idx = (C.c_void_p * pkg.B200_MAX_PEERS)(), (C.c_void_p * pkg.B200_MAX_PEERS)()
+    a_val[0], a_idx[0] = d_val.data_ptr(), d_idx.data_ptr()
+    y = run_matvec(lib, pkg, d_w, stride, rows, cols, wtype, x, d_argmax_val=a_val, d_argmax_idx=a_idx, **kw)
+    if wtype == pkg.B200_WT_Q8:
+        ref = O.q8_matvec(O.q8_quantize(w), x, rows, cols)
+    else:
+        ref = O.f16_matvec(O.f16_bits(w), x)
+    assert np.abs(y - ref).max() <= 2e-4 * np.abs(ref).max()
+    assert int(d_idx.item()) == int(np.argmax(y)) and float(d_val.item()) == float(y.max())
+
+
+def test_matvec_wait_on_a_flag_nobody_raises_gives_up(lib, pkg, synth):
+    """Bounded wait of the per-stage kernels: n_wait = 1 on a flag that stays 0. The launch must complete with
+    *d_err == 1 (and the product computed from whatever the slots held); nothing hangs."""
+    rows, cols = 64, 512
+    w = weights(synth, rows, cols, 41)
+    d_w, stride = pack(lib, pkg, w, pkg.B200_WT_Q8)
+    d_flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    d_epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    d_err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = weights(synth, 1, cols, 90, std=1.0)[0]
+    run_matvec(lib, pkg, d_w, stride, rows, cols, pkg.B200_WT_Q8, x, d_wait_flags=d_flags.data_ptr(), n_wait=1,
+               d_epoch=d_epoch.data_ptr(), epoch_mul=1, epoch_add=0, d_err=d_err.data_ptr(), spin_limit=1000)
+    assert int(d_err.item()) == 1
+    d_err.zero_()
+    d_flags[0] = 1                                   # raised: the same launch goes through
+    y = run_matvec(lib, pkg, d_w, stride, rows, cols, pkg.B200_WT_Q8, x, d_wait_flags=d_flags.data_ptr(), n_wait=1,
+                   d_epoch=d_epoch.data_ptr(), epoch_mul=1, epoch_add=0, d_err=d_err.data_ptr(), spin_limit=1000)
+    assert int(d_err.item()) == 0
+    ref = O.q8_matvec(O.q8_quantize(w), x, rows, cols)
+    assert np.abs(y - ref).max() <= 2e-4 * np.abs(ref).max()
+
+
 def test_matvec_rejects_bad_arguments(lib, pkg):
     a = pkg.MatvecArgs()
     assert lib.b200_matvec(C.byref(a), None) < 0

@@ -4,8 +4,9 @@ Some callers of this library cannot allocate device memory at the point where th
 memory was handed out in full at start-up, or a cudaMalloc would stall the whole device in the middle of
 a latency-critical loop. For them the split-sequence scratch lives inside the library. This test calls that
 entry point through the C ABI, twice in a row (the built-in arrays keep the previous call's contents), and
-checks each result against b200_attn_decode with caller-provided scratch. The two run the same kernel, so
-the results must be identical; the bar used is the attention tests' 2e-3 of max|out|.
+checks each result against b200_attn_decode with caller-provided scratch (the two run the same kernel, so
+the results must be identical) and against the fp32 restatement of the attention the kernel tests use; the
+bar is the attention tests' 2e-3 of max|out|.
 """
 import ctypes as C
 
@@ -45,6 +46,11 @@ def test_static_scratch_matches_caller_scratch_twice(lib, pkg):
         assert np.isfinite(o1).all() and np.abs(o1).max() > 0
         assert np.abs(o1 - o0).max() <= 2e-3 * np.abs(o0).max()
         assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
+        # and directly against the restatement: cache rows below pos as binary16 values, row pos from q/k/v
+        from test_gpu_kernels import attn_reference
+        want = attn_reference(qkv.cpu().numpy(), d_qg.cpu().numpy(), d_kg.cpu().numpy(), 1e6, kc.astype(np.float32),
+                              vc.astype(np.float32), pos, n_q, n_kv, hd)
+        assert np.abs(o1 - want).max() <= 2e-3 * np.abs(want).max()
 
 
 def test_static_scratch_refuses_oversized_requests(lib, pkg):
@@ -52,5 +58,8 @@ def test_static_scratch_refuses_oversized_requests(lib, pkg):
     a.n_q, a.n_kv, a.hd, a.max_seq, a.n_split = 64, 8, 256, 4096, 64        # 64*64*258 floats > 2^18
     assert lib.b200_attn_decode_static(C.byref(a), None) == -2              # B200_E_TOOLARGE
     a.n_q, a.n_kv, a.n_split = 128, 128, 1                                   # too many KV heads
+    assert lib.b200_attn_decode_static(C.byref(a), None) == -2
+    # the batched form needs scratch and tickets per item: refused, nothing is launched
+    a.n_q, a.n_kv, a.hd, a.n_split, a.n_items = 32, 8, 128, 18, 2
     assert lib.b200_attn_decode_static(C.byref(a), None) == -2
     assert lib.b200_attn_decode_static(None, None) == -1

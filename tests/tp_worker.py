@@ -2,6 +2,8 @@
 
 Launched by torch.distributed.run with one process per GPU. Every rank builds the same seeded model, keeps its
 own shard (llmb200_set_tp), connects to its peers and generates; all ranks must return the oracle's tokens.
+Architecture "wide-qwen3" is the two-layer cut of Qwen3-4B at full width (8 KV heads: shards over 2, 4 and 8
+ranks) and is checked against tests/golden/wide_golden.npz, vectors the reference's own C code produced.
 """
 import ctypes as C
 import os
@@ -25,11 +27,13 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = entry.load_package()
     L, S = pkg.lib(), pkg.synth()
-    sp = pkg.spec(arch, gamma_jitter=0.1)
+    wide = arch == "wide-qwen3"
+    golden = np.load(os.path.join(ROOT, "tests", "golden", "wide_golden.npz")) if wide else None
+    sp = pkg.spec("qwen3-4b", gamma_jitter=0.1, n_layers=int(golden["layers"])) if wide else pkg.spec(arch, gamma_jitter=0.1)
     gemma = arch.endswith("gemma3")
     model = (S.llmb200_synth_gemma3 if gemma else S.llmb200_synth_qwen3)(C.byref(sp), 4)
     assert L.llmb200_set_tp(rank, world) == 0
-    max_seq, P, G = 96, 16, 32
+    max_seq, P, G = (int(golden["max_seq"]) if wide else 96), 16, 32
     st = (L.inference_state_create_gemma3 if gemma else L.inference_state_create)(model, max_seq, use_fp16)
     assert st, "state create failed"
     h = (C.c_ubyte * pkg.LLMB200_HANDLE_BYTES)()
@@ -54,13 +58,28 @@ def main():
         assert p
         lg = np.ctypeslib.as_array(p, shape=(sp.vocab_size,)).copy()
     dist.barrier()
-    om = (O.model_gemma3 if gemma else O.model_qwen3)(model, use_fp16, max_seq, vocab=sp.vocab_size)
-    ref, _ = O.generate(om, prompt, G)
-    ref_lg = None
-    om2 = (O.model_gemma3 if gemma else O.model_qwen3)(model, use_fp16, max_seq, vocab=sp.vocab_size)
-    for i, t in enumerate(prompt[:4]):
-        ref_lg = O.forward_token(om2, t, i)
-    ok = list(out) == list(ref) and np.abs(lg - ref_lg).max() <= 1e-2 * np.abs(ref_lg).max()
+    if wide:
+        # reference vectors: tokens of the greedy decode; the fourth prompt position's logits are not in the file,
+        # so the logits check runs along the generated path instead (sampled every `stride`-th logit)
+        ref = golden["qwen3_tokens"]
+        assert list(prompt) == list(golden["qwen3_prompt"])
+        L.inference_state_reset(st)
+        seq = np.concatenate([prompt, ref[:1]])
+        for t in seq:
+            p = L.inference_forward_token(st, int(t))
+            lg = np.ctypeslib.as_array(p, shape=(sp.vocab_size,)).copy()
+        stride = int(golden["stride"])
+        err = np.abs(lg[::stride] - golden["qwen3_logit_sample"][1]).max() / golden["qwen3_logit_absmax"][1]
+        ok = list(out) == list(ref) and err <= 1e-2
+        ref_lg = lg if ok else lg + 1.0
+    else:
+        om = (O.model_gemma3 if gemma else O.model_qwen3)(model, use_fp16, max_seq, vocab=sp.vocab_size)
+        ref, _ = O.generate(om, prompt, G)
+        ref_lg = None
+        om2 = (O.model_gemma3 if gemma else O.model_qwen3)(model, use_fp16, max_seq, vocab=sp.vocab_size)
+        for i, t in enumerate(prompt[:4]):
+            ref_lg = O.forward_token(om2, t, i)
+        ok = list(out) == list(ref) and np.abs(lg - ref_lg).max() <= 1e-2 * np.abs(ref_lg).max()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
