@@ -15,9 +15,17 @@ architecture, quantised to Q8_0 on the GPU; token ids are uniform random.
   e2e        the same metric through the reference-facing call
              inference_generate() with host buffers: prompt ids copied in,
              every generated id copied back inside the timed region.
-  roofline   the dominant kernel (the gate/up Q8_0 matvec): algorithmic bytes
-             per launch / CUDA-event duration per launch, against the measured
-             HBM copy bandwidth.
+  roofline   the dominant kernel. With the whole-token kernel (the default) that
+             is the one kernel of a token: algorithmic bytes per launch (weights
+             + norm weights + F16 K/V rows + embedding row) / CUDA-event time per
+             launch, against the measured HBM copy bandwidth.
+  secondary  (N = 1, default workload) the other configurations of the
+             benchmark set, measured in child processes after the headline run:
+             the standalone Q8_0 matvec sweep, Gemma3-1B F16 decode, the LoRA SFT
+             step.
+  parity     tokens of a two-layer full-width cut of the architecture against
+             vectors the reference's own C code produced (tests/golden), checked
+             on the GPU(s) of this run before anything is timed.
   cpu_baseline  the reference's own C code path (oracle/_ref) on one host
              thread, on a bounded sample of the same workload.
 
@@ -47,6 +55,8 @@ WORKLOADS = {
     "gemma3-1b-f16": ("gemma3-1b", 1, 128, 256, 512),
     "tiny-gemma3-f16": ("tiny-gemma3", 1, 16, 32, 96),
 }
+# Standalone Q8_0 matvec, batch 1, the six shapes of Qwen3-4B (rows x cols), fp32 activations N(0,1)
+SWEEP_SHAPES = [(4096, 2560), (1024, 2560), (2560, 4096), (9728, 2560), (2560, 9728), (151936, 2560)]
 HBM_FALLBACK_GBS = 6650.0
 
 # Libraries (NCCL's version banner, the engine's progress lines) write to file descriptor 1 too; the
@@ -60,6 +70,10 @@ def emit(text):
     os.write(_JSON_FD, (text + "\n").encode())
 
 GATEUP_TRAFFIC_BYTES = 53_014_700
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_token_kernel launch, from the ncu capture of a
+# 4-layer cut at position ~520 (profiles/decode_token_qwen3-4b_4layers_full.md): per layer and for the rest
+# (LM head, embedding row). Traffic grows in proportion to the layers; null until such a capture exists.
+TOKEN_TRAFFIC = {"qwen3-4b": None}
 
 
 def measured_peaks():
@@ -580,14 +594,177 @@ def sft_main(args, rank, local_rank, world):
     return 0
 
 
+
+def sweep_main(args):
+    """Config 2: standalone Q8_0 matvec over the six Qwen3-4B shapes, one GPU. Each shape rotates over enough
+    weight copies to exceed L2 (>= 256 MB footprint, at least 8 copies), so every launch streams from HBM;
+    timed with CUDA events on the launching stream. Beside it the reference's CPU matvec on dequantised fp32
+    weights (oracle/_ref ref_linear, one thread)."""
+    import torch
+    pkg = entry.load_package()
+    L, S = pkg.lib(), pkg.synth()
+    torch.cuda.set_device(0)
+    peak, peak_kind = measured_peaks()
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    rows_out = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches = 0
+    for rows, cols in SWEEP_SHAPES:
+        stride = L.b200_packed_row_stride(pkg.B200_WT_Q8, cols)
+        one = stride * rows
+        copies = max(8, -(-(256 << 20) // one))
+        w = gen_f32(S, rows * cols, 1234, 7, 0.02, 16).reshape(rows, cols)
+        d_src = torch.from_numpy(w).cuda()
+        d_w = torch.empty(copies * one, dtype=torch.uint8, device="cuda")
+        for c in range(copies):
+            if L.b200_q8_pack(d_src.data_ptr(), cols, rows, cols, d_w.data_ptr() + c * one, stride, 0, 1, None) != 0:
+                raise RuntimeError("pack failed")
+        x = torch.from_numpy(gen_f32(S, cols, 99, 1, 1.0, 1)).cuda()
+        y = torch.zeros(rows, dtype=torch.float32, device="cuda")
+        a = pkg.MatvecArgs()
+        a.row_stride, a.rows, a.cols, a.wtype = stride, rows, cols, pkg.B200_WT_Q8
+        a.in_mode, a.d_in_vec = pkg.B200_IN_VEC, x.data_ptr()
+        a.out_mode, a.n_out, a.eps = pkg.B200_OUT_STORE, 1, 1e-6
+        a.d_out[0] = y.data_ptr()
+
+        def launch(c):
+            a.d_w = d_w.data_ptr() + c * one
+            if L.b200_matvec(C.byref(a), None) != 0:
+                raise RuntimeError("matvec failed")
+        for c in range(copies):
+            launch(c)
+        torch.cuda.synchronize()
+        reps = max(3, args.steps) * copies
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            launch(i % copies)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        launches += reps
+        alg = rows * cols * 34 // 32 + 4 * cols + 4 * rows
+        entry_ = {"rows": rows, "cols": cols, "us_per_launch": us, "algorithmic_bytes": alg, "gbs": alg / us / 1e3,
+                  "frac_of_hbm": alg / us / 1e3 / peak, "weight_copies": copies}
+        if not args.no_cpu_baseline:
+            import _oracle as O
+            if O.have_ref():
+                wd = O.q8_dequantize(O.q8_quantize(w), rows, cols)
+                xv = x.cpu().numpy()
+                yv = np.zeros(rows, dtype=np.float32)
+                t0 = time.perf_counter()
+                O.ref().ref_linear(wd.ctypes.data, xv.ctypes.data, yv.ctypes.data, rows, cols)
+                entry_["cpu_reference_us"] = (time.perf_counter() - t0) * 1e6
+                got = y.cpu().numpy()
+                entry_["max_rel_err_vs_reference"] = float(np.abs(got - yv).max() / np.abs(yv).max())
+        rows_out.append(entry_)
+        del d_w, d_src
+        torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    big = rows_out[-1]
+    total_bytes = sum(r["algorithmic_bytes"] for r in rows_out)
+    total_us = sum(r["us_per_launch"] for r in rows_out)
+    line = {"metric": "q8_matvec_hbm_gbs", "value": total_bytes / total_us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 accumulate over int8 (Q8_0) weights", "data": "synthetic",
+            "config": {"workload": "standalone Q8_0 matvec sweep, batch 1, six Qwen3-4B shapes", "shapes": [list(sh) for sh in SWEEP_SHAPES],
+                       "l2": "rotating weight copies, >= 256 MB footprint per shape"},
+            "e2e": {"value": total_bytes / total_us / 1e3, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "a kernel-level sweep: inputs are device-resident by definition of the configuration"},
+            "gpu_launches": launches, "shapes": rows_out, "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "matvec_kernel<Q8_0> 151936 x 2560", "achieved": big["gbs"], "peak": peak, "unit": "GB/s",
+                         "frac": big["frac_of_hbm"], "peak_source": peak_kind, "traffic": None,
+                         "algorithmic_bytes_per_launch": big["algorithmic_bytes"]}}
+    emit(json.dumps(line))
+    return 0
+
+
+def run_secondary(args):
+    """The other configurations of the benchmark set, each in a child process (one GPU, few steps)."""
+    out = {}
+    for key, wl, extra in (("matvec_sweep_q8", "matvec-sweep", []), ("gemma3_1b_f16_decode", "gemma3-1b-f16", []),
+                           ("qwen3_4b_sft_lora", "qwen3-4b-sft-lora", [])):
+        cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--workload", wl, "--steps", "2", "--warmup", "3", "--no-secondary"] + extra
+        if args.no_cpu_baseline or key == "qwen3_4b_sft_lora":
+            cmd.append("--no-cpu-baseline")
+        try:
+            r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+            lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+            d = json.loads(lines[-1]) if r.returncode == 0 and lines else None
+        except Exception as e:                     # a failed secondary never takes the headline down
+            d, r = None, None
+            sys.stderr.write(f"[bench] secondary {wl} failed: {e}\n")
+        if d is None:
+            out[key] = {"failed": (r.stderr[-300:] if r is not None else "exception")}
+            continue
+        keep = {k: d[k] for k in ("metric", "value", "unit", "dtype", "ms_per_step", "steps", "warmup") if k in d}
+        keep["workload"] = d["config"]["workload"]
+        for k in ("token_roofline", "roofline", "shapes", "step_tflops_per_gpu", "e2e", "clocks", "parity"):
+            if k in d:
+                keep[k] = d[k]
+        out[key] = keep
+    return out
+
+
+def wide_parity(pkg, L, S, rank, world, threads, dist):
+    """Greedy tokens of the two-layer full-width cut of Qwen3-4B (Q8_0) on the GPU(s) of this run against the
+    vectors the reference's own C code produced (tests/golden/wide_golden.npz); sampled logits of the last step."""
+    import torch
+    g = np.load(os.path.join(ROOT, "tests", "golden", "wide_golden.npz"))
+    sp = pkg.spec("qwen3-4b", gamma_jitter=0.1, n_layers=int(g["layers"]))
+    model = S.llmb200_synth_qwen3(C.byref(sp), threads)
+    st = L.inference_state_create(model, int(g["max_seq"]), 0)
+    L.metal_flush()
+    S.llmb200_synth_free_qwen3(model)
+    if not st:
+        raise RuntimeError("parity model could not be created")
+    if world > 1:
+        connect_ranks(pkg, L, st, world, dist)
+    L.llmb200_state_set_eos(st, None, 0)
+    prompt, ref = g["qwen3_prompt"], g["qwen3_tokens"]
+    out = np.zeros(len(ref), dtype=np.uint32)
+    n = L.inference_generate(st, prompt.ctypes.data_as(pkg.c_u32_p), len(prompt), out.ctypes.data_as(pkg.c_u32_p), len(ref))
+    L.inference_state_reset(st)
+    lg = None
+    for t in np.concatenate([prompt, ref[:-1]]):
+        p = L.inference_forward_token(st, int(t))
+        lg = np.ctypeslib.as_array(p, shape=(sp.vocab_size,)).copy()
+    err = float(np.abs(lg[::int(g["stride"])] - g["qwen3_logit_sample"][-1]).max() / g["qwen3_logit_absmax"][-1])
+    ok = n == len(ref) and list(out) == list(ref) and L.llmb200_state_error(st) == 0
+    L.inference_state_free(st)
+    if world > 1:
+        t = torch.tensor([1.0 if ok else 0.0, -err], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok, err = bool(t[0].item() > 0.5), float(-t[1].item())
+    return {"workload": "qwen3-4b widths, 2 layers, Q8_0, prompt 16, generate 32 (tests/golden/wide_golden.npz)",
+            "tokens_match_reference": bool(ok), "max_rel_logit_err": err, "ranks": world}
+
+
+def connect_ranks(pkg, L, st, world, dist):
+    import torch
+    h = (C.c_ubyte * pkg.LLMB200_HANDLE_BYTES)()
+    if L.llmb200_state_comm_handle(st, h) != 0:
+        raise RuntimeError("comm handle failed")
+    mine = torch.tensor(list(h), dtype=torch.uint8, device="cuda")
+    allh = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    table = bytes(torch.cat(allh).cpu().numpy().tobytes())
+    if L.llmb200_state_connect(st, table, world) != 0:
+        raise RuntimeError("connect failed")
+    dist.barrier()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="qwen3-4b-q8", choices=sorted(WORKLOADS) + sorted(SFT_WORKLOADS) + sorted(BATCH_WORKLOADS))
+    ap.add_argument("--workload", default="qwen3-4b-q8",
+                    choices=sorted(WORKLOADS) + sorted(SFT_WORKLOADS) + sorted(BATCH_WORKLOADS) + ["matvec-sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations and the parity stamp")
     ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (profiling runs)")
     ap.add_argument("--gen-len", type=int, default=0, help="override the workload's generation length (profiling runs)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small ncu captures)")
@@ -600,6 +777,13 @@ def main():
         return sft_main(args, rank, local_rank, world)
     if args.workload in BATCH_WORKLOADS:
         return batch_main(args, rank, local_rank, world)
+    if args.workload == "matvec-sweep":
+        if args.impl == "reference" or world > 1:
+            if rank == 0:
+                emit(json.dumps({"impl": args.impl, "unavailable": "the matvec sweep is a one-GPU kernel workload; its CPU reference "
+                                 "timing is part of its own line"}))
+            return 0
+        return sweep_main(args)
     arch, use_fp16, P, G, max_seq = WORKLOADS[args.workload]
     P, G = args.prompt_len or P, args.gen_len or G
     pkg = entry.load_package()
@@ -642,6 +826,9 @@ def main():
     L = pkg.lib()
     if L.llmb200_set_tp(rank, world) != 0:
         raise RuntimeError("llmb200_set_tp failed")
+    parity = None
+    if arch == "qwen3-4b" and not args.layers and not args.no_secondary:
+        parity = wide_parity(pkg, L, S, rank, world, threads, dist)
     t0 = time.time()
     if gemma:
         model = S.llmb200_synth_gemma3(C.byref(sp), threads)
@@ -653,16 +840,7 @@ def main():
     else:
         st = build_state_streaming(pkg, L, S, sp, max_seq, use_fp16, threads)
     if world > 1:
-        h = (C.c_ubyte * pkg.LLMB200_HANDLE_BYTES)()
-        if L.llmb200_state_comm_handle(st, h) != 0:
-            raise RuntimeError("comm handle failed")
-        mine = torch.tensor(list(h), dtype=torch.uint8, device="cuda")
-        allh = [torch.zeros_like(mine) for _ in range(world)]
-        dist.all_gather(allh, mine)
-        table = bytes(torch.cat(allh).cpu().numpy().tobytes())
-        if L.llmb200_state_connect(st, table, world) != 0:
-            raise RuntimeError("connect failed")
-        dist.barrier()
+        connect_ranks(pkg, L, st, world, dist)
     build_s = time.time() - t0
     L.llmb200_state_set_eos(st, None, 0)          # uniform random ids: never stop early
 
@@ -696,13 +874,15 @@ def main():
 
     def e2e_step():
         barrier()
+        t_call = time.perf_counter()
         n = L.inference_generate(st, pp, P, op, G)
+        wall_ms = (time.perf_counter() - t_call) * 1e3
         nd = C.c_int(0)
         ms = L.llmb200_last_decode_ms(st, C.byref(nd))
         barrier()
         if n != G:
             raise RuntimeError(f"generate returned {n} tokens")
-        return max_over_ranks(ms), nd.value
+        return max_over_ranks(ms), nd.value, max_over_ranks(wall_ms)
 
     for _ in range(args.warmup):
         device_step()
@@ -716,47 +896,64 @@ def main():
     if L.llmb200_state_error(st):
         raise RuntimeError("a device-side wait timed out")
 
-    # per-kernel durations: each kind of kernel launched back to back over all layers (different weights
-    # every launch, so L2 cannot serve them) between two CUDA events on the library's stream
-    L.inference_generate(st, pp, P, op, 1)
-    L.llmb200_state_run_device_steps(st, (G - 1) // 2)       # to the middle of the decode range
-    names = ["qkv_matvec", "attention", "o_matvec", "gateup_matvec", "down_matvec", "lm_head_matvec"]
-    prof = {}
-    for i, nme in enumerate(names):
-        nl = C.c_int(0)
-        ms = L.llmb200_state_time_kind(st, i, 8 if i < 5 else 24, C.byref(nl))
-        if ms <= 0 or nl.value <= 0:
-            raise RuntimeError("kernel timing failed")
-        prof[nme] = {"us_per_launch": 1e3 * ms / nl.value, "launches_timed": nl.value,
-                     "launches_per_token": sp.n_layers if i < 5 else 1}
+    per_token_kernels = L.llmb200_state_graph_kernels(st, 1)
+    token_kernel = per_token_kernels == 1
     peak, peak_kind = measured_peaks()
-    D, IS = sp.d_model, sp.intermediate_size
-    gu_rows, gu_cols = 2 * IS // world, D
-    gu_bytes = gu_rows * gu_cols * (2 if use_fp16 else 34 / 32) + 4 * gu_cols + 4 * (gu_rows // 2)
-    gu_bytes = int(gu_bytes)
-    gu_s = 1e-6 * prof["gateup_matvec"]["us_per_launch"]
-    achieved = gu_bytes / gu_s / 1e9
-    roofline = {"bound": "hbm", "kernel": "matvec_kernel<%s> gate/up (rows %d x cols %d)" % (wname, gu_rows, gu_cols),
-                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch from the ncu --set full capture
-                # (profiles/matvec_gateup_qwen3-4b_4layers_full.md): 53.01 MB at N=1; the rows, and with them the
-                # traffic, divide by the tensor-parallel degree
-                "traffic": (GATEUP_TRAFFIC_BYTES // world) if arch == "qwen3-4b" else None,
-                "algorithmic_bytes_per_launch": gu_bytes}
-
     n_tok = args.steps * (G - 1)
     value = n_tok / (sum(step_ms) / 1e3)
-    e2e_ms = sum(m for m, _ in e2e)
-    e2e_tok = sum(n for _, n in e2e)
+    e2e_ms = sum(m for m, _, _ in e2e)
+    e2e_tok = sum(n for _, n, _ in e2e)
+    call_ms = sum(w for _, _, w in e2e)
     mean_bytes = float(np.mean([algorithmic_bytes_per_token(sp, n, world, use_fp16, gemma) for n in range(P + 1, P + G)]))
-    per_token_kernels = L.llmb200_state_graph_kernels(st, 1)
+    us_per_token = 1e3 * sum(step_ms) / n_tok
+    prof = {}
+    if token_kernel:
+        # one persistent kernel per token: its launches are the timed region itself
+        prof["decode_token_kernel"] = {"us_per_launch": us_per_token, "launches_timed": n_tok, "launches_per_token": 1}
+        achieved = mean_bytes / (us_per_token * 1e-6) / 1e9
+        tr = TOKEN_TRAFFIC.get(arch)
+        traffic = None
+        if tr and world == 1 and not args.layers:
+            traffic = int(tr["per_layer"] * sp.n_layers + tr["rest"])
+        roofline = {"bound": "hbm", "kernel": "decode_token_kernel<%s> (whole token: %d layers + LM head)" % (wname, sp.n_layers),
+                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                    "traffic": traffic,
+                    "traffic_source": ("ncu capture of a 4-layer cut, scaled by layers (profiles/)" if traffic else
+                                       "none at N > 1 or for cuts: DRAM bytes are only measured on one GPU"),
+                    "algorithmic_bytes_per_launch": int(mean_bytes)}
+    else:
+        # one kernel per stage: each kind launched back to back over all layers (different weights every launch,
+        # so L2 cannot serve them) between two CUDA events on the library's stream
+        barrier()                                                # the ranks must enter the next request together
+        L.inference_generate(st, pp, P, op, 1)
+        L.llmb200_state_run_device_steps(st, (G - 1) // 2)       # to the middle of the decode range
+        names = ["qkv_matvec", "attention", "o_matvec", "gateup_matvec", "down_matvec", "lm_head_matvec"]
+        for i, nme in enumerate(names):
+            nl = C.c_int(0)
+            ms = L.llmb200_state_time_kind(st, i, 8 if i < 5 else 24, C.byref(nl))
+            if ms <= 0 or nl.value <= 0:
+                raise RuntimeError("kernel timing failed")
+            prof[nme] = {"us_per_launch": 1e3 * ms / nl.value, "launches_timed": nl.value,
+                         "launches_per_token": sp.n_layers if i < 5 else 1}
+        D, IS = sp.d_model, sp.intermediate_size
+        gu_rows, gu_cols = 2 * IS // world, D
+        gu_bytes = int(gu_rows * gu_cols * (2 if use_fp16 else 34 / 32) + 4 * gu_cols + 4 * (gu_rows // 2))
+        achieved = gu_bytes / (1e-6 * prof["gateup_matvec"]["us_per_launch"]) / 1e9
+        roofline = {"bound": "hbm", "kernel": "matvec_kernel<%s> gate/up (rows %d x cols %d)" % (wname, gu_rows, gu_cols),
+                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                    "traffic": GATEUP_TRAFFIC_BYTES if (arch == "qwen3-4b" and world == 1) else None,
+                    "traffic_source": "ncu capture of the N=1 4-layer cut (profiles/matvec_gateup_qwen3-4b_4layers_full.md)",
+                    "algorithmic_bytes_per_launch": gu_bytes}
     line = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sum(step_ms) / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 accumulate over %s weights" % ("binary16" if use_fp16 else "int8 (Q8_0)"),
         "data": "synthetic", "config": config,
+        # e2e.value: the reference's own metric (decode loop only, src/nn/fast_inference.c:643-672) through
+        # inference_generate with host buffers; whole_call_*: wall clock around the entire call, prefill included
         "e2e": {"value": e2e_tok / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": int(P * 4 + 8),
-                "d2h_bytes_per_step": int(G * 4)},
+                "d2h_bytes_per_step": int(G * 4), "whole_call_ms": call_ms / args.steps,
+                "whole_call_tokens_per_s": args.steps * (P + G - 1) / (call_ms / 1e3)},
         "gpu_launches": int(args.steps * (G - 1) * per_token_kernels),
         "roofline": roofline,
         "token_roofline": {"bytes_per_token_per_gpu": mean_bytes, "achieved_gbs": mean_bytes * value / 1e9,
@@ -764,6 +961,12 @@ def main():
         "kernels": prof, "clocks": clocks, "ms_per_token": sum(step_ms) / n_tok, "build_seconds": build_s,
         "first_tokens": first_tokens,
     }
+    if parity is not None:
+        line["parity"] = parity
+    if world > 1:
+        line["exchange"] = {"impl": "partial sums stored with their flags into every rank's slot over NVLink (plain peer stores), summed "
+                                    "in rank order inside the consumer stage of the same kernel; no separate all-reduce kernel",
+                            "exchanges_per_token": 2 * sp.n_layers}
     if world == 1 and not args.no_cpu_baseline and not gemma:
         if rank == 0:
             line["cpu_baseline"] = cpu_reference_sample(pkg, S, sp, threads)
@@ -771,6 +974,9 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if world == 1 and arch == "qwen3-4b" and not args.layers and not args.no_secondary:
+        torch.cuda.empty_cache()
+        line["secondary"] = run_secondary(args)
     if rank == 0:
         emit(json.dumps(line))
     return 0
