@@ -7,11 +7,13 @@ sft_apply_ce_loss :754-760, sft_backward_ex :766-982 LoRA branch, clip_grad_norm
 adamw_update :1045-1058, lora_update :1090-1107, sft_train_step :1113-1157, sft_save_lora :1255-1285)
 with the per-kernel arithmetic of shaders/q8_kernels.metal (line numbers at each function).
 
-Parity status: UNPINNED against the reference's own execution -- the reference runs this path only
-through Metal dispatches, which cannot run here, and its CPU autograd does not cover attention
-backward. The restatement is instead cross-checked by tests against (1) an independent float64
-torch-autograd model of the same network, and (2) the decode oracle's logits for the forward half
-(which IS pinned against the reference's C code).
+Parity status: PINNED. The reference's own fast_sft.c, compiled unmodified over a CPU stand-in for its
+Metal dispatch layer (oracle/fast_metal_cpu.c -> oracle/_ref/libllmref_fast.so), produced
+tests/golden/sft_golden.npz (tests/golden/make_sft_golden.py): three training steps on the tiny Qwen3
+configuration. tests/test_cpu_pinned_by_reference_engines.py holds this file to those vectors within 1e-5
+(loss, per-position losses, all 4*L gradient buffers of every step, the weights and the adapter file after
+the third). Independent cross-checks remain: a float64 torch-autograd model of the same network, finite
+differences, and the decode oracle's logits for the forward half.
 
 `dtype` selects float32 (as the reference computes) or float64 (to separate rounding from logic).
 A batch of S sequences is handled as S independent passes whose LoRA gradients are averaged; S = 1

@@ -4,11 +4,14 @@ Bars (the north-star's): Q8_0 bytes on the device bit-exact; logits within 1e-2 
 step; greedy tokens identical over the first 32 generated.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
 
 import _oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -118,6 +121,32 @@ def test_tiny_gemma3_matches_oracle(lib, pkg, synth, use_fp16):
     finally:
         lib.inference_state_free(state)
         synth.llmb200_synth_free_gemma3(model)
+
+
+FAST = np.load(os.path.join(ROOT, "tests", "golden", "fast_decode_golden.npz"))
+
+
+@pytest.mark.parametrize("arch", ["tiny-qwen3", "tiny-gemma3"])
+@pytest.mark.parametrize("use_fp16", [0, 1])
+def test_tiny_models_match_the_reference_engine_vectors(lib, pkg, synth, arch, use_fp16):
+    """Tokens and logits the reference's own fast_inference.c produced (tests/golden/make_sft_golden.py)."""
+    gemma = arch.endswith("gemma3")
+    sp = pkg.spec(arch, gamma_jitter=0.1)
+    model = (synth.llmb200_synth_gemma3 if gemma else synth.llmb200_synth_qwen3)(C.byref(sp), 8)
+    state = (lib.inference_state_create_gemma3 if gemma else lib.inference_state_create)(model, int(FAST["max_seq"]), use_fp16)
+    assert state
+    try:
+        tag = f"{arch}_{'f16' if use_fp16 else 'q8'}"
+        prompt = FAST[f"{arch}_prompt"]
+        lib.llmb200_state_set_eos(state, None, 0)
+        got = gpu_generate(lib, pkg, state, prompt, int(FAST["gen_len"]))
+        lg = gpu_logits_trace(lib, state, prompt, sp.vocab_size)[-1]
+        ref = FAST[f"{tag}_logits"]
+        assert np.abs(lg - ref).max() <= 1e-2 * np.abs(ref).max()
+        assert list(got) == list(FAST[f"{tag}_tokens"])
+    finally:
+        lib.inference_state_free(state)
+        (synth.llmb200_synth_free_gemma3 if gemma else synth.llmb200_synth_free_qwen3)(model)
 
 
 def test_generate_semantics(lib, pkg, synth):
@@ -254,9 +283,7 @@ def test_whole_token_kernel_gives_the_same_tokens(lib, pkg, synth, monkeypatch):
 # the kernel configurations the benchmarks run: rows of 2560 / 4096 / 9728 (Q8_0) and 1152 / 1024 / 6912
 # (F16) columns, head_dim 128 and 256, the 151936- and 262144-row LM heads with the arg-max over all blocks.
 # ---------------------------------------------------------------------------------------------------
-import os  # noqa: E402
-
-WIDE = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "wide_golden.npz"))
+WIDE = np.load(os.path.join(ROOT, "tests", "golden", "wide_golden.npz"))
 
 
 def check_wide(lib, pkg, state, tag, vocab):

@@ -392,6 +392,44 @@ def test_engine_tensor_core_path_within_stated_tolerance(pkg):
     eng.close()
 
 
+def test_engine_against_the_reference_engine_vectors(pkg):
+    """Three steps on the tiny configuration against what the reference's own fast_sft.c computed
+    (tests/golden/sft_golden.npz, made by tests/golden/make_sft_golden.py): loss and the clipped gradient
+    buffers of every step, the weights after the third."""
+    import os
+    G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "sft_golden.npz"))
+    cfg = dict(sc.TINY)
+    rank, alpha, lr, n = int(G["rank"]), float(G["alpha"]), float(G["lr"]), int(G["seq_len"])
+    w = sc.make_weights(pkg, cfg)
+    init = sc.make_lora(pkg, cfg, rank)
+    eng = sc.Engine(pkg, cfg, w, init, n, 1, rank, alpha, tensor_cores=False)
+    try:
+        for step in range(3):
+            loss = eng.forward_backward(G["inputs"], G["targets"])
+            assert abs(loss - float(G[f"loss_{step}"])) < 1e-4 * abs(loss), (step, loss)
+            assert sc.rel_err(eng.export(sc.LOSSES, 0, n), G[f"losses_{step}"]) < 1e-4
+            got = eng.grads()
+            norm = np.sqrt(sum(float((got[L][k].astype(np.float64) ** 2).sum()) for L in range(cfg["n_layers"]) for k in o.KEYS))
+            scale = 1.0 / norm if norm > 1.0 else 1.0             # the reference's buffers hold the clipped values
+            for L in range(cfg["n_layers"]):
+                for k in o.KEYS:
+                    want = G[f"grad_{step}_{L}_{k}"]
+                    if not want.any():
+                        assert not got[L][k].any(), (step, L, k)
+                    else:
+                        # free-running: from the second step on the weights carry AdamW's amplified rounding
+                        assert sc.rel_err(got[L][k] * scale, want) < (1e-4 if step == 0 else 2e-3), (step, L, k)
+            eng.L.llmb200_sft_apply_update(eng.h, lr)
+        got_p = eng.params()
+        for L in range(cfg["n_layers"]):
+            for k in o.KEYS:
+                want = G[f"weight_{L}_{k}"]
+                d = got_p[L][k].astype(np.float64) - want
+                assert np.sqrt((d * d).sum() / (want.astype(np.float64) ** 2).sum()) < 1e-3, (L, k)
+    finally:
+        eng.close()
+
+
 def test_saved_activations_and_logits(pkg):
     cfg, n = sc.SMALL, 12
     eng, lora, ow, (x, y) = run_case(pkg, cfg, n, 1, 0.02, False, 1e-4, 1e-4, steps=1)
