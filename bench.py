@@ -71,9 +71,10 @@ def emit(text):
 
 GATEUP_TRAFFIC_BYTES = 53_014_700
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_token_kernel launch, from the ncu capture of a
-# 4-layer cut at position ~520 (profiles/decode_token_qwen3-4b_4layers_full.md): per layer and for the rest
-# (LM head, embedding row). Traffic grows in proportion to the layers; null until such a capture exists.
-TOKEN_TRAFFIC = {"qwen3-4b": None}
+# 4-layer and an 8-layer cut at position ~515 (profiles/decode_token_kernel_qwen3-4b_4and8layer_cuts_full.md):
+# per layer (difference of the two captures / 4) and for the rest (LM head, embedding row, logits). Traffic
+# grows in proportion to the layers.
+TOKEN_TRAFFIC = {"qwen3-4b": {"per_layer": 110.03e6, "rest": 420.6e6}}
 
 
 def measured_peaks():
@@ -918,7 +919,7 @@ def main():
         roofline = {"bound": "hbm", "kernel": "decode_token_kernel<%s> (whole token: %d layers + LM head)" % (wname, sp.n_layers),
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                     "traffic": traffic,
-                    "traffic_source": ("ncu capture of a 4-layer cut, scaled by layers (profiles/)" if traffic else
+                    "traffic_source": ("ncu captures of a 4- and an 8-layer cut, scaled by layers (profiles/)" if traffic else
                                        "none at N > 1 or for cuts: DRAM bytes are only measured on one GPU"),
                     "algorithmic_bytes_per_launch": int(mean_bytes)}
     else:

@@ -83,6 +83,14 @@ int qwen3_generate_fast_batch(llmb200_qwen3_model *model, const uint32_t *prompt
 struct SFTState;
 void inference_state_set_lora(InferenceState *state, struct SFTState *sft);
 
+/* A decode state over the weights an SFT state already holds on the device,
+ * with that state's LoRA attached. F16 weights, one GPU; the frozen matrices
+ * are re-laid for the decode kernels by device-to-device copies (they never
+ * change in LoRA training), the LoRA matrices are read in place. The SFT state
+ * must outlive the decode state. Replaces inference_state_create_from_sft
+ * (src/nn/fast_inference.c:526-608; declared in fast_inference.h:50). */
+InferenceState *inference_state_create_from_sft(struct SFTState *sft, int max_seq_len);
+
 /* ========================= Part 2: additions ============================== */
 
 /* Tensor parallelism. One process per GPU; rank r of `world` holds the r-th

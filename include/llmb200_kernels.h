@@ -289,6 +289,10 @@ typedef struct b200_token_args {
     /* Bytes of the following stage's weights that a block asks L2 for when it starts streaming a stage
      * (0 = none, the default: the ring alone measured faster on Qwen3-4B). */
     int l2_ahead_bytes;
+    /* Iterations one thread per block spends watching an arrival counter before the block polls the flagged
+     * words themselves. 0: no counter wait at all, every thread re-reads its own words until their flags
+     * match. */
+    int counter_spin_limit;
 } b200_token_args;
 
 /* Fills the geometry (g[k].T ... direct_in), n_split limits and the launch shape for `n_blocks` blocks

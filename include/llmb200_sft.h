@@ -4,8 +4,7 @@
  * Part 1 declares, under the reference's names and with the same argument
  * meaning, the LoRA subset of llm.metal's fast SFT engine
  * (src/nn/fast_sft.h:14-111; implementation src/nn/fast_sft.c). Not provided:
- * the Gemma3 and full-parameter constructors, gradient accumulation in F16,
- * and the weight-sharing accessors (sft_get_layers ... sft_get_rope_thetas).
+ * the Gemma3 and full-parameter constructors and gradient accumulation in F16.
  *
  * Part 2 is additive: layer-by-layer construction, several sequences per
  * step (their LoRA gradients are averaged, then one clip + AdamW as in the
@@ -85,6 +84,22 @@ float sft_get_lora_scaling(SFTState *state);
  * attached (the reference attaches them itself through qwen3_attach_lora,
  * which lives outside this library; :1163-1181). Returns silently otherwise. */
 void sft_sync_lora_to_model(SFTState *state, llmb200_qwen3_model *model);
+
+/* Weight-sharing accessors, used by inference_state_create_from_sft
+ * (src/nn/fast_sft.h:101-111; src/nn/fast_sft.c:1346-1354). The containers are
+ * views of this state's device memory: every WMat is one projection as
+ * row-major binary16 [rows, cols] (metal_buf_ptr on its buffer gives the
+ * reference's canonical bytes), every norm vector an fp32 buffer. They stay
+ * valid until sft_state_free and must not be freed by the caller. */
+LayerW *sft_get_layers(SFTState *state);
+WMat *sft_get_lm_head(SFTState *state);
+MetalBuf *sft_get_final_norm_g(SFTState *state);
+ModelType sft_get_model_type(SFTState *state);
+int sft_get_n_q_heads(SFTState *state);
+int sft_get_n_kv_heads(SFTState *state);
+int sft_get_head_dim(SFTState *state);
+int sft_get_intermediate_size(SFTState *state);
+const float *sft_get_rope_thetas(SFTState *state);
 
 /* ========================= Part 2: additions ============================== */
 

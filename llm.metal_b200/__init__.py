@@ -107,6 +107,7 @@ class TokenArgs(C.Structure):
         ("spin_limit", C.c_int),
         ("d_trace", C.c_void_p),
         ("n_blocks", C.c_int), ("smem_bytes", C.c_int), ("scratch_floats", C.c_int), ("att_keys", C.c_int), ("l2_ahead_bytes", C.c_int),
+        ("counter_spin_limit", C.c_int),
     ]
 
 
@@ -143,6 +144,12 @@ class WMat(C.Structure):
     _fields_ = [("mbuf", C.c_void_p), ("rows", C.c_int), ("cols", C.c_int), ("nb", C.c_int)]
 
 
+class LayerW(C.Structure):
+    """LayerW (include/llmb200_wmat.h): seven WMat pointers and six norm buffers."""
+    _fields_ = [(n, C.POINTER(WMat)) for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")] + \
+               [(n, C.c_void_p) for n in ("input_norm_g", "post_attn_norm_g", "pre_ff_norm_g", "post_ff_norm_g", "q_norm_g", "k_norm_g")]
+
+
 class SynthSpec(C.Structure):
     """llmb200_synth_spec (include/llmb200_synth.h)."""
     _fields_ = [("seed", C.c_uint64),
@@ -164,7 +171,7 @@ SYMBOLS_MAIN = {
     "llmb200_inference.h": ["inference_state_create", "inference_state_create_gemma3", "inference_state_free",
                             "inference_generate", "inference_state_model_type", "inference_state_vocab_size",
                             "inference_state_reset", "inference_forward_token", "inference_state_load_eos",
-                            "qwen3_generate_fast", "qwen3_generate_fast_batch", "inference_state_set_lora", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
+                            "qwen3_generate_fast", "qwen3_generate_fast_batch", "inference_state_set_lora", "inference_state_create_from_sft", "llmb200_set_tp", "llmb200_state_comm_handle", "llmb200_state_connect",
                             "llmb200_state_begin", "llmb200_state_load_layer", "llmb200_state_finish",
                             "llmb200_state_set_eos", "llmb200_last_decode_ms", "llmb200_last_prefill_ms",
                             "llmb200_state_error", "llmb200_state_connect_loopback", "llmb200_state_run_device_steps", "llmb200_state_profile_token",
@@ -186,6 +193,8 @@ SYMBOLS_MAIN = {
                       "sft_get_emb_scale", "sft_get_token_emb", "sft_get_step_count", "sft_set_step_count",
                       "sft_get_n_lora_grad_bufs", "sft_get_lora_grad_ptr", "sft_set_lora_grad", "sft_lora_update",
                       "sft_save_lora", "sft_get_lora_weight_buf", "sft_get_lora_scaling", "sft_sync_lora_to_model",
+                      "sft_get_layers", "sft_get_lm_head", "sft_get_final_norm_g", "sft_get_model_type", "sft_get_n_q_heads",
+                      "sft_get_n_kv_heads", "sft_get_head_dim", "sft_get_intermediate_size", "sft_get_rope_thetas",
                       "llmb200_sft_begin", "llmb200_sft_load_layer", "llmb200_sft_finish",
                       "llmb200_sft_forward_backward", "llmb200_sft_apply_update", "llmb200_sft_train_batch",
                       "llmb200_sft_grad_vector", "llmb200_sft_param_vector", "llmb200_sft_last_grad_norm",
@@ -240,6 +249,7 @@ def lib():
         "inference_state_load_eos": (None, [vp, C.c_char_p]),
         "qwen3_generate_fast": (i, [vp, c_u32_p, i, c_u32_p, i, i, i]),
         "inference_state_set_lora": (None, [vp, vp]),
+        "inference_state_create_from_sft": (vp, [vp, i]),
         "qwen3_generate_fast_batch": (i, [vp, c_u32_p, i, c_u32_p, i, i, i]),
         "llmb200_batch_begin": (vp, [C.POINTER(Config), i, i]),
         "llmb200_batch_load_layer": (i, [vp, i, C.POINTER(LayerWeightRef), C.c_float]),
@@ -303,6 +313,9 @@ def lib():
         "sft_set_lora_grad": (None, [vp, i, c_float_p, i]), "sft_lora_update": (None, [vp, fl]),
         "sft_save_lora": (None, [vp, C.c_char_p]), "sft_get_lora_weight_buf": (vp, [vp, i, i]),
         "sft_get_lora_scaling": (fl, [vp]), "sft_sync_lora_to_model": (None, [vp, vp]),
+        "sft_get_layers": (vp, [vp]), "sft_get_lm_head": (vp, [vp]), "sft_get_final_norm_g": (vp, [vp]),
+        "sft_get_model_type": (i, [vp]), "sft_get_n_q_heads": (i, [vp]), "sft_get_n_kv_heads": (i, [vp]),
+        "sft_get_head_dim": (i, [vp]), "sft_get_intermediate_size": (i, [vp]), "sft_get_rope_thetas": (c_float_p, [vp]),
         "llmb200_sft_begin": (vp, [C.POINTER(Config), i, i, i, fl]),
         "llmb200_sft_load_layer": (i, [vp, i, C.POINTER(LayerWeightRef), fl, C.POINTER(c_float_p * 4)]),
         "llmb200_sft_finish": (i, [vp, c_float_p, c_float_p, c_float_p, i]),

@@ -143,6 +143,16 @@ __device__ __forceinline__ Smem smem_of(const b200_token_args &p)
 }
 
 __device__ __forceinline__ int spin_of(const b200_token_args &p) { return p.spin_limit > 0 ? p.spin_limit : TK_SPIN_DEFAULT; }
+// Iteration limit of a wait on an arrival counter: none at all when the readers poll the data directly.
+__device__ __forceinline__ int cspin_of(const b200_token_args &p) { return p.counter_spin_limit; }
+
+// Where element i of a stage's input vector (residual, norm weights, flagged input) lives in shared memory.
+// A consumer thread later pulls 16 consecutive elements (64 bytes) into registers with 16-byte loads; with
+// the elements in natural order the eight lanes of a load phase would hit the same two bank groups (four-way
+// conflict, ~1 us per stage). Exchanging the 16-byte chunks inside each 64-byte group by a pattern that
+// changes every 128 bytes spreads them over all banks. i and swz(i) share their 16-byte chunk offset, so
+// float2/float4 accesses stay whole; the pattern repeats every 128 elements.
+__device__ __forceinline__ int swz(int i) { return i ^ (((i >> 5) & 3) << 2); }
 
 __device__ __forceinline__ unsigned long long global_ns()
 {
@@ -320,8 +330,8 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
             float4 v = *reinterpret_cast<const float4 *>(er + i);
             const float4 g4 = *reinterpret_cast<const float4 *>(norm_gamma + i);
             v.x *= p.emb_scale; v.y *= p.emb_scale; v.z *= p.emb_scale; v.w *= p.emb_scale;
-            *reinterpret_cast<float4 *>(sm.resid + i) = v;
-            *reinterpret_cast<float4 *>(gam + i) = g4;
+            *reinterpret_cast<float4 *>(sm.resid + swz(i)) = v;
+            *reinterpret_cast<float4 *>(gam + swz(i)) = g4;
             ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
         }
     } else {
@@ -336,7 +346,8 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
 #pragma unroll
             for (int u = 0; u < NB; ++u) gq[u] = u < cnt0 ? *reinterpret_cast<const float2 *>(norm_gamma + tid * 2 + u * TK_NC * 2) : make_float2(0, 0);
         }
-        if (tid == 0) { cnt_wait<MULTI>(in_cnt, target, sm.flags, spin); if (trace) trace[8] = global_ns(); }
+        const int cspin = cspin_of(p);
+        if (tid == 0) { cnt_wait<MULTI>(in_cnt, target, sm.flags, cspin); if (trace) trace[8] = global_ns(); }
         named_barrier(1, TK_NC);
         if (trace && tid == 0) trace[9] = global_ns();
 #pragma unroll 1
@@ -358,7 +369,7 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
             }
 #pragma unroll
             for (int u = 0; u < NB; ++u) {
-                const int i = i0 + u * TK_NC * 2;
+                const int i = swz(i0 + u * TK_NC * 2);
                 if (u < cnt) {
                     *reinterpret_cast<float2 *>(gam + i) = gq[u];
                     if (slot_gamma) {
@@ -377,9 +388,10 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
             // the sum of the slots is normalised before it joins the residual (Gemma3's post norms)
             const float inv_s = 1.0f / sqrtf(cons_sum(sq, sm.red, 0, tid) / (float)D + p.eps);
 #pragma unroll 1
-            for (int i = tid * 2; i < D; i += TK_NC * 2) {
-                const float r0 = sm.resid[i] + slot_gamma[i] * sm.scratch[i] * inv_s;
-                const float r1 = sm.resid[i + 1] + slot_gamma[i + 1] * sm.scratch[i + 1] * inv_s;
+            for (int n = tid * 2; n < D; n += TK_NC * 2) {
+                const int i = swz(n);
+                const float r0 = sm.resid[i] + slot_gamma[n] * sm.scratch[i] * inv_s;
+                const float r1 = sm.resid[i + 1] + slot_gamma[n + 1] * sm.scratch[i + 1] * inv_s;
                 sm.resid[i] = r0; sm.resid[i + 1] = r1;
                 ss = fmaf(r0, r0, ss); ss = fmaf(r1, r1, ss);
             }
@@ -402,7 +414,7 @@ __device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind,
     const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
     const b200_flagged *in_vec = kind == B200_ST_O ? p.d_attn_out : p.d_act;
     const unsigned *in_cnt = p.d_counters + (kind == B200_ST_O ? B200_CNT_ATTN : B200_CNT_ACT) * B200_CNT_STRIDE;
-    if (tid == 0) { cnt_wait<false>(in_cnt, cnt_mul * (unsigned)cols, sm.flags, spin); if (trace) trace[8] = global_ns(); }
+    if (tid == 0) { cnt_wait<false>(in_cnt, cnt_mul * (unsigned)cols, sm.flags, cspin_of(p)); if (trace) trace[8] = global_ns(); }
     named_barrier(1, TK_NC);
     if (trace && tid == 0) trace[9] = global_ns();
     constexpr int NB = 4;
@@ -413,12 +425,72 @@ __device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind,
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
             const int i = i0 + u * TK_NC * 2;
-            if (i < cols) *reinterpret_cast<float2 *>(sm.scratch + i) = make_float2(a[u], b[u]);
+            if (i < cols) *reinterpret_cast<float2 *>(sm.scratch + swz(i)) = make_float2(a[u], b[u]);
         }
     }
     if (trace && tid == 0) trace[10] = global_ns();
     named_barrier(1, TK_NC);
     if (trace && tid == 0) trace[11] = global_ns();
+}
+
+// Q8_0 stages multiply in integers: the input vector is rewritten once per stage as block fixed point.
+// Each 16-column slice (what one consumer thread owns) gets a scale s = max|x| / 2^22 and its values
+// X = round(x / s), |X| <= 2^22, split into three signed bytes X = a + 256 b + 65536 c (a, b in
+// [-128, 127], |c| <= 64). A row's share of the slice is then three dp4a sums per four weights, exact in
+// int32, recombined in fp32 -- the rounding of x is 2^-23 of the slice's largest element, below what the
+// fp32 accumulation of the same products loses. One thread converts one slice; the 64-byte record
+// [a0..a3][b0..b3][c0..c3][s, -, -, -] (byte k of word j = element 4j + k, the order of the weight bytes)
+// replaces the slice in scratch[0 .. cols), chunks swizzled like the vector they come from. Normalised
+// stages read residual * norm weight * inv from shared memory; the others convert scratch in place.
+__device__ __forceinline__ void quantize_input(const b200_token_args &p, int kind, float inv)
+{
+    const Smem sm = smem_of(p);
+    const int tid = threadIdx.x, cols = p.g[kind].cols;
+    const bool normed = kind != B200_ST_O && kind != B200_ST_DOWN;
+    const float *xv = normed ? sm.resid : sm.scratch;
+    const float *gam = sm.scratch + p.d_model;
+    uint32_t *rec = reinterpret_cast<uint32_t *>(sm.scratch);
+    // One work item = four consecutive elements (one 16-byte chunk of the vector, one word of each byte
+    // plane); the four items of a slice sit in adjacent lanes and agree on the slice's maximum by two
+    // shuffles. cols is a multiple of 32, so a warp's items are all inside the vector or all outside.
+    // In-place stages: the items of a slice read their chunks before any of them writes (the shuffles
+    // are in between), and no other slice shares those 64 bytes.
+#pragma unroll 1
+    for (int it = tid; it * 4 < ((cols + 127) & ~127); it += TK_NC) {
+        const int e0 = it * 4;
+        const bool on = e0 < cols;
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (on) {
+            v4 = *reinterpret_cast<const float4 *>(xv + swz(e0));
+            if (normed) {
+                const float4 g4 = *reinterpret_cast<const float4 *>(gam + swz(e0));
+                v4.x = g4.x * v4.x * inv; v4.y = g4.y * v4.y * inv; v4.z = g4.z * v4.z * inv; v4.w = g4.w * v4.w * inv;
+            }
+        }
+        float amax = fmaxf(fmaxf(fabsf(v4.x), fabsf(v4.y)), fmaxf(fabsf(v4.z), fabsf(v4.w)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float scale = amax * (1.0f / 4194304.0f);
+        const float rinv = amax > 1e-30f ? 4194304.0f / amax : 0.0f;     // a slice of zeros (or denormals) reads as zero
+        // round to nearest through the 1.5 * 2^23 constant: exact for |X| <= 2^22
+        const int X0 = __float_as_int(fmaf(v4.x, rinv, 12582912.0f)) - 0x4B400000;
+        const int X1 = __float_as_int(fmaf(v4.y, rinv, 12582912.0f)) - 0x4B400000;
+        const int X2 = __float_as_int(fmaf(v4.z, rinv, 12582912.0f)) - 0x4B400000;
+        const int X3 = __float_as_int(fmaf(v4.w, rinv, 12582912.0f)) - 0x4B400000;
+        const int Y0 = (X0 + 128) >> 8, Y1 = (X1 + 128) >> 8, Y2 = (X2 + 128) >> 8, Y3 = (X3 + 128) >> 8;
+        const int Z0 = (Y0 + 128) >> 8, Z1 = (Y1 + 128) >> 8, Z2 = (Y2 + 128) >> 8, Z3 = (Y3 + 128) >> 8;
+        const uint32_t wa = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
+        const uint32_t wb = __byte_perm(__byte_perm(Y0, Y1, 0x0040), __byte_perm(Y2, Y3, 0x0040), 0x5410);
+        const uint32_t wc = __byte_perm(__byte_perm(Z0, Z1, 0x0040), __byte_perm(Z2, Z3, 0x0040), 0x5410);
+        if (on) {
+            const int base = (it >> 2) * 16, j = it & 3;     // the slice's record, this item's word in each plane
+            rec[swz(base + j)] = wa;
+            rec[swz(base + 4 + j)] = wb;
+            rec[swz(base + 8 + j)] = wc;
+            if (j == 0) rec[swz(base + 12)] = __float_as_uint(scale);
+        }
+    }
+    named_barrier(1, TK_NC);
 }
 
 // Rows [w0, w1) of the block: every warp works on every chunk. A thread owns SPT 16-byte column
@@ -441,7 +513,9 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
 
     // ---------------- this thread's slices of the input vector -> registers ----------------
     if (TRACE && trace && tid == 0) trace[14] = (unsigned long long)g + global_ns();
-    float x[SPT][E];
+    float x[WT == B200_WT_Q8 ? 1 : SPT][WT == B200_WT_Q8 ? 1 : E];   // F16 weights: the slices as fp32
+    uint4 xa[SPT], xb[SPT], xc[SPT];                                  // Q8_0 weights: the slices' three byte planes
+    float xs[SPT];                                                    //   and scales (see quantize_input)
     uint32_t qoff[SPT], soff[SPT];
     {
         const bool normed = kind != B200_ST_O && kind != B200_ST_DOWN;
@@ -451,17 +525,29 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
         for (int s = 0; s < SPT; ++s) {
             const int col = (s * T + t) * E;
             const bool on = active && col < G.cols;
+            if (WT == B200_WT_Q8) {
+                const uint32_t *rec = reinterpret_cast<const uint32_t *>(sm.scratch);
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                xa[s] = on ? *reinterpret_cast<const uint4 *>(rec + swz(col)) : z;
+                xb[s] = on ? *reinterpret_cast<const uint4 *>(rec + swz(col + 4)) : z;
+                xc[s] = on ? *reinterpret_cast<const uint4 *>(rec + swz(col + 8)) : z;
+                xs[s] = on ? __uint_as_float(rec[swz(col + 12)]) : 0.0f;
+            } else {
 #pragma unroll
-            for (int e = 0; e < E; e += 4) {
-                float4 v4 = make_float4(0, 0, 0, 0);
-                if (on) {
-                    v4 = *reinterpret_cast<const float4 *>(xv + col + e);
-                    if (normed) {
-                        const float4 g4 = *reinterpret_cast<const float4 *>(gam + col + e);
-                        v4.x = g4.x * v4.x * inv; v4.y = g4.y * v4.y * inv; v4.z = g4.z * v4.z * inv; v4.w = g4.w * v4.w * inv;
+                for (int e = 0; e < E; e += 4) {
+                    float4 v4 = make_float4(0, 0, 0, 0);
+                    if (on) {
+                        v4 = *reinterpret_cast<const float4 *>(xv + swz(col + e));
+                        if (normed) {
+                            const float4 g4 = *reinterpret_cast<const float4 *>(gam + swz(col + e));
+                            v4.x = g4.x * v4.x * inv; v4.y = g4.y * v4.y * inv; v4.z = g4.z * v4.z * inv; v4.w = g4.w * v4.w * inv;
+                        }
                     }
+                    x[WT == B200_WT_Q8 ? 0 : s][WT == B200_WT_Q8 ? 0 : e] = v4.x;
+                    x[WT == B200_WT_Q8 ? 0 : s][WT == B200_WT_Q8 ? 0 : e + 1] = v4.y;
+                    x[WT == B200_WT_Q8 ? 0 : s][WT == B200_WT_Q8 ? 0 : e + 2] = v4.z;
+                    x[WT == B200_WT_Q8 ? 0 : s][WT == B200_WT_Q8 ? 0 : e + 3] = v4.w;
                 }
-                x[s][e] = v4.x; x[s][e + 1] = v4.y; x[s][e + 2] = v4.z; x[s][e + 3] = v4.w;
             }
             // Byte offsets of the slice inside a row. Threads past the end of the row read slice 0 (valid
             // memory) against a zero input slice.
@@ -496,26 +582,31 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
                 if (active) {
                     // rows past the end of a short chunk hold bytes of an earlier chunk: computed, never stored
                     const uint32_t sb = ring_s + slot * TK_SLOT_BYTES + grow;
-                    uint4 wq[RG][SPT];
-                    uint32_t ws[RG][SPT];
+                    // at most four rows' slices in flight per thread (eight cost registers ptxas found on the stack)
+                    constexpr int JB = RG < 4 ? RG : 4;
 #pragma unroll
-                    for (int j = 0; j < RG; ++j)
+                    for (int j0 = 0; j0 < RG; j0 += JB) {
+                        uint4 wq[JB][SPT];
+                        uint32_t ws[JB][SPT];
 #pragma unroll
-                        for (int s = 0; s < SPT; ++s) {
-                            wq[j][s] = lds_128(sb + (uint32_t)j * stride + qoff[s]);
-                            if (WT == B200_WT_Q8) ws[j][s] = lds_u16(sb + (uint32_t)j * stride + soff[s]);
+                        for (int j = 0; j < JB; ++j)
+#pragma unroll
+                            for (int s = 0; s < SPT; ++s) {
+                                wq[j][s] = lds_128(sb + (uint32_t)(j0 + j) * stride + qoff[s]);
+                                if (WT == B200_WT_Q8) ws[j][s] = lds_u16(sb + (uint32_t)(j0 + j) * stride + soff[s]);
+                            }
+#pragma unroll
+                        for (int j = 0; j < JB; ++j) {
+                            float acc = 0.0f;
+#pragma unroll
+                            for (int s = 0; s < SPT; ++s) {
+                                float d;
+                                if (WT == B200_WT_Q8) d = (__half2float(__ushort_as_half((unsigned short)ws[j][s])) * xs[s]) * dot16_q8_planes(wq[j][s], xa[s], xb[s], xc[s]);
+                                else d = dot8_f16(wq[j][s], x[WT == B200_WT_Q8 ? 0 : s]);
+                                acc += d;
+                            }
+                            v[u * RG + j0 + j] = acc;
                         }
-#pragma unroll
-                    for (int j = 0; j < RG; ++j) {
-                        float acc = 0.0f;
-#pragma unroll
-                        for (int s = 0; s < SPT; ++s) {
-                            float d;
-                            if (WT == B200_WT_Q8) d = __half2float(__ushort_as_half((unsigned short)ws[j][s])) * dot16_q8(wq[j][s], x[s]);
-                            else d = dot8_f16(wq[j][s], x[s]);
-                            acc += d;
-                        }
-                        v[u * RG + j] = acc;
                     }
                 }
                 __syncwarp();
@@ -608,6 +699,7 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
     else inv = stage_residual<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
     if (TRACE && trace && tid == 0) trace[12] = global_ns();
     if (kind == B200_ST_LM && !p.with_lm) return state;          // only the residual update that ends a prompt position
+    if (WT == B200_WT_Q8) quantize_input(p, kind, inv);
     unsigned seq = (unsigned)state, win = (unsigned)(state >> 32);
     unsigned long long best = ((unsigned long long)0x7fffffffu << 32) | (unsigned long long)__float_as_uint(-INFINITY);
     const RowRange br = block_rows(G, blockIdx.x);
@@ -661,16 +753,6 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
 // attends over its slice with one online softmax per key lane and leaves (max, sum, output) as a
 // flagged record; block (kv head, split g) then merges all splits of query head g of that KV head.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void halves8_to_float(const uint4 &u, float *f)
-{
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-        f[2 * i] = t.x; f[2 * i + 1] = t.y;
-    }
-}
-
 template <int HD, bool TRACE, bool MULTI>
 __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l, unsigned ep, unsigned long long *trace)
 {
@@ -722,7 +804,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         if (tid == 0) stage_rows(j0, min(j0 + KCH, j1));
 
         // ---- the new rows of this KV head ----
-        if (tid == 0) cnt_wait<false>(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, spin);
+        if (tid == 0) cnt_wait<false>(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, cspin_of(p));
         named_barrier(2, ATT_T);
         {
             // q heads of this KV head are contiguous; its k row and v row follow at their own offsets
@@ -778,6 +860,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             }
         }
         named_barrier(2, ATT_T);
+        if (TRACE && trace && tid == 0) trace[5] = global_ns();
 
         // ---- the keys of this lane, from shared memory: online softmax in registers ----
         float q[DPT], acc[DPT];
@@ -798,16 +881,29 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
 #pragma unroll 1
             for (int it = 0, j = c0 + kl; it < rounds; ++it, j += KL) {
                 const bool valid = j < c1;           // every lane of the warp runs the shuffles; only valid keys count
+                // One unconditional 16-byte load of the staged key and value (row 0 for an idle lane), then a
+                // select against the row of the new position, which is not in the cache yet: three separate
+                // branches filling kf/vf cost registers that ptxas could only find on the stack.
                 float kf[DPT], vf[DPT];
-                if (!valid) {
+                {
+                    const int jj = valid ? j - c0 : 0;
+                    const uint4 ku = *reinterpret_cast<const uint4 *>(ks + (size_t)jj * HD + dl * DPT);
+                    const uint4 vu = *reinterpret_cast<const uint4 *>(vs + (size_t)jj * HD + dl * DPT);
+                    const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+                    const bool fresh = j == pos;
 #pragma unroll
-                    for (int e = 0; e < DPT; ++e) { kf[e] = 0.0f; vf[e] = 0.0f; }
-                } else if (j == pos) {
+                    for (int i = 0; i < 4; ++i) {
+                        const float k0 = __half2float(__ushort_as_half((unsigned short)(kw[i] & 0xffffu)));
+                        const float k1 = __half2float(__ushort_as_half((unsigned short)(kw[i] >> 16)));
+                        const float v0 = __half2float(__ushort_as_half((unsigned short)(vw[i] & 0xffffu)));
+                        const float v1 = __half2float(__ushort_as_half((unsigned short)(vw[i] >> 16)));
+                        kf[2 * i] = fresh ? k_new[dl * DPT + 2 * i] : k0; kf[2 * i + 1] = fresh ? k_new[dl * DPT + 2 * i + 1] : k1;
+                        vf[2 * i] = fresh ? v_new[dl * DPT + 2 * i] : v0; vf[2 * i + 1] = fresh ? v_new[dl * DPT + 2 * i + 1] : v1;
+                    }
+                    if (!valid) {
 #pragma unroll
-                    for (int e = 0; e < DPT; ++e) { kf[e] = k_new[dl * DPT + e]; vf[e] = v_new[dl * DPT + e]; }
-                } else {
-                    halves8_to_float(*reinterpret_cast<const uint4 *>(ks + (size_t)(j - c0) * HD + dl * DPT), kf);
-                    halves8_to_float(*reinterpret_cast<const uint4 *>(vs + (size_t)(j - c0) * HD + dl * DPT), vf);
+                        for (int e = 0; e < DPT; ++e) { kf[e] = 0.0f; vf[e] = 0.0f; }
+                    }
                 }
                 float s = 0.0f;
 #pragma unroll
@@ -826,6 +922,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             }
         }
 
+        if (TRACE && trace && tid == 0) trace[6] = global_ns();
         // ---- merge the key lanes of a head: inside the warp, then across the head's warps ----
 #pragma unroll 1
         for (int o = DLN; o < 32; o <<= 1) {
@@ -845,6 +942,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             if (dl == 0) { dst[HD] = m; dst[HD + 1] = lsum; }
         }
         named_barrier(2, ATT_T);
+        if (TRACE && trace && tid == 0) trace[7] = global_ns();
         // record of (head, split): unnormalised output [HD], running max, sum
         unsigned nst = 0;
 #pragma unroll 1
@@ -877,7 +975,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             const int head = kvh * G + gm;
             const b200_flagged *rec = p.d_attn_part + (size_t)head * p.n_split * (HD + 2);
             if (tid == 0)
-                cnt_wait<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, cnt_mul * (unsigned)(p.n_split * G * (HD + 2)), sm.flags, spin);
+                cnt_wait<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, cnt_mul * (unsigned)(p.n_split * G * (HD + 2)), sm.flags, cspin_of(p));
             named_barrier(2, ATT_T);                 // also: the staging area is free (keys done, previous head merged)
             {
                 constexpr int NB = 4;
@@ -894,22 +992,25 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 }
             }
             named_barrier(2, ATT_T);
+            // One warp turns the (max, sum) pairs of the splits into normalised weights, left where the
+            // maxima were; every output element is then a plain weighted sum over the splits.
+            if (warp == 0) {
+                const bool has = lane < p.n_split;
+                const float ms = stg[(has ? lane : 0) * (HD + 2) + HD];
+                const float ls = has ? stg[lane * (HD + 2) + HD + 1] : 0.0f;
+                const float M = warp_max(ls > 0.0f ? ms : -INFINITY);
+                const float wgt = ls > 0.0f ? expf(ms - M) : 0.0f;
+                const float Lsum = warp_sum(ls * wgt);
+                if (has) stg[lane * (HD + 2) + HD] = wgt / Lsum;
+            }
+            named_barrier(2, ATT_T);
             unsigned nout = 0;
 #pragma unroll 1
             for (int d = tid; d < HD; d += ATT_T) {
-                float M = -INFINITY;
+                float O = 0.0f;
 #pragma unroll 1
-                for (int s = 0; s < p.n_split; ++s)
-                    if (stg[s * (HD + 2) + HD + 1] > 0.0f) M = fmaxf(M, stg[s * (HD + 2) + HD]);
-                float Lsum = 0.0f, O = 0.0f;
-#pragma unroll 1
-                for (int s = 0; s < p.n_split; ++s) {
-                    const float ls = stg[s * (HD + 2) + HD + 1];
-                    const float wgt = ls > 0.0f ? expf(stg[s * (HD + 2) + HD] - M) : 0.0f;
-                    Lsum = fmaf(ls, wgt, Lsum);
-                    O = fmaf(stg[s * (HD + 2) + d], wgt, O);
-                }
-                fl_store<false>(p.d_attn_out + (size_t)head * HD + d, O / Lsum, flag);
+                for (int s = 0; s < p.n_split; ++s) O = fmaf(stg[s * (HD + 2) + d], stg[s * (HD + 2) + HD], O);
+                fl_store<false>(p.d_attn_out + (size_t)head * HD + d, O, flag);
                 ++nout;
             }
             nout = (unsigned)__reduce_add_sync(0xffffffffu, nout);

@@ -81,6 +81,18 @@ __device__ __forceinline__ float dot16_q8(const uint4 &w, const float *x)
     return (a.x + a.y) + (b.x + b.y);
 }
 
+// 16 int8 weights against a 16-element slice of the input held as three signed byte planes
+// (x = scale * (a + 256 b + 65536 c), see quantize_input in decode_token.cu): twelve dp4a, exact in
+// int32 (each sum stays below 2^18), then a + 256 b joined in integers and c joined in fp32.
+__device__ __forceinline__ float dot16_q8_planes(const uint4 &w, const uint4 &a, const uint4 &b, const uint4 &c)
+{
+    int sa = __dp4a((int)w.x, (int)a.x, 0), sb = __dp4a((int)w.x, (int)b.x, 0), sc = __dp4a((int)w.x, (int)c.x, 0);
+    sa = __dp4a((int)w.y, (int)a.y, sa); sb = __dp4a((int)w.y, (int)b.y, sb); sc = __dp4a((int)w.y, (int)c.y, sc);
+    sa = __dp4a((int)w.z, (int)a.z, sa); sb = __dp4a((int)w.z, (int)b.z, sb); sc = __dp4a((int)w.z, (int)c.z, sc);
+    sa = __dp4a((int)w.w, (int)a.w, sa); sb = __dp4a((int)w.w, (int)b.w, sb); sc = __dp4a((int)w.w, (int)c.w, sc);
+    return fmaf((float)sc, 65536.0f, (float)(sa + (sb << 8)));
+}
+
 __device__ __forceinline__ float dot8_f16(const uint4 &w, const float *x)
 {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};

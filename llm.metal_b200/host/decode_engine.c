@@ -32,6 +32,7 @@
 #include "../../include/llmb200_sft.h"
 
 #include <math.h>
+#include <pthread.h>
 #include <stdlib.h>
 #include <string.h>
 #include <sys/stat.h>
@@ -76,6 +77,9 @@ struct InferenceState {
     size_t comm_bytes, off_slots_o, off_slots_dn, off_flags, off_am_val, off_am_idx, off_logits;
     char *peer[B200_MAX_PEERS];
     int connected, loopback;
+    /* single-process tensor parallelism (LLMB200_TP=k): the handle a caller holds is rank 0's state */
+    int group_n, group_dev[B200_MAX_PEERS], local_peers;
+    struct InferenceState *group[B200_MAX_PEERS];
 
     /* host side */
     float *h_logits;
@@ -109,7 +113,8 @@ struct InferenceState {
     int *prof_kind;
 };
 
-static int g_tp_rank = -1, g_tp_size = -1;
+/* per host thread: the ranks of a single-process group are threads */
+static __thread int g_tp_rank = -1, g_tp_size = -1;
 
 int llmb200_set_tp(int rank, int world)
 {
@@ -582,6 +587,11 @@ static int build_plan(InferenceState *s)
     {
         const char *sl = getenv("LLMB200_SPIN_LIMIT");
         a->spin_limit = sl && atoi(sl) > 0 ? atoi(sl) : 0;
+        /* Readers poll the flagged words straight away (measured on Qwen3-4B: 675 tok/s against 639 with one
+         * thread per block watching the arrival counter first); LLMB200_DIRECT_POLL=0 brings the counters back. */
+        const char *dp = getenv("LLMB200_DIRECT_POLL");
+        const int direct = dp ? atoi(dp) > 0 : 1;
+        a->counter_spin_limit = direct ? 0 : (a->spin_limit > 0 ? a->spin_limit : 1 << 20);
     }
     s->tk_planned = 1;
     return 0;
@@ -715,7 +725,7 @@ static void fill_refs_common(LayerWeightRef *r, llmb200_gqa *at, llmb200_linear 
     r->d_model = D; r->head_dim = hd;
 }
 
-InferenceState *inference_state_create(llmb200_qwen3_model *m, int max_seq_len, int use_fp16)
+static InferenceState *create_qwen3_one(llmb200_qwen3_model *m, int max_seq_len, int use_fp16)
 {
     if (!m) return NULL;
     llmb200_config c = {MODEL_QWEN3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
@@ -743,7 +753,7 @@ InferenceState *inference_state_create(llmb200_qwen3_model *m, int max_seq_len, 
     return s;
 }
 
-InferenceState *inference_state_create_gemma3(llmb200_gemma3_model *m, int max_seq_len, int use_fp16)
+static InferenceState *create_gemma3_one(llmb200_gemma3_model *m, int max_seq_len, int use_fp16)
 {
     if (!m) return NULL;
     llmb200_config c = {MODEL_GEMMA3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
@@ -778,6 +788,95 @@ InferenceState *inference_state_create_gemma3(llmb200_gemma3_model *m, int max_s
 /* Attaches the SFT state's LoRA matrices (Q and V projections) to the decode step; the adapter is read in
  * place, so later training steps are seen by later tokens. Replaces inference_state_set_lora
  * (src/nn/fast_inference.c:496-520). One GPU only: with tensor parallelism the call is refused. */
+/* One F16 projection of the SFT state (binary16 [rows, ld] row-major on the device, as sft_get_layers hands it
+ * out) into packed rows dst_row0 + r*dst_row_step: the packed F16 layout is row-major binary16 with a padded
+ * stride, so this is a strided device-to-device copy. */
+static int share_rows(const WMat *w, int col0, int cols, PackedMat *dst, int dst_row0, int dst_row_step)
+{
+    if (!w || !w->mbuf || !w->mbuf->dev) return B200_E_BADARG;
+    CU_TRY(cudaMemcpy2DAsync((char *)dst->w + (size_t)dst_row0 * dst->stride, (size_t)dst->stride * dst_row_step,
+                             (const char *)w->mbuf->dev + (size_t)col0 * 2, (size_t)w->cols * 2, (size_t)cols * 2,
+                             (size_t)w->rows, cudaMemcpyDeviceToDevice, g_rt.stream), return -1);
+    return 0;
+}
+
+static float *clone_f32(const void *d_src, size_t n)
+{
+    float *p = NULL;
+    CU_TRY(cudaMalloc((void **)&p, n * 4), return NULL);
+    CU_TRY(cudaMemcpyAsync(p, d_src, n * 4, cudaMemcpyDeviceToDevice, g_rt.stream), { cudaFree(p); return NULL; });
+    return p;
+}
+
+/* A decode state over the weights an SFT state already holds on the device, with that state's LoRA attached
+ * (read in place, so decoding follows training). The frozen matrices are re-laid for the decode kernels by
+ * device-to-device copies -- no host round trip, no second conversion; they never change in LoRA training, so
+ * a copy and the reference's aliasing behave the same. F16 weights, one GPU. max_seq_len above 4096 is
+ * clamped. Replaces inference_state_create_from_sft (src/nn/fast_inference.c:526-608; fast_inference.h:50). */
+InferenceState *inference_state_create_from_sft(SFTState *sft, int max_seq_len)
+{
+    if (!sft) return NULL;
+    LayerW *lw = sft_get_layers(sft);
+    WMat *lm = sft_get_lm_head(sft);
+    MetalBuf *fg = sft_get_final_norm_g(sft);
+    const float *thetas = sft_get_rope_thetas(sft);
+    const float *d_emb = llmb200_sft_device_emb(sft);
+    if (!lw || !lm || !fg || !thetas || !d_emb) {
+        fprintf(stderr, "[FastGen] the SFT state is not complete\n");
+        return NULL;
+    }
+    llmb200_config c = { sft_get_model_type(sft), sft_get_d_model(sft), sft_get_n_q_heads(sft), sft_get_n_kv_heads(sft),
+                         sft_get_head_dim(sft), sft_get_intermediate_size(sft), sft_get_vocab_size(sft), sft_get_n_layers(sft),
+                         max_seq_len, 1 };
+    InferenceState *s = llmb200_state_begin(&c);
+    if (!s) return NULL;
+    if (s->tp_size != 1) {
+        fprintf(stderr, "[FastGen] sharing weights with an SFT state needs one GPU (tensor parallelism is %d)\n", s->tp_size);
+        inference_state_free(s);
+        return NULL;
+    }
+    const int D = s->D, hd = s->hd, ql = s->Hq * hd, kl = s->Hkv * hd;
+    int rc = 0;
+    for (int i = 0; i < s->L && !rc; ++i) {
+        Layer *ly = &s->layers[i];
+        const LayerW *r = &lw[i];
+        rc |= share_rows(r->q_proj, 0, D, &ly->qkv, 0, 1);
+        rc |= share_rows(r->k_proj, 0, D, &ly->qkv, ql, 1);
+        rc |= share_rows(r->v_proj, 0, D, &ly->qkv, ql + kl, 1);
+        rc |= share_rows(r->o_proj, 0, ql, &ly->o, 0, 1);
+        rc |= share_rows(r->gate_proj, 0, D, &ly->gateup, 0, 2);
+        rc |= share_rows(r->up_proj, 0, D, &ly->gateup, 1, 2);
+        rc |= share_rows(r->down_proj, 0, s->IS, &ly->down, 0, 1);
+        ly->g_input = clone_f32(r->input_norm_g->dev, (size_t)D);
+        ly->g_post_attn = clone_f32(r->post_attn_norm_g->dev, (size_t)D);
+        ly->g_qn = r->q_norm_g ? clone_f32(r->q_norm_g->dev, (size_t)hd) : NULL;
+        ly->g_kn = r->k_norm_g ? clone_f32(r->k_norm_g->dev, (size_t)hd) : NULL;
+        float *f = malloc((size_t)(hd / 2) * sizeof(float));
+        if (!f || !ly->g_input || !ly->g_post_attn) { free(f); rc = -1; break; }
+        for (int d = 0; d < hd / 2; ++d) f[d] = 1.0f / powf(thetas[i], (float)(2 * d) / (float)hd);
+        ly->inv_freq = llmb200_upload_f32(f, (size_t)(hd / 2));
+        free(f);
+        if (!ly->inv_freq) rc = -1;
+        ly->loaded = 1;
+    }
+    if (!rc) rc = share_rows(lm, 0, D, &s->lm, 0, 1);
+    if (!rc) {
+        s->g_final = clone_f32(fg->dev, (size_t)D);
+        s->emb = clone_f32(d_emb, (size_t)s->V * D);
+        if (!s->g_final || !s->emb) rc = -1;
+    }
+    if (!rc && cudaStreamSynchronize(g_rt.stream) != cudaSuccess) rc = -1;
+    if (rc) {
+        fprintf(stderr, "[FastGen] taking over the SFT state's weights failed\n");
+        inference_state_free(s);
+        return NULL;
+    }
+    s->finished = 1;
+    inference_state_set_lora(s, sft);
+    fprintf(stderr, "[FastGen] Created from SFT (weights taken over on the device, no host upload)\n");
+    return s;
+}
+
 void inference_state_set_lora(InferenceState *s, SFTState *sft)
 {
     if (!s || !sft) return;
@@ -807,7 +906,7 @@ void inference_state_set_lora(InferenceState *s, SFTState *sft)
     free_graphs(s);                      /* the per-token graph gains one kernel per layer */
 }
 
-void inference_state_free(InferenceState *s)
+static void free_one(InferenceState *s)
 {
     if (!s) return;
     if (g_rt.refs > 0) cudaStreamSynchronize(g_rt.stream);
@@ -831,7 +930,7 @@ void inference_state_free(InferenceState *s)
     cudaFree(s->attn_scratch); cudaFree(s->am_scratch); cudaFree(s->attn_tickets); cudaFree(s->mv_ticket);
     cudaFree(s->d_pos);
     for (int p = 0; p < s->tp_size; ++p)
-        if (p != s->tp_rank && s->peer[p] && !s->loopback) cudaIpcCloseMemHandle(s->peer[p]);
+        if (p != s->tp_rank && s->peer[p] && !s->loopback && !s->local_peers) cudaIpcCloseMemHandle(s->peer[p]);
     cudaFree(s->comm);
     if (s->h_logits) cudaFreeHost(s->h_logits);
     if (s->h_tok) cudaFreeHost(s->h_tok);
@@ -849,7 +948,12 @@ void inference_state_free(InferenceState *s)
 
 ModelType inference_state_model_type(InferenceState *s) { return s->mt; }
 int inference_state_vocab_size(InferenceState *s) { return s->V; }
-void inference_state_reset(InferenceState *s) { s->cur_len = 0; }
+void inference_state_reset(InferenceState *s)
+{
+    if (!s) return;
+    s->cur_len = 0;
+    for (int r = 1; r < s->group_n; ++r) s->group[r]->cur_len = 0;
+}
 int llmb200_state_position(InferenceState *s) { return s ? s->cur_len : -1; }
 int llmb200_state_graph_kernels(InferenceState *s, int with_lm_head)
 {
@@ -878,6 +982,7 @@ void llmb200_state_set_eos(InferenceState *s, const int *eos, int n)
     if (n > 4) n = 4;
     for (int i = 0; i < n; ++i) s->eos[i] = eos[i];
     s->n_eos = n;
+    for (int r = 1; r < s->group_n; ++r) llmb200_state_set_eos(s->group[r], eos, n);
 }
 
 int llmb200_state_error(InferenceState *s)
@@ -885,6 +990,7 @@ int llmb200_state_error(InferenceState *s)
     if (!s) return 1;
     int err = 0;
     if (cudaMemcpy(&err, s->d_err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 1;
+    for (int r = 1; r < s->group_n && !err; ++r) err = llmb200_state_error(s->group[r]);
     return err;
 }
 
@@ -912,7 +1018,7 @@ static int set_control(InferenceState *s, int pos, int prompt_len, const uint32_
     return 0;
 }
 
-const float *inference_forward_token(InferenceState *s, int token)
+static const float *forward_token_one(InferenceState *s, int token)
 {
     if (!s || ensure_graphs(s) != 0) return NULL;
     if (s->cur_len >= s->max_seq) { fprintf(stderr, "[FastGen] KV cache is full (%d positions)\n", s->max_seq); return NULL; }
@@ -942,7 +1048,7 @@ static int is_eos(const InferenceState *s, int tok)
     return 0;
 }
 
-int inference_generate(InferenceState *s, const uint32_t *prompt, int prompt_len, uint32_t *out, int max_gen_len)
+static int generate_one(InferenceState *s, const uint32_t *prompt, int prompt_len, uint32_t *out, int max_gen_len)
 {
     if (!s || !prompt || !out || prompt_len <= 0 || max_gen_len <= 0) return 0;
     if (ensure_graphs(s) != 0) return 0;
@@ -1009,6 +1115,210 @@ int inference_generate(InferenceState *s, const uint32_t *prompt, int prompt_len
                 s->last_decode_ms, s->last_n_decoded * 1000.0 / s->last_decode_ms, s->last_decode_ms / s->last_n_decoded);
     if (llmb200_state_error(s)) fprintf(stderr, "[FastGen] a device-side wait timed out; results are invalid\n");
     return n_gen;
+}
+
+/* ------------------------------------------------------------ single-process tensor parallelism
+ *
+ * LLMB200_TP=k (2, 4 or 8) makes the reference's own calls -- inference_state_create, inference_generate,
+ * inference_forward_token, ... -- run k-way tensor parallel inside the calling process: one host thread per
+ * GPU (the caller's thread drives rank 0 on its current device, devices dev+1 .. dev+k-1 hold the other
+ * ranks), each with its own state, stream and upload staging, exactly the states a one-process-per-GPU
+ * launch builds. The exchange regions are plain peer pointers (cudaDeviceEnablePeerAccess) instead of IPC
+ * mappings. Every rank runs the same host loop on the same prompt and meets the others on the device. */
+
+enum { G_CREATE_QWEN3, G_CREATE_GEMMA3, G_GENERATE, G_FORWARD, G_FREE };
+
+typedef struct {
+    int op, rank, world, dev, rc;
+    InferenceState *s, **all;
+    void *model;
+    int max_seq, use_fp16, token;
+    const uint32_t *prompt;
+    uint32_t *out;
+    int prompt_len, max_gen;
+    const float *logits;
+    pthread_barrier_t *bar;
+} GroupJob;
+
+static int single_process_tp(void)
+{
+    if (g_tp_size > 0 || getenv("LLMB200_TP_SIZE")) return 1;      /* one process per GPU: the caller places the ranks */
+    const char *e = getenv("LLMB200_TP");
+    const int k = e ? atoi(e) : 1;
+    return (k == 2 || k == 4 || k == 8) ? k : 1;
+}
+
+static void *group_thread(void *arg)
+{
+    GroupJob *j = arg;
+    j->rc = -1;
+    if (cudaSetDevice(j->dev) != cudaSuccess) {
+        fprintf(stderr, "[FastGen] rank %d: cannot use device %d\n", j->rank, j->dev);
+        if (j->op <= G_CREATE_GEMMA3) { pthread_barrier_wait(j->bar); pthread_barrier_wait(j->bar); }
+        return NULL;
+    }
+    switch (j->op) {
+    case G_CREATE_QWEN3:
+    case G_CREATE_GEMMA3: {
+        g_tp_rank = j->rank; g_tp_size = j->world;
+        InferenceState *s = j->op == G_CREATE_QWEN3 ? create_qwen3_one(j->model, j->max_seq, j->use_fp16)
+                                                     : create_gemma3_one(j->model, j->max_seq, j->use_fp16);
+        g_tp_rank = -1; g_tp_size = -1;
+        j->all[j->rank] = s;
+        pthread_barrier_wait(j->bar);                    /* every rank has built (or failed to build) its state */
+        int ok = 1;
+        for (int r = 0; r < j->world; ++r) if (!j->all[r]) ok = 0;
+        if (ok) {
+            for (int r = 0; r < j->world && ok; ++r) {
+                if (r == j->rank) continue;
+                int dev_r = 0;
+                struct cudaPointerAttributes at;
+                if (cudaPointerGetAttributes(&at, j->all[r]->comm) != cudaSuccess) { ok = 0; break; }
+                dev_r = at.device;
+                cudaError_t e = cudaDeviceEnablePeerAccess(dev_r, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) { (void)cudaGetLastError(); e = cudaSuccess; }
+                if (e != cudaSuccess) {
+                    fprintf(stderr, "[FastGen] no peer access from device %d to device %d: %s\n", j->dev, dev_r, cudaGetErrorString(e));
+                    ok = 0;
+                    break;
+                }
+                s->peer[r] = j->all[r]->comm;
+            }
+            if (ok) { s->local_peers = 1; s->connected = 1; free_graphs(s); j->rc = 0; }
+        }
+        pthread_barrier_wait(j->bar);                    /* nobody launches before everybody is connected */
+        j->s = s;
+        break;
+    }
+    case G_GENERATE:
+        j->rc = generate_one(j->s, j->prompt, j->prompt_len, j->out, j->max_gen);
+        break;
+    case G_FORWARD:
+        j->logits = forward_token_one(j->s, j->token);
+        j->rc = j->logits ? 0 : -1;
+        break;
+    case G_FREE:
+        free_one(j->s);
+        j->rc = 0;
+        break;
+    }
+    return NULL;
+}
+
+/* Runs jobs[0] on the caller's thread and jobs[1..k-1] on one thread each; the caller's device is restored. */
+static void group_run(GroupJob *jobs, int k)
+{
+    pthread_t th[B200_MAX_PEERS];
+    int started[B200_MAX_PEERS] = {0};
+    int dev0 = 0;
+    cudaGetDevice(&dev0);
+    for (int r = 1; r < k; ++r) started[r] = pthread_create(&th[r], NULL, group_thread, &jobs[r]) == 0;
+    group_thread(&jobs[0]);
+    for (int r = 1; r < k; ++r) {
+        if (started[r]) pthread_join(th[r], NULL);
+        else {
+            /* a rank without a thread would leave the others waiting: run it here (slow, but nothing hangs) */
+            group_thread(&jobs[r]);
+        }
+    }
+    cudaSetDevice(dev0);
+}
+
+static InferenceState *group_create(int op, void *model, int max_seq_len, int use_fp16, int k)
+{
+    int dev0 = 0, n_dev = 0;
+    if (cudaGetDevice(&dev0) != cudaSuccess || cudaGetDeviceCount(&n_dev) != cudaSuccess || dev0 + k > n_dev) {
+        fprintf(stderr, "[FastGen] LLMB200_TP=%d needs devices %d..%d; %d visible\n", k, dev0, dev0 + k - 1, n_dev);
+        (void)cudaGetLastError();
+        return NULL;
+    }
+    InferenceState *all[B200_MAX_PEERS] = {0};
+    GroupJob jobs[B200_MAX_PEERS];
+    pthread_barrier_t bar;
+    if (pthread_barrier_init(&bar, NULL, (unsigned)k) != 0) return NULL;
+    memset(jobs, 0, sizeof(jobs));
+    for (int r = 0; r < k; ++r)
+        jobs[r] = (GroupJob){ .op = op, .rank = r, .world = k, .dev = dev0 + r, .all = all, .model = model,
+                              .max_seq = max_seq_len, .use_fp16 = use_fp16, .bar = &bar };
+    group_run(jobs, k);
+    pthread_barrier_destroy(&bar);
+    int ok = 1;
+    for (int r = 0; r < k; ++r) if (!all[r] || jobs[r].rc != 0) ok = 0;
+    if (!ok) {
+        for (int r = 0; r < k; ++r)
+            if (all[r]) { cudaSetDevice(dev0 + r); free_one(all[r]); }
+        cudaSetDevice(dev0);
+        fprintf(stderr, "[FastGen] building the %d-way tensor-parallel state failed\n", k);
+        return NULL;
+    }
+    InferenceState *g = all[0];
+    g->group_n = k;
+    for (int r = 0; r < k; ++r) { g->group[r] = all[r]; g->group_dev[r] = dev0 + r; }
+    fprintf(stderr, "[FastGen] %d-way tensor parallel on devices %d..%d, one host thread each\n", k, dev0, dev0 + k - 1);
+    return g;
+}
+
+InferenceState *inference_state_create(llmb200_qwen3_model *m, int max_seq_len, int use_fp16)
+{
+    const int k = single_process_tp();
+    if (m && k > 1) return group_create(G_CREATE_QWEN3, m, max_seq_len, use_fp16, k);
+    return create_qwen3_one(m, max_seq_len, use_fp16);
+}
+
+InferenceState *inference_state_create_gemma3(llmb200_gemma3_model *m, int max_seq_len, int use_fp16)
+{
+    const int k = single_process_tp();
+    if (m && k > 1) return group_create(G_CREATE_GEMMA3, m, max_seq_len, use_fp16, k);
+    return create_gemma3_one(m, max_seq_len, use_fp16);
+}
+
+void inference_state_free(InferenceState *s)
+{
+    if (!s) return;
+    if (s->group_n <= 1) { free_one(s); return; }
+    const int k = s->group_n;
+    GroupJob jobs[B200_MAX_PEERS];
+    memset(jobs, 0, sizeof(jobs));
+    for (int r = 0; r < k; ++r) jobs[r] = (GroupJob){ .op = G_FREE, .rank = r, .world = k, .dev = s->group_dev[r], .s = s->group[r] };
+    group_run(jobs, k);
+}
+
+const float *inference_forward_token(InferenceState *s, int token)
+{
+    if (!s || s->group_n <= 1) return forward_token_one(s, token);
+    const int k = s->group_n;
+    GroupJob jobs[B200_MAX_PEERS];
+    memset(jobs, 0, sizeof(jobs));
+    for (int r = 0; r < k; ++r)
+        jobs[r] = (GroupJob){ .op = G_FORWARD, .rank = r, .world = k, .dev = s->group_dev[r], .s = s->group[r], .token = token };
+    group_run(jobs, k);
+    for (int r = 0; r < k; ++r) if (jobs[r].rc != 0) return NULL;
+    return jobs[0].logits;
+}
+
+int inference_generate(InferenceState *s, const uint32_t *prompt, int prompt_len, uint32_t *out, int max_gen_len)
+{
+    if (!s || s->group_n <= 1) return generate_one(s, prompt, prompt_len, out, max_gen_len);
+    if (!prompt || !out || prompt_len <= 0 || max_gen_len <= 0) return 0;
+    const int k = s->group_n;
+    GroupJob jobs[B200_MAX_PEERS];
+    uint32_t *tmp = malloc((size_t)(k - 1) * (size_t)max_gen_len * sizeof(uint32_t));
+    if (!tmp) return 0;
+    memset(jobs, 0, sizeof(jobs));
+    for (int r = 0; r < k; ++r)
+        jobs[r] = (GroupJob){ .op = G_GENERATE, .rank = r, .world = k, .dev = s->group_dev[r], .s = s->group[r], .prompt = prompt,
+                              .prompt_len = prompt_len, .out = r == 0 ? out : tmp + (size_t)(r - 1) * max_gen_len,
+                              .max_gen = max_gen_len };
+    group_run(jobs, k);
+    int n = jobs[0].rc;
+    /* every rank folds the same arg-max: a rank that disagrees means the exchange went wrong */
+    for (int r = 1; r < k; ++r)
+        if (jobs[r].rc != n || memcmp(jobs[r].out, out, (size_t)(n > 0 ? n : 0) * sizeof(uint32_t)) != 0) {
+            fprintf(stderr, "[FastGen] rank %d generated different tokens than rank 0; results are invalid\n", r);
+            n = 0;
+        }
+    free(tmp);
+    return n;
 }
 
 int qwen3_generate_fast(llmb200_qwen3_model *model, const uint32_t *prompt, int prompt_len, uint32_t *out,
@@ -1092,6 +1402,7 @@ void inference_state_load_eos(InferenceState *s, const char *model_path)
     fprintf(stderr, "[FastGen] EOS tokens (%d):", s->n_eos);
     for (int i = 0; i < s->n_eos; ++i) fprintf(stderr, " %d", s->eos[i]);
     fprintf(stderr, "\n");
+    for (int r = 1; r < s->group_n; ++r) llmb200_state_set_eos(s->group[r], s->eos, s->n_eos);
 }
 
 /* ------------------------------------------------------------ measurement */

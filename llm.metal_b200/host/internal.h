@@ -35,7 +35,17 @@ typedef struct {
     int stage_next;
 } llmb200_runtime;
 
-extern llmb200_runtime g_rt;
+/* One runtime (stream + staging buffers) per CUDA device. A host thread works with the runtime of its
+ * current device, so several devices can be driven from one process -- one thread each. */
+#define LLMB200_MAX_DEVICES 16
+extern llmb200_runtime g_rts[LLMB200_MAX_DEVICES];
+static inline llmb200_runtime *llmb200_rt(void)
+{
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= LLMB200_MAX_DEVICES) { (void)cudaGetLastError(); d = 0; }
+    return &g_rts[d];
+}
+#define g_rt (*llmb200_rt())
 
 #define CU_TRY(call, onfail)                                                          \
     do {                                                                              \
@@ -74,5 +84,9 @@ int llmb200_upload_f16_into(void *d_dst, const float *src, size_t n);
 /* A MetalBuf handle over device memory the caller keeps owning. metal_buf_ptr
  * on it returns a host copy refreshed by every call. */
 MetalBuf *llmb200_buf_wrap(void *dev, size_t size);
+
+/* The embedding table of an SFT state on the device (decode states built from it copy it). */
+struct SFTState;
+const float *llmb200_sft_device_emb(struct SFTState *s);
 
 #endif

@@ -87,6 +87,11 @@ struct SFTState {
     float *h_loss;              /* pinned [M + 1] */
     MetalBuf *mb_logits, *mb_dlogits;
 
+    /* views handed out by the weight-sharing accessors, made on first use */
+    LayerW *share_layers;
+    WMat *share_lm;
+    MetalBuf *share_final_g;
+
     cudaEvent_t ev[4];
     float last_step_ms, last_update_ms, last_norm;
 };
@@ -508,6 +513,108 @@ SFTState *sft_state_create(llmb200_qwen3_model *m, int seq_len, int lora_rank, f
     return s;
 }
 
+/* ---------------------------------------------------------------- weight sharing (src/nn/fast_sft.h:101-111) */
+
+/* A WMat over `rows` rows of binary16 [., cols] device memory. The tensor-core mode keeps its frozen
+ * matrices in exactly that form, so the view borrows them; the CUDA-core mode keeps fp32 copies of the
+ * binary16 values, which are narrowed (losslessly) into memory the view owns. */
+static WMat *share_view(SFTState *s, const SftMat *m, int row0, int rows)
+{
+    WMat *w = calloc(1, sizeof(WMat));
+    MetalBuf *b = calloc(1, sizeof(MetalBuf));
+    if (!w || !b) { free(w); free(b); return NULL; }
+    const size_t n = (size_t)rows * m->cols;
+    b->kind = MB_F16; b->rows = rows; b->cols = m->cols; b->row_stride = (long long)m->cols * 2; b->size = n * 2;
+    if (m->wh) {
+        b->dev = (char *)m->wh + (size_t)row0 * m->cols * 2;
+        b->borrowed = 1;
+    } else {
+        if (cudaMalloc(&b->dev, n * 2) != cudaSuccess ||
+            b200_f32_to_f16(m->w + (size_t)row0 * m->cols, n, 1.0f, b->dev, g_rt.stream) != 0) {
+            if (b->dev) cudaFree(b->dev);
+            free(w); free(b);
+            return NULL;
+        }
+    }
+    w->mbuf = b; w->rows = rows; w->cols = m->cols; w->nb = 0;
+    return w;
+}
+
+static void share_free(SFTState *s)
+{
+    if (s->share_layers) {
+        for (int L = 0; L < s->NL; ++L) {
+            LayerW *lw = &s->share_layers[L];
+            WMat *ws[] = { lw->q_proj, lw->k_proj, lw->v_proj, lw->o_proj, lw->gate_proj, lw->up_proj, lw->down_proj };
+            for (int i = 0; i < 7; ++i) if (ws[i]) { metal_buf_free(ws[i]->mbuf); free(ws[i]); }
+            MetalBuf *gs[] = { lw->input_norm_g, lw->post_attn_norm_g, lw->q_norm_g, lw->k_norm_g };
+            for (int i = 0; i < 4; ++i) metal_buf_free(gs[i]);
+        }
+        free(s->share_layers);
+        s->share_layers = NULL;
+    }
+    if (s->share_lm) { metal_buf_free(s->share_lm->mbuf); free(s->share_lm); s->share_lm = NULL; }
+    metal_buf_free(s->share_final_g);
+    s->share_final_g = NULL;
+}
+
+/* The frozen base as the reference's containers: one WMat per projection (binary16 [rows, cols], row-major)
+ * and one buffer per norm vector, all views of this state's device memory; valid until sft_state_free.
+ * Replaces sft_get_layers (src/nn/fast_sft.c:1346; declared in fast_sft.h:103). */
+LayerW *sft_get_layers(SFTState *s)
+{
+    if (!s || !s->finished) return NULL;
+    if (s->share_layers) return s->share_layers;
+    LayerW *out = calloc((size_t)s->NL, sizeof(LayerW));
+    if (!out) return NULL;
+    s->share_layers = out;
+    for (int L = 0; L < s->NL; ++L) {
+        SftLayer *l = &s->layers[L];
+        LayerW *lw = &out[L];
+        lw->q_proj = share_view(s, &l->qkv, 0, s->Hq_hd);
+        lw->k_proj = share_view(s, &l->qkv, s->Hq_hd, s->Hkv_hd);
+        lw->v_proj = share_view(s, &l->qkv, s->Hq_hd + s->Hkv_hd, s->Hkv_hd);
+        lw->o_proj = share_view(s, &l->o, 0, s->D);
+        lw->gate_proj = share_view(s, &l->gu, 0, s->IS);
+        lw->up_proj = share_view(s, &l->gu, s->IS, s->IS);
+        lw->down_proj = share_view(s, &l->down, 0, s->D);
+        lw->input_norm_g = llmb200_buf_wrap(l->g_in, (size_t)s->D * 4);
+        lw->post_attn_norm_g = llmb200_buf_wrap(l->g_post, (size_t)s->D * 4);
+        lw->q_norm_g = llmb200_buf_wrap(l->g_q, (size_t)s->hd * 4);
+        lw->k_norm_g = llmb200_buf_wrap(l->g_k, (size_t)s->hd * 4);
+        if (!lw->q_proj || !lw->k_proj || !lw->v_proj || !lw->o_proj || !lw->gate_proj || !lw->up_proj || !lw->down_proj ||
+            !lw->input_norm_g || !lw->post_attn_norm_g || !lw->q_norm_g || !lw->k_norm_g) {
+            share_free(s);
+            return NULL;
+        }
+    }
+    metal_flush();
+    return out;
+}
+
+WMat *sft_get_lm_head(SFTState *s)                                  /* src/nn/fast_sft.c:1347 */
+{
+    if (!s || !s->finished) return NULL;
+    if (!s->share_lm) { s->share_lm = share_view(s, &s->lm_head, 0, s->V); metal_flush(); }
+    return s->share_lm;
+}
+
+MetalBuf *sft_get_final_norm_g(SFTState *s)                         /* :1348 */
+{
+    if (!s || !s->finished) return NULL;
+    if (!s->share_final_g) s->share_final_g = llmb200_buf_wrap(s->final_g, (size_t)s->D * 4);
+    return s->share_final_g;
+}
+
+ModelType sft_get_model_type(SFTState *s) { return s ? (ModelType)s->model_type : MODEL_QWEN3; }   /* :1349 */
+int sft_get_n_q_heads(SFTState *s) { return s ? s->Hq : 0; }                                      /* :1350 */
+int sft_get_n_kv_heads(SFTState *s) { return s ? s->Hkv : 0; }
+int sft_get_head_dim(SFTState *s) { return s ? s->hd : 0; }
+int sft_get_intermediate_size(SFTState *s) { return s ? s->IS : 0; }
+const float *sft_get_rope_thetas(SFTState *s) { return s ? s->rope_thetas : NULL; }               /* :1354 */
+/* The embedding table on the device (the reference hands out its host copy through sft_get_token_emb). */
+const float *llmb200_sft_device_emb(SFTState *s) { return s ? s->d_emb : NULL; }
+
 void sft_state_free(SFTState *s)
 {
     if (!s) return;
@@ -528,6 +635,7 @@ void sft_state_free(SFTState *s)
     for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
     cudaFreeHost(s->h_grad); cudaFreeHost(s->h_tok); cudaFreeHost(s->h_loss);
     metal_buf_free(s->mb_logits); metal_buf_free(s->mb_dlogits);
+    share_free(s);
     for (int i = 0; i < 4; ++i) if (s->ev[i]) cudaEventDestroy(s->ev[i]);
     free(s->token_emb_host);
     free(s->rope_thetas);

@@ -15,7 +15,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-llmb200_runtime g_rt = {0};
+llmb200_runtime g_rts[LLMB200_MAX_DEVICES] = {{0}};
 
 int fast_metal_init(void)
 {

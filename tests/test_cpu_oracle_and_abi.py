@@ -214,3 +214,22 @@ def test_product_never_touches_the_oracle():
                 if re.search(r"oracle/|liboracle|_oracle|libllmref|_work/", open(os.path.join(base, f), errors="ignore").read()):
                     bad.append(f)
     assert not bad
+
+
+# ---------------------------------------------------------------- the drop-in program
+
+DROP_IN = os.path.join(ROOT, "tests", "c_api", "_bin", "drop_in")
+
+
+@pytest.mark.skipif(not os.path.exists(DROP_IN), reason="tests/c_api/_bin/drop_in was not built (reference tree absent)")
+def test_drop_in_program_links_and_fails_loudly_without_a_gpu():
+    """tests/c_api/drop_in.c includes the reference's own headers and links against libllmb200.so: every
+    engine symbol it uses resolved at build time. Without a CUDA device it must stop at the first engine
+    call with the library's message -- there is no CPU path to fall back to."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the GPU suite runs the program for real")
+    r = subprocess.run([DROP_IN], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert r.returncode == 3, (r.returncode, r.stderr[-500:])
+    assert "no CUDA device available" in r.stderr and "no CPU path" in r.stderr
+    assert "DROP_IN ok" not in r.stdout

@@ -96,3 +96,35 @@ def test_plan_refuses_what_the_kernel_cannot_run(lib, pkg):
     # launching without a plan is refused before anything touches the GPU
     c = pkg.TokenArgs()
     assert lib.b200_decode_token(C.byref(c), None) != 0
+
+
+def test_token_kernel_has_no_register_spills():
+    """The whole-token kernel keeps ~220 KB of shared memory per block, which leaves the L1 that backs the
+    stack a few KB: a spilled register costs a round trip to L2 (about a microsecond) every time it is
+    touched, and ptxas sits at the 80-register cap of a 672-thread block. The instantiations the engine
+    launches (no trace) must compile without spill code."""
+    import os
+    import re
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "llm.metal_b200", "csrc", "decode_token.cu")
+    r = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xptxas", "-v",
+                        "-c", src, "-o", os.devnull], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:]
+    lines = r.stdout.splitlines()
+    seen = 0
+    for i, line in enumerate(lines):
+        m = re.search(r"Function properties for (\S*decode_token_kernelILi(\d)ELb(\d)ELb(\d)E\S*)", line)
+        if not m:
+            continue
+        trace = m.group(3) == "1"                                                  # <WT, TRACE, MULTI>
+        spill = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", lines[i + 1])
+        assert spill, lines[i + 1]
+        if not trace:
+            seen += 1
+            assert spill.group(1) == "0" and spill.group(2) == "0", (m.group(1), lines[i + 1])
+    assert seen == 4          # Q8_0 / F16 x one GPU / several GPUs

@@ -417,3 +417,16 @@ def test_layer_containers_roundtrip(lib, pkg, synth):
     assert nb
     assert np.array_equal(np.ctypeslib.as_array(C.cast(lib.metal_buf_ptr(nb), fp), shape=(D,)), keep[7][2])
     lib.metal_buf_free(nb)
+
+
+def test_drop_in_program_built_against_the_reference_headers():
+    """tests/c_api/drop_in.c: a caller compiled against the reference's own qwen3.h / fast_inference.h /
+    fast_sft.h, with a model made by the reference's qwen3_create, linked against libllmb200.so. Decodes in
+    Q8_0 and F16 (tokens identical to the reference's CPU path), trains four LoRA steps, takes a decode state
+    from the SFT state and saves the adapter."""
+    import subprocess
+    exe = os.path.join(ROOT, "tests", "c_api", "_bin", "drop_in")
+    if not os.path.exists(exe):
+        pytest.skip("tests/c_api/_bin/drop_in was not built (reference tree absent at build time)")
+    r = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+    assert r.returncode == 0 and "DROP_IN ok" in r.stdout, r.stdout[-2000:]

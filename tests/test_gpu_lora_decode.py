@@ -102,6 +102,52 @@ def test_decode_with_adapter_matches_the_sft_forward(pkg, lib):
         eng.close()
 
 
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_decode_state_made_from_the_sft_state(pkg, lib, tensor_cores):
+    """inference_state_create_from_sft: the decode state takes its weights from the SFT state's device memory
+    (binary16 views in tensor-core mode, narrowed fp32 copies in CUDA-core mode) and follows its LoRA."""
+    cfg = dict(sc.TINY, n_layers=2, vocab_size=1024)
+    V = cfg["vocab_size"]
+    w = sc.make_weights(pkg, cfg)
+    ow = sc.oracle_model(cfg, w)
+    toks = sc.tokens(pkg, N + 1, 99, V)
+    x, y = toks[:-1], toks[1:]
+    init = sc.make_lora(pkg, cfg, RANK, b_std=0.05)
+    lora = o.LoRA(init, RANK, ALPHA)
+    eng = sc.Engine(pkg, cfg, w, init, N, 1, RANK, ALPHA, tensor_cores=tensor_cores)
+    st = lib.inference_state_create_from_sft(eng.h, 32)
+    assert st
+    try:
+        assert lib.inference_state_model_type(st) == pkg.MODEL_QWEN3 and lib.inference_state_vocab_size(st) == V
+        assert lib.sft_get_n_q_heads(eng.h) == cfg["n_q_heads"] and lib.sft_get_n_kv_heads(eng.h) == cfg["n_kv_heads"]
+        assert lib.sft_get_head_dim(eng.h) == cfg["head_dim"] and lib.sft_get_intermediate_size(eng.h) == cfg["intermediate_size"]
+        th = lib.sft_get_rope_thetas(eng.h)
+        assert [th[i] for i in range(cfg["n_layers"])] == [cfg["rope_theta"]] * cfg["n_layers"]
+        # the shared containers hold the reference's canonical bytes: row-major binary16 of the fp32 matrix
+        lw = C.cast(lib.sft_get_layers(eng.h), C.POINTER(pkg.LayerW))
+        for name, field in (("q", "q_proj"), ("k", "k_proj"), ("v", "v_proj"), ("o", "o_proj"), ("gate", "gate_proj"),
+                            ("up", "up_proj"), ("down", "down_proj")):
+            wm = getattr(lw[1], field).contents
+            want_bits = w["layers"][1][name].astype(np.float16)
+            assert (wm.rows, wm.cols, wm.nb) == (want_bits.shape[0], want_bits.shape[1], 0)
+            got_bits = np.ctypeslib.as_array(C.cast(lib.metal_buf_ptr(wm.mbuf), C.POINTER(C.c_uint16)), shape=want_bits.shape)
+            assert np.array_equal(got_bits, want_bits.view(np.uint16)), name
+        got = decode_logits(lib, st, x, V)
+        want, _ = o.forward(ow, lora, x)
+        assert np.abs(got - want).max() < 1e-2 * np.abs(want).max()
+        # one training step: the decode state reads the SFT state's LoRA in place, so it must now follow the
+        # engine's own updated matrices (taken back from the device: the tensor-core step rounds activations to
+        # binary16, so its update differs a little from an fp32 restatement of the step)
+        eng.train(x, y, 5e-2)
+        got2 = decode_logits(lib, st, x, V)
+        want2, _ = o.forward(ow, o.LoRA(eng.params(), RANK, ALPHA), x)
+        assert np.abs(got2 - want2).max() < 1e-2 * np.abs(want2).max()
+        assert np.abs(got2 - got).max() > 1e-3 * np.abs(want).max()
+    finally:
+        lib.inference_state_free(st)
+        eng.close()
+
+
 def test_lora_decode_kernel(lib):
     rng = np.random.default_rng(2)
     D, qr, kr, R = 200, 96, 32, 5
