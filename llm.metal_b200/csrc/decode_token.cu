@@ -386,7 +386,7 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
         if (trace && tid == 0) trace[10] = global_ns();
         if (slot_gamma) {
             // the sum of the slots is normalised before it joins the residual (Gemma3's post norms)
-            const float inv_s = 1.0f / sqrtf(cons_sum(sq, sm.red, 0, tid) / (float)D + p.eps);
+            const float inv_s = rsqrtf(cons_sum(sq, sm.red, 0, tid) / (float)D + p.eps);
 #pragma unroll 1
             for (int n = tid * 2; n < D; n += TK_NC * 2) {
                 const int i = swz(n);
@@ -399,7 +399,7 @@ __device__ __forceinline__ float stage_residual(const b200_token_args &p, int ki
     }
     const float tot = cons_sum(ss, sm.red, 1, tid);
     if (trace && tid == 0) trace[11] = global_ns();
-    return 1.0f / sqrtf(tot / (float)D + p.eps);
+    return rsqrtf(tot / (float)D + p.eps);       // 2 ulp, as the shader's rsqrt (q8_kernels.metal:156)
 }
 
 // Input vector of the o and down stages: the flagged vector, fetched once per block with coalesced
@@ -442,6 +442,39 @@ __device__ __forceinline__ void stage_vector(const b200_token_args &p, int kind,
 // [a0..a3][b0..b3][c0..c3][s, -, -, -] (byte k of word j = element 4j + k, the order of the weight bytes)
 // replaces the slice in scratch[0 .. cols), chunks swizzled like the vector they come from. Normalised
 // stages read residual * norm weight * inv from shared memory; the others convert scratch in place.
+// One work item of that conversion: four consecutive elements v4 (element 4 * it .. 4 * it + 3; one word
+// of each byte plane). The four items of a slice sit in adjacent lanes and agree on the slice's maximum by
+// two shuffles, so every lane of the warp must call this (lanes past the end of the vector with on = false).
+__device__ __forceinline__ void quantize_item(uint32_t *rec, int it, float4 v4, bool on)
+{
+    float amax = fmaxf(fmaxf(fabsf(v4.x), fabsf(v4.y)), fmaxf(fabsf(v4.z), fabsf(v4.w)));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float scale = amax * (1.0f / 4194304.0f);
+    const float rinv = amax > 1e-30f ? 4194304.0f * __frcp_rn(amax) : 0.0f;     // a slice of zeros (or denormals) reads as zero
+    // round to nearest through the 1.5 * 2^23 constant: exact for |X| <= 2^22
+    const int X0 = __float_as_int(fmaf(v4.x, rinv, 12582912.0f)) - 0x4B400000;
+    const int X1 = __float_as_int(fmaf(v4.y, rinv, 12582912.0f)) - 0x4B400000;
+    const int X2 = __float_as_int(fmaf(v4.z, rinv, 12582912.0f)) - 0x4B400000;
+    const int X3 = __float_as_int(fmaf(v4.w, rinv, 12582912.0f)) - 0x4B400000;
+    const int Y0 = (X0 + 128) >> 8, Y1 = (X1 + 128) >> 8, Y2 = (X2 + 128) >> 8, Y3 = (X3 + 128) >> 8;
+    const int Z0 = (Y0 + 128) >> 8, Z1 = (Y1 + 128) >> 8, Z2 = (Y2 + 128) >> 8, Z3 = (Y3 + 128) >> 8;
+    const uint32_t wa = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
+    const uint32_t wb = __byte_perm(__byte_perm(Y0, Y1, 0x0040), __byte_perm(Y2, Y3, 0x0040), 0x5410);
+    const uint32_t wc = __byte_perm(__byte_perm(Z0, Z1, 0x0040), __byte_perm(Z2, Z3, 0x0040), 0x5410);
+    if (on) {
+        const int base = (it >> 2) * 16, j = it & 3;         // the slice's record, this item's word in each plane
+        rec[swz(base + j)] = wa;
+        rec[swz(base + 4 + j)] = wb;
+        rec[swz(base + 8 + j)] = wc;
+        if (j == 0) rec[swz(base + 12)] = __float_as_uint(scale);
+    }
+}
+
+// The conversion as a pass of its own over a vector that is already in shared memory (stages whose
+// residual update goes through a post norm first; see stage_residual). cols is a multiple of 32, so a
+// warp's items are all inside the vector or all outside. In-place stages: the items of a slice read their
+// chunks before any of them writes (the shuffles are in between), and no other slice shares those 64 bytes.
 __device__ __forceinline__ void quantize_input(const b200_token_args &p, int kind, float inv)
 {
     const Smem sm = smem_of(p);
@@ -450,11 +483,6 @@ __device__ __forceinline__ void quantize_input(const b200_token_args &p, int kin
     const float *xv = normed ? sm.resid : sm.scratch;
     const float *gam = sm.scratch + p.d_model;
     uint32_t *rec = reinterpret_cast<uint32_t *>(sm.scratch);
-    // One work item = four consecutive elements (one 16-byte chunk of the vector, one word of each byte
-    // plane); the four items of a slice sit in adjacent lanes and agree on the slice's maximum by two
-    // shuffles. cols is a multiple of 32, so a warp's items are all inside the vector or all outside.
-    // In-place stages: the items of a slice read their chunks before any of them writes (the shuffles
-    // are in between), and no other slice shares those 64 bytes.
 #pragma unroll 1
     for (int it = tid; it * 4 < ((cols + 127) & ~127); it += TK_NC) {
         const int e0 = it * 4;
@@ -467,30 +495,108 @@ __device__ __forceinline__ void quantize_input(const b200_token_args &p, int kin
                 v4.x = g4.x * v4.x * inv; v4.y = g4.y * v4.y * inv; v4.z = g4.z * v4.z * inv; v4.w = g4.w * v4.w * inv;
             }
         }
-        float amax = fmaxf(fmaxf(fabsf(v4.x), fabsf(v4.y)), fmaxf(fabsf(v4.z), fabsf(v4.w)));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        const float scale = amax * (1.0f / 4194304.0f);
-        const float rinv = amax > 1e-30f ? 4194304.0f / amax : 0.0f;     // a slice of zeros (or denormals) reads as zero
-        // round to nearest through the 1.5 * 2^23 constant: exact for |X| <= 2^22
-        const int X0 = __float_as_int(fmaf(v4.x, rinv, 12582912.0f)) - 0x4B400000;
-        const int X1 = __float_as_int(fmaf(v4.y, rinv, 12582912.0f)) - 0x4B400000;
-        const int X2 = __float_as_int(fmaf(v4.z, rinv, 12582912.0f)) - 0x4B400000;
-        const int X3 = __float_as_int(fmaf(v4.w, rinv, 12582912.0f)) - 0x4B400000;
-        const int Y0 = (X0 + 128) >> 8, Y1 = (X1 + 128) >> 8, Y2 = (X2 + 128) >> 8, Y3 = (X3 + 128) >> 8;
-        const int Z0 = (Y0 + 128) >> 8, Z1 = (Y1 + 128) >> 8, Z2 = (Y2 + 128) >> 8, Z3 = (Y3 + 128) >> 8;
-        const uint32_t wa = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
-        const uint32_t wb = __byte_perm(__byte_perm(Y0, Y1, 0x0040), __byte_perm(Y2, Y3, 0x0040), 0x5410);
-        const uint32_t wc = __byte_perm(__byte_perm(Z0, Z1, 0x0040), __byte_perm(Z2, Z3, 0x0040), 0x5410);
-        if (on) {
-            const int base = (it >> 2) * 16, j = it & 3;     // the slice's record, this item's word in each plane
-            rec[swz(base + j)] = wa;
-            rec[swz(base + 4 + j)] = wb;
-            rec[swz(base + 8 + j)] = wc;
-            if (j == 0) rec[swz(base + 12)] = __float_as_uint(scale);
-        }
+        quantize_item(rec, it, v4, on);
     }
     named_barrier(1, TK_NC);
+}
+
+// Q8_0 stages without a post norm: the input is converted while it is assembled, four consecutive
+// elements per thread, straight from the polled words -- no fp32 copy in shared memory, no second pass.
+//
+// Residual stages (q/k/v, gate/up, LM head): residual <- embedding row | residual + sum of the slots; the
+// records hold residual * norm weight WITHOUT the 1/rms factor, which is a scalar known only after the
+// block-wide sum: it is returned and multiplies the stage's outputs instead.
+template <bool MULTI>
+__device__ __forceinline__ float fused_residual_q8(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long *trace)
+{
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const int tid = threadIdx.x, D = p.d_model, L = p.n_layers;
+    const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+    const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
+    const b200_token_layer *ly = sm.layers + (l < L ? l : L - 1);
+    const float *norm_gamma;
+    const b200_flagged *slots;
+    const unsigned *in_cnt;
+    unsigned slots_flag, target;
+    if (kind == B200_ST_GATEUP) {
+        norm_gamma = p.gemma ? ly->g_pre_ff : ly->g_post_attn;
+        slots = p.d_slots_o; slots_flag = flag;
+        in_cnt = p.d_counters + B200_CNT_SLOTS_O * B200_CNT_STRIDE; target = cnt_mul * (unsigned)(D * p.n_ranks);
+    } else {
+        norm_gamma = kind == B200_ST_LM ? p.g_final : ly->g_input;
+        slots = p.d_slots_dn; slots_flag = flag - 1u;
+        in_cnt = p.d_counters + B200_CNT_SLOTS_DN * B200_CNT_STRIDE; target = (cnt_mul - 1u) * (unsigned)(D * p.n_ranks);
+    }
+    const bool from_emb = kind == B200_ST_QKV && l == 0;
+    uint32_t *rec = reinterpret_cast<uint32_t *>(sm.scratch);
+    const float *er = nullptr;
+    if (from_emb) {
+        long long tok = p.d_tokens[*p.d_pos];
+        if (tok < 0 || tok >= p.emb_rows) tok = 0;   // never index outside the table
+        er = p.d_emb + tok * (long long)D;
+    } else {
+        const int cspin = cspin_of(p);
+        if (tid == 0) { cnt_wait<MULTI>(in_cnt, target, sm.flags, cspin); if (trace) trace[8] = global_ns(); }
+        named_barrier(1, TK_NC);
+    }
+    if (trace && tid == 0) trace[9] = global_ns();
+    float ss = 0.0f;
+#pragma unroll 1
+    for (int it = tid; it * 4 < ((D + 127) & ~127); it += TK_NC) {
+        const int e0 = it * 4;
+        const bool on = e0 < D;
+        float4 g4 = make_float4(0.f, 0.f, 0.f, 0.f), r4 = g4;
+        if (on) g4 = *reinterpret_cast<const float4 *>(norm_gamma + e0);     // in flight while the slots are polled
+        if (from_emb) {
+            if (on) {
+                r4 = *reinterpret_cast<const float4 *>(er + e0);
+                r4.x *= p.emb_scale; r4.y *= p.emb_scale; r4.z *= p.emb_scale; r4.w *= p.emb_scale;
+            }
+        } else {
+            if (on) r4 = *reinterpret_cast<const float4 *>(sm.resid + swz(e0));
+#pragma unroll 1
+            for (int k = 0; k < p.n_ranks; ++k) {
+                float a[2], b[2];
+                fl_poll<2, 2, MULTI>(slots + (size_t)k * D + e0, on ? 2 : 0, slots_flag, a, b, sm.flags, p.d_err, spin);
+                r4.x += a[0]; r4.y += b[0]; r4.z += a[1]; r4.w += b[1];
+            }
+        }
+        if (on) *reinterpret_cast<float4 *>(sm.resid + swz(e0)) = r4;
+        ss = fmaf(r4.x, r4.x, ss); ss = fmaf(r4.y, r4.y, ss); ss = fmaf(r4.z, r4.z, ss); ss = fmaf(r4.w, r4.w, ss);
+        quantize_item(rec, it, make_float4(r4.x * g4.x, r4.y * g4.y, r4.z * g4.z, r4.w * g4.w), on);
+    }
+    if (trace && tid == 0) trace[10] = global_ns();
+    const float tot = cons_sum(ss, sm.red, 1, tid);       // its barrier also publishes the records
+    if (trace && tid == 0) trace[11] = global_ns();
+    return rsqrtf(tot / (float)D + p.eps);
+}
+
+// Vector stages (o, down): the flagged input vector, polled and converted in one go.
+template <bool MULTI>
+__device__ __forceinline__ void fused_vector_q8(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long *trace)
+{
+    const Smem sm = smem_of(p);
+    const int spin = spin_of(p);
+    const int tid = threadIdx.x, L = p.n_layers, cols = p.g[kind].cols;
+    const unsigned flag = ep * (unsigned)(L + 1) + (unsigned)l + 1u;
+    const unsigned cnt_mul = ep * (unsigned)L + (unsigned)l + 1u;
+    const b200_flagged *in_vec = kind == B200_ST_O ? p.d_attn_out : p.d_act;
+    const unsigned *in_cnt = p.d_counters + (kind == B200_ST_O ? B200_CNT_ATTN : B200_CNT_ACT) * B200_CNT_STRIDE;
+    uint32_t *rec = reinterpret_cast<uint32_t *>(sm.scratch);
+    if (tid == 0) { cnt_wait<false>(in_cnt, cnt_mul * (unsigned)cols, sm.flags, cspin_of(p)); if (trace) trace[8] = global_ns(); }
+    named_barrier(1, TK_NC);
+    if (trace && tid == 0) trace[9] = global_ns();
+#pragma unroll 1
+    for (int it = tid; it * 4 < ((cols + 127) & ~127); it += TK_NC) {
+        const bool on = it * 4 < cols;
+        float a[2], b[2];
+        fl_poll<2, 2, false>(in_vec + it * 4, on ? 2 : 0, flag, a, b, sm.flags, p.d_err, spin);
+        quantize_item(rec, it, make_float4(a[0], b[0], a[1], b[1]), on);
+    }
+    if (trace && tid == 0) trace[10] = global_ns();
+    named_barrier(1, TK_NC);
+    if (trace && tid == 0) trace[11] = global_ns();
 }
 
 // Rows [w0, w1) of the block: every warp works on every chunk. A thread owns SPT 16-byte column
@@ -629,7 +735,7 @@ __device__ __forceinline__ unsigned stage_rows(const b200_token_args &p, int kin
 // best (value bits | row << 32) carries the LM head's running arg-max of this thread.
 template <bool TRACE, bool MULTI>
 __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &p, int kind, int l, unsigned ep, int w0, int w1, unsigned win,
-                                                      unsigned long long best, unsigned long long *trace)
+                                                      unsigned long long best, float oscale, unsigned long long *trace)
 {
     const b200_stage_geom &G = p.g[kind];
     const Smem sm = smem_of(p);
@@ -645,7 +751,7 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
     if (kind == B200_ST_GATEUP) {
 #pragma unroll 1
         for (int i = tid; i < n / 2; i += TK_NC) {
-            const float gte = row_sum(part + (2 * i) * nwgp, nwg), up = row_sum(part + (2 * i + 1) * nwgp, nwg);
+            const float gte = oscale * row_sum(part + (2 * i) * nwgp, nwg), up = oscale * row_sum(part + (2 * i + 1) * nwgp, nwg);
             const float a = p.gemma ? act_gelu_tanh(gte) : act_silu(gte);
             fl_store<false>(p.d_act + (w0 >> 1) + i, a * up, flag);
             ++stored;
@@ -658,7 +764,7 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
     int best_i = (int)(best >> 32);
 #pragma unroll 1
     for (int i = tid; i < n; i += TK_NC) {
-        const float y = row_sum(part + i * nwgp, nwg);
+        const float y = oscale * row_sum(part + i * nwgp, nwg);     // oscale: the 1/rms of a converted input, else 1
         const int row = w0 + i;
         if (kind == B200_ST_QKV) fl_store<false>(p.d_qkv + row, y, flag);
         else if (kind == B200_ST_LM) {
@@ -694,12 +800,22 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
     const b200_stage_geom &G = p.g[kind];
     const int tid = threadIdx.x;
     if (TRACE && trace && tid == 0) trace[0] = global_ns();
-    float inv = 0.0f;
-    if (kind == B200_ST_O || kind == B200_ST_DOWN) stage_vector<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
-    else inv = stage_residual<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
-    if (TRACE && trace && tid == 0) trace[12] = global_ns();
-    if (kind == B200_ST_LM && !p.with_lm) return state;          // only the residual update that ends a prompt position
-    if (WT == B200_WT_Q8) quantize_input(p, kind, inv);
+    float inv = 0.0f, oscale = 1.0f;
+    const bool vec = kind == B200_ST_O || kind == B200_ST_DOWN;
+    // a residual update that goes through a post norm (Gemma3, except the embedding of layer 0) takes two passes
+    const bool post_norm = p.gemma && !(kind == B200_ST_QKV && l == 0);
+    if (WT == B200_WT_Q8 && (vec || !post_norm)) {
+        if (vec) fused_vector_q8<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
+        else oscale = fused_residual_q8<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
+        if (TRACE && trace && tid == 0) trace[12] = global_ns();
+        if (kind == B200_ST_LM && !p.with_lm) return state;      // only the residual update that ends a prompt position
+    } else {
+        if (vec) stage_vector<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
+        else inv = stage_residual<MULTI>(p, kind, l, ep, TRACE ? trace : nullptr);
+        if (TRACE && trace && tid == 0) trace[12] = global_ns();
+        if (kind == B200_ST_LM && !p.with_lm) return state;      // only the residual update that ends a prompt position
+        if (WT == B200_WT_Q8) quantize_input(p, kind, inv);
+    }
     unsigned seq = (unsigned)state, win = (unsigned)(state >> 32);
     unsigned long long best = ((unsigned long long)0x7fffffffu << 32) | (unsigned long long)__float_as_uint(-INFINITY);
     const RowRange br = block_rows(G, blockIdx.x);
@@ -715,7 +831,7 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
             if (G.rg == 2) seq = stage_rows<WT, 2, 2, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
             else seq = stage_rows<WT, 2, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
         }
-        best = stage_emit<TRACE, MULTI>(p, kind, l, ep, w0, w1, win, best, trace);
+        best = stage_emit<TRACE, MULTI>(p, kind, l, ep, w0, w1, win, best, oscale, trace);
         ++win;
     }
     if (TRACE && trace && tid == 0) trace[4] = global_ns();
@@ -803,6 +919,29 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         };
         if (tid == 0) stage_rows(j0, min(j0 + KCH, j1));
 
+        // ---- what the rotation needs and does not depend on q/k/v: cos/sin of this position and the two
+        // norm weight vectors, fetched by the threads that have no row to poll, while the rows are awaited.
+        // The table lives in the merge buffer, which is not used before the keys are done. ----
+        float *rot_c = mrg, *rot_s = mrg + HALF, *gam_q = mrg + 2 * HALF, *gam_k = gam_q + HD;
+        {
+            const int first = ((G + 2) * HD / 2 + 31) & ~31;            // threads below poll the rows
+            const int nt = ATT_T - first > 0 ? ATT_T - first : ATT_T;     // helpers (all threads if every one polls)
+            const int r0 = ATT_T - first > 0 ? tid - first : tid;
+            if (r0 >= 0) {
+#pragma unroll 1
+                for (int d = r0; d < HALF; d += nt) {
+                    float sn, cs;
+                    sincosf((float)pos * ly.inv_freq[d], &sn, &cs);
+                    rot_c[d] = cs; rot_s[d] = sn;
+                }
+#pragma unroll 1
+                for (int d = r0; d < HD; d += nt) {
+                    gam_q[d] = ly.g_qn ? ly.g_qn[d] : 1.0f;
+                    gam_k[d] = ly.g_kn ? ly.g_kn[d] : 1.0f;
+                }
+            }
+        }
+
         // ---- the new rows of this KV head ----
         if (tid == 0) cnt_wait<false>(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, cspin_of(p));
         named_barrier(2, ATT_T);
@@ -826,19 +965,19 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         if (warp <= G) {
             const bool is_k = (warp == G);
             const float *src = raw + warp * HD;
-            const float *gamma = is_k ? ly.g_kn : ly.g_qn;
+            const bool has_norm = is_k ? ly.g_kn != nullptr : ly.g_qn != nullptr;
+            const float *gamma = is_k ? gam_k : gam_q;
             float ss = 0.0f;
 #pragma unroll 1
             for (int d = lane; d < HD; d += 32) ss = fmaf(src[d], src[d], ss);
             ss = warp_sum(ss);
-            const float inv = gamma ? 1.0f / sqrtf(ss / (float)HD + p.eps) : 1.0f;
+            const float inv = has_norm ? rsqrtf(ss / (float)HD + p.eps) : 1.0f;
             __half *kdst = const_cast<__half *>(kc) + (size_t)pos * HD, *vdst = const_cast<__half *>(vc) + (size_t)pos * HD;
 #pragma unroll 1
             for (int d = lane; d < HALF; d += 32) {
                 float ra = src[d], rb = src[d + HALF];
-                if (gamma) { ra = gamma[d] * ra * inv; rb = gamma[d + HALF] * rb * inv; }
-                float sn, cs;
-                sincosf((float)pos * ly.inv_freq[d], &sn, &cs);
+                if (has_norm) { ra = gamma[d] * ra * inv; rb = gamma[d + HALF] * rb * inv; }
+                const float sn = rot_s[d], cs = rot_c[d];
                 const float r0 = ra * cs - rb * sn;
                 const float r1 = ra * sn + rb * cs;
                 if (is_k) {
@@ -876,47 +1015,45 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 if (tid == 0) stage_rows(c0, c1);
             }
             if (!mbar_wait_abort(sm.att_bar, (unsigned)(l * nsub + sub) & 1u, sm.flags, spin) && !sm.flags[0]) raise(sm.flags, p.d_err, 6);
+            if (TRACE && trace && tid == 0 && sub == 0) trace[8] = global_ns();
             // same trip count for every key lane of the block, so that the warp-wide shuffles stay convergent
             const int rounds = (c1 - c0 + KL - 1) / KL;
 #pragma unroll 1
             for (int it = 0, j = c0 + kl; it < rounds; ++it, j += KL) {
                 const bool valid = j < c1;           // every lane of the warp runs the shuffles; only valid keys count
-                // One unconditional 16-byte load of the staged key and value (row 0 for an idle lane), then a
-                // select against the row of the new position, which is not in the cache yet: three separate
-                // branches filling kf/vf cost registers that ptxas could only find on the stack.
-                float kf[DPT], vf[DPT];
-                {
-                    const int jj = valid ? j - c0 : 0;
-                    const uint4 ku = *reinterpret_cast<const uint4 *>(ks + (size_t)jj * HD + dl * DPT);
-                    const uint4 vu = *reinterpret_cast<const uint4 *>(vs + (size_t)jj * HD + dl * DPT);
-                    const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
-                    const bool fresh = j == pos;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float k0 = __half2float(__ushort_as_half((unsigned short)(kw[i] & 0xffffu)));
-                        const float k1 = __half2float(__ushort_as_half((unsigned short)(kw[i] >> 16)));
-                        const float v0 = __half2float(__ushort_as_half((unsigned short)(vw[i] & 0xffffu)));
-                        const float v1 = __half2float(__ushort_as_half((unsigned short)(vw[i] >> 16)));
-                        kf[2 * i] = fresh ? k_new[dl * DPT + 2 * i] : k0; kf[2 * i + 1] = fresh ? k_new[dl * DPT + 2 * i + 1] : k1;
-                        vf[2 * i] = fresh ? v_new[dl * DPT + 2 * i] : v0; vf[2 * i + 1] = fresh ? v_new[dl * DPT + 2 * i + 1] : v1;
-                    }
-                    if (!valid) {
-#pragma unroll
-                        for (int e = 0; e < DPT; ++e) { kf[e] = 0.0f; vf[e] = 0.0f; }
-                    }
-                }
+                // One unconditional 16-byte load of the staged key and value (row 0 for an idle lane); both stay
+                // packed until they are used, and the row of the new position, which is not in the cache yet,
+                // is selected element by element: unpacked copies of both rows, or separate branches filling
+                // them, cost registers that ptxas could only find on the stack.
+                const int jj = valid ? j - c0 : 0;
+                const uint4 ku = *reinterpret_cast<const uint4 *>(ks + (size_t)jj * HD + dl * DPT);
+                const uint4 vu = *reinterpret_cast<const uint4 *>(vs + (size_t)jj * HD + dl * DPT);
+                const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+                const bool fresh = j == pos;
                 float s = 0.0f;
 #pragma unroll
-                for (int e = 0; e < DPT; ++e) s = fmaf(q[e], kf[e], s);
+                for (int i = 0; i < 4; ++i) {
+                    float k0 = __half2float(__ushort_as_half((unsigned short)(kw[i] & 0xffffu)));
+                    float k1 = __half2float(__ushort_as_half((unsigned short)(kw[i] >> 16)));
+                    if (fresh) { k0 = k_new[dl * DPT + 2 * i]; k1 = k_new[dl * DPT + 2 * i + 1]; }
+                    s = fmaf(q[2 * i], k0, s);
+                    s = fmaf(q[2 * i + 1], k1, s);
+                }
 #pragma unroll
                 for (int o = 1; o < DLN; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 s *= scale;
                 if (valid) {
                     const float mn = fmaxf(m, s);
-                    const float corr = expf(m - mn), pj = expf(s - mn);
+                    const float corr = __expf(m - mn), pj = __expf(s - mn);
                     lsum = fmaf(lsum, corr, pj);
 #pragma unroll
-                    for (int e = 0; e < DPT; ++e) acc[e] = fmaf(acc[e], corr, pj * vf[e]);
+                    for (int i = 0; i < 4; ++i) {
+                        float v0 = __half2float(__ushort_as_half((unsigned short)(vw[i] & 0xffffu)));
+                        float v1 = __half2float(__ushort_as_half((unsigned short)(vw[i] >> 16)));
+                        if (fresh) { v0 = v_new[dl * DPT + 2 * i]; v1 = v_new[dl * DPT + 2 * i + 1]; }
+                        acc[2 * i] = fmaf(acc[2 * i], corr, pj * v0);
+                        acc[2 * i + 1] = fmaf(acc[2 * i + 1], corr, pj * v1);
+                    }
                     m = mn;
                 }
             }
@@ -928,7 +1065,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         for (int o = DLN; o < 32; o <<= 1) {
             const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, lsum, o);
             const float mn = fmaxf(m, mo);
-            const float ca = (m == -INFINITY) ? 0.0f : expf(m - mn), cb = (mo == -INFINITY) ? 0.0f : expf(mo - mn);
+            const float ca = (m == -INFINITY) ? 0.0f : __expf(m - mn), cb = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
             lsum = lsum * ca + lo * cb;
 #pragma unroll
             for (int e = 0; e < DPT; ++e) acc[e] = acc[e] * ca + __shfl_xor_sync(0xffffffffu, acc[e], o) * cb;
@@ -943,27 +1080,28 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         }
         named_barrier(2, ATT_T);
         if (TRACE && trace && tid == 0) trace[7] = global_ns();
-        // record of (head, split): unnormalised output [HD], running max, sum
+        // record of (head, split): unnormalised output [HD], running max, sum. One pass: thread (head, d)
+        // folds the head's warps for output element d; the thread of d = 0 also leaves the max and the sum.
         unsigned nst = 0;
 #pragma unroll 1
-        for (int o = tid; o < G * (HD + 2); o += ATT_T) {
-            const int gg = o / (HD + 2), d = o - gg * (HD + 2);
+        for (int o = tid; o < G * HD; o += ATT_T) {
+            const int gg = o / HD, d = o - gg * HD;
             const float *src = mrg + (size_t)gg * WPH * (HD + 2);
             float M = -INFINITY;
 #pragma unroll 1
             for (int w = 0; w < WPH; ++w) M = fmaxf(M, src[w * (HD + 2) + HD]);
-            float v = 0.0f;
-            if (d == HD) v = M;
-            else {
+            float v = 0.0f, lt = 0.0f;
 #pragma unroll 1
-                for (int w = 0; w < WPH; ++w) {
-                    const float mw = src[w * (HD + 2) + HD];
-                    const float cf = (mw == -INFINITY) ? 0.0f : expf(mw - M);
-                    v = fmaf(src[w * (HD + 2) + d], cf, v);
-                }
+            for (int w = 0; w < WPH; ++w) {
+                const float mw = src[w * (HD + 2) + HD];
+                const float cf = (mw == -INFINITY) ? 0.0f : __expf(mw - M);
+                v = fmaf(src[w * (HD + 2) + d], cf, v);
+                lt = fmaf(src[w * (HD + 2) + HD + 1], cf, lt);
             }
-            fl_store<false>(p.d_attn_part + ((size_t)(kvh * G + gg) * p.n_split + split) * (HD + 2) + d, v, flag);
+            b200_flagged *rec = p.d_attn_part + ((size_t)(kvh * G + gg) * p.n_split + split) * (HD + 2);
+            fl_store<false>(rec + d, v, flag);
             ++nst;
+            if (d == 0) { fl_store<false>(rec + HD, M, flag); fl_store<false>(rec + HD + 1, lt, flag); nst += 2; }
         }
         nst = (unsigned)__reduce_add_sync(0xffffffffu, nst);
         if (lane == 0 && nst) cnt_add<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, nst);
@@ -999,7 +1137,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 const float ms = stg[(has ? lane : 0) * (HD + 2) + HD];
                 const float ls = has ? stg[lane * (HD + 2) + HD + 1] : 0.0f;
                 const float M = warp_max(ls > 0.0f ? ms : -INFINITY);
-                const float wgt = ls > 0.0f ? expf(ms - M) : 0.0f;
+                const float wgt = ls > 0.0f ? __expf(ms - M) : 0.0f;
                 const float Lsum = warp_sum(ls * wgt);
                 if (has) stg[lane * (HD + 2) + HD] = wgt / Lsum;
             }
