@@ -223,7 +223,10 @@ enum { B200_CNT_QKV = 0, B200_CNT_ATTN = 1, B200_CNT_ACT = 2, B200_CNT_SLOTS_O =
 typedef struct b200_token_layer {
     const void *w_qkv, *w_o, *w_gateup, *w_down;     /* packed rows, see the layout note above */
     const float *g_input, *g_post_attn, *g_pre_ff, *g_post_ff, *g_qn, *g_kn;
-    const float *inv_freq;                           /* [hd/2] */
+    /* This layer's rotation for every position: [max_seq][hd/2] pairs (cos, sin) of pos * inv_freq[d], made on
+     * the host with the C library's cosf / sinf, i.e. the values the reference's CPU path multiplies with
+     * (src/nn/attention.c:757-766). Layers with the same base share one table. */
+    const float *rope;
     void *k_cache, *v_cache;                         /* binary16 [n_kv][max_seq][hd] */
 } b200_token_layer;
 

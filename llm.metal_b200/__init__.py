@@ -82,7 +82,7 @@ class StageGeom(C.Structure):
 class TokenLayer(C.Structure):
     """b200_token_layer (include/llmb200_kernels.h)."""
     _fields_ = [(n, C.c_void_p) for n in ("w_qkv", "w_o", "w_gateup", "w_down", "g_input", "g_post_attn", "g_pre_ff",
-                                          "g_post_ff", "g_qn", "g_kn", "inv_freq", "k_cache", "v_cache")]
+                                          "g_post_ff", "g_qn", "g_kn", "rope", "k_cache", "v_cache")]
 
 
 B200_ST_QKV, B200_ST_O, B200_ST_GATEUP, B200_ST_DOWN, B200_ST_LM, B200_ST_KINDS = 0, 1, 2, 3, 4, 5

@@ -213,11 +213,13 @@ __device__ __forceinline__ void cnt_wait(const unsigned *cnt, unsigned target, v
     }
 }
 
-// Reads N pairs of flagged words, pair k STEP words after pair k-1; only the first `count` pairs exist
-// (the others read as zero). All loads of a round are issued before the first flag is looked at, so a
-// ready vector costs one round trip to L2 however many words a thread needs; a round with a stale
-// flag is repeated as a whole. On a timeout the abort flag goes up and the values read as zero.
-template <int N, int STEP, bool MULTI>
+// Reads N pairs of flagged words: pair k sits (k / INNER) * STEP + (k % INNER) * 2 words after the first
+// (INNER = 1: one pair every STEP words; INNER = 2: two adjacent pairs, i.e. four consecutive words, every
+// STEP words). Only the first `count` pairs exist (the others read as zero). All loads of a round are
+// issued before the first flag is looked at, so a ready vector costs one round trip to L2 however many
+// words a thread needs; a round with a stale flag is repeated as a whole. On a timeout the abort flag goes
+// up and the values read as zero.
+template <int N, int STEP, bool MULTI, int INNER = 1>
 __device__ __forceinline__ void fl_poll(const b200_flagged *base, int count, unsigned flag, float (&a)[N], float (&b)[N],
                                         volatile int *flags, int *d_err, int spin)
 {
@@ -228,8 +230,9 @@ __device__ __forceinline__ void fl_poll(const b200_flagged *base, int count, uns
         for (int k = 0; k < N; ++k) {
             v0[k] = 0ull; v1[k] = 0ull;
             if (k < count) {
-                if (MULTI) asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(base + (size_t)k * STEP) : "memory");
-                else asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(base + (size_t)k * STEP) : "memory");
+                const b200_flagged *src = base + (size_t)(k / INNER) * STEP + (k % INNER) * 2;
+                if (MULTI) asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(src) : "memory");
+                else asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(src) : "memory");
             }
         }
         bool ok = true;
@@ -587,12 +590,21 @@ __device__ __forceinline__ void fused_vector_q8(const b200_token_args &p, int ki
     if (tid == 0) { cnt_wait<false>(in_cnt, cnt_mul * (unsigned)cols, sm.flags, cspin_of(p)); if (trace) trace[8] = global_ns(); }
     named_barrier(1, TK_NC);
     if (trace && tid == 0) trace[9] = global_ns();
+    // Up to four items per thread and round, all eight loads in flight together (one round trip, not four).
+    constexpr int NI = 4;
+    const int lim = (cols + 127) & ~127;
 #pragma unroll 1
-    for (int it = tid; it * 4 < ((cols + 127) & ~127); it += TK_NC) {
-        const bool on = it * 4 < cols;
-        float a[2], b[2];
-        fl_poll<2, 2, false>(in_vec + it * 4, on ? 2 : 0, flag, a, b, sm.flags, p.d_err, spin);
-        quantize_item(rec, it, make_float4(a[0], b[0], a[1], b[1]), on);
+    for (int it0 = tid; it0 * 4 < lim; it0 += TK_NC * NI) {
+        const int left = cols - it0 * 4;                                 // elements from this thread's first item on
+        const int n_on = left <= 0 ? 0 : (left + TK_NC * 4 - 1) / (TK_NC * 4);       // its items inside the vector
+        float a[2 * NI], b[2 * NI];
+        fl_poll<2 * NI, TK_NC * 4, false, 2>(in_vec + it0 * 4, 2 * (n_on < NI ? n_on : NI), flag, a, b, sm.flags, p.d_err, spin);
+#pragma unroll
+        for (int k = 0; k < NI; ++k) {
+            const int it = it0 + k * TK_NC;
+            if (it * 4 < lim)                                            // the same for every lane of a warp
+                quantize_item(rec, it, make_float4(a[2 * k], b[2 * k], a[2 * k + 1], b[2 * k + 1]), k < n_on);
+        }
     }
     if (trace && tid == 0) trace[10] = global_ns();
     named_barrier(1, TK_NC);
@@ -794,7 +806,7 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
 
 // One matvec stage. `state`: running chunk number (low word) and window number (high word).
 template <int WT, bool TRACE, bool MULTI>
-__device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &p, int kind, int l, unsigned ep, unsigned long long state,
+__device__ __forceinline__ unsigned run_matvec(const b200_token_args &p, int kind, int l, unsigned ep, unsigned state,
                                                       unsigned long long *trace)
 {
     const b200_stage_geom &G = p.g[kind];
@@ -816,7 +828,7 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
         if (kind == B200_ST_LM && !p.with_lm) return state;      // only the residual update that ends a prompt position
         if (WT == B200_WT_Q8) quantize_input(p, kind, inv);
     }
-    unsigned seq = (unsigned)state, win = (unsigned)(state >> 32);
+    unsigned seq = state & 0x7fffffffu, win = state >> 31;        // only the parity of the window number is ever used
     unsigned long long best = ((unsigned long long)0x7fffffffu << 32) | (unsigned long long)__float_as_uint(-INFINITY);
     const RowRange br = block_rows(G, blockIdx.x);
 #pragma unroll 1
@@ -827,9 +839,11 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
             else if (G.rg == 4) seq = stage_rows<WT, 1, 4, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
             else if (G.rg == 8) seq = stage_rows<WT, 1, 8, 1, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
             else seq = stage_rows<WT, 1, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
-        } else {
-            if (G.rg == 2) seq = stage_rows<WT, 2, 2, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
-            else seq = stage_rows<WT, 2, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+        } else if (WT == B200_WT_F16) {
+            // two slices per thread exist for binary16 rows only (more than 5120 columns); a Q8_0 thread with two
+            // slices would carry 26 registers of input planes and push ptxas over the 80-register cap
+            if (G.rg == 2) seq = stage_rows<B200_WT_F16, 2, 2, 4, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
+            else seq = stage_rows<B200_WT_F16, 2, 1, 8, TRACE>(p, kind, inv, w0, w1, seq, win, trace);
         }
         best = stage_emit<TRACE, MULTI>(p, kind, l, ep, w0, w1, win, best, oscale, trace);
         ++win;
@@ -860,7 +874,7 @@ __device__ __forceinline__ unsigned long long run_matvec(const b200_token_args &
             fl_store<false>(p.d_am + 2 * blockIdx.x + 1, __int_as_float(best_i), flag);
         }
     }
-    return ((unsigned long long)win << 32) | seq;
+    return ((win & 1u) << 31) | seq;
 }
 
 // ---------------------------------------------------------------------------
@@ -888,7 +902,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         const int kvh = item / p.n_split, split = item - kvh * p.n_split;
         const int TPH = ATT_T / G, WPH = TPH / 32, KL = TPH / DLN;
         const int g = tid / TPH, r = tid - g * TPH, kl = r / DLN, dl = r - kl * DLN;
-        const int pos = *p.d_pos, n = pos + 1;
+        const int pos = sm.flags[3], n = pos + 1;
         const int chunk = (n + p.n_split - 1) / p.n_split;
         const int j0 = min(split * chunk, n), j1 = min(j0 + chunk, n);
         const int KCH = p.att_keys;                  // cache rows staged in shared memory at a time
@@ -919,7 +933,8 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         };
         if (tid == 0) stage_rows(j0, min(j0 + KCH, j1));
 
-        // ---- what the rotation needs and does not depend on q/k/v: cos/sin of this position and the two
+        // ---- what the rotation needs and does not depend on q/k/v: cos/sin of this position (from the layer's
+        // table) and the two
         // norm weight vectors, fetched by the threads that have no row to poll, while the rows are awaited.
         // The table lives in the merge buffer, which is not used before the keys are done. ----
         float *rot_c = mrg, *rot_s = mrg + HALF, *gam_q = mrg + 2 * HALF, *gam_k = gam_q + HD;
@@ -930,9 +945,8 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             if (r0 >= 0) {
 #pragma unroll 1
                 for (int d = r0; d < HALF; d += nt) {
-                    float sn, cs;
-                    sincosf((float)pos * ly.inv_freq[d], &sn, &cs);
-                    rot_c[d] = cs; rot_s[d] = sn;
+                    const float2 cs = *reinterpret_cast<const float2 *>(ly.rope + ((size_t)pos * HALF + d) * 2);
+                    rot_c[d] = cs.x; rot_s[d] = cs.y;
                 }
 #pragma unroll 1
                 for (int d = r0; d < HD; d += nt) {
@@ -942,9 +956,12 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             }
         }
 
-        // ---- the new rows of this KV head ----
-        if (tid == 0) cnt_wait<false>(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, cspin_of(p));
-        named_barrier(2, ATT_T);
+        // ---- the new rows of this KV head (with arrival counters: one thread watches, the others wait for it;
+        // without, everybody polls at once and the table work above overlaps the wait) ----
+        if (cspin_of(p) > 0) {
+            if (tid == 0) cnt_wait<false>(p.d_counters + B200_CNT_QKV * B200_CNT_STRIDE, cnt_mul * (unsigned)((p.n_q + 2 * p.n_kv) * HD), sm.flags, cspin_of(p));
+            named_barrier(2, ATT_T);
+        }
         {
             // q heads of this KV head are contiguous; its k row and v row follow at their own offsets
             const int nq = G * HD;
@@ -1226,6 +1243,8 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
         for (int i = 0; i < TK_SLOTS; ++i) { mbar_init(&sm.full[i], 1); mbar_init(&sm.empty[i], TK_NWARP); }
         mbar_init(sm.att_bar, 1);
         sm.flags[0] = 0; sm.flags[1] = 0;
+        sm.flags[2] = (int)*p.d_epoch;               // read back from shared memory wherever it is needed: one
+        sm.flags[3] = *p.d_pos;                      // register less to carry through every stage
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -1277,9 +1296,7 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
     // ---------------- consumers ----------------
     // One loop over the stages with a single (inlined) call site per stage type: no function calls,
     // hence nothing saved to and restored from the stack between stages.
-    const int pos = *p.d_pos;
-    const unsigned ep = *p.d_epoch;
-    unsigned long long state = 0;                    // chunk number | window number << 32
+    unsigned state = 0;                              // chunk number | parity of the window number << 31
     const bool tail = p.with_lm || p.n_ranks > 1;    // the LM head, or the residual update that ends a prompt position
 #pragma unroll 1
     for (int l = 0; l <= L; ++l) {
@@ -1289,16 +1306,18 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
             if (l == L && k > 0) break;
             unsigned long long *t = tr ? tr + (size_t)(6 * l + k) * TK_TRACE_WORDS : nullptr;
             if (k == 1) {
-                if (p.hd == 128) attention_stage<128, TRACE, MULTI>(p, l, ep, t);
-                else if (p.hd == 64) attention_stage<64, TRACE, MULTI>(p, l, ep, t);
-                else attention_stage<256, TRACE, MULTI>(p, l, ep, t);
+                if (p.hd == 128) attention_stage<128, TRACE, MULTI>(p, l, (unsigned)sm.flags[2], t);
+                else if (p.hd == 64) attention_stage<64, TRACE, MULTI>(p, l, (unsigned)sm.flags[2], t);
+                else attention_stage<256, TRACE, MULTI>(p, l, (unsigned)sm.flags[2], t);
             } else {
                 const int kind = l == L ? B200_ST_LM : k == 0 ? B200_ST_QKV : k - 1;     // 2, 3, 4 -> o, gate/up, down
-                state = run_matvec<WT, TRACE, MULTI>(p, kind, l, ep, state, t);
+                state = run_matvec<WT, TRACE, MULTI>(p, kind, l, (unsigned)sm.flags[2], state, t);
             }
         }
     }
 
+    const unsigned ep = (unsigned)sm.flags[2];
+    const int pos = sm.flags[3];
     const unsigned flag_lm = ep * (unsigned)(L + 1) + (unsigned)L + 1u;
     if (p.with_lm) {
         // --- block 0 folds the best rows of all blocks (and all ranks) ---
@@ -1374,8 +1393,10 @@ int plan_stage(b200_stage_geom &g, int wtype, int n_blocks, int xin_floats)
     if (g.rows % ralign) return B200_E_BADARG;
     const int E = wtype == B200_WT_Q8 ? 16 : 8;
     const int nsl = (g.cols + E - 1) / E;
-    // Up to two slices per thread; a group is at most 320 threads so that wide rows still leave two groups.
-    g.spt = nsl <= 320 ? 1 : 2;
+    // One 16-byte slice per thread up to 640 slices; two per thread beyond that, for binary16 rows only
+    // (Q8_0 rows of more than 10240 columns are refused: the caller keeps its per-stage kernels).
+    g.spt = nsl <= TK_NC ? 1 : 2;
+    if (g.spt == 2 && wtype == B200_WT_Q8) return B200_E_TOOLARGE;
     g.T = (((nsl + g.spt - 1) / g.spt) + 31) / 32 * 32;
     if (g.T > TK_NC) return B200_E_TOOLARGE;
     g.NG = TK_NC / g.T;

@@ -44,6 +44,8 @@ typedef struct {
     PackedMat qkv, o, gateup, down;
     float *g_input, *g_post_attn, *g_pre_ff, *g_post_ff, *g_qn, *g_kn;
     float *inv_freq;
+    float rope_theta;
+    const float *rope;       /* this layer's table in InferenceState.rope_tab (whole-token kernel) */
     void *k_cache, *v_cache;
     int loaded;
 } Layer;
@@ -104,6 +106,8 @@ struct InferenceState {
     int prof_n, prof_cap, prof_on;
     /* whole-token kernel: layer table on the device, flagged hand-over vectors, launch arguments */
     b200_token_layer *d_tk_layers;
+    float *rope_tab[8];      /* rotation tables, one per distinct RoPE base */
+    int n_rope_tab;
     b200_flagged *fl_qkv, *fl_part, *fl_attn, *fl_act, *fl_am;
     size_t off_fl_slots_o, off_fl_slots_dn, off_fl_am, off_counters;
     b200_token_args tk;              /* planned arguments; with_lm is set per launch */
@@ -330,6 +334,7 @@ int llmb200_state_load_layer(InferenceState *s, int li, const LayerWeightRef *r,
     ly->inv_freq = llmb200_upload_f32(f, (size_t)(hd / 2));
     free(f);
     if (!ly->inv_freq) return -1;
+    ly->rope_theta = rope_theta;
     ly->loaded = 1;
     return 0;
 }
@@ -556,13 +561,41 @@ static int build_plan(InferenceState *s)
     int rc = b200_token_plan(a, s->n_sm);
     if (rc != 0) return 1;
 
+    /* Rotation tables: cos / sin of pos * inv_freq[d] for every position, one table per distinct base, from
+     * the C library's cosf / sinf on the angle formed as the reference's CPU path forms it
+     * (src/nn/attention.c:757-766): no trigonometry on the device's critical path. */
+    for (int l = 0; l < L; ++l) {
+        Layer *ly = &s->layers[l];
+        if (ly->rope) continue;
+        for (int m = 0; m < l && !ly->rope; ++m)
+            if (s->layers[m].rope_theta == ly->rope_theta) ly->rope = s->layers[m].rope;
+        if (ly->rope) continue;
+        if (s->n_rope_tab >= 8) { fprintf(stderr, "[FastGen] more than 8 distinct RoPE bases\n"); return 1; }
+        const int half = s->hd / 2;
+        const size_t n = (size_t)s->max_seq * half * 2;
+        float *h = malloc(n * sizeof(float));
+        if (!h) return -1;
+        for (int d = 0; d < half; ++d) {
+            const float freq = 1.0f / powf(ly->rope_theta, (float)(2 * d) / (float)s->hd);
+            for (int pos = 0; pos < s->max_seq; ++pos) {
+                const float angle = (float)pos * freq;
+                h[((size_t)pos * half + d) * 2] = cosf(angle);
+                h[((size_t)pos * half + d) * 2 + 1] = sinf(angle);
+            }
+        }
+        float *dt = llmb200_upload_f32(h, n);
+        free(h);
+        if (!dt) return -1;
+        s->rope_tab[s->n_rope_tab++] = dt;
+        ly->rope = dt;
+    }
     b200_token_layer *tl = calloc((size_t)L, sizeof(*tl));
     if (!tl) return -1;
     for (int l = 0; l < L; ++l) {
         const Layer *ly = &s->layers[l];
         tl[l].w_qkv = ly->qkv.w; tl[l].w_o = ly->o.w; tl[l].w_gateup = ly->gateup.w; tl[l].w_down = ly->down.w;
         tl[l].g_input = ly->g_input; tl[l].g_post_attn = ly->g_post_attn; tl[l].g_pre_ff = ly->g_pre_ff;
-        tl[l].g_post_ff = ly->g_post_ff; tl[l].g_qn = ly->g_qn; tl[l].g_kn = ly->g_kn; tl[l].inv_freq = ly->inv_freq;
+        tl[l].g_post_ff = ly->g_post_ff; tl[l].g_qn = ly->g_qn; tl[l].g_kn = ly->g_kn; tl[l].rope = ly->rope;
         tl[l].k_cache = ly->k_cache; tl[l].v_cache = ly->v_cache;
     }
     if (!s->d_tk_layers) CU_TRY(cudaMalloc((void **)&s->d_tk_layers, (size_t)L * sizeof(*tl)), { free(tl); return -1; });
@@ -857,6 +890,7 @@ InferenceState *inference_state_create_from_sft(SFTState *sft, int max_seq_len)
         ly->inv_freq = llmb200_upload_f32(f, (size_t)(hd / 2));
         free(f);
         if (!ly->inv_freq) rc = -1;
+        ly->rope_theta = thetas[i];
         ly->loaded = 1;
     }
     if (!rc) rc = share_rows(lm, 0, D, &s->lm, 0, 1);
@@ -923,6 +957,7 @@ static void free_one(InferenceState *s)
     }
     cudaFree(s->lm.w); cudaFree(s->g_final); cudaFree(s->emb);
     cudaFree(s->resid[0]); cudaFree(s->resid[1]); cudaFree(s->qkv); cudaFree(s->attn_out); cudaFree(s->act);
+    for (int i = 0; i < s->n_rope_tab; ++i) cudaFree(s->rope_tab[i]);
     cudaFree(s->d_tk_layers); cudaFree(s->fl_qkv); cudaFree(s->fl_part); cudaFree(s->fl_attn); cudaFree(s->fl_act);
     cudaFree(s->fl_am); cudaFree(s->d_step_ns);
     cudaFree(s->xnorm);
