@@ -329,6 +329,8 @@ int b200_argmax_rows(const float *logits, int n_rows, int vocab, unsigned *next_
 /* Number of kernel launches issued through this ABI since the last reset
  * (what bench.py reports as gpu_launches). */
 unsigned long long b200_launch_count(int reset);
+/* For callers that replay captured launches (a CUDA graph): adds the kernel nodes of a replay to the count. */
+void b200_launch_count_add(unsigned long long n);
 
 #ifdef __cplusplus
 }

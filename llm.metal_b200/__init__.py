@@ -167,7 +167,7 @@ SYMBOLS_MAIN = {
                        "norm_upload", "layers_convert_upload", "layers_free"],
     "llmb200_kernels.h": ["b200_packed_row_stride", "b200_q8_pack", "b200_f16_pack", "b200_q8_unpack_blocks", "b200_matvec",
                           "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_token_plan", "b200_token_chunks", "b200_decode_token", "b200_lora_decode", "b200_argmax_rows",
-                          "b200_launch_count"],
+                          "b200_launch_count", "b200_launch_count_add"],
     "llmb200_inference.h": ["inference_state_create", "inference_state_create_gemma3", "inference_state_free",
                             "inference_generate", "inference_state_model_type", "inference_state_vocab_size",
                             "inference_state_reset", "inference_forward_token", "inference_state_load_eos",
@@ -240,7 +240,7 @@ def lib():
         "b200_decode_token": (i, [C.POINTER(TokenArgs), vp]),
         "b200_lora_decode": (i, [vp, vp, vp, vp, vp, vp, i, i, i, i, fl, vp]),
         "b200_argmax_rows": (i, [vp, i, i, vp, vp, i, vp, vp, vp]),
-        "b200_launch_count": (C.c_ulonglong, [i]),
+        "b200_launch_count": (C.c_ulonglong, [i]), "b200_launch_count_add": (None, [C.c_ulonglong]),
         "inference_state_create": (vp, [vp, i, i]), "inference_state_create_gemma3": (vp, [vp, i, i]),
         "inference_state_free": (None, [vp]),
         "inference_generate": (i, [vp, c_u32_p, i, c_u32_p, i]),

@@ -251,6 +251,40 @@ __device__ __forceinline__ void fl_poll(const b200_flagged *base, int count, uns
     for (int k = 0; k < N; ++k) { a[k] = 0.0f; b[k] = 0.0f; }
 }
 
+// The same with the distance between groups of INNER pairs given at run time (the slots of the tensor-
+// parallel ranks lie d_model words apart).
+template <int N, bool MULTI, int INNER>
+__device__ __forceinline__ void fl_poll_step(const b200_flagged *base, size_t step, int count, unsigned flag, float (&a)[N], float (&b)[N],
+                                             volatile int *flags, int *d_err, int spin)
+{
+#pragma unroll 1
+    for (int it = 0;; ++it) {
+        unsigned long long v0[N], v1[N];
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            v0[k] = 0ull; v1[k] = 0ull;
+            if (k < count) {
+                const b200_flagged *src = base + (size_t)(k / INNER) * step + (k % INNER) * 2;
+                if (MULTI) asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(src) : "memory");
+                else asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(v0[k]), "=l"(v1[k]) : "l"(src) : "memory");
+            }
+        }
+        bool ok = true;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            ok = ok && (k >= count || ((unsigned)(v0[k] >> 32) == flag && (unsigned)(v1[k] >> 32) == flag));
+            a[k] = __uint_as_float((unsigned)v0[k]);
+            b[k] = __uint_as_float((unsigned)v1[k]);
+        }
+        if (ok) return;
+        if (it >= spin || ((it & 31) == 0 && flags[0])) break;       // an aborted block no longer waits
+        if (it > 4) __nanosleep(40);
+    }
+    raise(flags, d_err, 5);
+#pragma unroll
+    for (int k = 0; k < N; ++k) { a[k] = 0.0f; b[k] = 0.0f; }
+}
+
 // Sum over the consumer threads; every thread gets it. One block-wide barrier. `buf` (0 or 1) picks
 // the exchange buffer: two calls on the same buffer must have another consumer barrier between them.
 __device__ __forceinline__ float cons_sum(float v, float *red, int buf, int tid)
@@ -558,10 +592,19 @@ __device__ __forceinline__ float fused_residual_q8(const b200_token_args &p, int
             }
         } else {
             if (on) r4 = *reinterpret_cast<const float4 *>(sm.resid + swz(e0));
+            if (MULTI) {
+                // the slots of up to four ranks per round, all loads in flight together; added in rank order
 #pragma unroll 1
-            for (int k = 0; k < p.n_ranks; ++k) {
+                for (int k0 = 0; k0 < p.n_ranks; k0 += 4) {
+                    const int nk = p.n_ranks - k0 < 4 ? p.n_ranks - k0 : 4;
+                    float a[8], b[8];
+                    fl_poll_step<8, true, 2>(slots + (size_t)k0 * D + e0, (size_t)D, on ? 2 * nk : 0, slots_flag, a, b, sm.flags, p.d_err, spin);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { r4.x += a[2 * k]; r4.y += b[2 * k]; r4.z += a[2 * k + 1]; r4.w += b[2 * k + 1]; }
+                }
+            } else {
                 float a[2], b[2];
-                fl_poll<2, 2, MULTI>(slots + (size_t)k * D + e0, on ? 2 : 0, slots_flag, a, b, sm.flags, p.d_err, spin);
+                fl_poll<2, 2, false>(slots + e0, on ? 2 : 0, slots_flag, a, b, sm.flags, p.d_err, spin);
                 r4.x += a[0]; r4.y += b[0]; r4.z += a[1]; r4.w += b[1];
             }
         }
@@ -978,7 +1021,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         named_barrier(2, ATT_T);
         if (TRACE && trace && tid == 0) trace[1] = global_ns();
 
-        // ---- normalise + rotate: warp vi < G takes query head vi, warp G the new key and value ----
+        // ---- normalise + rotate: warp vi < G takes query head vi, warp G the new key, warp G + 1 the new value ----
         if (warp <= G) {
             const bool is_k = (warp == G);
             const float *src = raw + warp * HD;
@@ -989,7 +1032,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             for (int d = lane; d < HD; d += 32) ss = fmaf(src[d], src[d], ss);
             ss = warp_sum(ss);
             const float inv = has_norm ? rsqrtf(ss / (float)HD + p.eps) : 1.0f;
-            __half *kdst = const_cast<__half *>(kc) + (size_t)pos * HD, *vdst = const_cast<__half *>(vc) + (size_t)pos * HD;
+            __half *kdst = const_cast<__half *>(kc) + (size_t)pos * HD;
 #pragma unroll 1
             for (int d = lane; d < HALF; d += 32) {
                 float ra = src[d], rb = src[d + HALF];
@@ -1005,14 +1048,15 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                     q_s[warp * HD + d] = r0; q_s[warp * HD + d + HALF] = r1;
                 }
             }
-            if (is_k) {
-                const float *vsrc = raw + (G + 1) * HD;
+        } else if (warp == G + 1) {
+            // the new value row: rounded to the cache's binary16 by a warp of its own
+            const float *vsrc = raw + (G + 1) * HD;
+            __half *vdst = const_cast<__half *>(vc) + (size_t)pos * HD;
 #pragma unroll 1
-                for (int d = lane; d < HD; d += 32) {
-                    const __half h = __float2half_rn(vsrc[d]);
-                    v_new[d] = __half2float(h);
-                    if (split == 0) vdst[d] = h;
-                }
+            for (int d = lane; d < HD; d += 32) {
+                const __half h = __float2half_rn(vsrc[d]);
+                v_new[d] = __half2float(h);
+                if (split == 0) vdst[d] = h;
             }
         }
         named_barrier(2, ATT_T);

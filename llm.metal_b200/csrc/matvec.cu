@@ -36,6 +36,8 @@ extern "C" unsigned long long b200_launch_count(int reset)
     return v;
 }
 
+extern "C" void b200_launch_count_add(unsigned long long n) { g_b200_launches += n; }
+
 namespace {
 
 struct Geometry {

@@ -103,7 +103,8 @@ __device__ __forceinline__ float dot8_f16(const uint4 &w, const float *x)
     return a.x + a.y;
 }
 
-__device__ __forceinline__ float act_silu(float g) { return g / (1.0f + expf(-g)); }
+// exp through ex2.approx (2 ulp), what the shader's fast-math exp is (q8_kernels.metal:336)
+__device__ __forceinline__ float act_silu(float g) { return g / (1.0f + __expf(-g)); }
 __device__ __forceinline__ float act_gelu_tanh(float g)
 {
     float inner = 0.7978845608f * (g + 0.044715f * g * g * g);

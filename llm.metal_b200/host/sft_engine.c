@@ -92,6 +92,12 @@ struct SFTState {
     WMat *share_lm;
     MetalBuf *share_final_g;
 
+    /* forward + loss + backward of a step as one CUDA graph: captured on the second step (the first one runs
+     * eagerly and finishes every lazy initialisation), replayed from then on */
+    cudaGraphExec_t step_graph;
+    int step_graph_state;       /* 0 first step pending, 1 capture pending, 2 ready, -1 not available */
+    unsigned long long step_graph_kernels;
+
     cudaEvent_t ev[4];
     float last_step_ms, last_update_ms, last_norm;
 };
@@ -635,6 +641,7 @@ void sft_state_free(SFTState *s)
     for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
     cudaFreeHost(s->h_grad); cudaFreeHost(s->h_tok); cudaFreeHost(s->h_loss);
     metal_buf_free(s->mb_logits); metal_buf_free(s->mb_dlogits);
+    if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
     share_free(s);
     for (int i = 0; i < 4; ++i) if (s->ev[i]) cudaEventDestroy(s->ev[i]);
     free(s->token_emb_host);
@@ -813,10 +820,41 @@ float llmb200_sft_forward_backward(SFTState *s, const uint32_t *inputs, const ui
     S_TRY(s, (int)cudaMemcpyAsync(s->tokens, s->h_tok, (size_t)s->M * 4, cudaMemcpyHostToDevice, st));
     S_TRY(s, (int)cudaMemcpyAsync(s->targets, s->h_tok + s->M, (size_t)s->M * 4, cudaMemcpyHostToDevice, st));
     cudaEventRecord(s->ev[0], st);
-    S_TRY(s, b200_embed_rows(s->d_emb, s->tokens, s->M, s->D, s->V, s->emb_scale, s->layers[0].x_in, st));
-    forward_device(s);
-    loss_device(s);
-    backward_device(s);
+    if (s->step_graph_state == 1 && !s->err) {
+        /* capture: nothing runs here, the launches only become nodes */
+        s->step_graph_state = -1;
+        const unsigned long long before = b200_launch_count(0);
+        if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            S_TRY(s, b200_embed_rows(s->d_emb, s->tokens, s->M, s->D, s->V, s->emb_scale, s->layers[0].x_in, st));
+            forward_device(s);
+            loss_device(s);
+            backward_device(s);
+            cudaGraph_t g = NULL;
+            const cudaError_t ce = cudaStreamEndCapture(st, &g);
+            if (ce == cudaSuccess && g && !s->err && cudaGraphInstantiate(&s->step_graph, g, 0) == cudaSuccess) {
+                s->step_graph_kernels = b200_launch_count(0) - before;
+                s->step_graph_state = 2;
+            } else {
+                (void)cudaGetLastError();
+                s->err = 0;                      /* a launch refused under capture is not a failed step */
+                fprintf(stderr, "[FastSFT] the step could not be captured as a CUDA graph; launching kernel by kernel\n");
+            }
+            if (g) cudaGraphDestroy(g);
+        } else (void)cudaGetLastError();
+        /* the capture advanced the count without launching anything */
+        b200_launch_count_add(0ull - (b200_launch_count(0) - before));
+    }
+    if (s->step_graph_state == 2) {
+        S_TRY(s, (int)cudaGraphLaunch(s->step_graph, st));
+        b200_launch_count_add(s->step_graph_kernels);
+        s->xh_has_dlogits = 0;
+    } else {
+        S_TRY(s, b200_embed_rows(s->d_emb, s->tokens, s->M, s->D, s->V, s->emb_scale, s->layers[0].x_in, st));
+        forward_device(s);
+        loss_device(s);
+        backward_device(s);
+        if (s->step_graph_state == 0) s->step_graph_state = getenv("LLMB200_SFT_NO_GRAPH") ? -1 : 1;
+    }
     cudaEventRecord(s->ev[1], st);
     const float loss = mean_loss_host(s);
     cudaEventElapsedTime(&s->last_step_ms, s->ev[0], s->ev[1]);

@@ -124,6 +124,8 @@ void *metal_buf_ptr(MetalBuf *b)
         return b->host_mirror;
     }
     if (b->kind == MB_F16) {
+        /* the conversion ran on the library's own (non-blocking) stream: a copy on the default stream does not wait for it */
+        metal_flush();
         size_t row_bytes = (size_t)b->cols * 2;
         b->host_mirror = malloc((size_t)b->rows * row_bytes + 1);
         if (!b->host_mirror) return NULL;
