@@ -812,7 +812,7 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
             ++stored;
         }
         stored = (unsigned)__reduce_add_sync(0xffffffffu, stored);
-        if (lane == 0 && stored) cnt_add<false>(cn + B200_CNT_ACT * B200_CNT_STRIDE, stored);
+        if (lane == 0 && stored && cspin_of(p) > 0) cnt_add<false>(cn + B200_CNT_ACT * B200_CNT_STRIDE, stored);
         return best;
     }
     float best_v = __uint_as_float((unsigned)best);
@@ -832,7 +832,7 @@ __device__ __forceinline__ unsigned long long stage_emit(const b200_token_args &
         }
         ++stored;
     }
-    if (kind != B200_ST_LM) {
+    if (kind != B200_ST_LM && cspin_of(p) > 0) {       // nobody watches the counters when the readers poll the words themselves
         // one add per warp and receiver: the words this warp has stored
         stored = (unsigned)__reduce_add_sync(0xffffffffu, stored);
         if (lane == 0 && stored) {
@@ -1165,7 +1165,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
             if (d == 0) { fl_store<false>(rec + HD, M, flag); fl_store<false>(rec + HD + 1, lt, flag); nst += 2; }
         }
         nst = (unsigned)__reduce_add_sync(0xffffffffu, nst);
-        if (lane == 0 && nst) cnt_add<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, nst);
+        if (lane == 0 && nst && cspin_of(p) > 0) cnt_add<false>(p.d_counters + (B200_CNT_PART + kvh) * B200_CNT_STRIDE, nst);
         if (TRACE && trace && tid == 0) trace[3] = global_ns();
 
         // ---- this block merges the splits of query heads split, split + n_split, ... of its KV head ----
@@ -1213,7 +1213,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 ++nout;
             }
             nout = (unsigned)__reduce_add_sync(0xffffffffu, nout);
-            if (lane == 0 && nout) cnt_add<false>(p.d_counters + B200_CNT_ATTN * B200_CNT_STRIDE, nout);
+            if (lane == 0 && nout && cspin_of(p) > 0) cnt_add<false>(p.d_counters + B200_CNT_ATTN * B200_CNT_STRIDE, nout);
         }
     }
     // the o stage reuses the scratch area: nobody goes on before the attention threads are done with it
