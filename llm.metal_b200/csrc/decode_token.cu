@@ -926,7 +926,10 @@ __device__ __forceinline__ unsigned run_matvec(const b200_token_args &p, int kin
 // attends over its slice with one online softmax per key lane and leaves (max, sum, output) as a
 // flagged record; block (kv head, split g) then merges all splits of query head g of that KV head.
 // ---------------------------------------------------------------------------
-template <int HD, bool TRACE, bool MULTI>
+// OWNROW: the row of the new position joins the staged rows (written by the block itself) instead of being
+// selected element by element in the key loop. Shorter and faster; the instantiations with binary16 weights keep
+// the select, where the other form pushed ptxas over its register cap.
+template <int HD, bool TRACE, bool MULTI, bool OWNROW>
 __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l, unsigned ep, unsigned long long *trace)
 {
     constexpr int DPT = 8;                           // head-dim values per thread
@@ -952,8 +955,9 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
         const int nsub = (chunk + KCH - 1) / KCH;    // the same for every block and layer of this token
 
         float *q_s = sm.scratch;                     // [G][HD]
-        float *k_new = q_s + G * HD;                 // [HD]
-        float *v_new = k_new + HD;                   // [HD]
+        float *k_new = q_s + G * HD;                 // [HD] the new key row (OWNROW: as binary16, see k_new_h)
+        float *v_new = k_new + HD;                   // [HD] the new value row
+        __half *k_new_h = reinterpret_cast<__half *>(k_new), *v_new_h = reinterpret_cast<__half *>(v_new);
         float *mrg = v_new + HD;                     // [G][WPH][HD + 2]
         float *raw = mrg + G * WPH * (HD + 2);       // [(G + 2) * HD] new q heads, k row, v row as produced
         __half *ks = reinterpret_cast<__half *>(raw + (G + 2) * HD);   // [KCH][HD] staged keys
@@ -965,8 +969,10 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
 
         // The block's slice of the cache is two contiguous byte ranges: one bulk copy each into shared
         // memory, started before the wait for q/k/v so that its latency hides behind that wait. The row
-        // of the new position (not in the cache yet) is copied like the others and never read.
+        // of the new position (not in the cache yet) is copied like the others and never read, or (OWNROW)
+        // left out and written by the block itself.
         auto stage_rows = [&](int c0, int c1) {
+            if (OWNROW && c1 > pos) c1 = pos;        // the block writes that row itself (below)
             const unsigned bytes = c1 > c0 ? (unsigned)(c1 - c0) * HD * 2u : 0u;
             mbar_expect_tx(sm.att_bar, 2u * bytes);
             if (bytes) {
@@ -1042,7 +1048,8 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 const float r1 = ra * sn + rb * cs;
                 if (is_k) {
                     const __half h0 = __float2half_rn(r0), h1 = __float2half_rn(r1);
-                    k_new[d] = __half2float(h0); k_new[d + HALF] = __half2float(h1);
+                    if (OWNROW) { k_new_h[d] = h0; k_new_h[d + HALF] = h1; }
+                    else { k_new[d] = __half2float(h0); k_new[d + HALF] = __half2float(h1); }
                     if (split == 0) { kdst[d] = h0; kdst[d + HALF] = h1; }
                 } else {
                     q_s[warp * HD + d] = r0; q_s[warp * HD + d + HALF] = r1;
@@ -1055,7 +1062,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
 #pragma unroll 1
             for (int d = lane; d < HD; d += 32) {
                 const __half h = __float2half_rn(vsrc[d]);
-                v_new[d] = __half2float(h);
+                if (OWNROW) v_new_h[d] = h; else v_new[d] = __half2float(h);
                 if (split == 0) vdst[d] = h;
             }
         }
@@ -1075,6 +1082,14 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 named_barrier(2, ATT_T);             // everybody is done with the rows staged before
                 if (tid == 0) stage_rows(c0, c1);
             }
+            if (OWNROW && pos >= c0 && pos < c1) {   // the same for the whole block: the last split only
+                // the row of this position joins the staged rows (the bulk copies leave its place alone)
+                if (tid < HD / 8) {
+                    reinterpret_cast<uint4 *>(ks + (size_t)(pos - c0) * HD)[tid] = reinterpret_cast<const uint4 *>(k_new_h)[tid];
+                    reinterpret_cast<uint4 *>(vs + (size_t)(pos - c0) * HD)[tid] = reinterpret_cast<const uint4 *>(v_new_h)[tid];
+                }
+                named_barrier(2, ATT_T);
+            }
             if (!mbar_wait_abort(sm.att_bar, (unsigned)(l * nsub + sub) & 1u, sm.flags, spin) && !sm.flags[0]) raise(sm.flags, p.d_err, 6);
             if (TRACE && trace && tid == 0 && sub == 0) trace[8] = global_ns();
             // same trip count for every key lane of the block, so that the warp-wide shuffles stay convergent
@@ -1090,7 +1105,7 @@ __device__ __forceinline__ void attention_stage(const b200_token_args &p, int l,
                 const uint4 ku = *reinterpret_cast<const uint4 *>(ks + (size_t)jj * HD + dl * DPT);
                 const uint4 vu = *reinterpret_cast<const uint4 *>(vs + (size_t)jj * HD + dl * DPT);
                 const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
-                const bool fresh = j == pos;
+                const bool fresh = !OWNROW && j == pos;
                 float s = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -1350,9 +1365,10 @@ decode_token_kernel(const __grid_constant__ b200_token_args p)
             if (l == L && k > 0) break;
             unsigned long long *t = tr ? tr + (size_t)(6 * l + k) * TK_TRACE_WORDS : nullptr;
             if (k == 1) {
-                if (p.hd == 128) attention_stage<128, TRACE, MULTI>(p, l, (unsigned)sm.flags[2], t);
-                else if (p.hd == 64) attention_stage<64, TRACE, MULTI>(p, l, (unsigned)sm.flags[2], t);
-                else attention_stage<256, TRACE, MULTI>(p, l, (unsigned)sm.flags[2], t);
+                constexpr bool OWN = WT == B200_WT_Q8;
+                if (p.hd == 128) attention_stage<128, TRACE, MULTI, OWN>(p, l, (unsigned)sm.flags[2], t);
+                else if (p.hd == 64) attention_stage<64, TRACE, MULTI, OWN>(p, l, (unsigned)sm.flags[2], t);
+                else attention_stage<256, TRACE, MULTI, OWN>(p, l, (unsigned)sm.flags[2], t);
             } else {
                 const int kind = l == L ? B200_ST_LM : k == 0 ? B200_ST_QKV : k - 1;     // 2, 3, 4 -> o, gate/up, down
                 state = run_matvec<WT, TRACE, MULTI>(p, kind, l, (unsigned)sm.flags[2], state, t);
