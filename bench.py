@@ -967,7 +967,11 @@ def main():
     if world > 1:
         line["exchange"] = {"impl": "partial sums stored with their flags into every rank's slot over NVLink (plain peer stores), summed "
                                     "in rank order inside the consumer stage of the same kernel; no separate all-reduce kernel",
-                            "exchanges_per_token": 2 * sp.n_layers}
+                            "exchanges_per_token": 2 * sp.n_layers,
+                            # everything a layer costs (rows, attention, five hand-overs, both exchanges), halved:
+                            # an upper bound on what one fused exchange can cost
+                            "us_per_token_over_exchanges": 1e3 * sum(step_ms) / n_tok / (2 * sp.n_layers),
+                            "nccl_arm": nccl_exchange_arm(torch, dist, sp.d_model, 2 * sp.n_layers, max_over_ranks)}
     if world == 1 and not args.no_cpu_baseline and not gemma:
         if rank == 0:
             line["cpu_baseline"] = cpu_reference_sample(pkg, S, sp, threads)
@@ -981,6 +985,51 @@ def main():
     if rank == 0:
         emit(json.dumps(line))
     return 0
+
+
+def nccl_exchange_arm(torch, dist, d_model, per_token, max_over_ranks):
+    """The exchange as a stage-by-stage design would do it: an NCCL all-reduce (sum) of one d_model fp32 vector
+    after the o and after the down projection, i.e. 2 x layers calls per token. Timed on its own, the calls of
+    one token captured in a CUDA graph (no host launch cost), CUDA events, max over ranks. A comparison figure
+    beside the fused exchange of the token kernel; nothing of it is on the measured decode path."""
+    try:
+        x = torch.zeros(d_model, dtype=torch.float32, device="cuda")
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for _ in range(8):
+                dist.all_reduce(x)
+        s.synchronize()
+        mode = "the calls of one token in a CUDA graph"
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(per_token):
+                    dist.all_reduce(x)
+            run = g.replay
+        except Exception:                                         # capture refused: launch the calls one by one
+            mode = "eager launches (host launch cost included)"
+            torch.cuda.synchronize()
+
+            def run():
+                for _ in range(per_token):
+                    dist.all_reduce(x)
+        reps = 20
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                run()
+            s.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            for _ in range(reps):
+                run()
+            e1.record(s)
+            e1.synchronize()
+        us = max_over_ranks(1e3 * e0.elapsed_time(e1) / (reps * per_token))
+        return {"us_per_allreduce": us, "us_per_token": us * per_token, "bytes": 4 * d_model, "mode": mode,
+                "what": "torch.distributed all_reduce (NCCL, sum) of one d_model fp32 vector, back to back"}
+    except Exception as exc:                                      # a comparison figure must not cost the bench line
+        return {"unavailable": "%s: %s" % (type(exc).__name__, str(exc)[:200])}
 
 
 if __name__ == "__main__":
