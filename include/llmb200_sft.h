@@ -3,8 +3,11 @@
  *
  * Part 1 declares, under the reference's names and with the same argument
  * meaning, the LoRA subset of llm.metal's fast SFT engine
- * (src/nn/fast_sft.h:14-111; implementation src/nn/fast_sft.c). Not provided:
- * the Gemma3 and full-parameter constructors and gradient accumulation in F16.
+ * (src/nn/fast_sft.h:14-111; implementation src/nn/fast_sft.c). The Gemma3
+ * and full-parameter modes are not built: their constructors exist, so that a
+ * caller written for all modes (src/nn/fast_grpo.c) links, and refuse with a
+ * message and NULL; sft_is_full_param answers 0 for every state this library
+ * can make.
  *
  * Part 2 is additive: layer-by-layer construction, several sequences per
  * step (their LoRA gradients are averaged, then one clip + AdamW as in the
@@ -100,6 +103,21 @@ int sft_get_n_kv_heads(SFTState *state);
 int sft_get_head_dim(SFTState *state);
 int sft_get_intermediate_size(SFTState *state);
 const float *sft_get_rope_thetas(SFTState *state);
+
+/* ---- modes that are not built (src/nn/fast_sft.h:17-41, 55) ----
+ * The constructors print "[FastSFT] ... not provided" and return NULL, like any other failed create.
+ * No state of these kinds can therefore reach the other calls; given one anyway they print the same
+ * message and change nothing. sft_is_full_param is 0 for every state made by sft_state_create. */
+SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int lora_rank, float lora_alpha);
+SFTState *sft_state_create_full(llmb200_qwen3_model *model, int seq_len);
+SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len);
+int  sft_is_full_param(SFTState *state);
+void sft_backward_sgd(SFTState *state, float lr);
+void sft_alloc_grad_accum(SFTState *state);
+void sft_backward_accum(SFTState *state);
+void sft_apply_grad_sgd(SFTState *state, float lr);
+void sft_save_full_checkpoint(SFTState *state, const char *path);
+void sft_sync_lora_to_gemma3(SFTState *state, llmb200_gemma3_model *model);
 
 /* ========================= Part 2: additions ============================== */
 

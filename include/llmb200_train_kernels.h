@@ -146,6 +146,15 @@ int b200_xty_skinny(const float *X, long long ld_x, const float *Y, long long ld
 int b200_softmax_ce_rows(const float *logits, const uint32_t *targets, int rows, int vocab, float grad_scale,
                          float *losses, float *dlogits, void *stream);
 
+/* grpo_policy_grad (shaders/q8_kernels.metal:698-761; dispatch fast_metal.m:963-981), one row per position:
+ * new_logprobs[m] = logit[action] - logsumexp; ratio = exp(new - old); the PPO clip keeps the position
+ * (weight = -advantage) or drops it (0); dlogits = weight * ratio * (softmax - onehot(action)). */
+int b200_grpo_policy_grad(const float *logits, const uint32_t *actions, const float *old_logprobs, const float *advantages,
+                          float *new_logprobs, float *dlogits, int rows, int vocab, float clip_eps, void *stream);
+
+/* scale_tensor (fast_metal.m:722-731): x[i] *= alpha for i < n. */
+int b200_scale(float *x, float alpha, size_t n, void *stream);
+
 /* Global-norm clip + AdamW over one flat parameter vector
  * (src/nn/fast_sft.c:1045-1107). Step 1 writes per-block double partial sums
  * of g^2 into partials[n_partials]; step 2 adds them in index order (double),

@@ -10,6 +10,10 @@
  *   MetalBuf, metal_buf_*      replaces src/nn/fast_metal.h:12-17 (src/nn/fast_metal.m:197-217)
  *   fast_metal_init/shutdown   replaces src/nn/fast_metal.h:8-9   (src/nn/fast_metal.m:75-195)
  *   metal_flush                replaces src/nn/fast_metal.h:84    (src/nn/fast_metal.m:239-247)
+ *   metal_enqueue_scale, metal_enqueue_grpo_policy_grad
+ *                              replace src/nn/fast_metal.h:124, :179-181 (src/nn/fast_metal.m:722-731, 963-981):
+ *                              the two dispatches a caller outside the engines issues itself (the GRPO
+ *                              step, src/nn/fast_grpo.c:449-457); every other dispatch stays inside the engines
  *   WMat, LayerW, WeightRef, LayerWeightRef, ModelType   src/nn/wmat.h:10-56
  *   wmat_create_q8/f16, wmat_free, layers_convert_upload, layers_free,
  *   wmat_convert, norm_upload  replaces src/nn/wmat.c:47-156
@@ -43,6 +47,12 @@ MetalBuf *metal_buf_create(size_t size);                     /* zero-filled */
 MetalBuf *metal_buf_from_data(const void *data, size_t sz);  /* copies sz bytes in */
 void      metal_buf_free(MetalBuf *b);                       /* NULL is accepted */
 void     *metal_buf_ptr(MetalBuf *b);                        /* host-visible pointer */
+
+/* ---- dispatches on buffers (asynchronous on the library's stream, like the reference's encoder) ---- */
+void metal_enqueue_scale(MetalBuf *x, float alpha, int n);   /* x[i] *= alpha, fp32 */
+/* One position per row of logits [N, V]: writes new_lp [N] and dlogits [N, V] (see llmb200_train_kernels.h). */
+void metal_enqueue_grpo_policy_grad(MetalBuf *logits, MetalBuf *actions, MetalBuf *old_lp, MetalBuf *advs, MetalBuf *new_lp,
+                                    MetalBuf *dlogits, int N, int V, float clip_eps);
 
 /* ---- containers (layouts as in src/nn/wmat.h:10-56) ---- */
 typedef enum { MODEL_QWEN3, MODEL_GEMMA3 } ModelType;

@@ -164,7 +164,7 @@ class SynthSpec(C.Structure):
 SYMBOLS_MAIN = {
     "llmb200_wmat.h": ["fast_metal_init", "fast_metal_shutdown", "metal_flush", "metal_buf_create", "metal_buf_from_data",
                        "metal_buf_free", "metal_buf_ptr", "wmat_create_q8", "wmat_create_f16", "wmat_free", "wmat_convert",
-                       "norm_upload", "layers_convert_upload", "layers_free"],
+                       "norm_upload", "layers_convert_upload", "layers_free", "metal_enqueue_scale", "metal_enqueue_grpo_policy_grad"],
     "llmb200_kernels.h": ["b200_packed_row_stride", "b200_q8_pack", "b200_f16_pack", "b200_q8_unpack_blocks", "b200_matvec",
                           "b200_attn_scratch_floats", "b200_attn_decode", "b200_attn_decode_static", "b200_tp_argmax_finalize", "b200_token_plan", "b200_token_chunks", "b200_decode_token", "b200_lora_decode", "b200_argmax_rows",
                           "b200_launch_count", "b200_launch_count_add"],
@@ -186,7 +186,8 @@ SYMBOLS_MAIN = {
                                 "b200_attn_train_bwd", "b200_silu_mul_rows", "b200_silu_mul_bwd_rows", "b200_lora_add", "b200_lora_pack", "b200_xty_skinny",
                                 "b200_softmax_ce_rows", "b200_sumsq_partials", "b200_clip_adamw",
                                 "b200_rms_norm_rows_h", "b200_rms_norm_bwd_rows_h", "b200_attn_train_fwd_h",
-                                "b200_silu_mul_rows_h", "b200_silu_mul_bwd_rows_h", "b200_softmax_ce_rows_h"],
+                                "b200_silu_mul_rows_h", "b200_silu_mul_bwd_rows_h", "b200_softmax_ce_rows_h",
+                                "b200_grpo_policy_grad", "b200_scale"],
     "llmb200_sft.h": ["sft_state_create", "sft_state_free", "sft_train_step", "forward_to_logits", "sft_backward",
                       "sft_get_logits", "sft_get_dlogits", "sft_get_x_cpu", "sft_get_losses_cpu", "sft_get_seq_len",
                       "sft_get_vocab_size", "sft_get_d_model", "sft_get_lora_rank", "sft_get_n_layers",
@@ -199,7 +200,10 @@ SYMBOLS_MAIN = {
                       "llmb200_sft_forward_backward", "llmb200_sft_apply_update", "llmb200_sft_train_batch",
                       "llmb200_sft_grad_vector", "llmb200_sft_param_vector", "llmb200_sft_last_grad_norm",
                       "llmb200_sft_last_step_ms", "llmb200_sft_use_tensor_cores", "llmb200_sft_error",
-                      "llmb200_sft_export"],
+                      "llmb200_sft_export",
+                      "sft_state_create_gemma3", "sft_state_create_full", "sft_state_create_gemma3_full", "sft_is_full_param",
+                      "sft_backward_sgd", "sft_alloc_grad_accum", "sft_backward_accum", "sft_apply_grad_sgd",
+                      "sft_save_full_checkpoint", "sft_sync_lora_to_gemma3"],
 }
 SYMBOLS_SYNTH = {
     "llmb200_synth.h": ["llmb200_synth_tensor_id", "llmb200_synth_normal_range", "llmb200_synth_normal",
@@ -300,6 +304,8 @@ def lib():
         "b200_silu_mul_rows_h": (i, [vp, i, i, vp, vp, vp]),
         "b200_silu_mul_bwd_rows_h": (i, [vp, vp, i, i, vp, vp, fl, vp]),
         "b200_softmax_ce_rows_h": (i, [vp, vp, i, i, fl, vp, vp, vp, fl, vp]),
+        "b200_grpo_policy_grad": (i, [vp, vp, vp, vp, vp, vp, i, i, fl, vp]),
+        "b200_scale": (i, [vp, fl, sz, vp]),
         # ---- llmb200_sft.h
         "sft_state_create": (vp, [vp, i, i, fl]), "sft_state_free": (None, [vp]),
         "sft_train_step": (fl, [vp, c_u32_p, c_u32_p, fl]),
@@ -326,6 +332,13 @@ def lib():
         "llmb200_sft_last_grad_norm": (fl, [vp]), "llmb200_sft_last_step_ms": (fl, [vp, c_float_p]),
         "llmb200_sft_use_tensor_cores": (i, [vp, i]), "llmb200_sft_error": (i, [vp]),
         "llmb200_sft_export": (sz, [vp, i, i, vp, sz]),
+        "sft_state_create_gemma3": (vp, [vp, i, i, fl]), "sft_state_create_full": (vp, [vp, i]),
+        "sft_state_create_gemma3_full": (vp, [vp, i]), "sft_is_full_param": (i, [vp]),
+        "sft_backward_sgd": (None, [vp, fl]), "sft_alloc_grad_accum": (None, [vp]), "sft_backward_accum": (None, [vp]),
+        "sft_apply_grad_sgd": (None, [vp, fl]), "sft_save_full_checkpoint": (None, [vp, C.c_char_p]),
+        "sft_sync_lora_to_gemma3": (None, [vp, vp]),
+        "metal_enqueue_scale": (None, [vp, fl, i]),
+        "metal_enqueue_grpo_policy_grad": (None, [vp, vp, vp, vp, vp, vp, i, i, fl]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

@@ -812,6 +812,96 @@ softmax_ce_rows_kernel(const float *logits, const uint32_t *targets, int vocab, 
     }
 }
 
+// ---- GRPO: PPO-clip gradient of the sampled-token log-probability w.r.t. the logits ----------------
+// One block per position (grpo_policy_grad, shaders/q8_kernels.metal:698-761): log-softmax of the row,
+// new_logprob = logit[action] - logsumexp, ratio = exp(new - old), the clip decides whether the position
+// contributes (weight = -advantage) or not (0), dlogits = weight * ratio * (softmax - onehot(action)).
+// Positions with no contribution (prompt positions carry advantage 0) are written as zeros without a
+// second pass over the logits.
+__global__ void __launch_bounds__(1024)
+grpo_policy_grad_rows_kernel(const float *logits, const uint32_t *actions, const float *old_logprobs, const float *advantages,
+                             float *new_logprobs, float *dlogits, int vocab, float clip_eps)
+{
+    __shared__ float sh_m[32], sh_s[32];
+    const size_t off = (size_t)blockIdx.x * vocab;
+    const float *lr = logits + off;
+    uint32_t action = actions[blockIdx.x];
+    if (action >= (uint32_t)vocab) action = 0;                     // never index outside the row
+    const bool vec = (vocab & 3) == 0 && ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0;
+    float m = -1e30f, sum = 0.f;
+    if (vec) {
+        const float4 *lr4 = reinterpret_cast<const float4 *>(lr);
+        for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+            const float4 v = lr4[i];
+            lse_add(m, sum, v.x); lse_add(m, sum, v.y); lse_add(m, sum, v.z); lse_add(m, sum, v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) lse_add(m, sum, lr[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m, o), so = __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mn = fmaxf(m, mo);
+        sum = sum * expf(m - mn) + so * expf(mo - mn);
+        m = mn;
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (l == 0) { sh_m[w] = m; sh_s[w] = sum; }
+    __syncthreads();
+    float M = sh_m[0];
+    for (int i = 1; i < nw; ++i) M = fmaxf(M, sh_m[i]);
+    float S = 0.f;
+    for (int i = 0; i < nw; ++i) S += sh_s[i] * expf(sh_m[i] - M);
+    const float lse = logf(S) + M;
+
+    const float new_lp = lr[action] - lse;
+    if (threadIdx.x == 0) new_logprobs[blockIdx.x] = new_lp;
+    const float adv = advantages[blockIdx.x];
+    const float ratio = expf(new_lp - old_logprobs[blockIdx.x]);
+    const float clipped = fminf(fmaxf(ratio, 1.0f - clip_eps), 1.0f + clip_eps);
+    const float weight = adv >= 0.f ? (ratio <= clipped ? -adv : 0.0f) : (ratio >= clipped ? -adv : 0.0f);
+    const float coef = weight * ratio;
+
+    float *dr = dlogits + off;
+    if (vec) {
+        const float4 *lr4 = reinterpret_cast<const float4 *>(lr);
+        for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            if (coef != 0.0f) {
+                const float4 v = lr4[i];
+                d[0] = expf(v.x - lse); d[1] = expf(v.y - lse); d[2] = expf(v.z - lse); d[3] = expf(v.w - lse);
+                if ((uint32_t)i == action / 4) d[action & 3] -= 1.0f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) d[c] *= coef;
+            }
+            reinterpret_cast<float4 *>(dr)[i] = make_float4(d[0], d[1], d[2], d[3]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+            dr[i] = coef != 0.0f ? coef * (expf(lr[i] - lse) - ((uint32_t)i == action ? 1.0f : 0.0f)) : 0.0f;
+    }
+}
+
+// x *= alpha (scale_tensor, the 1/G of the group mean in the GRPO step)
+__global__ void scale_kernel(float *x, float alpha, size_t n)
+{
+    const size_t i0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4, stride = (size_t)gridDim.x * blockDim.x * 4;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        for (size_t i = i0; i < n; i += stride) {
+            if (i + 4 <= n) {
+                float4 v = *reinterpret_cast<float4 *>(x + i);
+                v.x *= alpha; v.y *= alpha; v.z *= alpha; v.w *= alpha;
+                *reinterpret_cast<float4 *>(x + i) = v;
+            } else {
+                for (size_t j = i; j < n; ++j) x[j] *= alpha;
+            }
+        }
+    } else {
+        for (size_t i = i0; i < n; i += stride)
+            for (size_t j = i; j < n && j < i + 4; ++j) x[j] *= alpha;
+    }
+}
+
 // ---- frozen weights: binary16 values held as fp32, and their transposes ---------------------------
 __global__ void round_f16_kernel(float *w, size_t n)
 {
@@ -1235,6 +1325,27 @@ extern "C" int b200_softmax_ce_rows(const float *logits, const uint32_t *targets
                                     float grad_scale, float *losses, float *dlogits, void *stream)
 {
     return b200_softmax_ce_rows_h(logits, targets, rows, vocab, grad_scale, losses, dlogits, nullptr, 1.0f, stream);
+}
+
+extern "C" int b200_grpo_policy_grad(const float *logits, const uint32_t *actions, const float *old_logprobs,
+                                     const float *advantages, float *new_logprobs, float *dlogits, int rows, int vocab,
+                                     float clip_eps, void *stream)
+{
+    if (!logits || !actions || !old_logprobs || !advantages || !new_logprobs || !dlogits || rows <= 0 || vocab <= 0)
+        return B200_E_BADARG;
+    grpo_policy_grad_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, actions, old_logprobs, advantages,
+                                                                         new_logprobs, dlogits, vocab, clip_eps);
+    return done();
+}
+
+extern "C" int b200_scale(float *x, float alpha, size_t n, void *stream)
+{
+    if (!x) return B200_E_BADARG;
+    if (n == 0) return 0;
+    const size_t want = (n / 4 + 255) / 256;
+    const unsigned grid = (unsigned)(want < 148 * 8 ? (want ? want : 1) : 148 * 8);
+    scale_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, alpha, n);
+    return done();
 }
 
 extern "C" int b200_sumsq_partials(const float *g, size_t n, double *partials, int n_partials, void *stream)

@@ -909,6 +909,39 @@ void sft_lora_update(SFTState *s, float lr)
     update_device(s, lr, s->step_count);
 }
 
+/* ---------------------------------------------------------------- modes that are not built */
+
+static void not_provided(const char *what)
+{
+    fprintf(stderr, "[FastSFT] %s: not provided by libllmb200 (LoRA on Qwen3 is the mode that is built)\n", what);
+}
+
+SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int lora_rank, float lora_alpha)
+{
+    (void)model; (void)seq_len; (void)lora_rank; (void)lora_alpha;
+    not_provided("sft_state_create_gemma3");
+    return NULL;
+}
+SFTState *sft_state_create_full(llmb200_qwen3_model *model, int seq_len)
+{
+    (void)model; (void)seq_len;
+    not_provided("sft_state_create_full");
+    return NULL;
+}
+SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len)
+{
+    (void)model; (void)seq_len;
+    not_provided("sft_state_create_gemma3_full");
+    return NULL;
+}
+int sft_is_full_param(SFTState *s) { (void)s; return 0; }
+void sft_backward_sgd(SFTState *s, float lr) { (void)s; (void)lr; not_provided("sft_backward_sgd"); }
+void sft_alloc_grad_accum(SFTState *s) { (void)s; not_provided("sft_alloc_grad_accum"); }
+void sft_backward_accum(SFTState *s) { (void)s; not_provided("sft_backward_accum"); }
+void sft_apply_grad_sgd(SFTState *s, float lr) { (void)s; (void)lr; not_provided("sft_apply_grad_sgd"); }
+void sft_save_full_checkpoint(SFTState *s, const char *path) { (void)s; (void)path; not_provided("sft_save_full_checkpoint"); }
+void sft_sync_lora_to_gemma3(SFTState *s, llmb200_gemma3_model *m) { (void)s; (void)m; not_provided("sft_sync_lora_to_gemma3"); }
+
 /* ---------------------------------------------------------------- accessors */
 
 MetalBuf *sft_get_logits(SFTState *s) { return s ? s->mb_logits : NULL; }

@@ -144,6 +144,37 @@ void *metal_buf_ptr(MetalBuf *b)
     return b->host_mirror;
 }
 
+/* ---------------------------------------------------------------- dispatches on buffers */
+
+/* Size checks against the buffers' own sizes: a wrong count would otherwise write past a device allocation.
+ * A refused dispatch says so; the caller's next read of the output sees it unchanged. */
+static int buf_holds(const MetalBuf *b, size_t bytes) { return b && b->dev && b->size >= bytes; }
+
+void metal_enqueue_scale(MetalBuf *x, float alpha, int n)
+{
+    if (n <= 0) return;
+    if (!buf_holds(x, (size_t)n * 4)) {
+        fprintf(stderr, "[llmb200] metal_enqueue_scale: buffer smaller than %d floats\n", n);
+        return;
+    }
+    K_TRY(b200_scale((float *)x->dev, alpha, (size_t)n, g_rt.stream), return);
+}
+
+void metal_enqueue_grpo_policy_grad(MetalBuf *logits, MetalBuf *actions, MetalBuf *old_lp, MetalBuf *advs, MetalBuf *new_lp,
+                                    MetalBuf *dlogits, int N, int V, float clip_eps)
+{
+    if (N <= 0 || V <= 0) return;
+    const size_t nv = (size_t)N * (size_t)V * 4, n4 = (size_t)N * 4;
+    if (!buf_holds(logits, nv) || !buf_holds(dlogits, nv) || !buf_holds(actions, n4) || !buf_holds(old_lp, n4) ||
+        !buf_holds(advs, n4) || !buf_holds(new_lp, n4)) {
+        fprintf(stderr, "[llmb200] metal_enqueue_grpo_policy_grad: a buffer is missing or smaller than N = %d, V = %d need\n", N, V);
+        return;
+    }
+    K_TRY(b200_grpo_policy_grad((const float *)logits->dev, (const uint32_t *)actions->dev, (const float *)old_lp->dev,
+                                (const float *)advs->dev, (float *)new_lp->dev, (float *)dlogits->dev, N, V, clip_eps,
+                                g_rt.stream), return);
+}
+
 /* ---------------------------------------------------------------- upload */
 
 int llmb200_upload_packed(int wtype, const float *src, long long ld, int rows, int col0, int cols,

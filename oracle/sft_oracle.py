@@ -156,6 +156,29 @@ def softmax_ce(logits, targets):
 
 # ---- forward / backward over one sequence ----------------------------------------------------------
 
+def grpo_policy_grad(logits, actions, old_logprobs, advantages, clip_eps):
+    """grpo_policy_grad, shaders/q8_kernels.metal:698-761, one row per position: returns (new_logprobs [N],
+    dlogits [N, V]). PPO clip: a position whose ratio already sits on the far side of the clip interval
+    (above 1 + eps with a positive advantage, below 1 - eps with a negative one) contributes nothing.
+    Pinned together with the step that uses it: tests/golden/grpo_golden.bin is the record of the reference's
+    own src/nn/fast_grpo.c over its engines on the CPU stand-in for the Metal layer, and the `new log-prob`
+    and gradient sections of that record come out of the C restatement of this kernel
+    (oracle/fast_metal_cpu.c)."""
+    logits = np.asarray(logits, dtype=np.float32)
+    n, v = logits.shape
+    mx = logits.max(axis=1, keepdims=True)
+    lse = (np.log(np.exp(logits - mx, dtype=np.float32).sum(axis=1, dtype=np.float32)) + mx[:, 0]).astype(np.float32)
+    a = np.asarray(actions, dtype=np.int64)
+    new_lp = (logits[np.arange(n), a] - lse).astype(np.float32)
+    ratio = np.exp(new_lp - np.asarray(old_logprobs, dtype=np.float32), dtype=np.float32)
+    clipped = np.clip(ratio, np.float32(1.0 - clip_eps), np.float32(1.0 + clip_eps))
+    adv = np.asarray(advantages, dtype=np.float32)
+    weight = np.where(adv >= 0, np.where(ratio <= clipped, -adv, 0.0), np.where(ratio >= clipped, -adv, 0.0)).astype(np.float32)
+    prob = np.exp(logits - lse[:, None], dtype=np.float32)
+    prob[np.arange(n), a] -= 1.0
+    return new_lp, ((weight * ratio)[:, None] * prob).astype(np.float32)
+
+
 def forward(w, lora, tokens, dtype=np.float32):
     """forward_to_logits (fast_sft.c:616-752) after the embedding gather of sft_train_step (:1118-1120).
     Returns (logits [N,V], saves)."""

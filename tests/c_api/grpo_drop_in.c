@@ -1,0 +1,118 @@
+/*
+ * The reference's GRPO step on top of the drop-in library: src/nn/fast_grpo.c runs unchanged
+ * (oracle/_ref/libllmref_grpo.so, see oracle/grpo_caller.c) and everything it calls --
+ * sft_state_create, inference_state_create_from_sft, inference_forward_token, forward_to_logits,
+ * metal_enqueue_grpo_policy_grad, metal_enqueue_scale, sft_backward, sft_set_lora_grad,
+ * sft_lora_update, sft_save_lora -- comes from the library the executable is linked with:
+ *
+ *     _bin/grpo_b200   libllmb200.so (the CUDA engines)
+ *     _bin/grpo_ref    the reference's own engines over the CPU stand-in for its Metal layer
+ *
+ * Both write the same record file (argv[1]): per step the sampled tokens, their log-probabilities,
+ * rewards, advantages and the LoRA gradients summed over the group, then the adapter after the last
+ * step. tests/golden/grpo_golden.bin is the record of grpo_ref; the GPU test compares grpo_b200 with it.
+ *
+ * Exit codes: 0 ok, 3 the state could not be created (no CUDA device), 1 anything else.
+ */
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "nn/qwen3.h"
+#include "nn/fast_sft.h"
+#include "nn/fast_grpo.h"
+
+/* oracle/grpo_caller.c */
+int grpo_dbg_gen_len(const GRPOState *g, int i);
+const uint32_t *grpo_dbg_tokens(const GRPOState *g, int i);
+const float *grpo_dbg_logprobs(const GRPOState *g, int i);
+float grpo_dbg_reward(const GRPOState *g, int i);
+float grpo_dbg_advantage(const GRPOState *g, int i);
+int grpo_dbg_n_grad_bufs(const GRPOState *g);
+const float *grpo_dbg_accum_grad(const GRPOState *g, int b, int *size);
+const float *grpo_dbg_new_logprobs(GRPOState *g);
+SFTState *grpo_dbg_sft(GRPOState *g);
+
+enum { GROUP = 4, MAX_GEN = 8, SEQ = 16, PROMPT = 8, RANK = 4, STEPS = 2 };
+enum { K_REWARD = 1, K_LEN = 2, K_TOKENS = 3, K_LOGPROBS = 4, K_REWARDS = 5, K_ADVANTAGES = 6, K_GRADS = 7, K_NEW_LP = 8,
+       K_ADAPTER = 9 };
+
+static FILE *out;
+static void section(int kind, const float *v, int n)
+{
+    const int32_t head[2] = {kind, n};
+    fwrite(head, 4, 2, out);
+    fwrite(v, 4, (size_t)n, out);
+}
+
+int main(int argc, char **argv)
+{
+    if (argc < 2) { fprintf(stderr, "usage: %s <record file>\n", argv[0]); return 1; }
+    srand(11);
+    Qwen3Config cfg = { .n_layers = 2, .d_model = 256, .n_q_heads = 4, .n_kv_heads = 2, .head_dim = 64,
+                        .intermediate_size = 512, .vocab_size = 64, .rope_theta = 1e6f, .rms_norm_eps = 1e-6f };
+    Qwen3Model *model = qwen3_create(cfg);
+    if (!model) return 1;
+    GRPOConfig gc = { .group_size = GROUP, .max_gen_len = MAX_GEN, .temperature = 0.7f, .clip_eps = 0.2f,
+                      .reward = "combined", .accurate = 0 };
+    GRPOState *g = grpo_state_create(model, gc, SEQ, RANK, 8.0f, NULL);
+    if (!g) return 3;
+    out = fopen(argv[1], "wb");
+    if (!out) return 1;
+
+    /* the sampler draws from rand(); the default seed is one whose groups end on the EOS id 1 at different
+     * lengths in both steps, so that rewards differ inside a group and the gradients are not all zero */
+    srand(argc > 2 ? (unsigned)atoi(argv[2]) : 5u);
+    uint32_t prompt[PROMPT];
+    for (int i = 0; i < PROMPT; ++i) prompt[i] = (uint32_t)(2 + rand() % (cfg.vocab_size - 2));
+    float buf[GROUP * MAX_GEN];
+    for (int step = 0; step < STEPS; ++step) {
+        const float mean_reward = grpo_train_step(g, prompt, PROMPT, 1e-2f);
+        if (!isfinite(mean_reward)) { fprintf(stderr, "GRPO_DROP_IN failed: mean reward not finite\n"); return 1; }
+        section(K_REWARD, &mean_reward, 1);
+        for (int i = 0; i < GROUP; ++i) buf[i] = (float)grpo_dbg_gen_len(g, i);
+        section(K_LEN, buf, GROUP);
+        memset(buf, 0, sizeof buf);
+        for (int i = 0; i < GROUP; ++i)
+            for (int t = 0; t < grpo_dbg_gen_len(g, i); ++t) buf[i * MAX_GEN + t] = (float)grpo_dbg_tokens(g, i)[t];
+        section(K_TOKENS, buf, GROUP * MAX_GEN);
+        memset(buf, 0, sizeof buf);
+        for (int i = 0; i < GROUP; ++i)
+            for (int t = 0; t < grpo_dbg_gen_len(g, i); ++t) buf[i * MAX_GEN + t] = grpo_dbg_logprobs(g, i)[t];
+        section(K_LOGPROBS, buf, GROUP * MAX_GEN);
+        for (int i = 0; i < GROUP; ++i) buf[i] = grpo_dbg_reward(g, i);
+        section(K_REWARDS, buf, GROUP);
+        for (int i = 0; i < GROUP; ++i) buf[i] = grpo_dbg_advantage(g, i);
+        section(K_ADVANTAGES, buf, GROUP);
+        for (int b = 0; b < grpo_dbg_n_grad_bufs(g); ++b) {
+            int n = 0;
+            const float *a = grpo_dbg_accum_grad(g, b, &n);
+            section(K_GRADS, a, n);
+        }
+        section(K_NEW_LP, grpo_dbg_new_logprobs(g), SEQ);
+    }
+
+    /* the adapter as the reference saves it (12-byte header, then the matrices) */
+    char path[512];
+    snprintf(path, sizeof path, "%s.lora", argv[1]);
+    grpo_save_lora(g, path);
+    FILE *fp = fopen(path, "rb");
+    if (!fp) { fprintf(stderr, "GRPO_DROP_IN failed: adapter file\n"); return 1; }
+    fseek(fp, 0, SEEK_END);
+    const long bytes = ftell(fp) - 12;
+    fseek(fp, 12, SEEK_SET);
+    float *w = malloc((size_t)bytes);
+    if (!w || fread(w, 1, (size_t)bytes, fp) != (size_t)bytes) { fprintf(stderr, "GRPO_DROP_IN failed: adapter read\n"); return 1; }
+    fclose(fp);
+    remove(path);
+    section(K_ADAPTER, w, (int)(bytes / 4));
+    free(w);
+    fclose(out);
+
+    if (sft_is_full_param(grpo_dbg_sft(g))) { fprintf(stderr, "GRPO_DROP_IN failed: LoRA state reads as full-parameter\n"); return 1; }
+    grpo_state_free(g);
+    qwen3_free(model);
+    printf("GRPO_DROP_IN ok\n");
+    return 0;
+}

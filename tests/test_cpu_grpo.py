@@ -1,0 +1,84 @@
+"""The GRPO step (the reference's src/nn/fast_grpo.c as a caller of the drop-in library), CPU side: the
+committed record of the reference run is what the reference produces here, it exercises the step (rewards
+differ inside the groups, gradients are not zero), the numpy restatement of the policy-gradient kernel has the
+properties its formula implies, and the CUDA build of the same program stops loudly without a GPU."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+import sft_oracle as o  # noqa: E402
+import _grpo_record as gr  # noqa: E402
+
+GOLDEN = os.path.join(ROOT, "tests", "golden", "grpo_golden.bin")
+REF_BIN = os.path.join(ROOT, "tests", "c_api", "_bin", "grpo_ref")
+B200_BIN = os.path.join(ROOT, "tests", "c_api", "_bin", "grpo_b200")
+
+
+def test_golden_record_exercises_the_step():
+    steps, adapter = gr.by_step(gr.read(GOLDEN))
+    assert len(steps) == gr.STEPS and adapter is not None and np.abs(adapter).max() > 0
+    for st in steps:
+        assert st[gr.REWARDS].std() > 0, "equal rewards give zero advantages and an all-zero gradient"
+        assert abs(float(st[gr.ADVANTAGES].mean())) < 1e-5
+        assert abs(float(st[gr.REWARD][0]) - float(st[gr.REWARDS].mean())) < 1e-6
+        lens = st[gr.LEN].astype(int)
+        assert ((lens >= 1) & (lens <= gr.MAX_GEN)).all() and len(set(lens.tolist())) > 1
+        assert max(float(np.abs(g).max()) for g in st[gr.GRADS]) > 1e-2
+        lp = st[gr.LOGPROBS].reshape(gr.GROUP, gr.MAX_GEN)
+        for i, n in enumerate(lens):
+            assert (lp[i, :n] < 0).all() and (lp[i, n:] == 0).all()
+    # B starts at zero: the first step has no gradient on A (dA = (dq B^T ...)), the second has
+    assert all(np.abs(g).max() == 0 for g in steps[0][gr.GRADS][0::2])
+    assert all(np.abs(g).max() > 0 for g in steps[1][gr.GRADS])
+
+
+@pytest.mark.skipif(not os.path.exists(REF_BIN), reason="tests/c_api/_bin/grpo_ref was not built (reference tree absent)")
+def test_golden_record_is_what_the_reference_run_writes(tmp_path):
+    """The reference's own fast_grpo.c, fast_sft.c and fast_inference.c over the CPU stand-in for the Metal layer."""
+    out = str(tmp_path / "ref.bin")
+    r = subprocess.run([REF_BIN, out], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+    assert r.returncode == 0 and "GRPO_DROP_IN ok" in r.stdout, r.stderr[-800:]
+    assert open(out, "rb").read() == open(GOLDEN, "rb").read()
+
+
+def test_policy_gradient_restatement_properties():
+    """oracle.grpo_policy_grad: rows sum to zero, clipped positions and zero advantages give zero rows, the
+    unclipped gradient is -advantage * ratio * d(log p_action)/d(logits)."""
+    rng = np.random.default_rng(3)
+    n, v = 12, 50
+    logits = rng.standard_normal((n, v)).astype(np.float32) * 3
+    actions = rng.integers(0, v, n)
+    logp = logits - np.log(np.exp(logits.astype(np.float64)).sum(1, keepdims=True))
+    true_lp = logp[np.arange(n), actions].astype(np.float32)
+    old = true_lp.copy()
+    adv = rng.standard_normal(n).astype(np.float32)
+    old[0] -= 0.5; adv[0] = 1.0        # ratio 1.65 > 1.2, positive advantage: clipped away
+    old[1] += 0.5; adv[1] = -1.0       # ratio 0.61 < 0.8, negative advantage: clipped away
+    old[2] -= 0.5; adv[2] = -1.0       # ratio high, negative advantage: kept
+    old[3] += 0.5; adv[3] = 1.0        # ratio low, positive advantage: kept
+    adv[4] = 0.0
+    new_lp, d = o.grpo_policy_grad(logits, actions, old, adv, 0.2)
+    assert np.abs(new_lp - true_lp).max() < 1e-5
+    assert np.abs(d.sum(1)).max() < 1e-5
+    assert (d[0] == 0).all() and (d[1] == 0).all() and (d[4] == 0).all()
+    for r in (2, 3, 5, 6):
+        ratio = np.exp(true_lp[r] - old[r])
+        want = -adv[r] * ratio * (-np.exp(logp[r]))
+        want[actions[r]] += -adv[r] * ratio
+        assert np.abs(d[r] + want).max() < 1e-5 * max(1.0, np.abs(want).max()), r
+
+
+@pytest.mark.skipif(not os.path.exists(B200_BIN), reason="tests/c_api/_bin/grpo_b200 was not built (reference tree absent)")
+def test_cuda_build_of_the_program_fails_loudly_without_a_gpu(tmp_path):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the GPU suite runs the program for real")
+    r = subprocess.run([B200_BIN, str(tmp_path / "x.bin")], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert r.returncode == 3, (r.returncode, r.stderr[-500:])
+    assert "no CUDA device available" in r.stderr and "no CPU path" in r.stderr
+    assert "GRPO_DROP_IN ok" not in r.stdout
