@@ -3,11 +3,10 @@
  *
  * Part 1 declares, under the reference's names and with the same argument
  * meaning, the LoRA subset of llm.metal's fast SFT engine
- * (src/nn/fast_sft.h:14-111; implementation src/nn/fast_sft.c). The Gemma3
- * and full-parameter modes are not built: their constructors exist, so that a
- * caller written for all modes (src/nn/fast_grpo.c) links, and refuse with a
- * message and NULL; sft_is_full_param answers 0 for every state this library
- * can make.
+ * (src/nn/fast_sft.h:14-111; implementation src/nn/fast_sft.c): LoRA and
+ * full-parameter training of Qwen3. The Gemma3 modes are not built: their
+ * constructors exist, so that a caller written for all modes
+ * (src/nn/fast_grpo.c) links, and refuse with a message and NULL.
  *
  * Part 2 is additive: layer-by-layer construction, several sequences per
  * step (their LoRA gradients are averaged, then one clip + AdamW as in the
@@ -104,19 +103,34 @@ int sft_get_head_dim(SFTState *state);
 int sft_get_intermediate_size(SFTState *state);
 const float *sft_get_rope_thetas(SFTState *state);
 
-/* ---- modes that are not built (src/nn/fast_sft.h:17-41, 55) ----
- * The constructors print "[FastSFT] ... not provided" and return NULL, like any other failed create.
- * No state of these kinds can therefore reach the other calls; given one anyway they print the same
- * message and change nothing. sft_is_full_param is 0 for every state made by sft_state_create. */
-SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int lora_rank, float lora_alpha);
+/* ---- full-parameter mode (src/nn/fast_sft.h:21-41) ----
+ * sft_state_create_full: no adapter; q, k, v, o, gate, up, down of every layer and the LM head are trained by
+ * plain SGD on their binary16 values (src/nn/fast_sft.c:402-501). Held as fp32 copies of binary16 values; every
+ * product of such a state runs in fp32 on the CUDA cores. On such a state
+ *   sft_train_step        forward, loss, and a backward pass that steps each weight as its gradient is formed:
+ *                         W <- half(W - lr dY^T X) (f16_sgd_fused, q8_kernels.metal:1097-1125); q, k, v step
+ *                         before the gradient goes on through them, the others after (:766-982). No optimizer
+ *                         state, the step count stays.
+ *   sft_backward_sgd      that backward pass alone, from the gradient in sft_get_dlogits().
+ *   sft_alloc_grad_accum  binary16 accumulators for every matrix, zeroed (:996-1019). From then on every
+ *                         backward pass of the state (sft_train_step and sft_backward_sgd included, as in the
+ *                         reference) adds G <- half(G + dY^T X) (f16_grad_accum, :1164-1191) and moves no weight.
+ *   sft_backward_accum    the accumulating backward pass (:986).
+ *   sft_apply_grad_sgd    W <- half(W - lr G), G <- 0 (f16_sgd_apply, :1195-1206; :1021-1039).
+ *   sft_save_full_checkpoint   "FULL" header of nine words, then every matrix as binary16 (:1287-1343).
+ * A decode state made from the state (inference_state_create_from_sft) follows the stepped weights. */
 SFTState *sft_state_create_full(llmb200_qwen3_model *model, int seq_len);
-SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len);
 int  sft_is_full_param(SFTState *state);
 void sft_backward_sgd(SFTState *state, float lr);
 void sft_alloc_grad_accum(SFTState *state);
 void sft_backward_accum(SFTState *state);
 void sft_apply_grad_sgd(SFTState *state, float lr);
 void sft_save_full_checkpoint(SFTState *state, const char *path);
+
+/* ---- modes that are not built (src/nn/fast_sft.h:17-19, 23, 55): Gemma3 ----
+ * The constructors print "[FastSFT] ... not provided" and return NULL, like any other failed create. */
+SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int lora_rank, float lora_alpha);
+SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len);
 void sft_sync_lora_to_gemma3(SFTState *state, llmb200_gemma3_model *model);
 
 /* ========================= Part 2: additions ============================== */

@@ -152,6 +152,10 @@ int b200_softmax_ce_rows(const float *logits, const uint32_t *targets, int rows,
 int b200_grpo_policy_grad(const float *logits, const uint32_t *actions, const float *old_logprobs, const float *advantages,
                           float *new_logprobs, float *dlogits, int rows, int vocab, float clip_eps, void *stream);
 
+/* f16_sgd_apply (shaders/q8_kernels.metal:1195-1206) for weights and accumulated gradients kept as fp32
+ * holders of binary16 values: w[i] = half(w[i] - lr * g[i]); g[i] = 0. */
+int b200_sgd_apply_f16(float *w, float *g, size_t n, float lr, void *stream);
+
 /* scale_tensor (fast_metal.m:722-731): x[i] *= alpha for i < n. */
 int b200_scale(float *x, float alpha, size_t n, void *stream);
 

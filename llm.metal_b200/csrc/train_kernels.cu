@@ -882,6 +882,16 @@ grpo_policy_grad_rows_kernel(const float *logits, const uint32_t *actions, const
     }
 }
 
+// f16_sgd_apply (shaders/q8_kernels.metal:1195-1206) on fp32 holders of binary16 values:
+// w <- half(w - lr * g), g <- 0
+__global__ void sgd_apply_f16_kernel(float *w, float *g, size_t n, float lr)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        w[i] = __half2float(__float2half_rn(w[i] - lr * g[i]));
+        g[i] = 0.0f;
+    }
+}
+
 // x *= alpha (scale_tensor, the 1/G of the group mean in the GRPO step)
 __global__ void scale_kernel(float *x, float alpha, size_t n)
 {
@@ -1335,6 +1345,16 @@ extern "C" int b200_grpo_policy_grad(const float *logits, const uint32_t *action
         return B200_E_BADARG;
     grpo_policy_grad_rows_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(logits, actions, old_logprobs, advantages,
                                                                          new_logprobs, dlogits, vocab, clip_eps);
+    return done();
+}
+
+extern "C" int b200_sgd_apply_f16(float *w, float *g, size_t n, float lr, void *stream)
+{
+    if (!w || !g) return B200_E_BADARG;
+    if (n == 0) return 0;
+    const size_t want = (n + 255) / 256;
+    const unsigned grid = (unsigned)(want < 148 * 8 ? want : 148 * 8);
+    sgd_apply_f16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w, g, n, lr);
     return done();
 }
 

@@ -96,6 +96,8 @@ struct InferenceState {
     struct { const float *A_q, *B_q, *A_v, *B_v; } *lora;
     int lora_rank;
     float lora_scaling;
+    SFTState *sft_src;                    /* the SFT state whose matrices this state copied, or NULL */
+    unsigned long long sft_version;       /* its weights_version at the time of the copy */
     float *xnorm;            /* [D]: the normalised layer input, kept by the q/k/v matvec for the LoRA kernel */
     int cur_len;
     double last_decode_ms, last_prefill_ms;
@@ -841,6 +843,44 @@ static float *clone_f32(const void *d_src, size_t n)
     return p;
 }
 
+/* The seven projections of every layer and the LM head, re-laid for the decode kernels by device-to-device
+ * copies from the SFT state's views. Also run again whenever full-parameter training has changed them. */
+static int take_sft_matrices(InferenceState *s, SFTState *sft)
+{
+    LayerW *lw = sft_get_layers(sft);
+    WMat *lm = sft_get_lm_head(sft);
+    if (!lw || !lm) return -1;
+    llmb200_sft_refresh_views(sft);
+    const int D = s->D, ql = s->Hq * s->hd, kl = s->Hkv * s->hd;
+    int rc = 0;
+    for (int i = 0; i < s->L && !rc; ++i) {
+        Layer *ly = &s->layers[i];
+        const LayerW *r = &lw[i];
+        rc |= share_rows(r->q_proj, 0, D, &ly->qkv, 0, 1);
+        rc |= share_rows(r->k_proj, 0, D, &ly->qkv, ql, 1);
+        rc |= share_rows(r->v_proj, 0, D, &ly->qkv, ql + kl, 1);
+        rc |= share_rows(r->o_proj, 0, ql, &ly->o, 0, 1);
+        rc |= share_rows(r->gate_proj, 0, D, &ly->gateup, 0, 2);
+        rc |= share_rows(r->up_proj, 0, D, &ly->gateup, 1, 2);
+        rc |= share_rows(r->down_proj, 0, s->IS, &ly->down, 0, 1);
+    }
+    if (!rc) rc = share_rows(lm, 0, D, &s->lm, 0, 1);
+    s->sft_src = sft;
+    s->sft_version = llmb200_sft_weights_version(sft);
+    return rc;
+}
+
+/* The reference's decode state aliases the SFT state's buffers, so a full-parameter step shows in the next
+ * token; here the matrices are copies in the decode layout, taken again when the SFT state says they changed.
+ * The SFT state must outlive the decode state made from it (as in the reference). */
+static void follow_sft(InferenceState *s)
+{
+    if (!s || !s->sft_src || llmb200_sft_weights_version(s->sft_src) == s->sft_version) return;
+    if (take_sft_matrices(s, s->sft_src) != 0) {
+        fprintf(stderr, "[FastGen] re-reading the SFT state's weights failed\n");
+    }
+}
+
 /* A decode state over the weights an SFT state already holds on the device, with that state's LoRA attached
  * (read in place, so decoding follows training). The frozen matrices are re-laid for the decode kernels by
  * device-to-device copies -- no host round trip, no second conversion; they never change in LoRA training, so
@@ -868,18 +908,11 @@ InferenceState *inference_state_create_from_sft(SFTState *sft, int max_seq_len)
         inference_state_free(s);
         return NULL;
     }
-    const int D = s->D, hd = s->hd, ql = s->Hq * hd, kl = s->Hkv * hd;
-    int rc = 0;
+    const int D = s->D, hd = s->hd;
+    int rc = take_sft_matrices(s, sft);
     for (int i = 0; i < s->L && !rc; ++i) {
         Layer *ly = &s->layers[i];
         const LayerW *r = &lw[i];
-        rc |= share_rows(r->q_proj, 0, D, &ly->qkv, 0, 1);
-        rc |= share_rows(r->k_proj, 0, D, &ly->qkv, ql, 1);
-        rc |= share_rows(r->v_proj, 0, D, &ly->qkv, ql + kl, 1);
-        rc |= share_rows(r->o_proj, 0, ql, &ly->o, 0, 1);
-        rc |= share_rows(r->gate_proj, 0, D, &ly->gateup, 0, 2);
-        rc |= share_rows(r->up_proj, 0, D, &ly->gateup, 1, 2);
-        rc |= share_rows(r->down_proj, 0, s->IS, &ly->down, 0, 1);
         ly->g_input = clone_f32(r->input_norm_g->dev, (size_t)D);
         ly->g_post_attn = clone_f32(r->post_attn_norm_g->dev, (size_t)D);
         ly->g_qn = r->q_norm_g ? clone_f32(r->q_norm_g->dev, (size_t)hd) : NULL;
@@ -893,7 +926,6 @@ InferenceState *inference_state_create_from_sft(SFTState *sft, int max_seq_len)
         ly->rope_theta = thetas[i];
         ly->loaded = 1;
     }
-    if (!rc) rc = share_rows(lm, 0, D, &s->lm, 0, 1);
     if (!rc) {
         s->g_final = clone_f32(fg->dev, (size_t)D);
         s->emb = clone_f32(d_emb, (size_t)s->V * D);
@@ -1055,6 +1087,7 @@ static int set_control(InferenceState *s, int pos, int prompt_len, const uint32_
 
 static const float *forward_token_one(InferenceState *s, int token)
 {
+    follow_sft(s);
     if (!s || ensure_graphs(s) != 0) return NULL;
     if (s->cur_len >= s->max_seq) { fprintf(stderr, "[FastGen] KV cache is full (%d positions)\n", s->max_seq); return NULL; }
     if (token < 0 || token >= s->V) { fprintf(stderr, "[FastGen] token id %d out of range\n", token); return NULL; }
@@ -1086,6 +1119,7 @@ static int is_eos(const InferenceState *s, int tok)
 static int generate_one(InferenceState *s, const uint32_t *prompt, int prompt_len, uint32_t *out, int max_gen_len)
 {
     if (!s || !prompt || !out || prompt_len <= 0 || max_gen_len <= 0) return 0;
+    follow_sft(s);
     if (ensure_graphs(s) != 0) return 0;
     if (prompt_len > s->max_seq) {
         fprintf(stderr, "[FastGen] prompt of %d tokens exceeds the KV cache (%d)\n", prompt_len, s->max_seq);

@@ -88,5 +88,9 @@ MetalBuf *llmb200_buf_wrap(void *dev, size_t size);
 /* The embedding table of an SFT state on the device (decode states built from it copy it). */
 struct SFTState;
 const float *llmb200_sft_device_emb(struct SFTState *s);
+/* Full-parameter training changes the matrices a decode state copied from an SFT state: a count of the
+ * changes, and the SFT state's weight views brought up to date before they are copied again. */
+unsigned long long llmb200_sft_weights_version(struct SFTState *s);
+void llmb200_sft_refresh_views(struct SFTState *s);
 
 #endif

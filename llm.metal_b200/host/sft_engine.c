@@ -49,6 +49,7 @@ typedef struct {
     float *x_in, *ln1, *qkv_out, *q_f, *k_f, *probs, *x_mid, *ln2, *gu_out;
     float *mid_q, *mid_v;               /* columns QKV.. of qkv_out (row stride QKVX), not separate buffers */
     size_t lora_off;                    /* offset of this layer in the flat LoRA vectors */
+    float *acc[4];                      /* full-parameter mode: gradient accumulators of qkv, o, gu, down (binary16 values) */
     MetalBuf *lora_buf[4];              /* handles made on demand by sft_get_lora_weight_buf */
     int loaded;
 } SftLayer;
@@ -60,6 +61,13 @@ struct SFTState {
     float eps, lora_scaling, emb_scale;
     int lora_rank, step_count, model_type;
     int use_tc, err, finished;
+    /* Full-parameter mode (sft_state_create_full): no LoRA (rank 0); every projection and the LM head are
+     * trained by plain SGD inside the backward pass. wmode says what a backward pass does with a weight
+     * gradient dW = dY^T X: 0 nothing, 1 W <- half(W - lr dW) at once, 2 G <- half(G + dW) into accumulators. */
+    int full_param, wmode;
+    float sgd_lr;
+    float *acc_lm;
+    unsigned long long weights_version;   /* counts changes of the base matrices: a decode state made from this one re-reads them */
     float *rope_thetas;
 
     SftLayer *layers;
@@ -263,9 +271,9 @@ static void gemm_small(SFTState *s, const float *A, long long a_row, long long a
 
 /* ---------------------------------------------------------------- create */
 
-SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, int lora_rank, float lora_alpha)
+static SFTState *sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, int lora_rank, float lora_alpha, int full_param)
 {
-    if (!cfg || seq_len <= 0 || n_seq <= 0 || lora_rank <= 0 || lora_rank > 64) {
+    if (!cfg || seq_len <= 0 || n_seq <= 0 || lora_rank < (full_param ? 0 : 1) || lora_rank > 64 || (full_param && lora_rank)) {
         fprintf(stderr, "[FastSFT] bad arguments (seq_len %d, sequences %d, rank %d; rank must be 1..64)\n", seq_len,
                 n_seq, lora_rank);
         return NULL;
@@ -296,12 +304,15 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     s->emb_scale = 1.0f;
     s->eps = 1e-6f;
     s->lora_rank = lora_rank;
-    s->lora_scaling = lora_alpha / (float)lora_rank;
+    s->lora_scaling = lora_rank ? lora_alpha / (float)lora_rank : 0.0f;
+    s->full_param = full_param;
     /* Tensor cores need 16-byte operand rows (dimensions in multiples of 8 halves) and at least 16 x 64
      * outputs; otherwise, or with LLMB200_SFT_TC=0, every product runs on the CUDA cores in fp32. */
     const char *tc = getenv("LLMB200_SFT_TC");
     s->use_tc = !(tc && tc[0] == '0') && s->M >= 16 && s->D >= 64 && s->V >= 64 && !(s->D % 8) && !(s->Hq_hd % 8) &&
                 !(s->Hkv_hd % 8) && !(s->IS % 8);
+    /* the weight gradients and their SGD steps are fp32 products over fp32 activations: CUDA-core mode */
+    if (full_param) s->use_tc = 0;
     /* gradients reach at most 1/M (the loss scale) at the logits: 8 * M rounded up to a power of two maps
      * them to ~8 in binary16 and leaves four decades below before the subnormals start */
     s->gscale = 8.0f;
@@ -324,7 +335,7 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
         cudaMemsetAsync(s->lora_m, 0, s->n_lora * 4, g_rt.stream);
         cudaMemsetAsync(s->lora_v, 0, s->n_lora * 4, g_rt.stream);
     }
-    if (cudaMallocHost((void **)&s->h_grad, s->n_lora * 4) != cudaSuccess) s->err = -10;
+    if (cudaMallocHost((void **)&s->h_grad, (s->n_lora ? s->n_lora : 1) * 4) != cudaSuccess) s->err = -10;
 
     for (int L = 0; L < s->NL && !s->err; ++L) {
         SftLayer *l = &s->layers[L];
@@ -391,6 +402,11 @@ SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, i
     return s;
 }
 
+SFTState *llmb200_sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, int lora_rank, float lora_alpha)
+{
+    return sft_begin(cfg, seq_len, n_seq, lora_rank, lora_alpha, 0);
+}
+
 static int upload_small(float *d, const float *src, size_t n)
 {
     return src ? llmb200_upload_f32_into(d, src, n) : B200_E_BADARG;
@@ -438,6 +454,7 @@ int llmb200_sft_load_layer(SFTState *s, int L, const LayerWeightRef *r, float ro
     for (int sub = 0; sub < 4 && !rc; ++sub) {
         float *dst = s->lora_p + l->lora_off + s->sub_off[sub];
         const size_t n = s->sizes[sub];
+        if (n == 0) continue;                                    /* full-parameter mode: no LoRA, no rand() drawn */
         if (lora && lora[sub]) {
             rc = llmb200_upload_f32_into(dst, lora[sub], n);
         } else if (sub == 0 || sub == 2) {
@@ -476,16 +493,17 @@ int llmb200_sft_finish(SFTState *s, const float *lm_head, const float *final_nor
     return rc;
 }
 
-SFTState *sft_state_create(llmb200_qwen3_model *m, int seq_len, int lora_rank, float lora_alpha)
+static SFTState *create_from_qwen3(llmb200_qwen3_model *m, int seq_len, int lora_rank, float lora_alpha, int full_param)
 {
     if (!m) return NULL;
     struct timespec t0, t1;
     clock_gettime(CLOCK_MONOTONIC, &t0);
-    printf("[FastSFT] Converting weights to F16...\n");
+    printf(full_param ? "[FastSFT] Converting Qwen3 weights to F16 (full-param)...\n" : "[FastSFT] Converting weights to F16...\n");
     llmb200_config cfg = { MODEL_QWEN3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
                            m->vocab_size, m->n_layers, seq_len, 1 };
-    SFTState *s = llmb200_sft_begin(&cfg, seq_len, 1, lora_rank, lora_alpha);
+    SFTState *s = sft_begin(&cfg, seq_len, 1, lora_rank, lora_alpha, full_param);
     if (!s) return NULL;
+    if (full_param) s->step_graph_state = -1;      /* the learning rate is an argument of every step's kernels: no replay */
     const int Hq_hd = s->Hq_hd, Hkv_hd = s->Hkv_hd;
     for (int i = 0; i < s->NL; ++i) {
         llmb200_qwen3_block *b = m->blocks[i];
@@ -505,8 +523,8 @@ SFTState *sft_state_create(llmb200_qwen3_model *m, int seq_len, int lora_rank, f
         r.d_model = s->D;
         r.head_dim = s->hd;
         const float *lora[4] = { NULL, NULL, NULL, NULL };
-        if (m->q_loras && m->q_loras[i]) { lora[0] = m->q_loras[i]->lora_A->data; lora[1] = m->q_loras[i]->lora_B->data; }
-        if (m->v_loras && m->v_loras[i]) { lora[2] = m->v_loras[i]->lora_A->data; lora[3] = m->v_loras[i]->lora_B->data; }
+        if (!full_param && m->q_loras && m->q_loras[i]) { lora[0] = m->q_loras[i]->lora_A->data; lora[1] = m->q_loras[i]->lora_B->data; }
+        if (!full_param && m->v_loras && m->v_loras[i]) { lora[2] = m->v_loras[i]->lora_A->data; lora[3] = m->v_loras[i]->lora_B->data; }
         if (llmb200_sft_load_layer(s, i, &r, m->rope_theta, lora) != 0) { sft_state_free(s); return NULL; }
     }
     if (llmb200_sft_finish(s, m->lm_head->weight->data, m->final_norm->gamma->data, m->token_emb->weight->data, 1) != 0) {
@@ -515,8 +533,21 @@ SFTState *sft_state_create(llmb200_qwen3_model *m, int seq_len, int lora_rank, f
     }
     clock_gettime(CLOCK_MONOTONIC, &t1);
     const double ms = (t1.tv_sec - t0.tv_sec) * 1000.0 + (t1.tv_nsec - t0.tv_nsec) / 1e6;
-    printf("[FastSFT] Init: %.0f ms, seq=%d, lora_rank=%d\n", ms, seq_len, lora_rank);
+    if (full_param) printf("[FastSFT] Qwen3 Full-param Init: %.0f ms, seq=%d\n", ms, seq_len);
+    else printf("[FastSFT] Init: %.0f ms, seq=%d, lora_rank=%d\n", ms, seq_len, lora_rank);
     return s;
+}
+
+SFTState *sft_state_create(llmb200_qwen3_model *m, int seq_len, int lora_rank, float lora_alpha)
+{
+    return create_from_qwen3(m, seq_len, lora_rank, lora_alpha, 0);
+}
+
+/* Every projection and the LM head trainable by SGD, no adapter (src/nn/fast_sft.c:402-501). The matrices are
+ * kept as fp32 holders of binary16 values and every product runs in fp32 on the CUDA cores. */
+SFTState *sft_state_create_full(llmb200_qwen3_model *m, int seq_len)
+{
+    return create_from_qwen3(m, seq_len, 0, 0.0f, 1);
 }
 
 /* ---------------------------------------------------------------- weight sharing (src/nn/fast_sft.h:101-111) */
@@ -563,6 +594,37 @@ static void share_free(SFTState *s)
     metal_buf_free(s->share_final_g);
     s->share_final_g = NULL;
 }
+
+/* Views that own narrowed copies (CUDA-core mode) go stale when full-parameter training changes a matrix:
+ * narrow them again and drop any host mirror made from the old bytes. */
+static void share_refresh_one(SFTState *s, WMat *w, const SftMat *m, int row0)
+{
+    if (!w || !w->mbuf || w->mbuf->borrowed || !m->w) return;
+    S_TRY(s, b200_f32_to_f16(m->w + (size_t)row0 * m->cols, (size_t)w->rows * m->cols, 1.0f, w->mbuf->dev, g_rt.stream));
+    free(w->mbuf->host_mirror);
+    w->mbuf->host_mirror = NULL;
+}
+
+static void share_refresh(SFTState *s)
+{
+    for (int L = 0; L < s->NL && s->share_layers; ++L) {
+        SftLayer *l = &s->layers[L];
+        LayerW *lw = &s->share_layers[L];
+        share_refresh_one(s, lw->q_proj, &l->qkv, 0);
+        share_refresh_one(s, lw->k_proj, &l->qkv, s->Hq_hd);
+        share_refresh_one(s, lw->v_proj, &l->qkv, s->Hq_hd + s->Hkv_hd);
+        share_refresh_one(s, lw->o_proj, &l->o, 0);
+        share_refresh_one(s, lw->gate_proj, &l->gu, 0);
+        share_refresh_one(s, lw->up_proj, &l->gu, s->IS);
+        share_refresh_one(s, lw->down_proj, &l->down, 0);
+    }
+    if (s->share_lm) share_refresh_one(s, s->share_lm, &s->lm_head, 0);
+}
+
+/* For a decode state made from this one: how often the base matrices have changed, and the views brought
+ * up to date (on the library's stream) before it copies them again. */
+unsigned long long llmb200_sft_weights_version(SFTState *s) { return s ? s->weights_version : 0; }
+void llmb200_sft_refresh_views(SFTState *s) { if (s && s->finished) share_refresh(s); }
 
 /* The frozen base as the reference's containers: one WMat per projection (binary16 [rows, cols], row-major)
  * and one buffer per norm vector, all views of this state's device memory; valid until sft_state_free.
@@ -632,7 +694,9 @@ void sft_state_free(SFTState *s)
                           l->probs, l->x_mid, l->ln2, l->gu_out };
         for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
         for (int i = 0; i < 4; ++i) metal_buf_free(l->lora_buf[i]);
+        for (int i = 0; i < 4; ++i) cudaFree(l->acc[i]);
     }
+    cudaFree(s->acc_lm);
     mat_free(&s->lm_head);
     void *bufs[] = { s->final_g, s->d_emb, s->lora_p, s->lora_g, s->lora_m, s->lora_v, s->x_final, s->ln_final, s->att,
                      s->act, s->logits, s->dlogits, s->losses, s->dx, s->d_ln, s->d_act, s->d_gu, s->d_att, s->dqkv,
@@ -669,16 +733,20 @@ static void forward_device(SFTState *s)
         S_TRY(s, b200_rms_norm_rows_h(l->x_in, l->g_in, l->ln1, s->xh, M, s->D, s->eps, st));
         /* the LoRA matrices ride along with the frozen q/k/v weight: the product below also yields
          * mid_q = ln1 A_q^T and mid_v = ln1 A_v^T in the last columns of qkv_out (:639, :652) */
-        if (s->use_tc)
-            S_TRY(s, b200_lora_pack_f16(l->qkv.wh, l->qkv.wth, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR,
-                                        sc, st));
-        else
-            S_TRY(s, b200_lora_pack(l->qkv.w, l->qkv.wt, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR, sc,
-                                    st));
+        if (R > 0) {
+            if (s->use_tc)
+                S_TRY(s, b200_lora_pack_f16(l->qkv.wh, l->qkv.wth, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR,
+                                            sc, st));
+            else
+                S_TRY(s, b200_lora_pack(l->qkv.w, l->qkv.wt, pA_q, pB_q, pA_v, pB_v, s->D, s->Hq_hd, s->Hkv_hd, R, s->XR, sc,
+                                        st));
+        }
         gemm_fwd(s, s->use_tc ? NULL : l->ln1, &l->qkv, l->qkv_out, NULL);
-        /* q += sc * mid_q B_q^T, v += sc * mid_v B_v^T (:641-643, :654-656) */
-        S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, 0, s->Hq_hd, l->mid_q, s->QKVX, pB_q, R, sc, M, st));
-        S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, s->Hq_hd + s->Hkv_hd, s->Hkv_hd, l->mid_v, s->QKVX, pB_v, R, sc, M, st));
+        if (R > 0) {
+            /* q += sc * mid_q B_q^T, v += sc * mid_v B_v^T (:641-643, :654-656) */
+            S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, 0, s->Hq_hd, l->mid_q, s->QKVX, pB_q, R, sc, M, st));
+            S_TRY(s, b200_lora_add(l->qkv_out, s->QKVX, s->Hq_hd + s->Hkv_hd, s->Hkv_hd, l->mid_v, s->QKVX, pB_v, R, sc, M, st));
+        }
         S_TRY(s, b200_qk_norm_rope(l->qkv_out, s->QKVX, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq, s->Hkv, s->hd,
                                    s->eps, l->q_f, l->k_f, st));
         /* with tensor cores on, the operand of the next product is written as binary16 straight into xh and
@@ -706,6 +774,32 @@ static void loss_device(SFTState *s)
 
 /* ---------------------------------------------------------------- backward */
 
+/* Full-parameter mode: the weight gradient dW = dY^T X over the M token rows (dY [M, ldy], X [M, ldx]) goes
+ * into rows 0..rows-1 of the matrix the way wmode says: W <- half(W - lr dW) (f16_sgd_fused,
+ * shaders/q8_kernels.metal:1097-1125) or G <- half(G + dW) (f16_grad_accum, :1164-1191). One fp32 sum over
+ * the tokens in ascending order per element, one rounding to binary16, as there. The matrices are fp32
+ * holders of binary16 values in this mode, so the product adds into them in place and a rounding pass follows. */
+static void weight_step(SFTState *s, SftMat *W, float *acc, int rows, const float *dY, long long ldy, const float *X,
+                        long long ldx)
+{
+    if (!s->full_param || !s->wmode) return;
+    float *dst = s->wmode == 2 ? acc : W->w;
+    if (!dst) {
+        if (!s->err) { s->err = B200_E_STATE; fprintf(stderr, "[FastSFT] gradient accumulation without sft_alloc_grad_accum\n"); }
+        return;
+    }
+    b200_gemm_args g = {0};
+    g.A = dY; g.a_row = 1; g.a_col = ldy;          /* A[m, k] = dY[k, m] */
+    g.B = X; g.b_row = ldx; g.b_col = 1;           /* B[k, n] = X[k, n] */
+    g.C = dst; g.ldc = W->cols;
+    g.R = dst; g.ldr = W->cols;                    /* in place: every element is read and written by one thread */
+    g.M = rows; g.N = W->cols; g.K = s->M;
+    g.alpha = s->wmode == 2 ? 1.0f : -s->sgd_lr;
+    S_TRY(s, b200_gemm_f32(&g, g_rt.stream));
+    S_TRY(s, b200_round_f16(dst, (size_t)rows * W->cols, g_rt.stream));
+    if (s->wmode == 1) s->weights_version++;
+}
+
 static void backward_device(SFTState *s)
 {
     cudaStream_t st = g_rt.stream;
@@ -714,6 +808,7 @@ static void backward_device(SFTState *s)
     /* the loss kernel leaves the binary16 copy of dlogits in xh; a caller that wrote dlogits itself
      * (sft_get_dlogits + sft_backward) gets it converted here */
     gemm_bwd(s, s->xh_has_dlogits ? NULL : s->dlogits, &s->lm_head, s->d_ln);                /* :777 */
+    weight_step(s, &s->lm_head, s->acc_lm, s->V, s->dlogits, s->V, s->ln_final, s->D);       /* :778-785 */
     s->xh_has_dlogits = 0;
     const float hs = s->gscale;
     S_TRY(s, b200_rms_norm_bwd_rows_h(s->x_final, s->d_ln, s->D, s->final_g, s->dx, M, s->D, s->eps, 0, 0.f, s->xh, hs, st));
@@ -725,12 +820,24 @@ static void backward_device(SFTState *s)
         float *gA_v = s->lora_g + l->lora_off + s->sub_off[2], *gB_v = s->lora_g + l->lora_off + s->sub_off[3];
         /* FFN (:841-872) */
         gemm_bwd(s, s->use_tc ? NULL : s->dx, &l->down, s->d_act);           /* dx is in xh already */
+        if (s->full_param && s->wmode) {
+            /* the activation of this layer is not kept by the forward pass: made again from the saved gate/up (:842-849) */
+            S_TRY(s, b200_silu_mul_rows_h(l->gu_out, M, s->IS, s->act, NULL, st));
+            weight_step(s, &l->down, l->acc[3], s->D, s->dx, s->D, s->act, s->IS);
+        }
         S_TRY(s, b200_silu_mul_bwd_rows_h(s->d_act, l->gu_out, M, s->IS, s->use_tc ? NULL : s->d_gu, s->xh, hs, st));
         gemm_bwd(s, s->use_tc ? NULL : s->d_gu, &l->gu, s->d_ln);
+        weight_step(s, &l->gu, l->acc[2], 2 * s->IS, s->d_gu, 2 * s->IS, l->ln2, s->D);      /* gate and up rows (:853-868) */
         S_TRY(s, b200_rms_norm_bwd_rows_h(l->x_mid, s->d_ln, s->D, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, s->xh, hs, st));
         /* attention (:889-918) */
         gemm_bwd(s, s->use_tc ? NULL : s->dx, &l->o, s->d_att);
         const float *v = l->qkv_out + s->Hq_hd + s->Hkv_hd;
+        if (s->full_param && s->wmode) {
+            /* likewise the attention output, from the saved q, k, v (probs is rewritten with the same values) (:892-899) */
+            S_TRY(s, b200_attn_train_fwd_h(l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd, attn_scale, l->probs,
+                                           s->att, NULL, st));
+            weight_step(s, &l->o, l->acc[1], s->D, s->dx, s->D, s->att, s->Hq_hd);
+        }
         S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd,
                                      attn_scale, s->d_score, s->dqkv, QKV, st));
         S_TRY(s, b200_qk_norm_rope_bwd(s->dqkv, l->qkv_out, s->QKVX, QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq,
@@ -740,6 +847,12 @@ static void backward_device(SFTState *s)
          * sc*B_v as extra rows, so the same product leaves tmp_q = sc dq B_q and tmp_v = sc dv B_v (:948-949,
          * :963-964) in columns D.. of d_lnx. */
         const int DX = s->D + s->XR;
+        if (s->full_param && s->wmode) {
+            /* q, k, v take their step BEFORE the gradient goes on through them (:922-945): the product below
+             * reads the updated matrices when the step is immediate */
+            weight_step(s, &l->qkv, l->acc[0], QKV, s->dqkv, QKV, l->ln1, s->D);
+            if (s->wmode == 1) S_TRY(s, mat_finish_rows(s, &l->qkv, QKV));
+        }
         if (s->use_tc) {
             gemm_tc(s, s->dqkv, s->gscale, l->qkv.wth, s->d_lnx, DX, NULL, DX, QKV);
         } else {
@@ -752,7 +865,9 @@ static void backward_device(SFTState *s)
         }
         const float *tmp_q = s->d_lnx + s->D, *tmp_v = tmp_q + R;
         /* dB = sc dq^T mid (:946-947, :961-962); dA = tmp^T ln1 (:950, :965) */
-        if (R <= 16) {
+        if (R == 0) {
+            /* full-parameter mode: no adapter */
+        } else if (R <= 16) {
             S_TRY(s, b200_xty_skinny(dq, QKV, l->mid_q, s->QKVX, M, s->Hq_hd, R, sc, gB_q, R, 1, st));
             S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_q, DX, M, s->D, R, 1.0f, gA_q, 1, s->D, st));
             S_TRY(s, b200_xty_skinny(dv, QKV, l->mid_v, s->QKVX, M, s->Hkv_hd, R, sc, gB_v, R, 1, st));
@@ -764,7 +879,8 @@ static void backward_device(SFTState *s)
             gemm_small(s, tmp_v, 1, DX, l->ln1, s->D, 1, gA_v, s->D, NULL, R, s->D, M, 1.0f);
         }
         /* d_ln += tmp_q A_q + tmp_v A_v (:951-953, :966, :970): one product over the 2R packed rows of the weight */
-        if (s->use_tc) {                       /* the packed rows are binary16 there: take A_q, A_v from the LoRA vector */
+        if (R == 0) {
+        } else if (s->use_tc) {                       /* the packed rows are binary16 there: take A_q, A_v from the LoRA vector */
             gemm_small(s, tmp_q, DX, 1, pA_q, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, R, 1.0f);
             gemm_small(s, tmp_v, DX, 1, pA_v, s->D, 1, s->d_lnx, DX, s->d_lnx, M, s->D, R, 1.0f);
         } else {
@@ -779,6 +895,7 @@ static void backward_device(SFTState *s)
 
 static void update_device(SFTState *s, float lr, int step)
 {
+    if (s->n_lora == 0) return;                  /* a full-parameter state has no adapter to update */
     const float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, wd = 0.01f;
     const float bc1 = 1.0f - powf(beta1, (float)step), bc2 = 1.0f - powf(beta2, (float)step);
     cudaStream_t st = g_rt.stream;
@@ -870,6 +987,14 @@ void llmb200_sft_apply_update(SFTState *s, float lr)
 
 float llmb200_sft_train_batch(SFTState *s, const uint32_t *inputs, const uint32_t *targets, float lr)
 {
+    if (s && s->full_param) {
+        /* full-parameter step (:1136-1137): the weights move inside the backward pass; no optimizer state, no step count */
+        s->wmode = s->acc_lm ? 2 : 1;             /* with accumulators allocated the reference's step accumulates (:778-785) */
+        s->sgd_lr = lr;
+        const float l = llmb200_sft_forward_backward(s, inputs, targets);
+        s->wmode = 0;
+        return l;
+    }
     const float loss = llmb200_sft_forward_backward(s, inputs, targets);
     /* A failed pass (a device wait gave up, a launch failed) or a loss that is not finite leaves partial
      * gradients: the parameters, the Adam moments and the step count stay as they were. */
@@ -898,6 +1023,7 @@ void forward_to_logits(SFTState *s)
 void sft_backward(SFTState *s)
 {
     if (!s || !s->finished) return;
+    s->wmode = 0;                 /* a full-parameter state: the reference steps with lr = 0 here, which changes nothing */
     backward_device(s);
 }
 
@@ -922,24 +1048,113 @@ SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int 
     not_provided("sft_state_create_gemma3");
     return NULL;
 }
-SFTState *sft_state_create_full(llmb200_qwen3_model *model, int seq_len)
-{
-    (void)model; (void)seq_len;
-    not_provided("sft_state_create_full");
-    return NULL;
-}
 SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len)
 {
     (void)model; (void)seq_len;
     not_provided("sft_state_create_gemma3_full");
     return NULL;
 }
-int sft_is_full_param(SFTState *s) { (void)s; return 0; }
-void sft_backward_sgd(SFTState *s, float lr) { (void)s; (void)lr; not_provided("sft_backward_sgd"); }
-void sft_alloc_grad_accum(SFTState *s) { (void)s; not_provided("sft_alloc_grad_accum"); }
-void sft_backward_accum(SFTState *s) { (void)s; not_provided("sft_backward_accum"); }
-void sft_apply_grad_sgd(SFTState *s, float lr) { (void)s; (void)lr; not_provided("sft_apply_grad_sgd"); }
-void sft_save_full_checkpoint(SFTState *s, const char *path) { (void)s; (void)path; not_provided("sft_save_full_checkpoint"); }
+int sft_is_full_param(SFTState *s) { return s ? s->full_param : 0; }                       /* src/nn/fast_sft.c:987 */
+
+static int full_only(SFTState *s, const char *what)
+{
+    if (s && s->finished && s->full_param) return 1;
+    fprintf(stderr, "[FastSFT] %s: not a full-parameter state\n", what);
+    return 0;
+}
+
+/* Backward from the gradient in sft_get_dlogits() with every weight stepped as its gradient is formed
+ * (sft_backward_ex with a learning rate, :766-982). */
+void sft_backward_sgd(SFTState *s, float lr)
+{
+    if (!full_only(s, "sft_backward_sgd")) return;
+    s->wmode = s->acc_lm ? 2 : 1;                 /* as above: accumulators, once allocated, take every gradient */
+    s->sgd_lr = lr;
+    backward_device(s);
+    s->wmode = 0;
+}
+
+/* Accumulators for every matrix, zeroed (:996-1019); binary16 values, like the reference's F16 buffers. */
+void sft_alloc_grad_accum(SFTState *s)
+{
+    if (!full_only(s, "sft_alloc_grad_accum") || s->acc_lm) return;
+    size_t total = 0;
+    for (int L = 0; L < s->NL; ++L) {
+        SftLayer *l = &s->layers[L];
+        const SftMat *ms[4] = { &l->qkv, &l->o, &l->gu, &l->down };
+        for (int i = 0; i < 4; ++i) {
+            const size_t n = (size_t)(i == 0 ? s->QKV : ms[i]->rows) * ms[i]->cols;
+            l->acc[i] = dalloc(s, n);
+            if (l->acc[i]) cudaMemsetAsync(l->acc[i], 0, n * 4, g_rt.stream);
+            total += n;
+        }
+    }
+    s->acc_lm = dalloc(s, (size_t)s->V * s->D);
+    if (s->acc_lm) cudaMemsetAsync(s->acc_lm, 0, (size_t)s->V * s->D * 4, g_rt.stream);
+    total += (size_t)s->V * s->D;
+    printf("[FastSFT] Grad accum buffers allocated: %.2f MB\n", (float)(total * 2) / (1024.0f * 1024.0f));
+}
+
+/* Backward that adds every weight gradient into its accumulator and leaves the weights alone (:986). */
+void sft_backward_accum(SFTState *s)
+{
+    if (!full_only(s, "sft_backward_accum")) return;
+    s->wmode = s->acc_lm ? 2 : 1;                 /* without accumulators the reference steps with lr = 0: nothing changes */
+    s->sgd_lr = 0.0f;
+    backward_device(s);
+    s->wmode = 0;
+}
+
+/* W <- half(W - lr G), G <- 0 for every matrix (:1021-1039). */
+void sft_apply_grad_sgd(SFTState *s, float lr)
+{
+    if (!full_only(s, "sft_apply_grad_sgd") || !s->acc_lm) return;
+    cudaStream_t st = g_rt.stream;
+    for (int L = 0; L < s->NL; ++L) {
+        SftLayer *l = &s->layers[L];
+        SftMat *ms[4] = { &l->qkv, &l->o, &l->gu, &l->down };
+        for (int i = 0; i < 4; ++i)
+            S_TRY(s, b200_sgd_apply_f16(ms[i]->w, l->acc[i], (size_t)(i == 0 ? s->QKV : ms[i]->rows) * ms[i]->cols, lr, st));
+        S_TRY(s, mat_finish_rows(s, &l->qkv, s->QKV));
+    }
+    S_TRY(s, b200_sgd_apply_f16(s->lm_head.w, s->acc_lm, (size_t)s->V * s->D, lr, st));
+    s->weights_version++;
+}
+
+/* Header of nine 32-bit words, then per layer q, k, v, o, gate, up, down and at the end the LM head, each as
+ * row-major binary16 (:1287-1343). */
+void sft_save_full_checkpoint(SFTState *s, const char *path)
+{
+    if (!s || !s->finished || !path) return;
+    FILE *fp = fopen(path, "wb");
+    if (!fp) {
+        fprintf(stderr, "[FastSFT] Failed to open %s for writing\n", path);
+        return;
+    }
+    LayerW *lw = sft_get_layers(s);
+    WMat *lm = sft_get_lm_head(s);
+    if (!lw || !lm) { fclose(fp); fprintf(stderr, "[FastSFT] reading the weights back failed\n"); return; }
+    share_refresh(s);
+    const uint32_t head[9] = { 0x46554C4Cu, (uint32_t)s->model_type, (uint32_t)s->NL, (uint32_t)s->D, (uint32_t)s->Hq,
+                               (uint32_t)s->Hkv, (uint32_t)s->hd, (uint32_t)s->IS, (uint32_t)s->V };
+    fwrite(head, 4, 9, fp);
+    size_t total = 0;
+    for (int L = 0; L < s->NL; ++L) {
+        WMat *ws[7] = { lw[L].q_proj, lw[L].k_proj, lw[L].v_proj, lw[L].o_proj, lw[L].gate_proj, lw[L].up_proj, lw[L].down_proj };
+        for (int i = 0; i < 7; ++i) {
+            const size_t bytes = (size_t)ws[i]->rows * ws[i]->cols * 2;
+            const void *h = metal_buf_ptr(ws[i]->mbuf);
+            if (h) fwrite(h, 1, bytes, fp);
+            total += bytes;
+        }
+    }
+    const size_t lm_bytes = (size_t)s->V * s->D * 2;
+    const void *h = metal_buf_ptr(lm->mbuf);
+    if (h) fwrite(h, 1, lm_bytes, fp);
+    total += lm_bytes;
+    fclose(fp);
+    printf("[FastSFT] Full checkpoint saved to %s (%.2f MB)\n", path, (float)total / (1024.0f * 1024.0f));
+}
 void sft_sync_lora_to_gemma3(SFTState *s, llmb200_gemma3_model *m) { (void)s; (void)m; not_provided("sft_sync_lora_to_gemma3"); }
 
 /* ---------------------------------------------------------------- accessors */
