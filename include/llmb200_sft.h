@@ -4,9 +4,7 @@
  * Part 1 declares, under the reference's names and with the same argument
  * meaning, the LoRA subset of llm.metal's fast SFT engine
  * (src/nn/fast_sft.h:14-111; implementation src/nn/fast_sft.c): LoRA and
- * full-parameter training of Qwen3. The Gemma3 modes are not built: their
- * constructors exist, so that a caller written for all modes
- * (src/nn/fast_grpo.c) links, and refuse with a message and NULL.
+ * full-parameter training of Qwen3 and of Gemma3.
  *
  * Part 2 is additive: layer-by-layer construction, several sequences per
  * step (their LoRA gradients are averaged, then one clip + AdamW as in the
@@ -127,8 +125,11 @@ void sft_backward_accum(SFTState *state);
 void sft_apply_grad_sgd(SFTState *state, float lr);
 void sft_save_full_checkpoint(SFTState *state, const char *path);
 
-/* ---- modes that are not built (src/nn/fast_sft.h:17-19, 23, 55): Gemma3 ----
- * The constructors print "[FastSFT] ... not provided" and return NULL, like any other failed create. */
+/* ---- Gemma3 (src/nn/fast_sft.h:17-19, 23, 55; src/nn/fast_sft.c:284-396, 507-610) ----
+ * The same calls on a Gemma3 model: four norms per layer (the post-attention and post-feedforward norms act on
+ * the projection outputs before the residual add), GeGLU, embeddings scaled by sqrt(d_model), the LM head a
+ * binary16 copy of the embedding table, the RoPE base per layer by position in the stack (every sixth layer
+ * global). Such a state computes every product in fp32 on the CUDA cores. */
 SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int lora_rank, float lora_alpha);
 SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len);
 void sft_sync_lora_to_gemma3(SFTState *state, llmb200_gemma3_model *model);

@@ -146,6 +146,13 @@ int b200_xty_skinny(const float *X, long long ld_x, const float *Y, long long ld
 int b200_softmax_ce_rows(const float *logits, const uint32_t *targets, int rows, int vocab, float grad_scale,
                          float *losses, float *dlogits, void *stream);
 
+/* GeGLU on the fused gate|up layout gu [rows, 2 * inter] (gelu_mul :351-363, gelu_mul_backward :561-580; tanh form,
+ * argument clamped to +-15): act[rows, inter] = gelu(gate) * up; d_gu[rows, 2 * inter] = (d gate | d up). */
+int b200_gelu_mul_rows(const float *gu, int rows, int inter, float *act, void *stream);
+int b200_gelu_mul_bwd_rows(const float *d_act, const float *gu, int rows, int inter, float *d_gu, void *stream);
+/* out[i] = a[i] + b[i] (residual_add :369-375); out may be a or b. */
+int b200_add(const float *a, const float *b, float *out, size_t n, void *stream);
+
 /* grpo_policy_grad (shaders/q8_kernels.metal:698-761; dispatch fast_metal.m:963-981), one row per position:
  * new_logprobs[m] = logit[action] - logsumexp; ratio = exp(new - old); the PPO clip keeps the position
  * (weight = -advantage) or drops it (0); dlogits = weight * ratio * (softmax - onehot(action)). */

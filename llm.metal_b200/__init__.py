@@ -187,7 +187,7 @@ SYMBOLS_MAIN = {
                                 "b200_softmax_ce_rows", "b200_sumsq_partials", "b200_clip_adamw",
                                 "b200_rms_norm_rows_h", "b200_rms_norm_bwd_rows_h", "b200_attn_train_fwd_h",
                                 "b200_silu_mul_rows_h", "b200_silu_mul_bwd_rows_h", "b200_softmax_ce_rows_h",
-                                "b200_grpo_policy_grad", "b200_scale", "b200_sgd_apply_f16"],
+                                "b200_grpo_policy_grad", "b200_scale", "b200_sgd_apply_f16", "b200_gelu_mul_rows", "b200_gelu_mul_bwd_rows", "b200_add"],
     "llmb200_sft.h": ["sft_state_create", "sft_state_free", "sft_train_step", "forward_to_logits", "sft_backward",
                       "sft_get_logits", "sft_get_dlogits", "sft_get_x_cpu", "sft_get_losses_cpu", "sft_get_seq_len",
                       "sft_get_vocab_size", "sft_get_d_model", "sft_get_lora_rank", "sft_get_n_layers",
@@ -307,6 +307,8 @@ def lib():
         "b200_grpo_policy_grad": (i, [vp, vp, vp, vp, vp, vp, i, i, fl, vp]),
         "b200_scale": (i, [vp, fl, sz, vp]),
         "b200_sgd_apply_f16": (i, [vp, vp, sz, fl, vp]),
+        "b200_gelu_mul_rows": (i, [vp, i, i, vp, vp]), "b200_gelu_mul_bwd_rows": (i, [vp, vp, i, i, vp, vp]),
+        "b200_add": (i, [vp, vp, vp, sz, vp]),
         # ---- llmb200_sft.h
         "sft_state_create": (vp, [vp, i, i, fl]), "sft_state_free": (None, [vp]),
         "sft_train_step": (fl, [vp, c_u32_p, c_u32_p, fl]),

@@ -605,6 +605,41 @@ __global__ void silu_mul_bwd_rows_kernel(const float *d_act, const float *gu, in
     }
 }
 
+// GeGLU (Gemma3): gelu_mul / gelu_mul_backward, shaders/q8_kernels.metal:351-363, 561-580 -- the tanh form with
+// its argument clamped to +-15, on the fused [rows, 2 * inter] gate|up layout.
+__global__ void gelu_mul_rows_kernel(const float *gu, int inter, float *act, size_t total)
+{
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = e / inter, i = e % inter;
+        const float g = gu[m * 2 * inter + i], u = gu[m * 2 * inter + inter + i];
+        float inner = 0.7978845608f * (g + 0.044715f * (g * g * g));
+        inner = fminf(fmaxf(inner, -15.0f), 15.0f);
+        act[e] = 0.5f * g * (1.0f + tanhf(inner)) * u;
+    }
+}
+
+__global__ void gelu_mul_bwd_rows_kernel(const float *d_act, const float *gu, int inter, float *d_gu, size_t total)
+{
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = e / inter, i = e % inter;
+        const float g = gu[m * 2 * inter + i], u = gu[m * 2 * inter + inter + i], dy = d_act[e];
+        float inner = 0.7978845608f * (g + 0.044715f * (g * g * g));
+        inner = fminf(fmaxf(inner, -15.0f), 15.0f);
+        const float th = tanhf(inner);
+        const float gelu_g = 0.5f * g * (1.0f + th);
+        const float sech2 = 1.0f - th * th;
+        const float grad = 0.5f * (1.0f + th) + 0.5f * g * sech2 * 0.7978845608f * (1.0f + 3.0f * 0.044715f * g * g);
+        d_gu[m * 2 * inter + i] = dy * u * grad;
+        d_gu[m * 2 * inter + inter + i] = dy * gelu_g;
+    }
+}
+
+// out = a + b (residual_add :369-375 with its result in a third buffer)
+__global__ void add_kernel(const float *a, const float *b, float *out, size_t n)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = a[i] + b[i];
+}
+
 // ---- LoRA up-projection added into the base projection -------------------------------------------
 // One thread per output column keeps its row of B in registers and walks LORA_ROWS token rows whose
 // mid vectors sit in shared memory.
@@ -1252,6 +1287,33 @@ extern "C" int b200_silu_mul_bwd_rows(const float *d_act, const float *gu, int r
 {
     if (!d_gu) return B200_E_BADARG;
     return b200_silu_mul_bwd_rows_h(d_act, gu, rows, inter, d_gu, nullptr, 1.0f, stream);
+}
+
+extern "C" int b200_gelu_mul_rows(const float *gu, int rows, int inter, float *act, void *stream)
+{
+    if (!gu || !act || rows <= 0 || inter <= 0) return B200_E_BADARG;
+    const size_t total = (size_t)rows * inter;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    gelu_mul_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gu, inter, act, total);
+    return done();
+}
+
+extern "C" int b200_gelu_mul_bwd_rows(const float *d_act, const float *gu, int rows, int inter, float *d_gu, void *stream)
+{
+    if (!d_act || !gu || !d_gu || rows <= 0 || inter <= 0) return B200_E_BADARG;
+    const size_t total = (size_t)rows * inter;
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    gelu_mul_bwd_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(d_act, gu, inter, d_gu, total);
+    return done();
+}
+
+extern "C" int b200_add(const float *a, const float *b, float *out, size_t n, void *stream)
+{
+    if (!a || !b || !out) return B200_E_BADARG;
+    if (n == 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    add_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a, b, out, n);
+    return done();
 }
 
 extern "C" int b200_lora_add(float *y, long long ld, int col0, int n_cols, const float *mid, long long mid_ld,

@@ -327,6 +327,10 @@ int llmb200_state_load_layer(InferenceState *s, int li, const LayerWeightRef *r,
     ly->g_qn = upload_gamma(r->q_norm_g, hd);
     ly->g_kn = upload_gamma(r->k_norm_g, hd);
     if (!ly->g_input || !ly->g_post_attn) return -1;
+    if (s->mt == MODEL_GEMMA3 && (!ly->g_pre_ff || !ly->g_post_ff)) {
+        fprintf(stderr, "[FastGen] layer %d: a Gemma3 layer needs its pre- and post-feedforward norm weights\n", li);
+        return B200_E_BADARG;
+    }
 
     /* RoPE frequencies exactly as the reference's CPU path forms them:
      * 1.0f / powf(theta, (float)(2*d) / (float)hd)  (src/nn/attention.c:757-758) */
@@ -917,8 +921,10 @@ InferenceState *inference_state_create_from_sft(SFTState *sft, int max_seq_len)
         ly->g_post_attn = clone_f32(r->post_attn_norm_g->dev, (size_t)D);
         ly->g_qn = r->q_norm_g ? clone_f32(r->q_norm_g->dev, (size_t)hd) : NULL;
         ly->g_kn = r->k_norm_g ? clone_f32(r->k_norm_g->dev, (size_t)hd) : NULL;
+        ly->g_pre_ff = r->pre_ff_norm_g ? clone_f32(r->pre_ff_norm_g->dev, (size_t)D) : NULL;      /* Gemma3 */
+        ly->g_post_ff = r->post_ff_norm_g ? clone_f32(r->post_ff_norm_g->dev, (size_t)D) : NULL;
         float *f = malloc((size_t)(hd / 2) * sizeof(float));
-        if (!f || !ly->g_input || !ly->g_post_attn) { free(f); rc = -1; break; }
+        if (!f || !ly->g_input || !ly->g_post_attn || (s->mt == MODEL_GEMMA3 && (!ly->g_pre_ff || !ly->g_post_ff))) { free(f); rc = -1; break; }
         for (int d = 0; d < hd / 2; ++d) f[d] = 1.0f / powf(thetas[i], (float)(2 * d) / (float)hd);
         ly->inv_freq = llmb200_upload_f32(f, (size_t)(hd / 2));
         free(f);

@@ -44,6 +44,8 @@ typedef struct {
 typedef struct {
     SftMat qkv, o, gu, down;
     float *g_in, *g_post, *g_q, *g_k;   /* norm gammas */
+    float *g_pre_ff, *g_post_ff;        /* Gemma3: the two norms around the FFN */
+    float *o_out, *ff_raw;              /* Gemma3: saved o-projection and down-projection outputs (inputs of its post norms) */
     float *inv_freq;                    /* [hd/2] */
     /* saved activations */
     float *x_in, *ln1, *qkv_out, *q_f, *k_f, *probs, *x_mid, *ln2, *gu_out;
@@ -64,6 +66,7 @@ struct SFTState {
     /* Full-parameter mode (sft_state_create_full): no LoRA (rank 0); every projection and the LM head are
      * trained by plain SGD inside the backward pass. wmode says what a backward pass does with a weight
      * gradient dW = dY^T X: 0 nothing, 1 W <- half(W - lr dW) at once, 2 G <- half(G + dW) into accumulators. */
+    int gemma;                  /* Gemma3 block order: four norms per layer, GeGLU, embeddings scaled and tied to the LM head */
     int full_param, wmode;
     float sgd_lr;
     float *acc_lm;
@@ -278,8 +281,8 @@ static SFTState *sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, in
                 n_seq, lora_rank);
         return NULL;
     }
-    if (cfg->model_type != MODEL_QWEN3) {
-        fprintf(stderr, "[FastSFT] only the Qwen3 block order is implemented\n");
+    if (cfg->model_type != MODEL_QWEN3 && cfg->model_type != MODEL_GEMMA3) {
+        fprintf(stderr, "[FastSFT] unknown model type %d\n", (int)cfg->model_type);
         return NULL;
     }
     if (cfg->n_kv_heads <= 0 || cfg->n_q_heads % cfg->n_kv_heads ||
@@ -294,14 +297,15 @@ static SFTState *sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, in
     }
     SFTState *s = calloc(1, sizeof(SFTState));
     if (!s) { fast_metal_shutdown(); return NULL; }
-    s->model_type = MODEL_QWEN3;
+    s->model_type = cfg->model_type;
+    s->gemma = cfg->model_type == MODEL_GEMMA3;
     s->D = cfg->d_model; s->Hq = cfg->n_q_heads; s->Hkv = cfg->n_kv_heads; s->hd = cfg->head_dim;
     s->IS = cfg->intermediate_size; s->V = cfg->vocab_size; s->NL = cfg->n_layers;
     s->N = seq_len; s->S = n_seq; s->M = seq_len * n_seq;
     s->Hq_hd = s->Hq * s->hd; s->Hkv_hd = s->Hkv * s->hd; s->QKV = s->Hq_hd + 2 * s->Hkv_hd;
     s->XR = (2 * lora_rank + 3) & ~3;
     s->QKVX = s->QKV + s->XR;
-    s->emb_scale = 1.0f;
+    s->emb_scale = s->gemma ? sqrtf((float)s->D) : 1.0f;       /* src/nn/fast_sft.c:302 */
     s->eps = 1e-6f;
     s->lora_rank = lora_rank;
     s->lora_scaling = lora_rank ? lora_alpha / (float)lora_rank : 0.0f;
@@ -313,6 +317,8 @@ static SFTState *sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, in
                 !(s->Hkv_hd % 8) && !(s->IS % 8);
     /* the weight gradients and their SGD steps are fp32 products over fp32 activations: CUDA-core mode */
     if (full_param) s->use_tc = 0;
+    /* the Gemma3 block order is implemented on the fp32 path only */
+    if (s->gemma) s->use_tc = 0;
     /* gradients reach at most 1/M (the loss scale) at the logits: 8 * M rounded up to a power of two maps
      * them to ~8 in binary16 and leaves four decades below before the subnormals start */
     s->gscale = 8.0f;
@@ -354,6 +360,10 @@ static SFTState *sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, in
         l->probs = dalloc(s, (size_t)s->S * s->Hq * s->N * s->N);
         l->x_mid = dalloc(s, (size_t)M * s->D); l->ln2 = dalloc(s, (size_t)M * s->D);
         l->gu_out = dalloc(s, (size_t)M * 2 * s->IS);
+        if (s->gemma) {
+            l->g_pre_ff = dalloc(s, s->D); l->g_post_ff = dalloc(s, s->D);
+            l->o_out = dalloc(s, (size_t)M * s->D); l->ff_raw = dalloc(s, (size_t)M * s->D);
+        }
     }
     mat_alloc(s, &s->lm_head, s->V, s->D);
     s->final_g = dalloc(s, s->D);
@@ -439,6 +449,8 @@ int llmb200_sft_load_layer(SFTState *s, int L, const LayerWeightRef *r, float ro
     if (!rc) rc = upload_small(l->g_post, r->post_attn_norm_g, s->D);
     if (!rc) rc = upload_small(l->g_q, r->q_norm_g, s->hd);
     if (!rc) rc = upload_small(l->g_k, r->k_norm_g, s->hd);
+    if (!rc && s->gemma) rc = upload_small(l->g_pre_ff, r->pre_ff_norm_g, s->D);
+    if (!rc && s->gemma) rc = upload_small(l->g_post_ff, r->post_ff_norm_g, s->D);
     if (rc) return rc;
 
     /* 1 / pow(theta, 2d/hd) as the shader computes it per element (q8_kernels.metal:531) */
@@ -584,8 +596,8 @@ static void share_free(SFTState *s)
             LayerW *lw = &s->share_layers[L];
             WMat *ws[] = { lw->q_proj, lw->k_proj, lw->v_proj, lw->o_proj, lw->gate_proj, lw->up_proj, lw->down_proj };
             for (int i = 0; i < 7; ++i) if (ws[i]) { metal_buf_free(ws[i]->mbuf); free(ws[i]); }
-            MetalBuf *gs[] = { lw->input_norm_g, lw->post_attn_norm_g, lw->q_norm_g, lw->k_norm_g };
-            for (int i = 0; i < 4; ++i) metal_buf_free(gs[i]);
+            MetalBuf *gs[] = { lw->input_norm_g, lw->post_attn_norm_g, lw->q_norm_g, lw->k_norm_g, lw->pre_ff_norm_g, lw->post_ff_norm_g };
+            for (int i = 0; i < 6; ++i) metal_buf_free(gs[i]);
         }
         free(s->share_layers);
         s->share_layers = NULL;
@@ -650,6 +662,10 @@ LayerW *sft_get_layers(SFTState *s)
         lw->post_attn_norm_g = llmb200_buf_wrap(l->g_post, (size_t)s->D * 4);
         lw->q_norm_g = llmb200_buf_wrap(l->g_q, (size_t)s->hd * 4);
         lw->k_norm_g = llmb200_buf_wrap(l->g_k, (size_t)s->hd * 4);
+        if (s->gemma) {
+            lw->pre_ff_norm_g = llmb200_buf_wrap(l->g_pre_ff, (size_t)s->D * 4);
+            lw->post_ff_norm_g = llmb200_buf_wrap(l->g_post_ff, (size_t)s->D * 4);
+        }
         if (!lw->q_proj || !lw->k_proj || !lw->v_proj || !lw->o_proj || !lw->gate_proj || !lw->up_proj || !lw->down_proj ||
             !lw->input_norm_g || !lw->post_attn_norm_g || !lw->q_norm_g || !lw->k_norm_g) {
             share_free(s);
@@ -691,7 +707,7 @@ void sft_state_free(SFTState *s)
         SftLayer *l = &s->layers[L];
         mat_free(&l->qkv); mat_free(&l->o); mat_free(&l->gu); mat_free(&l->down);
         float *bufs[] = { l->g_in, l->g_post, l->g_q, l->g_k, l->inv_freq, l->x_in, l->ln1, l->qkv_out, l->q_f, l->k_f,
-                          l->probs, l->x_mid, l->ln2, l->gu_out };
+                          l->probs, l->x_mid, l->ln2, l->gu_out, l->g_pre_ff, l->g_post_ff, l->o_out, l->ff_raw };
         for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) cudaFree(bufs[i]);
         for (int i = 0; i < 4; ++i) metal_buf_free(l->lora_buf[i]);
         for (int i = 0; i < 4; ++i) cudaFree(l->acc[i]);
@@ -753,6 +769,21 @@ static void forward_device(SFTState *s)
          * the fp32 copy of a tensor nothing else reads (attention output, activation) is not written at all */
         S_TRY(s, b200_attn_train_fwd_h(l->q_f, l->k_f, l->qkv_out + s->Hq_hd + s->Hkv_hd, s->QKVX, s->S, s->N, s->Hq,
                                        s->Hkv, s->hd, attn_scale, l->probs, s->use_tc ? NULL : s->att, s->xh, st));
+        if (s->gemma) {
+            /* Gemma3 (:697-704, :725-738): o -> post-attention norm -> + residual -> pre-FFN norm -> GeGLU FFN ->
+             * post-FFN norm -> + residual; the raw projection outputs are saved for the backward pass. dx is free here. */
+            const size_t md = (size_t)M * s->D;
+            gemm_fwd(s, s->att, &l->o, l->o_out, NULL);
+            S_TRY(s, b200_rms_norm_rows(l->o_out, l->g_post, s->dx, M, s->D, s->eps, st));
+            S_TRY(s, b200_add(l->x_in, s->dx, l->x_mid, md, st));
+            S_TRY(s, b200_rms_norm_rows(l->x_mid, l->g_pre_ff, l->ln2, M, s->D, s->eps, st));
+            gemm_fwd(s, l->ln2, &l->gu, l->gu_out, NULL);
+            S_TRY(s, b200_gelu_mul_rows(l->gu_out, M, s->IS, s->act, st));
+            gemm_fwd(s, s->act, &l->down, l->ff_raw, NULL);
+            S_TRY(s, b200_rms_norm_rows(l->ff_raw, l->g_post_ff, s->dx, M, s->D, s->eps, st));
+            S_TRY(s, b200_add(l->x_mid, s->dx, layer_out(s, L), md, st));
+            continue;
+        }
         gemm_fwd(s, s->use_tc ? NULL : s->att, &l->o, l->x_mid, l->x_in);    /* + residual (:686) */
         S_TRY(s, b200_rms_norm_rows_h(l->x_mid, l->g_post, l->ln2, s->xh, M, s->D, s->eps, st));
         gemm_fwd(s, s->use_tc ? NULL : l->ln2, &l->gu, l->gu_out, NULL);
@@ -818,6 +849,24 @@ static void backward_device(SFTState *s)
         float *pA_v = s->lora_p + l->lora_off + s->sub_off[2], *pB_v = s->lora_p + l->lora_off + s->sub_off[3];
         float *gA_q = s->lora_g + l->lora_off + s->sub_off[0], *gB_q = s->lora_g + l->lora_off + s->sub_off[1];
         float *gA_v = s->lora_g + l->lora_off + s->sub_off[2], *gB_v = s->lora_g + l->lora_off + s->sub_off[3];
+        const float *d_o = s->dx;          /* the gradient that enters the o projection: dx, or (Gemma3) dx through the post-attention norm */
+        if (s->gemma) {
+            /* FFN, Gemma3 (:797-838): post-FFN norm, down, GeGLU, gate/up, pre-FFN norm; dx gains the result */
+            S_TRY(s, b200_rms_norm_bwd_rows(l->ff_raw, s->dx, s->D, l->g_post_ff, s->d_ln, M, s->D, s->eps, 0, 0.f, st));
+            gemm_bwd(s, s->d_ln, &l->down, s->d_act);
+            if (s->full_param && s->wmode) {
+                S_TRY(s, b200_gelu_mul_rows(l->gu_out, M, s->IS, s->act, st));
+                weight_step(s, &l->down, l->acc[3], s->D, s->d_ln, s->D, s->act, s->IS);
+            }
+            S_TRY(s, b200_gelu_mul_bwd_rows(s->d_act, l->gu_out, M, s->IS, s->d_gu, st));
+            gemm_bwd(s, s->d_gu, &l->gu, s->d_ln);
+            weight_step(s, &l->gu, l->acc[2], 2 * s->IS, s->d_gu, 2 * s->IS, l->ln2, s->D);
+            S_TRY(s, b200_rms_norm_bwd_rows(l->x_mid, s->d_ln, s->D, l->g_pre_ff, s->dx, M, s->D, s->eps, 1, 0.f, st));
+            /* attention, Gemma3 (:875-888): through the post-attention norm first */
+            S_TRY(s, b200_rms_norm_bwd_rows(l->o_out, s->dx, s->D, l->g_post, s->d_ln, M, s->D, s->eps, 0, 0.f, st));
+            d_o = s->d_ln;
+            goto attention;
+        }
         /* FFN (:841-872) */
         gemm_bwd(s, s->use_tc ? NULL : s->dx, &l->down, s->d_act);           /* dx is in xh already */
         if (s->full_param && s->wmode) {
@@ -830,13 +879,14 @@ static void backward_device(SFTState *s)
         weight_step(s, &l->gu, l->acc[2], 2 * s->IS, s->d_gu, 2 * s->IS, l->ln2, s->D);      /* gate and up rows (:853-868) */
         S_TRY(s, b200_rms_norm_bwd_rows_h(l->x_mid, s->d_ln, s->D, l->g_post, s->dx, M, s->D, s->eps, 1, 0.f, s->xh, hs, st));
         /* attention (:889-918) */
-        gemm_bwd(s, s->use_tc ? NULL : s->dx, &l->o, s->d_att);
+    attention:;
+        gemm_bwd(s, s->use_tc ? NULL : d_o, &l->o, s->d_att);
         const float *v = l->qkv_out + s->Hq_hd + s->Hkv_hd;
         if (s->full_param && s->wmode) {
             /* likewise the attention output, from the saved q, k, v (probs is rewritten with the same values) (:892-899) */
             S_TRY(s, b200_attn_train_fwd_h(l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd, attn_scale, l->probs,
                                            s->att, NULL, st));
-            weight_step(s, &l->o, l->acc[1], s->D, s->dx, s->D, s->att, s->Hq_hd);
+            weight_step(s, &l->o, l->acc[1], s->D, d_o, s->D, s->att, s->Hq_hd);
         }
         S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd,
                                      attn_scale, s->d_score, s->dqkv, QKV, st));
@@ -1035,25 +1085,69 @@ void sft_lora_update(SFTState *s, float lr)
     update_device(s, lr, s->step_count);
 }
 
-/* ---------------------------------------------------------------- modes that are not built */
+/* ---------------------------------------------------------------- Gemma3 and full-parameter modes */
 
-static void not_provided(const char *what)
+/* Gemma3 (src/nn/fast_sft.c:284-396 LoRA, :507-610 full-parameter): four norms per layer, GeGLU, embeddings scaled by
+ * sqrt(d_model), the LM head a binary16 copy of the embedding table, the RoPE base per layer by position in the
+ * stack (every sixth layer global, the others local: :310-313). fp32 path. */
+static SFTState *create_from_gemma3(llmb200_gemma3_model *m, int seq_len, int lora_rank, float lora_alpha, int full_param)
 {
-    fprintf(stderr, "[FastSFT] %s: not provided by libllmb200 (LoRA on Qwen3 is the mode that is built)\n", what);
+    if (!m) return NULL;
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    printf(full_param ? "[FastSFT] Converting Gemma3 weights to F16 (full-param)...\n" : "[FastSFT] Converting Gemma3 weights to F16...\n");
+    llmb200_config cfg = { MODEL_GEMMA3, m->d_model, m->n_q_heads, m->n_kv_heads, m->head_dim, m->intermediate_size,
+                           m->vocab_size, m->n_layers, seq_len, 1 };
+    SFTState *s = sft_begin(&cfg, seq_len, 1, lora_rank, lora_alpha, full_param);
+    if (!s) return NULL;
+    s->step_graph_state = -1;                    /* the fp32 path is launched kernel by kernel */
+    const int Hq_hd = s->Hq_hd, Hkv_hd = s->Hkv_hd;
+    for (int i = 0; i < s->NL; ++i) {
+        llmb200_gemma3_block *b = m->blocks[i];
+        LayerWeightRef r;
+        memset(&r, 0, sizeof(r));
+        r.q_proj = (WeightRef){ b->attn->q_proj->weight->data, Hq_hd, s->D };
+        r.k_proj = (WeightRef){ b->attn->k_proj->weight->data, Hkv_hd, s->D };
+        r.v_proj = (WeightRef){ b->attn->v_proj->weight->data, Hkv_hd, s->D };
+        r.o_proj = (WeightRef){ b->attn->o_proj->weight->data, s->D, Hq_hd };
+        r.gate_proj = (WeightRef){ b->gate_proj->weight->data, s->IS, s->D };
+        r.up_proj = (WeightRef){ b->up_proj->weight->data, s->IS, s->D };
+        r.down_proj = (WeightRef){ b->down_proj->weight->data, s->D, s->IS };
+        r.input_norm_g = b->input_norm->gamma->data;
+        r.post_attn_norm_g = b->post_attn_norm->gamma->data;
+        r.pre_ff_norm_g = b->pre_ff_norm->gamma->data;
+        r.post_ff_norm_g = b->post_ff_norm->gamma->data;
+        r.q_norm_g = b->attn->q_norm->gamma->data;
+        r.k_norm_g = b->attn->k_norm->gamma->data;
+        r.d_model = s->D;
+        r.head_dim = s->hd;
+        const float *lora[4] = { NULL, NULL, NULL, NULL };
+        if (!full_param && m->q_loras && m->q_loras[i]) { lora[0] = m->q_loras[i]->lora_A->data; lora[1] = m->q_loras[i]->lora_B->data; }
+        if (!full_param && m->v_loras && m->v_loras[i]) { lora[2] = m->v_loras[i]->lora_A->data; lora[3] = m->v_loras[i]->lora_B->data; }
+        const float theta = (i % 6) != 0 ? m->local_rope_theta : m->global_rope_theta;
+        if (llmb200_sft_load_layer(s, i, &r, theta, lora) != 0) { sft_state_free(s); return NULL; }
+    }
+    if (llmb200_sft_finish(s, m->token_emb->weight->data, m->final_norm->gamma->data, m->token_emb->weight->data, 1) != 0) {
+        sft_state_free(s);
+        return NULL;
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    const double ms = (t1.tv_sec - t0.tv_sec) * 1000.0 + (t1.tv_nsec - t0.tv_nsec) / 1e6;
+    if (full_param) printf("[FastSFT] Gemma3 Full-param Init: %.0f ms, seq=%d\n", ms, seq_len);
+    else printf("[FastSFT] Gemma3 Init: %.0f ms, seq=%d, lora_rank=%d\n", ms, seq_len, lora_rank);
+    return s;
 }
 
 SFTState *sft_state_create_gemma3(llmb200_gemma3_model *model, int seq_len, int lora_rank, float lora_alpha)
 {
-    (void)model; (void)seq_len; (void)lora_rank; (void)lora_alpha;
-    not_provided("sft_state_create_gemma3");
-    return NULL;
+    return create_from_gemma3(model, seq_len, lora_rank, lora_alpha, 0);
 }
+
 SFTState *sft_state_create_gemma3_full(llmb200_gemma3_model *model, int seq_len)
 {
-    (void)model; (void)seq_len;
-    not_provided("sft_state_create_gemma3_full");
-    return NULL;
+    return create_from_gemma3(model, seq_len, 0, 0.0f, 1);
 }
+
 int sft_is_full_param(SFTState *s) { return s ? s->full_param : 0; }                       /* src/nn/fast_sft.c:987 */
 
 static int full_only(SFTState *s, const char *what)
@@ -1155,8 +1249,6 @@ void sft_save_full_checkpoint(SFTState *s, const char *path)
     fclose(fp);
     printf("[FastSFT] Full checkpoint saved to %s (%.2f MB)\n", path, (float)total / (1024.0f * 1024.0f));
 }
-void sft_sync_lora_to_gemma3(SFTState *s, llmb200_gemma3_model *m) { (void)s; (void)m; not_provided("sft_sync_lora_to_gemma3"); }
-
 /* ---------------------------------------------------------------- accessors */
 
 MetalBuf *sft_get_logits(SFTState *s) { return s ? s->mb_logits : NULL; }
@@ -1246,6 +1338,25 @@ void sft_save_lora(SFTState *s, const char *path)
 void sft_sync_lora_to_model(SFTState *s, llmb200_qwen3_model *m)
 {
     if (!s || !m || !m->q_loras || !m->v_loras) return;
+    float *h = lora_params_host(s);
+    if (!h) return;
+    for (int L = 0; L < s->NL; ++L) {
+        const float *base = h + s->layers[L].lora_off;
+        if (m->q_loras[L]) {
+            memcpy(m->q_loras[L]->lora_A->data, base + s->sub_off[0], s->sizes[0] * 4);
+            memcpy(m->q_loras[L]->lora_B->data, base + s->sub_off[1], s->sizes[1] * 4);
+        }
+        if (m->v_loras[L]) {
+            memcpy(m->v_loras[L]->lora_A->data, base + s->sub_off[2], s->sizes[2] * 4);
+            memcpy(m->v_loras[L]->lora_B->data, base + s->sub_off[3], s->sizes[3] * 4);
+        }
+    }
+    free(h);
+}
+
+void sft_sync_lora_to_gemma3(SFTState *s, llmb200_gemma3_model *m)                          /* src/nn/fast_sft.c:1184-1206 */
+{
+    if (!s || !m || !m->q_loras || !m->v_loras || !s->n_lora) return;
     float *h = lora_params_host(s);
     if (!h) return;
     for (int L = 0; L < s->NL; ++L) {

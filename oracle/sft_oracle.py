@@ -143,6 +143,23 @@ def silu_mul_backward(dy, g, u):
     return dy * u * (sig * (t(1) + g * (t(1) - sig))), dy * (g * sig)
 
 
+def gelu_mul(g, u):
+    """gelu_mul, shaders/q8_kernels.metal:351-363 (Gemma3's GeGLU): tanh form, its argument clamped to +-15."""
+    g = np.asarray(g, dtype=np.float32)
+    inner = np.clip(np.float32(0.7978845608) * (g + np.float32(0.044715) * g * g * g), -15.0, 15.0).astype(np.float32)
+    return (np.float32(0.5) * g * (np.float32(1.0) + np.tanh(inner)) * u).astype(np.float32)
+
+
+def gelu_mul_backward(dy, g, u):
+    """gelu_mul_backward, shaders/q8_kernels.metal:561-580: returns (d_gate, d_up)."""
+    g = np.asarray(g, dtype=np.float32)
+    inner = np.clip(np.float32(0.7978845608) * (g + np.float32(0.044715) * g * g * g), -15.0, 15.0).astype(np.float32)
+    th = np.tanh(inner)
+    gelu_g = np.float32(0.5) * g * (1.0 + th)
+    grad = 0.5 * (1.0 + th) + 0.5 * g * (1.0 - th * th) * np.float32(0.7978845608) * (1.0 + 3.0 * np.float32(0.044715) * g * g)
+    return (dy * u * grad).astype(np.float32), (dy * gelu_g).astype(np.float32)
+
+
 def softmax_ce(logits, targets):
     """softmax_ce_train :646-690: loss = logsumexp - logit[target]; dlogits = softmax - onehot."""
     mx = logits.max(axis=-1, keepdims=True)

@@ -13,7 +13,8 @@
  * step. argv[2] picks the mode: "lora" (default), "full" (grpo_state_create_full: every weight stepped by
  * SGD inside each completion's backward pass) or "full-accurate" (gradients accumulated in binary16 over the
  * group, one step at the end); the full-parameter modes go on with two sft_train_step calls on the same
- * state and record a sample of the saved checkpoint instead of an adapter.
+ * state and record a sample of the saved checkpoint instead of an adapter. "gemma" and "gemma-full" are the
+ * LoRA and the immediate full-parameter mode on a Gemma3 model (grpo_state_create_gemma3 / _gemma3_full).
  * tests/golden/grpo_golden*.bin are the records of grpo_ref; the GPU test compares grpo_b200 with them.
  *
  * Exit codes: 0 ok, 3 the state could not be created (no CUDA device), 1 anything else.
@@ -24,6 +25,7 @@
 #include <string.h>
 
 #include "nn/qwen3.h"
+#include "nn/gemma3.h"
 #include "nn/fast_sft.h"
 #include "nn/fast_grpo.h"
 
@@ -53,17 +55,23 @@ static void section(int kind, const float *v, int n)
 
 int main(int argc, char **argv)
 {
-    if (argc < 2) { fprintf(stderr, "usage: %s <record file> [lora|full|full-accurate] [seed]\n", argv[0]); return 1; }
+    if (argc < 2) { fprintf(stderr, "usage: %s <record file> [lora|full|full-accurate|gemma|gemma-full] [seed]\n", argv[0]); return 1; }
     const char *mode = argc > 2 ? argv[2] : "lora";
-    const int full = strncmp(mode, "full", 4) == 0, accurate = strcmp(mode, "full-accurate") == 0;
+    const int gemma = strncmp(mode, "gemma", 5) == 0;
+    const int full = strncmp(mode, "full", 4) == 0 || strcmp(mode, "gemma-full") == 0, accurate = strcmp(mode, "full-accurate") == 0;
     srand(11);
     Qwen3Config cfg = { .n_layers = 2, .d_model = 256, .n_q_heads = 4, .n_kv_heads = 2, .head_dim = 64,
                         .intermediate_size = 512, .vocab_size = 64, .rope_theta = 1e6f, .rms_norm_eps = 1e-6f };
-    Qwen3Model *model = qwen3_create(cfg);
-    if (!model) return 1;
+    Gemma3Config gcfg = { .n_layers = 2, .d_model = 256, .n_q_heads = 4, .n_kv_heads = 2, .head_dim = 64,
+                          .intermediate_size = 512, .vocab_size = 64, .sliding_window = 512, .local_rope_theta = 1e4f,
+                          .global_rope_theta = 1e6f, .rms_norm_eps = 1e-6f };
+    Qwen3Model *model = gemma ? NULL : qwen3_create(cfg);
+    Gemma3Model *gmodel = gemma ? gemma3_create(gcfg) : NULL;
+    if (!model && !gmodel) return 1;
     GRPOConfig gc = { .group_size = GROUP, .max_gen_len = MAX_GEN, .temperature = 0.7f, .clip_eps = 0.2f,
                       .reward = "combined", .accurate = accurate };
-    GRPOState *g = full ? grpo_state_create_full(model, gc, SEQ, NULL) : grpo_state_create(model, gc, SEQ, RANK, 8.0f, NULL);
+    GRPOState *g = gemma ? (full ? grpo_state_create_gemma3_full(gmodel, gc, SEQ, NULL) : grpo_state_create_gemma3(gmodel, gc, SEQ, RANK, 8.0f, NULL))
+                         : (full ? grpo_state_create_full(model, gc, SEQ, NULL) : grpo_state_create(model, gc, SEQ, RANK, 8.0f, NULL));
     if (!g) return 3;
     out = fopen(argv[1], "wb");
     if (!out) return 1;
@@ -73,7 +81,7 @@ int main(int argc, char **argv)
      * clear of the far tail of the distribution: multinomial sampling is ill-conditioned there -- a draw that
      * lands between two tokens of probability 1e-3 picks the other one at a logit difference far inside the
      * decode path's 1e-2 tolerance (3 of 42 compared steps over seven seeds and three modes did). */
-    srand(argc > 3 ? (unsigned)atoi(argv[3]) : 4u);
+    srand(argc > 3 ? (unsigned)atoi(argv[3]) : gemma ? 13u : 4u);
     uint32_t prompt[PROMPT];
     for (int i = 0; i < PROMPT; ++i) prompt[i] = (uint32_t)(2 + rand() % (cfg.vocab_size - 2));
     float buf[GROUP * MAX_GEN];
@@ -157,7 +165,8 @@ int main(int argc, char **argv)
 
     if (sft_is_full_param(grpo_dbg_sft(g)) != full) { fprintf(stderr, "GRPO_DROP_IN failed: sft_is_full_param\n"); return 1; }
     grpo_state_free(g);
-    qwen3_free(model);
+    if (model) qwen3_free(model);
+    if (gmodel) gemma3_free(gmodel);
     printf("GRPO_DROP_IN ok\n");
     return 0;
 }

@@ -37,7 +37,8 @@ def test_golden_record_exercises_the_step():
     assert all(np.abs(g).max() > 0 for g in steps[1][gr.GRADS])
 
 
-MODES = {"lora": GOLDEN, "full": GOLDEN.replace(".bin", "_full.bin"), "full-accurate": GOLDEN.replace(".bin", "_full_accurate.bin")}
+MODES = {"lora": GOLDEN, "full": GOLDEN.replace(".bin", "_full.bin"), "full-accurate": GOLDEN.replace(".bin", "_full_accurate.bin"),
+         "gemma": GOLDEN.replace(".bin", "_gemma.bin"), "gemma-full": GOLDEN.replace(".bin", "_gemma_full.bin")}
 
 
 @pytest.mark.skipif(not os.path.exists(REF_BIN), reason="tests/c_api/_bin/grpo_ref was not built (reference tree absent)")
@@ -50,23 +51,31 @@ def test_golden_record_is_what_the_reference_run_writes(tmp_path, mode):
     assert open(out, "rb").read() == open(MODES[mode], "rb").read()
 
 
-@pytest.mark.parametrize("mode", ["full", "full-accurate"])
+def test_gemma3_lora_record_exercises_the_step():
+    steps, adapter = gr.by_step(gr.read(MODES["gemma"]))
+    assert len(steps) == gr.STEPS and np.abs(adapter).max() > 0
+    assert all(st[gr.REWARDS].std() > 0 for st in steps)
+    assert all(max(float(np.abs(g).max()) for g in st[gr.GRADS]) > 1e-3 for st in steps)
+    assert (steps[0][gr.TOKENS] != gr.by_step(gr.read(GOLDEN))[0][0][gr.TOKENS]).any()      # another model, another seed
+
+
+@pytest.mark.parametrize("mode", ["full", "full-accurate", "gemma-full"])
 def test_full_parameter_records_exercise_the_step(mode):
     """Full-parameter modes: rewards differ inside the groups, the second step samples from changed weights, the
     two SFT steps on the same batch lower the loss (immediate mode), and the checkpoint has the reference's header."""
     steps, tail = gr.by_step(gr.read(MODES[mode]))
-    lora_steps, _ = gr.by_step(gr.read(GOLDEN))
+    lora_steps, _ = gr.by_step(gr.read(MODES["gemma"] if mode.startswith("gemma") else GOLDEN))
     assert len(steps) == gr.STEPS and all(st[gr.REWARDS].std() > 0 for st in steps)
     assert not steps[0][gr.GRADS]                                          # no adapter, no LoRA gradient buffers
     assert (steps[0][gr.TOKENS] == lora_steps[0][gr.TOKENS]).all()        # first samples: the untouched base model
     assert (steps[1][gr.TOKENS] != lora_steps[1][gr.TOKENS]).any()
     loss = tail[gr.SFT_LOSS]
     assert np.isfinite(loss).all()
-    if mode == "full":
+    if mode != "full-accurate":
         assert loss[1] < loss[0]
     else:
         assert loss[1] == loss[0]          # accumulators allocated: the reference's step accumulates and moves no weight
-    assert tail[gr.CKPT_HEAD].astype(int).tolist() == [0x46554C4C & 0xffffff, 0, 2, 256, 4, 2, 64, 512, 64]
+    assert tail[gr.CKPT_HEAD].astype(int).tolist() == [0x46554C4C & 0xffffff, int(mode.startswith("gemma")), 2, 256, 4, 2, 64, 512, 64]
     n = int(tail[gr.CKPT_SUMS][0])
     assert n == 2 * (512 * 256 + 256 * 256 + 1024 * 256 + 256 * 512) + 64 * 256
     assert len(tail[gr.CKPT_SAMPLE]) == (n + 96) // 97
@@ -108,3 +117,16 @@ def test_cuda_build_of_the_program_fails_loudly_without_a_gpu(tmp_path):
     assert r.returncode == 3, (r.returncode, r.stderr[-500:])
     assert "no CUDA device available" in r.stderr and "no CPU path" in r.stderr
     assert "GRPO_DROP_IN ok" not in r.stdout
+
+
+def test_geglu_restatement_backward_matches_finite_differences():
+    rng = np.random.default_rng(9)
+    g = (rng.standard_normal(200) * 2).astype(np.float32)
+    u = rng.standard_normal(200).astype(np.float32)
+    dy = rng.standard_normal(200).astype(np.float32)
+    dg, du = o.gelu_mul_backward(dy, g, u)
+    h = 1e-3
+    f = lambda gg, uu: o.gelu_mul(gg.astype(np.float32), uu.astype(np.float32)).astype(np.float64)
+    num_g = (f(g + h, u) - f(g - h, u)) / (2 * h) * dy
+    num_u = (f(g, u + h) - f(g, u - h)) / (2 * h) * dy
+    assert np.abs(dg - num_g).max() < 2e-3 and np.abs(du - num_u).max() < 2e-3

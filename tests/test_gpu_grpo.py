@@ -88,11 +88,14 @@ def compare_step(got, want, grad_tol):
 
 
 @pytest.mark.skipif(not os.path.exists(B200_BIN), reason="tests/c_api/_bin/grpo_b200 was not built (reference tree absent)")
-def test_reference_grpo_loop_on_the_cuda_engines_fp32_path(tmp_path):
-    """LLMB200_SFT_TC=0: every product in fp32 on the CUDA cores, as the reference computes. Both steps are
-    compared: the second one generates with the adapter the first one trained."""
-    want, want_adapter = gr.by_step(gr.read(GOLDEN))
-    got, got_adapter = run_program(tmp_path, {"LLMB200_SFT_TC": "0"})
+@pytest.mark.parametrize("mode", ["lora", "gemma"])
+def test_reference_grpo_loop_on_the_cuda_engines_fp32_path(tmp_path, mode):
+    """LLMB200_SFT_TC=0: every product in fp32 on the CUDA cores, as the reference computes (the Gemma3 block
+    order always runs that way). Both steps are compared: the second one generates with the adapter the first one
+    trained. "gemma": grpo_state_create_gemma3 -- four norms per layer, GeGLU, scaled and tied embeddings, a RoPE
+    base per layer."""
+    want, want_adapter = gr.by_step(gr.read(GOLDEN if mode == "lora" else GOLDEN.replace(".bin", "_gemma.bin")))
+    got, got_adapter = run_program(tmp_path, {"LLMB200_SFT_TC": "0"}, mode)
     assert len(got) == len(want) == gr.STEPS
     for g, w in zip(got, want):
         compare_step(g, w, 5e-3)
@@ -134,14 +137,15 @@ def test_sgd_apply_kernel(lib):
 
 
 @pytest.mark.skipif(not os.path.exists(B200_BIN), reason="tests/c_api/_bin/grpo_b200 was not built (reference tree absent)")
-@pytest.mark.parametrize("mode", ["full", "full-accurate"])
+@pytest.mark.parametrize("mode", ["full", "full-accurate", "gemma-full"])
 def test_reference_grpo_loop_full_parameter_modes(tmp_path, mode):
     """grpo_state_create_full: every projection and the LM head stepped by SGD inside the backward passes
     ("full": at once, completion by completion; "full-accurate": accumulated in binary16 over the group, applied
     once), the decode state following the changed weights, then two sft_train_step calls and the checkpoint.
     Tokens must be the reference's in both steps (the second step samples from the stepped weights); the
     checkpoint must hold the reference's binary16 values up to single roundings."""
-    want, want_tail = gr.by_step(gr.read(GOLDEN.replace(".bin", "_full.bin" if mode == "full" else "_full_accurate.bin")))
+    want, want_tail = gr.by_step(gr.read(GOLDEN.replace(".bin", {"full": "_full.bin", "full-accurate": "_full_accurate.bin",
+                                                                 "gemma-full": "_gemma_full.bin"}[mode])))
     got, got_tail = run_program(tmp_path, {}, mode)
     assert len(got) == len(want) == gr.STEPS
     for k, (g, w) in enumerate(zip(got, want)):
@@ -164,3 +168,29 @@ def test_reference_grpo_loop_full_parameter_modes(tmp_path, mode):
     assert (a == b).mean() > 0.9, float((a == b).mean())
     assert got_tail[gr.CKPT_SUMS][0] == want_tail[gr.CKPT_SUMS][0]
     assert abs(float(got_tail[gr.CKPT_SUMS][2]) - float(want_tail[gr.CKPT_SUMS][2])) < 1e-3 * float(want_tail[gr.CKPT_SUMS][2])
+
+
+def test_geglu_and_add_kernels(lib):
+    rng = np.random.default_rng(11)
+    rows, inter = 37, 300
+    gu = (rng.standard_normal((rows, 2 * inter)) * 2).astype(np.float32)
+    gu[0, :4] = [40.0, -40.0, 0.0, 1e-4]                       # the clamp region and the origin
+    dy = rng.standard_normal((rows, inter)).astype(np.float32)
+    g, u = gu[:, :inter], gu[:, inter:]
+    d_gu, d_dy = dev(gu), dev(dy)
+    act = torch.empty(rows, inter, dtype=torch.float32, device="cuda")
+    dgu = torch.empty(rows, 2 * inter, dtype=torch.float32, device="cuda")
+    assert lib.b200_gelu_mul_rows(d_gu.data_ptr(), rows, inter, act.data_ptr(), None) == 0
+    assert lib.b200_gelu_mul_bwd_rows(d_dy.data_ptr(), d_gu.data_ptr(), rows, inter, dgu.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    want = o.gelu_mul(g, u)
+    wg, wu = o.gelu_mul_backward(dy, g, u)
+    assert np.abs(act.cpu().numpy() - want).max() < 1e-5 * max(1.0, np.abs(want).max())
+    got = dgu.cpu().numpy()
+    assert np.abs(got[:, :inter] - wg).max() < 1e-5 * max(1.0, np.abs(wg).max())
+    assert np.abs(got[:, inter:] - wu).max() < 1e-5 * max(1.0, np.abs(wu).max())
+    a, b = rng.standard_normal(1001).astype(np.float32), rng.standard_normal(1001).astype(np.float32)
+    d_a, d_b = dev(a), dev(b)
+    assert lib.b200_add(d_a.data_ptr(), d_b.data_ptr(), d_a.data_ptr(), 1001, None) == 0      # in place
+    torch.cuda.synchronize()
+    assert (d_a.cpu().numpy() == a + b).all()
