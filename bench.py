@@ -1000,19 +1000,24 @@ def nccl_exchange_arm(torch, dist, d_model, per_token, max_over_ranks):
                 dist.all_reduce(x)
         s.synchronize()
         mode = "the calls of one token in a CUDA graph"
+        g, captured = None, 1.0
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=s):
                 for _ in range(per_token):
                     dist.all_reduce(x)
-            run = g.replay
-        except Exception:                                         # capture refused: launch the calls one by one
-            mode = "eager launches (host launch cost included)"
+        except Exception:                                         # capture refused on this rank
+            captured = 0.0
             torch.cuda.synchronize()
+        # every rank must time the same thing: replay only if all of them captured
+        if max_over_ranks(-captured) > -1.0:
+            mode = "eager launches (host launch cost included)"
 
             def run():
                 for _ in range(per_token):
                     dist.all_reduce(x)
+        else:
+            run = g.replay
         reps = 20
         with torch.cuda.stream(s):
             for _ in range(3):

@@ -17,14 +17,27 @@ def oracle_tokens(pkg, synth, sp, model, prompt, n):
     return _oracle.generate(m, prompt, n, want_logits=True)
 
 
-def check_against_oracle(got, ref_tokens, ref_logits):
-    for i, t in enumerate(got):
-        if int(t) == int(ref_tokens[i]):
-            continue
-        top = np.sort(ref_logits[i])[-2:]
-        assert (top[1] - top[0]) < 2e-3 * np.abs(ref_logits[i]).max(), (i, int(t), int(ref_tokens[i]))
-        return i            # after a near-tie flip the continuations differ legitimately
-    return len(got)
+def check_against_oracle(oracle_fn, prompt, got):
+    """Every generated token must be the restatement's choice given the tokens before it, or its runner-up where
+    the two best logits are a near-tie. After such a flip the restatement is run again on the engine's own prefix,
+    so the whole continuation is checked, not only the part before the first flip. Returns the number of flips."""
+    done, flips = 0, 0
+    while done < len(got):
+        ref_tokens, ref_logits = oracle_fn(np.concatenate([prompt, got[:done]]).astype(np.uint32), len(got) - done)
+        for i in range(len(got) - done):
+            t = int(got[done + i])
+            if t == int(ref_tokens[i]):
+                continue
+            order = np.argsort(ref_logits[i])
+            top = ref_logits[i][order[-2:]]
+            assert (top[1] - top[0]) < 2e-3 * np.abs(ref_logits[i]).max(), (done + i, t, int(ref_tokens[i]))
+            assert t == int(order[-2]), (done + i, t, int(order[-2]))         # the runner-up, nothing else
+            flips += 1
+            done += i + 1
+            break
+        else:
+            return flips
+    return flips
 
 
 def test_same_prompt_batch_matches_the_single_sequence_oracle(pkg, lib, synth):
@@ -39,9 +52,8 @@ def test_same_prompt_batch_matches_the_single_sequence_oracle(pkg, lib, synth):
         assert n == G
         for b in range(1, B):
             assert np.array_equal(out[b], out[0])             # same prompt, greedy: identical sequences
-        ref_tokens, ref_logits = oracle_tokens(pkg, synth, sp, model, prompt, G)
-        agreed = check_against_oracle(out[0], ref_tokens, ref_logits)
-        assert agreed >= 8
+        flips = check_against_oracle(lambda pr, n: oracle_tokens(pkg, synth, sp, model, pr, n), prompt, out[0])
+        assert flips <= 2, flips
     finally:
         synth.llmb200_synth_free_qwen3(model)
 
