@@ -110,6 +110,11 @@ struct SFTState {
     unsigned long long step_graph_kernels;
 
     cudaEvent_t ev[4];
+    /* The four LoRA-gradient products of a layer feed nothing before the optimizer: they run on a second stream
+     * beside the rest of the backward pass and are joined before the buffers they read are written again. */
+    cudaStream_t side;
+    cudaEvent_t ev_fork, ev_join;
+    int side_pending;
     float last_step_ms, last_update_ms, last_norm;
 };
 
@@ -403,6 +408,12 @@ static SFTState *sft_begin(const llmb200_config *cfg, int seq_len, int n_seq, in
         s->mb_dlogits = llmb200_buf_wrap(s->dlogits, (size_t)M * s->V * 4);
         for (int i = 0; i < 4; ++i)
             if (cudaEventCreate(&s->ev[i]) != cudaSuccess) s->err = -12;
+        if (!getenv("LLMB200_SFT_NO_OVERLAP") && lora_rank > 0) {
+            if (cudaStreamCreateWithFlags(&s->side, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming) != cudaSuccess)
+                s->err = -13;
+        }
     }
     if (s->err) {
         fprintf(stderr, "[FastSFT] state allocation failed\n");
@@ -724,6 +735,9 @@ void sft_state_free(SFTState *s)
     if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
     share_free(s);
     for (int i = 0; i < 4; ++i) if (s->ev[i]) cudaEventDestroy(s->ev[i]);
+    if (s->ev_fork) cudaEventDestroy(s->ev_fork);
+    if (s->ev_join) cudaEventDestroy(s->ev_join);
+    if (s->side) cudaStreamDestroy(s->side);
     free(s->token_emb_host);
     free(s->rope_thetas);
     free(s->layers);
@@ -888,6 +902,8 @@ static void backward_device(SFTState *s)
                                            s->att, NULL, st));
             weight_step(s, &l->o, l->acc[1], s->D, d_o, s->D, s->att, s->Hq_hd);
         }
+        /* dqkv is about to be rewritten: the LoRA-gradient products of the layer above must have read it */
+        if (s->side_pending) { S_TRY(s, (int)cudaStreamWaitEvent(st, s->ev_join, 0)); s->side_pending = 0; }
         S_TRY(s, b200_attn_train_bwd(s->d_att, l->probs, l->q_f, l->k_f, v, s->QKVX, s->S, s->N, s->Hq, s->Hkv, s->hd,
                                      attn_scale, s->d_score, s->dqkv, QKV, st));
         S_TRY(s, b200_qk_norm_rope_bwd(s->dqkv, l->qkv_out, s->QKVX, QKV, l->g_q, l->g_k, l->inv_freq, M, s->N, s->Hq,
@@ -918,10 +934,19 @@ static void backward_device(SFTState *s)
         if (R == 0) {
             /* full-parameter mode: no adapter */
         } else if (R <= 16) {
-            S_TRY(s, b200_xty_skinny(dq, QKV, l->mid_q, s->QKVX, M, s->Hq_hd, R, sc, gB_q, R, 1, st));
-            S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_q, DX, M, s->D, R, 1.0f, gA_q, 1, s->D, st));
-            S_TRY(s, b200_xty_skinny(dv, QKV, l->mid_v, s->QKVX, M, s->Hkv_hd, R, sc, gB_v, R, 1, st));
-            S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_v, DX, M, s->D, R, 1.0f, gA_v, 1, s->D, st));
+            /* They read dqkv, the saved mid and ln1 of this layer and the tmp columns of d_lnx, none of which
+             * changes before the next layer's attention backward (dqkv) and q/k/v product (d_lnx) -- both after the join. */
+            cudaStream_t xs = st;
+            if (s->side) {
+                S_TRY(s, (int)cudaEventRecord(s->ev_fork, st));
+                S_TRY(s, (int)cudaStreamWaitEvent(s->side, s->ev_fork, 0));
+                xs = s->side;
+            }
+            S_TRY(s, b200_xty_skinny(dq, QKV, l->mid_q, s->QKVX, M, s->Hq_hd, R, sc, gB_q, R, 1, xs));
+            S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_q, DX, M, s->D, R, 1.0f, gA_q, 1, s->D, xs));
+            S_TRY(s, b200_xty_skinny(dv, QKV, l->mid_v, s->QKVX, M, s->Hkv_hd, R, sc, gB_v, R, 1, xs));
+            S_TRY(s, b200_xty_skinny(l->ln1, s->D, tmp_v, DX, M, s->D, R, 1.0f, gA_v, 1, s->D, xs));
+            if (s->side) { S_TRY(s, (int)cudaEventRecord(s->ev_join, s->side)); s->side_pending = 1; }
         } else {
             gemm_small(s, dq, 1, QKV, l->mid_q, s->QKVX, 1, gB_q, R, NULL, s->Hq_hd, R, M, sc);
             gemm_small(s, tmp_q, 1, DX, l->ln1, s->D, 1, gA_q, s->D, NULL, R, s->D, M, 1.0f);
@@ -939,6 +964,8 @@ static void backward_device(SFTState *s)
         /* input norm + residual + clamp (:974-979) */
         S_TRY(s, b200_rms_norm_bwd_rows_h(l->x_in, s->d_lnx, DX, l->g_in, s->dx, M, s->D, s->eps, 1, 1e6f, s->xh, hs, st));
     }
+    /* the gradients of the first layer: whatever follows on the main stream (the optimizer, a read-back) waits for them */
+    if (s->side_pending) { S_TRY(s, (int)cudaStreamWaitEvent(st, s->ev_join, 0)); s->side_pending = 0; }
 }
 
 /* ---------------------------------------------------------------- update */
