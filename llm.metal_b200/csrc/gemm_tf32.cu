@@ -414,6 +414,8 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, EpiArgs e, cudaStream_t
         if (ksub_env < 0 || ksub_env > 4) ksub_env = 0;
     }
     if (ksub_env) e.ksub = ksub_env;
+    // One CTA per SM with a 200 KB ring; two resident CTAs with 100 KB rings each (the epilogue of one under the
+    // mainloop of the other) measured 2.5 % slower on the multi-wave products: the shallower ring costs more.
     while (e.ksub > 1 && (size_t)(BM + e.bn) * BK * 4 * e.ksub * 2 > 200 * 1024) --e.ksub;
     const size_t stage = (size_t)(BM + e.bn) * BK * 4 * e.ksub;
     int stages = (int)((200 * 1024) / stage);
