@@ -56,16 +56,6 @@ struct EpiArgs {
 constexpr int MAX_SPLIT_TILES = 1024;
 __device__ unsigned g_split_flags[MAX_SPLIT_TILES];
 
-// Timeline of CTA (0,0,0) of the last launch, in globaltimer nanoseconds: 0 start, 1 first operands landed,
-// 2 accumulator complete, 3 this CTA's turn to store (split-k), 4 epilogue done. Diagnostics only.
-__device__ unsigned long long g_gemm_trace[8];
-__device__ __forceinline__ unsigned long long now_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
 constexpr int MAX_STAGES = 8;
 
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
@@ -153,10 +143,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int kb0 = blockIdx.z * per_split;
     const int nkb = min(per_split, nkb_all - kb0);               // > 0: the host never launches an empty split
     volatile int *abort_flag = &abort_sh;
-    const bool traced = (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
 
     if (threadIdx.x == 0) {
-        if (traced) g_gemm_trace[0] = now_ns();
         abort_sh = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
@@ -204,7 +192,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (traced && kb == 0) g_gemm_trace[1] = now_ns();
                 const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES * KSUB;
                 for (int u = 0; u < KSUB; ++u) {
                     const uint64_t adesc = smem_desc_sw128(a_addr + u * A_BYTES), bdesc = smem_desc_sw128(b_addr + u * B_BYTES);
@@ -228,7 +215,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (lane == 0 && !*abort_flag) { *abort_flag = 1; if (p.d_err) atomicExch(p.d_err, 0x7103u); }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (traced && threadIdx.x == 64) g_gemm_trace[2] = now_ns();
             // Serial split-k: the CTAs of a tile add their partial sums into C one after the other, in split
             // order (deterministic), handing over through a turn counter. All of them are resident at once
             // (the host keeps tiles * splits <= SMs), so the wait cannot deadlock; it is bounded anyway.
@@ -251,7 +237,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     ok = false;
                 }
             }
-            if (traced && threadIdx.x == 64) g_gemm_trace[3] = now_ns();
             const bool first = split == 0;
             float *crow = p.C + (long long)row * p.ldc;
             // split 0 adds the residual; later splits add what is already in C
@@ -290,7 +275,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
             }
         }
-        if (traced && threadIdx.x == 64) g_gemm_trace[4] = now_ns();
         if (p.splits > 1) {
             // every epilogue warp comes here on every path, so the barrier always has its 128 threads
             named_barrier(1, 128);                              // the four warps have stored their rows
@@ -470,12 +454,3 @@ static int gemm_tc(const b200_gemm_args *a, int f16, void *stream)
 
 extern "C" int b200_gemm_tf32(const b200_gemm_args *a, void *stream) { return gemm_tc(a, 0, stream); }
 extern "C" int b200_gemm_f16(const b200_gemm_args *a, void *stream) { return gemm_tc(a, 1, stream); }
-
-// Diagnostics: the timeline of CTA (0,0,0) of the last launch (see g_gemm_trace). Synchronises the device.
-extern "C" int b200_gemm_tf32_trace(unsigned long long *out8)
-{
-    if (!out8) return B200_E_BADARG;
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out8, g_gemm_trace, 8 * sizeof(unsigned long long));
-    return (int)e;
-}
