@@ -14,7 +14,8 @@
  * SGD inside each completion's backward pass) or "full-accurate" (gradients accumulated in binary16 over the
  * group, one step at the end); the full-parameter modes go on with two sft_train_step calls on the same
  * state and record a sample of the saved checkpoint instead of an adapter. "gemma" and "gemma-full" are the
- * LoRA and the immediate full-parameter mode on a Gemma3 model (grpo_state_create_gemma3 / _gemma3_full).
+ * LoRA and the immediate full-parameter mode on a Gemma3 model (grpo_state_create_gemma3 / _gemma3_full);
+ * "gemma-hd256" is the LoRA mode with Gemma3-1B's head layout (four query heads of 256 on one key/value head).
  * tests/golden/grpo_golden*.bin are the records of grpo_ref; the GPU test compares grpo_b200 with them.
  *
  * Exit codes: 0 ok, 3 the state could not be created (no CUDA device), 1 anything else.
@@ -55,7 +56,7 @@ static void section(int kind, const float *v, int n)
 
 int main(int argc, char **argv)
 {
-    if (argc < 2) { fprintf(stderr, "usage: %s <record file> [lora|full|full-accurate|gemma|gemma-full] [seed]\n", argv[0]); return 1; }
+    if (argc < 2) { fprintf(stderr, "usage: %s <record file> [lora|full|full-accurate|gemma|gemma-full|gemma-hd256] [seed]\n", argv[0]); return 1; }
     const char *mode = argc > 2 ? argv[2] : "lora";
     const int gemma = strncmp(mode, "gemma", 5) == 0;
     const int full = strncmp(mode, "full", 4) == 0 || strcmp(mode, "gemma-full") == 0, accurate = strcmp(mode, "full-accurate") == 0;
@@ -65,6 +66,7 @@ int main(int argc, char **argv)
     Gemma3Config gcfg = { .n_layers = 2, .d_model = 256, .n_q_heads = 4, .n_kv_heads = 2, .head_dim = 64,
                           .intermediate_size = 512, .vocab_size = 64, .sliding_window = 512, .local_rope_theta = 1e4f,
                           .global_rope_theta = 1e6f, .rms_norm_eps = 1e-6f };
+    if (strcmp(mode, "gemma-hd256") == 0) { gcfg.head_dim = 256; gcfg.n_kv_heads = 1; }
     Qwen3Model *model = gemma ? NULL : qwen3_create(cfg);
     Gemma3Model *gmodel = gemma ? gemma3_create(gcfg) : NULL;
     if (!model && !gmodel) return 1;

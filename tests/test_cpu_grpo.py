@@ -38,7 +38,8 @@ def test_golden_record_exercises_the_step():
 
 
 MODES = {"lora": GOLDEN, "full": GOLDEN.replace(".bin", "_full.bin"), "full-accurate": GOLDEN.replace(".bin", "_full_accurate.bin"),
-         "gemma": GOLDEN.replace(".bin", "_gemma.bin"), "gemma-full": GOLDEN.replace(".bin", "_gemma_full.bin")}
+         "gemma": GOLDEN.replace(".bin", "_gemma.bin"), "gemma-full": GOLDEN.replace(".bin", "_gemma_full.bin"),
+         "gemma-hd256": GOLDEN.replace(".bin", "_gemma_hd256.bin")}
 
 
 @pytest.mark.skipif(not os.path.exists(REF_BIN), reason="tests/c_api/_bin/grpo_ref was not built (reference tree absent)")
@@ -51,8 +52,9 @@ def test_golden_record_is_what_the_reference_run_writes(tmp_path, mode):
     assert open(out, "rb").read() == open(MODES[mode], "rb").read()
 
 
-def test_gemma3_lora_record_exercises_the_step():
-    steps, adapter = gr.by_step(gr.read(MODES["gemma"]))
+@pytest.mark.parametrize("mode", ["gemma", "gemma-hd256"])
+def test_gemma3_lora_record_exercises_the_step(mode):
+    steps, adapter = gr.by_step(gr.read(MODES[mode]))
     assert len(steps) == gr.STEPS and np.abs(adapter).max() > 0
     assert all(st[gr.REWARDS].std() > 0 for st in steps)
     assert all(max(float(np.abs(g).max()) for g in st[gr.GRADS]) > 1e-3 for st in steps)

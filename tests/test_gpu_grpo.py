@@ -88,13 +88,14 @@ def compare_step(got, want, grad_tol):
 
 
 @pytest.mark.skipif(not os.path.exists(B200_BIN), reason="tests/c_api/_bin/grpo_b200 was not built (reference tree absent)")
-@pytest.mark.parametrize("mode", ["lora", "gemma"])
+@pytest.mark.parametrize("mode", ["lora", "gemma", "gemma-hd256"])
 def test_reference_grpo_loop_on_the_cuda_engines_fp32_path(tmp_path, mode):
     """LLMB200_SFT_TC=0: every product in fp32 on the CUDA cores, as the reference computes (the Gemma3 block
     order always runs that way). Both steps are compared: the second one generates with the adapter the first one
     trained. "gemma": grpo_state_create_gemma3 -- four norms per layer, GeGLU, scaled and tied embeddings, a RoPE
-    base per layer."""
-    want, want_adapter = gr.by_step(gr.read(GOLDEN if mode == "lora" else GOLDEN.replace(".bin", "_gemma.bin")))
+    base per layer; "gemma-hd256": the same with Gemma3-1B's head layout, four query heads of 256 on one key/value head."""
+    want, want_adapter = gr.by_step(gr.read(GOLDEN.replace(".bin", {"lora": ".bin", "gemma": "_gemma.bin",
+                                                                    "gemma-hd256": "_gemma_hd256.bin"}[mode])))
     got, got_adapter = run_program(tmp_path, {"LLMB200_SFT_TC": "0"}, mode)
     assert len(got) == len(want) == gr.STEPS
     for g, w in zip(got, want):
