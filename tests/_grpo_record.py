@@ -18,19 +18,17 @@ def read(path):
 
 
 def by_step(sections):
-    """-> (steps, tail): steps[k] maps kind -> array (GRADS: the list of all gradient buffers in order); tail is
-    the adapter (LoRA mode) or a dict of the sections written after the last step (full-parameter modes)."""
-    steps, cur, adapter, tail = [], None, None, {}
+    """-> (steps, tail): steps[k] maps kind -> array (GRADS: the list of all gradient buffers in order); tail maps
+    the kinds written after the last step (SFT_LOSS, then ADAPTER or the CKPT_* sections) to their arrays."""
+    steps, cur, tail = [], None, {}
     for kind, v in sections:
         if kind == REWARD:
             cur = {GRADS: []}
             steps.append(cur)
-        if kind == ADAPTER:
-            adapter = v
-        elif kind >= SFT_LOSS:
+        if kind >= ADAPTER:
             tail[kind] = v
         elif kind == GRADS:
             cur[GRADS].append(v)
         else:
             cur[kind] = v
-    return steps, (adapter if adapter is not None else tail)
+    return steps, tail

@@ -9,8 +9,8 @@
  *     _bin/grpo_ref    the reference's own engines over the CPU stand-in for its Metal layer
  *
  * Both write the same record file (argv[1]): per step the sampled tokens, their log-probabilities,
- * rewards, advantages and the LoRA gradients summed over the group, then the adapter after the last
- * step. argv[2] picks the mode: "lora" (default), "full" (grpo_state_create_full: every weight stepped by
+ * rewards, advantages and the LoRA gradients summed over the group; then the losses of two plain
+ * sft_train_step calls on the same state and the adapter after them. argv[2] picks the mode: "lora" (default), "full" (grpo_state_create_full: every weight stepped by
  * SGD inside each completion's backward pass) or "full-accurate" (gradients accumulated in binary16 over the
  * group, one step at the end); the full-parameter modes go on with two sft_train_step calls on the same
  * state and record a sample of the saved checkpoint instead of an adapter. "gemma" and "gemma-full" are the
@@ -115,7 +115,15 @@ int main(int argc, char **argv)
 
     char path[512];
     if (!full) {
-        /* the adapter as the reference saves it (12-byte header, then the matrices) */
+        /* two plain LoRA-SFT steps on the same state (sft_train_step: embedding gather with the model's embedding
+         * scale, loss, backward, clip + AdamW), then the adapter as the reference saves it (12-byte header, matrices) */
+        SFTState *sft = grpo_dbg_sft(g);
+        uint32_t in[SEQ], tg[SEQ];
+        const int V = gemma ? gcfg.vocab_size : cfg.vocab_size;
+        for (int i = 0; i < SEQ; ++i) { in[i] = (uint32_t)(rand() % V); tg[i] = (uint32_t)(rand() % V); }
+        float loss[2];
+        for (int k = 0; k < 2; ++k) loss[k] = sft_train_step(sft, in, tg, 1e-3f);
+        section(K_SFT_LOSS, loss, 2);
         snprintf(path, sizeof path, "%s.lora", argv[1]);
         grpo_save_lora(g, path);
         FILE *fp = fopen(path, "rb");

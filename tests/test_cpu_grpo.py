@@ -20,8 +20,10 @@ B200_BIN = os.path.join(ROOT, "tests", "c_api", "_bin", "grpo_b200")
 
 
 def test_golden_record_exercises_the_step():
-    steps, adapter = gr.by_step(gr.read(GOLDEN))
-    assert len(steps) == gr.STEPS and adapter is not None and np.abs(adapter).max() > 0
+    steps, tail = gr.by_step(gr.read(GOLDEN))
+    adapter, loss = tail[gr.ADAPTER], tail[gr.SFT_LOSS]
+    assert len(steps) == gr.STEPS and np.abs(adapter).max() > 0
+    assert np.isfinite(loss).all() and loss[1] < loss[0]       # two LoRA-SFT steps on one batch after the GRPO steps
     for st in steps:
         assert st[gr.REWARDS].std() > 0, "equal rewards give zero advantages and an all-zero gradient"
         assert abs(float(st[gr.ADVANTAGES].mean())) < 1e-5
@@ -54,8 +56,9 @@ def test_golden_record_is_what_the_reference_run_writes(tmp_path, mode):
 
 @pytest.mark.parametrize("mode", ["gemma", "gemma-hd256"])
 def test_gemma3_lora_record_exercises_the_step(mode):
-    steps, adapter = gr.by_step(gr.read(MODES[mode]))
-    assert len(steps) == gr.STEPS and np.abs(adapter).max() > 0
+    steps, tail = gr.by_step(gr.read(MODES[mode]))
+    assert len(steps) == gr.STEPS and np.abs(tail[gr.ADAPTER]).max() > 0
+    assert np.isfinite(tail[gr.SFT_LOSS]).all() and tail[gr.SFT_LOSS][1] < tail[gr.SFT_LOSS][0]
     assert all(st[gr.REWARDS].std() > 0 for st in steps)
     assert all(max(float(np.abs(g).max()) for g in st[gr.GRADS]) > 1e-3 for st in steps)
     assert (steps[0][gr.TOKENS] != gr.by_step(gr.read(GOLDEN))[0][0][gr.TOKENS]).any()      # another model, another seed
