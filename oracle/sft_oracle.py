@@ -7,12 +7,20 @@ sft_apply_ce_loss :754-760, sft_backward_ex :766-982 LoRA branch, clip_grad_norm
 adamw_update :1045-1058, lora_update :1090-1107, sft_train_step :1113-1157, sft_save_lora :1255-1285)
 with the per-kernel arithmetic of shaders/q8_kernels.metal (line numbers at each function).
 
+It also restates the Gemma3 block order of the same functions (four norms per layer, GeGLU, scaled and tied
+embeddings, a RoPE base per layer: the is_gemma3 branches of :697-738 and :797-888), the full-parameter mode (every
+matrix stepped inside the backward pass, or accumulated and applied: :778-785 and the like, :996-1039) and the
+GRPO step's policy-gradient kernel.
+
 Parity status: PINNED. The reference's own fast_sft.c, compiled unmodified over a CPU stand-in for its
 Metal dispatch layer (oracle/fast_metal_cpu.c -> oracle/_ref/libllmref_fast.so), produced
 tests/golden/sft_golden.npz (tests/golden/make_sft_golden.py): three training steps on the tiny Qwen3
 configuration. tests/test_cpu_pinned_by_reference_engines.py holds this file to those vectors within 1e-5
 (loss, per-position losses, all 4*L gradient buffers of every step, the weights and the adapter file after
-the third). Independent cross-checks remain: a float64 torch-autograd model of the same network, finite
+the third). The same file holds the Gemma3 branch to tests/golden/sft_golden_gemma3.npz (three steps of
+sft_state_create_gemma3 + sft_train_step, 1e-5 on everything) and the full-parameter mode to
+tests/golden/sft_golden_full.npz (losses 1e-5; more than 99.5 % of the sampled binary16 weights bit-equal after
+three stepping calls, and after two accumulating calls and one apply). Independent cross-checks remain: a float64 torch-autograd model of the same network, finite
 differences, and the decode oracle's logits for the forward half.
 
 `dtype` selects float32 (as the reference computes) or float64 (to separate rounding from logic).
@@ -196,95 +204,202 @@ def grpo_policy_grad(logits, actions, old_logprobs, advantages, clip_eps):
     return new_lp, ((weight * ratio)[:, None] * prob).astype(np.float32)
 
 
+def layer_theta(c, L):
+    """RoPE base of layer L: one for all (Qwen3) or per layer (Gemma3: every sixth layer global, :310-313)."""
+    return c["rope_thetas"][L] if "rope_thetas" in c else c["rope_theta"]
+
+
 def forward(w, lora, tokens, dtype=np.float32):
     """forward_to_logits (fast_sft.c:616-752) after the embedding gather of sft_train_step (:1118-1120).
     Returns (logits [N,V], saves)."""
     c, t = w.cfg, dtype
     D, Hq, Hkv, hd = c["d_model"], c["n_q_heads"], c["n_kv_heads"], c["head_dim"]
-    eps, sc = c["eps"], t(lora.scaling)
+    eps = c["eps"]
+    gemma = bool(c.get("gemma"))          # Gemma3 block order (:697-704, :716-738); lora None: a full-parameter state
+    sc = t(lora.scaling) if lora is not None else t(0)
     G = Hq // Hkv
     n = len(tokens)
     scale = np.float32(1.0) / np.sqrt(np.float32(hd))
     x = w.token_emb[np.asarray(tokens, dtype=np.int64)].astype(t)
+    if gemma:
+        x = x * t(np.sqrt(np.float32(D)))                                        # emb_scale (:302, :1124-1126)
     saves = []
     for L, lw in enumerate(w.layers):
-        lp = {k: v.astype(t) for k, v in lora.p[L].items()}
         W = {k: v.astype(t) for k, v in lw.items()}
         sv = {"x_in": x}
         ln1 = rms_norm(x, W["input_norm"], eps)
         sv["ln1"] = ln1
-        q_mid = ln1 @ lp["A_q"].T
-        q = ln1 @ W["q"].T + sc * (q_mid @ lp["B_q"].T)
-        k = ln1 @ W["k"].T
-        v_mid = ln1 @ lp["A_v"].T
-        v = ln1 @ W["v"].T + sc * (v_mid @ lp["B_v"].T)
-        sv["q_mid"], sv["v_mid"] = q_mid, v_mid
+        q, k, v = ln1 @ W["q"].T, ln1 @ W["k"].T, ln1 @ W["v"].T
+        if lora is not None:
+            lp = {k_: v_.astype(t) for k_, v_ in lora.p[L].items()}
+            q_mid, v_mid = ln1 @ lp["A_q"].T, ln1 @ lp["A_v"].T
+            q = q + sc * (q_mid @ lp["B_q"].T)
+            v = v + sc * (v_mid @ lp["B_v"].T)
+            sv["q_mid"], sv["v_mid"] = q_mid, v_mid
         q_t, k_t, v_t = heads_fwd(q, Hq, hd), heads_fwd(k, Hkv, hd), heads_fwd(v, Hkv, hd)
         sv["q_pre"], sv["k_pre"] = q_t, k_t
-        cos, sin = rope_angles(n, hd, c["rope_theta"], t)
+        cos, sin = rope_angles(n, hd, layer_theta(c, L), t)
         q_f = rope(rms_norm(q_t, W["q_norm"], eps), cos, sin)
         k_f = rope(rms_norm(k_t, W["k_norm"], eps), cos, sin)
         k_exp, v_exp = np.repeat(k_f, G, axis=0), np.repeat(v_t, G, axis=0)      # repeat_kv :476-492
         sv["q_final"], sv["k_exp"], sv["v_exp"] = q_f, k_exp, v_exp
         att, probs = attn_fwd(q_f, k_exp, v_exp, scale)
         sv["probs"] = probs
-        x = x + heads_rev(att) @ W["o"].T
-        sv["x_mid"] = x
-        ln2 = rms_norm(x, W["post_attn_norm"], eps)
+        sv["attn_flat"] = heads_rev(att)
+        if gemma:
+            sv["o_out"] = sv["attn_flat"] @ W["o"].T
+            x = x + rms_norm(sv["o_out"], W["post_attn_norm"], eps)
+            sv["x_mid"] = x
+            ln2 = rms_norm(x, W["pre_ff_norm"], eps)
+        else:
+            x = x + sv["attn_flat"] @ W["o"].T
+            sv["x_mid"] = x
+            ln2 = rms_norm(x, W["post_attn_norm"], eps)
         sv["ln2"] = ln2
         g, u = ln2 @ W["gate"].T, ln2 @ W["up"].T
         sv["gate_pre"], sv["up"] = g, u
-        x = x + silu_mul(g, u) @ W["down"].T
+        sv["act"] = gelu_mul(g, u).astype(t) if gemma else silu_mul(g, u)
+        if gemma:
+            sv["ff_raw"] = sv["act"] @ W["down"].T
+            x = x + rms_norm(sv["ff_raw"], W["post_ff_norm"], eps)
+        else:
+            x = x + sv["act"] @ W["down"].T
         saves.append(sv)
     fin = {"x_final": x, "ln_final": rms_norm(x, w.final_norm.astype(t), eps)}
     logits = fin["ln_final"] @ w.lm_head.astype(t).T
     return logits, (saves, fin)
 
 
-def backward(w, lora, saved, dlogits):
-    """sft_backward_ex LoRA branch (fast_sft.c:766-982). Returns per-layer dict of LoRA gradients."""
+class SGD:
+    """What a full-parameter backward pass does with a weight gradient dW = dY^T X (fast_sft.c:778-785 and the
+    like): step the binary16 weight at once, W <- half(W - lr dW) (f16_sgd_fused, q8_kernels.metal:1097-1125), or,
+    once accumulators exist, G <- half(G + dW) (f16_grad_accum, :1164-1191) and leave W alone."""
+
+    def __init__(self, lr, accum=None):
+        self.lr, self.accum = np.float32(lr), accum
+
+    def take(self, holder, key, dY, X, where):
+        dW = (np.asarray(dY, np.float32).T @ np.asarray(X, np.float32)).astype(np.float32)
+        if self.accum is not None:
+            g = self.accum[where]
+            g[key] = f16_round(g[key] + dW)
+        else:
+            holder[key] = f16_round(holder[key] - self.lr * dW)
+
+
+def new_accum(w):
+    """sft_alloc_grad_accum (fast_sft.c:996-1019): zeroed accumulators, one per matrix; index = layer, -1 = LM head."""
+    acc = {L: {k: np.zeros_like(lw[k], dtype=np.float32) for k in ("q", "k", "v", "o", "gate", "up", "down")}
+           for L, lw in enumerate(w.layers)}
+    acc[-1] = {"lm_head": np.zeros_like(w.lm_head, dtype=np.float32)}
+    return acc
+
+
+def apply_accum(w, acc, lr):
+    """sft_apply_grad_sgd (:1021-1039): W <- half(W - lr G), G <- 0."""
+    lr = np.float32(lr)
+    for L, lw in enumerate(w.layers):
+        for k in ("q", "k", "v", "o", "gate", "up", "down"):
+            lw[k] = f16_round(lw[k] - lr * acc[L][k])
+            acc[L][k][...] = 0
+    w.lm_head = f16_round(w.lm_head - lr * acc[-1]["lm_head"])
+    acc[-1]["lm_head"][...] = 0
+
+
+def backward(w, lora, saved, dlogits, sgd=None):
+    """sft_backward_ex (fast_sft.c:766-982). Returns the per-layer dict of LoRA gradients (None entries for a
+    full-parameter state, lora None). With `sgd` (full-parameter mode) every matrix takes its gradient as the
+    pass goes, in the reference's order: the LM head, down, gate, up and o after the product that sends the
+    gradient on through them, q, k and v before it (:922-945) -- w is changed in place."""
     c = w.cfg
     t = dlogits.dtype.type
     Hq, Hkv, hd = c["n_q_heads"], c["n_kv_heads"], c["head_dim"]
-    eps, sc, G = c["eps"], t(lora.scaling), Hq // Hkv
+    eps, G = c["eps"], Hq // Hkv
+    gemma = bool(c.get("gemma"))
+    sc = t(lora.scaling) if lora is not None else t(0)
     n = dlogits.shape[0]
     scale = np.float32(1.0) / np.sqrt(np.float32(hd))
     saves, fin = saved
     dx = dlogits @ w.lm_head.astype(t)                                            # :777
+    if sgd is not None:
+        holder = {"lm_head": w.lm_head}
+        sgd.take(holder, "lm_head", dlogits, fin["ln_final"], -1)
+        w.lm_head = holder["lm_head"]
     dx = rms_norm_backward(fin["x_final"], dx, w.final_norm.astype(t), eps)       # :788-790
     grads = [None] * len(w.layers)
     for L in range(len(w.layers) - 1, -1, -1):
-        W = {k: v.astype(t) for k, v in w.layers[L].items()}
-        lp = {k: v.astype(t) for k, v in lora.p[L].items()}
+        lw = w.layers[L]
+        W = {k: v.astype(t) for k, v in lw.items()}
         sv = saves[L]
-        # FFN (:841-872)
-        d_act = dx @ W["down"]
-        dg, du = silu_mul_backward(d_act, sv["gate_pre"], sv["up"])
-        dln = dg @ W["gate"] + du @ W["up"]
-        dx = dx + rms_norm_backward(sv["x_mid"], dln, W["post_attn_norm"], eps)
-        # attention (:889-918)
-        d_att = heads_fwd(dx @ W["o"], Hq, hd)
+        if gemma:
+            # FFN, Gemma3 (:797-838)
+            dff = rms_norm_backward(sv["ff_raw"], dx, W["post_ff_norm"], eps)
+            d_act = dff @ W["down"]
+            if sgd is not None:
+                sgd.take(lw, "down", dff, sv["act"], L)
+            dg, du = gelu_mul_backward(d_act, sv["gate_pre"], sv["up"])
+            dg, du = dg.astype(t), du.astype(t)
+        else:
+            # FFN (:841-872)
+            d_act = dx @ W["down"]
+            if sgd is not None:
+                sgd.take(lw, "down", dx, sv["act"], L)
+            dg, du = silu_mul_backward(d_act, sv["gate_pre"], sv["up"])
+        dln = dg @ W["gate"]
+        if sgd is not None:
+            sgd.take(lw, "gate", dg, sv["ln2"], L)
+        dln = dln + du @ W["up"]
+        if sgd is not None:
+            sgd.take(lw, "up", du, sv["ln2"], L)
+        dx = dx + rms_norm_backward(sv["x_mid"], dln, W["pre_ff_norm"] if gemma else W["post_attn_norm"], eps)
+        # attention (:875-918)
+        d_o = rms_norm_backward(sv["o_out"], dx, W["post_attn_norm"], eps) if gemma else dx
+        d_att = heads_fwd(d_o @ W["o"], Hq, hd)
+        if sgd is not None:
+            sgd.take(lw, "o", d_o, sv["attn_flat"], L)
         dq, dk_e, dv_e = attn_bwd(d_att, sv["probs"], sv["q_final"], sv["k_exp"], sv["v_exp"], scale)
         dk = dk_e.reshape(Hkv, G, n, hd).sum(axis=1)                              # repeat_kv_bwd :973-992
         dv = dv_e.reshape(Hkv, G, n, hd).sum(axis=1)
-        cos, sin = rope_angles(n, hd, c["rope_theta"], t)
+        cos, sin = rope_angles(n, hd, layer_theta(c, L), t)
         dq = rms_norm_backward(sv["q_pre"], rope(dq, cos, sin, inverse=True), W["q_norm"], eps)
         dk = rms_norm_backward(sv["k_pre"], rope(dk, cos, sin, inverse=True), W["k_norm"], eps)
         dq, dk, dv = heads_rev(dq), heads_rev(dk), heads_rev(dv)
-        # LoRA Q (:946-952), base (:955-958), LoRA V (:961-966), base V (:968-970)
-        g = {}
-        g["B_q"] = (dq.T @ sv["q_mid"]) * sc
-        tmp = (dq @ lp["B_q"]) * sc
-        g["A_q"] = tmp.T @ sv["ln1"]
-        dln = dq @ W["q"] + tmp @ lp["A_q"] + dk @ W["k"]
-        g["B_v"] = (dv.T @ sv["v_mid"]) * sc
-        tmp = (dv @ lp["B_v"]) * sc
-        g["A_v"] = tmp.T @ sv["ln1"]
-        dln = dln + dv @ W["v"] + tmp @ lp["A_v"]
+        if sgd is not None:
+            # q, k, v step first; the gradient then goes on through the stepped matrices (:922-945)
+            sgd.take(lw, "q", dq, sv["ln1"], L)
+            sgd.take(lw, "k", dk, sv["ln1"], L)
+            sgd.take(lw, "v", dv, sv["ln1"], L)
+            W = {k: v.astype(t) for k, v in lw.items()}
+        if lora is None:
+            dln = dq @ W["q"] + dk @ W["k"]
+            dln = dln + dv @ W["v"]
+        else:
+            lp = {k: v.astype(t) for k, v in lora.p[L].items()}
+            # LoRA Q (:946-952), base (:955-958), LoRA V (:961-966), base V (:968-970)
+            g = {}
+            g["B_q"] = (dq.T @ sv["q_mid"]) * sc
+            tmp = (dq @ lp["B_q"]) * sc
+            g["A_q"] = tmp.T @ sv["ln1"]
+            dln = dq @ W["q"] + tmp @ lp["A_q"] + dk @ W["k"]
+            g["B_v"] = (dv.T @ sv["v_mid"]) * sc
+            tmp = (dv @ lp["B_v"]) * sc
+            g["A_v"] = tmp.T @ sv["ln1"]
+            dln = dln + dv @ W["v"] + tmp @ lp["A_v"]
+            grads[L] = g
         dx = dx + rms_norm_backward(sv["x_in"], dln, W["input_norm"], eps)        # :974-976
         dx = np.clip(dx, t(-1e6), t(1e6))                                         # :979
-        grads[L] = g
     return grads
+
+
+def full_train_step(w, inputs, targets, lr, accum=None, dtype=np.float32):
+    """sft_train_step on a full-parameter state (fast_sft.c:1113-1140): forward, loss, and the backward pass that
+    steps (or, with accumulators, accumulates into) every matrix. Returns (mean loss, per-position losses)."""
+    logits, saved = forward(w, None, inputs, dtype)
+    losses, d = softmax_ce(logits, np.asarray(targets, dtype=np.int64))
+    n = len(inputs)
+    d = d * dtype(np.float32(1.0) / np.float32(n))
+    backward(w, None, saved, d, SGD(lr, accum))
+    return float(losses.sum() / dtype(n)), losses
 
 
 def loss_and_grads(w, lora, inputs, targets, dtype=np.float32):

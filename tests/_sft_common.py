@@ -77,6 +77,31 @@ def make_weights(pkg, cfg, seed=1234, gamma_jitter=0.1):
                             else np.ones(D, np.float32)))
 
 
+T_PRE_FF_NORM, T_POST_FF_NORM = 11, 12
+
+
+def gemma_cfg(sp):
+    """Configuration dict of a Gemma3 SynthSpec as the SFT restatement takes it: the RoPE base per layer by
+    position in the stack (src/nn/fast_sft.c:310-313), tied and scaled embeddings."""
+    c = dict(n_layers=sp.n_layers, d_model=sp.d_model, n_q_heads=sp.n_q_heads, n_kv_heads=sp.n_kv_heads,
+             head_dim=sp.head_dim, intermediate_size=sp.intermediate_size, vocab_size=sp.vocab_size, gemma=True)
+    c["rope_thetas"] = [float(sp.local_rope_theta) if (i % 6) != 0 else float(sp.rope_theta) for i in range(sp.n_layers)]
+    c["rope_theta"] = float(sp.rope_theta)
+    return c
+
+
+def make_weights_gemma(pkg, cfg, seed=1234, gamma_jitter=0.1):
+    """The seeded tensors of a synthetic Gemma3 model (llmb200_synth_gemma3) as numpy arrays: the Qwen3 set plus the
+    two feed-forward norms; the LM head is the embedding table."""
+    w = make_weights(pkg, cfg, seed, gamma_jitter)
+    D = cfg["d_model"]
+    for L, l in enumerate(w["layers"]):
+        g = lambda which: normal(pkg, (D,), seed, L, which, 1.0, gamma_jitter) if gamma_jitter else np.ones(D, np.float32)
+        l["pre_ff_norm"], l["post_ff_norm"] = g(T_PRE_FF_NORM), g(T_POST_FF_NORM)
+    w["lm_head"] = w["emb"]
+    return w
+
+
 def make_lora(pkg, cfg, rank, seed=77, b_std=0.0):
     """A ~ N(0, 0.01); B = 0 (the configured start) or N(0, b_std) so that every gradient is non-zero."""
     D, Hq, Hkv, hd = cfg["d_model"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["head_dim"]
@@ -99,7 +124,7 @@ def oracle_model(cfg, w):
     layers = []
     for l in w["layers"]:
         d = {k: o.f16_round(l[k]) for k in ("q", "k", "v", "o", "gate", "up", "down")}
-        d.update({k: l[k] for k in ("input_norm", "post_attn_norm", "q_norm", "k_norm")})
+        d.update({k: l[k] for k in ("input_norm", "post_attn_norm", "q_norm", "k_norm", "pre_ff_norm", "post_ff_norm") if k in l})
         layers.append(d)
     c = dict(cfg)
     c["eps"] = 1e-6
@@ -173,8 +198,9 @@ class Engine:
     def __init__(self, pkg, cfg, w, lora_layers, seq_len, n_seq, rank, alpha, tensor_cores=None):
         self.pkg, self.L, self.cfg = pkg, pkg.lib(), cfg
         self.keep = []
-        c = pkg.Config(pkg.MODEL_QWEN3, cfg["d_model"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["head_dim"],
-                       cfg["intermediate_size"], cfg["vocab_size"], cfg["n_layers"], seq_len, 1)
+        gemma = bool(cfg.get("gemma"))
+        c = pkg.Config(pkg.MODEL_GEMMA3 if gemma else pkg.MODEL_QWEN3, cfg["d_model"], cfg["n_q_heads"], cfg["n_kv_heads"],
+                       cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"], cfg["n_layers"], seq_len, 1)
         if tensor_cores is not None:
             os.environ["LLMB200_SFT_TC"] = "1" if tensor_cores else "0"
         try:
@@ -190,8 +216,11 @@ class Engine:
                 a = np.ascontiguousarray(l[name], dtype=np.float32)
                 self.keep.append(a)
                 setattr(r, name + "_proj", pkg.WeightRef(fptr(a), rows, cols))
-            for name, field in (("input_norm", "input_norm_g"), ("post_attn_norm", "post_attn_norm_g"),
-                                ("q_norm", "q_norm_g"), ("k_norm", "k_norm_g")):
+            norms = [("input_norm", "input_norm_g"), ("post_attn_norm", "post_attn_norm_g"), ("q_norm", "q_norm_g"),
+                     ("k_norm", "k_norm_g")]
+            if gemma:
+                norms += [("pre_ff_norm", "pre_ff_norm_g"), ("post_ff_norm", "post_ff_norm_g")]
+            for name, field in norms:
                 a = np.ascontiguousarray(l[name], dtype=np.float32)
                 self.keep.append(a)
                 setattr(r, field, fptr(a))
@@ -202,7 +231,7 @@ class Engine:
                     a = np.ascontiguousarray(lora_layers[i][k], dtype=np.float32)
                     self.keep.append(a)
                     arr[j] = fptr(a)
-            rc = self.L.llmb200_sft_load_layer(self.h, i, C.byref(r), cfg["rope_theta"],
+            rc = self.L.llmb200_sft_load_layer(self.h, i, C.byref(r), cfg["rope_thetas"][i] if "rope_thetas" in cfg else cfg["rope_theta"],
                                                C.byref(arr) if lora_layers is not None else None)
             assert rc == 0, rc
         lm, fn, emb = (np.ascontiguousarray(w[k], dtype=np.float32) for k in ("lm_head", "final_norm", "emb"))

@@ -1,8 +1,8 @@
-"""Generates tests/golden/sft_golden.npz and tests/golden/fast_decode_golden.npz by running the reference's
+"""Generates tests/golden/sft_golden.npz, sft_golden_gemma3.npz, sft_golden_full.npz and fast_decode_golden.npz by running the reference's
 own fast engines -- src/nn/fast_sft.c and src/nn/fast_inference.c, compiled unmodified into
 oracle/_ref/libllmref_fast.so over a CPU stand-in for their Metal dispatch layer (oracle/fast_metal_cpu.c).
 
-    python tests/golden/make_sft_golden.py        (where the reference tree is mounted)
+    python tests/golden/make_sft_golden.py [lora] [decode] [gemma3] [full]       (where the reference tree is mounted)
 
 sft_golden.npz -- three sft_train_step calls (fast_sft.c:1113-1157) on the tiny Qwen3 configuration
 (hidden 512, 4 layers, 8/2 heads, head_dim 64, ffn 1536, vocab 4096; seeded weights 1234, norm gammas
@@ -141,8 +141,116 @@ def decode_golden(pkg, R):
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def sft_golden_gemma3(pkg, R):
+    """sft_golden_gemma3.npz -- the same three sft_train_step calls on a Gemma3 state (sft_state_create_gemma3,
+    fast_sft.c:284-396): the tiny Gemma3 configuration cut to two layers (hidden 384, four query heads of 256 on
+    one key/value head, ffn 1152, vocab 2048; layer 0 takes the global RoPE base, layer 1 the local one), LoRA
+    rank 4, alpha 8, lr 1e-3, A overwritten with the seeded values as above."""
+    S = pkg.synth()
+    sp = pkg.spec("tiny-gemma3", gamma_jitter=0.1, n_layers=2)
+    cfg = sc.gemma_cfg(sp)
+    model = S.llmb200_synth_gemma3(C.byref(sp), 4)
+    R.sft_state_create_gemma3.restype, R.sft_state_create_gemma3.argtypes = C.c_void_p, [C.c_void_p, C.c_int, C.c_int, C.c_float]
+    st = R.sft_state_create_gemma3(model, N, RANK, ALPHA)
+    assert st
+    shapes = dict(A_q=(RANK, cfg["d_model"]), B_q=(cfg["n_q_heads"] * cfg["head_dim"], RANK),
+                  A_v=(RANK, cfg["d_model"]), B_v=(cfg["n_kv_heads"] * cfg["head_dim"], RANK))
+
+    def weight(L, sub):
+        return np.ctypeslib.as_array(R.metal_buf_ptr(R.sft_get_lora_weight_buf(st, L, sub)), shape=shapes[KEYS[sub]])
+
+    start = sc.make_lora(pkg, cfg, RANK)
+    for L in range(cfg["n_layers"]):
+        for sub, k in enumerate(KEYS):
+            weight(L, sub)[...] = start[L][k]
+    toks = sc.tokens(pkg, N + 1, 4321, cfg["vocab_size"])
+    x, y = np.ascontiguousarray(toks[:-1]), np.ascontiguousarray(toks[1:])
+    out = dict(rank=np.array(RANK), alpha=np.array(ALPHA, np.float32), seq_len=np.array(N), lr=np.array(LR, np.float32),
+               inputs=x, targets=y)
+    for step in range(STEPS):
+        loss = R.sft_train_step(st, x.ctypes.data, y.ctypes.data, LR)
+        out[f"loss_{step}"] = np.array(loss, np.float32)
+        out[f"losses_{step}"] = np.ctypeslib.as_array(R.sft_get_losses_cpu(st), shape=(N,)).copy()
+        for L in range(cfg["n_layers"]):
+            for sub, k in enumerate(KEYS):
+                n = C.c_int(0)
+                p = R.sft_get_lora_grad_ptr(st, 4 * L + sub, C.byref(n))
+                out[f"grad_{step}_{L}_{k}"] = np.ctypeslib.as_array(p, shape=shapes[k]).copy()
+        print(f"gemma3 step {step}: loss {loss:.6f}")
+    for L in range(cfg["n_layers"]):
+        for sub, k in enumerate(KEYS):
+            out[f"weight_{L}_{k}"] = weight(L, sub).copy()
+    R.sft_state_free(st)
+    S.llmb200_synth_free_gemma3(model)
+    path = os.path.join(HERE, "sft_golden_gemma3.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+FULL_STRIDE = 211
+MATS = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+def sft_golden_full(pkg, R):
+    """sft_golden_full.npz -- full-parameter training (sft_state_create_full, fast_sft.c:402-501) on the tiny Qwen3
+    configuration cut to two layers, one sequence of 16 tokens, lr 1e-3. State one: three sft_train_step calls (SGD
+    inside the backward pass). State two: sft_alloc_grad_accum, two sft_train_step calls (which then accumulate),
+    sft_apply_grad_sgd. Kept: the losses of every step and, for both states, every FULL_STRIDE-th element of every
+    matrix after the last call (binary16, in the order q k v o gate up down per layer, then the LM head)."""
+    S = pkg.synth()
+    vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+    R.sft_state_create_full.restype, R.sft_state_create_full.argtypes = vp, [vp, i32]
+    R.sft_get_layers.restype, R.sft_get_layers.argtypes = C.POINTER(pkg.LayerW), [vp]
+    R.sft_get_lm_head.restype, R.sft_get_lm_head.argtypes = C.POINTER(pkg.WMat), [vp]
+    R.sft_alloc_grad_accum.argtypes = [vp]
+    R.sft_apply_grad_sgd.argtypes = [vp, f32]
+    half_p = C.POINTER(C.c_uint16)
+
+    def sample(st, n_layers):
+        lw = R.sft_get_layers(st)
+        parts = []
+        mats = [getattr(lw[L], m).contents for L in range(n_layers) for m in MATS] + [R.sft_get_lm_head(st).contents]
+        for wm in mats:
+            a = np.ctypeslib.as_array(C.cast(R.metal_buf_ptr(wm.mbuf), half_p), shape=(wm.rows * wm.cols,))
+            parts.append(a[::FULL_STRIDE].copy())
+        return np.concatenate(parts).view(np.float16)
+
+    sp = pkg.spec("tiny-qwen3", gamma_jitter=0.1, n_layers=2)
+    toks = sc.tokens(pkg, N + 1, 4321, sp.vocab_size)
+    x, y = np.ascontiguousarray(toks[:-1]), np.ascontiguousarray(toks[1:])
+    out = dict(seq_len=np.array(N), lr=np.array(LR, np.float32), stride=np.array(FULL_STRIDE), inputs=x, targets=y)
+    for tag in ("sgd", "accum"):
+        model = S.llmb200_synth_qwen3(C.byref(sp), 4)
+        st = R.sft_state_create_full(model, N)
+        assert st
+        start = sample(st, sp.n_layers)
+        if tag == "accum":
+            R.sft_alloc_grad_accum(st)
+        losses = []
+        for step in range(3 if tag == "sgd" else 2):
+            losses.append(R.sft_train_step(st, x.ctypes.data, y.ctypes.data, LR))
+            out[f"{tag}_losses_{step}"] = np.ctypeslib.as_array(R.sft_get_losses_cpu(st), shape=(N,)).copy()
+        if tag == "accum":
+            R.sft_apply_grad_sgd(st, LR)
+        out[f"{tag}_loss"] = np.array(losses, np.float32)
+        out[f"{tag}_weights"] = sample(st, sp.n_layers)
+        print(tag, losses, "changed", float((out[f"{tag}_weights"] != start).mean()))
+        R.sft_state_free(st)
+        S.llmb200_synth_free_qwen3(model)
+    path = os.path.join(HERE, "sft_golden_full.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     pkg = entry.load_package()
     R = fast_ref()
-    sft_golden(pkg, R)
-    decode_golden(pkg, R)
+    which = sys.argv[1:] or ["lora", "decode", "gemma3", "full"]
+    if "lora" in which:
+        sft_golden(pkg, R)
+    if "decode" in which:
+        decode_golden(pkg, R)
+    if "gemma3" in which:
+        sft_golden_gemma3(pkg, R)
+    if "full" in which:
+        sft_golden_full(pkg, R)

@@ -430,6 +430,86 @@ def test_engine_against_the_reference_engine_vectors(pkg):
         eng.close()
 
 
+def test_gemma3_engine_against_the_reference_engine_vectors(pkg):
+    """The Gemma3 block order of the engine (fp32 path) against sft_state_create_gemma3 + sft_train_step of the
+    reference (tests/golden/sft_golden_gemma3.npz): two layers, four query heads of 256 on one key/value head, a
+    global and a local RoPE base."""
+    import os
+    G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "sft_golden_gemma3.npz"))
+    sp = pkg.spec("tiny-gemma3", gamma_jitter=0.1, n_layers=2)
+    cfg = sc.gemma_cfg(sp)
+    rank, alpha, lr, n = int(G["rank"]), float(G["alpha"]), float(G["lr"]), int(G["seq_len"])
+    eng = sc.Engine(pkg, cfg, sc.make_weights_gemma(pkg, cfg), sc.make_lora(pkg, cfg, rank), n, 1, rank, alpha)
+    try:
+        for step in range(3):
+            loss = eng.forward_backward(G["inputs"], G["targets"])
+            assert abs(loss - float(G[f"loss_{step}"])) < 1e-4 * abs(loss), (step, loss)
+            assert sc.rel_err(eng.export(sc.LOSSES, 0, n), G[f"losses_{step}"]) < 1e-4
+            got = eng.grads()
+            norm = np.sqrt(sum(float((got[L][k].astype(np.float64) ** 2).sum()) for L in range(cfg["n_layers"]) for k in o.KEYS))
+            scale = 1.0 / norm if norm > 1.0 else 1.0
+            for L in range(cfg["n_layers"]):
+                for k in o.KEYS:
+                    want = G[f"grad_{step}_{L}_{k}"]
+                    if not want.any():
+                        assert not got[L][k].any(), (step, L, k)
+                    else:
+                        assert sc.rel_err(got[L][k] * scale, want) < (1e-4 if step == 0 else 2e-3), (step, L, k)
+            eng.L.llmb200_sft_apply_update(eng.h, lr)
+        got_p = eng.params()
+        for L in range(cfg["n_layers"]):
+            for k in o.KEYS:
+                want = G[f"weight_{L}_{k}"]
+                d = got_p[L][k].astype(np.float64) - want
+                assert np.sqrt((d * d).sum() / (want.astype(np.float64) ** 2).sum()) < 1e-3, (L, k)
+    finally:
+        eng.close()
+
+
+@pytest.mark.parametrize("mode", ["sgd", "accum"])
+def test_full_parameter_engine_against_the_reference_engine_vectors(pkg, lib, synth, mode):
+    """sft_state_create_full through the reference's calls: three sft_train_step calls that step every matrix
+    inside the backward pass, or accumulators, two accumulating steps and one apply
+    (tests/golden/sft_golden_full.npz). Losses to 1e-4; the sampled binary16 weights equal the reference's except
+    for single roundings."""
+    import ctypes as C
+    import os
+    G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "sft_golden_full.npz"))
+    stride, lr, n = int(G["stride"]), float(G["lr"]), int(G["seq_len"])
+    sp = pkg.spec("tiny-qwen3", gamma_jitter=0.1, n_layers=2)
+    model = synth.llmb200_synth_qwen3(C.byref(sp), 4)
+    st = lib.sft_state_create_full(model, n)
+    assert st and lib.sft_is_full_param(st) == 1 and lib.sft_get_lora_rank(st) == 0
+    try:
+        x = np.ascontiguousarray(G["inputs"], dtype=np.uint32)
+        y = np.ascontiguousarray(G["targets"], dtype=np.uint32)
+        if mode == "accum":
+            lib.sft_alloc_grad_accum(st)
+        for step in range(3 if mode == "sgd" else 2):
+            loss = lib.sft_train_step(st, x.ctypes.data_as(pkg.c_u32_p), y.ctypes.data_as(pkg.c_u32_p), lr)
+            assert abs(loss - float(G[f"{mode}_loss"][step])) < 1e-4 * abs(loss), (step, loss)
+            losses = np.ctypeslib.as_array(lib.sft_get_losses_cpu(st), shape=(n,)).copy()
+            assert sc.rel_err(losses, G[f"{mode}_losses_{step}"]) < 1e-4
+        if mode == "accum":
+            lib.sft_apply_grad_sgd(st, lr)
+        lw = C.cast(lib.sft_get_layers(st), C.POINTER(pkg.LayerW))
+        mats = [getattr(lw[L], m).contents for L in range(sp.n_layers)
+                for m in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")]
+        mats.append(C.cast(lib.sft_get_lm_head(st), C.POINTER(pkg.WMat)).contents)
+        parts = []
+        for wm in mats:
+            a = np.ctypeslib.as_array(C.cast(lib.metal_buf_ptr(wm.mbuf), C.POINTER(C.c_uint16)), shape=(wm.rows * wm.cols,))
+            parts.append(a[::stride].copy())
+        got = np.concatenate(parts).view(np.float16).astype(np.float32)
+        want = G[f"{mode}_weights"].astype(np.float32)
+        assert got.shape == want.shape
+        assert (got == want).mean() > 0.97, float((got == want).mean())
+        assert np.abs(got - want).max() <= 2.0 ** -10 * np.abs(want).max()
+    finally:
+        lib.sft_state_free(st)
+        synth.llmb200_synth_free_qwen3(model)
+
+
 def test_saved_activations_and_logits(pkg):
     cfg, n = sc.SMALL, 12
     eng, lora, ow, (x, y) = run_case(pkg, cfg, n, 1, 0.02, False, 1e-4, 1e-4, steps=1)
